@@ -1,0 +1,141 @@
+/*
+ * libbas — batch-shared block-sparse activation GEMM for LLM decoding on NVIDIA B200 (sm_100a).
+ *
+ *   Y[b, n] = sum over active 64-channel blocks j of  X[b, 64j:64j+64] . W[n, 64j:64j+64]
+ *
+ * One mask over 64-channel blocks of the input activation is shared by every row of the decode
+ * batch; only the weight slabs of active blocks are read.  fp16 in, fp32 accumulate, fp16 out.
+ *
+ * This is the C ABI that a binding of the reference's Python operator module
+ * (kernels/shared_mask_batched_triton_min_runtime.py) calls instead of launching Triton kernels.
+ * All pointers named *_dev are device pointers on the current CUDA device, `stream` is a
+ * cudaStream_t passed as void*, and every function returns a bas_status (0 = success).  No entry
+ * point in the "device pointer" group allocates, synchronises or reads device memory on the host,
+ * so all of them may be captured in a CUDA graph after one warm-up call.
+ */
+#ifndef BAS_H_
+#define BAS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BAS_BLOCK_K 64   /* channels per activation block: INDEX_BLOCK_META_SIZE, kernels/...min_runtime.py:17 */
+#define BAS_TILE_N 128   /* output columns per packed weight tile */
+#define BAS_MAX_BLOCKS 4096 /* largest K/64 the kernels accept */
+#define BAS_MAX_BATCH 64 /* largest decode batch of one call */
+
+typedef enum bas_status {
+  BAS_OK = 0,
+  BAS_ERR_INVALID_ARGUMENT = 1, /* null pointer, non-positive size, misaligned pointer or stride */
+  BAS_ERR_UNSUPPORTED = 2,      /* batch > BAS_MAX_BATCH, K/64 > BAS_MAX_BLOCKS, wrong GPU architecture */
+  BAS_ERR_WORKSPACE = 3,        /* workspace missing or smaller than bas_gemm_workspace_bytes() */
+  BAS_ERR_CUDA = 4,             /* a CUDA runtime or driver call failed; see bas_last_cuda_error() */
+  BAS_ERR_DEVICE_FLAG = 5,      /* a kernel reported a bad block id or an expired wait (bas_read_device_status) */
+  BAS_ERR_TOO_LARGE = 6         /* size beyond the fixed capacity of a no-allocation entry point */
+} bas_status;
+
+/* Bits of the device status word (first 4 bytes of every GEMM workspace). */
+#define BAS_DEV_BAD_BLOCK_ID 1u  /* an id outside [0, K/64) was skipped */
+#define BAS_DEV_WAIT_EXPIRED 2u  /* a bounded barrier wait ran out; the output is not valid */
+
+typedef enum bas_score_kind {
+  BAS_SCORE_NORM = 0,  /* mean_b ||x_b,block||_2 : scripts/bench_roundrobin_e2e_decode.py:103-105 */
+  BAS_SCORE_ENERGY = 1 /* mean_b ||x_b,block||^2 : scripts/bench_alpaca_energy_budget_e2e.py:43-46 */
+} bas_score_kind;
+
+const char* bas_status_string(int status);
+/* cudaError_t of the last failing CUDA call made by this library on the calling thread. */
+int bas_last_cuda_error(void);
+/* Number of kernels this library has launched from this process (all threads). */
+unsigned long long bas_launch_count(void);
+
+/* ---- weight prepack -------------------------------------------------------------------------
+ * Replaces _get_prepacked_weight_block_major (kernels/...min_runtime.py:3133-3163): a one-time
+ * repack of an nn.Linear weight W[N, K] (row stride ldw elements).  The reference packs to
+ * [K/64, 64, N]; this library packs to its own tile-major layout [ceil(K/64)][ceil(N/128)][128][64]
+ * with the 128-byte shared-memory swizzle pre-applied, so that every (block, column-tile) pair is
+ * one contiguous 16 KiB chunk.  The packed tensor is opaque to callers, as it is in the reference. */
+size_t bas_packed_weight_bytes(int n, int k);
+int bas_pack_weight(const void* w_dev, int n, int k, int64_t ldw, void* packed_dev, void* stream);
+
+/* ---- the contraction ------------------------------------------------------------------------
+ * Replaces the launch sites of the reference's index-list and bitmap kernels and their split-K
+ * pairs (kernels/...min_runtime.py:1124, :1288, :1310+:1334, :1400, :1417+:1441, :3331).
+ *
+ * The active set is given EITHER as an id list (ids_dev, k_host entries; if count_dev is non-null
+ * the kernel reads the number of entries from device memory instead, k_host being an upper bound)
+ * OR as a byte map (bitmap_dev[K/64], non-zero = active), the form the bitmap kernels consume
+ * (kernels/...min_runtime.py:847).  ids may be unsorted; they must be distinct.  An id outside
+ * [0, ceil(K/64)) is skipped and flagged in the device status word.  An empty set writes zeros
+ * (kernels/...min_runtime.py:1252-1254).
+ *
+ *   x_dev   fp16 [batch, K], row stride ldx elements (16-byte aligned rows)
+ *   y_dev   fp16 [batch, N], row stride ldy elements, fully overwritten
+ *   ws_dev  workspace of at least bas_gemm_workspace_bytes(batch, n) bytes, zero-filled once with
+ *           bas_workspace_init() and then reusable by any number of calls that do not overlap on
+ *           the GPU.  It holds the status word, the per-column-tile arrival counters and the fp32
+ *           partial sums of the split-K combine.
+ * Batches of 1..8 rows run the CUDA-core split-K kernel, 9..64 rows the tcgen05 kernel. */
+size_t bas_gemm_workspace_bytes(int batch, int n);
+int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream);
+int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
+             const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
+             void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, void* stream);
+/* As bas_gemm, with the kernel family forced: 0 = by batch size, 1 = CUDA-core, 2 = tcgen05. */
+int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
+                const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
+                void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int family, void* stream);
+/* Synchronous: copies the status word of a workspace to *flags_out (0 = clean) and clears it. */
+int bas_read_device_status(void* ws_dev, unsigned int* flags_out, void* stream);
+
+/* ---- bitmap ---------------------------------------------------------------------------------
+ * Replaces _build_active_k_bitmap (kernels/...min_runtime.py:1056-1061): u8[nb], 1 at active ids.
+ * count_dev may be null (then k_host ids are used). */
+int bas_build_bitmap(const int32_t* ids_dev, const int32_t* count_dev, int k_host, int nb,
+                     uint8_t* bitmap_dev, void* stream);
+
+/* ---- per-step batch-shared mask selection ---------------------------------------------------
+ * Replaces _select_active_blocks (scripts/bench_roundrobin_e2e_decode.py:90-113) and
+ * _block_energy + _topk_active / _energy_budget_active
+ * (scripts/bench_alpaca_energy_budget_e2e.py:43-62): one launch, no host synchronisation.
+ * Scores are accumulated in fp64 from the exact fp16 inputs; equal scores go to the lower id.
+ *
+ *   ids_out_dev     int32 [>= n_keep] (top-k) or [>= K/64] (budget): ascending active ids
+ *   count_out_dev   int32 [1]: number of ids written
+ *   bitmap_out_dev  optional u8 [K/64]
+ *   scores_out_dev  optional fp64 [K/64]: the batch-mean scores
+ *   ws_dev          at least bas_select_workspace_bytes(K) bytes, zero-filled once with
+ *                   bas_workspace_init()
+ * bas_select_topk keeps n_keep blocks (callers compute n_keep = max(1, min(nb, round(density*nb)))).
+ * bas_select_budget keeps the shortest descending-energy prefix reaching energy_keep of the total,
+ * clamped to [min_keep, nb]. */
+size_t bas_select_workspace_bytes(int k);
+int bas_select_topk(const void* x_dev, int64_t ldx, int batch, int k, int n_keep, int score_kind,
+                    int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
+                    double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream);
+int bas_select_budget(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
+                      int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
+                      double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream);
+
+/* ---- host-buffer operator -------------------------------------------------------------------
+ * The call pattern of _sparse_linear (scripts/bench_roundrobin_e2e_decode.py:179-284) for a caller
+ * whose activations live in host memory: a handle owns the packed weight, the device staging
+ * buffers, a workspace and a stream.  forward copies X host->device, selects the mask on the
+ * device (or takes the caller's ids), runs the contraction, copies Y (and the ids) back and waits.
+ * w_host is fp16 [n, k] row-major.  x_host/y_host are fp16 [batch, k] / [batch, n]. */
+typedef struct bas_linear bas_linear;
+int bas_linear_create(bas_linear** out, const void* w_host, int n, int k, int max_batch);
+int bas_linear_forward_host(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind,
+                            void* y_host, int32_t* ids_host_out);
+int bas_linear_forward_host_ids(bas_linear* h, const void* x_host, int batch, const int32_t* ids_host,
+                                int n_ids, void* y_host);
+void bas_linear_destroy(bas_linear* h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BAS_H_ */

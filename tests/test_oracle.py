@@ -1,0 +1,136 @@
+"""The CPU oracle against the golden vectors recorded from the reference's own code."""
+
+import numpy as np
+import pytest
+
+from oracle import bas_oracle as O
+
+
+def _gap(scores, ids):
+    """Relative gap between the weakest kept and the strongest dropped score."""
+    keep = np.zeros(scores.size, bool)
+    keep[ids] = True
+    if keep.all():
+        return float("inf")
+    lo, hi = scores[keep].min(), scores[~keep].max()
+    return float((lo - hi) / max(abs(lo), 1e-300))
+
+
+def test_selection_norm_matches_reference(golden):
+    data, meta = golden
+    for ci, c in enumerate(meta["select"]):
+        x = O.make_activations(c["batch"], c["k"], c["seed"], c["dist"])
+        s = O.block_scores(x, O.SCORE_NORM)
+        ids = O.topk_ids(s, O.n_keep_from_density(c["density"], s.size))
+        ref = data[f"select{ci}_norm_ids"]
+        assert ids.dtype == np.int32
+        assert np.array_equal(ids, ref), f"case {ci} {c}: threshold gap {_gap(s, ids):.3e}"
+
+
+def test_selection_energy_matches_reference(golden):
+    data, meta = golden
+    for ci, c in enumerate(meta["select"]):
+        x = O.make_activations(c["batch"], c["k"], c["seed"], c["dist"])
+        s = O.block_scores(x, O.SCORE_ENERGY)
+        ids = O.topk_ids(s, O.n_keep_from_density(c["density"], s.size))
+        assert np.array_equal(ids, data[f"select{ci}_energy_ids"]), f"case {ci}: gap {_gap(s, ids):.3e}"
+        # the float64 score is what the reference's float32 evaluation approximates
+        np.testing.assert_allclose(s, data[f"select{ci}_energy_f32"].astype(np.float64), rtol=2e-6)
+
+
+def test_selection_budget_matches_reference(golden):
+    data, meta = golden
+    for ci, c in enumerate(meta["select"]):
+        x = O.make_activations(c["batch"], c["k"], c["seed"], c["dist"])
+        s = O.block_scores(x, O.SCORE_ENERGY)
+        for keep in (0.5, 0.9, 0.99):
+            ids = O.energy_budget_ids(s, keep)
+            ref = data[f"select{ci}_budget{int(round(keep * 100))}_ids"]
+            assert np.array_equal(ids, ref), f"case {ci} keep {keep}: {ids.size} vs {ref.size}"
+
+
+def test_norm_and_energy_select_different_sets(golden):
+    data, _ = golden
+    assert not np.array_equal(data["select0_norm_ids"], data["select0_energy_ids"])
+
+
+def test_n_keep_rule():
+    assert O.n_keep_from_density(0.5, 64) == 32
+    assert O.n_keep_from_density(0.36, 172) == 62
+    assert O.n_keep_from_density(0.0, 64) == 1          # never empty
+    assert O.n_keep_from_density(1.5, 64) == 64
+    assert O.n_keep_from_density(2.5 / 64, 64) == 2     # half-to-even
+    assert O.n_keep_from_density(3.5 / 64, 64) == 4
+
+
+def test_topk_ties_go_to_lower_index():
+    s = np.array([1.0, 3.0, 3.0, 0.5, 3.0])
+    assert O.topk_ids(s, 2).tolist() == [1, 2]
+    assert O.topk_ids(np.zeros(6), 3).tolist() == [0, 1, 2]
+
+
+def test_bitmap_matches_reference(golden):
+    data, meta = golden
+    for bi, c in enumerate(meta["bitmap"]):
+        ids = O.random_active_blocks(c["nb"], c["n_keep"], c["seed"])
+        assert np.array_equal(O.build_bitmap(ids, c["nb"]), data[f"bitmap{bi}"])
+
+
+def test_prepack_matches_reference(golden):
+    data, meta = golden
+    for pi, c in enumerate(meta["prepack"]):
+        w = O.make_weight(c["n"], c["k"], c["seed"])
+        assert np.array_equal(O.pack_weight_block_major(w), data[f"prepack{pi}"])
+
+
+def test_tile_layout_is_a_permutation_of_the_reference_layout():
+    w = O.make_weight(200, 200, 5)
+    tiles = O.pack_weight_tiles(w)                    # [nb, nt, 128, 64] swizzled
+    nb, nt = tiles.shape[:2]
+    assert (nb, nt) == (4, 2)
+    ref = O.pack_weight_block_major(w)                # [nb, 64, N]
+    r = np.arange(128)
+    for q in range(8):
+        chunk = tiles.reshape(nb, nt, 128, 8, 8)[:, :, r, q ^ (r % 8), :]   # logical chunk q
+        for t in range(nt):
+            rows = min(128, 200 - 128 * t)
+            want = ref[:, 8 * q:8 * q + 8, 128 * t:128 * t + rows].transpose(0, 2, 1)
+            assert np.array_equal(chunk[:, t, :rows], want)
+            assert not chunk[:, t, rows:].any()
+
+
+def test_contraction_matches_reference_kernels(golden):
+    data, meta = golden
+    for gi, c in enumerate(meta["gemm"]):
+        nb = (c["k"] + 63) // 64
+        x = O.make_activations(c["batch"], c["k"], c["seed"], c["dist"])
+        w = O.make_weight(c["n"], c["k"], c["seed"], std=0.05)
+        ids = O.random_active_blocks(nb, c["n_keep"], c["seed"])
+        ref = O.masked_gemm(x, w, ids)
+        for name in ("triton_list", "triton_bitmap", "torch_f16"):
+            y = data[f"gemm{gi}_{name}"]
+            assert y.dtype == np.float16 and y.shape == ref.shape
+            assert O.max_err_ratio(y, ref) <= 2e-3, (gi, name)
+        assert O.max_err_ratio(O.masked_gemm_blocks_f32(x, w, ids), ref) <= 1e-5
+
+
+def test_contraction_edge_cases():
+    x = O.make_activations(3, 256, 1)
+    w = O.make_weight(16, 256, 1)
+    assert not O.masked_gemm(x, w, np.zeros(0, np.int32)).any()          # empty mask -> zeros
+    full = O.masked_gemm(x, w, np.arange(4, dtype=np.int32))
+    np.testing.assert_allclose(full, x.astype(np.float64) @ w.astype(np.float64).T, rtol=1e-6)
+    a = O.masked_gemm(x, w, np.array([3, 0], np.int32))                   # order does not matter
+    b = O.masked_gemm(x, w, np.array([0, 3], np.int32))
+    assert np.array_equal(a, b)
+
+
+def test_torch_cpu_legs_agree_with_oracle():
+    torch = pytest.importorskip("torch")
+    x = O.make_activations(16, 4096, 0)
+    w = O.make_weight(512, 4096, 0)
+    ids = O.select_active_blocks(x, 0.5, O.SCORE_NORM)
+    t_ids = O.select_active_blocks_torch_cpu(torch.from_numpy(x).reshape(16, 1, 4096), 0.5, O.SCORE_NORM)
+    assert np.array_equal(ids, t_ids.numpy())
+    y = O.masked_linear_torch_cpu(torch.from_numpy(x), torch.from_numpy(w), ids).numpy()
+    assert O.max_err_ratio(y, O.masked_gemm(x, w, ids)) <= 2e-3
