@@ -19,6 +19,12 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#if defined(__GNUC__)
+#define BAS_API __attribute__((visibility("default")))
+#else
+#define BAS_API
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -47,11 +53,11 @@ typedef enum bas_score_kind {
   BAS_SCORE_ENERGY = 1 /* mean_b ||x_b,block||^2 : scripts/bench_alpaca_energy_budget_e2e.py:43-46 */
 } bas_score_kind;
 
-const char* bas_status_string(int status);
+BAS_API const char* bas_status_string(int status);
 /* cudaError_t of the last failing CUDA call made by this library on the calling thread. */
-int bas_last_cuda_error(void);
+BAS_API int bas_last_cuda_error(void);
 /* Number of kernels this library has launched from this process (all threads). */
-unsigned long long bas_launch_count(void);
+BAS_API unsigned long long bas_launch_count(void);
 
 /* ---- weight prepack -------------------------------------------------------------------------
  * Replaces _get_prepacked_weight_block_major (kernels/...min_runtime.py:3133-3163): a one-time
@@ -59,8 +65,8 @@ unsigned long long bas_launch_count(void);
  * [K/64, 64, N]; this library packs to its own tile-major layout [ceil(K/64)][ceil(N/128)][128][64]
  * with the 128-byte shared-memory swizzle pre-applied, so that every (block, column-tile) pair is
  * one contiguous 16 KiB chunk.  The packed tensor is opaque to callers, as it is in the reference. */
-size_t bas_packed_weight_bytes(int n, int k);
-int bas_pack_weight(const void* w_dev, int n, int k, int64_t ldw, void* packed_dev, void* stream);
+BAS_API size_t bas_packed_weight_bytes(int n, int k);
+BAS_API int bas_pack_weight(const void* w_dev, int n, int k, int64_t ldw, void* packed_dev, void* stream);
 
 /* ---- the contraction ------------------------------------------------------------------------
  * Replaces the launch sites of the reference's index-list and bitmap kernels and their split-K
@@ -80,22 +86,22 @@ int bas_pack_weight(const void* w_dev, int n, int k, int64_t ldw, void* packed_d
  *           the GPU.  It holds the status word, the per-column-tile arrival counters and the fp32
  *           partial sums of the split-K combine.
  * Batches of 1..8 rows run the CUDA-core split-K kernel, 9..64 rows the tcgen05 kernel. */
-size_t bas_gemm_workspace_bytes(int batch, int n);
-int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream);
-int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
+BAS_API size_t bas_gemm_workspace_bytes(int batch, int n);
+BAS_API int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream);
+BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
              const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
              void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, void* stream);
 /* As bas_gemm, with the kernel family forced: 0 = by batch size, 1 = CUDA-core, 2 = tcgen05. */
-int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
+BAS_API int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
                 const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
                 void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int family, void* stream);
 /* Synchronous: copies the status word of a workspace to *flags_out (0 = clean) and clears it. */
-int bas_read_device_status(void* ws_dev, unsigned int* flags_out, void* stream);
+BAS_API int bas_read_device_status(void* ws_dev, unsigned int* flags_out, void* stream);
 
 /* ---- bitmap ---------------------------------------------------------------------------------
  * Replaces _build_active_k_bitmap (kernels/...min_runtime.py:1056-1061): u8[nb], 1 at active ids.
  * count_dev may be null (then k_host ids are used). */
-int bas_build_bitmap(const int32_t* ids_dev, const int32_t* count_dev, int k_host, int nb,
+BAS_API int bas_build_bitmap(const int32_t* ids_dev, const int32_t* count_dev, int k_host, int nb,
                      uint8_t* bitmap_dev, void* stream);
 
 /* ---- per-step batch-shared mask selection ---------------------------------------------------
@@ -113,11 +119,11 @@ int bas_build_bitmap(const int32_t* ids_dev, const int32_t* count_dev, int k_hos
  * bas_select_topk keeps n_keep blocks (callers compute n_keep = max(1, min(nb, round(density*nb)))).
  * bas_select_budget keeps the shortest descending-energy prefix reaching energy_keep of the total,
  * clamped to [min_keep, nb]. */
-size_t bas_select_workspace_bytes(int k);
-int bas_select_topk(const void* x_dev, int64_t ldx, int batch, int k, int n_keep, int score_kind,
+BAS_API size_t bas_select_workspace_bytes(int k);
+BAS_API int bas_select_topk(const void* x_dev, int64_t ldx, int batch, int k, int n_keep, int score_kind,
                     int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
                     double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream);
-int bas_select_budget(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
+BAS_API int bas_select_budget(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
                       int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
                       double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream);
 
@@ -128,12 +134,12 @@ int bas_select_budget(const void* x_dev, int64_t ldx, int batch, int k, double e
  * device (or takes the caller's ids), runs the contraction, copies Y (and the ids) back and waits.
  * w_host is fp16 [n, k] row-major.  x_host/y_host are fp16 [batch, k] / [batch, n]. */
 typedef struct bas_linear bas_linear;
-int bas_linear_create(bas_linear** out, const void* w_host, int n, int k, int max_batch);
-int bas_linear_forward_host(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind,
+BAS_API int bas_linear_create(bas_linear** out, const void* w_host, int n, int k, int max_batch);
+BAS_API int bas_linear_forward_host(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind,
                             void* y_host, int32_t* ids_host_out);
-int bas_linear_forward_host_ids(bas_linear* h, const void* x_host, int batch, const int32_t* ids_host,
+BAS_API int bas_linear_forward_host_ids(bas_linear* h, const void* x_host, int batch, const int32_t* ids_host,
                                 int n_ids, void* y_host);
-void bas_linear_destroy(bas_linear* h);
+BAS_API void bas_linear_destroy(bas_linear* h);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,114 @@
+"""CPU-side checks: the C ABI library loads and exports what include/bas.h declares, the pure
+host functions answer without a GPU, and the host layer refuses CPU tensors (no fallback)."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_symbols():
+    text = (ROOT / "include" / "bas.h").read_text()
+    return sorted(set(re.findall(r"BAS_API[^;(]*?\b(bas_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from bas import abi as L
+
+    declared = _declared_symbols()
+    assert len(declared) >= 18
+    for name in declared:
+        assert hasattr(L.lib, name), f"libbas.so does not export {name}"
+    assert sorted(L.EXPORTED) == [d for d in declared if d in L.EXPORTED]
+    missing_in_binding = [d for d in declared if d not in L.EXPORTED]
+    assert not missing_in_binding, f"ctypes binding lacks {missing_in_binding}"
+
+
+def test_host_only_entry_points():
+    from bas import abi as L
+
+    assert L.lib.bas_status_string(0) == b"ok"
+    assert b"workspace" in L.lib.bas_status_string(3)
+    assert L.lib.bas_packed_weight_bytes(4096, 11008) == 172 * 32 * 16384   # = the fp16 weight size
+    assert L.lib.bas_packed_weight_bytes(96, 200) == 4 * 1 * 16384          # padded to whole tiles
+    assert L.lib.bas_packed_weight_bytes(0, 64) == 0
+    assert L.lib.bas_gemm_workspace_bytes(16, 4096) > 16 * 128 * 4
+    assert L.lib.bas_select_workspace_bytes(11008) >= 256 + 172 * 8
+    assert L.launch_count() >= 0
+
+
+def test_argument_checks_need_no_gpu():
+    from bas import abi as L
+
+    st = L.lib.bas_gemm(None, 64, None, None, None, 0, None, 1, 64, 128, None, 128, None, 0, None)
+    assert st == 1
+    # batch beyond the kernels' limit
+    dummy = ctypes.c_void_p(4096)
+    st = L.lib.bas_gemm(dummy, 64, dummy, dummy, None, 1, None, 65, 64, 128, dummy, 128, dummy, 1 << 30, None)
+    assert st == 2
+    # K not a multiple of 8 cannot be bulk-copied
+    st = L.lib.bas_gemm(dummy, 72, dummy, dummy, None, 1, None, 2, 68, 128, dummy, 128, dummy, 1 << 30, None)
+    assert st == 1
+    with pytest.raises(L.BasError):
+        L.check(3, "x")
+
+
+def test_no_cpu_fallback():
+    torch = pytest.importorskip("torch")
+    from bas import ops
+    import kernels.shared_mask_batched_triton_min_runtime as K
+
+    x = torch.zeros(2, 1, 128, dtype=torch.float16)
+    w = torch.zeros(128, 128, dtype=torch.float16)
+    out = torch.zeros(2, 1, 128, dtype=torch.float16)
+    ids = torch.tensor([0], dtype=torch.int32)
+    with pytest.raises(ValueError):
+        K._prepacked_block_sparse_gemm_from_active_blocks_splitk(x, w, ids, out)
+    with pytest.raises(ValueError):
+        ops.select_topk(x.view(2, 128), 1)
+    # empty active set: zero fill, as the reference does, needs no kernel
+    out.fill_(1)
+    K._prepacked_block_sparse_gemm_from_active_blocks_splitk(x, w, ids[:0], out)
+    assert not out.any()
+
+
+def test_drop_in_module_surface():
+    import inspect
+    import kernels.shared_mask_batched_triton_min_runtime as K
+
+    assert K.INDEX_BLOCK_META_SIZE == 64
+    sig = inspect.signature(K._prepacked_block_sparse_gemm_from_active_blocks_bitmap_preload_splitk)
+    assert list(sig.parameters) == ["x", "weight", "active_blocks", "out", "cache_prefix", "total_k_blocks",
+                                    "prebuilt_bitmap", "num_split_k", "tile_b", "tile_n", "tile_warps", "tile_stages"]
+    sig = inspect.signature(K._prepacked_block_sparse_gemm_from_active_blocks_splitk)
+    assert list(sig.parameters) == ["x", "weight", "active_blocks", "out", "cache_prefix", "num_split_k",
+                                    "tile_b", "tile_n", "tile_warps", "tile_stages"]
+    sig = inspect.signature(K._prepacked_block_sparse_gemm_from_active_blocks)
+    assert list(sig.parameters) == ["x", "weight", "active_blocks", "out", "cache_prefix", "proj_tag",
+                                    "sort_active_blocks", "use_run_compressed", "active_blocks_limit"]
+    cfg = K.prepacked_block_sparse_gemm_bitmap_preload_batched_kernel.best_config
+    assert cfg.kwargs["BLOCK_B"] and cfg.kwargs["BLOCK_N"] and cfg.num_warps and cfg.num_stages
+    assert K._PREPACK_AUTOTUNE_CONFIGS
+
+
+def test_partition_arithmetic_matches_kernel_rules():
+    """The stream-K split used by the kernels: ranges tile the unit list, owners are consistent."""
+    def begin(c, total, g):
+        return c * total // g
+
+    def owner(u, total, g):
+        return ((u + 1) * g - 1) // total
+
+    for total, g in [(1, 148), (147, 148), (148, 148), (1088, 148), (1984, 148), (2656, 148), (5, 3), (7, 192)]:
+        covered = []
+        for c in range(g):
+            lo, hi = begin(c, total, g), begin(c + 1, total, g)
+            assert 0 <= lo <= hi <= total
+            covered += list(range(lo, hi))
+            for u in range(lo, hi):
+                assert owner(u, total, g) == c
+        assert covered == list(range(total))

@@ -1,0 +1,392 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle and the golden
+vectors recorded from the reference.  Bit-exact for ids, bitmaps and the packed layout;
+max|dY| <= 2e-3 * max|Y_ref| for the fp16-in / fp32-accumulate contraction."""
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from oracle import bas_oracle as O  # noqa: E402
+
+TOL = 2e-3   # max|y - ref| / max|ref|, the parity rule of the benchmark specification
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda", 0)
+
+
+def _ops():
+    from bas import ops
+    return ops
+
+
+def _run_gemm(dev, x, w, ids=None, bitmap=None, family=0, count=None, k_host=None):
+    ops = _ops()
+    tx, tw = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
+    packed = ops.pack_weight(tw)
+    out = torch.full((x.shape[0], w.shape[0]), float("nan"), dtype=torch.float16, device=dev)
+    kw = {}
+    if bitmap is not None:
+        kw["bitmap"] = torch.from_numpy(bitmap).to(dev)
+    else:
+        kw["ids"] = torch.from_numpy(np.ascontiguousarray(ids, dtype=np.int32)).to(dev)
+        if count is not None:
+            kw["count"] = torch.tensor([count], dtype=torch.int32, device=dev)
+            kw["k_host"] = k_host
+    ops.gemm(tx, packed, out, family=family, **kw)
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
+    return out.cpu().numpy()
+
+
+# ---------------------------------------------------------------------------------------------
+# prepack
+# ---------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("n,k", [(128, 64), (96, 200), (300, 520), (4096, 4096)])
+def test_pack_is_bit_exact(dev, n, k):
+    w = O.make_weight(n, k, seed=n + k)
+    packed = _ops().pack_weight(torch.from_numpy(w).to(dev)).cpu().numpy()
+    want = O.pack_weight_tiles(w)
+    assert packed.nbytes == want.nbytes
+    assert np.array_equal(packed.view(np.float16).reshape(want.shape), want)
+
+
+def test_pack_accepts_strided_rows(dev):
+    w = O.make_weight(130, 256, seed=3)
+    big = torch.zeros(130, 300, dtype=torch.float16, device=dev)
+    big[:, :256] = torch.from_numpy(w).to(dev)
+    packed = _ops().pack_weight(big[:, :256]).cpu().numpy()
+    assert np.array_equal(packed.view(np.float16).reshape(4, 2, 128, 64), O.pack_weight_tiles(w))
+
+
+# ---------------------------------------------------------------------------------------------
+# contraction
+# ---------------------------------------------------------------------------------------------
+
+SMALL = [(b, 1024, 512, nk) for b in (1, 2, 3, 4, 5, 8, 9, 16, 17, 32, 33, 48, 64) for nk in (1, 7, 16)]
+RAGGED = [(3, 200, 96, 3), (16, 200, 96, 4), (2, 72, 40, 2), (20, 136, 130, 3), (1, 64, 128, 1), (64, 64, 8, 1)]
+LLAMA = [(2, 11008, 4096, 34), (16, 11008, 4096, 62), (64, 11008, 4096, 83), (16, 4096, 4096, 32),
+         (4, 4096, 11008, 13), (32, 4096, 11008, 51), (8, 11008, 4096, 51), (1, 4096, 4096, 64)]
+
+
+@pytest.mark.parametrize("b,k,n,n_keep", SMALL + RAGGED + LLAMA)
+def test_gemm_matches_oracle(dev, b, k, n, n_keep):
+    nb = (k + 63) // 64
+    x = O.make_activations(b, k, seed=b * 1000 + n_keep, dist="laplace" if k == 11008 else "normal")
+    w = O.make_weight(n, k, seed=k + n, std=0.02 if k >= 4096 else 0.05)
+    ids = O.random_active_blocks(nb, min(n_keep, nb), seed=b + k)
+    y = _run_gemm(dev, x, w, ids=ids)
+    ref = O.masked_gemm(x, w, ids)
+    assert np.isfinite(y).all()
+    err = O.max_err_ratio(y, ref)
+    assert err <= TOL, f"B={b} K={k} N={n} keep={n_keep}: err ratio {err:.3e}"
+
+
+@pytest.mark.parametrize("b", [1, 2, 4, 8])
+def test_small_batches_agree_on_both_kernel_families(dev, b):
+    x = O.make_activations(b, 2048, seed=b)
+    w = O.make_weight(640, 2048, seed=9)
+    ids = O.random_active_blocks(32, 11, seed=b)
+    ref = O.masked_gemm(x, w, ids)
+    y1 = _run_gemm(dev, x, w, ids=ids, family=1)
+    y2 = _run_gemm(dev, x, w, ids=ids, family=2)
+    assert O.max_err_ratio(y1, ref) <= TOL and O.max_err_ratio(y2, ref) <= TOL
+    assert O.max_err_ratio(y1, y2.astype(np.float32)) <= 1e-3
+
+
+@pytest.mark.parametrize("b", [2, 16])
+def test_unsorted_ids_and_bitmap_give_the_same_sum(dev, b):
+    x = O.make_activations(b, 4096, seed=5)
+    w = O.make_weight(1024, 4096, seed=5)
+    ids = O.random_active_blocks(64, 20, seed=1)
+    ref = O.masked_gemm(x, w, ids)
+    rng = np.random.default_rng(0)
+    y_sorted = _run_gemm(dev, x, w, ids=ids)
+    y_perm = _run_gemm(dev, x, w, ids=rng.permutation(ids))
+    y_bitmap = _run_gemm(dev, x, w, bitmap=O.build_bitmap(ids, 64))
+    for y in (y_sorted, y_perm, y_bitmap):
+        assert O.max_err_ratio(y, ref) <= TOL
+    assert np.array_equal(y_sorted, y_bitmap)          # same list after compaction -> same bits
+
+
+@pytest.mark.parametrize("b", [2, 16])
+def test_device_side_count_and_empty_set(dev, b):
+    x = O.make_activations(b, 1024, seed=1)
+    w = O.make_weight(256, 1024, seed=1)
+    ids = O.random_active_blocks(16, 9, seed=2)
+    # only the first 5 ids count; the rest of the buffer is ignored
+    y = _run_gemm(dev, x, w, ids=ids, count=5, k_host=9)
+    assert O.max_err_ratio(y, O.masked_gemm(x, w, ids[:5])) <= TOL
+    # device-side count of zero and an all-zero bitmap both write zeros
+    assert not _run_gemm(dev, x, w, ids=ids, count=0, k_host=9).any()
+    assert not _run_gemm(dev, x, w, bitmap=np.zeros(16, np.uint8)).any()
+    # host-side empty list
+    assert not _run_gemm(dev, x, w, ids=ids[:0]).any()
+
+
+@pytest.mark.parametrize("b", [2, 16])
+def test_full_mask_equals_dense(dev, b):
+    x = O.make_activations(b, 4096, seed=11)
+    w = O.make_weight(4096, 4096, seed=11)
+    y = _run_gemm(dev, x, w, ids=np.arange(64, dtype=np.int32))
+    dense = (torch.from_numpy(x).to(dev).float() @ torch.from_numpy(w).to(dev).float().T).cpu().numpy()
+    assert O.max_err_ratio(y, dense) <= TOL
+
+
+@pytest.mark.parametrize("b", [2, 64])
+def test_block_additivity_at_full_size(dev, b):
+    """Y(A u B) = Y(A) + Y(B) for disjoint block sets: a size-independent property checked on the
+    down-projection shape without running the CPU oracle at that size."""
+    x = O.make_activations(b, 11008, seed=21, dist="laplace")
+    w = O.make_weight(4096, 11008, seed=21)
+    ids = O.random_active_blocks(172, 83, seed=3)
+    ya = _run_gemm(dev, x, w, ids=ids[:40]).astype(np.float32)
+    yb = _run_gemm(dev, x, w, ids=ids[40:]).astype(np.float32)
+    yab = _run_gemm(dev, x, w, ids=ids).astype(np.float32)
+    scale = np.abs(yab).max()
+    assert np.abs(ya + yb - yab).max() <= 2e-3 * scale
+
+
+def test_bad_block_id_is_skipped_and_flagged(dev):
+    ops = _ops()
+    x = O.make_activations(2, 1024, seed=1)
+    w = O.make_weight(256, 1024, seed=1)
+    tx, tw = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
+    out = torch.empty(2, 256, dtype=torch.float16, device=dev)
+    ids = torch.tensor([3, 99, 7, -1], dtype=torch.int32, device=dev)
+    ops.gemm(tx, ops.pack_weight(tw), out, ids=ids)
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 1                       # BAS_DEV_BAD_BLOCK_ID
+    assert ops.read_status(dev) == 0                       # reading clears it
+    assert O.max_err_ratio(out.cpu().numpy(), O.masked_gemm(x, w, np.array([3, 7]))) <= TOL
+
+
+@pytest.mark.parametrize("b", [2, 16, 64])
+def test_result_is_deterministic_and_workspace_reusable(dev, b):
+    x = O.make_activations(b, 11008, seed=31, dist="laplace")
+    w = O.make_weight(4096, 11008, seed=31)
+    ids = O.random_active_blocks(172, 62, seed=31)
+    ys = [_run_gemm(dev, x, w, ids=ids) for _ in range(3)]
+    assert np.array_equal(ys[0], ys[1]) and np.array_equal(ys[0], ys[2])
+
+
+def test_gemm_against_reference_kernel_outputs(dev, golden):
+    data, meta = golden
+    for gi, c in enumerate(meta["gemm"]):
+        nb = (c["k"] + 63) // 64
+        x = O.make_activations(c["batch"], c["k"], c["seed"], c["dist"])
+        w = O.make_weight(c["n"], c["k"], c["seed"], std=0.05)
+        ids = O.random_active_blocks(nb, c["n_keep"], c["seed"])
+        if c["k"] % 8:
+            continue
+        y = _run_gemm(dev, x, w, ids=ids)
+        ref = O.masked_gemm(x, w, ids)
+        assert O.max_err_ratio(y, ref) <= TOL
+        for name in ("triton_list", "triton_bitmap", "torch_f16"):
+            assert O.max_err_ratio(y, data[f"gemm{gi}_{name}"].astype(np.float32)) <= 2 * TOL, (gi, name)
+
+
+# ---------------------------------------------------------------------------------------------
+# selection
+# ---------------------------------------------------------------------------------------------
+
+def _select(dev, x, n_keep, kind, want_scores=False):
+    ops = _ops()
+    tx = torch.from_numpy(x).to(dev)
+    nb = x.shape[1] // 64
+    bm = torch.full((nb,), 7, dtype=torch.uint8, device=dev)
+    sc = torch.empty(nb, dtype=torch.float64, device=dev)
+    ids, cnt = ops.select_topk(tx, n_keep, kind, bitmap_out=bm, scores_out=sc)
+    torch.cuda.synchronize()
+    return ids.cpu().numpy(), int(cnt.item()), bm.cpu().numpy(), sc.cpu().numpy()
+
+
+def test_selection_matches_reference_golden(dev, golden):
+    data, meta = golden
+    for ci, c in enumerate(meta["select"]):
+        if c["k"] % 8:
+            continue
+        x = O.make_activations(c["batch"], c["k"], c["seed"], c["dist"])
+        nb = c["k"] // 64
+        n_keep = O.n_keep_from_density(c["density"], nb)
+        for kind, name in ((O.SCORE_NORM, "norm"), (O.SCORE_ENERGY, "energy")):
+            ids, cnt, bm, sc = _select(dev, x, n_keep, kind)
+            ref = data[f"select{ci}_{name}_ids"]
+            assert cnt == n_keep
+            assert np.array_equal(ids, ref), f"case {ci} {name}"
+            assert np.array_equal(bm, O.build_bitmap(ref, nb))
+            np.testing.assert_allclose(sc, O.block_scores(x, kind), rtol=1e-14)
+
+
+@pytest.mark.parametrize("b,k", [(1, 64), (2, 11008), (7, 4096), (64, 11008), (16, 704), (33, 8192)])
+@pytest.mark.parametrize("kind", [0, 1])
+def test_selection_matches_oracle(dev, b, k, kind):
+    x = O.make_activations(b, k, seed=b + k + kind, dist="laplace")
+    nb = k // 64
+    for n_keep in sorted({1, max(1, nb // 3), nb}):
+        ids, cnt, bm, sc = _select(dev, x, n_keep, kind)
+        want = O.topk_ids(O.block_scores(x, kind), n_keep)
+        assert cnt == n_keep and np.array_equal(ids, want)
+        assert bm.sum() == n_keep
+
+
+def test_selection_ties_go_to_lower_index(dev):
+    x = np.zeros((4, 640), np.float16)
+    x[:, 64:128] = 1.0
+    x[:, 320:384] = 1.0
+    x[:, 512:576] = 1.0
+    ids, cnt, _, _ = _select(dev, x, 2, O.SCORE_NORM)
+    assert ids.tolist() == [1, 5]
+    ids, cnt, _, _ = _select(dev, x, 5, O.SCORE_ENERGY)
+    assert ids.tolist() == [0, 1, 2, 5, 8]
+
+
+def test_budget_selection_matches_reference_golden(dev, golden):
+    ops = _ops()
+    data, meta = golden
+    for ci, c in enumerate(meta["select"]):
+        if c["k"] % 8:
+            continue
+        x = O.make_activations(c["batch"], c["k"], c["seed"], c["dist"])
+        tx = torch.from_numpy(x).to(dev)
+        for keep in (0.5, 0.9, 0.99):
+            ids, cnt = ops.select_budget(tx, keep)
+            torch.cuda.synchronize()
+            n = int(cnt.item())
+            ref = data[f"select{ci}_budget{int(round(keep * 100))}_ids"]
+            assert np.array_equal(ids[:n].cpu().numpy(), ref), f"case {ci} keep {keep}"
+
+
+def test_bitmap_builder(dev):
+    ops = _ops()
+    for nb, n_keep, seed in [(64, 32, 0), (172, 62, 1), (172, 0, 2), (7, 7, 3)]:
+        ids = O.random_active_blocks(nb, n_keep, seed)
+        bm = ops.build_bitmap(torch.from_numpy(ids).to(dev), nb, dev)
+        assert np.array_equal(bm.cpu().numpy(), O.build_bitmap(ids, nb))
+
+
+# ---------------------------------------------------------------------------------------------
+# fused select -> GEMM, the drop-in module and the host-buffer operator
+# ---------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("b,density", [(2, 0.197), (16, 0.36), (64, 0.48)])
+def test_sparse_linear_chain(dev, b, density):
+    ops = _ops()
+    k, n = 11008, 4096
+    w = O.make_weight(n, k, seed=77)
+    tw = torch.from_numpy(w).to(dev)
+    for step in range(3):
+        x = O.make_activations(b, k, seed=500 + step, dist="laplace")
+        tx = torch.from_numpy(x).to(dev).reshape(b, 1, k)
+        y = ops.sparse_linear(tx, tw, density, score_kind=O.SCORE_ENERGY)
+        torch.cuda.synchronize()
+        ids = O.select_active_blocks(x, density, O.SCORE_ENERGY)
+        assert y.shape == (b, 1, n)
+        assert O.max_err_ratio(y.reshape(b, n).cpu().numpy(), O.masked_gemm(x, w, ids)) <= TOL
+    assert ops.read_status(dev) == 0
+
+
+def test_drop_in_wrappers_and_graph_capture(dev):
+    import kernels.shared_mask_batched_triton_min_runtime as K
+
+    b, k, n = 16, 4096, 4096
+    x = O.make_activations(b, k, seed=0)
+    w = O.make_weight(n, k, seed=0)
+    ids = O.select_active_blocks(x, 0.5, O.SCORE_NORM)
+    ref = O.masked_gemm(x, w, ids)
+    tx = torch.from_numpy(x).to(dev).reshape(b, 1, k)
+    tw = torch.from_numpy(w).to(dev)
+    tids = torch.from_numpy(ids).to(dev)
+    bitmap = K._build_active_k_bitmap(tids, 64, "cuda")
+    assert np.array_equal(bitmap.cpu().numpy(), O.build_bitmap(ids, 64))
+    K._get_prepacked_weight_block_major(tw, 64, cache_prefix="t")
+
+    calls = {
+        "list": lambda o: K._prepacked_block_sparse_gemm_from_active_blocks_splitk(
+            tx, tw, tids, o, cache_prefix="t", num_split_k=4, tile_b=16, tile_n=64, tile_warps=2, tile_stages=3),
+        "bitmap": lambda o: K._prepacked_block_sparse_gemm_from_active_blocks_bitmap_preload(
+            tx, tw, tids, o, cache_prefix="t", total_k_blocks=64, prebuilt_bitmap=bitmap),
+        "bitmap_sk": lambda o: K._prepacked_block_sparse_gemm_from_active_blocks_bitmap_preload_splitk(
+            tx, tw, tids, o, cache_prefix="t", total_k_blocks=64, prebuilt_bitmap=bitmap, num_split_k=2),
+        "generic": lambda o: K._prepacked_block_sparse_gemm_from_active_blocks(
+            tx, tw, tids, o, cache_prefix="t", use_run_compressed=False),
+    }
+    for name, fn in calls.items():
+        out = torch.zeros(b, 1, n, dtype=torch.float16, device=dev)
+        fn(out)
+        torch.cuda.synchronize()
+        assert O.max_err_ratio(out.reshape(b, n).cpu().numpy(), ref) <= TOL, name
+
+    # the reference's timing protocol: warm up on a side stream, capture one call, replay
+    out = torch.zeros(b, 1, n, dtype=torch.float16, device=dev)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            calls["bitmap"](out)
+        torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        calls["bitmap"](out)
+    out.zero_()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert O.max_err_ratio(out.reshape(b, n).cpu().numpy(), ref) <= TOL
+
+    # empty list -> zeros; active_blocks_limit keeps a prefix
+    out.fill_(1)
+    K._prepacked_block_sparse_gemm_from_active_blocks_splitk(tx, tw, tids[:0], out)
+    assert not out.any()
+    K._prepacked_block_sparse_gemm_from_active_blocks(tx, tw, tids, out, active_blocks_limit=5)
+    torch.cuda.synchronize()
+    assert O.max_err_ratio(out.reshape(b, n).cpu().numpy(), O.masked_gemm(x, w, ids[:5])) <= TOL
+
+
+def test_batches_above_64_rows_are_sliced(dev):
+    import kernels.shared_mask_batched_triton_min_runtime as K
+
+    b, k, n = 100, 1024, 256
+    x = O.make_activations(b, k, seed=4)
+    w = O.make_weight(n, k, seed=4)
+    ids = O.random_active_blocks(16, 6, seed=4)
+    out = torch.zeros(b, 1, n, dtype=torch.float16, device=dev)
+    K._prepacked_block_sparse_gemm_from_active_blocks_splitk(
+        torch.from_numpy(x).to(dev).reshape(b, 1, k), torch.from_numpy(w).to(dev), torch.from_numpy(ids).to(dev), out)
+    torch.cuda.synchronize()
+    assert O.max_err_ratio(out.reshape(b, n).cpu().numpy(), O.masked_gemm(x, w, ids)) <= TOL
+
+
+@pytest.mark.parametrize("b,k,n", [(16, 4096, 4096), (2, 200, 96), (5, 203, 130)])
+def test_host_buffer_operator(dev, b, k, n):
+    import ctypes
+    from bas import abi as L
+
+    x = O.make_activations(b, k, seed=8)
+    w = O.make_weight(n, k, seed=8)
+    nb = k // 64
+    h = ctypes.c_void_p()
+    L.check(L.lib.bas_linear_create(ctypes.byref(h), w.ctypes.data, n, k, 64), "create")
+    try:
+        y = np.empty((b, n), np.float16)
+        n_keep = max(1, nb // 2)
+        ids_out = np.full(nb, -1, np.int32)
+        L.check(L.lib.bas_linear_forward_host(h, x.ctypes.data, b, n_keep, O.SCORE_NORM, y.ctypes.data,
+                                              ids_out.ctypes.data), "forward_host")
+        want_ids = O.topk_ids(O.block_scores(x, O.SCORE_NORM), n_keep)
+        assert np.array_equal(ids_out[:n_keep], want_ids)
+        assert O.max_err_ratio(y, O.masked_gemm(x, w, want_ids)) <= TOL
+        # caller-provided ids, including the ragged last block
+        ids = np.arange((k + 63) // 64, dtype=np.int32)[::-1].copy()
+        L.check(L.lib.bas_linear_forward_host_ids(h, x.ctypes.data, b, ids.ctypes.data, ids.size, y.ctypes.data),
+                "forward_host_ids")
+        assert O.max_err_ratio(y, O.masked_gemm(x, w, ids)) <= TOL
+        L.check(L.lib.bas_linear_forward_host_ids(h, x.ctypes.data, b, None, 0, y.ctypes.data), "empty")
+        assert not y.any()
+    finally:
+        L.lib.bas_linear_destroy(h)

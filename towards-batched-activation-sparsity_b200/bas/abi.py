@@ -1,0 +1,74 @@
+"""Loads ``libbas.so`` and declares the C ABI of ``include/bas.h`` for ctypes."""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+BLOCK_K = 64
+TILE_N = 128
+MAX_BATCH = 64
+SCORE_NORM = 0
+SCORE_ENERGY = 1
+
+_PKG = Path(__file__).resolve().parent.parent
+lib_path = _PKG / "libbas.so"
+
+
+class BasError(RuntimeError):
+    """A libbas entry point returned a non-zero status."""
+
+    def __init__(self, status: int, where: str):
+        self.status = int(status)
+        msg = lib.bas_status_string(self.status).decode()
+        extra = f" (cudaError {lib.bas_last_cuda_error()})" if self.status == 4 else ""
+        super().__init__(f"{where}: {msg}{extra}")
+
+
+def _load() -> C.CDLL:
+    if not lib_path.exists():
+        raise ImportError(
+            f"{lib_path} is missing: build it with `python {_PKG.name}/build.py` "
+            "(needs nvcc; there is no fallback implementation)")
+    return C.CDLL(str(lib_path))
+
+
+lib = _load()
+
+_vp, _i, _i64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
+_SIGNATURES = {
+    "bas_status_string": (C.c_char_p, [_i]),
+    "bas_last_cuda_error": (_i, []),
+    "bas_launch_count": (C.c_ulonglong, []),
+    "bas_packed_weight_bytes": (_sz, [_i, _i]),
+    "bas_pack_weight": (_i, [_vp, _i, _i, _i64, _vp, _vp]),
+    "bas_gemm_workspace_bytes": (_sz, [_i, _i]),
+    "bas_workspace_init": (_i, [_vp, _sz, _vp]),
+    "bas_gemm": (_i, [_vp, _i64, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i64, _vp, _sz, _vp]),
+    "bas_gemm_ex": (_i, [_vp, _i64, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i64, _vp, _sz, _i, _vp]),
+    "bas_read_device_status": (_i, [_vp, C.POINTER(C.c_uint), _vp]),
+    "bas_build_bitmap": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
+    "bas_select_workspace_bytes": (_sz, [_i]),
+    "bas_select_topk": (_i, [_vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "bas_select_budget": (_i, [_vp, _i64, _i, _i, C.c_double, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "bas_linear_create": (_i, [C.POINTER(_vp), _vp, _i, _i, _i]),
+    "bas_linear_forward_host": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
+    "bas_linear_forward_host_ids": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
+    "bas_linear_destroy": (None, [_vp]),
+}
+for _name, (_res, _args) in _SIGNATURES.items():
+    _fn = getattr(lib, _name)       # AttributeError here = the library does not export the symbol
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+EXPORTED = tuple(_SIGNATURES)
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        raise BasError(status, where)
+
+
+def launch_count() -> int:
+    """Kernels launched by libbas from this process so far."""
+    return int(lib.bas_launch_count())

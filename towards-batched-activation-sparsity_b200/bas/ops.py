@@ -1,0 +1,266 @@
+"""Torch-facing host layer over the C ABI: packed-weight cache, per-stream workspaces, launches.
+
+torch is used for device memory and streams only.  Every function here launches libbas kernels on
+``torch.cuda.current_stream()``; none synchronises, and after one warm-up call (which creates the
+per-stream workspace and the packed weight) none allocates, so calls can be captured in a CUDA
+graph the way the reference's benchmark captures its wrappers
+(scripts/bench_perstep_actual_kernel_speedup.py:60-77).
+"""
+
+from __future__ import annotations
+
+import weakref
+from typing import Optional
+
+import torch
+
+from . import abi as _abi
+from .abi import BLOCK_K, MAX_BATCH, SCORE_ENERGY, SCORE_NORM, check, lib
+
+_PACKED: dict[tuple, torch.Tensor] = {}
+_PACK_STATS = {"hits": 0, "misses": 0}
+_GEMM_WS: dict[tuple, torch.Tensor] = {}
+_SELECT_WS: dict[tuple, torch.Tensor] = {}
+_SELECT_OUT: dict[tuple, tuple] = {}
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda_fp16(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (libbas has no CPU path)")
+    if t.dtype != torch.float16:
+        raise TypeError(f"{name} must be float16, got {t.dtype}")
+
+
+def n_keep_from_density(density: float, nb: int, min_keep: int = 1) -> int:
+    """The reference's rule: max(min_keep, min(nb, int(round(density * nb))))
+    (scripts/bench_roundrobin_e2e_decode.py:102)."""
+    return max(int(min_keep), min(int(nb), int(round(float(density) * int(nb)))))
+
+
+# ---------------------------------------------------------------------------------------------
+# packed weights
+# ---------------------------------------------------------------------------------------------
+
+def pack_weight(weight: torch.Tensor) -> torch.Tensor:
+    """Repack an nn.Linear weight [N, K] into libbas's tile-major layout (uint8 tensor, opaque)."""
+    _require_cuda_fp16(weight, "weight")
+    if weight.dim() != 2 or weight.stride(1) != 1:
+        raise ValueError("weight must be [N, K] with unit stride along K")
+    n, k = weight.shape
+    packed = torch.empty(lib.bas_packed_weight_bytes(n, k), dtype=torch.uint8, device=weight.device)
+    with torch.cuda.device(weight.device):
+        check(lib.bas_pack_weight(weight.data_ptr(), n, k, weight.stride(0), packed.data_ptr(), _stream_ptr()),
+              "bas_pack_weight")
+    return packed
+
+
+def get_packed_weight(weight: torch.Tensor, block_k: int = BLOCK_K, cache_prefix: str = "gemm") -> torch.Tensor:
+    """Cached :func:`pack_weight`, keyed like the reference's cache
+    (kernels/shared_mask_batched_triton_min_runtime.py:3136-3146).  Unlike the reference's, an
+    entry dies with its weight tensor, so a recycled address can never alias a stale pack."""
+    if int(block_k) != BLOCK_K:
+        raise ValueError(f"block_k must be {BLOCK_K}")
+    key = (cache_prefix, weight.data_ptr(), str(weight.device), str(weight.dtype), tuple(weight.shape),
+           tuple(weight.stride()), int(block_k))
+    packed = _PACKED.get(key)
+    if packed is not None:
+        _PACK_STATS["hits"] += 1
+        return packed
+    _PACK_STATS["misses"] += 1
+    packed = pack_weight(weight)
+    _PACKED[key] = packed
+    weakref.finalize(weight, _PACKED.pop, key, None)
+    return packed
+
+
+def clear_caches() -> None:
+    _PACKED.clear()
+    _GEMM_WS.clear()
+    _SELECT_WS.clear()
+    _SELECT_OUT.clear()
+
+
+# ---------------------------------------------------------------------------------------------
+# workspaces (one per device and stream; calls on one stream never overlap)
+# ---------------------------------------------------------------------------------------------
+
+def gemm_workspace(device: torch.device) -> torch.Tensor:
+    key = (device.index, _stream_ptr())
+    ws = _GEMM_WS.get(key)
+    if ws is None:
+        nbytes = lib.bas_gemm_workspace_bytes(MAX_BATCH, 1)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        check(lib.bas_workspace_init(ws.data_ptr(), nbytes, _stream_ptr()), "bas_workspace_init")
+        _GEMM_WS[key] = ws
+    return ws
+
+
+def select_workspace(device: torch.device, k: int) -> torch.Tensor:
+    key = (device.index, _stream_ptr(), int(k))
+    ws = _SELECT_WS.get(key)
+    if ws is None:
+        nbytes = lib.bas_select_workspace_bytes(int(k))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        check(lib.bas_workspace_init(ws.data_ptr(), nbytes, _stream_ptr()), "bas_workspace_init")
+        _SELECT_WS[key] = ws
+    return ws
+
+
+def read_status(device: Optional[torch.device] = None) -> int:
+    """Synchronously read and clear the status word of the current stream's workspace."""
+    import ctypes
+
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    ws = gemm_workspace(device)
+    flags = ctypes.c_uint(0)
+    check(lib.bas_read_device_status(ws.data_ptr(), ctypes.byref(flags), _stream_ptr()), "bas_read_device_status")
+    return int(flags.value)
+
+
+# ---------------------------------------------------------------------------------------------
+# launches
+# ---------------------------------------------------------------------------------------------
+
+def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: Optional[torch.Tensor] = None,
+         count: Optional[torch.Tensor] = None, k_host: Optional[int] = None,
+         bitmap: Optional[torch.Tensor] = None, family: int = 0) -> None:
+    """out2d[B, N] = x2d[B, K] restricted to the active blocks, times W^T.
+
+    ``ids`` int32 device list (``count``: optional int32[1] device-side length, ``k_host`` an upper
+    bound) or ``bitmap`` uint8[K/64].  ``family``: 0 by batch size, 1 CUDA-core, 2 tcgen05.
+    Batches above 64 rows are run in slices of 64."""
+    _require_cuda_fp16(x2d, "x")
+    _require_cuda_fp16(out2d, "out")
+    if x2d.dim() != 2 or out2d.dim() != 2 or x2d.stride(1) != 1 or out2d.stride(1) != 1:
+        raise ValueError("x and out must be 2-D with unit inner stride")
+    bt, k = x2d.shape
+    n = out2d.shape[1]
+    if out2d.shape[0] != bt:
+        raise ValueError("x and out disagree on the batch")
+    if bitmap is None:
+        if ids is None:
+            raise ValueError("either ids or bitmap is required")
+        if ids.dtype != torch.int32 or not ids.is_contiguous():
+            raise TypeError("ids must be a contiguous int32 tensor")
+        if k_host is None:
+            k_host = int(ids.numel())
+    else:
+        if bitmap.dtype != torch.uint8 or not bitmap.is_contiguous():
+            raise TypeError("bitmap must be a contiguous uint8 tensor")
+        k_host = 0
+    if x2d.data_ptr() % 16 or x2d.stride(0) % 8 or k % 8:
+        raise ValueError("x rows must be 16-byte aligned and K a multiple of 8")
+    with torch.cuda.device(x2d.device):
+        ws = gemm_workspace(x2d.device)
+        stream = _stream_ptr()
+        for b0 in range(0, bt, MAX_BATCH):
+            bsz = min(MAX_BATCH, bt - b0)
+            xs, ys = x2d[b0:b0 + bsz], out2d[b0:b0 + bsz]
+            check(lib.bas_gemm_ex(
+                xs.data_ptr(), xs.stride(0), packed.data_ptr(),
+                ids.data_ptr() if ids is not None and bitmap is None else None,
+                count.data_ptr() if count is not None else None, int(k_host),
+                bitmap.data_ptr() if bitmap is not None else None,
+                bsz, k, n, ys.data_ptr(), ys.stride(0), ws.data_ptr(), ws.numel(), int(family), stream),
+                "bas_gemm")
+
+
+def build_bitmap(ids: torch.Tensor, nb: int, device=None, count: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """uint8[nb] with 1 at the active ids; one kernel, no host synchronisation."""
+    device = torch.device(device) if device is not None else ids.device
+    if device.type != "cuda":
+        raise ValueError("bitmap must live on a CUDA device (libbas has no CPU path)")
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    ids = ids.to(device=device, dtype=torch.int32).contiguous()
+    bm = torch.empty(int(nb), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        check(lib.bas_build_bitmap(ids.data_ptr() if ids.numel() else None,
+                                   count.data_ptr() if count is not None else None,
+                                   int(ids.numel()), int(nb), bm.data_ptr(), _stream_ptr()), "bas_build_bitmap")
+    return bm
+
+
+def _select_buffers(device: torch.device, nb: int):
+    key = (device.index, _stream_ptr(), nb)
+    bufs = _SELECT_OUT.get(key)
+    if bufs is None:
+        bufs = (torch.empty(nb, dtype=torch.int32, device=device),
+                torch.empty(1, dtype=torch.int32, device=device))
+        _SELECT_OUT[key] = bufs
+    return bufs
+
+
+def select_topk(x2d: torch.Tensor, n_keep: int, score_kind: int = SCORE_NORM, *,
+                ids_out: Optional[torch.Tensor] = None, count_out: Optional[torch.Tensor] = None,
+                bitmap_out: Optional[torch.Tensor] = None, scores_out: Optional[torch.Tensor] = None):
+    """Device-side batch-shared top-k selection.  Returns (ids[:n_keep] int32 ascending, count int32[1]);
+    both stay on the device.  Without explicit outputs, per-stream buffers are reused."""
+    return _select(x2d, 0, int(n_keep), score_kind, 0.0, ids_out, count_out, bitmap_out, scores_out)
+
+
+def select_budget(x2d: torch.Tensor, energy_keep: float, min_keep: int = 1, *,
+                  ids_out: Optional[torch.Tensor] = None, count_out: Optional[torch.Tensor] = None,
+                  bitmap_out: Optional[torch.Tensor] = None, scores_out: Optional[torch.Tensor] = None):
+    """Device-side energy-budget selection (variable count).  Returns (ids buffer [nb], count int32[1]);
+    only the first ``count`` ids are meaningful, and reading ``count`` on the host synchronises."""
+    return _select(x2d, 1, int(min_keep), SCORE_ENERGY, float(energy_keep), ids_out, count_out, bitmap_out, scores_out)
+
+
+def _select(x2d, mode, n_keep, score_kind, energy_keep, ids_out, count_out, bitmap_out, scores_out):
+    _require_cuda_fp16(x2d, "x")
+    if x2d.dim() != 2 or x2d.stride(1) != 1:
+        raise ValueError("x must be 2-D with unit inner stride")
+    bt, k = x2d.shape
+    nb = k // BLOCK_K
+    if nb < 1:
+        raise ValueError("K must be at least 64")
+    if ids_out is None or count_out is None:
+        ids_buf, cnt_buf = _select_buffers(x2d.device, nb)
+        ids_out = ids_out if ids_out is not None else ids_buf
+        count_out = count_out if count_out is not None else cnt_buf
+    if scores_out is not None and scores_out.dtype != torch.float64:
+        raise TypeError("scores_out must be float64")
+    with torch.cuda.device(x2d.device):
+        ws = select_workspace(x2d.device, k)
+        args = (ids_out.data_ptr(), count_out.data_ptr(),
+                bitmap_out.data_ptr() if bitmap_out is not None else None,
+                scores_out.data_ptr() if scores_out is not None else None,
+                ws.data_ptr(), ws.numel(), _stream_ptr())
+        if mode == 0:
+            check(lib.bas_select_topk(x2d.data_ptr(), x2d.stride(0), bt, k, n_keep, int(score_kind), *args),
+                  "bas_select_topk")
+            return ids_out[:n_keep], count_out
+        check(lib.bas_select_budget(x2d.data_ptr(), x2d.stride(0), bt, k, energy_keep, n_keep, *args),
+              "bas_select_budget")
+        return ids_out, count_out
+
+
+def sparse_linear(x: torch.Tensor, weight: torch.Tensor, density: float, *, score_kind: int = SCORE_NORM,
+                  cache_prefix: str = "sparse_linear", out: Optional[torch.Tensor] = None,
+                  fixed_active_blocks: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The decode-time operator of the reference's ``_sparse_linear``
+    (scripts/bench_roundrobin_e2e_decode.py:179-284) as two chained launches: select, then GEMM
+    reading the id list from device memory.  x is [B, K] or [B, 1, K]."""
+    x3 = x.reshape(x.shape[0], 1, x.shape[1]) if x.dim() == 2 else x
+    if x3.shape[1] != 1:
+        raise ValueError("decode only: the sequence dimension must be 1")
+    bt, k = x3.shape[0], x3.shape[2]
+    n = weight.shape[0]
+    x2d = x3.reshape(bt, k)
+    packed = get_packed_weight(weight, BLOCK_K, cache_prefix)
+    if out is None:
+        out = torch.empty(bt, 1, n, device=x.device, dtype=x.dtype)
+    out2d = out.view(bt, n)
+    if fixed_active_blocks is not None:
+        ids = fixed_active_blocks.to(device=x.device, dtype=torch.int32).contiguous()
+        gemm(x2d, packed, out2d, ids=ids)
+    else:
+        n_keep = n_keep_from_density(density, k // BLOCK_K)
+        ids, count = select_topk(x2d, n_keep, score_kind)
+        gemm(x2d, packed, out2d, ids=ids, count=count, k_host=n_keep)
+    return out.reshape(bt, n) if x.dim() == 2 else out

@@ -1,0 +1,380 @@
+// The C ABI of libbas: argument checks, workspace carving, kernel-family choice and the host-buffer
+// operator.  See include/bas.h for the contract of every entry point.
+#include <atomic>
+#include <cstring>
+#include <new>
+
+#include "bas_kernels.cuh"
+
+namespace bas {
+
+static std::atomic<unsigned long long> g_launches{0};
+static thread_local int g_last_cuda_error = 0;
+
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+
+namespace {
+
+int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  return BAS_ERR_CUDA;
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc_major = 0;
+};
+
+// Per-device facts, read once.
+int device_info(DeviceInfo* out) {
+  static DeviceInfo cache[64];
+  static std::atomic<int> ready[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= 64) return BAS_ERR_UNSUPPORTED;
+  if (!ready[dev].load(std::memory_order_acquire)) {
+    DeviceInfo d;
+    e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    cache[dev] = d;
+    ready[dev].store(1, std::memory_order_release);
+  }
+  *out = cache[dev];
+  return BAS_OK;
+}
+
+inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15u) == 0; }
+
+size_t partial_bytes(int batch) { return (size_t)kMaxGridCtas * 2 * (size_t)batch * 128 * sizeof(float); }
+
+}  // namespace
+}  // namespace bas
+
+using namespace bas;
+
+extern "C" {
+
+const char* bas_status_string(int status) {
+  switch (status) {
+    case BAS_OK: return "ok";
+    case BAS_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, bad size, misaligned pointer or stride)";
+    case BAS_ERR_UNSUPPORTED: return "unsupported size or device (needs sm_100, batch <= 64, K/64 <= 4096)";
+    case BAS_ERR_WORKSPACE: return "workspace missing or too small";
+    case BAS_ERR_CUDA: return "a CUDA call failed (see bas_last_cuda_error)";
+    case BAS_ERR_DEVICE_FLAG: return "a kernel flagged a bad block id or an expired wait";
+    case BAS_ERR_TOO_LARGE: return "size beyond the fixed capacity of this entry point";
+    default: return "unknown status";
+  }
+}
+
+int bas_last_cuda_error(void) { return g_last_cuda_error; }
+
+unsigned long long bas_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+size_t bas_packed_weight_bytes(int n, int k) {
+  if (n <= 0 || k <= 0) return 0;
+  const size_t nb = ((size_t)k + kBlockK - 1) / kBlockK, nt = ((size_t)n + kTileN - 1) / kTileN;
+  return nb * nt * (size_t)kTileBytes;
+}
+
+int bas_pack_weight(const void* w_dev, int n, int k, int64_t ldw, void* packed_dev, void* stream) {
+  if (w_dev == nullptr || packed_dev == nullptr || n <= 0 || k <= 0 || ldw < k) return BAS_ERR_INVALID_ARGUMENT;
+  if (!aligned16(packed_dev)) return BAS_ERR_INVALID_ARGUMENT;
+  if ((k + kBlockK - 1) / kBlockK > BAS_MAX_BLOCKS || (n + kTileN - 1) / kTileN > kMaxColumnTiles)
+    return BAS_ERR_UNSUPPORTED;
+  cudaError_t e = launch_pack((const __half*)w_dev, n, k, (long long)ldw, (uint8_t*)packed_dev, (cudaStream_t)stream);
+  return e == cudaSuccess ? BAS_OK : cuda_fail(e);
+}
+
+size_t bas_gemm_workspace_bytes(int batch, int n) {
+  (void)n;
+  if (batch <= 0) return 0;
+  return kWsHeaderBytes + partial_bytes(batch > BAS_MAX_BATCH ? BAS_MAX_BATCH : batch);
+}
+
+int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream) {
+  if (ws_dev == nullptr || ws_bytes == 0) return BAS_ERR_INVALID_ARGUMENT;
+  const size_t header = ws_bytes < kWsHeaderBytes ? ws_bytes : kWsHeaderBytes;
+  cudaError_t e = cudaMemsetAsync(ws_dev, 0, header, (cudaStream_t)stream);
+  return e == cudaSuccess ? BAS_OK : cuda_fail(e);
+}
+
+int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
+                const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
+                void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int family, void* stream) {
+  if (x_dev == nullptr || packed_dev == nullptr || y_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  if (batch <= 0 || k <= 0 || n <= 0 || k_host < 0 || ldx < k || ldy < n) return BAS_ERR_INVALID_ARGUMENT;
+  if (batch > BAS_MAX_BATCH) return BAS_ERR_UNSUPPORTED;
+  const int nb = (k + kBlockK - 1) / kBlockK, nt = (n + kTileN - 1) / kTileN;
+  if (nb > BAS_MAX_BLOCKS || nt > kMaxColumnTiles) return BAS_ERR_UNSUPPORTED;
+  if (bitmap_dev == nullptr && ids_dev == nullptr && k_host > 0) return BAS_ERR_INVALID_ARGUMENT;
+  if (bitmap_dev == nullptr && k_host > nb) return BAS_ERR_INVALID_ARGUMENT;  // ids are distinct
+  // bulk copies: 16-byte aligned rows whose valid length is a multiple of 16 bytes
+  if (!aligned16(x_dev) || !aligned16(packed_dev) || (ldx & 7) != 0 || (k & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
+  if (ws_dev == nullptr || ws_bytes < bas_gemm_workspace_bytes(batch, n)) return BAS_ERR_WORKSPACE;
+  if (family < 0 || family > 2) return BAS_ERR_INVALID_ARGUMENT;
+
+  DeviceInfo di;
+  int st = device_info(&di);
+  if (st != BAS_OK) return st;
+  if (di.cc_major != 10) return BAS_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+
+  if (bitmap_dev == nullptr && k_host == 0) {  // empty active set known on the host: Y = 0
+    cudaError_t e = cudaMemset2DAsync(y_dev, (size_t)ldy * 2, 0, (size_t)n * 2, (size_t)batch, s);
+    return e == cudaSuccess ? BAS_OK : cuda_fail(e);
+  }
+
+  GemmParams p;
+  p.x = (const __half*)x_dev;
+  p.ldx = (long long)ldx;
+  p.packed = (const uint8_t*)packed_dev;
+  p.ids = ids_dev;
+  p.count_dev = count_dev;
+  p.k_host = k_host;
+  p.bitmap = bitmap_dev;
+  p.batch = batch;
+  p.k = k;
+  p.n = n;
+  p.nb = nb;
+  p.nt = nt;
+  p.y = (__half*)y_dev;
+  p.ldy = (long long)ldy;
+  p.status = (unsigned int*)ws_dev;
+  p.counters = (int*)((uint8_t*)ws_dev + 256);
+  p.partials = (float*)((uint8_t*)ws_dev + kWsHeaderBytes);
+
+  const int grid_cap = di.sm_count < kMaxGridCtas ? di.sm_count : kMaxGridCtas;
+  const bool small = (family == 1) || (family == 0 && batch <= 8);
+  if (small && batch > 8) return BAS_ERR_UNSUPPORTED;
+  cudaError_t e = small ? launch_gemv(p, grid_cap, s) : launch_umma(p, grid_cap, s);
+  return e == cudaSuccess ? BAS_OK : cuda_fail(e);
+}
+
+int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev, const int32_t* count_dev,
+             int k_host, const uint8_t* bitmap_dev, int batch, int k, int n, void* y_dev, int64_t ldy, void* ws_dev,
+             size_t ws_bytes, void* stream) {
+  return bas_gemm_ex(x_dev, ldx, packed_dev, ids_dev, count_dev, k_host, bitmap_dev, batch, k, n, y_dev, ldy, ws_dev,
+                     ws_bytes, 0, stream);
+}
+
+int bas_read_device_status(void* ws_dev, unsigned int* flags_out, void* stream) {
+  if (ws_dev == nullptr || flags_out == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e = cudaMemcpyAsync(flags_out, ws_dev, sizeof(unsigned int), cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaMemsetAsync(ws_dev, 0, sizeof(unsigned int), s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaStreamSynchronize(s);
+  return e == cudaSuccess ? BAS_OK : cuda_fail(e);
+}
+
+int bas_build_bitmap(const int32_t* ids_dev, const int32_t* count_dev, int k_host, int nb, uint8_t* bitmap_dev,
+                     void* stream) {
+  if (bitmap_dev == nullptr || nb <= 0 || k_host < 0 || (k_host > 0 && ids_dev == nullptr))
+    return BAS_ERR_INVALID_ARGUMENT;
+  cudaError_t e = launch_build_bitmap(ids_dev, count_dev, k_host, nb, bitmap_dev, (cudaStream_t)stream);
+  return e == cudaSuccess ? BAS_OK : cuda_fail(e);
+}
+
+size_t bas_select_workspace_bytes(int k) {
+  if (k <= 0) return 0;
+  const size_t nb = (size_t)(k / kBlockK);
+  return 256 + sizeof(double) * (nb > 0 ? nb : 1);
+}
+
+static int select_common(const void* x_dev, int64_t ldx, int batch, int k, int mode, int n_keep, int score_kind,
+                         double energy_keep, int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
+                         double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream) {
+  if (x_dev == nullptr || ids_out_dev == nullptr || count_out_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  if (batch <= 0 || k < kBlockK || ldx < k || !aligned16(x_dev) || (ldx & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
+  const int nb = k / kBlockK;  // trailing K mod 64 channels are never scored (d_eff)
+  if (nb > BAS_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
+  if (score_kind != BAS_SCORE_NORM && score_kind != BAS_SCORE_ENERGY) return BAS_ERR_INVALID_ARGUMENT;
+  if (n_keep < 0 || n_keep > nb) return BAS_ERR_INVALID_ARGUMENT;
+  if (ws_dev == nullptr || ws_bytes < bas_select_workspace_bytes(k)) return BAS_ERR_WORKSPACE;
+  DeviceInfo di;
+  int st = device_info(&di);
+  if (st != BAS_OK) return st;
+  SelectParams p;
+  p.x = (const __half*)x_dev;
+  p.ldx = (long long)ldx;
+  p.batch = batch;
+  p.k = k;
+  p.nb = nb;
+  p.mode = mode;
+  p.n_keep = n_keep;
+  p.score_kind = score_kind;
+  p.energy_keep = energy_keep;
+  p.ids_out = ids_out_dev;
+  p.count_out = count_out_dev;
+  p.bitmap_out = bitmap_out_dev;
+  p.scores_out = scores_out_dev;
+  p.ws_done = (unsigned int*)ws_dev;
+  p.ws_scores = (double*)((uint8_t*)ws_dev + 256);
+  cudaError_t e = launch_select(p, di.sm_count, (cudaStream_t)stream);
+  return e == cudaSuccess ? BAS_OK : cuda_fail(e);
+}
+
+int bas_select_topk(const void* x_dev, int64_t ldx, int batch, int k, int n_keep, int score_kind, int32_t* ids_out_dev,
+                    int32_t* count_out_dev, uint8_t* bitmap_out_dev, double* scores_out_dev, void* ws_dev,
+                    size_t ws_bytes, void* stream) {
+  return select_common(x_dev, ldx, batch, k, 0, n_keep, score_kind, 0.0, ids_out_dev, count_out_dev, bitmap_out_dev,
+                       scores_out_dev, ws_dev, ws_bytes, stream);
+}
+
+int bas_select_budget(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
+                      int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev, double* scores_out_dev,
+                      void* ws_dev, size_t ws_bytes, void* stream) {
+  return select_common(x_dev, ldx, batch, k, 1, min_keep, BAS_SCORE_ENERGY, energy_keep, ids_out_dev, count_out_dev,
+                       bitmap_out_dev, scores_out_dev, ws_dev, ws_bytes, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host-buffer operator
+// ---------------------------------------------------------------------------------------------
+struct bas_linear {
+  int n = 0, k = 0, nb = 0, max_batch = 0;
+  cudaStream_t stream = nullptr;
+  uint8_t* packed = nullptr;
+  __half* x_dev = nullptr;
+  __half* y_dev = nullptr;
+  int32_t* ids_dev = nullptr;    // [nb] ids followed by [1] count
+  void* gemm_ws = nullptr;
+  size_t gemm_ws_bytes = 0;
+  void* sel_ws = nullptr;
+  size_t sel_ws_bytes = 0;
+  void* x_pin = nullptr;         // pinned staging, so that the copies are truly asynchronous
+  void* y_pin = nullptr;
+  int32_t* ids_pin = nullptr;
+  long long ldx = 0;
+};
+
+static void linear_free(bas_linear* h) {
+  if (h == nullptr) return;
+  if (h->packed) cudaFree(h->packed);
+  if (h->x_dev) cudaFree(h->x_dev);
+  if (h->y_dev) cudaFree(h->y_dev);
+  if (h->ids_dev) cudaFree(h->ids_dev);
+  if (h->gemm_ws) cudaFree(h->gemm_ws);
+  if (h->sel_ws) cudaFree(h->sel_ws);
+  if (h->x_pin) cudaFreeHost(h->x_pin);
+  if (h->y_pin) cudaFreeHost(h->y_pin);
+  if (h->ids_pin) cudaFreeHost(h->ids_pin);
+  if (h->stream) cudaStreamDestroy(h->stream);
+  delete h;
+}
+
+int bas_linear_create(bas_linear** out, const void* w_host, int n, int k, int max_batch) {
+  if (out == nullptr || w_host == nullptr || n <= 0 || k <= 0 || max_batch <= 0) return BAS_ERR_INVALID_ARGUMENT;
+  if (max_batch > BAS_MAX_BATCH) return BAS_ERR_UNSUPPORTED;
+  *out = nullptr;
+  bas_linear* h = new (std::nothrow) bas_linear();
+  if (h == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  h->n = n;
+  h->k = k;
+  h->nb = (k + kBlockK - 1) / kBlockK;
+  h->max_batch = max_batch;
+  h->ldx = ((long long)k + 7) / 8 * 8;
+  __half* w_dev = nullptr;
+  cudaError_t e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+#define BAS_TRY(call)            \
+  if (e == cudaSuccess) e = (call)
+  BAS_TRY(cudaMalloc(&w_dev, (size_t)n * k * 2));
+  BAS_TRY(cudaMalloc(&h->packed, bas_packed_weight_bytes(n, k)));
+  BAS_TRY(cudaMalloc(&h->x_dev, (size_t)max_batch * h->ldx * 2));
+  BAS_TRY(cudaMalloc(&h->y_dev, (size_t)max_batch * n * 2));
+  BAS_TRY(cudaMalloc(&h->ids_dev, sizeof(int32_t) * ((size_t)h->nb + 1)));
+  h->gemm_ws_bytes = bas_gemm_workspace_bytes(max_batch, n);
+  h->sel_ws_bytes = bas_select_workspace_bytes(k);
+  BAS_TRY(cudaMalloc(&h->gemm_ws, h->gemm_ws_bytes));
+  BAS_TRY(cudaMalloc(&h->sel_ws, h->sel_ws_bytes));
+  BAS_TRY(cudaMallocHost(&h->x_pin, (size_t)max_batch * h->ldx * 2));
+  BAS_TRY(cudaMallocHost(&h->y_pin, (size_t)max_batch * n * 2));
+  BAS_TRY(cudaMallocHost((void**)&h->ids_pin, sizeof(int32_t) * ((size_t)h->nb + 1)));
+  BAS_TRY(cudaMemsetAsync(h->x_dev, 0, (size_t)max_batch * h->ldx * 2, h->stream));
+  BAS_TRY(cudaMemsetAsync(h->gemm_ws, 0, kWsHeaderBytes, h->stream));
+  BAS_TRY(cudaMemsetAsync(h->sel_ws, 0, h->sel_ws_bytes, h->stream));
+  BAS_TRY(cudaMemcpyAsync(w_dev, w_host, (size_t)n * k * 2, cudaMemcpyHostToDevice, h->stream));
+#undef BAS_TRY
+  int st = BAS_OK;
+  if (e == cudaSuccess) st = bas_pack_weight(w_dev, n, k, k, h->packed, h->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+  if (w_dev) cudaFree(w_dev);
+  if (e != cudaSuccess || st != BAS_OK) {
+    linear_free(h);
+    return e != cudaSuccess ? cuda_fail(e) : st;
+  }
+  *out = h;
+  return BAS_OK;
+}
+
+static int linear_forward(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind,
+                          const int32_t* ids_host, int n_ids, void* y_host, int32_t* ids_host_out) {
+  if (h == nullptr || x_host == nullptr || y_host == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  if (batch <= 0 || batch > h->max_batch) return BAS_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = h->stream;
+  // host -> pinned -> device (rows padded to a multiple of 8 channels; the padding stays zero)
+  const size_t row = (size_t)h->k * 2;
+  std::memcpy(h->x_pin, x_host, row * batch);
+  cudaError_t e = cudaMemcpy2DAsync(h->x_dev, (size_t)h->ldx * 2, h->x_pin, row, row, batch, cudaMemcpyHostToDevice, s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  int st;
+  int k_host;
+  const int32_t* count_dev = nullptr;
+  if (ids_host != nullptr || n_ids == 0) {
+    if (n_ids < 0 || n_ids > h->nb) return BAS_ERR_INVALID_ARGUMENT;
+    if (n_ids > 0) {
+      std::memcpy(h->ids_pin, ids_host, sizeof(int32_t) * n_ids);
+      e = cudaMemcpyAsync(h->ids_dev, h->ids_pin, sizeof(int32_t) * n_ids, cudaMemcpyHostToDevice, s);
+      if (e != cudaSuccess) return cuda_fail(e);
+    }
+    k_host = n_ids;
+  } else {
+    st = bas_select_topk(h->x_dev, h->ldx, batch, h->k, n_keep, score_kind, h->ids_dev, h->ids_dev + h->nb, nullptr,
+                         nullptr, h->sel_ws, h->sel_ws_bytes, s);
+    if (st != BAS_OK) return st;
+    k_host = n_keep;
+    count_dev = h->ids_dev + h->nb;
+  }
+  st = bas_gemm(h->x_dev, h->ldx, h->packed, h->ids_dev, count_dev, k_host, nullptr, batch, (int)h->ldx, h->n, h->y_dev,
+                h->n, h->gemm_ws, h->gemm_ws_bytes, s);
+  if (st != BAS_OK) return st;
+  e = cudaMemcpyAsync(h->y_pin, h->y_dev, (size_t)batch * h->n * 2, cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (ids_host_out != nullptr && k_host > 0) {
+    e = cudaMemcpyAsync(h->ids_pin, h->ids_dev, sizeof(int32_t) * k_host, cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  unsigned int* flag_pin = (unsigned int*)(h->ids_pin + h->nb);
+  e = cudaMemcpyAsync(flag_pin, h->gemm_ws, sizeof(unsigned int), cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  std::memcpy(y_host, h->y_pin, (size_t)batch * h->n * 2);
+  if (ids_host_out != nullptr && k_host > 0) std::memcpy(ids_host_out, h->ids_pin, sizeof(int32_t) * k_host);
+  if (*flag_pin != 0) {
+    cudaMemsetAsync(h->gemm_ws, 0, sizeof(unsigned int), s);
+    return BAS_ERR_DEVICE_FLAG;
+  }
+  return BAS_OK;
+}
+
+int bas_linear_forward_host(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind, void* y_host,
+                            int32_t* ids_host_out) {
+  if (h == nullptr || n_keep < 1 || n_keep > h->k / kBlockK) return BAS_ERR_INVALID_ARGUMENT;
+  return linear_forward(h, x_host, batch, n_keep, score_kind, nullptr, -1, y_host, ids_host_out);
+}
+
+int bas_linear_forward_host_ids(bas_linear* h, const void* x_host, int batch, const int32_t* ids_host, int n_ids,
+                                void* y_host) {
+  if (n_ids < 0 || (n_ids > 0 && ids_host == nullptr)) return BAS_ERR_INVALID_ARGUMENT;
+  return linear_forward(h, x_host, batch, 0, 0, ids_host, n_ids, y_host, nullptr);
+}
+
+void bas_linear_destroy(bas_linear* h) { linear_free(h); }
+
+}  // extern "C"

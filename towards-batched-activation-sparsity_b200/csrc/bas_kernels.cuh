@@ -1,0 +1,50 @@
+// Kernel launch parameters shared by the two contraction kernels and their host launchers.
+#pragma once
+
+#include "bas_common.cuh"
+
+namespace bas {
+
+struct GemmParams {
+  const __half* x;          // [batch, K], row stride ldx
+  long long ldx;
+  const uint8_t* packed;    // [nb][nt][128][64] fp16, swizzled tiles of 16 KiB
+  const int32_t* ids;       // active block ids (or null when bitmap is given)
+  const int32_t* count_dev; // optional device-side number of ids
+  int k_host;               // number of ids (upper bound when count_dev is given)
+  const uint8_t* bitmap;    // optional byte map [nb]
+  int batch, k, n, nb, nt;
+  __half* y;                // [batch, N], row stride ldy
+  long long ldy;
+  unsigned int* status;     // workspace: status word
+  int* counters;            // workspace: one arrival counter per column tile
+  float* partials;          // workspace: [grid][2][batch][128] fp32
+};
+
+// Host launchers (defined next to their kernels).  `sm_count` is the persistent grid's upper bound.
+cudaError_t launch_gemv(const GemmParams& p, int sm_count, cudaStream_t stream);
+cudaError_t launch_umma(const GemmParams& p, int sm_count, cudaStream_t stream);
+cudaError_t launch_pack(const __half* w, int n, int k, long long ldw, uint8_t* packed, cudaStream_t stream);
+cudaError_t launch_build_bitmap(const int32_t* ids, const int32_t* count_dev, int k_host, int nb, uint8_t* bitmap,
+                                cudaStream_t stream);
+
+struct SelectParams {
+  const __half* x;
+  long long ldx;
+  int batch, k, nb;
+  int mode;           // 0 = top-k, 1 = energy budget
+  int n_keep;         // top-k: blocks to keep; budget: min_keep
+  int score_kind;     // BAS_SCORE_NORM / BAS_SCORE_ENERGY
+  double energy_keep; // budget mode
+  int32_t* ids_out;
+  int32_t* count_out;
+  uint8_t* bitmap_out;
+  double* scores_out;
+  double* ws_scores;      // workspace: [nb] fp64 batch-summed scores
+  unsigned int* ws_done;  // workspace: CTA arrival counter
+};
+cudaError_t launch_select(const SelectParams& p, int sm_count, cudaStream_t stream);
+
+void count_launch(int n = 1);
+
+}  // namespace bas

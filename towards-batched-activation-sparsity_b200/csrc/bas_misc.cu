@@ -1,0 +1,210 @@
+// Weight prepack, bitmap build and the per-step batch-shared mask selection.
+#include "bas_kernels.cuh"
+
+namespace bas {
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// Prepack: W[N, K] (row stride ldw) -> [nb][nt][128][64] fp16 tiles, 16-byte chunk q of tile row r
+// stored at chunk position q ^ (r % 8).  One CTA per tile, four chunks per thread.  Off the hot
+// path (once per weight), like the reference's _get_prepacked_weight_block_major
+// (kernels/shared_mask_batched_triton_min_runtime.py:3133-3163).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) pack_weight_kernel(const __half* __restrict__ w, int n, int k, long long ldw,
+                                                          uint8_t* __restrict__ packed, int nt) {
+  const int t = blockIdx.x, j = blockIdx.y;
+  uint8_t* tile = packed + ((size_t)j * nt + t) * kTileBytes;
+  const bool vec_ok = ((ldw & 7) == 0) && ((((uintptr_t)w) & 15) == 0);
+  for (int idx = threadIdx.x; idx < kTileN * 8; idx += blockDim.x) {
+    const int r = idx >> 3, q = idx & 7;
+    const int row = t * kTileN + r, col = j * kBlockK + q * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < n && col < k) {
+      const __half* src = w + (size_t)row * ldw + col;
+      if (vec_ok && col + 8 <= k) {
+        v = *(const uint4*)src;
+      } else {
+        __half h[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) h[e] = (col + e < k) ? src[e] : __float2half_rn(0.f);
+        v = *(const uint4*)h;
+      }
+    }
+    *(uint4*)(tile + r * 128 + ((q ^ (r & 7)) << 4)) = v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Bitmap: u8[nb], 1 at active ids (kernels/shared_mask_batched_triton_min_runtime.py:1056-1061).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) build_bitmap_kernel(const int32_t* __restrict__ ids,
+                                                           const int32_t* __restrict__ count_dev, int k_host, int nb,
+                                                           uint8_t* __restrict__ bitmap) {
+  // single CTA: clear, then set
+  for (int i = threadIdx.x; i < nb; i += blockDim.x) bitmap[i] = 0;
+  __syncthreads();
+  int cnt = k_host;
+  if (count_dev != nullptr) cnt = min(max(*count_dev, 0), k_host);
+  for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+    const int id = ids[i];
+    if (id >= 0 && id < nb) bitmap[id] = 1;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Selection.  Phase 1 (all CTAs): per-(batch row, block) energy in fp64 from exact fp16 squares,
+// optional sqrt, batch-summed in row order -> ws_scores[nb].  Phase 2 (the last CTA to finish):
+// rank every block by (score descending, id ascending), keep the first n_keep (top-k) or the
+// shortest prefix reaching the energy budget, and write the kept ids in ascending order.
+// Restates scripts/bench_roundrobin_e2e_decode.py:90-113 and
+// scripts/bench_alpaca_energy_budget_e2e.py:43-62 in one launch without host synchronisation.
+// ---------------------------------------------------------------------------------------------
+constexpr int kSelThreads = 256;
+constexpr int kSelBlocksPerCta = 2;                  // activation blocks scored per CTA
+constexpr int kSelMaxBatch = 1024;
+
+__global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams p) {
+  extern __shared__ double s_dyn[];   // phase 1: [kSelBlocksPerCta][batch]; phase 2: scores[nb] + ranks
+  __shared__ int s_last;
+  __shared__ int s_warp_cnt[kSelThreads / 32];
+  __shared__ int s_keep;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int j0 = blockIdx.x * kSelBlocksPerCta;
+  const int nj = min(kSelBlocksPerCta, p.nb - j0);
+
+  // ---- phase 1: 8 lanes per (row, block) pair, 16 bytes per lane ----
+  const int sub = tid & 7, grp = tid >> 3;           // 32 groups of 8 lanes
+  const int pairs = nj * p.batch;
+  for (int base = 0; base < pairs; base += kSelThreads / 8) {
+    const int pr = base + grp;
+    double e = 0.0;
+    if (pr < pairs) {
+      const int jj = pr / p.batch, b = pr - jj * p.batch;
+      const uint4 v = __ldg((const uint4*)(p.x + (size_t)b * p.ldx + (size_t)(j0 + jj) * kBlockK) + sub);
+      const __half2* h = (const __half2*)&v;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __half22float2(h[q]);
+        e += (double)(f.x * f.x);   // a product of two fp16 values is exact in fp32
+        e += (double)(f.y * f.y);
+      }
+    }
+    e += __shfl_xor_sync(0xffffffffu, e, 1);
+    e += __shfl_xor_sync(0xffffffffu, e, 2);
+    e += __shfl_xor_sync(0xffffffffu, e, 4);
+    if (pr < pairs && sub == 0) {
+      const int jj = pr / p.batch, b = pr - jj * p.batch;
+      s_dyn[jj * p.batch + b] = (p.score_kind == BAS_SCORE_NORM) ? sqrt(e) : e;
+    }
+  }
+  __syncthreads();
+  if (tid < nj) {
+    double s = 0.0;
+    for (int b = 0; b < p.batch; ++b) s += s_dyn[tid * p.batch + b];   // batch rows in order
+    p.ws_scores[j0 + tid] = s / (double)p.batch;
+    __threadfence();
+  }
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned int old = atomicAdd(p.ws_done, 1u);
+    s_last = (old == gridDim.x - 1) ? 1 : 0;
+    if (s_last) *p.ws_done = 0u;   // re-arm for the next call
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+
+  // ---- phase 2: one CTA ranks all blocks ----
+  double* s_score = s_dyn;                              // [nb]
+  int* s_rank = (int*)(s_dyn + p.nb);                   // [nb]
+  int* s_order = s_rank + p.nb;                         // [nb] block id at each rank (budget mode)
+  for (int j = tid; j < p.nb; j += kSelThreads) {
+    const double s = __ldcg(p.ws_scores + j);
+    s_score[j] = s;
+    if (p.scores_out != nullptr) p.scores_out[j] = s;
+  }
+  __syncthreads();
+  for (int j = tid; j < p.nb; j += kSelThreads) {
+    const double sj = s_score[j];
+    int rank = 0;
+    for (int i = 0; i < p.nb; ++i) {
+      const double si = s_score[i];
+      rank += (si > sj || (si == sj && i < j)) ? 1 : 0;
+    }
+    s_rank[j] = rank;
+    s_order[rank] = j;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int keep = p.n_keep;
+    if (p.mode == 1) {
+      // energy budget: shortest descending prefix whose sum reaches energy_keep of the total
+      double total = 0.0;
+      for (int r = 0; r < p.nb; ++r) total += s_score[s_order[r]];
+      const double thresh = p.energy_keep * total;
+      double cum = 0.0;
+      int kk = p.nb;
+      for (int r = 0; r < p.nb; ++r) {
+        cum += s_score[s_order[r]];
+        if (cum >= thresh) { kk = r + 1; break; }
+      }
+      keep = max(p.n_keep, min(p.nb, kk));
+    }
+    s_keep = min(max(keep, 0), p.nb);
+  }
+  __syncthreads();
+  const int keep = s_keep;
+  // ascending compaction of the kept ids
+  int running = 0;
+  for (int base = 0; base < p.nb; base += kSelThreads) {
+    const int j = base + tid;
+    const bool kept = (j < p.nb) && (s_rank[j] < keep);
+    if (j < p.nb && p.bitmap_out != nullptr) p.bitmap_out[j] = kept ? 1 : 0;
+    const unsigned m = __ballot_sync(0xffffffffu, kept);
+    if (lane == 0) s_warp_cnt[warp] = __popc(m);
+    __syncthreads();
+    int off = running;
+    for (int w = 0; w < warp; ++w) off += s_warp_cnt[w];
+    if (kept) p.ids_out[off + __popc(m & ((1u << lane) - 1u))] = j;
+    for (int w = 0; w < kSelThreads / 32; ++w) running += s_warp_cnt[w];
+    __syncthreads();
+  }
+  if (tid == 0) *p.count_out = keep;
+}
+
+}  // namespace
+
+cudaError_t launch_pack(const __half* w, int n, int k, long long ldw, uint8_t* packed, cudaStream_t stream) {
+  const int nb = (k + kBlockK - 1) / kBlockK, nt = (n + kTileN - 1) / kTileN;
+  pack_weight_kernel<<<dim3(nt, nb), 256, 0, stream>>>(w, n, k, ldw, packed, nt);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_build_bitmap(const int32_t* ids, const int32_t* count_dev, int k_host, int nb, uint8_t* bitmap,
+                                cudaStream_t stream) {
+  build_bitmap_kernel<<<1, 256, 0, stream>>>(ids, count_dev, k_host, nb, bitmap);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_select(const SelectParams& p, int sm_count, cudaStream_t stream) {
+  (void)sm_count;
+  if (p.batch > kSelMaxBatch) return cudaErrorInvalidValue;
+  const int grid = (p.nb + kSelBlocksPerCta - 1) / kSelBlocksPerCta;
+  const size_t phase1 = sizeof(double) * kSelBlocksPerCta * (size_t)p.batch;
+  const size_t phase2 = (sizeof(double) + 2 * sizeof(int)) * (size_t)p.nb;
+  const size_t smem = phase1 > phase2 ? phase1 : phase2;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e != cudaSuccess) return e;
+    if (smem > 96 * 1024) return cudaErrorInvalidValue;
+  }
+  select_kernel<<<grid, kSelThreads, smem, stream>>>(p);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace bas
