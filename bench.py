@@ -405,6 +405,8 @@ def run_gpu(args) -> None:
     for h in handles:
         abi.lib.bas_linear_destroy(h)
     for bb in BATCHES:      # the e2e outputs are real results: same masks, same sums as the resident path
+        ops.gemm(xs[bb], packed[0], outs[bb], ids=ids[bb])
+        torch.cuda.synchronize()
         d = np.abs(y_host[bb].astype(np.float32) - outs[bb].float().cpu().numpy()).max()
         if not d <= 2e-3 * float(outs[bb].float().abs().max().item()):
             raise SystemExit(f"end-to-end output differs from the resident-input path at B={bb}")

@@ -104,10 +104,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_splitk_kernel(const Gemm
     return;
   }
   const long long total = (long long)k_act * p.nt;
-  const int c = blockIdx.x, G = gridDim.x;
+  // Never more ranges than units: every participating CTA then owns at least one unit, so the
+  // contributors of a column tile are a contiguous run of CTAs.
+  const int c = blockIdx.x, G = (int)min((long long)gridDim.x, total);
+  if (c >= G) return;
   const long long u0 = part_begin(c, total, G), u1 = part_begin(c + 1, total, G);
   const int cnt = (int)(u1 - u0);
-  if (cnt == 0) return;
 
   int issued = 0;
   if (warp == 0) {

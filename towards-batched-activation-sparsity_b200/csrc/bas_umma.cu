@@ -110,9 +110,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   const uint32_t tmem_base = hdr->tmem_base;
 
   const long long total = (long long)k_act * p.nt;
-  const int c = blockIdx.x, G = gridDim.x;
-  const long long u0 = (k_act > 0) ? part_begin(c, total, G) : 0;
-  const long long u1 = (k_act > 0) ? part_begin(c + 1, total, G) : 0;
+  // Never more ranges than units: every participating CTA then owns at least one unit, so the
+  // contributors of a column tile are a contiguous run of CTAs.
+  const int c = blockIdx.x, G = (int)max(1LL, min((long long)gridDim.x, total));
+  const long long u0 = (k_act > 0 && c < G) ? part_begin(c, total, G) : 0;
+  const long long u1 = (k_act > 0 && c < G) ? part_begin(c + 1, total, G) : 0;
   const int cnt = (int)(u1 - u0);
   int issued = 0;  // tiles whose copies the producer thread has started
 
