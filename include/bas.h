@@ -91,10 +91,18 @@ BAS_API int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream);
 BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
              const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
              void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, void* stream);
-/* As bas_gemm, with the kernel family forced: 0 = by batch size, 1 = CUDA-core, 2 = tcgen05. */
+/* As bas_gemm, with flags:
+ *   bits 0-1  kernel family: 0 = chosen by batch size, 1 = CUDA-core kernel, 2 = tcgen05 kernel
+ *   BAS_GEMM_IDS_STABLE  the caller promises that ids_dev is NOT written by the kernel that
+ *             immediately precedes this call in the stream (a fixed mask, or one selected several
+ *             launches earlier).  The kernel is launched with programmatic stream serialization;
+ *             with this flag it starts streaming weight tiles while the previous kernel is still
+ *             draining, and waits for it only before reading X and writing Y.  Without the flag
+ *             only the kernel's own preamble overlaps.  Ignored when count_dev is given. */
+#define BAS_GEMM_IDS_STABLE 16
 BAS_API int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
                 const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
-                void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int family, void* stream);
+                void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream);
 /* Synchronous: copies the status word of a workspace to *flags_out (0 = clean) and clears it. */
 BAS_API int bas_read_device_status(void* ws_dev, unsigned int* flags_out, void* stream);
 

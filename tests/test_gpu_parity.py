@@ -25,7 +25,7 @@ def _ops():
     return ops
 
 
-def _run_gemm(dev, x, w, ids=None, bitmap=None, family=0, count=None, k_host=None):
+def _run_gemm(dev, x, w, ids=None, bitmap=None, family=0, count=None, k_host=None, ids_stable=False):
     ops = _ops()
     tx, tw = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
     packed = ops.pack_weight(tw)
@@ -38,7 +38,7 @@ def _run_gemm(dev, x, w, ids=None, bitmap=None, family=0, count=None, k_host=Non
         if count is not None:
             kw["count"] = torch.tensor([count], dtype=torch.int32, device=dev)
             kw["k_host"] = k_host
-    ops.gemm(tx, packed, out, family=family, **kw)
+    ops.gemm(tx, packed, out, family=family, ids_stable=ids_stable, **kw)
     torch.cuda.synchronize()
     assert ops.read_status(dev) == 0
     return out.cpu().numpy()
@@ -151,6 +151,42 @@ def test_block_additivity_at_full_size(dev, b):
     yab = _run_gemm(dev, x, w, ids=ids).astype(np.float32)
     scale = np.abs(yab).max()
     assert np.abs(ya + yb - yab).max() <= 2e-3 * scale
+
+
+@pytest.mark.parametrize("b", [2, 16, 64])
+def test_back_to_back_launches_with_stable_ids(dev, b):
+    """Chained launches overlap (programmatic dependent launch); with stable ids the next kernel
+    streams weights while the previous one drains.  Every result must still be exact."""
+    ops = _ops()
+    k, n = 11008, 4096
+    w = O.make_weight(n, k, seed=41)
+    packed = ops.pack_weight(torch.from_numpy(w).to(dev))
+    xs = [O.make_activations(b, k, seed=600 + i, dist="laplace") for i in range(4)]
+    idl = [O.random_active_blocks(172, 40 + 10 * i, seed=i) for i in range(4)]
+    txs = [torch.from_numpy(x).to(dev) for x in xs]
+    tids = [torch.from_numpy(i).to(dev) for i in idl]
+    outs = [torch.full((b, n), float("nan"), dtype=torch.float16, device=dev) for _ in range(4)]
+    torch.cuda.synchronize()
+    for rep in range(3):
+        for i in range(4):
+            ops.gemm(txs[i], packed, outs[i], ids=tids[i], ids_stable=True)
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
+    for i in range(4):
+        assert O.max_err_ratio(outs[i].cpu().numpy(), O.masked_gemm(xs[i], w, idl[i])) <= TOL
+
+
+@pytest.mark.parametrize("b", [2, 16])
+def test_all_ids_bad_writes_zeros(dev, b):
+    ops = _ops()
+    x = O.make_activations(b, 1024, seed=1)
+    w = O.make_weight(256, 1024, seed=1)
+    out = torch.full((b, 256), float("nan"), dtype=torch.float16, device=dev)
+    ids = torch.tensor([16, 99, -3], dtype=torch.int32, device=dev)
+    ops.gemm(torch.from_numpy(x).to(dev), ops.pack_weight(torch.from_numpy(w).to(dev)), out, ids=ids)
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 1
+    assert not out.cpu().numpy().any()
 
 
 def test_bad_block_id_is_skipped_and_flagged(dev):

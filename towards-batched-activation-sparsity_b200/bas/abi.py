@@ -10,6 +10,7 @@ TILE_N = 128
 MAX_BATCH = 64
 SCORE_NORM = 0
 SCORE_ENERGY = 1
+IDS_STABLE = 16          # BAS_GEMM_IDS_STABLE
 
 _PKG = Path(__file__).resolve().parent.parent
 lib_path = _PKG / "libbas.so"

@@ -1,6 +1,7 @@
 // The C ABI of libbas: argument checks, workspace carving, kernel-family choice and the host-buffer
 // operator.  See include/bas.h for the contract of every entry point.
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -12,6 +13,14 @@ static std::atomic<unsigned long long> g_launches{0};
 static thread_local int g_last_cuda_error = 0;
 
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("BAS_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
 
 namespace {
 
@@ -104,7 +113,7 @@ int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream) {
 
 int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
                 const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
-                void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int family, void* stream) {
+                void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream) {
   if (x_dev == nullptr || packed_dev == nullptr || y_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || k <= 0 || n <= 0 || k_host < 0 || ldx < k || ldy < n) return BAS_ERR_INVALID_ARGUMENT;
   if (batch > BAS_MAX_BATCH) return BAS_ERR_UNSUPPORTED;
@@ -115,7 +124,8 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   // bulk copies: 16-byte aligned rows whose valid length is a multiple of 16 bytes
   if (!aligned16(x_dev) || !aligned16(packed_dev) || (ldx & 7) != 0 || (k & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
   if (ws_dev == nullptr || ws_bytes < bas_gemm_workspace_bytes(batch, n)) return BAS_ERR_WORKSPACE;
-  if (family < 0 || family > 2) return BAS_ERR_INVALID_ARGUMENT;
+  const int family = flags & 3;
+  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE)) != 0) return BAS_ERR_INVALID_ARGUMENT;
 
   DeviceInfo di;
   int st = device_info(&di);
@@ -143,6 +153,7 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   p.nt = nt;
   p.y = (__half*)y_dev;
   p.ldy = (long long)ldy;
+  p.flags = flags;
   p.status = (unsigned int*)ws_dev;
   p.counters = (int*)((uint8_t*)ws_dev + 256);
   p.partials = (float*)((uint8_t*)ws_dev + kWsHeaderBytes);

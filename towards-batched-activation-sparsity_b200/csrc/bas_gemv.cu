@@ -52,15 +52,6 @@ size_t gemv_smem_bytes(int nb) {
          sizeof(float) * GemvCfg<B>::kExchFloats + (size_t)GemvCfg<B>::kStages * GemvCfg<B>::kStageBytes;
 }
 
-// Rendezvous of the four warps of a group on an mbarrier (arrival count 4), bounded.
-__device__ __forceinline__ bool group_sync(uint64_t* bar, uint32_t& phase, int lane, volatile int* abort_flag) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
-  const bool ok = mbar_wait(bar, phase, abort_flag);
-  phase ^= 1u;
-  return ok;
-}
-
 template <int B>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_splitk_kernel(const GemmParams p) {
   using Cfg = GemvCfg<B>;
@@ -93,13 +84,15 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_splitk_kernel(const Gemm
     hdr->last_flag = 0;
     fence_barrier_init();
   }
-  // Stage the valid active ids; the int scratch list lives in the (still unused) ring.
-  int* s_ids32 = (int*)s_stage;
-  const int k_act = stage_active_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids32, hdr->scan, p.status);
-  for (int i = tid; i < k_act; i += blockDim.x) s_ids[i] = (uint16_t)s_ids32[i];
-  __syncthreads();
+  // Nothing above touches global memory.  The id list may be the previous kernel's output unless
+  // the caller declared it stable; X, the workspace and Y always wait.
+  const bool early_ids = (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
+  if (!early_ids) pdl_wait();
+  const int k_act = stage_active_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids, hdr->scan, p.status);
+  pdl_launch_dependents();
 
   if (k_act == 0) {
+    if (early_ids) pdl_wait();
     zero_output(p.y, p.batch, p.n, p.ldy);
     return;
   }
@@ -111,20 +104,52 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_splitk_kernel(const Gemm
   const long long u0 = part_begin(c, total, G), u1 = part_begin(c + 1, total, G);
   const int cnt = (int)(u1 - u0);
 
-  int issued = 0;
+  int issued = 0;   // tiles whose copies the producer thread has started
   if (warp == 0) {
     // ------------------------------ producer (one thread) ------------------------------
     if (lane == 0) {
-      for (int n = 0; n < cnt; ++n) {
-        const int s = n % S;
-        if (n >= S && !mbar_wait(&hdr->empty[s], ((n / S) - 1) & 1, abort_flag)) {
+      int m = 0, n0 = 0;
+      if (early_ids) {
+        // The ids are not the previous kernel's output: stream the first ring-full of weight tiles
+        // while that kernel is still draining, then wait for it before touching the activations.
+        int ahead = 0;
+        for (int n = 0; n < cnt && ahead < S; ++n) {
+          const long long u = u0 + n;
+          const int t = (int)(u / k_act), j = s_ids[(int)(u - (long long)t * k_act)];
+          if (j == kSkipId) continue;
+          const int kvalid = min(kBlockK, p.k - j * kBlockK);
+          mbar_arrive_expect_tx(&hdr->full[ahead], kTileBytes + B * kvalid * 2);
+          bulk_copy_g2s(s_stage + (size_t)ahead * Cfg::kStageBytes, p.packed + ((size_t)j * p.nt + t) * kTileBytes,
+                        kTileBytes, &hdr->full[ahead]);
+          ++ahead;
+        }
+        issued = ahead;
+        pdl_wait();
+        for (; n0 < cnt && m < ahead; ++n0) {
+          const long long u = u0 + n0;
+          const int j = s_ids[(int)(u % k_act)];
+          if (j == kSkipId) continue;
+          const int kvalid = min(kBlockK, p.k - j * kBlockK);
+          uint8_t* st = s_stage + (size_t)m * Cfg::kStageBytes;
+#pragma unroll
+          for (int b = 0; b < B; ++b) {
+            bulk_copy_g2s(st + kTileBytes + b * 128, p.x + (size_t)b * p.ldx + (size_t)j * kBlockK, kvalid * 2,
+                          &hdr->full[m]);
+          }
+          ++m;
+        }
+      }
+      for (int n = n0; n < cnt; ++n) {
+        const long long u = u0 + n;
+        const int t = (int)(u / k_act), i = (int)(u - (long long)t * k_act);
+        const int j = s_ids[i];
+        if (j == kSkipId) continue;
+        const int s = m % S;
+        if (m >= S && !mbar_wait(&hdr->empty[s], ((m / S) - 1) & 1, abort_flag)) {
           atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
           hdr->abort_flag = 1;
           break;
         }
-        const long long u = u0 + n;
-        const int t = (int)(u / k_act), i = (int)(u - (long long)t * k_act);
-        const int j = s_ids[i];
         const int kvalid = min(kBlockK, p.k - j * kBlockK);
         uint8_t* st = s_stage + (size_t)s * Cfg::kStageBytes;
         mbar_arrive_expect_tx(&hdr->full[s], kTileBytes + B * kvalid * 2);
@@ -134,21 +159,23 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_splitk_kernel(const Gemm
           bulk_copy_g2s(st + kTileBytes + b * 128, p.x + (size_t)b * p.ldx + (size_t)j * kBlockK, kvalid * 2,
                         &hdr->full[s]);
         }
-        issued = n + 1;
+        issued = ++m;
       }
     }
   } else if (warp == 1) {
     // ------------------------------ converter: fp16 -> fp32 activations ------------------------------
+    int m = 0;
     for (int n = 0; n < cnt; ++n) {
-      const int s = n % S;
-      if (!mbar_wait(&hdr->full[s], (n / S) & 1, abort_flag)) {
+      const long long u = u0 + n;
+      const int j = s_ids[(int)(u % k_act)];
+      if (j == kSkipId) continue;
+      const int s = m % S;
+      if (!mbar_wait(&hdr->full[s], (m / S) & 1, abort_flag)) {
         atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
         hdr->abort_flag = 1;
         break;
       }
-      const long long u = u0 + n;
-      const int i = (int)(u % k_act);
-      const int kvalid = min(kBlockK, p.k - (int)s_ids[i] * kBlockK);
+      const int kvalid = min(kBlockK, p.k - j * kBlockK);
       const uint8_t* st = s_stage + (size_t)s * Cfg::kStageBytes;
       float* xf = (float*)(st + kTileBytes + Cfg::kXBytes);
 #pragma unroll
@@ -160,6 +187,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_splitk_kernel(const Gemm
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&hdr->xready[s]);
+      ++m;
     }
   } else {
     // ------------------------------ consumers ------------------------------
@@ -169,21 +197,23 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_splitk_kernel(const Gemm
     float acc[B][2];
 #pragma unroll
     for (int b = 0; b < B; ++b) acc[b][0] = acc[b][1] = 0.f;
-    int seg = 0;
+    int seg = 0, m = 0;
     int seg_i0 = (int)(u0 % k_act);
     const int t_first = (int)(u0 / k_act);
     uint32_t fix_phase = 0;
     bool ok = true;
+    if (early_ids) pdl_wait();   // before the first write to the workspace or Y
 
     for (int n = 0; n < cnt && ok; ++n) {
       const long long u = u0 + n;
       const int t = (int)(u / k_act), i = (int)(u - (long long)t * k_act);
-      if ((n & 1) == g) {
-        const int s = n % S;
+      const bool skip = s_ids[i] == kSkipId;
+      if (!skip && (m & 1) == g) {
+        const int s = m % S;
         // xready implies full (the converter waited on it); observing full directly as well makes
         // the bulk copy's writes visible to this thread without relying on transitivity.
-        if (!mbar_wait(&hdr->xready[s], (n / S) & 1, abort_flag) ||
-            !mbar_wait(&hdr->full[s], (n / S) & 1, abort_flag)) {
+        if (!mbar_wait(&hdr->xready[s], (m / S) & 1, abort_flag) ||
+            !mbar_wait(&hdr->full[s], (m / S) & 1, abort_flag)) {
           ok = false;
           break;
         }
@@ -214,6 +244,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_splitk_kernel(const Gemm
         __syncwarp();
         if (lane == 0) mbar_arrive(&hdr->empty[s]);
       }
+      if (!skip) ++m;
 
       if (i == k_act - 1 || n == cnt - 1) {
         // ---- end of a segment: all of this CTA's blocks of column tile t ----
@@ -240,52 +271,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_splitk_kernel(const Gemm
           for (int b = 0; b < B; ++b) v[b] += ex[b * 128 + r];   // fixed order: group 0 + group 1
           __syncwarp();
           if (lane == 0) mbar_arrive(&hdr->exch_empty[e]);
-
-          const int col = t * kTileN + r;
           const bool complete = (seg_i0 == 0) && (i == k_act - 1);
-          if (complete) {
-            if (col < p.n) {
-#pragma unroll
-              for (int b = 0; b < B; ++b) p.y[(size_t)b * p.ldy + col] = __float2half_rn(v[b]);
-            }
-          } else {
-            const int slot = (t == t_first) ? 0 : 1;
-            float* part = p.partials + ((size_t)(c * 2 + slot) * B) * 128;
-#pragma unroll
-            for (int b = 0; b < B; ++b) part[b * 128 + r] = v[b];
-            __threadfence();
-            if (!group_sync(&hdr->fix_bar, fix_phase, lane, abort_flag)) {
-              ok = false;
-              break;
-            }
-            const int cf = part_owner((long long)t * k_act, total, G);
-            const int cl = part_owner((long long)(t + 1) * k_act - 1, total, G);
-            if (r == 0) {
-              const int old = atomicAdd(p.counters + t, 1);
-              const int last = (old == cl - cf) ? 1 : 0;
-              if (last) p.counters[t] = 0;  // every contributor has arrived: re-arm for the next call
-              hdr->last_flag = last;
-            }
-            if (!group_sync(&hdr->fix_bar, fix_phase, lane, abort_flag)) {
-              ok = false;
-              break;
-            }
-            if (hdr->last_flag) {
-              __threadfence();
-              float sum[B];
-#pragma unroll
-              for (int b = 0; b < B; ++b) sum[b] = 0.f;
-              for (int cc = cf; cc <= cl; ++cc) {   // CTA order, independent of who arrived when
-                const int sl = ((int)(part_begin(cc, total, G) / k_act) == t) ? 0 : 1;
-                const float* pp = p.partials + ((size_t)(cc * 2 + sl) * B) * 128;
-#pragma unroll
-                for (int b = 0; b < B; ++b) sum[b] += __ldcg(pp + b * 128 + r);
-              }
-              if (col < p.n) {
-#pragma unroll
-                for (int b = 0; b < B; ++b) p.y[(size_t)b * p.ldy + col] = __float2half_rn(sum[b]);
-              }
-            }
+          if (!store_or_combine<B>(v, B, p.y, p.ldy, p.n, p.partials, p.counters, t, t_first, complete, c, G, k_act,
+                                   total, r, lane, &hdr->fix_bar, fix_phase, &hdr->last_flag, abort_flag)) {
+            ok = false;
+            break;
           }
         }
 #pragma unroll
@@ -323,9 +313,8 @@ cudaError_t launch_gemv_b(const GemmParams& p, int sm_count, cudaStream_t stream
   }
   const long long units = (long long)(p.bitmap != nullptr ? p.nb : p.k_host) * p.nt;
   const int grid = (int)(units < sm_count ? (units < 1 ? 1 : units) : sm_count);
-  gemv_splitk_kernel<B><<<grid, kGemvThreads, smem, stream>>>(p);
   count_launch();
-  return cudaGetLastError();
+  return launch_with_pdl(gemv_splitk_kernel<B>, grid, kGemvThreads, smem, stream, p);
 }
 
 }  // namespace

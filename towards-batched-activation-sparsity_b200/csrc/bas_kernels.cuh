@@ -16,10 +16,33 @@ struct GemmParams {
   int batch, k, n, nb, nt;
   __half* y;                // [batch, N], row stride ldy
   long long ldy;
+  int flags;                // kFlag* bits
   unsigned int* status;     // workspace: status word
   int* counters;            // workspace: one arrival counter per column tile
   float* partials;          // workspace: [grid][2][batch][128] fp32
 };
+
+constexpr int kFlagStableIds = 16;   // BAS_GEMM_IDS_STABLE: the id list is not written by the previous kernel
+
+// Launch with the programmatic-serialization attribute, so that this kernel's preamble (and, when
+// the ids are stable, its weight copies) may overlap the tail of the previous kernel in the stream.
+// BAS_PDL=0 in the environment turns the attribute off.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+cudaError_t launch_with_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t stream,
+                            Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 // Host launchers (defined next to their kernels).  `sm_count` is the persistent grid's upper bound.
 cudaError_t launch_gemv(const GemmParams& p, int sm_count, cudaStream_t stream);

@@ -57,14 +57,6 @@ size_t umma_smem_bytes(int nb) {
          (size_t)UmmaCfg<BPAD>::kStages * UmmaCfg<BPAD>::kStageBytes;
 }
 
-__device__ __forceinline__ bool epi_sync(uint64_t* bar, uint32_t& phase, int lane, volatile int* abort_flag) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
-  const bool ok = mbar_wait(bar, phase, abort_flag);
-  phase ^= 1u;
-  return ok;
-}
-
 template <int BPAD>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
     umma_splitk_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
@@ -101,9 +93,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     tmem_alloc(&hdr->tmem_base, kTmemCols);
     tmem_relinquish();
   }
-  int* s_ids32 = (int*)s_stage;
-  const int k_act = stage_active_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids32, hdr->scan, p.status);
-  for (int i = tid; i < k_act; i += blockDim.x) s_ids[i] = (uint16_t)s_ids32[i];
+  // Nothing above touches global memory.  The id list may be the previous kernel's output unless
+  // the caller declared it stable; X, the workspace and Y always wait.
+  const bool early_ids = (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
+  if (!early_ids) pdl_wait();
+  const int k_act = stage_active_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids, hdr->scan, p.status);
+  pdl_launch_dependents();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -119,60 +114,107 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   int issued = 0;  // tiles whose copies the producer thread has started
 
   if (k_act == 0) {
+    if (early_ids) pdl_wait();
     zero_output(p.y, p.batch, p.n, p.ldy);
   } else if (cnt > 0) {
     if (warp == 0) {
       // ------------------------------ producer (one thread) ------------------------------
       if (lane == 0) {
-        for (int n = 0; n < cnt; ++n) {
-          const int s = n % S;
-          if (n >= S && !mbar_wait(&hdr->empty[s], ((n / S) - 1) & 1, abort_flag)) {
+        int m = 0, n0 = 0;
+        if (early_ids) {
+          // The ids are not the previous kernel's output: stream the first ring-full of weight
+          // tiles while that kernel is still draining, then wait for it before loading X.
+          int ahead = 0;
+          for (int n = 0; n < cnt && ahead < S; ++n) {
+            const long long u = u0 + n;
+            const int t = (int)(u / k_act), j = s_ids[(int)(u - (long long)t * k_act)];
+            if (j == kSkipId) continue;
+            mbar_arrive_expect_tx(&hdr->full[ahead], kTileBytes + Cfg::kXTileBytes);
+            bulk_copy_g2s(s_stage + (size_t)ahead * Cfg::kStageBytes, p.packed + ((size_t)j * p.nt + t) * kTileBytes,
+                          kTileBytes, &hdr->full[ahead]);
+            ++ahead;
+          }
+          issued = ahead;
+          pdl_wait();
+          for (; n0 < cnt && m < ahead; ++n0) {
+            const long long u = u0 + n0;
+            const int j = s_ids[(int)(u % k_act)];
+            if (j == kSkipId) continue;
+            tma_load_2d(s_stage + (size_t)m * Cfg::kStageBytes + kTileBytes, &xmap, j * kBlockK, 0, &hdr->full[m]);
+            ++m;
+          }
+        }
+        for (int n = n0; n < cnt; ++n) {
+          const long long u = u0 + n;
+          const int t = (int)(u / k_act), i = (int)(u - (long long)t * k_act);
+          const int j = s_ids[i];
+          if (j == kSkipId) continue;
+          const int s = m % S;
+          if (m >= S && !mbar_wait(&hdr->empty[s], ((m / S) - 1) & 1, abort_flag)) {
             atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
             hdr->abort_flag = 1;
             break;
           }
-          const long long u = u0 + n;
-          const int t = (int)(u / k_act), i = (int)(u - (long long)t * k_act);
-          const int j = s_ids[i];
           uint8_t* st = s_stage + (size_t)s * Cfg::kStageBytes;
           mbar_arrive_expect_tx(&hdr->full[s], kTileBytes + Cfg::kXTileBytes);
           bulk_copy_g2s(st, p.packed + ((size_t)j * p.nt + t) * kTileBytes, kTileBytes, &hdr->full[s]);
           tma_load_2d(st + kTileBytes, &xmap, j * kBlockK, 0, &hdr->full[s]);
-          issued = n + 1;
+          issued = ++m;
         }
       }
     } else if (warp == 1) {
       // ------------------------------ MMA issuer (one thread) ------------------------------
       if (lane == 0) {
-        int seg = 0;
+        int seg = 0, m = 0;
+        bool fresh = true;      // the next MMA overwrites the accumulator instead of adding to it
+        bool any = false;       // this segment has issued at least one MMA
         for (int n = 0; n < cnt; ++n) {
           const long long u = u0 + n;
           const int i = (int)(u % k_act);
-          const int s = n % S;
           const int a = seg & 1;
-          const bool first = (n == 0) || (i == 0);
-          bool ok = true;
-          if (first && seg >= 2) ok = mbar_wait(&hdr->acc_empty[a], ((seg >> 1) - 1) & 1, abort_flag);
-          if (ok) ok = mbar_wait(&hdr->full[s], (n / S) & 1, abort_flag);
-          if (!ok) {
-            atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
-            hdr->abort_flag = 1;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t st = smem_u32(s_stage + (size_t)s * Cfg::kStageBytes);
-          const uint64_t adesc = umma_desc_kmajor_sw128(st);
-          const uint64_t bdesc = umma_desc_kmajor_sw128(st + kTileBytes);
-          const uint32_t d = tmem_base + (uint32_t)(a * 64);
+          const bool skip = s_ids[i] == kSkipId;
+          const bool last_of_seg = (i == k_act - 1 || n == cnt - 1);
+          if (!skip) {
+            const int s = m % S;
+            bool ok = true;
+            if (fresh && seg >= 2) ok = mbar_wait(&hdr->acc_empty[a], ((seg >> 1) - 1) & 1, abort_flag);
+            if (ok) ok = mbar_wait(&hdr->full[s], (m / S) & 1, abort_flag);
+            if (!ok) {
+              atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
+              hdr->abort_flag = 1;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t st = smem_u32(s_stage + (size_t)s * Cfg::kStageBytes);
+            const uint64_t adesc = umma_desc_kmajor_sw128(st);
+            const uint64_t bdesc = umma_desc_kmajor_sw128(st + kTileBytes);
+            const uint32_t d = tmem_base + (uint32_t)(a * 64);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units
-            umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc, (first && ks == 0) ? 0u : 1u);
+            for (int ks = 0; ks < 4; ++ks) {
+              // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units
+              umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc, (fresh && ks == 0) ? 0u : 1u);
+            }
+            umma_commit(&hdr->empty[s]);  // the stage is free once these MMAs have read it
+            fresh = false;
+            any = true;
+            ++m;
           }
-          umma_commit(&hdr->empty[s]);  // the stage is free once these MMAs have read it
-          if (i == k_act - 1 || n == cnt - 1) {
-            umma_commit(&hdr->acc_full[a]);
+          if (last_of_seg) {
+            // A segment made only of skipped units issues no MMA: the epilogue (which checks the
+            // id list itself) then takes zeros instead of reading an accumulator nobody wrote.
+            if (any) {
+              umma_commit(&hdr->acc_full[a]);
+            } else {
+              if (seg >= 2 && !mbar_wait(&hdr->acc_empty[a], ((seg >> 1) - 1) & 1, abort_flag)) {
+                atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
+                hdr->abort_flag = 1;
+                break;
+              }
+              mbar_arrive(&hdr->acc_full[a]);
+            }
             ++seg;
+            fresh = true;
+            any = false;
           }
         }
       }
@@ -185,6 +227,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       int seg = 0;
       long long us = u0;
       bool ok = true;
+      if (early_ids) pdl_wait();            // before the first write to the workspace or Y
       while (us < u1 && ok) {
         const int t = (int)(us / k_act);
         const long long ue = min(u1, (long long)(t + 1) * k_act);
@@ -196,67 +239,28 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         }
         tc_fence_after_sync();
         float v[BPAD];
+        bool has_data = false;
+        for (int i = i0 + lane; i < i1; i += 32) has_data |= (s_ids[i] != kSkipId);
+        has_data = __any_sync(0xffffffffu, has_data);
+        if (has_data) {
 #pragma unroll
-        for (int cc = 0; cc < BPAD / 16; ++cc) {
-          uint32_t regs[16];
-          tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 64 + cc * 16), regs);
+          for (int cc = 0; cc < BPAD / 16; ++cc) {
+            uint32_t regs[16];
+            tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 64 + cc * 16), regs);
 #pragma unroll
-          for (int e = 0; e < 16; ++e) v[cc * 16 + e] = __uint_as_float(regs[e]);
+            for (int e = 0; e < 16; ++e) v[cc * 16 + e] = __uint_as_float(regs[e]);
+          }
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int b = 0; b < BPAD; ++b) v[b] = 0.f;
         }
-        tmem_ld_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&hdr->acc_empty[a]);
-
-        const int col = t * kTileN + r;
         const bool complete = (i0 == 0) && (i1 == k_act);
-        if (complete) {
-          if (col < p.n) {
-#pragma unroll
-            for (int b = 0; b < BPAD; ++b)
-              if (b < p.batch) p.y[(size_t)b * p.ldy + col] = __float2half_rn(v[b]);
-          }
-        } else {
-          const int slot = (t == t_first) ? 0 : 1;
-          float* part = p.partials + ((size_t)(c * 2 + slot) * p.batch) * 128;
-#pragma unroll
-          for (int b = 0; b < BPAD; ++b)
-            if (b < p.batch) part[b * 128 + r] = v[b];
-          __threadfence();
-          if (!epi_sync(&hdr->fix_bar, fix_phase, lane, abort_flag)) {
-            ok = false;
-            break;
-          }
-          const int cf = part_owner((long long)t * k_act, total, G);
-          const int cl = part_owner((long long)(t + 1) * k_act - 1, total, G);
-          if (tid == 64) {
-            const int old = atomicAdd(p.counters + t, 1);
-            const int last = (old == cl - cf) ? 1 : 0;
-            if (last) p.counters[t] = 0;  // every contributor has arrived: re-arm for the next call
-            hdr->last_flag = last;
-          }
-          if (!epi_sync(&hdr->fix_bar, fix_phase, lane, abort_flag)) {
-            ok = false;
-            break;
-          }
-          if (hdr->last_flag) {
-            __threadfence();
-#pragma unroll
-            for (int b = 0; b < BPAD; ++b) v[b] = 0.f;
-            for (int cc = cf; cc <= cl; ++cc) {   // CTA order, independent of who arrived when
-              const int sl = ((int)(part_begin(cc, total, G) / k_act) == t) ? 0 : 1;
-              const float* pp = p.partials + ((size_t)(cc * 2 + sl) * p.batch) * 128;
-#pragma unroll
-              for (int b = 0; b < BPAD; ++b)
-                if (b < p.batch) v[b] += __ldcg(pp + b * 128 + r);
-            }
-            if (col < p.n) {
-#pragma unroll
-              for (int b = 0; b < BPAD; ++b)
-                if (b < p.batch) p.y[(size_t)b * p.ldy + col] = __float2half_rn(v[b]);
-            }
-          }
-        }
+        ok = store_or_combine<BPAD>(v, p.batch, p.y, p.ldy, p.n, p.partials, p.counters, t, t_first, complete, c, G,
+                                    k_act, total, r, lane, &hdr->fix_bar, fix_phase, &hdr->last_flag, abort_flag);
         ++seg;
         us = ue;
       }
@@ -364,9 +368,8 @@ cudaError_t launch_umma_b(const GemmParams& p, int sm_count, cudaStream_t stream
   if (e != cudaSuccess) return e;
   const long long units = (long long)(p.bitmap != nullptr ? p.nb : p.k_host) * p.nt;
   const int grid = (int)(units < sm_count ? (units < 1 ? 1 : units) : sm_count);
-  umma_splitk_kernel<BPAD><<<grid, kUmmaThreads, smem, stream>>>(p, xmap);
   count_launch();
-  return cudaGetLastError();
+  return launch_with_pdl(umma_splitk_kernel<BPAD>, grid, kUmmaThreads, smem, stream, p, xmap);
 }
 
 }  // namespace
