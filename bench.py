@@ -421,7 +421,7 @@ def run_gpu(args) -> None:
     if rank == 0:
         dom = per_batch["64"]
         roofline = {
-            "bound": "hbm", "kernel": "umma_splitk_kernel<64> (B=64, 83 of 172 blocks)",
+            "bound": "hbm", "kernel": "umma_colsplit_kernel<64> (B=64, 83 of 172 blocks)",
             "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
             "algorithmic_bytes_per_launch": N_KEEP[64] * SLAB_BYTES, "traffic": None,
@@ -429,7 +429,7 @@ def run_gpu(args) -> None:
         tp = ROOT / "profiles" / "traffic.json"
         if tp.exists():
             try:
-                roofline["traffic"] = json.loads(tp.read_text()).get("umma_splitk_kernel_b64_bytes_per_launch")
+                roofline["traffic"] = json.loads(tp.read_text()).get("umma_colsplit_kernel_b64_bytes_per_launch")
             except (ValueError, OSError):
                 pass
         cpu = cpu_baseline() if world == 1 else None

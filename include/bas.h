@@ -30,7 +30,7 @@ extern "C" {
 #endif
 
 #define BAS_BLOCK_K 64   /* channels per activation block: INDEX_BLOCK_META_SIZE, kernels/...min_runtime.py:17 */
-#define BAS_TILE_N 128   /* output columns per packed weight tile */
+#define BAS_TILE_N 128   /* widest column sub-tile one kernel pass handles */
 #define BAS_MAX_BLOCKS 4096 /* largest K/64 the kernels accept */
 #define BAS_MAX_BATCH 64 /* largest decode batch of one call */
 
@@ -62,9 +62,10 @@ BAS_API unsigned long long bas_launch_count(void);
 /* ---- weight prepack -------------------------------------------------------------------------
  * Replaces _get_prepacked_weight_block_major (kernels/...min_runtime.py:3133-3163): a one-time
  * repack of an nn.Linear weight W[N, K] (row stride ldw elements).  The reference packs to
- * [K/64, 64, N]; this library packs to its own tile-major layout [ceil(K/64)][ceil(N/128)][128][64]
- * with the 128-byte shared-memory swizzle pre-applied, so that every (block, column-tile) pair is
- * one contiguous 16 KiB chunk.  The packed tensor is opaque to callers, as it is in the reference. */
+ * [K/64, 64, N]; this library packs to its own layout [ceil(K/64)][N rounded up to 8][64]: per block,
+ * one 128-byte row per output column with the 128-byte shared-memory swizzle pre-applied, so that
+ * any range of output columns of a block is one contiguous chunk that lands in shared memory
+ * ready for the tensor cores.  The packed tensor is opaque to callers, as it is in the reference. */
 BAS_API size_t bas_packed_weight_bytes(int n, int k);
 BAS_API int bas_pack_weight(const void* w_dev, int n, int k, int64_t ldw, void* packed_dev, void* stream);
 
@@ -82,9 +83,8 @@ BAS_API int bas_pack_weight(const void* w_dev, int n, int k, int64_t ldw, void* 
  *   x_dev   fp16 [batch, K], row stride ldx elements (16-byte aligned rows)
  *   y_dev   fp16 [batch, N], row stride ldy elements, fully overwritten
  *   ws_dev  workspace of at least bas_gemm_workspace_bytes(batch, n) bytes, zero-filled once with
- *           bas_workspace_init() and then reusable by any number of calls that do not overlap on
- *           the GPU.  It holds the status word, the per-column-tile arrival counters and the fp32
- *           partial sums of the split-K combine.
+ *           bas_workspace_init().  It holds the device status word; the kernels keep all partial
+ *           sums on chip, so calls may share it freely.
  * Batches of 1..8 rows run the CUDA-core split-K kernel, 9..64 rows the tcgen05 kernel. */
 BAS_API size_t bas_gemm_workspace_bytes(int batch, int n);
 BAS_API int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream);
@@ -98,7 +98,9 @@ BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, con
  *             launches earlier).  The kernel is launched with programmatic stream serialization;
  *             with this flag it starts streaming weight tiles while the previous kernel is still
  *             draining, and waits for it only before reading X and writing Y.  Without the flag
- *             only the kernel's own preamble overlaps.  Ignored when count_dev is given. */
+ *             only the kernel's own preamble overlaps.  Ignored when count_dev is given.
+ *   bits 8-10 cluster size of the tcgen05 kernel: 0 = chosen by batch size, else 1, 2 or 4 CTAs
+ *             share the active blocks of one column range (reduced on chip, in rank order). */
 #define BAS_GEMM_IDS_STABLE 16
 BAS_API int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
                 const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,

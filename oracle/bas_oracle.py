@@ -36,7 +36,7 @@ from __future__ import annotations
 import numpy as np
 
 BLOCK_K = 64            # channels per activation block (INDEX_BLOCK_META_SIZE)
-TILE_N = 128            # output columns per packed weight tile
+TILE_N = 128            # widest column sub-tile one kernel pass handles
 SCORE_NORM = 0          # mean over batch of per-block L2 norm
 SCORE_ENERGY = 1        # mean over batch of per-block squared L2 norm
 
@@ -155,26 +155,26 @@ def pack_weight_block_major(w: np.ndarray, block_k: int = BLOCK_K) -> np.ndarray
     return np.ascontiguousarray(wt.reshape(nb, block_k, n))
 
 
-def pack_weight_tiles(w: np.ndarray) -> np.ndarray:
+def pack_weight_blocks(w: np.ndarray) -> np.ndarray:
     """The device library's private layout, bit for bit.
 
-    Shape [nb, nt, 128, 64] float16: tile (j, t) holds W[128t + r, 64j + c] for r < 128,
-    c < 64 (zero outside W), one 16 KiB contiguous chunk.  Inside a tile, row r is 128
-    bytes and its eight 16-byte chunks are stored at chunk position ``q ^ (r % 8)`` (the
-    128-byte shared-memory swizzle), so that a plain bulk copy of the chunk lands
-    bank-conflict-free and tensor-core-ready.
+    Shape [nb, npad, 64] float16 with npad = N rounded up to a multiple of 8: entry (j, n) holds
+    the 64 channels W[n, 64j : 64j+64] (zero outside W) as one 128-byte row, and the row's eight
+    16-byte chunks are stored at chunk position ``q ^ (n % 8)`` (the 128-byte shared-memory
+    swizzle).  Any range of output columns of a block is thus one contiguous chunk that a plain
+    bulk copy lands bank-conflict-free and tensor-core-ready.
     """
     n, k = w.shape
     nb = (k + BLOCK_K - 1) // BLOCK_K
-    nt = (n + TILE_N - 1) // TILE_N
-    wp = np.zeros((nt * TILE_N, nb * BLOCK_K), dtype=np.float16)
+    npad = (n + 7) // 8 * 8
+    wp = np.zeros((npad, nb * BLOCK_K), dtype=np.float16)
     wp[:n, :k] = w
-    t = wp.reshape(nt, TILE_N, nb, 8, 8).transpose(2, 0, 1, 3, 4)   # [nb, nt, r, q, e]
+    t = wp.reshape(npad, nb, 8, 8).transpose(1, 0, 2, 3)             # [nb, n, q, e]
     out = np.empty_like(t)
-    r = np.arange(TILE_N)
+    r = np.arange(npad)
     for q in range(8):
-        out[:, :, r, q ^ (r % 8), :] = t[:, :, r, q, :]
-    return np.ascontiguousarray(out.reshape(nb, nt, TILE_N, BLOCK_K))
+        out[:, r, q ^ (r % 8), :] = t[:, r, q, :]
+    return np.ascontiguousarray(out.reshape(nb, npad, BLOCK_K))
 
 
 # --------------------------------------------------------------------------

@@ -33,10 +33,10 @@ def test_host_only_entry_points():
 
     assert L.lib.bas_status_string(0) == b"ok"
     assert b"workspace" in L.lib.bas_status_string(3)
-    assert L.lib.bas_packed_weight_bytes(4096, 11008) == 172 * 32 * 16384   # = the fp16 weight size
-    assert L.lib.bas_packed_weight_bytes(96, 200) == 4 * 1 * 16384          # padded to whole tiles
+    assert L.lib.bas_packed_weight_bytes(4096, 11008) == 172 * 4096 * 128   # = the fp16 weight size
+    assert L.lib.bas_packed_weight_bytes(99, 200) == 4 * 104 * 128          # K to whole blocks, N to 8
     assert L.lib.bas_packed_weight_bytes(0, 64) == 0
-    assert L.lib.bas_gemm_workspace_bytes(16, 4096) > 16 * 128 * 4
+    assert L.lib.bas_gemm_workspace_bytes(16, 4096) >= 4
     assert L.lib.bas_select_workspace_bytes(11008) >= 256 + 172 * 8
     assert L.launch_count() >= 0
 
@@ -95,20 +95,15 @@ def test_drop_in_module_surface():
     assert K._PREPACK_AUTOTUNE_CONFIGS
 
 
-def test_partition_arithmetic_matches_kernel_rules():
-    """The stream-K split used by the kernels: ranges tile the unit list, owners are consistent."""
-    def begin(c, total, g):
-        return c * total // g
+def test_column_split_matches_kernel_rules():
+    """The column split used by the kernels: ranges of whole 8-column units tile the padded width."""
+    def begin(r, units, ranges):
+        return r * units // ranges * 8
 
-    def owner(u, total, g):
-        return ((u + 1) * g - 1) // total
-
-    for total, g in [(1, 148), (147, 148), (148, 148), (1088, 148), (1984, 148), (2656, 148), (5, 3), (7, 192)]:
-        covered = []
-        for c in range(g):
-            lo, hi = begin(c, total, g), begin(c + 1, total, g)
-            assert 0 <= lo <= hi <= total
-            covered += list(range(lo, hi))
-            for u in range(lo, hi):
-                assert owner(u, total, g) == c
-        assert covered == list(range(total))
+    for n, ranges in [(4096, 148), (11008, 148), (4096, 37), (4096, 74), (96, 12), (8, 1), (24000, 148)]:
+        units = (n + 7) // 8
+        ranges = min(ranges, units)
+        edges = [begin(r, units, ranges) for r in range(ranges + 1)]
+        assert edges[0] == 0 and edges[-1] == units * 8
+        widths = np.diff(edges)
+        assert (widths > 0).all() and widths.max() - widths.min() <= 8 and (widths % 8 == 0).all()

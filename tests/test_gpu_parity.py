@@ -25,7 +25,7 @@ def _ops():
     return ops
 
 
-def _run_gemm(dev, x, w, ids=None, bitmap=None, family=0, count=None, k_host=None, ids_stable=False):
+def _run_gemm(dev, x, w, ids=None, bitmap=None, family=0, count=None, k_host=None, ids_stable=False, cluster=0):
     ops = _ops()
     tx, tw = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
     packed = ops.pack_weight(tw)
@@ -38,7 +38,7 @@ def _run_gemm(dev, x, w, ids=None, bitmap=None, family=0, count=None, k_host=Non
         if count is not None:
             kw["count"] = torch.tensor([count], dtype=torch.int32, device=dev)
             kw["k_host"] = k_host
-    ops.gemm(tx, packed, out, family=family, ids_stable=ids_stable, **kw)
+    ops.gemm(tx, packed, out, family=family, ids_stable=ids_stable, cluster=cluster, **kw)
     torch.cuda.synchronize()
     assert ops.read_status(dev) == 0
     return out.cpu().numpy()
@@ -48,11 +48,11 @@ def _run_gemm(dev, x, w, ids=None, bitmap=None, family=0, count=None, k_host=Non
 # prepack
 # ---------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("n,k", [(128, 64), (96, 200), (300, 520), (4096, 4096)])
+@pytest.mark.parametrize("n,k", [(128, 64), (96, 200), (300, 520), (203, 203), (4096, 4096)])
 def test_pack_is_bit_exact(dev, n, k):
     w = O.make_weight(n, k, seed=n + k)
     packed = _ops().pack_weight(torch.from_numpy(w).to(dev)).cpu().numpy()
-    want = O.pack_weight_tiles(w)
+    want = O.pack_weight_blocks(w)
     assert packed.nbytes == want.nbytes
     assert np.array_equal(packed.view(np.float16).reshape(want.shape), want)
 
@@ -62,7 +62,7 @@ def test_pack_accepts_strided_rows(dev):
     big = torch.zeros(130, 300, dtype=torch.float16, device=dev)
     big[:, :256] = torch.from_numpy(w).to(dev)
     packed = _ops().pack_weight(big[:, :256]).cpu().numpy()
-    assert np.array_equal(packed.view(np.float16).reshape(4, 2, 128, 64), O.pack_weight_tiles(w))
+    assert np.array_equal(packed.view(np.float16).reshape(4, 136, 64), O.pack_weight_blocks(w))
 
 
 # ---------------------------------------------------------------------------------------------
@@ -98,6 +98,28 @@ def test_small_batches_agree_on_both_kernel_families(dev, b):
     y2 = _run_gemm(dev, x, w, ids=ids, family=2)
     assert O.max_err_ratio(y1, ref) <= TOL and O.max_err_ratio(y2, ref) <= TOL
     assert O.max_err_ratio(y1, y2.astype(np.float32)) <= 1e-3
+
+
+@pytest.mark.parametrize("b", [9, 16, 33, 64])
+@pytest.mark.parametrize("cluster", [1, 2, 4])
+def test_cluster_sizes_agree(dev, b, cluster):
+    """The tcgen05 kernel with the active blocks split over 1, 2 or 4 CTAs per column range."""
+    x = O.make_activations(b, 11008, seed=b, dist="laplace")
+    w = O.make_weight(4096, 11008, seed=2)
+    for n_keep in (1, 3, 62):
+        ids = O.random_active_blocks(172, n_keep, seed=b + n_keep)
+        y = _run_gemm(dev, x, w, ids=ids, cluster=cluster)
+        assert O.max_err_ratio(y, O.masked_gemm(x, w, ids)) <= TOL
+
+
+@pytest.mark.parametrize("b,n", [(2, 24000), (16, 24000), (64, 20000)])
+def test_wide_outputs_use_several_sub_tiles(dev, b, n):
+    """More than 128 columns per CTA: the column range is walked in sub-tiles."""
+    x = O.make_activations(b, 512, seed=b)
+    w = O.make_weight(n, 512, seed=3)
+    ids = O.random_active_blocks(8, 5, seed=b)
+    y = _run_gemm(dev, x, w, ids=ids)
+    assert O.max_err_ratio(y, O.masked_gemm(x, w, ids)) <= TOL
 
 
 @pytest.mark.parametrize("b", [2, 16])

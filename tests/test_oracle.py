@@ -83,20 +83,18 @@ def test_prepack_matches_reference(golden):
         assert np.array_equal(O.pack_weight_block_major(w), data[f"prepack{pi}"])
 
 
-def test_tile_layout_is_a_permutation_of_the_reference_layout():
-    w = O.make_weight(200, 200, 5)
-    tiles = O.pack_weight_tiles(w)                    # [nb, nt, 128, 64] swizzled
-    nb, nt = tiles.shape[:2]
-    assert (nb, nt) == (4, 2)
-    ref = O.pack_weight_block_major(w)                # [nb, 64, N]
-    r = np.arange(128)
+def test_private_layout_is_a_permutation_of_the_reference_layout():
+    w = O.make_weight(203, 200, 5)
+    blocks = O.pack_weight_blocks(w)                  # [nb, npad, 64] swizzled
+    nb, npad = blocks.shape[:2]
+    assert (nb, npad) == (4, 208)
+    ref = O.pack_weight_block_major(w)                # [nb, 64, N] (the reference's layout)
+    r = np.arange(npad)
     for q in range(8):
-        chunk = tiles.reshape(nb, nt, 128, 8, 8)[:, :, r, q ^ (r % 8), :]   # logical chunk q
-        for t in range(nt):
-            rows = min(128, 200 - 128 * t)
-            want = ref[:, 8 * q:8 * q + 8, 128 * t:128 * t + rows].transpose(0, 2, 1)
-            assert np.array_equal(chunk[:, t, :rows], want)
-            assert not chunk[:, t, rows:].any()
+        chunk = blocks.reshape(nb, npad, 8, 8)[:, r, q ^ (r % 8), :]      # logical chunk q: [nb, npad, 8]
+        want = ref[:, 8 * q:8 * q + 8, :].transpose(0, 2, 1)              # [nb, N, 8]
+        assert np.array_equal(chunk[:, :203], want)
+        assert not chunk[:, 203:].any()
 
 
 def test_contraction_matches_reference_kernels(golden):

@@ -57,8 +57,6 @@ int device_info(DeviceInfo* out) {
 
 inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15u) == 0; }
 
-size_t partial_bytes(int batch) { return (size_t)kMaxGridCtas * 2 * (size_t)batch * 128 * sizeof(float); }
-
 }  // namespace
 }  // namespace bas
 
@@ -85,15 +83,14 @@ unsigned long long bas_launch_count(void) { return g_launches.load(std::memory_o
 
 size_t bas_packed_weight_bytes(int n, int k) {
   if (n <= 0 || k <= 0) return 0;
-  const size_t nb = ((size_t)k + kBlockK - 1) / kBlockK, nt = ((size_t)n + kTileN - 1) / kTileN;
-  return nb * nt * (size_t)kTileBytes;
+  const size_t nb = ((size_t)k + kBlockK - 1) / kBlockK;
+  return nb * (size_t)padded_cols(n) * (size_t)kRowBytes;
 }
 
 int bas_pack_weight(const void* w_dev, int n, int k, int64_t ldw, void* packed_dev, void* stream) {
   if (w_dev == nullptr || packed_dev == nullptr || n <= 0 || k <= 0 || ldw < k) return BAS_ERR_INVALID_ARGUMENT;
   if (!aligned16(packed_dev)) return BAS_ERR_INVALID_ARGUMENT;
-  if ((k + kBlockK - 1) / kBlockK > BAS_MAX_BLOCKS || (n + kTileN - 1) / kTileN > kMaxColumnTiles)
-    return BAS_ERR_UNSUPPORTED;
+  if ((k + kBlockK - 1) / kBlockK > BAS_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
   cudaError_t e = launch_pack((const __half*)w_dev, n, k, (long long)ldw, (uint8_t*)packed_dev, (cudaStream_t)stream);
   return e == cudaSuccess ? BAS_OK : cuda_fail(e);
 }
@@ -101,13 +98,12 @@ int bas_pack_weight(const void* w_dev, int n, int k, int64_t ldw, void* packed_d
 size_t bas_gemm_workspace_bytes(int batch, int n) {
   (void)n;
   if (batch <= 0) return 0;
-  return kWsHeaderBytes + partial_bytes(batch > BAS_MAX_BATCH ? BAS_MAX_BATCH : batch);
+  return kWsBytes;
 }
 
 int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream) {
   if (ws_dev == nullptr || ws_bytes == 0) return BAS_ERR_INVALID_ARGUMENT;
-  const size_t header = ws_bytes < kWsHeaderBytes ? ws_bytes : kWsHeaderBytes;
-  cudaError_t e = cudaMemsetAsync(ws_dev, 0, header, (cudaStream_t)stream);
+  cudaError_t e = cudaMemsetAsync(ws_dev, 0, ws_bytes, (cudaStream_t)stream);
   return e == cudaSuccess ? BAS_OK : cuda_fail(e);
 }
 
@@ -117,15 +113,15 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   if (x_dev == nullptr || packed_dev == nullptr || y_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || k <= 0 || n <= 0 || k_host < 0 || ldx < k || ldy < n) return BAS_ERR_INVALID_ARGUMENT;
   if (batch > BAS_MAX_BATCH) return BAS_ERR_UNSUPPORTED;
-  const int nb = (k + kBlockK - 1) / kBlockK, nt = (n + kTileN - 1) / kTileN;
-  if (nb > BAS_MAX_BLOCKS || nt > kMaxColumnTiles) return BAS_ERR_UNSUPPORTED;
+  const int nb = (k + kBlockK - 1) / kBlockK;
+  if (nb > BAS_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
   if (bitmap_dev == nullptr && ids_dev == nullptr && k_host > 0) return BAS_ERR_INVALID_ARGUMENT;
   if (bitmap_dev == nullptr && k_host > nb) return BAS_ERR_INVALID_ARGUMENT;  // ids are distinct
   // bulk copies: 16-byte aligned rows whose valid length is a multiple of 16 bytes
   if (!aligned16(x_dev) || !aligned16(packed_dev) || (ldx & 7) != 0 || (k & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
   if (ws_dev == nullptr || ws_bytes < bas_gemm_workspace_bytes(batch, n)) return BAS_ERR_WORKSPACE;
   const int family = flags & 3;
-  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE)) != 0) return BAS_ERR_INVALID_ARGUMENT;
+  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | 0x700)) != 0) return BAS_ERR_INVALID_ARGUMENT;
 
   DeviceInfo di;
   int st = device_info(&di);
@@ -150,15 +146,14 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   p.k = k;
   p.n = n;
   p.nb = nb;
-  p.nt = nt;
+  p.npad = padded_cols(n);
+  p.ranges = p.cluster = p.stages = p.wslot = 0;   // chosen by the launcher
   p.y = (__half*)y_dev;
   p.ldy = (long long)ldy;
   p.flags = flags;
   p.status = (unsigned int*)ws_dev;
-  p.counters = (int*)((uint8_t*)ws_dev + 256);
-  p.partials = (float*)((uint8_t*)ws_dev + kWsHeaderBytes);
 
-  const int grid_cap = di.sm_count < kMaxGridCtas ? di.sm_count : kMaxGridCtas;
+  const int grid_cap = di.sm_count;
   const bool small = (family == 1) || (family == 0 && batch <= 8);
   if (small && batch > 8) return BAS_ERR_UNSUPPORTED;
   cudaError_t e = small ? launch_gemv(p, grid_cap, s) : launch_umma(p, grid_cap, s);
@@ -307,7 +302,7 @@ int bas_linear_create(bas_linear** out, const void* w_host, int n, int k, int ma
   BAS_TRY(cudaMallocHost(&h->y_pin, (size_t)max_batch * n * 2));
   BAS_TRY(cudaMallocHost((void**)&h->ids_pin, sizeof(int32_t) * ((size_t)h->nb + 1)));
   BAS_TRY(cudaMemsetAsync(h->x_dev, 0, (size_t)max_batch * h->ldx * 2, h->stream));
-  BAS_TRY(cudaMemsetAsync(h->gemm_ws, 0, kWsHeaderBytes, h->stream));
+  BAS_TRY(cudaMemsetAsync(h->gemm_ws, 0, h->gemm_ws_bytes, h->stream));
   BAS_TRY(cudaMemsetAsync(h->sel_ws, 0, h->sel_ws_bytes, h->stream));
   BAS_TRY(cudaMemcpyAsync(w_dev, w_host, (size_t)n * k * 2, cudaMemcpyHostToDevice, h->stream));
 #undef BAS_TRY

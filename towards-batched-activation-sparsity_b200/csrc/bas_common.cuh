@@ -1,5 +1,5 @@
-// Shared device helpers: mbarrier, bulk-async copies, tcgen05 wrappers and the stream-K partition
-// arithmetic used by both contraction kernels.  sm_100a only.
+// Shared device helpers: mbarrier, bulk-async copies, tcgen05 and cluster wrappers, and the column
+// split used by both contraction kernels.  sm_100a only.
 #pragma once
 
 #include <cuda.h>
@@ -12,26 +12,17 @@
 namespace bas {
 
 constexpr int kBlockK = BAS_BLOCK_K;                 // channels per activation block
-constexpr int kTileN = BAS_TILE_N;                   // output columns per packed weight tile
-constexpr int kTileBytes = kTileN * kBlockK * 2;     // one packed (block, column-tile) chunk: 16 KiB
+constexpr int kTileN = BAS_TILE_N;                   // widest column sub-tile one pass handles
+constexpr int kRowBytes = kBlockK * 2;               // one output column's 64 fp16 weights of a block
+constexpr int kMaxStages = 32;                       // ring slots (mbarrier arrays are sized for it)
 constexpr long long kWaitCycles = 2000000000LL;      // bound of every barrier wait, about one second
+constexpr size_t kWsBytes = 256;                     // workspace: [0,4) status word, rest reserved
 
-// Workspace layout (bytes): [0,4) status word, [256, 256+4*kMaxTiles) arrival counters,
-// [kWsHeaderBytes, ...) fp32 partial sums, two slots of [batch][128] per CTA.
-constexpr int kMaxColumnTiles = 8192;                // N up to 1,048,576
-constexpr size_t kWsHeaderBytes = 256 + 4 * (size_t)kMaxColumnTiles;
-constexpr int kMaxGridCtas = 192;                    // persistent grid cap; partial slots are sized for it
-
-// ---------------------------------------------------------------------------------------------
-// stream-K partition: the flattened list of (column tile t, active block position i), u = t*k + i,
-// is cut into G contiguous ranges of equal length (+-1); CTA c owns [part_begin(c), part_begin(c+1)).
-// ---------------------------------------------------------------------------------------------
-__host__ __device__ __forceinline__ long long part_begin(long long c, long long total, long long g) {
-  return c * total / g;
-}
-// the CTA whose range contains unit u
-__host__ __device__ __forceinline__ int part_owner(long long u, long long total, long long g) {
-  return (int)(((u + 1) * g - 1) / total);
+// Column split: the (padded) output columns are cut, in units of 8 columns, into `ranges` contiguous
+// ranges of near-equal width; one CTA (or one cluster of CTAs that split the active blocks among
+// themselves) owns a range and needs no other CTA's data to finish it.
+__host__ __device__ __forceinline__ int col_begin(int range, int units, int ranges) {
+  return (int)((long long)range * units / ranges) * 8;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -163,10 +154,6 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n) {
   return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
 // ---------------------------------------------------------------------------------------------
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
 // may start while the previous kernel of the stream is still draining.  Everything before
@@ -177,61 +164,67 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-__device__ __forceinline__ int atom_add_acq_rel_gpu(int* addr, int v) {
-  int old;
-  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
-  return old;
+// ---------------------------------------------------------------------------------------------
+// Thread-block clusters: rank, barrier and distributed shared memory
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// All threads of all CTAs of the cluster; orders shared-memory writes before it against reads after it.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float dsmem_ld_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
 }
 
 // ---------------------------------------------------------------------------------------------
-// Active-set staging: every CTA builds the same list of block ids in shared memory (16-bit).
-//  * id list: copied position by position; an entry outside [0, nb) becomes kSkipId (the unit is
-//    kept in the partition and contributes nothing) and is flagged in the status word;
+// Active-set staging by ONE warp (all 32 lanes call it): builds the 16-bit id list in shared memory.
+//  * id list: copied position by position; an entry outside [0, nb) becomes kSkipId (the position
+//    is kept and contributes nothing) and is flagged in the status word;
 //  * byte map: compacted in ascending order.
-// All threads of the CTA must call this; returns the list length (units per column tile).
+// Returns the list length.  The caller publishes it to the other warps.
 // ---------------------------------------------------------------------------------------------
 constexpr uint16_t kSkipId = 0xFFFFu;
 
-__device__ __forceinline__ int stage_active_ids(const int32_t* __restrict__ ids, const int32_t* __restrict__ count_dev,
-                                                int k_host, const uint8_t* __restrict__ bitmap, int nb,
-                                                uint16_t* __restrict__ s_ids, int* __restrict__ s_scan,
-                                                unsigned int* __restrict__ status) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+__device__ __forceinline__ int warp_stage_ids(const int32_t* __restrict__ ids, const int32_t* __restrict__ count_dev,
+                                              int k_host, const uint8_t* __restrict__ bitmap, int nb,
+                                              uint16_t* __restrict__ s_ids, unsigned int* __restrict__ status,
+                                              int lane) {
   if (bitmap == nullptr) {
     int n_src = k_host;
     if (count_dev != nullptr) n_src = min(max(__ldg(count_dev), 0), k_host);
     bool bad = false;
-    for (int e = tid; e < n_src; e += blockDim.x) {
+    for (int e = lane; e < n_src; e += 32) {
       const int id = __ldg(ids + e);
       const bool ok = (id >= 0) && (id < nb);
       s_ids[e] = ok ? (uint16_t)id : kSkipId;
       bad |= !ok;
     }
-    if (bad && blockIdx.x == 0) atomicOr(status, BAS_DEV_BAD_BLOCK_ID);
-    __syncthreads();
+    bad = __any_sync(0xffffffffu, bad);
+    if (bad && lane == 0 && blockIdx.x == 0) atomicOr(status, BAS_DEV_BAD_BLOCK_ID);
+    __syncwarp();
     return n_src;
   }
-  // s_scan: 33 ints of scratch: [0..31] per-warp counts, [32] running base
-  if (tid == 0) s_scan[32] = 0;
-  __syncthreads();
-  for (int base = 0; base < nb; base += blockDim.x) {
-    const int e = base + tid;
+  int off = 0;
+  for (int base = 0; base < nb; base += 32) {
+    const int e = base + lane;
     const bool valid = (e < nb) && (bitmap[e] != 0);
     const unsigned m = __ballot_sync(0xffffffffu, valid);
-    if (lane == 0) s_scan[warp] = __popc(m);
-    __syncthreads();
-    int off = s_scan[32];
-    for (int w = 0; w < warp; ++w) off += s_scan[w];
     if (valid) s_ids[off + __popc(m & ((1u << lane) - 1u))] = (uint16_t)e;
-    __syncthreads();
-    if (tid == 0) {
-      int tot = 0;
-      for (int w = 0; w < nwarps; ++w) tot += s_scan[w];
-      s_scan[32] += tot;
-    }
-    __syncthreads();
+    off += __popc(m);
   }
-  return s_scan[32];
+  __syncwarp();
+  return off;
 }
 
 // Zero-fill of Y when the active set is empty (the reference's `out.zero_()`).
@@ -240,96 +233,6 @@ __device__ __forceinline__ void zero_output(__half* __restrict__ y, int batch, i
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     y[(i / n) * ldy + (i % n)] = __float2half_rn(0.f);
   }
-}
-
-// Rendezvous of the four warps of a 128-thread group on an mbarrier (arrival count 4), bounded.
-// Orders the group's earlier memory operations before its later ones (release / acquire, CTA scope).
-__device__ __forceinline__ bool group_sync(uint64_t* bar, uint32_t& phase, int lane, volatile int* abort_flag) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
-  const bool ok = mbar_wait(bar, phase, abort_flag);
-  phase ^= 1u;
-  return ok;
-}
-
-// ---------------------------------------------------------------------------------------------
-// Output of one segment (this CTA's share of column tile t) by a 128-thread group; thread r holds
-// the fp32 sums v[b] of output column 128 t + r.
-//  * complete segment: round and store to Y;
-//  * otherwise store the fp32 partial to this CTA's slot, publish it with one release-atomic on
-//    the tile's counter, and let the last contributor to arrive add all partials in CTA order and
-//    store Y (so the sum never depends on arrival order).  The counter re-arms itself.
-// Returns false if a bounded wait ran out.
-// ---------------------------------------------------------------------------------------------
-template <int NV>
-__device__ __forceinline__ bool store_or_combine(float (&v)[NV], int batch, __half* __restrict__ y, long long ldy,
-                                                 int n_cols, float* __restrict__ partials, int* __restrict__ counters,
-                                                 int t, int t_first, bool complete, int c, int G, int k_act,
-                                                 long long total, int r, int lane, uint64_t* fix_bar,
-                                                 uint32_t& fix_phase, int* last_flag, volatile int* abort_flag) {
-  const int col = t * kTileN + r;
-  if (complete) {
-    if (col < n_cols) {
-#pragma unroll
-      for (int b = 0; b < NV; ++b)
-        if (b < batch) y[(size_t)b * ldy + col] = __float2half_rn(v[b]);
-    }
-    return true;
-  }
-  const int slot = (t == t_first) ? 0 : 1;
-  float* part = partials + ((size_t)(c * 2 + slot) * batch) * kTileN;
-#pragma unroll
-  for (int b = 0; b < NV; ++b)
-    if (b < batch) part[b * kTileN + r] = v[b];
-  if (!group_sync(fix_bar, fix_phase, lane, abort_flag)) return false;
-  const int cf = part_owner((long long)t * k_act, total, G);
-  const int cl = part_owner((long long)(t + 1) * k_act - 1, total, G);
-  if (r == 0) {
-    // release: the group's partial stores (ordered before this thread by the rendezvous) become
-    // visible before the count; acquire: the last arriver sees every earlier contributor's stores.
-    const int old = atom_add_acq_rel_gpu(counters + t, 1);
-    const int last = (old == cl - cf) ? 1 : 0;
-    if (last) counters[t] = 0;   // every contributor has arrived: re-arm for the next call
-    *last_flag = last;
-  }
-  if (!group_sync(fix_bar, fix_phase, lane, abort_flag)) return false;
-  if (*last_flag) {
-    constexpr int BV = NV < 8 ? NV : 8;          // batch rows per pass
-    constexpr int CU = 4;                        // contributors whose loads are in flight together
-#pragma unroll
-    for (int b0 = 0; b0 < NV; b0 += BV) {
-      if (b0 < batch) {
-        float s[BV];
-#pragma unroll
-        for (int i = 0; i < BV; ++i) s[i] = 0.f;
-        for (int cc = cf; cc <= cl; cc += CU) {
-          float tmp[CU][BV];
-#pragma unroll
-          for (int j = 0; j < CU; ++j) {
-            const int cj = min(cc + j, cl);
-            const int sl = ((int)(part_begin(cj, total, G) / k_act) == t) ? 0 : 1;
-            const float* pp = partials + ((size_t)(cj * 2 + sl) * batch) * kTileN + r;
-#pragma unroll
-            for (int i = 0; i < BV; ++i)
-              tmp[j][i] = (b0 + i < batch) ? __ldcg(pp + (size_t)(b0 + i) * kTileN) : 0.f;
-          }
-#pragma unroll
-          for (int j = 0; j < CU; ++j) {
-            if (cc + j <= cl) {                  // CTA order, independent of who arrived when
-#pragma unroll
-              for (int i = 0; i < BV; ++i) s[i] += tmp[j][i];
-            }
-          }
-        }
-        if (col < n_cols) {
-#pragma unroll
-          for (int i = 0; i < BV; ++i)
-            if (b0 + i < batch) y[(size_t)(b0 + i) * ldy + col] = __float2half_rn(s[i]);
-        }
-      }
-    }
-  }
-  return true;
 }
 
 }  // namespace bas

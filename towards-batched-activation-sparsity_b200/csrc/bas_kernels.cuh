@@ -8,18 +8,21 @@ namespace bas {
 struct GemmParams {
   const __half* x;          // [batch, K], row stride ldx
   long long ldx;
-  const uint8_t* packed;    // [nb][nt][128][64] fp16, swizzled tiles of 16 KiB
+  const uint8_t* packed;    // [nb][npad][64] fp16, 16-byte chunks of row n stored at chunk q ^ (n % 8)
   const int32_t* ids;       // active block ids (or null when bitmap is given)
   const int32_t* count_dev; // optional device-side number of ids
   int k_host;               // number of ids (upper bound when count_dev is given)
   const uint8_t* bitmap;    // optional byte map [nb]
-  int batch, k, n, nb, nt;
+  int batch, k, n, nb;
+  int npad;                 // n rounded up to a multiple of 8 (rows of the packed layout)
+  int ranges;               // column ranges = CTAs (clusters) of the grid
+  int cluster;              // CTAs per cluster splitting the active blocks of one range (1, 2 or 4)
+  int stages;               // ring slots
+  int wslot;                // bytes reserved per slot for a weight chunk (multiple of 1024)
   __half* y;                // [batch, N], row stride ldy
   long long ldy;
   int flags;                // kFlag* bits
   unsigned int* status;     // workspace: status word
-  int* counters;            // workspace: one arrival counter per column tile
-  float* partials;          // workspace: [grid][2][batch][128] fp32
 };
 
 constexpr int kFlagStableIds = 16;   // BAS_GEMM_IDS_STABLE: the id list is not written by the previous kernel
@@ -29,18 +32,29 @@ constexpr int kFlagStableIds = 16;   // BAS_GEMM_IDS_STABLE: the id list is not 
 // BAS_PDL=0 in the environment turns the attribute off.
 bool pdl_enabled();
 template <typename... KArgs, typename... Args>
-cudaError_t launch_with_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t stream,
-                            Args... args) {
+cudaError_t launch_with_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, int cluster,
+                            cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3((unsigned)block);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (cluster > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = (unsigned)cluster;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = na;
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
@@ -48,6 +62,7 @@ cudaError_t launch_with_pdl(void (*kernel)(KArgs...), int grid, int block, size_
 cudaError_t launch_gemv(const GemmParams& p, int sm_count, cudaStream_t stream);
 cudaError_t launch_umma(const GemmParams& p, int sm_count, cudaStream_t stream);
 cudaError_t launch_pack(const __half* w, int n, int k, long long ldw, uint8_t* packed, cudaStream_t stream);
+inline int padded_cols(int n) { return (n + 7) / 8 * 8; }
 cudaError_t launch_build_bitmap(const int32_t* ids, const int32_t* count_dev, int k_host, int nb, uint8_t* bitmap,
                                 cudaStream_t stream);
 

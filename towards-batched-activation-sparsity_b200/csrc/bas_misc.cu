@@ -6,19 +6,21 @@ namespace bas {
 namespace {
 
 // ---------------------------------------------------------------------------------------------
-// Prepack: W[N, K] (row stride ldw) -> [nb][nt][128][64] fp16 tiles, 16-byte chunk q of tile row r
-// stored at chunk position q ^ (r % 8).  One CTA per tile, four chunks per thread.  Off the hot
-// path (once per weight), like the reference's _get_prepacked_weight_block_major
+// Prepack: W[N, K] (row stride ldw) -> [nb][npad][64] fp16: block j holds, for every output column
+// n (padded to a multiple of 8 with zero rows), its 64 channels as one 128-byte row whose 16-byte
+// chunk q is stored at chunk position q ^ (n % 8).  Any range of columns of a block is therefore one
+// contiguous, already swizzled chunk.  One CTA per (128 columns, block).  Off the hot path (once per
+// weight), like the reference's _get_prepacked_weight_block_major
 // (kernels/shared_mask_batched_triton_min_runtime.py:3133-3163).
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) pack_weight_kernel(const __half* __restrict__ w, int n, int k, long long ldw,
-                                                          uint8_t* __restrict__ packed, int nt) {
+                                                          uint8_t* __restrict__ packed, int npad) {
   const int t = blockIdx.x, j = blockIdx.y;
-  uint8_t* tile = packed + ((size_t)j * nt + t) * kTileBytes;
   const bool vec_ok = ((ldw & 7) == 0) && ((((uintptr_t)w) & 15) == 0);
   for (int idx = threadIdx.x; idx < kTileN * 8; idx += blockDim.x) {
     const int r = idx >> 3, q = idx & 7;
     const int row = t * kTileN + r, col = j * kBlockK + q * 8;
+    if (row >= npad) continue;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (row < n && col < k) {
       const __half* src = w + (size_t)row * ldw + col;
@@ -31,7 +33,7 @@ __global__ void __launch_bounds__(256) pack_weight_kernel(const __half* __restri
         v = *(const uint4*)h;
       }
     }
-    *(uint4*)(tile + r * 128 + ((q ^ (r & 7)) << 4)) = v;
+    *(uint4*)(packed + ((size_t)j * npad + row) * kRowBytes + ((q ^ (row & 7)) << 4)) = v;
   }
 }
 
@@ -177,8 +179,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
 }  // namespace
 
 cudaError_t launch_pack(const __half* w, int n, int k, long long ldw, uint8_t* packed, cudaStream_t stream) {
-  const int nb = (k + kBlockK - 1) / kBlockK, nt = (n + kTileN - 1) / kTileN;
-  pack_weight_kernel<<<dim3(nt, nb), 256, 0, stream>>>(w, n, k, ldw, packed, nt);
+  const int nb = (k + kBlockK - 1) / kBlockK, npad = padded_cols(n), nt = (npad + kTileN - 1) / kTileN;
+  pack_weight_kernel<<<dim3(nt, nb), 256, 0, stream>>>(w, n, k, ldw, packed, npad);
   count_launch();
   return cudaGetLastError();
 }

@@ -1,16 +1,24 @@
 // Swapped-operand tcgen05 kernel for decode batches of 9..64 rows.
 //
-// The 128 output columns of a packed weight tile are the MMA's M dimension, the (padded) batch is
-// its N dimension, and each 64-channel block is four K=16 steps:
-//     D[128 x Bpad] (TMEM, fp32) += Wtile[128 x 64] (smem, K-major, 128B swizzle) * Xtile[Bpad x 64]^T
-// Weight tiles arrive by 1-D bulk copies of 16 KiB (they are stored pre-swizzled), activation tiles
-// by a 2-D tensor-map copy straight from X[batch, K] with the same swizzle; rows past the batch and
-// channels past K arrive as zeros.  Work split, stream-K ranges and the order-independent split-K
-// combine are the same as in the small-batch kernel.
+// Work split: the output columns are cut into one contiguous range per CTA (or per cluster); a CTA
+// walks the active blocks and keeps the whole [columns x batch] result of its range in tensor
+// memory, so no CTA ever needs another grid-mate's partial sums through global memory.  With a
+// cluster of 2 or 4 CTAs the active blocks of one (wider) range are dealt out round-robin to the
+// cluster's CTAs and their fp32 partials are added through distributed shared memory in rank
+// order; this divides the activation traffic per SM by the cluster size and fills the MMA's 128
+// rows, which is what large batches need.
 //
-// Roles: warp 0 issues copies, warp 1 issues MMAs (one elected thread each), warps 2..5 drain the
-// accumulators (tcgen05.ld), two accumulator buffers let a drain overlap the next segment's MMAs.
-// All waits are bounded mbarrier waits; TMEM is released on every path.
+// Per active block j and column sub-tile (up to 128 columns starting at n0):
+//     D[128 x Bpad] (TMEM, fp32) += Wchunk[cols x 64] (smem, K-major, 128B swizzle) * Xtile[Bpad x 64]^T
+// Wchunk is rows n0.. of block j in the packed layout: contiguous, stored pre-swizzled, fetched by
+// one 1-D bulk copy.  Xtile comes straight from X[batch, K] by a 2-D tensor-map copy with the same
+// swizzle; rows past the batch and channels past K arrive as zeros.  The MMA always spans 128 rows:
+// rows past the chunk read whatever the ring holds there and only feed accumulator lanes that are
+// never stored.
+//
+// Roles: warp 0 stages the id list and issues copies, warp 1 issues MMAs (one elected thread each),
+// warps 2..5 drain the accumulators (tcgen05.ld); two accumulator buffers let a drain overlap the
+// next sub-tile's MMAs.  All waits are bounded mbarrier waits; TMEM is released on every path.
 //
 // Replaces, for larger batches, the reference's bitmap/index-list tl.dot kernels and their split-K
 // pairs (kernels/shared_mask_batched_triton_min_runtime.py:814-874, 1150-1216, 1956-1988).
@@ -27,65 +35,56 @@ namespace {
 
 constexpr int kUmmaThreads = 64 + 128;
 constexpr int kEpiThreads = 128;
-constexpr int kTmemCols = 128;  // two accumulator buffers of 64 fp32 columns
-
-template <int BPAD>
-struct UmmaCfg {
-  static constexpr int kXTileBytes = BPAD * 128;  // multiple of 1024 for BPAD in {16,32,48,64}
-  static constexpr int kStageBytes = kTileBytes + kXTileBytes;
-  static constexpr int kStagesRaw = (192 * 1024) / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
-};
+constexpr int kTmemCols = 128;          // two accumulator buffers of 64 fp32 columns
+constexpr int kMmaSpanBytes = 128 * kRowBytes;   // an M=128 operand read spans 16 KiB from the slot base
 
 struct UmmaSmemHeader {
-  uint64_t full[16];
-  uint64_t empty[16];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
-  uint64_t fix_bar;
+  uint64_t ids_ready;
   uint32_t tmem_base;
-  int scan[34];
+  int k_act;
   int abort_flag;
-  int last_flag;
 };
 
-__host__ __device__ inline size_t umma_ids_bytes(int nb) { return ((size_t)nb * 2 + 127) / 128 * 128; }
-
-template <int BPAD>
-size_t umma_smem_bytes(int nb) {
+inline size_t umma_ids_bytes(int nb) { return ((size_t)nb * 2 + 127) / 128 * 128; }
+inline size_t umma_fixed_smem(int nb) {
   return 1024 /*alignment slack*/ + (sizeof(UmmaSmemHeader) + 127) / 128 * 128 + umma_ids_bytes(nb) + 1024 +
-         (size_t)UmmaCfg<BPAD>::kStages * UmmaCfg<BPAD>::kStageBytes;
+         kMmaSpanBytes /*tail pad for the MMA's full-height read of the last slot*/;
 }
 
 template <int BPAD>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
-    umma_splitk_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
-  using Cfg = UmmaCfg<BPAD>;
-  constexpr int S = Cfg::kStages;
+    umma_colsplit_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
   constexpr uint32_t kIdesc = umma_idesc_f16(128, BPAD);
+  constexpr int kXTileBytes = BPAD * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sp = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
   UmmaSmemHeader* hdr = (UmmaSmemHeader*)sp;
   sp += (sizeof(UmmaSmemHeader) + 127) / 128 * 128;
   uint16_t* s_ids = (uint16_t*)sp;
-  sp += umma_ids_bytes(p.nb);
+  sp += ((size_t)p.nb * 2 + 127) / 128 * 128;
   uint8_t* s_stage = (uint8_t*)(((uintptr_t)sp + 1023) & ~(uintptr_t)1023);  // swizzle atoms need 1 KiB alignment
+  const int S = p.stages;
+  const int stage_bytes = p.wslot + kXTileBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &hdr->abort_flag;
 
-  if (tid == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(&hdr->full[s], 1);
-      mbar_init(&hdr->empty[s], 1);
-    }
+  if (tid < S) {
+    mbar_init(&hdr->full[tid], 1);
+    mbar_init(&hdr->empty[tid], 1);
+    fence_barrier_init();
+  } else if (tid == 64) {
     for (int a = 0; a < 2; ++a) {
       mbar_init(&hdr->acc_full[a], 1);
       mbar_init(&hdr->acc_empty[a], kEpiThreads / 32);
     }
-    mbar_init(&hdr->fix_bar, kEpiThreads / 32);
+    mbar_init(&hdr->ids_ready, 1);
     hdr->abort_flag = 0;
-    hdr->last_flag = 0;
+    hdr->k_act = 0;
     fence_barrier_init();
     prefetch_tensormap(&xmap);
   }
@@ -93,176 +92,186 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     tmem_alloc(&hdr->tmem_base, kTmemCols);
     tmem_relinquish();
   }
-  // Nothing above touches global memory.  The id list may be the previous kernel's output unless
-  // the caller declared it stable; X, the workspace and Y always wait.
-  const bool early_ids = (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
-  if (!early_ids) pdl_wait();
-  const int k_act = stage_active_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids, hdr->scan, p.status);
-  pdl_launch_dependents();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = hdr->tmem_base;
 
-  const long long total = (long long)k_act * p.nt;
-  // Never more ranges than units: every participating CTA then owns at least one unit, so the
-  // contributors of a column tile are a contiguous run of CTAs.
-  const int c = blockIdx.x, G = (int)max(1LL, min((long long)gridDim.x, total));
-  const long long u0 = (k_act > 0 && c < G) ? part_begin(c, total, G) : 0;
-  const long long u1 = (k_act > 0 && c < G) ? part_begin(c + 1, total, G) : 0;
-  const int cnt = (int)(u1 - u0);
-  int issued = 0;  // tiles whose copies the producer thread has started
+  // this CTA's columns and its share of the active list
+  const int C = p.cluster;
+  const int rank = (C > 1) ? (int)cluster_ctarank() : 0;
+  const int range = blockIdx.x / C;
+  const int units = p.npad >> 3;
+  const int n0 = col_begin(range, units, p.ranges), n1 = col_begin(range + 1, units, p.ranges);
+  const int width = n1 - n0;
+  const int n_sub = (width + kTileN - 1) / kTileN;
 
-  if (k_act == 0) {
-    if (early_ids) pdl_wait();
-    zero_output(p.y, p.batch, p.n, p.ldy);
-  } else if (cnt > 0) {
-    if (warp == 0) {
-      // ------------------------------ producer (one thread) ------------------------------
-      if (lane == 0) {
-        int m = 0, n0 = 0;
-        if (early_ids) {
-          // The ids are not the previous kernel's output: stream the first ring-full of weight
-          // tiles while that kernel is still draining, then wait for it before loading X.
-          int ahead = 0;
-          for (int n = 0; n < cnt && ahead < S; ++n) {
-            const long long u = u0 + n;
-            const int t = (int)(u / k_act), j = s_ids[(int)(u - (long long)t * k_act)];
-            if (j == kSkipId) continue;
-            mbar_arrive_expect_tx(&hdr->full[ahead], kTileBytes + Cfg::kXTileBytes);
-            bulk_copy_g2s(s_stage + (size_t)ahead * Cfg::kStageBytes, p.packed + ((size_t)j * p.nt + t) * kTileBytes,
-                          kTileBytes, &hdr->full[ahead]);
-            ++ahead;
-          }
-          issued = ahead;
-          pdl_wait();
-          for (; n0 < cnt && m < ahead; ++n0) {
-            const long long u = u0 + n0;
-            const int j = s_ids[(int)(u % k_act)];
-            if (j == kSkipId) continue;
-            tma_load_2d(s_stage + (size_t)m * Cfg::kStageBytes + kTileBytes, &xmap, j * kBlockK, 0, &hdr->full[m]);
-            ++m;
-          }
-        }
-        for (int n = n0; n < cnt; ++n) {
-          const long long u = u0 + n;
-          const int t = (int)(u / k_act), i = (int)(u - (long long)t * k_act);
-          const int j = s_ids[i];
+  // Nothing so far touched global memory.  The id list may be the previous kernel's output unless
+  // the caller declared it stable; X and Y always wait for the previous kernel.
+  const bool early_ids = (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
+  int k_act = 0;
+  int issued = 0;   // tiles whose copies the producer thread has started
+
+  if (warp == 0) {
+    // ------------------------------ id staging + producer ------------------------------
+    if (!early_ids) pdl_wait();
+    k_act = warp_stage_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids, p.status, lane);
+    if (lane == 0) {
+      hdr->k_act = k_act;
+      mbar_arrive(&hdr->ids_ready);
+    }
+    pdl_launch_dependents();
+    const int k_mine = (k_act > rank) ? (k_act - rank + C - 1) / C : 0;
+    const int cnt = n_sub * k_mine;
+    if (lane == 0 && cnt > 0) {
+      int m = 0, n_resume = 0;
+      if (early_ids) {
+        // Stream the first ring-full of weight chunks while the previous kernel is still draining,
+        // then wait for it before loading X.
+        int ahead = 0;
+        for (int n = 0; n < cnt && ahead < S; ++n) {
+          const int sub = n / k_mine, j = s_ids[rank + (n - sub * k_mine) * C];
           if (j == kSkipId) continue;
-          const int s = m % S;
-          if (m >= S && !mbar_wait(&hdr->empty[s], ((m / S) - 1) & 1, abort_flag)) {
-            atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
-            hdr->abort_flag = 1;
-            break;
-          }
-          uint8_t* st = s_stage + (size_t)s * Cfg::kStageBytes;
-          mbar_arrive_expect_tx(&hdr->full[s], kTileBytes + Cfg::kXTileBytes);
-          bulk_copy_g2s(st, p.packed + ((size_t)j * p.nt + t) * kTileBytes, kTileBytes, &hdr->full[s]);
-          tma_load_2d(st + kTileBytes, &xmap, j * kBlockK, 0, &hdr->full[s]);
-          issued = ++m;
+          const int wsub = min(kTileN, width - sub * kTileN);
+          mbar_arrive_expect_tx(&hdr->full[ahead], wsub * kRowBytes + kXTileBytes);
+          bulk_copy_g2s(s_stage + (size_t)ahead * stage_bytes,
+                        p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wsub * kRowBytes,
+                        &hdr->full[ahead]);
+          ++ahead;
+        }
+        issued = ahead;
+        pdl_wait();
+        for (; n_resume < cnt && m < ahead; ++n_resume) {
+          const int sub = n_resume / k_mine, j = s_ids[rank + (n_resume - sub * k_mine) * C];
+          if (j == kSkipId) continue;
+          tma_load_2d(s_stage + (size_t)m * stage_bytes + p.wslot, &xmap, j * kBlockK, 0, &hdr->full[m]);
+          ++m;
         }
       }
-    } else if (warp == 1) {
+      for (int n = n_resume; n < cnt; ++n) {
+        const int sub = n / k_mine, j = s_ids[rank + (n - sub * k_mine) * C];
+        if (j == kSkipId) continue;
+        const int s = m % S;
+        if (m >= S && !mbar_wait(&hdr->empty[s], ((m / S) - 1) & 1, abort_flag)) {
+          atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
+          hdr->abort_flag = 1;
+          break;
+        }
+        const int wsub = min(kTileN, width - sub * kTileN);
+        uint8_t* st = s_stage + (size_t)s * stage_bytes;
+        mbar_arrive_expect_tx(&hdr->full[s], wsub * kRowBytes + kXTileBytes);
+        bulk_copy_g2s(st, p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wsub * kRowBytes,
+                      &hdr->full[s]);
+        tma_load_2d(st + p.wslot, &xmap, j * kBlockK, 0, &hdr->full[s]);
+        issued = ++m;
+      }
+    }
+  } else {
+    bool ok = __all_sync(0xffffffffu, mbar_wait(&hdr->ids_ready, 0, abort_flag));
+    k_act = hdr->k_act;
+    const int k_mine = (ok && k_act > rank) ? (k_act - rank + C - 1) / C : 0;
+
+    if (warp == 1) {
       // ------------------------------ MMA issuer (one thread) ------------------------------
-      if (lane == 0) {
-        int seg = 0, m = 0;
-        bool fresh = true;      // the next MMA overwrites the accumulator instead of adding to it
-        bool any = false;       // this segment has issued at least one MMA
-        for (int n = 0; n < cnt; ++n) {
-          const long long u = u0 + n;
-          const int i = (int)(u % k_act);
-          const int a = seg & 1;
-          const bool skip = s_ids[i] == kSkipId;
-          const bool last_of_seg = (i == k_act - 1 || n == cnt - 1);
-          if (!skip) {
+      if (lane == 0 && ok) {
+        int m = 0;
+        for (int sub = 0; sub < n_sub && ok && k_mine > 0; ++sub) {
+          const int a = sub & 1;
+          bool fresh = true;   // the next MMA overwrites the accumulator instead of adding to it
+          for (int ii = 0; ii < k_mine; ++ii) {
+            if (s_ids[rank + ii * C] == kSkipId) continue;
             const int s = m % S;
-            bool ok = true;
-            if (fresh && seg >= 2) ok = mbar_wait(&hdr->acc_empty[a], ((seg >> 1) - 1) & 1, abort_flag);
+            if (fresh && sub >= 2) ok = mbar_wait(&hdr->acc_empty[a], ((sub >> 1) - 1) & 1, abort_flag);
             if (ok) ok = mbar_wait(&hdr->full[s], (m / S) & 1, abort_flag);
-            if (!ok) {
-              atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
-              hdr->abort_flag = 1;
-              break;
-            }
+            if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t st = smem_u32(s_stage + (size_t)s * Cfg::kStageBytes);
+            const uint32_t st = smem_u32(s_stage + (size_t)s * stage_bytes);
             const uint64_t adesc = umma_desc_kmajor_sw128(st);
-            const uint64_t bdesc = umma_desc_kmajor_sw128(st + kTileBytes);
+            const uint64_t bdesc = umma_desc_kmajor_sw128(st + p.wslot);
             const uint32_t d = tmem_base + (uint32_t)(a * 64);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
               // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units
               umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc, (fresh && ks == 0) ? 0u : 1u);
             }
-            umma_commit(&hdr->empty[s]);  // the stage is free once these MMAs have read it
+            umma_commit(&hdr->empty[s]);  // the slot is free once these MMAs have read it
             fresh = false;
-            any = true;
             ++m;
           }
-          if (last_of_seg) {
-            // A segment made only of skipped units issues no MMA: the epilogue (which checks the
-            // id list itself) then takes zeros instead of reading an accumulator nobody wrote.
-            if (any) {
-              umma_commit(&hdr->acc_full[a]);
-            } else {
-              if (seg >= 2 && !mbar_wait(&hdr->acc_empty[a], ((seg >> 1) - 1) & 1, abort_flag)) {
-                atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
-                hdr->abort_flag = 1;
-                break;
-              }
-              mbar_arrive(&hdr->acc_full[a]);
-            }
-            ++seg;
-            fresh = true;
-            any = false;
+          if (!ok) break;
+          if (!fresh) {
+            umma_commit(&hdr->acc_full[a]);
+          } else {
+            // Every position was a skipped id: no MMA ran; the epilogue (which checks the list
+            // itself) takes zeros.  Keep the barrier phases in step.
+            if (sub >= 2) ok = mbar_wait(&hdr->acc_empty[a], ((sub >> 1) - 1) & 1, abort_flag);
+            if (ok) mbar_arrive(&hdr->acc_full[a]);
           }
+        }
+        if (!ok) {
+          atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
+          hdr->abort_flag = 1;
         }
       }
     } else {
       // ------------------------------ epilogue: 4 warps, one TMEM lane quarter each ------------------------------
       const int q = warp & 3;               // a warp may only read TMEM lanes [32*(warp%4), +32)
-      const int r = q * 32 + lane;          // row of the tile = output column within the tile
-      const int t_first = (int)(u0 / k_act);
-      uint32_t fix_phase = 0;
-      int seg = 0;
-      long long us = u0;
-      bool ok = true;
-      if (early_ids) pdl_wait();            // before the first write to the workspace or Y
-      while (us < u1 && ok) {
-        const int t = (int)(us / k_act);
-        const long long ue = min(u1, (long long)(t + 1) * k_act);
-        const int i0 = (int)(us - (long long)t * k_act), i1 = (int)(ue - (long long)t * k_act);
-        const int a = seg & 1;
-        if (!mbar_wait(&hdr->acc_full[a], (seg >> 1) & 1, abort_flag)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-        float v[BPAD];
+      const int r = q * 32 + lane;          // row of the sub-tile = output column n0 + 128*sub + r
+      float* red = (float*)s_stage;         // cluster mode: this CTA's fp32 partial [batch][128]
+      if (early_ids) pdl_wait();            // before the first write to Y
+      if (ok && k_act == 0) {
+        // empty active set: the epilogue threads of the whole grid zero Y between them
+        const long long total = (long long)p.batch * p.n;
+        for (long long e = (long long)blockIdx.x * kEpiThreads + (tid - 64); e < total;
+             e += (long long)gridDim.x * kEpiThreads)
+          p.y[(e / p.n) * p.ldy + (e % p.n)] = __float2half_rn(0.f);
+      } else if (ok) {
         bool has_data = false;
-        for (int i = i0 + lane; i < i1; i += 32) has_data |= (s_ids[i] != kSkipId);
+        for (int ii = lane; ii < k_mine; ii += 32) has_data |= (s_ids[rank + ii * C] != kSkipId);
         has_data = __any_sync(0xffffffffu, has_data);
-        if (has_data) {
-#pragma unroll
-          for (int cc = 0; cc < BPAD / 16; ++cc) {
-            uint32_t regs[16];
-            tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 64 + cc * 16), regs);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[cc * 16 + e] = __uint_as_float(regs[e]);
+        for (int sub = 0; sub < n_sub && ok; ++sub) {
+          const int a = sub & 1;
+          float v[BPAD];
+          if (k_mine > 0) {
+            // warp-uniform verdict: tcgen05.ld below needs the whole warp
+            if (!__all_sync(0xffffffffu, mbar_wait(&hdr->acc_full[a], (sub >> 1) & 1, abort_flag))) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
           }
-          tmem_ld_wait();
-        } else {
+          if (k_mine > 0 && has_data) {
 #pragma unroll
-          for (int b = 0; b < BPAD; ++b) v[b] = 0.f;
+            for (int cc = 0; cc < BPAD / 16; ++cc) {
+              uint32_t regs[16];
+              tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 64 + cc * 16), regs);
+#pragma unroll
+              for (int e = 0; e < 16; ++e) v[cc * 16 + e] = __uint_as_float(regs[e]);
+            }
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int b = 0; b < BPAD; ++b) v[b] = 0.f;
+          }
+          if (k_mine > 0) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&hdr->acc_empty[a]);
+          }
+          if (C == 1) {
+            const int col = n0 + sub * kTileN + r;
+            if (r < width - sub * kTileN && col < p.n) {
+#pragma unroll
+              for (int b = 0; b < BPAD; ++b)
+                if (b < p.batch) p.y[(size_t)b * p.ldy + col] = __float2half_rn(v[b]);
+            }
+          } else {
+            // one sub-tile per CTA in cluster mode; the ring is idle once the accumulator is final
+#pragma unroll
+            for (int b = 0; b < BPAD; ++b)
+              if (b < p.batch) red[b * kTileN + r] = v[b];
+          }
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&hdr->acc_empty[a]);
-        const bool complete = (i0 == 0) && (i1 == k_act);
-        ok = store_or_combine<BPAD>(v, p.batch, p.y, p.ldy, p.n, p.partials, p.counters, t, t_first, complete, c, G,
-                                    k_act, total, r, lane, &hdr->fix_bar, fix_phase, &hdr->last_flag, abort_flag);
-        ++seg;
-        us = ue;
       }
       if (!ok) {
         atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
@@ -273,6 +282,28 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 
   tc_fence_before_sync();
   __syncthreads();
+  if (C > 1) {
+    // Add the cluster's partials in rank order: rank i finishes batch rows i, i+C, ...
+    cluster_sync_all();
+    if (hdr->k_act > 0 && hdr->abort_flag == 0 && warp >= 2) {
+      const int r = tid - 64;
+      const int col = n0 + r;
+      if (r < width && col < p.n) {
+        const uint32_t mine = smem_u32(s_stage) + (uint32_t)r * 4u;
+        uint32_t peer[4];
+#pragma unroll
+        for (int cr = 0; cr < 4; ++cr) peer[cr] = dsmem_addr(mine, (uint32_t)min(cr, C - 1));
+        for (int b = rank; b < p.batch; b += C) {
+          float sum = 0.f;
+#pragma unroll
+          for (int cr = 0; cr < 4; ++cr)
+            if (cr < C) sum += dsmem_ld_f32(peer[cr] + (uint32_t)(b * kTileN) * 4u);
+          p.y[(size_t)b * p.ldy + col] = __float2half_rn(sum);
+        }
+      }
+    }
+    cluster_sync_all();   // nobody leaves while a peer may still read its shared memory
+  }
   if (hdr->abort_flag != 0 && tid == 0) {
     // Gave up somewhere: do not leave while copies may still be landing in this CTA's memory.
     int zero = 0;
@@ -285,7 +316,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------------------
-// host side: tensor maps for X and the launch
+// host side: tensor maps for X, the work split and the launch
 // ---------------------------------------------------------------------------------------------
 struct MapKey {
   const void* x;
@@ -350,26 +381,93 @@ cudaError_t get_x_tensor_map(const GemmParams& p, int bpad, CUtensorMap* out) {
   return cudaSuccess;
 }
 
+constexpr size_t kSmemBudget = 224 * 1024;
+
+// How many clusters of `cluster` CTAs of this kernel the device can hold at once (cached).
 template <int BPAD>
-cudaError_t launch_umma_b(const GemmParams& p, int sm_count, cudaStream_t stream) {
-  const size_t smem = umma_smem_bytes<BPAD>(p.nb);
-  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+int max_resident_clusters(int cluster, size_t smem, int sm_count) {
+  static std::mutex mu;
+  static std::unordered_map<long long, int> cache;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const long long key = ((long long)dev << 40) ^ ((long long)cluster << 32) ^ (long long)smem;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(sm_count / cluster * cluster));
+  cfg.blockDim = dim3(kUmmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, umma_colsplit_kernel<BPAD>, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    n = 0;
+  }
+  std::lock_guard<std::mutex> lk(mu);
+  cache[key] = n;
+  return n;
+}
+
+template <int BPAD>
+cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !attr_done[dev]) {
     cudaError_t e =
-        cudaFuncSetAttribute(umma_splitk_kernel<BPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(umma_colsplit_kernel<BPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
+  const int units = p.npad / 8;
+  const size_t fixed = umma_fixed_smem(p.nb);
+  if (fixed + 4 * (kTileN * kRowBytes + BPAD * 128) > kSmemBudget) return cudaErrorInvalidValue;
+
+  // cluster size: larger batches split the active blocks of a wider range over 2 or 4 CTAs
+  int want = (p.flags >> 8) & 7;
+  if (want == 0) want = p.batch > 32 ? 4 : (p.batch > 16 ? 2 : 1);
+  int cluster = 1, ranges = sm_count < units ? sm_count : units;
+  for (int c = want; c > 1; c >>= 1) {
+    if (c != 2 && c != 4) continue;
+    const int resident = max_resident_clusters<BPAD>(c, kSmemBudget, sm_count);
+    int r = resident < units ? resident : units;
+    if (r < 1) continue;
+    const int wmax = ((units + r - 1) / r) * 8;
+    if (wmax > kTileN) continue;               // cluster mode handles one sub-tile per CTA
+    if (r * c < (sm_count * 3) / 4) continue;  // too few SMs would be busy
+    cluster = c;
+    ranges = r;
+    break;
+  }
+  const int wmax = ((units + ranges - 1) / ranges) * 8;
+  const int wsub_max = wmax < kTileN ? wmax : kTileN;
+  p.cluster = cluster;
+  p.ranges = ranges;
+  p.wslot = (wsub_max * kRowBytes + 1023) / 1024 * 1024;
+  const size_t stage_bytes = (size_t)p.wslot + BPAD * 128;
+  const size_t room = kSmemBudget - fixed;
+  int stages = (int)(room / stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return cudaErrorInvalidValue;
+  p.stages = stages;
+  size_t smem = fixed + (size_t)stages * stage_bytes;
+  const size_t red_bytes = (size_t)p.batch * kTileN * 4;   // cluster mode reuses the ring for the partial
+  if (cluster > 1 && (size_t)stages * stage_bytes < red_bytes) smem = fixed + red_bytes;
+
   CUtensorMap xmap;
   cudaError_t e = get_x_tensor_map(p, BPAD, &xmap);
   if (e != cudaSuccess) return e;
-  const long long units = (long long)(p.bitmap != nullptr ? p.nb : p.k_host) * p.nt;
-  const int grid = (int)(units < sm_count ? (units < 1 ? 1 : units) : sm_count);
   count_launch();
-  return launch_with_pdl(umma_splitk_kernel<BPAD>, grid, kUmmaThreads, smem, stream, p, xmap);
+  return launch_with_pdl(umma_colsplit_kernel<BPAD>, ranges * cluster, kUmmaThreads, smem, cluster, stream, p, xmap);
 }
 
 }  // namespace
