@@ -36,17 +36,18 @@ def needs_build() -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not needs_build():
+def build(force: bool = False, verbose: bool = False, extra_flags=(), out: Path = LIB) -> Path:
+    if not force and not needs_build() and out == LIB:
         return LIB
     objs = []
-    build_dir = HERE / "build"
+    build_dir = HERE / ("build" if out == LIB else "build_" + out.stem)
     build_dir.mkdir(exist_ok=True)
     common = [
         _nvcc(), "-std=c++17", "-O3", "-lineinfo",
         "-gencode", "arch=compute_100a,code=sm_100a",
         "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     ]
+    common += list(extra_flags)
     if verbose:
         common += ["-Xptxas", "-v"]
     procs = []
@@ -57,19 +58,21 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for src, p in procs:
-        out, _ = p.communicate()
-        if out.strip() and (verbose or p.returncode != 0):
-            print(f"--- {src}\n{out}", file=sys.stderr)
+        log, _ = p.communicate()
+        if log.strip() and (verbose or p.returncode != 0):
+            print(f"--- {src}\n{log}", file=sys.stderr)
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed; see the messages above")
-    subprocess.check_call([_nvcc(), "-shared", "-o", str(LIB)] + objs)
-    return LIB
+    subprocess.check_call([_nvcc(), "-shared", "-o", str(out)] + objs)
+    return out
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register / shared-memory usage")
+    ap.add_argument("--define", action="append", default=[], help="extra -D macro (diagnostic builds)")
+    ap.add_argument("--out", default=str(LIB), help="output path (diagnostic builds)")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force or bool(a.define), a.verbose, ["-D" + d for d in a.define], Path(a.out)))

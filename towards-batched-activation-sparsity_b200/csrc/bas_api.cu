@@ -9,6 +9,10 @@
 
 namespace bas {
 
+#ifdef BAS_TRACE
+static long long* g_trace_dev = nullptr;   // diagnostic build only
+#endif
+
 static std::atomic<unsigned long long> g_launches{0};
 static thread_local int g_last_cuda_error = 0;
 
@@ -63,6 +67,15 @@ inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15u) == 0; }
 using namespace bas;
 
 extern "C" {
+
+#ifdef BAS_TRACE
+BAS_API int bas_debug_trace(long long* out64, int reset) {
+  if (g_trace_dev == nullptr) return 1;
+  cudaError_t e = cudaMemcpy(out64, g_trace_dev, sizeof(long long) * 512, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && reset) e = cudaMemset(g_trace_dev, 0, sizeof(long long) * 512);
+  return e == cudaSuccess ? 0 : 4;
+}
+#endif
 
 const char* bas_status_string(int status) {
   switch (status) {
@@ -152,6 +165,13 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   p.ldy = (long long)ldy;
   p.flags = flags;
   p.status = (unsigned int*)ws_dev;
+#ifdef BAS_TRACE
+  if (g_trace_dev == nullptr) {
+    cudaMalloc(&g_trace_dev, sizeof(long long) * 512);
+    cudaMemset(g_trace_dev, 0, sizeof(long long) * 512);
+  }
+  p.trace = g_trace_dev;
+#endif
 
   const int grid_cap = di.sm_count;
   const bool small = (family == 1) || (family == 0 && batch <= 8);

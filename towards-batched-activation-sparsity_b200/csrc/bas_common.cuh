@@ -11,6 +11,18 @@
 
 namespace bas {
 
+// Diagnostic build (-DBAS_TRACE): CTA 0 adds the cycles its roles spend waiting and working to a
+// small device array that bas_debug_trace() copies out.  Compiled out of the product.
+#ifdef BAS_TRACE
+#define BAS_TRACE_ADD(slot, cycles) do { if (blockIdx.x == 0 && p.trace != nullptr) atomicAdd((unsigned long long*)&p.trace[slot], (unsigned long long)(cycles)); } while (0)
+#define BAS_TRACE_CLOCK() clock64()
+#define BAS_TRACE_SET(slot, v) do { if (blockIdx.x == 0 && p.trace != nullptr && (slot) < 512) p.trace[slot] = (long long)(v); } while (0)
+#else
+#define BAS_TRACE_SET(slot, v) do { } while (0)
+#define BAS_TRACE_ADD(slot, cycles) do { } while (0)
+#define BAS_TRACE_CLOCK() 0LL
+#endif
+
 constexpr int kBlockK = BAS_BLOCK_K;                 // channels per activation block
 constexpr int kTileN = BAS_TILE_N;                   // widest column sub-tile one pass handles
 constexpr int kRowBytes = kBlockK * 2;               // one output column's 64 fp16 weights of a block
@@ -44,6 +56,10 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
+}
+// Adds to the pending byte count of the current phase without arriving.
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -188,41 +204,56 @@ __device__ __forceinline__ float dsmem_ld_f32(uint32_t addr) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Active-set staging by ONE warp (all 32 lanes call it): builds the 16-bit id list in shared memory.
-//  * id list: copied position by position; an entry outside [0, nb) becomes kSkipId (the position
-//    is kept and contributes nothing) and is flagged in the status word;
-//  * byte map: compacted in ascending order.
+// Active-set staging by ONE warp (all 32 lanes call it): builds the compact 16-bit list of valid
+// block ids in shared memory, in input order.
+//  * id list: an entry outside [0, nb) is dropped and flagged in the status word;
+//  * byte map: the non-zero positions in ascending order.
 // Returns the list length.  The caller publishes it to the other warps.
 // ---------------------------------------------------------------------------------------------
-constexpr uint16_t kSkipId = 0xFFFFu;
-
 __device__ __forceinline__ int warp_stage_ids(const int32_t* __restrict__ ids, const int32_t* __restrict__ count_dev,
                                               int k_host, const uint8_t* __restrict__ bitmap, int nb,
                                               uint16_t* __restrict__ s_ids, unsigned int* __restrict__ status,
                                               int lane) {
+  int n_src = nb;
   if (bitmap == nullptr) {
-    int n_src = k_host;
+    n_src = k_host;
     if (count_dev != nullptr) n_src = min(max(__ldg(count_dev), 0), k_host);
-    bool bad = false;
-    for (int e = lane; e < n_src; e += 32) {
-      const int id = __ldg(ids + e);
-      const bool ok = (id >= 0) && (id < nb);
-      s_ids[e] = ok ? (uint16_t)id : kSkipId;
-      bad |= !ok;
-    }
-    bad = __any_sync(0xffffffffu, bad);
-    if (bad && lane == 0 && blockIdx.x == 0) atomicOr(status, BAS_DEV_BAD_BLOCK_ID);
-    __syncwarp();
-    return n_src;
   }
   int off = 0;
-  for (int base = 0; base < nb; base += 32) {
-    const int e = base + lane;
-    const bool valid = (e < nb) && (bitmap[e] != 0);
-    const unsigned m = __ballot_sync(0xffffffffu, valid);
-    if (valid) s_ids[off + __popc(m & ((1u << lane) - 1u))] = (uint16_t)e;
-    off += __popc(m);
+  bool bad = false;
+  // Loads are issued eight chunks at a time so that their latencies overlap; the compaction that
+  // follows is a ballot per chunk.
+  for (int base0 = 0; base0 < n_src; base0 += 256) {
+    int raw[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int e = base0 + u * 32 + lane;
+      raw[u] = 0;
+      if (e < n_src) raw[u] = (bitmap != nullptr) ? (int)bitmap[e] : __ldg(ids + e);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int e = base0 + u * 32 + lane;
+      if (base0 + u * 32 < n_src) {     // warp-uniform
+        int id = e;
+        bool valid = false;
+        if (e < n_src) {
+          if (bitmap != nullptr) {
+            valid = raw[u] != 0;
+          } else {
+            id = raw[u];
+            valid = (id >= 0) && (id < nb);
+            bad |= !valid;
+          }
+        }
+        const unsigned m = __ballot_sync(0xffffffffu, valid);
+        if (valid) s_ids[off + __popc(m & ((1u << lane) - 1u))] = (uint16_t)id;
+        off += __popc(m);
+      }
+    }
   }
+  bad = __any_sync(0xffffffffu, bad);
+  if (bad && lane == 0 && blockIdx.x == 0) atomicOr(status, BAS_DEV_BAD_BLOCK_ID);
   __syncwarp();
   return off;
 }

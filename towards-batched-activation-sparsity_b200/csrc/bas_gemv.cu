@@ -49,9 +49,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
   sp += (sizeof(GemvSmemHeader) + 127) / 128 * 128;
   uint16_t* s_ids = (uint16_t*)sp;
   sp += ((size_t)p.nb * 2 + 127) / 128 * 128;
-  uint8_t* s_stage = sp;   // 128-byte aligned; per slot: [wslot weights][B*128 fp16 x][B*256 fp32 x]
-  const int S = p.stages;
-  const int stage_bytes = p.wslot + kXBytes + kXfBytes;
+  uint8_t* s_stage = sp;   // 128-byte aligned; a slot holds `group` tiles of [wslot weights][B*128 fp16 x][B*256 fp32 x]
+  const int S = p.stages, G = p.group;
+  const int tile_bytes = p.wslot + kXBytes + kXfBytes;
+  const int stage_bytes = G * tile_bytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &hdr->abort_flag;
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
   // Nothing so far touched global memory.  The id list may be the previous kernel's output unless
   // the caller declared it stable; X and Y always wait for the previous kernel.
   const bool early_ids = (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
-  int issued = 0;   // slots whose copies the producer thread has started
+  int armed = 0;   // ring slots (groups) whose copies the producer thread has started
 
   if (warp == 0) {
     // ------------------------------ id staging + producer ------------------------------
@@ -88,87 +89,117 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
       mbar_arrive(&hdr->ids_ready);
     }
     pdl_launch_dependents();
-    const int cnt = n_sub * k_act;
-    if (lane == 0 && cnt > 0) {
-      int m = 0, n_resume = 0;
+    const int M = n_sub * k_act;                 // tiles of this CTA: sub-tile major, active block minor
+    const int NG = (M + G - 1) / G;              // groups = barrier hand-offs
+    if (M > 0) {
+      // One pass per ring slot.  Lane l owns tile l of the slot's group: it works out that tile's
+      // addresses (the integer divisions run side by side in the lanes), the byte counts are added
+      // across the warp, lane 0 waits for the slot and arms its barrier, then every lane issues its
+      // tile's weight chunk and activation slices.  Slot index and phase are carried along.
+      int s = 0, ph = 0;   // slot of group g and the parity of its previous use
+      auto lane_tile = [&](int g, int& sub, int& j, int& wbytes, int& xbytes) -> bool {
+        const int m = g * G + lane;
+        if (lane >= G || m >= M) return false;
+        sub = (n_sub == 1) ? 0 : m / k_act;
+        j = s_ids[m - sub * k_act];
+        wbytes = min(kTileN, width - sub * kTileN) * kRowBytes;
+        xbytes = min(kBlockK, p.k - j * kBlockK) * 2;
+        return true;
+      };
+      auto issue_x = [&](uint8_t* st, int j, int xbytes, uint64_t* bar) {
+#pragma unroll
+        for (int b = 0; b < B; ++b)
+          bulk_copy_g2s(st + p.wslot + b * 128, p.x + (size_t)b * p.ldx + (size_t)j * kBlockK, xbytes, bar);
+      };
+      int g0 = 0;
       if (early_ids) {
         // Stream the first ring-full of weight chunks while the previous kernel is still draining,
         // then wait for it before touching the activations.
-        int ahead = 0;
-        for (int n = 0; n < cnt && ahead < S; ++n) {
-          const int sub = n / k_act, j = s_ids[n - sub * k_act];
-          if (j == kSkipId) continue;
-          const int wsub = min(kTileN, width - sub * kTileN);
-          const int kvalid = min(kBlockK, p.k - j * kBlockK);
-          mbar_arrive_expect_tx(&hdr->full[ahead], wsub * kRowBytes + B * kvalid * 2);
-          bulk_copy_g2s(s_stage + (size_t)ahead * stage_bytes,
-                        p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wsub * kRowBytes,
-                        &hdr->full[ahead]);
-          ++ahead;
+        const int ahead = min(S, NG);
+        for (int g = 0; g < ahead; ++g) {
+          int sub = 0, j = 0, wbytes = 0, xbytes = 0;
+          const bool have = lane_tile(g, sub, j, wbytes, xbytes);
+          const int total = __reduce_add_sync(0xffffffffu, have ? wbytes + B * xbytes : 0);
+          if (lane == 0) mbar_arrive_expect_tx(&hdr->full[g], total);
+          __syncwarp();
+          if (have)
+            bulk_copy_g2s(s_stage + (size_t)g * stage_bytes + (size_t)lane * tile_bytes,
+                          p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wbytes, &hdr->full[g]);
         }
-        issued = ahead;
+        armed = ahead;
         pdl_wait();
-        for (; n_resume < cnt && m < ahead; ++n_resume) {
-          const int j = s_ids[n_resume % k_act];
-          if (j == kSkipId) continue;
-          const int kvalid = min(kBlockK, p.k - j * kBlockK);
-          uint8_t* st = s_stage + (size_t)m * stage_bytes + p.wslot;
-#pragma unroll
-          for (int b = 0; b < B; ++b)
-            bulk_copy_g2s(st + b * 128, p.x + (size_t)b * p.ldx + (size_t)j * kBlockK, kvalid * 2, &hdr->full[m]);
-          ++m;
+        for (int g = 0; g < ahead; ++g) {
+          int sub = 0, j = 0, wbytes = 0, xbytes = 0;
+          if (lane_tile(g, sub, j, wbytes, xbytes))
+            issue_x(s_stage + (size_t)g * stage_bytes + (size_t)lane * tile_bytes, j, xbytes, &hdr->full[g]);
         }
+        g0 = ahead;
+        s = (ahead == S) ? 0 : ahead;
       }
-      for (int n = n_resume; n < cnt; ++n) {
-        const int sub = n / k_act, j = s_ids[n - sub * k_act];
-        if (j == kSkipId) continue;
-        const int s = m % S;
-        if (m >= S && !mbar_wait(&hdr->empty[s], ((m / S) - 1) & 1, abort_flag)) {
-          atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
-          hdr->abort_flag = 1;
+      for (int g = g0; g < NG; ++g) {
+        int sub = 0, j = 0, wbytes = 0, xbytes = 0;
+        const bool have = lane_tile(g, sub, j, wbytes, xbytes);
+        const int total = __reduce_add_sync(0xffffffffu, have ? wbytes + B * xbytes : 0);
+        bool ok = true;
+        if (lane == 0) {
+          if (g >= S) ok = mbar_wait(&hdr->empty[s], ph, abort_flag);
+          if (ok) mbar_arrive_expect_tx(&hdr->full[s], total);
+        }
+        if (!__shfl_sync(0xffffffffu, ok, 0)) {
+          if (lane == 0) {
+            atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
+            hdr->abort_flag = 1;
+          }
           break;
         }
-        const int wsub = min(kTileN, width - sub * kTileN);
-        const int kvalid = min(kBlockK, p.k - j * kBlockK);
-        uint8_t* st = s_stage + (size_t)s * stage_bytes;
-        mbar_arrive_expect_tx(&hdr->full[s], wsub * kRowBytes + B * kvalid * 2);
-        bulk_copy_g2s(st, p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wsub * kRowBytes,
-                      &hdr->full[s]);
-#pragma unroll
-        for (int b = 0; b < B; ++b)
-          bulk_copy_g2s(st + p.wslot + b * 128, p.x + (size_t)b * p.ldx + (size_t)j * kBlockK, kvalid * 2,
-                        &hdr->full[s]);
-        issued = ++m;
+        if (have) {
+          uint8_t* st = s_stage + (size_t)s * stage_bytes + (size_t)lane * tile_bytes;
+          bulk_copy_g2s(st, p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wbytes, &hdr->full[s]);
+          issue_x(st, j, xbytes, &hdr->full[s]);
+        }
+        armed = g + 1;
+        if (++s == S) {   // next slot; from the second lap on its previous use must have been released
+          s = 0;
+          if (g >= S) ph ^= 1;
+        }
       }
     }
   } else {
     bool ok = __all_sync(0xffffffffu, mbar_wait(&hdr->ids_ready, 0, abort_flag));
     const int k_act = ok ? hdr->k_act : 0;
+    const int M = n_sub * k_act;
+    const int NG = (M + G - 1) / G;
 
     if (warp == 1) {
       // ------------------------------ converter: fp16 -> fp32 activations ------------------------------
-      int m = 0;
-      for (int n = 0; n < n_sub * k_act && ok; ++n) {
-        const int j = s_ids[n % k_act];
-        if (j == kSkipId) continue;
-        const int s = m % S;
+      int s = 0, fph = 0;
+      for (int g = 0; g < NG && ok; ++g) {
         // the verdict is made warp-uniform so that the warp-level primitives below stay converged
-        if (!__all_sync(0xffffffffu, mbar_wait(&hdr->full[s], (m / S) & 1, abort_flag))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&hdr->full[s], fph, abort_flag))) {
           ok = false;
           break;
         }
-        const int kvalid = min(kBlockK, p.k - j * kBlockK);
-        const uint8_t* xh = s_stage + (size_t)s * stage_bytes + p.wslot;
-        float* xf = (float*)(xh + kXBytes);
+        const int cnt = min(M, (g + 1) * G) - g * G;
+        for (int t = 0; t < cnt; ++t) {
+          int mm = g * G + t;
+          if (n_sub > 1) mm %= k_act;
+          const int j = s_ids[mm];
+          const int kvalid = min(kBlockK, p.k - j * kBlockK);
+          const uint8_t* xh = s_stage + (size_t)s * stage_bytes + (size_t)t * tile_bytes + p.wslot;
+          float* xf = (float*)(xh + kXBytes);
 #pragma unroll
-        for (int b = 0; b < B; ++b) {
-          float2 f = __half22float2(*(const __half2*)(xh + b * 128 + lane * 4));
-          if (2 * lane >= kvalid) f = make_float2(0.f, 0.f);   // channels past K of a ragged last block
-          *(float2*)(xf + b * 64 + 2 * lane) = f;
+          for (int b = 0; b < B; ++b) {
+            float2 f = __half22float2(*(const __half2*)(xh + b * 128 + lane * 4));
+            if (2 * lane >= kvalid) f = make_float2(0.f, 0.f);   // channels past K of a ragged last block
+            *(float2*)(xf + b * 64 + 2 * lane) = f;
+          }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&hdr->xready[s]);
-        ++m;
+        if (++s == S) {
+          s = 0;
+          fph ^= 1;
+        }
       }
       if (!ok) {
         atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
@@ -184,7 +215,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
              e += (long long)gridDim.x * kConsumerThreads)
           p.y[(e / p.n) * p.ldy + (e % p.n)] = __float2half_rn(0.f);
       }
-      int m = 0;
+      int m = 0, s = 0, pos = 0, fph = 0;   // tile, its slot, position in the slot's group, slot parity
       for (int sub = 0; sub < n_sub && ok && k_act > 0; ++sub) {
         const int wsub = min(kTileN, width - sub * kTileN);
         const int npairs = wsub * 8;                 // (row, 16-byte chunk) pairs of this sub-tile
@@ -194,19 +225,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
 #pragma unroll
           for (int b = 0; b < B; ++b) acc[e][b] = 0.f;
 
-        for (int i = 0; i < k_act; ++i) {
-          if (s_ids[i] == kSkipId) continue;
-          const int s = m % S;
-          // xready implies full (the converter waited on it); observing full directly as well makes
-          // the bulk copy's writes visible to this thread without relying on transitivity.
-          // (The verdict is made warp-uniform so that the warp-level primitives stay converged.)
-          const bool landed = mbar_wait(&hdr->xready[s], (m / S) & 1, abort_flag) &&
-                              mbar_wait(&hdr->full[s], (m / S) & 1, abort_flag);
-          if (!__all_sync(0xffffffffu, landed)) {
-            ok = false;
-            break;
+        for (int i = 0; i < k_act; ++i, ++m) {
+          if (pos == 0 || i == 0) {
+            // xready is arrived by the converter after it has seen the slot's copies land; a slot that
+            // straddles two sub-tiles is waited for again, which returns at once.
+            if (!__all_sync(0xffffffffu, mbar_wait(&hdr->xready[s], fph, abort_flag) &&
+                                             mbar_wait(&hdr->full[s], fph, abort_flag))) {
+              ok = false;
+              break;
+            }
           }
-          const uint8_t* st = s_stage + (size_t)s * stage_bytes;
+          const uint8_t* st = s_stage + (size_t)s * stage_bytes + (size_t)pos * tile_bytes;
           const float* xf = (const float*)(st + p.wslot + kXBytes);
 #pragma unroll
           for (int e = 0; e < kMaxPairs; ++e) {
@@ -235,9 +264,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
               }
             }
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&hdr->empty[s]);
-          ++m;
+          if (pos == G - 1 || m == M - 1) {   // last tile of the slot: hand it back
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&hdr->empty[s]);
+            pos = 0;
+            if (++s == S) {
+              s = 0;
+              fph ^= 1;
+            }
+          } else {
+            ++pos;
+          }
         }
         if (!ok) break;
         // the 8 chunk-threads of a row are lanes 8g .. 8g+7: add their sums, lane 8g stores
@@ -267,7 +304,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
   if (hdr->abort_flag != 0 && tid == 0) {
     // Gave up somewhere: do not leave while bulk copies may still be landing in this CTA's memory.
     int zero = 0;
-    for (int n = max(0, issued - S); n < issued; ++n) (void)mbar_wait(&hdr->full[n % S], (n / S) & 1, &zero);
+    for (int g = max(0, armed - S); g < armed; ++g) (void)mbar_wait(&hdr->full[g % S], (g / S) & 1, &zero);
   }
 }
 
@@ -291,10 +328,20 @@ cudaError_t launch_gemv_b(GemmParams p, int sm_count, cudaStream_t stream) {
   const size_t fixed = gemv_fixed_smem(p.nb);
   const size_t stage_bytes = (size_t)p.wslot + B * 128 + B * 256;
   if (fixed + 2 * stage_bytes > kSmemBudget) return cudaErrorInvalidValue;
-  int stages = (int)((kSmemBudget - fixed) / stage_bytes);
+  // One barrier hand-off costs a few hundred cycles per role: a slot gathers enough blocks (about
+  // 24 KiB) for the hand-offs to stay off the critical path.
+  int group = (int)((24 * 1024 + stage_bytes - 1) / stage_bytes);
+  if (group > 16) group = 16;
+  if (group < 1) group = 1;
+  int stages = (int)((kSmemBudget - fixed) / (stage_bytes * group));
+  if (stages < 2) {
+    group = 1;
+    stages = (int)((kSmemBudget - fixed) / stage_bytes);
+  }
   if (stages > kMaxStages) stages = kMaxStages;
   p.stages = stages;
-  const size_t smem = fixed + (size_t)stages * stage_bytes;
+  p.group = group;
+  const size_t smem = fixed + (size_t)stages * group * stage_bytes;
   count_launch();
   return launch_with_pdl(gemv_colsplit_kernel<B>, p.ranges, kGemvThreads, smem, 1, stream, p);
 }

@@ -18,11 +18,15 @@ struct GemmParams {
   int ranges;               // column ranges = CTAs (clusters) of the grid
   int cluster;              // CTAs per cluster splitting the active blocks of one range (1, 2 or 4)
   int stages;               // ring slots
+  int group;                // blocks per ring slot: one barrier hand-off covers this many chunks
   int wslot;                // bytes reserved per slot for a weight chunk (multiple of 1024)
   __half* y;                // [batch, N], row stride ldy
   long long ldy;
   int flags;                // kFlag* bits
   unsigned int* status;     // workspace: status word
+#ifdef BAS_TRACE
+  long long* trace;         // diagnostic build only: per-role cycle counters of CTA 0
+#endif
 };
 
 constexpr int kFlagStableIds = 16;   // BAS_GEMM_IDS_STABLE: the id list is not written by the previous kernel

@@ -33,20 +33,23 @@ namespace bas {
 
 namespace {
 
-constexpr int kUmmaThreads = 64 + 128;
+constexpr int kIssuers = 4;             // MMA-issuing warps; each owns one accumulator
+constexpr int kEpiWarp0 = 1 + kIssuers; // first epilogue warp
 constexpr int kEpiThreads = 128;
-constexpr int kTmemCols = 128;          // two accumulator buffers of 64 fp32 columns
+constexpr int kUmmaThreads = 32 * kEpiWarp0 + kEpiThreads;
+constexpr int kTmemCols = 64 * kIssuers; // one 64-column fp32 accumulator per issuer
 constexpr int kMmaSpanBytes = 128 * kRowBytes;   // an M=128 operand read spans 16 KiB from the slot base
 
 struct UmmaSmemHeader {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
-  uint64_t acc_full[2];
-  uint64_t acc_empty[2];
+  uint64_t acc_full;      // every issuer has finished the sub-tile (kIssuers arrivals)
+  uint64_t acc_empty;     // the epilogue has drained the accumulators (4 arrivals)
   uint64_t ids_ready;
   uint32_t tmem_base;
   int k_act;
   int abort_flag;
+  long long t0;   // diagnostic builds: clock at kernel start
 };
 
 inline size_t umma_ids_bytes(int nb) { return ((size_t)nb * 2 + 127) / 128 * 128; }
@@ -67,28 +70,28 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   uint16_t* s_ids = (uint16_t*)sp;
   sp += ((size_t)p.nb * 2 + 127) / 128 * 128;
   uint8_t* s_stage = (uint8_t*)(((uintptr_t)sp + 1023) & ~(uintptr_t)1023);  // swizzle atoms need 1 KiB alignment
-  const int S = p.stages;
-  const int stage_bytes = p.wslot + kXTileBytes;
+  const int S = p.stages, G = p.group;
+  const int tile_bytes = p.wslot + kXTileBytes;   // multiple of 1024
+  const int stage_bytes = G * tile_bytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &hdr->abort_flag;
 
   if (tid < S) {
     mbar_init(&hdr->full[tid], 1);
-    mbar_init(&hdr->empty[tid], 1);
+    mbar_init(&hdr->empty[tid], kIssuers);
     fence_barrier_init();
   } else if (tid == 64) {
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&hdr->acc_full[a], 1);
-      mbar_init(&hdr->acc_empty[a], kEpiThreads / 32);
-    }
+    mbar_init(&hdr->acc_full, kIssuers);
+    mbar_init(&hdr->acc_empty, kEpiThreads / 32);
     mbar_init(&hdr->ids_ready, 1);
     hdr->abort_flag = 0;
     hdr->k_act = 0;
+    hdr->t0 = BAS_TRACE_CLOCK();
     fence_barrier_init();
     prefetch_tensormap(&xmap);
   }
-  if (warp == 2) {
+  if (warp == kEpiWarp0) {
     tmem_alloc(&hdr->tmem_base, kTmemCols);
     tmem_relinquish();
   }
@@ -110,7 +113,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   // the caller declared it stable; X and Y always wait for the previous kernel.
   const bool early_ids = (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
   int k_act = 0;
-  int issued = 0;   // tiles whose copies the producer thread has started
+  int armed = 0;   // ring slots (groups) whose copies the producer thread has started
 
   if (warp == 0) {
     // ------------------------------ id staging + producer ------------------------------
@@ -122,91 +125,150 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     }
     pdl_launch_dependents();
     const int k_mine = (k_act > rank) ? (k_act - rank + C - 1) / C : 0;
-    const int cnt = n_sub * k_mine;
-    if (lane == 0 && cnt > 0) {
-      int m = 0, n_resume = 0;
+    const int M = n_sub * k_mine;                // tiles of this CTA: sub-tile major, active block minor
+    const int NG = (M + G - 1) / G;              // groups = barrier hand-offs
+    if (M > 0) {
+      // One pass per ring slot.  Lane l owns tile l of the slot's group: it works out that tile's
+      // addresses (the integer divisions run side by side in the lanes), the byte counts are added
+      // across the warp, lane 0 waits for the slot and arms its barrier, then every lane issues its
+      // own two copies.  Slot index and phase are carried along instead of recomputed.
+      int s = 0, ph = 0;   // slot of group g and the parity of its previous use
+      auto lane_tile = [&](int g, int& sub, int& j, int& wbytes) -> bool {
+        const int m = g * G + lane;
+        if (lane >= G || m >= M) return false;
+        sub = (n_sub == 1) ? 0 : m / k_mine;
+        j = s_ids[rank + (m - sub * k_mine) * C];
+        wbytes = min(kTileN, width - sub * kTileN) * kRowBytes;
+        return true;
+      };
+      int g0 = 0;
       if (early_ids) {
         // Stream the first ring-full of weight chunks while the previous kernel is still draining,
         // then wait for it before loading X.
-        int ahead = 0;
-        for (int n = 0; n < cnt && ahead < S; ++n) {
-          const int sub = n / k_mine, j = s_ids[rank + (n - sub * k_mine) * C];
-          if (j == kSkipId) continue;
-          const int wsub = min(kTileN, width - sub * kTileN);
-          mbar_arrive_expect_tx(&hdr->full[ahead], wsub * kRowBytes + kXTileBytes);
-          bulk_copy_g2s(s_stage + (size_t)ahead * stage_bytes,
-                        p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wsub * kRowBytes,
-                        &hdr->full[ahead]);
-          ++ahead;
+        const int ahead = min(S, NG);
+        for (int g = 0; g < ahead; ++g) {
+          int sub = 0, j = 0, wbytes = 0;
+          const bool have = lane_tile(g, sub, j, wbytes);
+          const int total = __reduce_add_sync(0xffffffffu, have ? wbytes + kXTileBytes : 0);
+          if (lane == 0) mbar_arrive_expect_tx(&hdr->full[g], total);
+          __syncwarp();
+          if (have)
+            bulk_copy_g2s(s_stage + (size_t)g * stage_bytes + (size_t)lane * tile_bytes,
+                          p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wbytes, &hdr->full[g]);
         }
-        issued = ahead;
+        armed = ahead;
         pdl_wait();
-        for (; n_resume < cnt && m < ahead; ++n_resume) {
-          const int sub = n_resume / k_mine, j = s_ids[rank + (n_resume - sub * k_mine) * C];
-          if (j == kSkipId) continue;
-          tma_load_2d(s_stage + (size_t)m * stage_bytes + p.wslot, &xmap, j * kBlockK, 0, &hdr->full[m]);
-          ++m;
+        for (int g = 0; g < ahead; ++g) {
+          int sub = 0, j = 0, wbytes = 0;
+          if (lane_tile(g, sub, j, wbytes))
+            tma_load_2d(s_stage + (size_t)g * stage_bytes + (size_t)lane * tile_bytes + p.wslot, &xmap, j * kBlockK, 0,
+                        &hdr->full[g]);
         }
+        g0 = ahead;
+        s = (ahead == S) ? 0 : ahead;
+        ph = 0;
       }
-      for (int n = n_resume; n < cnt; ++n) {
-        const int sub = n / k_mine, j = s_ids[rank + (n - sub * k_mine) * C];
-        if (j == kSkipId) continue;
-        const int s = m % S;
-        if (m >= S && !mbar_wait(&hdr->empty[s], ((m / S) - 1) & 1, abort_flag)) {
-          atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
-          hdr->abort_flag = 1;
+      for (int g = g0; g < NG; ++g) {
+        [[maybe_unused]] const long long tr0 = BAS_TRACE_CLOCK();
+        int sub = 0, j = 0, wbytes = 0;
+        const bool have = lane_tile(g, sub, j, wbytes);
+        const int total = __reduce_add_sync(0xffffffffu, have ? wbytes + kXTileBytes : 0);
+        bool ok = true;
+        if (lane == 0) {
+          if (g >= S) ok = mbar_wait(&hdr->empty[s], ph, abort_flag);
+          if (ok) mbar_arrive_expect_tx(&hdr->full[s], total);
+        }
+        if (!__shfl_sync(0xffffffffu, ok, 0)) {
+          if (lane == 0) {
+            atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
+            hdr->abort_flag = 1;
+          }
           break;
         }
-        const int wsub = min(kTileN, width - sub * kTileN);
-        uint8_t* st = s_stage + (size_t)s * stage_bytes;
-        mbar_arrive_expect_tx(&hdr->full[s], wsub * kRowBytes + kXTileBytes);
-        bulk_copy_g2s(st, p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wsub * kRowBytes,
-                      &hdr->full[s]);
-        tma_load_2d(st + p.wslot, &xmap, j * kBlockK, 0, &hdr->full[s]);
-        issued = ++m;
+        [[maybe_unused]] const long long tr1 = BAS_TRACE_CLOCK();
+        if (have) {
+          uint8_t* st = s_stage + (size_t)s * stage_bytes + (size_t)lane * tile_bytes;
+          bulk_copy_g2s(st, p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wbytes, &hdr->full[s]);
+          tma_load_2d(st + p.wslot, &xmap, j * kBlockK, 0, &hdr->full[s]);
+        }
+        armed = g + 1;
+        if (lane == 0) {
+          BAS_TRACE_SET(64 + g, tr1 - hdr->t0);                     // slot free seen by the producer
+          BAS_TRACE_SET(128 + g, BAS_TRACE_CLOCK() - hdr->t0);      // group's copies issued
+          BAS_TRACE_ADD(0, tr1 - tr0);                              // producer: waiting for a free slot
+          BAS_TRACE_ADD(1, BAS_TRACE_CLOCK() - tr1);                // producer: issuing a slot's copies
+          BAS_TRACE_ADD(2, 1);
+        }
+        if (++s == S) {   // next slot; from the second lap on its previous use must have been released
+          s = 0;
+          if (g >= S) ph ^= 1;
+        }
       }
     }
   } else {
     bool ok = __all_sync(0xffffffffu, mbar_wait(&hdr->ids_ready, 0, abort_flag));
     k_act = hdr->k_act;
     const int k_mine = (ok && k_act > rank) ? (k_act - rank + C - 1) / C : 0;
+    const int M = n_sub * k_mine;
 
-    if (warp == 1) {
-      // ------------------------------ MMA issuer (one thread) ------------------------------
+    if (warp < kEpiWarp0) {
+      // ------------------------------ MMA issuers (one thread per warp) ------------------------------
+      // Issuing one tcgen05.mma costs its thread on the order of a hundred cycles, far more than the
+      // tensor core needs for a 128 x Bpad x 16 product.  Four warps therefore issue side by side:
+      // issuer w takes the tiles at positions w, w+4, ... of every sub-tile and adds them into an
+      // accumulator of its own; the epilogue adds the four accumulators in issuer order.
+      const int w = warp - 1;
       if (lane == 0 && ok) {
+        const uint32_t d = tmem_base + (uint32_t)(w * 64);
+        int s = 0, pos = 0, fph = 0;   // slot, position in its group, parity of the slot's current use
+        bool used = false;             // this issuer has read from the current slot
         int m = 0;
         for (int sub = 0; sub < n_sub && ok && k_mine > 0; ++sub) {
-          const int a = sub & 1;
-          bool fresh = true;   // the next MMA overwrites the accumulator instead of adding to it
-          for (int ii = 0; ii < k_mine; ++ii) {
-            if (s_ids[rank + ii * C] == kSkipId) continue;
-            const int s = m % S;
-            if (fresh && sub >= 2) ok = mbar_wait(&hdr->acc_empty[a], ((sub >> 1) - 1) & 1, abort_flag);
-            if (ok) ok = mbar_wait(&hdr->full[s], (m / S) & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t st = smem_u32(s_stage + (size_t)s * stage_bytes);
-            const uint64_t adesc = umma_desc_kmajor_sw128(st);
-            const uint64_t bdesc = umma_desc_kmajor_sw128(st + p.wslot);
-            const uint32_t d = tmem_base + (uint32_t)(a * 64);
+          if (sub >= 1) ok = mbar_wait(&hdr->acc_empty, (sub - 1) & 1, abort_flag);
+          if (!ok) break;
+          for (int ii = 0; ii < k_mine; ++ii, ++m) {
+            if ((ii & (kIssuers - 1)) == w) {
+              [[maybe_unused]] const long long tr0 = BAS_TRACE_CLOCK();
+              if (!mbar_wait(&hdr->full[s], fph, abort_flag)) {
+                ok = false;
+                break;
+              }
+              [[maybe_unused]] const long long tr1 = BAS_TRACE_CLOCK();
+              tc_fence_after_sync();
+              const uint32_t st = smem_u32(s_stage + (size_t)s * stage_bytes + (size_t)pos * tile_bytes);
+              const uint64_t adesc = umma_desc_kmajor_sw128(st);
+              const uint64_t bdesc = umma_desc_kmajor_sw128(st + p.wslot);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units
-              umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc, (fresh && ks == 0) ? 0u : 1u);
+              for (int ks = 0; ks < 4; ++ks) {
+                // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units; an
+                // issuer's first MMA of a sub-tile overwrites its accumulator instead of adding
+                umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc, (ii == w && ks == 0) ? 0u : 1u);
+              }
+              used = true;
+              if (w == 0) {
+                BAS_TRACE_ADD(4, tr1 - tr0);                    // issuer 0: waiting for data
+                BAS_TRACE_ADD(5, BAS_TRACE_CLOCK() - tr1);      // issuer 0: issuing a tile's MMAs
+                BAS_TRACE_ADD(6, 1);
+              }
             }
-            umma_commit(&hdr->empty[s]);  // the slot is free once these MMAs have read it
-            fresh = false;
-            ++m;
+            // every issuer signs off every slot: with a commit if it read from it (the arrival then
+            // waits for those MMAs), plainly otherwise
+            if (pos == G - 1 || m == M - 1) {
+              if (used) umma_commit(&hdr->empty[s]);
+              else mbar_arrive(&hdr->empty[s]);
+              used = false;
+              pos = 0;
+              if (++s == S) {
+                s = 0;
+                fph ^= 1;
+              }
+            } else {
+              ++pos;
+            }
           }
           if (!ok) break;
-          if (!fresh) {
-            umma_commit(&hdr->acc_full[a]);
-          } else {
-            // Every position was a skipped id: no MMA ran; the epilogue (which checks the list
-            // itself) takes zeros.  Keep the barrier phases in step.
-            if (sub >= 2) ok = mbar_wait(&hdr->acc_empty[a], ((sub >> 1) - 1) & 1, abort_flag);
-            if (ok) mbar_arrive(&hdr->acc_full[a]);
-          }
+          if (w < k_mine) umma_commit(&hdr->acc_full);   // this issuer's accumulator of the sub-tile is final
+          else mbar_arrive(&hdr->acc_full);              // nothing was dealt to this issuer
         }
         if (!ok) {
           atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
@@ -217,46 +279,42 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       // ------------------------------ epilogue: 4 warps, one TMEM lane quarter each ------------------------------
       const int q = warp & 3;               // a warp may only read TMEM lanes [32*(warp%4), +32)
       const int r = q * 32 + lane;          // row of the sub-tile = output column n0 + 128*sub + r
+      const int et = tid - 32 * kEpiWarp0;  // 0..127
       float* red = (float*)s_stage;         // cluster mode: this CTA's fp32 partial [batch][128]
       if (early_ids) pdl_wait();            // before the first write to Y
       if (ok && k_act == 0) {
         // empty active set: the epilogue threads of the whole grid zero Y between them
         const long long total = (long long)p.batch * p.n;
-        for (long long e = (long long)blockIdx.x * kEpiThreads + (tid - 64); e < total;
-             e += (long long)gridDim.x * kEpiThreads)
+        for (long long e = (long long)blockIdx.x * kEpiThreads + et; e < total; e += (long long)gridDim.x * kEpiThreads)
           p.y[(e / p.n) * p.ldy + (e % p.n)] = __float2half_rn(0.f);
       } else if (ok) {
-        bool has_data = false;
-        for (int ii = lane; ii < k_mine; ii += 32) has_data |= (s_ids[rank + ii * C] != kSkipId);
-        has_data = __any_sync(0xffffffffu, has_data);
         for (int sub = 0; sub < n_sub && ok; ++sub) {
-          const int a = sub & 1;
           float v[BPAD];
+#pragma unroll
+          for (int b = 0; b < BPAD; ++b) v[b] = 0.f;
           if (k_mine > 0) {
             // warp-uniform verdict: tcgen05.ld below needs the whole warp
-            if (!__all_sync(0xffffffffu, mbar_wait(&hdr->acc_full[a], (sub >> 1) & 1, abort_flag))) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&hdr->acc_full, sub & 1, abort_flag))) {
               ok = false;
               break;
             }
             tc_fence_after_sync();
-          }
-          if (k_mine > 0 && has_data) {
 #pragma unroll
-            for (int cc = 0; cc < BPAD / 16; ++cc) {
-              uint32_t regs[16];
-              tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 64 + cc * 16), regs);
+            for (int w = 0; w < kIssuers; ++w) {
+              if (w < k_mine) {   // issuer order: the sum never depends on timing
 #pragma unroll
-              for (int e = 0; e < 16; ++e) v[cc * 16 + e] = __uint_as_float(regs[e]);
+                for (int cc = 0; cc < BPAD / 16; ++cc) {
+                  uint32_t regs[16];
+                  tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(w * 64 + cc * 16), regs);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int e = 0; e < 16; ++e) v[cc * 16 + e] += __uint_as_float(regs[e]);
+                }
+              }
             }
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int b = 0; b < BPAD; ++b) v[b] = 0.f;
-          }
-          if (k_mine > 0) {
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&hdr->acc_empty[a]);
+            if (lane == 0) mbar_arrive(&hdr->acc_empty);
           }
           if (C == 1) {
             const int col = n0 + sub * kTileN + r;
@@ -266,7 +324,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 if (b < p.batch) p.y[(size_t)b * p.ldy + col] = __float2half_rn(v[b]);
             }
           } else {
-            // one sub-tile per CTA in cluster mode; the ring is idle once the accumulator is final
+            // one sub-tile per CTA in cluster mode; the ring is idle once the accumulators are final
 #pragma unroll
             for (int b = 0; b < BPAD; ++b)
               if (b < p.batch) red[b * kTileN + r] = v[b];
@@ -285,8 +343,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   if (C > 1) {
     // Add the cluster's partials in rank order: rank i finishes batch rows i, i+C, ...
     cluster_sync_all();
-    if (hdr->k_act > 0 && hdr->abort_flag == 0 && warp >= 2) {
-      const int r = tid - 64;
+    if (hdr->k_act > 0 && hdr->abort_flag == 0 && warp >= kEpiWarp0) {
+      const int r = tid - 32 * kEpiWarp0;
       const int col = n0 + r;
       if (r < width && col < p.n) {
         const uint32_t mine = smem_u32(s_stage) + (uint32_t)r * 4u;
@@ -307,9 +365,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   if (hdr->abort_flag != 0 && tid == 0) {
     // Gave up somewhere: do not leave while copies may still be landing in this CTA's memory.
     int zero = 0;
-    for (int n = max(0, issued - S); n < issued; ++n) (void)mbar_wait(&hdr->full[n % S], (n / S) & 1, &zero);
+    for (int g = max(0, armed - S); g < armed; ++g) (void)mbar_wait(&hdr->full[g % S], (g / S) & 1, &zero);
   }
-  if (warp == 2) {
+  if (warp == kEpiWarp0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -455,13 +513,22 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   p.wslot = (wsub_max * kRowBytes + 1023) / 1024 * 1024;
   const size_t stage_bytes = (size_t)p.wslot + BPAD * 128;
   const size_t room = kSmemBudget - fixed;
-  int stages = (int)(room / stage_bytes);
+  // One barrier hand-off costs a few hundred cycles per role: a slot gathers enough blocks (about
+  // 24 KiB) for the hand-offs to stay off the critical path.
+  int group = (int)((24 * 1024 + stage_bytes - 1) / stage_bytes);
+  if (group > 16) group = 16;
+  int stages = (int)(room / (stage_bytes * group));
+  if (stages < 3) {
+    group = 1;
+    stages = (int)(room / stage_bytes);
+  }
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return cudaErrorInvalidValue;
   p.stages = stages;
-  size_t smem = fixed + (size_t)stages * stage_bytes;
+  p.group = group;
+  size_t smem = fixed + (size_t)stages * group * stage_bytes;
   const size_t red_bytes = (size_t)p.batch * kTileN * 4;   // cluster mode reuses the ring for the partial
-  if (cluster > 1 && (size_t)stages * stage_bytes < red_bytes) smem = fixed + red_bytes;
+  if (cluster > 1 && (size_t)stages * group * stage_bytes < red_bytes) smem = fixed + red_bytes;
 
   CUtensorMap xmap;
   cudaError_t e = get_x_tensor_map(p, BPAD, &xmap);
