@@ -33,8 +33,9 @@ namespace bas {
 
 namespace {
 
+constexpr int kProducers = 4;           // copy-issuing warps; warp p takes ring groups p, p+4, ...
 constexpr int kIssuers = 4;             // MMA-issuing warps; each owns one accumulator
-constexpr int kEpiWarp0 = 1 + kIssuers; // first epilogue warp
+constexpr int kEpiWarp0 = kProducers + kIssuers;   // first epilogue warp (a multiple of 4: TMEM lane quarters)
 constexpr int kEpiThreads = 128;
 constexpr int kUmmaThreads = 32 * kEpiWarp0 + kEpiThreads;
 constexpr int kTmemCols = 64 * kIssuers; // one 64-column fp32 accumulator per issuer
@@ -69,6 +70,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   sp += (sizeof(UmmaSmemHeader) + 127) / 128 * 128;
   uint16_t* s_ids = (uint16_t*)sp;
   sp += ((size_t)p.nb * 2 + 127) / 128 * 128;
+  float* s_red = (float*)sp;   // cluster mode: partials pushed here by the cluster's CTAs, [source rank][row slot][128]
+  if (p.cluster > 1) sp += (size_t)BPAD * kTileN * sizeof(float);
   uint8_t* s_stage = (uint8_t*)(((uintptr_t)sp + 1023) & ~(uintptr_t)1023);  // swizzle atoms need 1 KiB alignment
   const int S = p.stages, G = p.group;
   const int tile_bytes = p.wslot + kXTileBytes;   // multiple of 1024
@@ -99,6 +102,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = hdr->tmem_base;
+  if (tid == 0) BAS_TRACE_SET(8, BAS_TRACE_CLOCK() - hdr->t0);     // preamble done
 
   // this CTA's columns and its share of the active list
   const int C = p.cluster;
@@ -113,26 +117,31 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   // the caller declared it stable; X and Y always wait for the previous kernel.
   const bool early_ids = (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
   int k_act = 0;
-  int armed = 0;   // ring slots (groups) whose copies the producer thread has started
+  int armed_next = warp, armed_cnt = 0;   // producer warps: next group to arm, groups armed so far
 
-  if (warp == 0) {
-    // ------------------------------ id staging + producer ------------------------------
-    if (!early_ids) pdl_wait();
-    k_act = warp_stage_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids, p.status, lane);
-    if (lane == 0) {
-      hdr->k_act = k_act;
-      mbar_arrive(&hdr->ids_ready);
+  if (warp < kProducers) {
+    // ------------------------------ id staging (warp 0) + producers ------------------------------
+    if (warp == 0) {
+      if (!early_ids) pdl_wait();
+      k_act = warp_stage_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids, p.status, lane);
+      if (lane == 0) {
+        hdr->k_act = k_act;
+        mbar_arrive(&hdr->ids_ready);
+        BAS_TRACE_SET(9, BAS_TRACE_CLOCK() - hdr->t0);    // id list staged
+      }
+      pdl_launch_dependents();
+    } else {
+      // ordered after warp 0's wait for the previous kernel by the barrier
+      if (__all_sync(0xffffffffu, mbar_wait(&hdr->ids_ready, 0, abort_flag))) k_act = hdr->k_act;
     }
-    pdl_launch_dependents();
     const int k_mine = (k_act > rank) ? (k_act - rank + C - 1) / C : 0;
     const int M = n_sub * k_mine;                // tiles of this CTA: sub-tile major, active block minor
     const int NG = (M + G - 1) / G;              // groups = barrier hand-offs
     if (M > 0) {
-      // One pass per ring slot.  Lane l owns tile l of the slot's group: it works out that tile's
-      // addresses (the integer divisions run side by side in the lanes), the byte counts are added
-      // across the warp, lane 0 waits for the slot and arms its barrier, then every lane issues its
-      // own two copies.  Slot index and phase are carried along instead of recomputed.
-      int s = 0, ph = 0;   // slot of group g and the parity of its previous use
+      // One pass per ring group; producer warp w takes groups w, w+4, ...  Lane l owns tile l of
+      // the group: it works out that tile's addresses (the integer divisions run side by side in the
+      // lanes), the byte counts are added across the warp, lane 0 waits for the slot and arms its
+      // barrier, then every lane issues its own two copies.  Slot index and lap are carried along.
       auto lane_tile = [&](int g, int& sub, int& j, int& wbytes) -> bool {
         const int m = g * G + lane;
         if (lane >= G || m >= M) return false;
@@ -141,41 +150,41 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         wbytes = min(kTileN, width - sub * kTileN) * kRowBytes;
         return true;
       };
-      int g0 = 0;
+      int g = warp;
       if (early_ids) {
         // Stream the first ring-full of weight chunks while the previous kernel is still draining,
         // then wait for it before loading X.
         const int ahead = min(S, NG);
-        for (int g = 0; g < ahead; ++g) {
+        for (int ga = warp; ga < ahead; ga += kProducers) {
           int sub = 0, j = 0, wbytes = 0;
-          const bool have = lane_tile(g, sub, j, wbytes);
+          const bool have = lane_tile(ga, sub, j, wbytes);
           const int total = __reduce_add_sync(0xffffffffu, have ? wbytes + kXTileBytes : 0);
-          if (lane == 0) mbar_arrive_expect_tx(&hdr->full[g], total);
+          if (lane == 0) mbar_arrive_expect_tx(&hdr->full[ga], total);
           __syncwarp();
           if (have)
-            bulk_copy_g2s(s_stage + (size_t)g * stage_bytes + (size_t)lane * tile_bytes,
-                          p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wbytes, &hdr->full[g]);
+            bulk_copy_g2s(s_stage + (size_t)ga * stage_bytes + (size_t)lane * tile_bytes,
+                          p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wbytes, &hdr->full[ga]);
+          armed_next = ga + kProducers;
+          ++armed_cnt;
         }
-        armed = ahead;
         pdl_wait();
-        for (int g = 0; g < ahead; ++g) {
+        for (int ga = warp; ga < ahead; ga += kProducers) {
           int sub = 0, j = 0, wbytes = 0;
-          if (lane_tile(g, sub, j, wbytes))
-            tma_load_2d(s_stage + (size_t)g * stage_bytes + (size_t)lane * tile_bytes + p.wslot, &xmap, j * kBlockK, 0,
-                        &hdr->full[g]);
+          if (lane_tile(ga, sub, j, wbytes))
+            tma_load_2d(s_stage + (size_t)ga * stage_bytes + (size_t)lane * tile_bytes + p.wslot, &xmap, j * kBlockK, 0,
+                        &hdr->full[ga]);
         }
-        g0 = ahead;
-        s = (ahead == S) ? 0 : ahead;
-        ph = 0;
+        g = armed_next;
       }
-      for (int g = g0; g < NG; ++g) {
+      int s = g % S, lap = g / S;   // slot of group g and how often the slot has been used before
+      for (; g < NG; g += kProducers) {
         [[maybe_unused]] const long long tr0 = BAS_TRACE_CLOCK();
         int sub = 0, j = 0, wbytes = 0;
         const bool have = lane_tile(g, sub, j, wbytes);
         const int total = __reduce_add_sync(0xffffffffu, have ? wbytes + kXTileBytes : 0);
         bool ok = true;
         if (lane == 0) {
-          if (g >= S) ok = mbar_wait(&hdr->empty[s], ph, abort_flag);
+          if (lap > 0) ok = mbar_wait(&hdr->empty[s], (lap - 1) & 1, abort_flag);
           if (ok) mbar_arrive_expect_tx(&hdr->full[s], total);
         }
         if (!__shfl_sync(0xffffffffu, ok, 0)) {
@@ -191,7 +200,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           bulk_copy_g2s(st, p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wbytes, &hdr->full[s]);
           tma_load_2d(st + p.wslot, &xmap, j * kBlockK, 0, &hdr->full[s]);
         }
-        armed = g + 1;
+        armed_next = g + kProducers;
+        ++armed_cnt;
         if (lane == 0) {
           BAS_TRACE_SET(64 + g, tr1 - hdr->t0);                     // slot free seen by the producer
           BAS_TRACE_SET(128 + g, BAS_TRACE_CLOCK() - hdr->t0);      // group's copies issued
@@ -199,9 +209,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           BAS_TRACE_ADD(1, BAS_TRACE_CLOCK() - tr1);                // producer: issuing a slot's copies
           BAS_TRACE_ADD(2, 1);
         }
-        if (++s == S) {   // next slot; from the second lap on its previous use must have been released
-          s = 0;
-          if (g >= S) ph ^= 1;
+        s += kProducers;
+        while (s >= S) {
+          s -= S;
+          ++lap;
         }
       }
     }
@@ -217,7 +228,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       // tensor core needs for a 128 x Bpad x 16 product.  Four warps therefore issue side by side:
       // issuer w takes the tiles at positions w, w+4, ... of every sub-tile and adds them into an
       // accumulator of its own; the epilogue adds the four accumulators in issuer order.
-      const int w = warp - 1;
+      const int w = warp - kProducers;
       if (lane == 0 && ok) {
         const uint32_t d = tmem_base + (uint32_t)(w * 64);
         int s = 0, pos = 0, fph = 0;   // slot, position in its group, parity of the slot's current use
@@ -227,12 +238,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           if (sub >= 1) ok = mbar_wait(&hdr->acc_empty, (sub - 1) & 1, abort_flag);
           if (!ok) break;
           for (int ii = 0; ii < k_mine; ++ii, ++m) {
+            // Every issuer observes every group landing, also groups it reads nothing from: its
+            // sign-off below must not run ahead of the ring (an arrival for the slot's NEXT use
+            // would be counted in the current phase).
+            [[maybe_unused]] const long long tr0 = BAS_TRACE_CLOCK();
+            if (pos == 0 && !mbar_wait(&hdr->full[s], fph, abort_flag)) {
+              ok = false;
+              break;
+            }
             if ((ii & (kIssuers - 1)) == w) {
-              [[maybe_unused]] const long long tr0 = BAS_TRACE_CLOCK();
-              if (!mbar_wait(&hdr->full[s], fph, abort_flag)) {
-                ok = false;
-                break;
-              }
               [[maybe_unused]] const long long tr1 = BAS_TRACE_CLOCK();
               tc_fence_after_sync();
               const uint32_t st = smem_u32(s_stage + (size_t)s * stage_bytes + (size_t)pos * tile_bytes);
@@ -280,7 +294,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       const int q = warp & 3;               // a warp may only read TMEM lanes [32*(warp%4), +32)
       const int r = q * 32 + lane;          // row of the sub-tile = output column n0 + 128*sub + r
       const int et = tid - 32 * kEpiWarp0;  // 0..127
-      float* red = (float*)s_stage;         // cluster mode: this CTA's fp32 partial [batch][128]
       if (early_ids) pdl_wait();            // before the first write to Y
       if (ok && k_act == 0) {
         // empty active set: the epilogue threads of the whole grid zero Y between them
@@ -299,6 +312,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
               break;
             }
             tc_fence_after_sync();
+            if (et == 0) BAS_TRACE_SET(10, BAS_TRACE_CLOCK() - hdr->t0);   // accumulators final
 #pragma unroll
             for (int w = 0; w < kIssuers; ++w) {
               if (w < k_mine) {   // issuer order: the sum never depends on timing
@@ -324,10 +338,17 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 if (b < p.batch) p.y[(size_t)b * p.ldy + col] = __float2half_rn(v[b]);
             }
           } else {
-            // one sub-tile per CTA in cluster mode; the ring is idle once the accumulators are final
+            // Cluster mode (one sub-tile per CTA): batch row b is finished by rank b % C.  Push this
+            // CTA's partial of each row into the owner's shared memory; the stores are posted, the
+            // cluster barrier below makes them visible.
+            const uint32_t nbi = (uint32_t)(BPAD / C);   // row slots per source rank
+            const uint32_t mine = smem_u32(s_red) + ((uint32_t)rank * nbi * kTileN + (uint32_t)r) * 4u;
+            uint32_t owner[4];
+#pragma unroll
+            for (int cr = 0; cr < 4; ++cr) owner[cr] = dsmem_addr(mine, (uint32_t)(cr & (C - 1)));
 #pragma unroll
             for (int b = 0; b < BPAD; ++b)
-              if (b < p.batch) red[b * kTileN + r] = v[b];
+              if (b < p.batch) dsmem_st_f32(owner[b & (C - 1)] + (uint32_t)((b / C) * kTileN) * 4u, v[b]);
           }
         }
       }
@@ -340,32 +361,34 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 
   tc_fence_before_sync();
   __syncthreads();
+  if (tid == 0) BAS_TRACE_SET(11, BAS_TRACE_CLOCK() - hdr->t0);    // roles done
   if (C > 1) {
-    // Add the cluster's partials in rank order: rank i finishes batch rows i, i+C, ...
+    // Every CTA of the cluster has pushed its partials once all have passed this barrier; rank i
+    // then adds, in rank order, what it received for batch rows i, i+C, ... and stores them.  Nothing
+    // touches a peer's shared memory after the barrier, so CTAs may leave independently.
     cluster_sync_all();
     if (hdr->k_act > 0 && hdr->abort_flag == 0 && warp >= kEpiWarp0) {
       const int r = tid - 32 * kEpiWarp0;
       const int col = n0 + r;
       if (r < width && col < p.n) {
-        const uint32_t mine = smem_u32(s_stage) + (uint32_t)r * 4u;
-        uint32_t peer[4];
-#pragma unroll
-        for (int cr = 0; cr < 4; ++cr) peer[cr] = dsmem_addr(mine, (uint32_t)min(cr, C - 1));
-        for (int b = rank; b < p.batch; b += C) {
+        const int nbi = BPAD / C;
+        for (int bi = 0; bi * C + rank < p.batch; ++bi) {
           float sum = 0.f;
 #pragma unroll
-          for (int cr = 0; cr < 4; ++cr)
-            if (cr < C) sum += dsmem_ld_f32(peer[cr] + (uint32_t)(b * kTileN) * 4u);
-          p.y[(size_t)b * p.ldy + col] = __float2half_rn(sum);
+          for (int q = 0; q < 4; ++q)
+            if (q < C) sum += s_red[(q * nbi + bi) * kTileN + r];
+          p.y[(size_t)(bi * C + rank) * p.ldy + col] = __float2half_rn(sum);
         }
       }
     }
-    cluster_sync_all();   // nobody leaves while a peer may still read its shared memory
   }
-  if (hdr->abort_flag != 0 && tid == 0) {
+  if (tid == 0) BAS_TRACE_SET(12, BAS_TRACE_CLOCK() - hdr->t0);    // cluster combine done
+  if (hdr->abort_flag != 0 && warp < kProducers && lane == 0) {
     // Gave up somewhere: do not leave while copies may still be landing in this CTA's memory.
     int zero = 0;
-    for (int g = max(0, armed - S); g < armed; ++g) (void)mbar_wait(&hdr->full[g % S], (g / S) & 1, &zero);
+    const int per_lap = (S + kProducers - 1) / kProducers;   // this warp's groups in one trip round the ring
+    for (int i = 0, g = armed_next - kProducers; i < min(armed_cnt, per_lap) && g >= 0; ++i, g -= kProducers)
+      (void)mbar_wait(&hdr->full[g % S], (g / S) & 1, &zero);
   }
   if (warp == kEpiWarp0) {
     tc_fence_after_sync();
@@ -492,7 +515,7 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
 
   // cluster size: larger batches split the active blocks of a wider range over 2 or 4 CTAs
   int want = (p.flags >> 8) & 7;
-  if (want == 0) want = p.batch > 32 ? 4 : (p.batch > 16 ? 2 : 1);
+  if (want == 0) want = 4;   // measured best at every batch size: fewest copy and MMA issues per byte
   int cluster = 1, ranges = sm_count < units ? sm_count : units;
   for (int c = want; c > 1; c >>= 1) {
     if (c != 2 && c != 4) continue;
@@ -512,10 +535,13 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   p.ranges = ranges;
   p.wslot = (wsub_max * kRowBytes + 1023) / 1024 * 1024;
   const size_t stage_bytes = (size_t)p.wslot + BPAD * 128;
-  const size_t room = kSmemBudget - fixed;
+  const size_t red_bytes = cluster > 1 ? (size_t)BPAD * kTileN * 4 : 0;   // partials pushed by the cluster
+  if (fixed + red_bytes + 2 * stage_bytes > kSmemBudget) return cudaErrorInvalidValue;
+  const size_t room = kSmemBudget - fixed - red_bytes;
   // One barrier hand-off costs a few hundred cycles per role: a slot gathers enough blocks (about
   // 24 KiB) for the hand-offs to stay off the critical path.
-  int group = (int)((24 * 1024 + stage_bytes - 1) / stage_bytes);
+  int group = (int)((24 * 1024 + stage_bytes / 2) / stage_bytes);   // nearest
+  if (group < 1) group = 1;
   if (group > 16) group = 16;
   int stages = (int)(room / (stage_bytes * group));
   if (stages < 3) {
@@ -526,9 +552,7 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   if (stages < 2) return cudaErrorInvalidValue;
   p.stages = stages;
   p.group = group;
-  size_t smem = fixed + (size_t)stages * group * stage_bytes;
-  const size_t red_bytes = (size_t)p.batch * kTileN * 4;   // cluster mode reuses the ring for the partial
-  if (cluster > 1 && (size_t)stages * group * stage_bytes < red_bytes) smem = fixed + red_bytes;
+  const size_t smem = fixed + red_bytes + (size_t)stages * group * stage_bytes;
 
   CUtensorMap xmap;
   cudaError_t e = get_x_tensor_map(p, BPAD, &xmap);
