@@ -426,12 +426,9 @@ def run_gpu(args) -> None:
             "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
             "algorithmic_bytes_per_launch": N_KEEP[64] * SLAB_BYTES, "traffic": None,
         }
-        tp = ROOT / "profiles" / "traffic.json"
-        if tp.exists():
-            try:
-                roofline["traffic"] = json.loads(tp.read_text()).get("umma_colsplit_kernel_b64_bytes_per_launch")
-            except (ValueError, OSError):
-                pass
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
+        # profiles/umma_colsplit_down_proj_b64.md (same workload, one launch)
+        roofline["traffic"] = 44_349_696
         cpu = cpu_baseline() if world == 1 else None
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
