@@ -137,6 +137,25 @@ BAS_API int bas_select_budget(const void* x_dev, int64_t ldx, int batch, int k, 
                       int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
                       double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream);
 
+/* ---- selection for callers that must not allocate -------------------------------------------
+ * No counterpart in the reference.  Same result as bas_select_topk, but the caller passes no
+ * workspace and the library allocates nothing: the kernel's scratch (one fp64 score per block and
+ * an arrival counter, BAS_NOALLOC_MAX_BLOCKS * 8 + 256 bytes) is a fixed device array inside the
+ * library image, which every GPU that loads libbas keeps until the process exits.
+ * It is meant for hosts that have handed every spare byte of device memory to a pool of their own
+ * (an inference server that sizes its KV-cache arena to fill the GPU) or whose decode loop runs
+ * under a rule that no CUDA allocation call may happen after start-up: for them cudaMalloc either
+ * fails or stalls the device, so a workspace cannot be conjured at call time.
+ *  - K / 64 above BAS_NOALLOC_MAX_BLOCKS returns BAS_ERR_TOO_LARGE.
+ *  - The first call on each device looks up the array's device address (the device must be
+ *    current); make that first call before starting any stream capture.
+ *  - All calls on a device share the one array: two calls that overlap on the GPU (different
+ *    streams) race on it.  Calls on one stream are safe back to back. */
+#define BAS_NOALLOC_MAX_BLOCKS 1024   /* K up to 65 536 */
+BAS_API int bas_select_topk_noalloc(const void* x_dev, int64_t ldx, int batch, int k, int n_keep, int score_kind,
+                                    int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
+                                    double* scores_out_dev, void* stream);
+
 /* ---- host-buffer operator -------------------------------------------------------------------
  * The call pattern of _sparse_linear (scripts/bench_roundrobin_e2e_decode.py:179-284) for a caller
  * whose activations live in host memory: a handle owns the packed weight, the device staging

@@ -52,6 +52,7 @@ _SIGNATURES = {
     "bas_select_workspace_bytes": (_sz, [_i]),
     "bas_select_topk": (_i, [_vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bas_select_budget": (_i, [_vp, _i64, _i, _i, C.c_double, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "bas_select_topk_noalloc": (_i, [_vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "bas_linear_create": (_i, [C.POINTER(_vp), _vp, _i, _i, _i]),
     "bas_linear_forward_host": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "bas_linear_forward_host_ids": (_i, [_vp, _vp, _i, _vp, _i, _vp]),

@@ -210,3 +210,60 @@ cudaError_t launch_select(const SelectParams& p, int sm_count, cudaStream_t stre
 }
 
 }  // namespace bas
+
+// ---------------------------------------------------------------------------------------------
+// Selection without any allocation: the kernel's scratch (per-block scores + the arrival counter)
+// lives in a fixed device array that is part of the library image.  See bas_select_topk_noalloc in
+// include/bas.h for who needs this and what it costs.
+// ---------------------------------------------------------------------------------------------
+namespace bas {
+namespace {
+// [0,256): arrival counter (first word), [256, ...): one fp64 score per activation block.
+static __device__ __align__(256) unsigned char g_select_scratch[256 + sizeof(double) * BAS_NOALLOC_MAX_BLOCKS];
+}  // namespace
+}  // namespace bas
+
+extern "C" BAS_API int bas_select_topk_noalloc(const void* x_dev, int64_t ldx, int batch, int k, int n_keep,
+                                               int score_kind, int32_t* ids_out_dev, int32_t* count_out_dev,
+                                               uint8_t* bitmap_out_dev, double* scores_out_dev, void* stream) {
+  using namespace bas;
+  if (x_dev == nullptr || ids_out_dev == nullptr || count_out_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  if (batch <= 0 || k < kBlockK || ldx < k || (((uintptr_t)x_dev) & 15u) != 0 || (ldx & 7) != 0)
+    return BAS_ERR_INVALID_ARGUMENT;
+  const int nb = k / kBlockK;
+  if (nb > BAS_NOALLOC_MAX_BLOCKS) return BAS_ERR_TOO_LARGE;   // the fixed scratch holds no more scores
+  if (score_kind != BAS_SCORE_NORM && score_kind != BAS_SCORE_ENERGY) return BAS_ERR_INVALID_ARGUMENT;
+  if (n_keep < 0 || n_keep > nb) return BAS_ERR_INVALID_ARGUMENT;
+
+  // In host code the array's name is only a handle; the device address has to be asked for, once per
+  // device, with that device current.  The first call on a device does this.
+  static void* scratch_addr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BAS_ERR_CUDA;
+  void* scratch = scratch_addr[dev];
+  if (scratch == nullptr) {
+    if (cudaGetSymbolAddress(&scratch, g_select_scratch) != cudaSuccess || scratch == nullptr) return BAS_ERR_CUDA;
+    scratch_addr[dev] = scratch;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  // The array keeps whatever the previous call left: the arrival counter must start at zero.
+  if (cudaMemsetAsync(scratch, 0, 256, s) != cudaSuccess) return BAS_ERR_CUDA;
+
+  SelectParams p;
+  p.x = (const __half*)x_dev;
+  p.ldx = (long long)ldx;
+  p.batch = batch;
+  p.k = k;
+  p.nb = nb;
+  p.mode = 0;
+  p.n_keep = n_keep;
+  p.score_kind = score_kind;
+  p.energy_keep = 0.0;
+  p.ids_out = ids_out_dev;
+  p.count_out = count_out_dev;
+  p.bitmap_out = bitmap_out_dev;
+  p.scores_out = scores_out_dev;
+  p.ws_done = (unsigned int*)scratch;
+  p.ws_scores = (double*)((unsigned char*)scratch + 256);
+  return launch_select(p, 0, s) == cudaSuccess ? BAS_OK : BAS_ERR_CUDA;
+}
