@@ -316,14 +316,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 #pragma unroll
             for (int w = 0; w < kIssuers; ++w) {
               if (w < k_mine) {   // issuer order: the sum never depends on timing
+                uint32_t regs[BPAD / 16][16];
 #pragma unroll
-                for (int cc = 0; cc < BPAD / 16; ++cc) {
-                  uint32_t regs[16];
-                  tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(w * 64 + cc * 16), regs);
-                  tmem_ld_wait();
+                for (int cc = 0; cc < BPAD / 16; ++cc)
+                  tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(w * 64 + cc * 16), regs[cc]);
+                tmem_ld_wait();
 #pragma unroll
-                  for (int e = 0; e < 16; ++e) v[cc * 16 + e] += __uint_as_float(regs[e]);
-                }
+                for (int cc = 0; cc < BPAD / 16; ++cc)
+#pragma unroll
+                  for (int e = 0; e < 16; ++e) v[cc * 16 + e] += __uint_as_float(regs[cc][e]);
               }
             }
             tc_fence_before_sync();
@@ -341,14 +342,30 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             // Cluster mode (one sub-tile per CTA): batch row b is finished by rank b % C.  Push this
             // CTA's partial of each row into the owner's shared memory; the stores are posted, the
             // cluster barrier below makes them visible.
-            const uint32_t nbi = (uint32_t)(BPAD / C);   // row slots per source rank
-            const uint32_t mine = smem_u32(s_red) + ((uint32_t)rank * nbi * kTileN + (uint32_t)r) * 4u;
+            // Layout of the receive buffer: [source rank][column r][row slot], slots contiguous, so
+            // that four of a thread's values for one owner go out as one 16-byte store.
+            const int nbi = BPAD / C;        // row slots per (source rank, column); a multiple of 4
+            const uint32_t mine = smem_u32(s_red) + (uint32_t)((rank * kTileN + r) * nbi) * 4u;
             uint32_t owner[4];
 #pragma unroll
-            for (int cr = 0; cr < 4; ++cr) owner[cr] = dsmem_addr(mine, (uint32_t)(cr & (C - 1)));
+            for (int o = 0; o < 4; ++o) owner[o] = dsmem_addr(mine, (uint32_t)(o & (C - 1)));
+            if (C == 4) {
 #pragma unroll
-            for (int b = 0; b < BPAD; ++b)
-              if (b < p.batch) dsmem_st_f32(owner[b & (C - 1)] + (uint32_t)((b / C) * kTileN) * 4u, v[b]);
+              for (int o = 0; o < 4; ++o)
+#pragma unroll
+                for (int b4 = 0; b4 < BPAD / 16; ++b4)   // slots 4*b4 .. 4*b4+3 <-> rows 16*b4 + o + {0,4,8,12}
+                  if (16 * b4 + o < p.batch)
+                    dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * b4), v[16 * b4 + o], v[16 * b4 + o + 4],
+                                    v[16 * b4 + o + 8], v[16 * b4 + o + 12]);
+            } else {
+#pragma unroll
+              for (int o = 0; o < 2; ++o)
+#pragma unroll
+                for (int b8 = 0; b8 < BPAD / 8; ++b8)    // slots 4*b8 .. 4*b8+3 <-> rows 8*b8 + o + {0,2,4,6}
+                  if (8 * b8 + o < p.batch)
+                    dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * b8), v[8 * b8 + o], v[8 * b8 + o + 2],
+                                    v[8 * b8 + o + 4], v[8 * b8 + o + 6]);
+            }
           }
         }
       }
@@ -376,7 +393,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           float sum = 0.f;
 #pragma unroll
           for (int q = 0; q < 4; ++q)
-            if (q < C) sum += s_red[(q * nbi + bi) * kTileN + r];
+            if (q < C) sum += s_red[(q * kTileN + r) * nbi + bi];
           p.y[(size_t)(bi * C + rank) * p.ldy + col] = __float2half_rn(sum);
         }
       }
