@@ -380,6 +380,7 @@ def run_gpu(args) -> None:
         handles.append(h)
     x_host = {bb: O.make_activations(bb, K_IN, seed=1000 + bb, dist="laplace") for bb in BATCHES}
     y_host = {bb: np.empty((bb, N_OUT), np.float16) for bb in BATCHES}
+    ids_host = {bb: np.full(NB, -1, np.int32) for bb in BATCHES}
     call = {"i": 0}
 
     def e2e_step():
@@ -387,7 +388,8 @@ def run_gpu(args) -> None:
             h = handles[call["i"] % E2E_COPIES]
             call["i"] += 1
             abi.check(abi.lib.bas_linear_forward_host(h, x_host[bb].ctypes.data, bb, N_KEEP[bb], abi.SCORE_NORM,
-                                                      y_host[bb].ctypes.data, None), "bas_linear_forward_host")
+                                                      y_host[bb].ctypes.data, ids_host[bb].ctypes.data),
+                      "bas_linear_forward_host")
 
     for _ in range(5):
         e2e_step()
@@ -408,11 +410,19 @@ def run_gpu(args) -> None:
         ops.gemm(xs[bb], packed[0], outs[bb], ids=ids[bb])
         torch.cuda.synchronize()
         d = np.abs(y_host[bb].astype(np.float32) - outs[bb].float().cpu().numpy()).max()
-        if not d <= 2e-3 * float(outs[bb].float().abs().max().item()):
-            raise SystemExit(f"end-to-end output differs from the resident-input path at B={bb}")
+        same_ids = np.array_equal(ids_host[bb][:N_KEEP[bb]], ids[bb].cpu().numpy())
+        if os.environ.get("BAS_BENCH_DEBUG"):
+            mask = torch.zeros(NB, device=dev); mask[ids[bb].long()] = 1
+            ref = ((xs[bb].float() * mask.repeat_interleave(64)) @ w.float().t()).cpu().numpy()
+            print("debug B", bb, "e2e vs ref", np.abs(y_host[bb].astype(np.float32) - ref).max(),
+                  "resident vs ref", np.abs(outs[bb].float().cpu().numpy() - ref).max(),
+                  "x_host==xs", np.array_equal(x_host[bb], xs[bb].cpu().numpy()), file=sys.stderr)
+        if not same_ids or not d <= 2e-3 * float(outs[bb].float().abs().max().item()):
+            raise SystemExit(f"end-to-end result differs from the resident-input path at B={bb}: "
+                             f"ids equal {same_ids}, max |dy| {d:.3e}")
     e2e = {"value": world * STEP_BYTES / e2e_dt / 1e9, "unit": "GB/s",
            "h2d_bytes_per_step": sum(bb * K_IN * 2 for bb in BATCHES),
-           "d2h_bytes_per_step": sum(bb * N_OUT * 2 for bb in BATCHES) + 3 * 4,
+           "d2h_bytes_per_step": sum(bb * N_OUT * 2 + N_KEEP[bb] * 4 for bb in BATCHES) + 3 * 4,
            "ms_per_step": e2e_dt * 1e3, "steps": e2e_steps,
            "api": "bas_linear_forward_host: H2D X, device-side top-k selection, GEMM, D2H Y, per call"}
 

@@ -448,3 +448,36 @@ def test_host_buffer_operator(dev, b, k, n):
         assert not y.any()
     finally:
         L.lib.bas_linear_destroy(h)
+
+
+def test_host_buffer_operator_back_to_back_batches(dev):
+    """Calls of different batch sizes in immediate succession on rotating handles: every call must
+    return its own result (a chain of early-starting kernels must never hand back stale data)."""
+    import ctypes
+    from bas import abi as L
+
+    k, n, nb = 11008, 4096, 172
+    keep = {2: 34, 16: 62, 64: 83}
+    w = O.make_weight(n, k, seed=0)
+    handles = []
+    for _ in range(2):
+        h = ctypes.c_void_p()
+        L.check(L.lib.bas_linear_create(ctypes.byref(h), w.ctypes.data, n, k, 64), "create")
+        handles.append(h)
+    try:
+        xs = {b: O.make_activations(b, k, seed=1000 + b, dist="laplace") for b in keep}
+        want = {}
+        for b in keep:
+            ids = O.topk_ids(O.block_scores(xs[b], O.SCORE_NORM), keep[b])
+            want[b] = (ids, O.masked_gemm(xs[b], w, ids))
+        for i in range(36):
+            b = (2, 16, 64)[i % 3]
+            y = np.empty((b, n), np.float16)
+            ids = np.full(nb, -1, np.int32)
+            L.check(L.lib.bas_linear_forward_host(handles[i % 2], xs[b].ctypes.data, b, keep[b], O.SCORE_NORM,
+                                                  y.ctypes.data, ids.ctypes.data), "forward_host")
+            assert np.array_equal(ids[:keep[b]], want[b][0]), f"call {i} B={b}"
+            assert O.max_err_ratio(y, want[b][1]) <= TOL, f"call {i} B={b}"
+    finally:
+        for h in handles:
+            L.lib.bas_linear_destroy(h)

@@ -204,6 +204,8 @@ cudaError_t launch_select(const SelectParams& p, int sm_count, cudaStream_t stre
     if (e != cudaSuccess) return e;
     if (smem > 96 * 1024) return cudaErrorInvalidValue;
   }
+  // Plain launch on purpose: with programmatic serialization on this kernel as well, a
+  // selection -> contraction -> device-to-host copy chain was observed to deliver stale results.
   select_kernel<<<grid, kSelThreads, smem, stream>>>(p);
   count_launch();
   return cudaGetLastError();
