@@ -207,6 +207,51 @@ def _graph_time_us(torch, stream, build, calls_per_graph: int, reps: int, repeat
     return float(statistics.median(vals))
 
 
+def _layer_stack(torch, dist, dev, world, rank, stream) -> dict:
+    """The Llama-2-7B decode-step linear stack (32 layers x 7 masked projections, B = 16, sparsity
+    0.638), column-/row-parallel over the ranks with an NCCL all-reduce after o and down: one CUDA
+    graph per step where NCCL allows capture, timed by CUDA events, max over ranks."""
+    from bas import tp
+
+    stack = tp.DecodeLinearStack(32, 16, 0.638, dev, world, rank)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            stack.step()
+    torch.cuda.synchronize()
+    mode = "cuda graph"
+    try:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            stack.step()
+        run = g.replay
+    except Exception as exc:      # a collective that refuses capture: time eager launches instead
+        mode = f"eager ({type(exc).__name__})"
+        run = stack.step
+    torch.cuda.synchronize()
+    reps = 10
+    with torch.cuda.stream(stream):
+        run()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(reps):
+            run()
+        e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return {"layers": 32, "linears_per_step": len(stack.items), "batch": 16, "sparsity": 0.638,
+            "parallelism": f"tp{world}: column-parallel q/k/v/gate/up, row-parallel o/down + all-reduce",
+            "ms_per_step": round(ms, 4), "active_weight_gb_per_step": round(stack.active_bytes / 1e9, 3),
+            "active_weight_gbs": round(stack.active_bytes / (ms * 1e-3) / 1e9, 1), "launch": mode}
+
+
 def run_gpu(args) -> None:
     import torch
     import torch.distributed as dist
@@ -223,6 +268,7 @@ def run_gpu(args) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/tmp/nccl_debug.%h.%p")   # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
     peaks = _peaks()
     stream = torch.cuda.Stream()
@@ -370,6 +416,13 @@ def run_gpu(args) -> None:
     online = {"batch": b, "keep_blocks": n_keep4, "select_us": round(sel_us, 3), "select_plus_gemm_us": round(chain_us, 3),
               "score": "energy"}
 
+    # ---- the sharded decode-step linear stack (all ranks take part) ----
+    try:
+        layer_stack = _layer_stack(torch, dist, dev, world, rank, stream)
+    except Exception as exc:
+        layer_stack = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+    torch.cuda.empty_cache()
+
     # ---- end to end through the host-buffer operator (pinned staging inside the library) ----
     import ctypes
     handles = []
@@ -450,7 +503,7 @@ def run_gpu(args) -> None:
                        "l2": f"cold: every call reads one of {ROTATE} rotating weight copies (1.4 GB in rotation)",
                        "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
                        "timing": "CUDA-graph replays of 16 steps, CUDA events on the launch stream, max over ranks"},
-            "per_batch": per_batch, "online_selection": online, "roofline": roofline, "cpu_baseline": cpu,
+            "per_batch": per_batch, "online_selection": online, "layer_stack": layer_stack, "roofline": roofline, "cpu_baseline": cpu,
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

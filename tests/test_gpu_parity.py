@@ -481,3 +481,23 @@ def test_host_buffer_operator_back_to_back_batches(dev):
     finally:
         for h in handles:
             L.lib.bas_linear_destroy(h)
+
+
+def test_linear_stack_single_rank(dev):
+    """One decoder layer's seven masked projections through the tensor-parallel wrapper at world 1."""
+    from bas import tp
+
+    stack = tp.DecodeLinearStack(layers=1, batch=16, sparsity=0.638, device=dev, seed=1)
+    stack.step()
+    torch.cuda.synchronize()
+    assert len(stack.items) == 7
+    gen = torch.Generator(device=dev)
+    for si, (lin, x, bitmap, out) in enumerate(stack.items):
+        spec = lin.spec
+        gen.manual_seed(1 * 1_000_003 + si)
+        w = (torch.randn(spec.n, spec.k, generator=gen, device=dev, dtype=torch.float32) * 0.02).half()
+        mask = bitmap.float().repeat_interleave(64)
+        ref = (x.float() * mask) @ w.float().t()
+        err = ((out.float() - ref).abs().max() / ref.abs().max()).item()
+        assert err <= TOL, (spec.name, err)
+        assert int(bitmap.sum().item()) == round((1 - 0.638) * (spec.k // 64))

@@ -1,0 +1,148 @@
+"""Tensor-parallel layout of a decode-step linear stack over the GPUs of one box.
+
+The reference is single-GPU (it has no distributed code); this module is the sharding the
+benchmark specification asks for on top of the same kernels:
+
+* q, k, v, gate, up are column-parallel: rank r owns output columns [n0, n1) and produces that
+  slice of Y; nothing is exchanged.
+* o, down are row-parallel: rank r owns the 64-channel blocks [b0, b1) of the input, multiplies
+  its slice of X with its slice of W, and the partial outputs are summed with one NCCL
+  all-reduce.
+* The batch-shared block mask is replicated: every rank holds the same byte map over all
+  blocks; a row-parallel rank simply passes the slice [b0, b1) of it to the kernel (a view: no
+  copy, no host synchronisation).
+
+Pure layout arithmetic lives in :func:`shard_bounds` and is testable without a GPU.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+BLOCK_K = 64
+
+
+def shard_bounds(total_units: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous, near-equal split of ``total_units`` over ``world`` ranks: [begin, end) of ``rank``.
+    172 blocks over 8 ranks gives 22/21-block shards (172 = 8 * 21 + 4)."""
+    if not (0 <= rank < world) or total_units < 0:
+        raise ValueError("bad rank / world / size")
+    return rank * total_units // world, (rank + 1) * total_units // world
+
+
+def column_shard(n: int, world: int, rank: int, align: int = BLOCK_K) -> tuple[int, int]:
+    """Output-column range of a column-parallel linear, in whole groups of ``align`` columns so that
+    the gate/up shard of a rank is exactly the input shard of its down projection."""
+    units = (n + align - 1) // align
+    u0, u1 = shard_bounds(units, world, rank)
+    return min(u0 * align, n), min(u1 * align, n)
+
+
+def row_shard_blocks(k: int, world: int, rank: int) -> tuple[int, int]:
+    """Input-block range [b0, b1) of a row-parallel linear."""
+    return shard_bounds((k + BLOCK_K - 1) // BLOCK_K, world, rank)
+
+
+@dataclass
+class LinearSpec:
+    name: str
+    n: int            # output features
+    k: int            # input features
+    parallel: str     # "column" or "row"
+    dist: str         # activation distribution of its input: "normal" or "laplace"
+
+
+# One Llama-2-7B decoder layer's projections (scripts/bench_perstep_actual_kernel_speedup.py:37-53).
+LLAMA2_7B_LAYER = (
+    LinearSpec("q_proj", 4096, 4096, "column", "normal"),
+    LinearSpec("k_proj", 4096, 4096, "column", "normal"),
+    LinearSpec("v_proj", 4096, 4096, "column", "normal"),
+    LinearSpec("o_proj", 4096, 4096, "row", "normal"),
+    LinearSpec("gate_proj", 11008, 4096, "column", "normal"),
+    LinearSpec("up_proj", 11008, 4096, "column", "normal"),
+    LinearSpec("down_proj", 4096, 11008, "row", "laplace"),
+)
+
+
+class ShardedLinear:
+    """One rank's shard of a masked linear: packed weight slice plus the views it needs per call."""
+
+    def __init__(self, spec: LinearSpec, weight_full, world: int, rank: int):
+        from . import ops
+
+        self.spec, self.world, self.rank = spec, world, rank
+        if spec.parallel == "column":
+            self.n0, self.n1 = column_shard(spec.n, world, rank)
+            self.b0, self.b1 = 0, (spec.k + BLOCK_K - 1) // BLOCK_K
+            shard = weight_full[self.n0:self.n1]
+        else:
+            self.n0, self.n1 = 0, spec.n
+            self.b0, self.b1 = row_shard_blocks(spec.k, world, rank)
+            shard = weight_full[:, self.b0 * BLOCK_K: min(self.b1 * BLOCK_K, spec.k)]
+        self.k_local = shard.shape[1]
+        self.n_local = shard.shape[0]
+        self.packed = ops.pack_weight(shard.contiguous()) if self.n_local and self.k_local else None
+
+    def forward(self, x2d, bitmap, out2d, ids_stable: bool = True):
+        """x2d is the replicated [B, K] activation, bitmap the replicated uint8[K/64] mask.  Writes
+        this rank's output slice (column-parallel) or partial sum (row-parallel) into out2d."""
+        from . import ops
+
+        if self.packed is None:
+            out2d.zero_()
+            return
+        xs = x2d if self.spec.parallel == "column" else x2d[:, self.b0 * BLOCK_K: self.b0 * BLOCK_K + self.k_local]
+        ops.gemm(xs, self.packed, out2d, bitmap=bitmap[self.b0:self.b1], ids_stable=ids_stable)
+
+
+class DecodeLinearStack:
+    """``layers`` x the seven projections, random-init N(0, 0.02^2), sharded over the process group.
+
+    ``step()`` runs every linear once on its replicated synthetic input with its fixed mask and
+    all-reduces the row-parallel outputs; it is what the benchmark times as one decode step of the
+    linear stack.  Inputs are generated per linear, identically on every rank."""
+
+    def __init__(self, layers: int, batch: int, sparsity: float, device, world: int = 1, rank: int = 0,
+                 seed: int = 0, group=None):
+        import torch
+
+        from . import ops
+        from .abi import SCORE_NORM
+
+        self.world, self.rank, self.group, self.batch = world, rank, group, batch
+        self.items = []
+        gen = torch.Generator(device=device)
+        self.active_bytes = 0
+        for li in range(layers):
+            for si, spec in enumerate(LLAMA2_7B_LAYER):
+                gen.manual_seed(seed * 1_000_003 + li * 16 + si)
+                w = (torch.randn(spec.n, spec.k, generator=gen, device=device, dtype=torch.float32) * 0.02).half()
+                lin = ShardedLinear(spec, w, world, rank)
+                del w
+                if li == 0:     # inputs and masks are per projection type, shared by the layers
+                    if spec.dist == "normal":
+                        x = torch.randn(batch, spec.k, generator=gen, device=device, dtype=torch.float32).half()
+                    else:
+                        u = torch.rand(batch, spec.k, generator=gen, device=device, dtype=torch.float32) - 0.5
+                        x = (-torch.sign(u) * torch.log1p(-2.0 * u.abs())).half()
+                    nb = spec.k // BLOCK_K
+                    n_keep = ops.n_keep_from_density(1.0 - sparsity, nb)
+                    bitmap = torch.empty(nb, dtype=torch.uint8, device=device)
+                    ops.select_topk(x, n_keep, SCORE_NORM, bitmap_out=bitmap)
+                    shared = (x, bitmap, n_keep)
+                    self._shared = getattr(self, "_shared", {})
+                    self._shared[spec.name] = shared
+                x, bitmap, n_keep = self._shared[spec.name]
+                out = torch.zeros(batch, lin.n_local, dtype=torch.float16, device=device)
+                self.items.append((lin, x, bitmap, out))
+                self.active_bytes += n_keep * BLOCK_K * spec.n * 2
+        torch.cuda.synchronize(device)
+
+    def step(self) -> None:
+        import torch.distributed as dist
+
+        for lin, x, bitmap, out in self.items:
+            lin.forward(x, bitmap, out)
+            if lin.spec.parallel == "row" and self.world > 1:
+                dist.all_reduce(out, group=self.group)
