@@ -49,6 +49,18 @@ WORKLOAD = ("llama2-7b down_proj X[B,11008] Laplace x W[4096,11008] N(0,0.02), B
             "batch-shared top-k block masks 34/62/83 of 172")
 
 
+_STDOUT_FD = None
+
+
+def _emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _STDOUT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_STDOUT_FD, data)
+
+
 def _peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -125,7 +137,7 @@ def run_reference(args) -> None:
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    _emit(line)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -506,7 +518,7 @@ def run_gpu(args) -> None:
             "per_batch": per_batch, "online_selection": online, "layer_stack": layer_stack, "roofline": roofline, "cpu_baseline": cpu,
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
-        print(json.dumps(line), flush=True)
+        _emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -541,6 +553,12 @@ def main() -> None:
     ap.add_argument("--profile-case", type=int, default=0, metavar="B",
                     help="run only a few eager launches at batch B (for profiler captures) and exit")
     args = ap.parse_args()
+    # stdout carries exactly one JSON line: libraries that chat on fd 1 (NCCL prints its version
+    # there) are sent to stderr, and the line is written to the saved descriptor at the end.
+    global _STDOUT_FD
+    sys.stdout.flush()
+    _STDOUT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.profile_case:
         run_profile_case(args.profile_case)
     elif args.impl == "reference":
