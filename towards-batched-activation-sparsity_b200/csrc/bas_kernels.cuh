@@ -20,6 +20,8 @@ struct GemmParams {
   int stages;               // ring slots
   int group;                // blocks per ring slot: one barrier hand-off covers this many chunks
   int wslot;                // bytes reserved per slot for a weight chunk (multiple of 1024)
+  int issuers;              // MMA-issuing warps in use (2 or 4), each with its own accumulators
+  int tile_cols;            // output columns one pass of a CTA covers: 128, or 256 (two MMA halves)
   __half* y;                // [batch, N], row stride ldy
   long long ldy;
   int flags;                // kFlag* bits

@@ -38,7 +38,8 @@ constexpr int kIssuers = 4;             // MMA-issuing warps; each owns one accu
 constexpr int kEpiWarp0 = kProducers + kIssuers;   // first epilogue warp (a multiple of 4: TMEM lane quarters)
 constexpr int kEpiThreads = 128;
 constexpr int kUmmaThreads = 32 * kEpiWarp0 + kEpiThreads;
-constexpr int kTmemCols = 64 * kIssuers; // one 64-column fp32 accumulator per issuer
+constexpr int kHalves = 2;               // a pass covers up to 2 x 128 output columns
+constexpr int kTmemCols = 64 * kIssuers * kHalves;   // one 64-column fp32 accumulator per (issuer, half): all 512
 constexpr int kMmaSpanBytes = 128 * kRowBytes;   // an M=128 operand read spans 16 KiB from the slot base
 
 struct UmmaSmemHeader {
@@ -71,7 +72,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   uint16_t* s_ids = (uint16_t*)sp;
   sp += ((size_t)p.nb * 2 + 127) / 128 * 128;
   float* s_red = (float*)sp;   // cluster mode: partials pushed here by the cluster's CTAs, [source rank][row slot][128]
-  if (p.cluster > 1) sp += (size_t)BPAD * kTileN * sizeof(float);
+  if (p.cluster > 1) sp += (size_t)(p.tile_cols / kTileN) * BPAD * kTileN * sizeof(float);
   uint8_t* s_stage = (uint8_t*)(((uintptr_t)sp + 1023) & ~(uintptr_t)1023);  // swizzle atoms need 1 KiB alignment
   const int S = p.stages, G = p.group;
   const int tile_bytes = p.wslot + kXTileBytes;   // multiple of 1024
@@ -82,10 +83,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 
   if (tid < S) {
     mbar_init(&hdr->full[tid], 1);
-    mbar_init(&hdr->empty[tid], kIssuers);
+    mbar_init(&hdr->empty[tid], p.issuers);
     fence_barrier_init();
   } else if (tid == 64) {
-    mbar_init(&hdr->acc_full, kIssuers);
+    mbar_init(&hdr->acc_full, p.issuers);
     mbar_init(&hdr->acc_empty, kEpiThreads / 32);
     mbar_init(&hdr->ids_ready, 1);
     hdr->abort_flag = 0;
@@ -102,7 +103,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = hdr->tmem_base;
-  if (tid == 0) BAS_TRACE_SET(8, BAS_TRACE_CLOCK() - hdr->t0);     // preamble done
+  if (tid == 0) {
+    BAS_TRACE_SET(8, BAS_TRACE_CLOCK() - hdr->t0);     // preamble done
+    BAS_TRACE_SET(13, p.cluster * 1000000 + p.tile_cols * 1000 + p.stages * 10 + p.group);
+    BAS_TRACE_SET(14, p.ranges);
+  }
 
   // this CTA's columns and its share of the active list
   const int C = p.cluster;
@@ -111,7 +116,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   const int units = p.npad >> 3;
   const int n0 = col_begin(range, units, p.ranges), n1 = col_begin(range + 1, units, p.ranges);
   const int width = n1 - n0;
-  const int n_sub = (width + kTileN - 1) / kTileN;
+  const int TW = p.tile_cols;                       // columns per pass: 128 or 256
+  const int n_sub = (width + TW - 1) / TW;
 
   // Nothing so far touched global memory.  The id list may be the previous kernel's output unless
   // the caller declared it stable; X and Y always wait for the previous kernel.
@@ -147,7 +153,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         if (lane >= G || m >= M) return false;
         sub = (n_sub == 1) ? 0 : m / k_mine;
         j = s_ids[rank + (m - sub * k_mine) * C];
-        wbytes = min(kTileN, width - sub * kTileN) * kRowBytes;
+        wbytes = min(TW, width - sub * TW) * kRowBytes;
         return true;
       };
       int g = warp;
@@ -163,7 +169,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           __syncwarp();
           if (have)
             bulk_copy_g2s(s_stage + (size_t)ga * stage_bytes + (size_t)lane * tile_bytes,
-                          p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wbytes, &hdr->full[ga]);
+                          p.packed + ((size_t)j * p.npad + n0 + sub * TW) * kRowBytes, wbytes, &hdr->full[ga]);
           armed_next = ga + kProducers;
           ++armed_cnt;
         }
@@ -197,7 +203,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         [[maybe_unused]] const long long tr1 = BAS_TRACE_CLOCK();
         if (have) {
           uint8_t* st = s_stage + (size_t)s * stage_bytes + (size_t)lane * tile_bytes;
-          bulk_copy_g2s(st, p.packed + ((size_t)j * p.npad + n0 + sub * kTileN) * kRowBytes, wbytes, &hdr->full[s]);
+          bulk_copy_g2s(st, p.packed + ((size_t)j * p.npad + n0 + sub * TW) * kRowBytes, wbytes, &hdr->full[s]);
           tma_load_2d(st + p.wslot, &xmap, j * kBlockK, 0, &hdr->full[s]);
         }
         armed_next = g + kProducers;
@@ -229,8 +235,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       // issuer w takes the tiles at positions w, w+4, ... of every sub-tile and adds them into an
       // accumulator of its own; the epilogue adds the four accumulators in issuer order.
       const int w = warp - kProducers;
-      if (lane == 0 && ok) {
-        const uint32_t d = tmem_base + (uint32_t)(w * 64);
+      const int NI = p.issuers;   // 2 or 4
+      if (lane == 0 && ok && w < NI) {
+        const uint32_t d = tmem_base + (uint32_t)(w * kHalves * 64);   // this issuer's accumulators, one per half
         int s = 0, pos = 0, fph = 0;   // slot, position in its group, parity of the slot's current use
         bool used = false;             // this issuer has read from the current slot
         int m = 0;
@@ -246,17 +253,21 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
               ok = false;
               break;
             }
-            if ((ii & (kIssuers - 1)) == w) {
+            if ((ii & (NI - 1)) == w) {
               [[maybe_unused]] const long long tr1 = BAS_TRACE_CLOCK();
               tc_fence_after_sync();
               const uint32_t st = smem_u32(s_stage + (size_t)s * stage_bytes + (size_t)pos * tile_bytes);
-              const uint64_t adesc = umma_desc_kmajor_sw128(st);
               const uint64_t bdesc = umma_desc_kmajor_sw128(st + p.wslot);
+              const int halves = (min(TW, width - sub * TW) > kTileN) ? 2 : 1;
+              for (int h = 0; h < halves; ++h) {
+                const uint64_t adesc = umma_desc_kmajor_sw128(st + (uint32_t)(h * kMmaSpanBytes));
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks) {
-                // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units; an
-                // issuer's first MMA of a sub-tile overwrites its accumulator instead of adding
-                umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc, (ii == w && ks == 0) ? 0u : 1u);
+                for (int ks = 0; ks < 4; ++ks) {
+                  // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units; an
+                  // issuer's first MMA of a sub-tile overwrites its accumulator instead of adding
+                  umma_f16_ss(d + (uint32_t)(h * 64), adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc,
+                              (ii == w && ks == 0) ? 0u : 1u);
+                }
               }
               used = true;
               if (w == 0) {
@@ -302,9 +313,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           p.y[(e / p.n) * p.ldy + (e % p.n)] = __float2half_rn(0.f);
       } else if (ok) {
         for (int sub = 0; sub < n_sub && ok; ++sub) {
-          float v[BPAD];
-#pragma unroll
-          for (int b = 0; b < BPAD; ++b) v[b] = 0.f;
+          const int wsub = min(TW, width - sub * TW);
+          const int halves = (wsub > kTileN) ? 2 : 1;
           if (k_mine > 0) {
             // warp-uniform verdict: tcgen05.ld below needs the whole warp
             if (!__all_sync(0xffffffffu, mbar_wait(&hdr->acc_full, sub & 1, abort_flag))) {
@@ -313,59 +323,81 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             }
             tc_fence_after_sync();
             if (et == 0) BAS_TRACE_SET(10, BAS_TRACE_CLOCK() - hdr->t0);   // accumulators final
+          }
+          for (int h = 0; h < halves; ++h) {   // columns 128 h + r of the pass
+            float v[BPAD];
 #pragma unroll
-            for (int w = 0; w < kIssuers; ++w) {
-              if (w < k_mine) {   // issuer order: the sum never depends on timing
-                uint32_t regs[BPAD / 16][16];
+            for (int b = 0; b < BPAD; ++b) v[b] = 0.f;
+            if (k_mine > 0) {
 #pragma unroll
-                for (int cc = 0; cc < BPAD / 16; ++cc)
-                  tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(w * 64 + cc * 16), regs[cc]);
-                tmem_ld_wait();
+              for (int w = 0; w < kIssuers; ++w) {
+                if (w < k_mine && w < p.issuers) {   // issuer order: the sum never depends on timing
+                  uint32_t regs[BPAD / 16][16];
 #pragma unroll
-                for (int cc = 0; cc < BPAD / 16; ++cc)
+                  for (int cc = 0; cc < BPAD / 16; ++cc)
+                    tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) +
+                                           (uint32_t)((w * kHalves + h) * 64 + cc * 16), regs[cc]);
+                  tmem_ld_wait();
 #pragma unroll
-                  for (int e = 0; e < 16; ++e) v[cc * 16 + e] += __uint_as_float(regs[cc][e]);
+                  for (int cc = 0; cc < BPAD / 16; ++cc)
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) v[cc * 16 + e] += __uint_as_float(regs[cc][e]);
+                }
               }
             }
+            const int rr = h * kTileN + r;   // column within the pass
+            if (C == 1) {
+              const int col = n0 + sub * TW + rr;
+              if (rr < wsub && col < p.n) {
+#pragma unroll
+                for (int b = 0; b < BPAD; ++b)
+                  if (b < p.batch) p.y[(size_t)b * p.ldy + col] = __float2half_rn(v[b]);
+              }
+            } else {
+              // Cluster mode (one pass per CTA): batch row b is finished by rank b % C.  Push this
+              // CTA's partial of each row into the owner's shared memory; the stores are posted, the
+              // cluster barrier below makes them visible.
+              // Layout of the receive buffer: [half][source rank][column r][row slot], slots contiguous,
+              // so that four of a thread's values for one owner go out as one 16-byte store.
+              const int nbi = BPAD / C;        // row slots per (source rank, column); a multiple of 4
+              const uint32_t mine =
+                  smem_u32(s_red) + (uint32_t)(h * BPAD * kTileN + (rank * kTileN + r) * nbi) * 4u;
+              uint32_t owner[4];
+#pragma unroll
+              for (int o = 0; o < 4; ++o) owner[o] = dsmem_addr(mine, (uint32_t)(o & (C - 1)));
+              if (C == 4) {
+#pragma unroll
+                for (int o = 0; o < 4; ++o)
+#pragma unroll
+                  for (int b4 = 0; b4 < BPAD / 16; ++b4)   // slots 4*b4 .. 4*b4+3 <-> rows 16*b4 + o + {0,4,8,12}
+                    if (16 * b4 + o < p.batch) {
+                      if (o == rank)   // own rows stay local
+                        *(float4*)(s_red + h * BPAD * kTileN + (rank * kTileN + r) * nbi + 4 * b4) =
+                            make_float4(v[16 * b4 + o], v[16 * b4 + o + 4], v[16 * b4 + o + 8], v[16 * b4 + o + 12]);
+                      else
+                        dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * b4), v[16 * b4 + o], v[16 * b4 + o + 4],
+                                        v[16 * b4 + o + 8], v[16 * b4 + o + 12]);
+                    }
+              } else {
+#pragma unroll
+                for (int o = 0; o < 2; ++o)
+#pragma unroll
+                  for (int b8 = 0; b8 < BPAD / 8; ++b8)    // slots 4*b8 .. 4*b8+3 <-> rows 8*b8 + o + {0,2,4,6}
+                    if (8 * b8 + o < p.batch) {
+                      if (o == rank)   // own rows stay local
+                        *(float4*)(s_red + h * BPAD * kTileN + (rank * kTileN + r) * nbi + 4 * b8) =
+                            make_float4(v[8 * b8 + o], v[8 * b8 + o + 2], v[8 * b8 + o + 4], v[8 * b8 + o + 6]);
+                      else
+                        dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * b8), v[8 * b8 + o], v[8 * b8 + o + 2],
+                                        v[8 * b8 + o + 4], v[8 * b8 + o + 6]);
+                    }
+              }
+            }
+          }
+          if (k_mine > 0) {
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&hdr->acc_empty);
-          }
-          if (C == 1) {
-            const int col = n0 + sub * kTileN + r;
-            if (r < width - sub * kTileN && col < p.n) {
-#pragma unroll
-              for (int b = 0; b < BPAD; ++b)
-                if (b < p.batch) p.y[(size_t)b * p.ldy + col] = __float2half_rn(v[b]);
-            }
-          } else {
-            // Cluster mode (one sub-tile per CTA): batch row b is finished by rank b % C.  Push this
-            // CTA's partial of each row into the owner's shared memory; the stores are posted, the
-            // cluster barrier below makes them visible.
-            // Layout of the receive buffer: [source rank][column r][row slot], slots contiguous, so
-            // that four of a thread's values for one owner go out as one 16-byte store.
-            const int nbi = BPAD / C;        // row slots per (source rank, column); a multiple of 4
-            const uint32_t mine = smem_u32(s_red) + (uint32_t)((rank * kTileN + r) * nbi) * 4u;
-            uint32_t owner[4];
-#pragma unroll
-            for (int o = 0; o < 4; ++o) owner[o] = dsmem_addr(mine, (uint32_t)(o & (C - 1)));
-            if (C == 4) {
-#pragma unroll
-              for (int o = 0; o < 4; ++o)
-#pragma unroll
-                for (int b4 = 0; b4 < BPAD / 16; ++b4)   // slots 4*b4 .. 4*b4+3 <-> rows 16*b4 + o + {0,4,8,12}
-                  if (16 * b4 + o < p.batch)
-                    dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * b4), v[16 * b4 + o], v[16 * b4 + o + 4],
-                                    v[16 * b4 + o + 8], v[16 * b4 + o + 12]);
-            } else {
-#pragma unroll
-              for (int o = 0; o < 2; ++o)
-#pragma unroll
-                for (int b8 = 0; b8 < BPAD / 8; ++b8)    // slots 4*b8 .. 4*b8+3 <-> rows 8*b8 + o + {0,2,4,6}
-                  if (8 * b8 + o < p.batch)
-                    dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * b8), v[8 * b8 + o], v[8 * b8 + o + 2],
-                                    v[8 * b8 + o + 4], v[8 * b8 + o + 6]);
-            }
           }
         }
       }
@@ -386,15 +418,18 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     cluster_sync_all();
     if (hdr->k_act > 0 && hdr->abort_flag == 0 && warp >= kEpiWarp0) {
       const int r = tid - 32 * kEpiWarp0;
-      const int col = n0 + r;
-      if (r < width && col < p.n) {
-        const int nbi = BPAD / C;
-        for (int bi = 0; bi * C + rank < p.batch; ++bi) {
-          float sum = 0.f;
+      const int nbi = BPAD / C;
+      for (int h = 0; h * kTileN < width; ++h) {
+        const int rr = h * kTileN + r, col = n0 + rr;
+        if (rr < width && col < p.n) {
+          const float* half_red = s_red + h * BPAD * kTileN;
+          for (int bi = 0; bi * C + rank < p.batch; ++bi) {
+            float sum = 0.f;
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            if (q < C) sum += s_red[(q * kTileN + r) * nbi + bi];
-          p.y[(size_t)(bi * C + rank) * p.ldy + col] = __float2half_rn(sum);
+            for (int q = 0; q < 4; ++q)
+              if (q < C) sum += half_red[(q * kTileN + r) * nbi + bi];
+            p.y[(size_t)(bi * C + rank) * p.ldy + col] = __float2half_rn(sum);
+          }
         }
       }
     }
@@ -528,31 +563,36 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   }
   const int units = p.npad / 8;
   const size_t fixed = umma_fixed_smem(p.nb);
-  if (fixed + 4 * (kTileN * kRowBytes + BPAD * 128) > kSmemBudget) return cudaErrorInvalidValue;
 
-  // cluster size: larger batches split the active blocks of a wider range over 2 or 4 CTAs
-  int want = (p.flags >> 8) & 7;
-  if (want == 0) want = 4;   // measured best at every batch size: fewest copy and MMA issues per byte
-  int cluster = 1, ranges = sm_count < units ? sm_count : units;
-  for (int c = want; c > 1; c >>= 1) {
-    if (c != 2 && c != 4) continue;
+  // Work split.  Fewest copy and MMA issues per byte win (measured): clusters of 4 with passes of up
+  // to 128 columns, else of up to 256 columns (two MMA halves per block), else clusters of 2, else one
+  // CTA per range walking 128-column passes.  Cluster modes finish a range in one pass.
+  const int forced = (p.flags >> 8) & 7;
+  int cluster = 1, tile_cols = kTileN, ranges = sm_count < units ? sm_count : units;
+  const int cand[4][2] = {{4, 128}, {4, 256}, {2, 256}, {2, 128}};
+  for (int ci = 0; ci < 4 && forced != 1; ++ci) {
+    const int c = cand[ci][0], tw = cand[ci][1];
+    if (forced != 0 && c != forced) continue;
+    if (tw > kTileN && BPAD > 32) continue;   // measured: at batch > 32 the two-half epilogue costs more than it saves
     const int resident = max_resident_clusters<BPAD>(c, kSmemBudget, sm_count);
-    int r = resident < units ? resident : units;
+    const int r = resident < units ? resident : units;
     if (r < 1) continue;
-    const int wmax = ((units + r - 1) / r) * 8;
-    if (wmax > kTileN) continue;               // cluster mode handles one sub-tile per CTA
-    if (r * c < (sm_count * 3) / 4) continue;  // too few SMs would be busy
+    if (((units + r - 1) / r) * 8 > tw) continue;   // the widest range must fit one pass
+    if (r * c < (sm_count * 3) / 4) continue;       // too few SMs would be busy
     cluster = c;
+    tile_cols = tw;
     ranges = r;
     break;
   }
   const int wmax = ((units + ranges - 1) / ranges) * 8;
-  const int wsub_max = wmax < kTileN ? wmax : kTileN;
+  const int wsub_max = wmax < tile_cols ? wmax : tile_cols;
   p.cluster = cluster;
   p.ranges = ranges;
+  p.tile_cols = tile_cols;
+  p.issuers = kIssuers;   // two issuers were measured slower (MMA issue becomes the limit)
   p.wslot = (wsub_max * kRowBytes + 1023) / 1024 * 1024;
   const size_t stage_bytes = (size_t)p.wslot + BPAD * 128;
-  const size_t red_bytes = cluster > 1 ? (size_t)BPAD * kTileN * 4 : 0;   // partials pushed by the cluster
+  const size_t red_bytes = cluster > 1 ? (size_t)(tile_cols / kTileN) * BPAD * kTileN * 4 : 0;   // partials pushed by the cluster
   if (fixed + red_bytes + 2 * stage_bytes > kSmemBudget) return cudaErrorInvalidValue;
   const size_t room = kSmemBudget - fixed - red_bytes;
   // One barrier hand-off costs a few hundred cycles per role: a slot gathers enough blocks (about
