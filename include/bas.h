@@ -100,7 +100,9 @@ BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, con
  *             draining, and waits for it only before reading X and writing Y.  Without the flag
  *             only the kernel's own preamble overlaps.  Ignored when count_dev is given.
  *   bits 8-10 cluster size of the tcgen05 kernel: 0 = chosen by batch size, else 1, 2 or 4 CTAs
- *             share the active blocks of one column range (reduced on chip, in rank order). */
+ *             share the active blocks of one column range (reduced on chip, in rank order).
+ *   bits 12-14 copy/MMA warp pairs of the tcgen05 kernel: 0 = chosen by the ring size, else 2, 3
+ *             or 4 (a tuning knob; results differ only in fp32 summation order). */
 #define BAS_GEMM_IDS_STABLE 16
 BAS_API int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
                 const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,

@@ -25,7 +25,8 @@ def _ops():
     return ops
 
 
-def _run_gemm(dev, x, w, ids=None, bitmap=None, family=0, count=None, k_host=None, ids_stable=False, cluster=0):
+def _run_gemm(dev, x, w, ids=None, bitmap=None, family=0, count=None, k_host=None, ids_stable=False, cluster=0,
+              pairs=0):
     ops = _ops()
     tx, tw = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
     packed = ops.pack_weight(tw)
@@ -38,7 +39,7 @@ def _run_gemm(dev, x, w, ids=None, bitmap=None, family=0, count=None, k_host=Non
         if count is not None:
             kw["count"] = torch.tensor([count], dtype=torch.int32, device=dev)
             kw["k_host"] = k_host
-    ops.gemm(tx, packed, out, family=family, ids_stable=ids_stable, cluster=cluster, **kw)
+    ops.gemm(tx, packed, out, family=family, ids_stable=ids_stable, cluster=cluster, pairs=pairs, **kw)
     torch.cuda.synchronize()
     assert ops.read_status(dev) == 0
     return out.cpu().numpy()
@@ -109,6 +110,21 @@ def test_cluster_sizes_agree(dev, b, cluster):
     for n_keep in (1, 3, 62):
         ids = O.random_active_blocks(172, n_keep, seed=b + n_keep)
         y = _run_gemm(dev, x, w, ids=ids, cluster=cluster)
+        assert O.max_err_ratio(y, O.masked_gemm(x, w, ids)) <= TOL
+
+
+@pytest.mark.parametrize("pairs", [2, 3, 4])
+@pytest.mark.parametrize("b,k,n,cluster", [(16, 11008, 4096, 0), (64, 11008, 4096, 0), (5, 4096, 11008, 0),
+                                           (16, 512, 24000, 1), (48, 1024, 20000, 1)])
+def test_pair_counts_agree(dev, b, k, n, cluster, pairs):
+    """2, 3 or 4 copy/MMA warp pairs sharing the ring, in cluster mode and with several sub-tiles
+    per CTA (groups that straddle sub-tile boundaries)."""
+    x = O.make_activations(b, k, seed=b + pairs, dist="laplace")
+    w = O.make_weight(n, k, seed=4)
+    nb = k // 64
+    for n_keep in sorted({1, 2, 5, nb // 3, nb}):
+        ids = O.random_active_blocks(nb, n_keep, seed=b + n_keep)
+        y = _run_gemm(dev, x, w, ids=ids, cluster=cluster, pairs=pairs, ids_stable=bool(n_keep & 1))
         assert O.max_err_ratio(y, O.masked_gemm(x, w, ids)) <= TOL
 
 

@@ -128,7 +128,7 @@ def read_status(device: Optional[torch.device] = None) -> int:
 def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: Optional[torch.Tensor] = None,
          count: Optional[torch.Tensor] = None, k_host: Optional[int] = None,
          bitmap: Optional[torch.Tensor] = None, family: int = 0, ids_stable: bool = False,
-         cluster: int = 0) -> None:
+         cluster: int = 0, pairs: int = 0) -> None:
     """out2d[B, N] = x2d[B, K] restricted to the active blocks, times W^T.
 
     ``ids`` int32 device list (``count``: optional int32[1] device-side length, ``k_host`` an upper
@@ -136,6 +136,7 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
     ``ids_stable``: promise that ``ids`` is not written by the kernel launched just before this
     call on the stream; the kernel then streams weights while that kernel is still finishing.
     ``cluster``: 0 lets the library choose; 1, 2 or 4 forces the tcgen05 kernel's cluster size.
+    ``pairs``: 0 lets the library choose; 2, 3 or 4 forces its number of copy/MMA warp pairs.
     Batches above 64 rows are run in slices of 64."""
     _require_cuda_fp16(x2d, "x")
     _require_cuda_fp16(out2d, "out")
@@ -170,7 +171,7 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
                 count.data_ptr() if count is not None else None, int(k_host),
                 bitmap.data_ptr() if bitmap is not None else None,
                 bsz, k, n, ys.data_ptr(), ys.stride(0), ws.data_ptr(), ws.numel(),
-                int(family) | (IDS_STABLE if ids_stable else 0) | (int(cluster) << 8), stream),
+                int(family) | (IDS_STABLE if ids_stable else 0) | (int(cluster) << 8) | (int(pairs) << 12), stream),
                 "bas_gemm")
 
 

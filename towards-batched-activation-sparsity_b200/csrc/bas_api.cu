@@ -71,8 +71,8 @@ extern "C" {
 #ifdef BAS_TRACE
 BAS_API int bas_debug_trace(long long* out64, int reset) {
   if (g_trace_dev == nullptr) return 1;
-  cudaError_t e = cudaMemcpy(out64, g_trace_dev, sizeof(long long) * 512, cudaMemcpyDeviceToHost);
-  if (e == cudaSuccess && reset) e = cudaMemset(g_trace_dev, 0, sizeof(long long) * 512);
+  cudaError_t e = cudaMemcpy(out64, g_trace_dev, sizeof(long long) * 1024, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && reset) e = cudaMemset(g_trace_dev, 0, sizeof(long long) * 1024);
   return e == cudaSuccess ? 0 : 4;
 }
 #endif
@@ -134,7 +134,7 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   if (!aligned16(x_dev) || !aligned16(packed_dev) || (ldx & 7) != 0 || (k & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
   if (ws_dev == nullptr || ws_bytes < bas_gemm_workspace_bytes(batch, n)) return BAS_ERR_WORKSPACE;
   const int family = flags & 3;
-  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | 0x700)) != 0) return BAS_ERR_INVALID_ARGUMENT;
+  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | 0x700 | 0x7000)) != 0) return BAS_ERR_INVALID_ARGUMENT;
 
   DeviceInfo di;
   int st = device_info(&di);
@@ -167,8 +167,8 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   p.status = (unsigned int*)ws_dev;
 #ifdef BAS_TRACE
   if (g_trace_dev == nullptr) {
-    cudaMalloc(&g_trace_dev, sizeof(long long) * 512);
-    cudaMemset(g_trace_dev, 0, sizeof(long long) * 512);
+    cudaMalloc(&g_trace_dev, sizeof(long long) * 1024);
+    cudaMemset(g_trace_dev, 0, sizeof(long long) * 1024);
   }
   p.trace = g_trace_dev;
 #endif

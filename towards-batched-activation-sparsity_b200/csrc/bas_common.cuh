@@ -216,10 +216,25 @@ __device__ __forceinline__ float dsmem_ld_f32(uint32_t addr) {
 //  * byte map: the non-zero positions in ascending order.
 // Returns the list length.  The caller publishes it to the other warps.
 // ---------------------------------------------------------------------------------------------
+// One batch of up to 256 source entries (ids or byte-map bytes), eight per lane, loaded together so
+// that their latencies overlap.
+__device__ __forceinline__ void warp_load_id_batch(const int32_t* __restrict__ ids, const uint8_t* __restrict__ bitmap,
+                                                   int n_src, int base0, int lane, int (&raw)[8]) {
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int e = base0 + u * 32 + lane;
+    raw[u] = 0;
+    if (e < n_src) raw[u] = (bitmap != nullptr) ? (int)bitmap[e] : __ldg(ids + e);
+  }
+}
+
+// With `have_first`, `first` is the batch at offset 0 already loaded by the caller with
+// warp_load_id_batch and the same n_src: a kernel issues it before its set-up work when the list is
+// known not to depend on the kernel running before it.
 __device__ __forceinline__ int warp_stage_ids(const int32_t* __restrict__ ids, const int32_t* __restrict__ count_dev,
                                               int k_host, const uint8_t* __restrict__ bitmap, int nb,
                                               uint16_t* __restrict__ s_ids, unsigned int* __restrict__ status,
-                                              int lane) {
+                                              int lane, bool have_first, const int (&first)[8]) {
   int n_src = nb;
   if (bitmap == nullptr) {
     n_src = k_host;
@@ -227,15 +242,13 @@ __device__ __forceinline__ int warp_stage_ids(const int32_t* __restrict__ ids, c
   }
   int off = 0;
   bool bad = false;
-  // Loads are issued eight chunks at a time so that their latencies overlap; the compaction that
-  // follows is a ballot per chunk.
   for (int base0 = 0; base0 < n_src; base0 += 256) {
     int raw[8];
+    if (base0 == 0 && have_first) {
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int e = base0 + u * 32 + lane;
-      raw[u] = 0;
-      if (e < n_src) raw[u] = (bitmap != nullptr) ? (int)bitmap[e] : __ldg(ids + e);
+      for (int u = 0; u < 8; ++u) raw[u] = first[u];
+    } else {
+      warp_load_id_batch(ids, bitmap, n_src, base0, lane, raw);
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -262,6 +275,14 @@ __device__ __forceinline__ int warp_stage_ids(const int32_t* __restrict__ ids, c
   if (bad && lane == 0 && blockIdx.x == 0) atomicOr(status, BAS_DEV_BAD_BLOCK_ID);
   __syncwarp();
   return off;
+}
+
+__device__ __forceinline__ int warp_stage_ids(const int32_t* __restrict__ ids, const int32_t* __restrict__ count_dev,
+                                              int k_host, const uint8_t* __restrict__ bitmap, int nb,
+                                              uint16_t* __restrict__ s_ids, unsigned int* __restrict__ status,
+                                              int lane) {
+  const int none[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  return warp_stage_ids(ids, count_dev, k_host, bitmap, nb, s_ids, status, lane, false, none);
 }
 
 // Zero-fill of Y when the active set is empty (the reference's `out.zero_()`).

@@ -300,6 +300,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
     }
   }
 
+  __syncwarp();   // warps with single-lane roles join the barrier whole
   __syncthreads();
   if (hdr->abort_flag != 0 && tid == 0) {
     // Gave up somewhere: do not leave while bulk copies may still be landing in this CTA's memory.

@@ -16,9 +16,10 @@
 // rows past the chunk read whatever the ring holds there and only feed accumulator lanes that are
 // never stored.
 //
-// Roles: warp 0 stages the id list and issues copies, warp 1 issues MMAs (one elected thread each),
-// warps 2..5 drain the accumulators (tcgen05.ld); two accumulator buffers let a drain overlap the
-// next sub-tile's MMAs.  All waits are bounded mbarrier waits; TMEM is released on every path.
+// Roles: warps 0..3 issue copies (warp 0 first stages the id list), warps 4..7 issue MMAs (one
+// elected thread each, one accumulator each), warps 8..11 drain the accumulators (tcgen05.ld), add
+// them and store or, in cluster mode, push them to the owning CTA.  All waits are bounded mbarrier
+// waits; TMEM is released on every path.
 //
 // Replaces, for larger batches, the reference's bitmap/index-list tl.dot kernels and their split-K
 // pairs (kernels/shared_mask_batched_triton_min_runtime.py:814-874, 1150-1216, 1956-1988).
@@ -33,14 +34,25 @@ namespace bas {
 
 namespace {
 
-constexpr int kProducers = 4;           // copy-issuing warps; warp p takes ring groups p, p+4, ...
-constexpr int kIssuers = 4;             // MMA-issuing warps; each owns one accumulator
+// The ring is worked by P = GemmParams::issuers pairs (2..4) of one copy-issuing warp and one
+// MMA-issuing warp: pair w owns ring groups w, w+P, ... and, the slot count being a multiple of P,
+// always the same slots.  A pair is thus an in-order ring of its own, and no mbarrier is ever waited
+// on by a thread that could be more than one phase away from it.
+constexpr int kProducers = 4;           // copy-issuing warps available
+constexpr int kIssuers = 4;             // MMA-issuing warps available; each owns one accumulator
 constexpr int kEpiWarp0 = kProducers + kIssuers;   // first epilogue warp (a multiple of 4: TMEM lane quarters)
 constexpr int kEpiThreads = 128;
 constexpr int kUmmaThreads = 32 * kEpiWarp0 + kEpiThreads;
 constexpr int kHalves = 2;               // a pass covers up to 2 x 128 output columns
 constexpr int kTmemCols = 64 * kIssuers * kHalves;   // one 64-column fp32 accumulator per (issuer, half): all 512
 constexpr int kMmaSpanBytes = 128 * kRowBytes;   // an M=128 operand read spans 16 KiB from the slot base
+
+// XOR applied to the index of a four-slot group within a column of the cluster receive buffer
+// (nbi slots = nbi * 4 bytes per column): makes 16-byte accesses of eight neighbouring columns fall
+// into eight different bank groups.  Group counts that are not powers of two are left alone.
+__device__ __forceinline__ int red_swizzle(int nbi, int r) {
+  return nbi == 32 ? (r & 7) : nbi == 16 ? ((r >> 1) & 3) : nbi == 8 ? ((r >> 2) & 1) : 0;
+}
 
 struct UmmaSmemHeader {
   uint64_t full[kMaxStages];
@@ -56,8 +68,7 @@ struct UmmaSmemHeader {
 
 inline size_t umma_ids_bytes(int nb) { return ((size_t)nb * 2 + 127) / 128 * 128; }
 inline size_t umma_fixed_smem(int nb) {
-  return 1024 /*alignment slack*/ + (sizeof(UmmaSmemHeader) + 127) / 128 * 128 + umma_ids_bytes(nb) + 1024 +
-         kMmaSpanBytes /*tail pad for the MMA's full-height read of the last slot*/;
+  return 1024 /*alignment slack*/ + (sizeof(UmmaSmemHeader) + 127) / 128 * 128 + umma_ids_bytes(nb) + 1024;
 }
 
 template <int BPAD>
@@ -80,10 +91,32 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &hdr->abort_flag;
+#ifdef BAS_TRACE
+  int trace_launch = -1;   // diagnostic builds: wall-clock start and end of CTA 0 of every launch
+  if (blockIdx.x == 0 && tid == 0 && p.trace != nullptr) {
+    trace_launch = (int)atomicAdd((unsigned long long*)&p.trace[30], 1ull);
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    if (trace_launch < 100) p.trace[300 + 2 * trace_launch] = (long long)gt;
+  }
+  if (tid == 0 && p.trace != nullptr && blockIdx.x < 200) {   // every CTA of the latest launch
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    p.trace[600 + 2 * blockIdx.x] = (long long)gt;
+  }
+#endif
+
+  // The id list may be the previous kernel's output unless the caller declared it stable; X and Y
+  // always wait for the previous kernel.  A stable list is requested right away, so that its load
+  // latency runs under the set-up below.
+  const bool early_ids = (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
+  int first_ids[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (warp == 0 && early_ids)
+    warp_load_id_batch(p.ids, p.bitmap, p.bitmap != nullptr ? p.nb : p.k_host, 0, lane, first_ids);
 
   if (tid < S) {
     mbar_init(&hdr->full[tid], 1);
-    mbar_init(&hdr->empty[tid], p.issuers);
+    mbar_init(&hdr->empty[tid], 1);
     fence_barrier_init();
   } else if (tid == 64) {
     mbar_init(&hdr->acc_full, p.issuers);
@@ -99,6 +132,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     tmem_alloc(&hdr->tmem_base, kTmemCols);
     tmem_relinquish();
   }
+  __syncwarp();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -119,17 +153,16 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   const int TW = p.tile_cols;                       // columns per pass: 128 or 256
   const int n_sub = (width + TW - 1) / TW;
 
-  // Nothing so far touched global memory.  The id list may be the previous kernel's output unless
-  // the caller declared it stable; X and Y always wait for the previous kernel.
-  const bool early_ids = (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
   int k_act = 0;
   int armed_next = warp, armed_cnt = 0;   // producer warps: next group to arm, groups armed so far
 
+  const int P = p.issuers;
   if (warp < kProducers) {
     // ------------------------------ id staging (warp 0) + producers ------------------------------
     if (warp == 0) {
       if (!early_ids) pdl_wait();
-      k_act = warp_stage_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids, p.status, lane);
+      k_act = warp_stage_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids, p.status, lane,
+                             early_ids, first_ids);
       if (lane == 0) {
         hdr->k_act = k_act;
         mbar_arrive(&hdr->ids_ready);
@@ -143,8 +176,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     const int k_mine = (k_act > rank) ? (k_act - rank + C - 1) / C : 0;
     const int M = n_sub * k_mine;                // tiles of this CTA: sub-tile major, active block minor
     const int NG = (M + G - 1) / G;              // groups = barrier hand-offs
-    if (M > 0) {
-      // One pass per ring group; producer warp w takes groups w, w+4, ...  Lane l owns tile l of
+    if (M > 0 && warp < P) {
+      // One pass per ring group; producer warp w takes groups w, w+P, ...  Lane l owns tile l of
       // the group: it works out that tile's addresses (the integer divisions run side by side in the
       // lanes), the byte counts are added across the warp, lane 0 waits for the slot and arms its
       // barrier, then every lane issues its own two copies.  Slot index and lap are carried along.
@@ -161,7 +194,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         // Stream the first ring-full of weight chunks while the previous kernel is still draining,
         // then wait for it before loading X.
         const int ahead = min(S, NG);
-        for (int ga = warp; ga < ahead; ga += kProducers) {
+        for (int ga = warp; ga < ahead; ga += P) {
           int sub = 0, j = 0, wbytes = 0;
           const bool have = lane_tile(ga, sub, j, wbytes);
           const int total = __reduce_add_sync(0xffffffffu, have ? wbytes + kXTileBytes : 0);
@@ -170,11 +203,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           if (have)
             bulk_copy_g2s(s_stage + (size_t)ga * stage_bytes + (size_t)lane * tile_bytes,
                           p.packed + ((size_t)j * p.npad + n0 + sub * TW) * kRowBytes, wbytes, &hdr->full[ga]);
-          armed_next = ga + kProducers;
+          armed_next = ga + P;
           ++armed_cnt;
         }
         pdl_wait();
-        for (int ga = warp; ga < ahead; ga += kProducers) {
+        for (int ga = warp; ga < ahead; ga += P) {
           int sub = 0, j = 0, wbytes = 0;
           if (lane_tile(ga, sub, j, wbytes))
             tma_load_2d(s_stage + (size_t)ga * stage_bytes + (size_t)lane * tile_bytes + p.wslot, &xmap, j * kBlockK, 0,
@@ -183,7 +216,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         g = armed_next;
       }
       int s = g % S, lap = g / S;   // slot of group g and how often the slot has been used before
-      for (; g < NG; g += kProducers) {
+      for (; g < NG; g += P) {
         [[maybe_unused]] const long long tr0 = BAS_TRACE_CLOCK();
         int sub = 0, j = 0, wbytes = 0;
         const bool have = lane_tile(g, sub, j, wbytes);
@@ -206,7 +239,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           bulk_copy_g2s(st, p.packed + ((size_t)j * p.npad + n0 + sub * TW) * kRowBytes, wbytes, &hdr->full[s]);
           tma_load_2d(st + p.wslot, &xmap, j * kBlockK, 0, &hdr->full[s]);
         }
-        armed_next = g + kProducers;
+        armed_next = g + P;
         ++armed_cnt;
         if (lane == 0) {
           BAS_TRACE_SET(64 + g, tr1 - hdr->t0);                     // slot free seen by the producer
@@ -215,7 +248,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           BAS_TRACE_ADD(1, BAS_TRACE_CLOCK() - tr1);                // producer: issuing a slot's copies
           BAS_TRACE_ADD(2, 1);
         }
-        s += kProducers;
+        s += P;
         while (s >= S) {
           s -= S;
           ++lap;
@@ -231,70 +264,88 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     if (warp < kEpiWarp0) {
       // ------------------------------ MMA issuers (one thread per warp) ------------------------------
       // Issuing one tcgen05.mma costs its thread on the order of a hundred cycles, far more than the
-      // tensor core needs for a 128 x Bpad x 16 product.  Four warps therefore issue side by side:
-      // issuer w takes the tiles at positions w, w+4, ... of every sub-tile and adds them into an
-      // accumulator of its own; the epilogue adds the four accumulators in issuer order.
+      // tensor core needs for a 128 x Bpad x 16 product.  Up to four warps therefore issue side by
+      // side, each into an accumulator of its own; the epilogue adds them in issuer order.
       const int w = warp - kProducers;
-      const int NI = p.issuers;   // 2 or 4
-      if (lane == 0 && ok && w < NI) {
+      const int NI = P;
+      if (lane == 0 && ok && w < NI && M > 0) {
+        // Ring group g belongs to issuer g % NI alone: it waits for the group, multiplies its tiles
+        // and frees the slot, so a hand-off costs one wait and one commit per group, not one per
+        // issuer.  The assignment is a function of the shape only, hence so is the summation order.
         const uint32_t d = tmem_base + (uint32_t)(w * kHalves * 64);   // this issuer's accumulators, one per half
-        int s = 0, pos = 0, fph = 0;   // slot, position in its group, parity of the slot's current use
-        bool used = false;             // this issuer has read from the current slot
-        int m = 0;
-        for (int sub = 0; sub < n_sub && ok && k_mine > 0; ++sub) {
-          if (sub >= 1) ok = mbar_wait(&hdr->acc_empty, (sub - 1) & 1, abort_flag);
-          if (!ok) break;
-          for (int ii = 0; ii < k_mine; ++ii, ++m) {
-            // Every issuer observes every group landing, also groups it reads nothing from: its
-            // sign-off below must not run ahead of the ring (an arrival for the slot's NEXT use
-            // would be counted in the current phase).
-            [[maybe_unused]] const long long tr0 = BAS_TRACE_CLOCK();
-            if (pos == 0 && !mbar_wait(&hdr->full[s], fph, abort_flag)) {
+        const int NG = (M + G - 1) / G;
+        int cur_sub = 0;       // sub-tile this issuer's accumulator currently holds
+        bool fresh = true;     // nothing multiplied into it yet
+        // Finish with sub-tiles [cur_sub, target): tell the epilogue (the commit waits for this
+        // issuer's MMAs), then wait until it has drained them before the accumulator is reused.
+        auto advance_to = [&](int target) -> bool {
+          while (cur_sub < target) {
+            if (w == 0) BAS_TRACE_SET(16, BAS_TRACE_CLOCK() - hdr->t0);   // issuer 0: last MMA of the sub-tile issued
+            if (!fresh) umma_commit(&hdr->acc_full);
+            else mbar_arrive(&hdr->acc_full);
+            if (cur_sub + 1 < n_sub && !mbar_wait(&hdr->acc_empty, cur_sub & 1, abort_flag)) return false;
+            ++cur_sub;
+            fresh = true;
+          }
+          return true;
+        };
+        int s = w % S, fph = (w / S) & 1;
+        for (int g = w; g < NG && ok; g += NI) {
+          [[maybe_unused]] const long long tr0 = BAS_TRACE_CLOCK();
+          if (!mbar_wait(&hdr->full[s], fph, abort_flag)) {
+            ok = false;
+            break;
+          }
+          if (g == 0) BAS_TRACE_SET(15, BAS_TRACE_CLOCK() - hdr->t0);   // first group landed
+          [[maybe_unused]] const long long tr1 = BAS_TRACE_CLOCK();
+          tc_fence_after_sync();
+          int m = g * G;
+          int sub = (n_sub == 1) ? 0 : m / k_mine;
+          int ii = m - sub * k_mine;
+          for (int pos = 0; pos < G && m < M; ++pos, ++m) {
+            if (sub != cur_sub && !advance_to(sub)) {
               ok = false;
               break;
             }
-            if ((ii & (NI - 1)) == w) {
-              [[maybe_unused]] const long long tr1 = BAS_TRACE_CLOCK();
-              tc_fence_after_sync();
-              const uint32_t st = smem_u32(s_stage + (size_t)s * stage_bytes + (size_t)pos * tile_bytes);
-              const uint64_t bdesc = umma_desc_kmajor_sw128(st + p.wslot);
-              const int halves = (min(TW, width - sub * TW) > kTileN) ? 2 : 1;
-              for (int h = 0; h < halves; ++h) {
-                const uint64_t adesc = umma_desc_kmajor_sw128(st + (uint32_t)(h * kMmaSpanBytes));
+            const uint32_t st = smem_u32(s_stage + (size_t)s * stage_bytes + (size_t)pos * tile_bytes);
+            const uint64_t bdesc = umma_desc_kmajor_sw128(st + p.wslot);
+            const int halves = (min(TW, width - sub * TW) > kTileN) ? 2 : 1;
+            for (int h = 0; h < halves; ++h) {
+              const uint64_t adesc = umma_desc_kmajor_sw128(st + (uint32_t)(h * kMmaSpanBytes));
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                  // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units; an
-                  // issuer's first MMA of a sub-tile overwrites its accumulator instead of adding
-                  umma_f16_ss(d + (uint32_t)(h * 64), adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc,
-                              (ii == w && ks == 0) ? 0u : 1u);
-                }
-              }
-              used = true;
-              if (w == 0) {
-                BAS_TRACE_ADD(4, tr1 - tr0);                    // issuer 0: waiting for data
-                BAS_TRACE_ADD(5, BAS_TRACE_CLOCK() - tr1);      // issuer 0: issuing a tile's MMAs
-                BAS_TRACE_ADD(6, 1);
+              for (int ks = 0; ks < 4; ++ks) {
+                // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units; the
+                // first MMA into a fresh accumulator overwrites it instead of adding
+                umma_f16_ss(d + (uint32_t)(h * 64), adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc,
+                            (fresh && ks == 0) ? 0u : 1u);
               }
             }
-            // every issuer signs off every slot: with a commit if it read from it (the arrival then
-            // waits for those MMAs), plainly otherwise
-            if (pos == G - 1 || m == M - 1) {
-              if (used) umma_commit(&hdr->empty[s]);
-              else mbar_arrive(&hdr->empty[s]);
-              used = false;
-              pos = 0;
-              if (++s == S) {
-                s = 0;
-                fph ^= 1;
-              }
-            } else {
-              ++pos;
+            fresh = false;
+            if (++ii == k_mine) {
+              ii = 0;
+              ++sub;
             }
           }
           if (!ok) break;
-          if (w < k_mine) umma_commit(&hdr->acc_full);   // this issuer's accumulator of the sub-tile is final
-          else mbar_arrive(&hdr->acc_full);              // nothing was dealt to this issuer
+          umma_commit(&hdr->empty[s]);   // the slot is free once these MMAs have read it
+          if (w == 0) {
+            BAS_TRACE_ADD(4, tr1 - tr0);                    // issuer 0: waiting for data
+            BAS_TRACE_ADD(5, BAS_TRACE_CLOCK() - tr1);      // issuer 0: issuing a group's MMAs
+            BAS_TRACE_ADD(6, 1);
+          }
+          s += NI;
+          while (s >= S) {
+            s -= S;
+            fph ^= 1;
+          }
+          // nothing more of the current sub-tile in this issuer's next group: let the epilogue have
+          // it now rather than when that group has landed
+          if (n_sub > 1 && (g + NI) * G < M) {
+            const int sub2 = ((g + NI) * G) / k_mine;
+            if (sub2 > cur_sub) ok = advance_to(sub2);
+          }
         }
+        if (ok) ok = advance_to(n_sub);
         if (!ok) {
           atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
           hdr->abort_flag = 1;
@@ -324,6 +375,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             tc_fence_after_sync();
             if (et == 0) BAS_TRACE_SET(10, BAS_TRACE_CLOCK() - hdr->t0);   // accumulators final
           }
+          // issuer w holds a partial of this sub-tile iff one of the ring groups w, w + issuers, ...
+          // contains one of its tiles
+          const int g_lo = (k_mine > 0) ? (sub * k_mine) / G : 0;
+          const int g_hi = (k_mine > 0) ? ((sub + 1) * k_mine - 1) / G : -1;
           for (int h = 0; h < halves; ++h) {   // columns 128 h + r of the pass
             float v[BPAD];
 #pragma unroll
@@ -331,7 +386,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             if (k_mine > 0) {
 #pragma unroll
               for (int w = 0; w < kIssuers; ++w) {
-                if (w < k_mine && w < p.issuers) {   // issuer order: the sum never depends on timing
+                if (w < P && (w - g_lo % P + P) % P <= g_hi - g_lo) {   // issuer order: the sum never depends on timing
                   uint32_t regs[BPAD / 16][16];
 #pragma unroll
                   for (int cc = 0; cc < BPAD / 16; ++cc)
@@ -345,6 +400,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 }
               }
             }
+            if (et == 0) BAS_TRACE_SET(18, BAS_TRACE_CLOCK() - hdr->t0);   // accumulators read and added
             const int rr = h * kTileN + r;   // column within the pass
             if (C == 1) {
               const int col = n0 + sub * TW + rr;
@@ -359,7 +415,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
               // cluster barrier below makes them visible.
               // Layout of the receive buffer: [half][source rank][column r][row slot], slots contiguous,
               // so that four of a thread's values for one owner go out as one 16-byte store.
+              // Within a column the four-slot groups are XOR-swizzled by the column index, so that
+              // neither these 16-byte stores nor the owner's 16-byte loads pile up on a few banks.
               const int nbi = BPAD / C;        // row slots per (source rank, column); a multiple of 4
+              const int sw = red_swizzle(nbi, r);
               const uint32_t mine =
                   smem_u32(s_red) + (uint32_t)(h * BPAD * kTileN + (rank * kTileN + r) * nbi) * 4u;
               uint32_t owner[4];
@@ -372,10 +431,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                   for (int b4 = 0; b4 < BPAD / 16; ++b4)   // slots 4*b4 .. 4*b4+3 <-> rows 16*b4 + o + {0,4,8,12}
                     if (16 * b4 + o < p.batch) {
                       if (o == rank)   // own rows stay local
-                        *(float4*)(s_red + h * BPAD * kTileN + (rank * kTileN + r) * nbi + 4 * b4) =
+                        *(float4*)(s_red + h * BPAD * kTileN + (rank * kTileN + r) * nbi + 4 * (b4 ^ sw)) =
                             make_float4(v[16 * b4 + o], v[16 * b4 + o + 4], v[16 * b4 + o + 8], v[16 * b4 + o + 12]);
                       else
-                        dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * b4), v[16 * b4 + o], v[16 * b4 + o + 4],
+                        dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * (b4 ^ sw)), v[16 * b4 + o], v[16 * b4 + o + 4],
                                         v[16 * b4 + o + 8], v[16 * b4 + o + 12]);
                     }
               } else {
@@ -385,15 +444,16 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                   for (int b8 = 0; b8 < BPAD / 8; ++b8)    // slots 4*b8 .. 4*b8+3 <-> rows 8*b8 + o + {0,2,4,6}
                     if (8 * b8 + o < p.batch) {
                       if (o == rank)   // own rows stay local
-                        *(float4*)(s_red + h * BPAD * kTileN + (rank * kTileN + r) * nbi + 4 * b8) =
+                        *(float4*)(s_red + h * BPAD * kTileN + (rank * kTileN + r) * nbi + 4 * (b8 ^ sw)) =
                             make_float4(v[8 * b8 + o], v[8 * b8 + o + 2], v[8 * b8 + o + 4], v[8 * b8 + o + 6]);
                       else
-                        dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * b8), v[8 * b8 + o], v[8 * b8 + o + 2],
+                        dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * (b8 ^ sw)), v[8 * b8 + o], v[8 * b8 + o + 2],
                                         v[8 * b8 + o + 4], v[8 * b8 + o + 6]);
                     }
               }
             }
           }
+          if (et == 0) BAS_TRACE_SET(17, BAS_TRACE_CLOCK() - hdr->t0);   // accumulators drained and stored / pushed
           if (k_mine > 0) {
             tc_fence_before_sync();
             __syncwarp();
@@ -408,6 +468,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     }
   }
 
+  // A warp of which single lanes ran a role above must be whole again before it joins a CTA-wide
+  // barrier: an arrival counts for 32 threads however many lanes make it.
+  __syncwarp();
   tc_fence_before_sync();
   __syncthreads();
   if (tid == 0) BAS_TRACE_SET(11, BAS_TRACE_CLOCK() - hdr->t0);    // roles done
@@ -419,33 +482,57 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     if (hdr->k_act > 0 && hdr->abort_flag == 0 && warp >= kEpiWarp0) {
       const int r = tid - 32 * kEpiWarp0;
       const int nbi = BPAD / C;
+      const int sw = red_swizzle(nbi, r);
       for (int h = 0; h * kTileN < width; ++h) {
         const int rr = h * kTileN + r, col = n0 + rr;
         if (rr < width && col < p.n) {
           const float* half_red = s_red + h * BPAD * kTileN;
-          for (int bi = 0; bi * C + rank < p.batch; ++bi) {
-            float sum = 0.f;
+          // slot t of this rank is batch row t * C + rank; four slots per 16-byte load
+          for (int qd = 0; 4 * qd * C + rank < p.batch; ++qd) {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int q = 0; q < 4; ++q)
-              if (q < C) sum += half_red[(q * kTileN + r) * nbi + bi];
-            p.y[(size_t)(bi * C + rank) * p.ldy + col] = __float2half_rn(sum);
+              if (q < C) {
+                const float4 t = *(const float4*)(half_red + (q * kTileN + r) * nbi + 4 * (qd ^ sw));
+                sum.x += t.x;
+                sum.y += t.y;
+                sum.z += t.z;
+                sum.w += t.w;
+              }
+            const int row0 = 4 * qd * C + rank;
+            p.y[(size_t)row0 * p.ldy + col] = __float2half_rn(sum.x);
+            if (row0 + C < p.batch) p.y[(size_t)(row0 + C) * p.ldy + col] = __float2half_rn(sum.y);
+            if (row0 + 2 * C < p.batch) p.y[(size_t)(row0 + 2 * C) * p.ldy + col] = __float2half_rn(sum.z);
+            if (row0 + 3 * C < p.batch) p.y[(size_t)(row0 + 3 * C) * p.ldy + col] = __float2half_rn(sum.w);
           }
         }
       }
     }
   }
-  if (tid == 0) BAS_TRACE_SET(12, BAS_TRACE_CLOCK() - hdr->t0);    // cluster combine done
-  if (hdr->abort_flag != 0 && warp < kProducers && lane == 0) {
+  if (tid == 32 * kEpiWarp0) BAS_TRACE_SET(12, BAS_TRACE_CLOCK() - hdr->t0);    // cluster combine done
+  if (hdr->abort_flag != 0 && warp < P && lane == 0) {
     // Gave up somewhere: do not leave while copies may still be landing in this CTA's memory.
     int zero = 0;
-    const int per_lap = (S + kProducers - 1) / kProducers;   // this warp's groups in one trip round the ring
-    for (int i = 0, g = armed_next - kProducers; i < min(armed_cnt, per_lap) && g >= 0; ++i, g -= kProducers)
+    const int per_lap = S / P;   // this warp's groups in one trip round the ring
+    for (int i = 0, g = armed_next - P; i < min(armed_cnt, per_lap) && g >= 0; ++i, g -= P)
       (void)mbar_wait(&hdr->full[g % S], (g / S) & 1, &zero);
   }
   if (warp == kEpiWarp0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+#ifdef BAS_TRACE
+  if (trace_launch >= 0 && trace_launch < 100) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    p.trace[301 + 2 * trace_launch] = (long long)gt;
+  }
+  if (tid == 0 && p.trace != nullptr && blockIdx.x < 200) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    p.trace[601 + 2 * blockIdx.x] = (long long)gt;
+  }
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -589,27 +676,47 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   p.cluster = cluster;
   p.ranges = ranges;
   p.tile_cols = tile_cols;
-  p.issuers = kIssuers;   // two issuers were measured slower (MMA issue becomes the limit)
   p.wslot = (wsub_max * kRowBytes + 1023) / 1024 * 1024;
   const size_t stage_bytes = (size_t)p.wslot + BPAD * 128;
   const size_t red_bytes = cluster > 1 ? (size_t)(tile_cols / kTileN) * BPAD * kTileN * 4 : 0;   // partials pushed by the cluster
-  if (fixed + red_bytes + 2 * stage_bytes > kSmemBudget) return cudaErrorInvalidValue;
-  const size_t room = kSmemBudget - fixed - red_bytes;
+  // An MMA reads 128 rows (16 KiB) per half from the tile base whatever the tile's width: what the
+  // widest tile does not cover itself is padding behind the ring.
+  const size_t span = (size_t)((wsub_max + kTileN - 1) / kTileN) * kMmaSpanBytes;
+  const size_t pad = span > (size_t)p.wslot ? span - (size_t)p.wslot : 0;
+  if (fixed + red_bytes + pad + 2 * stage_bytes > kSmemBudget) return cudaErrorInvalidValue;
+  const size_t room = kSmemBudget - fixed - red_bytes - pad;
   // One barrier hand-off costs a few hundred cycles per role: a slot gathers enough blocks (about
   // 24 KiB) for the hand-offs to stay off the critical path.
   int group = (int)((24 * 1024 + stage_bytes / 2) / stage_bytes);   // nearest
   if (group < 1) group = 1;
   if (group > 16) group = 16;
-  int stages = (int)(room / (stage_bytes * group));
-  if (stages < 3) {
+  int slots = (int)(room / (stage_bytes * group));
+  if (slots < 4) {
     group = 1;
-    stages = (int)(room / stage_bytes);
+    slots = (int)(room / stage_bytes);
   }
-  if (stages > kMaxStages) stages = kMaxStages;
-  if (stages < 2) return cudaErrorInvalidValue;
-  p.stages = stages;
+  if (slots > kMaxStages) slots = kMaxStages;
+  if (slots < 2) return cudaErrorInvalidValue;
+  // Producer/issuer pairs: as many as possible while the ring (a multiple of the pair count) keeps
+  // at least three quarters of the slots that fit; otherwise whatever keeps the most slots.
+  int pairs = (p.flags >> 12) & 7;
+  if (pairs < 2 || pairs > kIssuers || slots / pairs == 0) {
+    pairs = 0;
+    int best = 2;
+    for (int c = kIssuers; c >= 2; --c) {
+      const int kept = slots / c * c;
+      if (kept * 4 >= slots * 3) {
+        pairs = c;
+        break;
+      }
+      if (kept > slots / best * best) best = c;
+    }
+    if (pairs == 0) pairs = best;
+  }
+  p.issuers = pairs;
+  p.stages = slots / pairs * pairs;
   p.group = group;
-  const size_t smem = fixed + red_bytes + (size_t)stages * group * stage_bytes;
+  const size_t smem = fixed + red_bytes + pad + (size_t)p.stages * group * stage_bytes;
 
   CUtensorMap xmap;
   cudaError_t e = get_x_tensor_map(p, BPAD, &xmap);
