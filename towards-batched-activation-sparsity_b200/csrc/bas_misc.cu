@@ -72,6 +72,12 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   __shared__ int s_warp_cnt[kSelThreads / 32];
   __shared__ int s_keep;
 
+  // Launched with programmatic stream serialization: everything this kernel reads (X) or writes
+  // (ids, count, byte map, workspace) may still be in use by the kernel before it, so the wait comes
+  // first; the kernel after it may be set up meanwhile and waits for this grid's completion itself.
+  pdl_wait();
+  pdl_launch_dependents();
+
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int j0 = blockIdx.x * kSelBlocksPerCta;
   const int nj = min(kSelBlocksPerCta, p.nb - j0);
@@ -204,11 +210,8 @@ cudaError_t launch_select(const SelectParams& p, int sm_count, cudaStream_t stre
     if (e != cudaSuccess) return e;
     if (smem > 96 * 1024) return cudaErrorInvalidValue;
   }
-  // Plain launch on purpose: with programmatic serialization on this kernel as well, a
-  // selection -> contraction -> device-to-host copy chain was observed to deliver stale results.
-  select_kernel<<<grid, kSelThreads, smem, stream>>>(p);
   count_launch();
-  return cudaGetLastError();
+  return launch_with_pdl(select_kernel, grid, kSelThreads, smem, 1, stream, p);
 }
 
 }  // namespace bas
