@@ -1,4 +1,4 @@
-// Swapped-operand tcgen05 kernel for decode batches of 9..64 rows.
+// Swapped-operand tcgen05 kernel for decode batches of 1..64 rows.
 //
 // Work split: the output columns are cut into one contiguous range per CTA (or per cluster); a CTA
 // walks the active blocks and keeps the whole [columns x batch] result of its range in tensor
@@ -17,17 +17,18 @@
 // never stored.
 //
 // Roles: warps 0..3 issue copies (warp 0 first stages the id list), warps 4..7 issue MMAs (one
-// elected thread each, one accumulator each), warps 8..11 drain the accumulators (tcgen05.ld), add
+// elected thread each, one accumulator each), warps 8..15 drain the accumulators (tcgen05.ld), add
 // them and store or, in cluster mode, push them to the owning CTA.  All waits are bounded mbarrier
 // waits; TMEM is released on every path.
 //
-// Replaces, for larger batches, the reference's bitmap/index-list tl.dot kernels and their split-K
+// Replaces the reference's bitmap/index-list tl.dot kernels and their split-K
 // pairs (kernels/shared_mask_batched_triton_min_runtime.py:814-874, 1150-1216, 1956-1988).
 #include "bas_kernels.cuh"
 
 #include <cudaTypedefs.h>
 
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 namespace bas {
@@ -41,10 +42,9 @@ namespace {
 constexpr int kProducers = 4;           // copy-issuing warps available
 constexpr int kIssuers = 4;             // MMA-issuing warps available; each owns one accumulator
 constexpr int kEpiWarp0 = kProducers + kIssuers;   // first epilogue warp (a multiple of 4: TMEM lane quarters)
-constexpr int kEpiThreads = 128;
+constexpr int kEpiThreads = 256;   // two sets of four warps
 constexpr int kUmmaThreads = 32 * kEpiWarp0 + kEpiThreads;
-constexpr int kHalves = 2;               // a pass covers up to 2 x 128 output columns
-constexpr int kTmemCols = 64 * kIssuers * kHalves;   // one 64-column fp32 accumulator per (issuer, half): all 512
+constexpr int kTmemCols = 64 * kIssuers;   // one 64-column fp32 accumulator per issuer
 constexpr int kMmaSpanBytes = 128 * kRowBytes;   // an M=128 operand read spans 16 KiB from the slot base
 
 // XOR applied to the index of a four-slot group within a column of the cluster receive buffer
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   uint16_t* s_ids = (uint16_t*)sp;
   sp += ((size_t)p.nb * 2 + 127) / 128 * 128;
   float* s_red = (float*)sp;   // cluster mode: partials pushed here by the cluster's CTAs, [source rank][row slot][128]
-  if (p.cluster > 1) sp += (size_t)(p.tile_cols / kTileN) * BPAD * kTileN * sizeof(float);
+  if (p.cluster > 1) sp += (size_t)BPAD * kTileN * sizeof(float);
   uint8_t* s_stage = (uint8_t*)(((uintptr_t)sp + 1023) & ~(uintptr_t)1023);  // swizzle atoms need 1 KiB alignment
   const int S = p.stages, G = p.group;
   const int tile_bytes = p.wslot + kXTileBytes;   // multiple of 1024
@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   const uint32_t tmem_base = hdr->tmem_base;
   if (tid == 0) {
     BAS_TRACE_SET(8, BAS_TRACE_CLOCK() - hdr->t0);     // preamble done
-    BAS_TRACE_SET(13, p.cluster * 1000000 + p.tile_cols * 1000 + p.stages * 10 + p.group);
+    BAS_TRACE_SET(13, p.cluster * 1000000 + p.issuers * 1000 + p.stages * 10 + p.group);
     BAS_TRACE_SET(14, p.ranges);
   }
 
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   const int units = p.npad >> 3;
   const int n0 = col_begin(range, units, p.ranges), n1 = col_begin(range + 1, units, p.ranges);
   const int width = n1 - n0;
-  const int TW = p.tile_cols;                       // columns per pass: 128 or 256
+  constexpr int TW = kTileN;                        // columns per pass
   const int n_sub = (width + TW - 1) / TW;
 
   int k_act = 0;
@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         // Ring group g belongs to issuer g % NI alone: it waits for the group, multiplies its tiles
         // and frees the slot, so a hand-off costs one wait and one commit per group, not one per
         // issuer.  The assignment is a function of the shape only, hence so is the summation order.
-        const uint32_t d = tmem_base + (uint32_t)(w * kHalves * 64);   // this issuer's accumulators, one per half
+        const uint32_t d = tmem_base + (uint32_t)(w * 64);   // this issuer's accumulator
         const int NG = (M + G - 1) / G;
         int cur_sub = 0;       // sub-tile this issuer's accumulator currently holds
         bool fresh = true;     // nothing multiplied into it yet
@@ -309,16 +309,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             }
             const uint32_t st = smem_u32(s_stage + (size_t)s * stage_bytes + (size_t)pos * tile_bytes);
             const uint64_t bdesc = umma_desc_kmajor_sw128(st + p.wslot);
-            const int halves = (min(TW, width - sub * TW) > kTileN) ? 2 : 1;
-            for (int h = 0; h < halves; ++h) {
-              const uint64_t adesc = umma_desc_kmajor_sw128(st + (uint32_t)(h * kMmaSpanBytes));
+            const uint64_t adesc = umma_desc_kmajor_sw128(st);
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks) {
-                // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units; the
-                // first MMA into a fresh accumulator overwrites it instead of adding
-                umma_f16_ss(d + (uint32_t)(h * 64), adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc,
-                            (fresh && ks == 0) ? 0u : 1u);
-              }
+            for (int ks = 0; ks < 4; ++ks) {
+              // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units; the
+              // first MMA into a fresh accumulator overwrites it instead of adding
+              umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc, (fresh && ks == 0) ? 0u : 1u);
             }
             fresh = false;
             if (++ii == k_mine) {
@@ -352,10 +348,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         }
       }
     } else {
-      // ------------------------------ epilogue: 4 warps, one TMEM lane quarter each ------------------------------
+      // ---------------- epilogue: two sets of 4 warps, one TMEM lane quarter per warp ----------------
+      // Both sets see the same 128 accumulator rows (output columns); they divide the batch columns
+      // in chunks of 16 (a batch of up to 16 rows is one chunk: the second set then idles).
       const int q = warp & 3;               // a warp may only read TMEM lanes [32*(warp%4), +32)
       const int r = q * 32 + lane;          // row of the sub-tile = output column n0 + 128*sub + r
-      const int et = tid - 32 * kEpiWarp0;  // 0..127
+      const int et = tid - 32 * kEpiWarp0;  // 0..255
+      const int eset = et >> 7;             // 0 or 1
+      constexpr int kChunks = BPAD / 16;
+      constexpr int kChunks0 = (kChunks + 1) / 2;   // set 0's chunks; set 1 takes the rest
       if (early_ids) pdl_wait();            // before the first write to Y
       if (ok && k_act == 0) {
         // empty active set: the epilogue threads of the whole grid zero Y between them
@@ -365,7 +366,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       } else if (ok) {
         for (int sub = 0; sub < n_sub && ok; ++sub) {
           const int wsub = min(TW, width - sub * TW);
-          const int halves = (wsub > kTileN) ? 2 : 1;
           if (k_mine > 0) {
             // warp-uniform verdict: tcgen05.ld below needs the whole warp
             if (!__all_sync(0xffffffffu, mbar_wait(&hdr->acc_full, sub & 1, abort_flag))) {
@@ -375,52 +375,70 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             tc_fence_after_sync();
             if (et == 0) BAS_TRACE_SET(10, BAS_TRACE_CLOCK() - hdr->t0);   // accumulators final
           }
-          // issuer w holds a partial of this sub-tile iff one of the ring groups w, w + issuers, ...
+          // issuer w holds a partial of this sub-tile iff one of the ring groups w, w + P, ...
           // contains one of its tiles
           const int g_lo = (k_mine > 0) ? (sub * k_mine) / G : 0;
           const int g_hi = (k_mine > 0) ? ((sub + 1) * k_mine - 1) / G : -1;
-          for (int h = 0; h < halves; ++h) {   // columns 128 h + r of the pass
-            float v[BPAD];
+
+          // Batch columns [16*CH0, 16*(CH0+NCH)): read the issuers' accumulators (as many
+          // per tcgen05.wait as the registers allow), add them in issuer order, then store the
+          // values (no cluster) or push them to the CTAs that own the rows.
+          auto emit = [&](auto ch0_c, auto nch_c) {
+            constexpr int CH0 = decltype(ch0_c)::value, NCH = decltype(nch_c)::value;
+            constexpr int NV = NCH * 16;
+            constexpr int IB = (BPAD == 16) ? 4 : (NCH == 1) ? 2 : 1;   // issuers read per wait (register budget: 128 per thread)
+            float v[NV];
 #pragma unroll
-            for (int b = 0; b < BPAD; ++b) v[b] = 0.f;
+            for (int b = 0; b < NV; ++b) v[b] = 0.f;
             if (k_mine > 0) {
 #pragma unroll
-              for (int w = 0; w < kIssuers; ++w) {
-                if (w < P && (w - g_lo % P + P) % P <= g_hi - g_lo) {   // issuer order: the sum never depends on timing
-                  uint32_t regs[BPAD / 16][16];
+              for (int w0 = 0; w0 < kIssuers; w0 += IB) {
+                if (w0 < P) {   // warp-uniform
+                  uint32_t regs[IB][NCH][16];
 #pragma unroll
-                  for (int cc = 0; cc < BPAD / 16; ++cc)
-                    tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) +
-                                           (uint32_t)((w * kHalves + h) * 64 + cc * 16), regs[cc]);
+                  for (int wi = 0; wi < IB; ++wi)
+                    if (w0 + wi < P) {
+#pragma unroll
+                      for (int cc = 0; cc < NCH; ++cc)
+                        tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) +
+                                               (uint32_t)((w0 + wi) * 64 + (CH0 + cc) * 16),
+                                           regs[wi][cc]);
+                    }
                   tmem_ld_wait();
 #pragma unroll
-                  for (int cc = 0; cc < BPAD / 16; ++cc)
+                  for (int wi = 0; wi < IB; ++wi) {
+                    const int w = w0 + wi;
+                    if (w < P && (w - g_lo % P + P) % P <= g_hi - g_lo) {   // issuer order: the sum never depends on timing
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) v[cc * 16 + e] += __uint_as_float(regs[cc][e]);
+                      for (int cc = 0; cc < NCH; ++cc)
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) v[cc * 16 + e] += __uint_as_float(regs[wi][cc][e]);
+                    }
+                  }
                 }
               }
             }
             if (et == 0) BAS_TRACE_SET(18, BAS_TRACE_CLOCK() - hdr->t0);   // accumulators read and added
-            const int rr = h * kTileN + r;   // column within the pass
+            const int rr = r;   // column within the pass
             if (C == 1) {
               const int col = n0 + sub * TW + rr;
               if (rr < wsub && col < p.n) {
 #pragma unroll
-                for (int b = 0; b < BPAD; ++b)
-                  if (b < p.batch) p.y[(size_t)b * p.ldy + col] = __float2half_rn(v[b]);
+                for (int b = 0; b < NV; ++b)
+                  if (16 * CH0 + b < p.batch) p.y[(size_t)(16 * CH0 + b) * p.ldy + col] = __float2half_rn(v[b]);
               }
             } else {
               // Cluster mode (one pass per CTA): batch row b is finished by rank b % C.  Push this
               // CTA's partial of each row into the owner's shared memory; the stores are posted, the
               // cluster barrier below makes them visible.
-              // Layout of the receive buffer: [half][source rank][column r][row slot], slots contiguous,
+              // Layout of the receive buffer: [source rank][column r][row slot], slots contiguous,
               // so that four of a thread's values for one owner go out as one 16-byte store.
               // Within a column the four-slot groups are XOR-swizzled by the column index, so that
               // neither these 16-byte stores nor the owner's 16-byte loads pile up on a few banks.
               const int nbi = BPAD / C;        // row slots per (source rank, column); a multiple of 4
               const int sw = red_swizzle(nbi, r);
-              const uint32_t mine =
-                  smem_u32(s_red) + (uint32_t)(h * BPAD * kTileN + (rank * kTileN + r) * nbi) * 4u;
+              float* mine_l = s_red + (rank * kTileN + r) * nbi;
+              const uint32_t mine = smem_u32(mine_l);
               uint32_t owner[4];
 #pragma unroll
               for (int o = 0; o < 4; ++o) owner[o] = dsmem_addr(mine, (uint32_t)(o & (C - 1)));
@@ -428,30 +446,37 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 #pragma unroll
                 for (int o = 0; o < 4; ++o)
 #pragma unroll
-                  for (int b4 = 0; b4 < BPAD / 16; ++b4)   // slots 4*b4 .. 4*b4+3 <-> rows 16*b4 + o + {0,4,8,12}
+                  for (int c4 = 0; c4 < NCH; ++c4) {   // slots 4*b4 .. 4*b4+3 <-> rows 16*b4 + o + {0,4,8,12}
+                    const int b4 = CH0 + c4;
                     if (16 * b4 + o < p.batch) {
-                      if (o == rank)   // own rows stay local
-                        *(float4*)(s_red + h * BPAD * kTileN + (rank * kTileN + r) * nbi + 4 * (b4 ^ sw)) =
-                            make_float4(v[16 * b4 + o], v[16 * b4 + o + 4], v[16 * b4 + o + 8], v[16 * b4 + o + 12]);
-                      else
-                        dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * (b4 ^ sw)), v[16 * b4 + o], v[16 * b4 + o + 4],
-                                        v[16 * b4 + o + 8], v[16 * b4 + o + 12]);
+                      const float4 val = make_float4(v[16 * c4 + o], v[16 * c4 + o + 4], v[16 * c4 + o + 8],
+                                                     v[16 * c4 + o + 12]);
+                      if (o == rank) *(float4*)(mine_l + 4 * (b4 ^ sw)) = val;   // own rows stay local
+                      else dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * (b4 ^ sw)), val.x, val.y, val.z, val.w);
                     }
+                  }
               } else {
 #pragma unroll
                 for (int o = 0; o < 2; ++o)
 #pragma unroll
-                  for (int b8 = 0; b8 < BPAD / 8; ++b8)    // slots 4*b8 .. 4*b8+3 <-> rows 8*b8 + o + {0,2,4,6}
+                  for (int c8 = 0; c8 < 2 * NCH; ++c8) {   // slots 4*b8 .. 4*b8+3 <-> rows 8*b8 + o + {0,2,4,6}
+                    const int b8 = 2 * CH0 + c8;
                     if (8 * b8 + o < p.batch) {
-                      if (o == rank)   // own rows stay local
-                        *(float4*)(s_red + h * BPAD * kTileN + (rank * kTileN + r) * nbi + 4 * (b8 ^ sw)) =
-                            make_float4(v[8 * b8 + o], v[8 * b8 + o + 2], v[8 * b8 + o + 4], v[8 * b8 + o + 6]);
-                      else
-                        dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * (b8 ^ sw)), v[8 * b8 + o], v[8 * b8 + o + 2],
-                                        v[8 * b8 + o + 4], v[8 * b8 + o + 6]);
+                      const float4 val = make_float4(v[8 * c8 + o], v[8 * c8 + o + 2], v[8 * c8 + o + 4],
+                                                     v[8 * c8 + o + 6]);
+                      if (o == rank) *(float4*)(mine_l + 4 * (b8 ^ sw)) = val;   // own rows stay local
+                      else dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * (b8 ^ sw)), val.x, val.y, val.z, val.w);
                     }
+                  }
               }
             }
+          };
+          using std::integral_constant;
+          if constexpr (kChunks == 1) {
+            if (eset == 0) emit(integral_constant<int, 0>{}, integral_constant<int, 1>{});
+          } else {
+            if (eset == 0) emit(integral_constant<int, 0>{}, integral_constant<int, kChunks0>{});
+            else emit(integral_constant<int, kChunks0>{}, integral_constant<int, kChunks - kChunks0>{});
           }
           if (et == 0) BAS_TRACE_SET(17, BAS_TRACE_CLOCK() - hdr->t0);   // accumulators drained and stored / pushed
           if (k_mine > 0) {
@@ -480,15 +505,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     // touches a peer's shared memory after the barrier, so CTAs may leave independently.
     cluster_sync_all();
     if (hdr->k_act > 0 && hdr->abort_flag == 0 && warp >= kEpiWarp0) {
-      const int r = tid - 32 * kEpiWarp0;
+      const int r = (tid - 32 * kEpiWarp0) & 127, eset = (tid - 32 * kEpiWarp0) >> 7;
       const int nbi = BPAD / C;
       const int sw = red_swizzle(nbi, r);
-      for (int h = 0; h * kTileN < width; ++h) {
-        const int rr = h * kTileN + r, col = n0 + rr;
+      {
+        const int rr = r, col = n0 + rr;
         if (rr < width && col < p.n) {
-          const float* half_red = s_red + h * BPAD * kTileN;
+          const float* half_red = s_red;
           // slot t of this rank is batch row t * C + rank; four slots per 16-byte load
-          for (int qd = 0; 4 * qd * C + rank < p.batch; ++qd) {
+          for (int qd = eset; 4 * qd * C + rank < p.batch; qd += 2) {   // the two warp sets alternate
             float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int q = 0; q < 4; ++q)
@@ -651,26 +676,25 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   const int units = p.npad / 8;
   const size_t fixed = umma_fixed_smem(p.nb);
 
-  // Work split.  Fewest copy and MMA issues per byte win (measured): clusters of 4 with passes of up
-  // to 128 columns, else of up to 256 columns (two MMA halves per block), else clusters of 2, else one
-  // CTA per range walking 128-column passes.  Cluster modes finish a range in one pass.
+  // Work split (measured): a cluster of 4 CTAs per column range of up to 128 columns when the
+  // output is narrow enough for that (up to 4224 columns on a 148-SM part), for batches of up to 32
+  // rows else a cluster of 2, else one CTA per range walking 128-column passes.  A cluster finishes
+  // its range in one pass.  Passes of 256 columns were tried and lost to these at every width.
   const int forced = (p.flags >> 8) & 7;
-  int cluster = 1, tile_cols = kTileN, ranges = sm_count < units ? sm_count : units;
-  const int cand[4][2] = {{4, 128}, {4, 256}, {2, 256}, {2, 128}};
-  for (int ci = 0; ci < 4 && forced != 1; ++ci) {
-    const int c = cand[ci][0], tw = cand[ci][1];
+  int cluster = 1, ranges = sm_count < units ? sm_count : units;
+  for (int c = 4; c >= 2 && forced != 1; c -= 2) {
     if (forced != 0 && c != forced) continue;
-    if (tw > kTileN && BPAD > 32) continue;   // measured: at batch > 32 the two-half epilogue costs more than it saves
+    if (forced == 0 && c == 2 && BPAD > 32) continue;
     const int resident = max_resident_clusters<BPAD>(c, kSmemBudget, sm_count);
     const int r = resident < units ? resident : units;
     if (r < 1) continue;
-    if (((units + r - 1) / r) * 8 > tw) continue;   // the widest range must fit one pass
-    if (r * c < (sm_count * 3) / 4) continue;       // too few SMs would be busy
+    if (((units + r - 1) / r) * 8 > kTileN) continue;   // the widest range must fit one pass
+    if (r * c < (sm_count * 3) / 4) continue;           // too few SMs would be busy
     cluster = c;
-    tile_cols = tw;
     ranges = r;
     break;
   }
+  const int tile_cols = kTileN;
   const int wmax = ((units + ranges - 1) / ranges) * 8;
   const int wsub_max = wmax < tile_cols ? wmax : tile_cols;
   p.cluster = cluster;
@@ -678,11 +702,10 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   p.tile_cols = tile_cols;
   p.wslot = (wsub_max * kRowBytes + 1023) / 1024 * 1024;
   const size_t stage_bytes = (size_t)p.wslot + BPAD * 128;
-  const size_t red_bytes = cluster > 1 ? (size_t)(tile_cols / kTileN) * BPAD * kTileN * 4 : 0;   // partials pushed by the cluster
-  // An MMA reads 128 rows (16 KiB) per half from the tile base whatever the tile's width: what the
-  // widest tile does not cover itself is padding behind the ring.
-  const size_t span = (size_t)((wsub_max + kTileN - 1) / kTileN) * kMmaSpanBytes;
-  const size_t pad = span > (size_t)p.wslot ? span - (size_t)p.wslot : 0;
+  const size_t red_bytes = cluster > 1 ? (size_t)BPAD * kTileN * 4 : 0;   // partials pushed by the cluster
+  // An MMA reads 128 rows (16 KiB) from the tile base whatever the tile's width: what the widest
+  // tile does not cover itself is padding behind the ring.
+  const size_t pad = (size_t)kMmaSpanBytes > (size_t)p.wslot ? (size_t)kMmaSpanBytes - (size_t)p.wslot : 0;
   if (fixed + red_bytes + pad + 2 * stage_bytes > kSmemBudget) return cudaErrorInvalidValue;
   const size_t room = kSmemBudget - fixed - red_bytes - pad;
   // One barrier hand-off costs a few hundred cycles per role: a slot gathers enough blocks (about
