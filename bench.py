@@ -219,13 +219,13 @@ def _graph_time_us(torch, stream, build, calls_per_graph: int, reps: int, repeat
     return float(statistics.median(vals))
 
 
-def _layer_stack(torch, dist, dev, world, rank, stream) -> dict:
+def _layer_stack(torch, dist, dev, world, rank, stream, fuse=False) -> dict:
     """The Llama-2-7B decode-step linear stack (32 layers x 7 masked projections, B = 16, sparsity
     0.638), column-/row-parallel over the ranks with an NCCL all-reduce after o and down: one CUDA
     graph per step where NCCL allows capture, timed by CUDA events, max over ranks."""
     from bas import tp
 
-    stack = tp.DecodeLinearStack(32, 16, 0.638, dev, world, rank)
+    stack = tp.DecodeLinearStack(32, 16, 0.638, dev, world, rank, fuse_shared_inputs=fuse)
     with torch.cuda.stream(stream):
         for _ in range(3):
             stack.step()
@@ -431,6 +431,12 @@ def run_gpu(args) -> None:
     # ---- the sharded decode-step linear stack (all ranks take part) ----
     try:
         layer_stack = _layer_stack(torch, dist, dev, world, rank, stream)
+        torch.cuda.empty_cache()
+        # the same step with q/k/v and gate/up stacked into one masked GEMM each (they share their
+        # input and mask in the model; here the q and gate inputs and masks stand for the group)
+        stacked = _layer_stack(torch, dist, dev, world, rank, stream, fuse=True)
+        layer_stack["stacked_qkv_gateup"] = {k: stacked[k] for k in
+                                             ("linears_per_step", "ms_per_step", "active_weight_gbs", "launch")}
     except Exception as exc:
         layer_stack = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     torch.cuda.empty_cache()

@@ -517,3 +517,26 @@ def test_linear_stack_single_rank(dev):
         err = ((out.float() - ref).abs().max() / ref.abs().max()).item()
         assert err <= TOL, (spec.name, err)
         assert int(bitmap.sum().item()) == round((1 - 0.638) * (spec.k // 64))
+
+
+def test_linear_stack_with_stacked_projections(dev):
+    """q/k/v and gate/up as one masked GEMM each over their stacked output columns."""
+    from bas import tp
+
+    stack = tp.DecodeLinearStack(layers=1, batch=16, sparsity=0.638, device=dev, seed=1, fuse_shared_inputs=True)
+    stack.step()
+    torch.cuda.synchronize()
+    assert [lin.spec.name for lin, *_ in stack.items] == ["qkv_proj", "o_proj", "gate_up_proj", "down_proj"]
+    members = {"qkv_proj": (0, 1, 2), "o_proj": (3,), "gate_up_proj": (4, 5), "down_proj": (6,)}
+    gen = torch.Generator(device=dev)
+    for lin, x, bitmap, out in stack.items:
+        ws = []
+        for si in members[lin.spec.name]:
+            spec = tp.LLAMA2_7B_LAYER[si]
+            gen.manual_seed(1 * 1_000_003 + si)
+            ws.append((torch.randn(spec.n, spec.k, generator=gen, device=dev, dtype=torch.float32) * 0.02).half())
+        w = torch.cat(ws)
+        assert out.shape == (16, w.shape[0])
+        ref = (x.float() * bitmap.float().repeat_interleave(64)) @ w.float().t()
+        err = ((out.float() - ref).abs().max() / ref.abs().max()).item()
+        assert err <= TOL, (lin.spec.name, err)

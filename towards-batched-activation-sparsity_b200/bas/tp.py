@@ -65,21 +65,36 @@ LLAMA2_7B_LAYER = (
 )
 
 
+# Projections that read the same activation through the same mask can run as one masked GEMM over
+# their concatenated output columns (the reference's own CLI assumes this for q/k/v,
+# kernels/shared_mask_batched_triton_min_runtime.py:4645): q+k+v and gate+up.
+FUSED_GROUPS = (("qkv_proj", ("q_proj", "k_proj", "v_proj")), ("gate_up_proj", ("gate_proj", "up_proj")))
+
+
 class ShardedLinear:
-    """One rank's shard of a masked linear: packed weight slice plus the views it needs per call."""
+    """One rank's shard of a masked linear: packed weight slice plus the views it needs per call.
+    ``weight_full`` may be a list of [n_i, k] matrices of column-parallel projections sharing one
+    input: the rank's column shard of each is taken and they are stacked into one packed weight."""
 
     def __init__(self, spec: LinearSpec, weight_full, world: int, rank: int):
+        import torch
+
         from . import ops
 
         self.spec, self.world, self.rank = spec, world, rank
+        parts = list(weight_full) if isinstance(weight_full, (list, tuple)) else [weight_full]
         if spec.parallel == "column":
-            self.n0, self.n1 = column_shard(spec.n, world, rank)
+            self.part_bounds = [column_shard(w.shape[0], world, rank) for w in parts]
+            self.n0, self.n1 = self.part_bounds[0] if len(parts) == 1 else (0, sum(b - a for a, b in self.part_bounds))
             self.b0, self.b1 = 0, (spec.k + BLOCK_K - 1) // BLOCK_K
-            shard = weight_full[self.n0:self.n1]
+            shard = torch.cat([w[a:b] for w, (a, b) in zip(parts, self.part_bounds)]) if len(parts) > 1 \
+                else parts[0][self.n0:self.n1]
         else:
+            if len(parts) != 1:
+                raise ValueError("only column-parallel projections can be stacked")
             self.n0, self.n1 = 0, spec.n
             self.b0, self.b1 = row_shard_blocks(spec.k, world, rank)
-            shard = weight_full[:, self.b0 * BLOCK_K: min(self.b1 * BLOCK_K, spec.k)]
+            shard = parts[0][:, self.b0 * BLOCK_K: min(self.b1 * BLOCK_K, spec.k)]
         self.k_local = shard.shape[1]
         self.n_local = shard.shape[0]
         self.packed = ops.pack_weight(shard.contiguous()) if self.n_local and self.k_local else None
@@ -101,10 +116,13 @@ class DecodeLinearStack:
 
     ``step()`` runs every linear once on its replicated synthetic input with its fixed mask and
     all-reduces the row-parallel outputs; it is what the benchmark times as one decode step of the
-    linear stack.  Inputs are generated per linear, identically on every rank."""
+    linear stack.  Inputs are generated per linear, identically on every rank.
+
+    ``fuse_shared_inputs``: q/k/v and gate/up read one activation through one mask (as they do in
+    the model) and run as one masked GEMM each: four launches per layer instead of seven."""
 
     def __init__(self, layers: int, batch: int, sparsity: float, device, world: int = 1, rank: int = 0,
-                 seed: int = 0, group=None):
+                 seed: int = 0, group=None, fuse_shared_inputs: bool = False):
         import torch
 
         from . import ops
@@ -112,28 +130,46 @@ class DecodeLinearStack:
 
         self.world, self.rank, self.group, self.batch = world, rank, group, batch
         self.items = []
+        self._shared = {}
         gen = torch.Generator(device=device)
         self.active_bytes = 0
+        fused_of = {m: name for name, members in FUSED_GROUPS for m in members} if fuse_shared_inputs else {}
+
+        def shared_input(spec):
+            if spec.name not in self._shared:     # inputs and masks are per projection type, shared by the layers
+                if spec.dist == "normal":
+                    x = torch.randn(batch, spec.k, generator=gen, device=device, dtype=torch.float32).half()
+                else:
+                    u = torch.rand(batch, spec.k, generator=gen, device=device, dtype=torch.float32) - 0.5
+                    x = (-torch.sign(u) * torch.log1p(-2.0 * u.abs())).half()
+                nb = spec.k // BLOCK_K
+                n_keep = ops.n_keep_from_density(1.0 - sparsity, nb)
+                bitmap = torch.empty(nb, dtype=torch.uint8, device=device)
+                ops.select_topk(x, n_keep, SCORE_NORM, bitmap_out=bitmap)
+                self._shared[spec.name] = (x, bitmap, n_keep)
+            return self._shared[spec.name]
+
         for li in range(layers):
+            pending = {}     # fused group name -> [spec, weights]
             for si, spec in enumerate(LLAMA2_7B_LAYER):
                 gen.manual_seed(seed * 1_000_003 + li * 16 + si)
                 w = (torch.randn(spec.n, spec.k, generator=gen, device=device, dtype=torch.float32) * 0.02).half()
-                lin = ShardedLinear(spec, w, world, rank)
+                group_name = fused_of.get(spec.name)
+                if group_name is not None:
+                    members = dict(FUSED_GROUPS)[group_name]
+                    entry = pending.setdefault(group_name, [spec, []])
+                    entry[1].append(w)
+                    if len(entry[1]) < len(members):
+                        continue
+                    first, ws = entry
+                    spec = LinearSpec(group_name, sum(t.shape[0] for t in ws), first.k, "column", first.dist)
+                    x, bitmap, n_keep = shared_input(first)
+                    lin = ShardedLinear(spec, ws, world, rank)
+                    del ws, entry[1][:]
+                else:
+                    x, bitmap, n_keep = shared_input(spec)
+                    lin = ShardedLinear(spec, w, world, rank)
                 del w
-                if li == 0:     # inputs and masks are per projection type, shared by the layers
-                    if spec.dist == "normal":
-                        x = torch.randn(batch, spec.k, generator=gen, device=device, dtype=torch.float32).half()
-                    else:
-                        u = torch.rand(batch, spec.k, generator=gen, device=device, dtype=torch.float32) - 0.5
-                        x = (-torch.sign(u) * torch.log1p(-2.0 * u.abs())).half()
-                    nb = spec.k // BLOCK_K
-                    n_keep = ops.n_keep_from_density(1.0 - sparsity, nb)
-                    bitmap = torch.empty(nb, dtype=torch.uint8, device=device)
-                    ops.select_topk(x, n_keep, SCORE_NORM, bitmap_out=bitmap)
-                    shared = (x, bitmap, n_keep)
-                    self._shared = getattr(self, "_shared", {})
-                    self._shared[spec.name] = shared
-                x, bitmap, n_keep = self._shared[spec.name]
                 out = torch.zeros(batch, lin.n_local, dtype=torch.float16, device=device)
                 self.items.append((lin, x, bitmap, out))
                 self.active_bytes += n_keep * BLOCK_K * spec.n * 2
