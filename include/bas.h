@@ -50,7 +50,8 @@ typedef enum bas_status {
 
 typedef enum bas_score_kind {
   BAS_SCORE_NORM = 0,  /* mean_b ||x_b,block||_2 : scripts/bench_roundrobin_e2e_decode.py:103-105 */
-  BAS_SCORE_ENERGY = 1 /* mean_b ||x_b,block||^2 : scripts/bench_alpaca_energy_budget_e2e.py:43-46 */
+  BAS_SCORE_ENERGY = 1, /* mean_b ||x_b,block||^2 : scripts/bench_alpaca_energy_budget_e2e.py:43-46 */
+  BAS_SCORE_BF16 = 256  /* OR into score_kind: x holds bfloat16 instead of fp16 */
 } bas_score_kind;
 
 BAS_API const char* bas_status_string(int status);
@@ -101,9 +102,12 @@ BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, con
  *             only the kernel's own preamble overlaps.  Ignored when count_dev is given.
  *   bits 8-10 cluster size of the tcgen05 kernel: 0 = chosen by batch size, else 1, 2 or 4 CTAs
  *             share the active blocks of one column range (reduced on chip, in rank order).
+ *   BAS_GEMM_BF16  X, the packed weight and Y hold bfloat16 instead of fp16 (the reference's kernels
+ *             take either, kernels/...min_runtime.py:21); tcgen05 kernel only.
  *   bits 12-14 copy/MMA warp pairs of the tcgen05 kernel: 0 = chosen by the ring size, else 2, 3
  *             or 4 (a tuning knob; results differ only in fp32 summation order). */
 #define BAS_GEMM_IDS_STABLE 16
+#define BAS_GEMM_BF16 32
 BAS_API int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
                 const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
                 void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream);
@@ -120,7 +124,7 @@ BAS_API int bas_build_bitmap(const int32_t* ids_dev, const int32_t* count_dev, i
  * Replaces _select_active_blocks (scripts/bench_roundrobin_e2e_decode.py:90-113) and
  * _block_energy + _topk_active / _energy_budget_active
  * (scripts/bench_alpaca_energy_budget_e2e.py:43-62): one launch, no host synchronisation.
- * Scores are accumulated in fp64 from the exact fp16 inputs; equal scores go to the lower id.
+ * Scores are accumulated in fp64 from the exact fp16 (or, with BAS_SCORE_BF16, bfloat16) inputs; equal scores go to the lower id.
  *
  *   ids_out_dev     int32 [>= n_keep] (top-k) or [>= K/64] (budget): ascending active ids
  *   count_out_dev   int32 [1]: number of ids written
@@ -138,6 +142,10 @@ BAS_API int bas_select_topk(const void* x_dev, int64_t ldx, int batch, int k, in
 BAS_API int bas_select_budget(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
                       int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
                       double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream);
+/* The same with score_flags = 0 or BAS_SCORE_BF16. */
+BAS_API int bas_select_budget_ex(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
+                         int score_flags, int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
+                         double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream);
 
 /* ---- selection for callers that must not allocate -------------------------------------------
  * No counterpart in the reference.  Same result as bas_select_topk, but the caller passes no

@@ -246,6 +246,14 @@ def select_active_blocks_torch_cpu(x3, density: float, kind: int = SCORE_NORM,
     return torch.topk(score, k=n_keep).indices.sort()[0].to(torch.int32)
 
 
+def round_to_bf16(a: np.ndarray) -> np.ndarray:
+    """fp32 array whose every value is exactly representable in bfloat16 (round to nearest even on
+    the upper 16 bits): the oracle's stand-in for a bf16 tensor, numpy having no such dtype."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32).reshape(np.shape(a))
+
+
 def max_err_ratio(y: np.ndarray, ref: np.ndarray) -> float:
     """max|y - ref| / max|ref|, the quantity the parity rule bounds by 2e-3."""
     ref = np.asarray(ref, dtype=np.float64)

@@ -540,3 +540,69 @@ def test_linear_stack_with_stacked_projections(dev):
         ref = (x.float() * bitmap.float().repeat_interleave(64)) @ w.float().t()
         err = ((out.float() - ref).abs().max() / ref.abs().max()).item()
         assert err <= TOL, (lin.spec.name, err)
+
+
+# ---------------------------------------------------------------------------------------------
+# bfloat16 (the reference's kernels take fp16 or bf16 tensors alike)
+# ---------------------------------------------------------------------------------------------
+# bf16 keeps 8 significant bits: one unit in the last place of the largest output is
+# 2^-8 * max|ref|, and the fp32-accumulated result may round to the neighbour of the fp64 oracle's.
+TOL_BF16 = 2.0 ** -7
+
+
+def _bf16_inputs(b, k, n, seed, dist="normal"):
+    x = O.round_to_bf16(O.make_activations(b, k, seed=seed, dist=dist).astype(np.float32))
+    w = O.round_to_bf16(O.make_weight(n, k, seed=seed + 1).astype(np.float32))
+    return x, w
+
+
+@pytest.mark.parametrize("b,k,n,n_keep", [(2, 4096, 1024, 20), (16, 11008, 4096, 62), (64, 11008, 4096, 83),
+                                          (5, 512, 24000, 5), (33, 1088, 4104, 9)])
+def test_bf16_gemm_matches_oracle(dev, b, k, n, n_keep):
+    ops = _ops()
+    x, w = _bf16_inputs(b, k, n, seed=b)
+    ids = O.random_active_blocks((k + 63) // 64, n_keep, seed=b)
+    tx = torch.from_numpy(x).to(dev).to(torch.bfloat16)
+    tw = torch.from_numpy(w).to(dev).to(torch.bfloat16)
+    assert torch.equal(tx.float().cpu(), torch.from_numpy(x))      # the conversion lost nothing
+    packed = ops.pack_weight(tw)
+    out = torch.full((b, n), float("nan"), dtype=torch.bfloat16, device=dev)
+    for kw in ({"ids": torch.from_numpy(ids).to(dev)},
+               {"bitmap": torch.from_numpy(O.build_bitmap(ids, (k + 63) // 64)).to(dev), "ids_stable": True}):
+        out.fill_(float("nan"))
+        ops.gemm(tx, packed, out, **kw)
+        torch.cuda.synchronize()
+        assert ops.read_status(dev) == 0
+        assert O.max_err_ratio(out.float().cpu().numpy(), O.masked_gemm(x, w, ids)) <= TOL_BF16
+
+
+def test_bf16_and_fp16_must_not_be_mixed(dev):
+    ops = _ops()
+    x = torch.zeros(2, 128, dtype=torch.bfloat16, device=dev)
+    w = torch.zeros(64, 128, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros(2, 64, dtype=torch.float16, device=dev)
+    with pytest.raises(TypeError):
+        ops.gemm(x, ops.pack_weight(w), out, ids=torch.zeros(1, dtype=torch.int32, device=dev))
+    with pytest.raises(Exception):      # the CUDA-core kernel is fp16 only
+        ops.gemm(x, ops.pack_weight(w), out.to(torch.bfloat16), ids=torch.zeros(1, dtype=torch.int32, device=dev),
+                 family=1)
+
+
+@pytest.mark.parametrize("b,k,kind", [(16, 11008, 1), (3, 4096, 0), (64, 4160, 1)])
+def test_bf16_selection_is_bit_exact(dev, b, k, kind):
+    ops = _ops()
+    x = O.round_to_bf16(O.make_activations(b, k, seed=77 + b, dist="laplace").astype(np.float32))
+    tx = torch.from_numpy(x).to(dev).to(torch.bfloat16)
+    nb = k // 64
+    scores = O.block_scores(x, kind)
+    n_keep = O.n_keep_from_density(0.36, nb)
+    got_scores = torch.empty(nb, dtype=torch.float64, device=dev)
+    ids, count = ops.select_topk(tx, n_keep, kind, scores_out=got_scores)
+    assert int(count.item()) == n_keep
+    assert np.array_equal(ids.cpu().numpy(), O.topk_ids(scores, n_keep))
+    assert np.array_equal(got_scores.cpu().numpy(), scores)
+    if kind == 1:
+        ids_b, count_b = ops.select_budget(tx, 0.8, 2)
+        want = O.energy_budget_ids(scores, 0.8, 2)
+        assert int(count_b.item()) == want.size
+        assert np.array_equal(ids_b[: want.size].cpu().numpy(), want)

@@ -132,3 +132,15 @@ def test_torch_cpu_legs_agree_with_oracle():
     assert np.array_equal(ids, t_ids.numpy())
     y = O.masked_linear_torch_cpu(torch.from_numpy(x), torch.from_numpy(w), ids).numpy()
     assert O.max_err_ratio(y, O.masked_gemm(x, w, ids)) <= 2e-3
+
+
+def test_bf16_rounding_matches_torch():
+    """The oracle's bf16 stand-in (fp32 values rounded to nearest even on 16 bits) against torch's
+    own float32 -> bfloat16 conversion."""
+    import torch
+
+    rng = np.random.default_rng(3)
+    a = np.concatenate([rng.standard_normal(5000).astype(np.float32) * 10.0 ** rng.integers(-6, 6, 5000),
+                        np.array([0.0, -0.0, 1.0, 1.00390625, 1.005859375, 3.0e38, 1e-40], np.float32)])
+    want = torch.from_numpy(a).to(torch.bfloat16).to(torch.float32).numpy()
+    assert np.array_equal(O.round_to_bf16(a), want)

@@ -11,6 +11,8 @@ MAX_BATCH = 64
 SCORE_NORM = 0
 SCORE_ENERGY = 1
 IDS_STABLE = 16          # BAS_GEMM_IDS_STABLE
+GEMM_BF16 = 32           # BAS_GEMM_BF16
+SCORE_BF16 = 256         # BAS_SCORE_BF16
 
 _PKG = Path(__file__).resolve().parent.parent
 lib_path = _PKG / "libbas.so"
@@ -52,6 +54,7 @@ _SIGNATURES = {
     "bas_select_workspace_bytes": (_sz, [_i]),
     "bas_select_topk": (_i, [_vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bas_select_budget": (_i, [_vp, _i64, _i, _i, C.c_double, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "bas_select_budget_ex": (_i, [_vp, _i64, _i, _i, C.c_double, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bas_select_topk_noalloc": (_i, [_vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "bas_linear_create": (_i, [C.POINTER(_vp), _vp, _i, _i, _i]),
     "bas_linear_forward_host": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),

@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 from . import abi as _abi
-from .abi import BLOCK_K, IDS_STABLE, MAX_BATCH, SCORE_ENERGY, SCORE_NORM, check, lib
+from .abi import BLOCK_K, GEMM_BF16, IDS_STABLE, MAX_BATCH, SCORE_BF16, SCORE_ENERGY, SCORE_NORM, check, lib
 
 _PACKED: dict[tuple, torch.Tensor] = {}
 _PACK_STATS = {"hits": 0, "misses": 0}
@@ -29,10 +29,12 @@ def _stream_ptr() -> int:
 
 
 def _require_cuda_fp16(t: torch.Tensor, name: str) -> None:
+    """CUDA tensor of one of the two 16-bit float types the kernels take (the reference's kernels
+    accept both, kernels/shared_mask_batched_triton_min_runtime.py:21)."""
     if not t.is_cuda:
         raise ValueError(f"{name} must be a CUDA tensor (libbas has no CPU path)")
-    if t.dtype != torch.float16:
-        raise TypeError(f"{name} must be float16, got {t.dtype}")
+    if t.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"{name} must be float16 or bfloat16, got {t.dtype}")
 
 
 def n_keep_from_density(density: float, nb: int, min_keep: int = 1) -> int:
@@ -137,9 +139,13 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
     call on the stream; the kernel then streams weights while that kernel is still finishing.
     ``cluster``: 0 lets the library choose; 1, 2 or 4 forces the tcgen05 kernel's cluster size.
     ``pairs``: 0 lets the library choose; 2, 3 or 4 forces its number of copy/MMA warp pairs.
+    x, out (and the weight that was packed) are all float16 or all bfloat16.
     Batches above 64 rows are run in slices of 64."""
     _require_cuda_fp16(x2d, "x")
     _require_cuda_fp16(out2d, "out")
+    if x2d.dtype != out2d.dtype:
+        raise TypeError("x and out must have the same dtype (the packed weight must hold that type too)")
+    bf16 = GEMM_BF16 if x2d.dtype == torch.bfloat16 else 0
     if x2d.dim() != 2 or out2d.dim() != 2 or x2d.stride(1) != 1 or out2d.stride(1) != 1:
         raise ValueError("x and out must be 2-D with unit inner stride")
     bt, k = x2d.shape
@@ -171,7 +177,7 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
                 count.data_ptr() if count is not None else None, int(k_host),
                 bitmap.data_ptr() if bitmap is not None else None,
                 bsz, k, n, ys.data_ptr(), ys.stride(0), ws.data_ptr(), ws.numel(),
-                int(family) | (IDS_STABLE if ids_stable else 0) | (int(cluster) << 8) | (int(pairs) << 12), stream),
+                int(family) | (IDS_STABLE if ids_stable else 0) | bf16 | (int(cluster) << 8) | (int(pairs) << 12), stream),
                 "bas_gemm")
 
 
@@ -237,12 +243,13 @@ def _select(x2d, mode, n_keep, score_kind, energy_keep, ids_out, count_out, bitm
                 bitmap_out.data_ptr() if bitmap_out is not None else None,
                 scores_out.data_ptr() if scores_out is not None else None,
                 ws.data_ptr(), ws.numel(), _stream_ptr())
+        bf16 = SCORE_BF16 if x2d.dtype == torch.bfloat16 else 0
         if mode == 0:
-            check(lib.bas_select_topk(x2d.data_ptr(), x2d.stride(0), bt, k, n_keep, int(score_kind), *args),
+            check(lib.bas_select_topk(x2d.data_ptr(), x2d.stride(0), bt, k, n_keep, int(score_kind) | bf16, *args),
                   "bas_select_topk")
             return ids_out[:n_keep], count_out
-        check(lib.bas_select_budget(x2d.data_ptr(), x2d.stride(0), bt, k, energy_keep, n_keep, *args),
-              "bas_select_budget")
+        check(lib.bas_select_budget_ex(x2d.data_ptr(), x2d.stride(0), bt, k, energy_keep, n_keep, bf16, *args),
+              "bas_select_budget_ex")
         return ids_out, count_out
 
 

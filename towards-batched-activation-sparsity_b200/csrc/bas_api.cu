@@ -134,7 +134,7 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   if (!aligned16(x_dev) || !aligned16(packed_dev) || (ldx & 7) != 0 || (k & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
   if (ws_dev == nullptr || ws_bytes < bas_gemm_workspace_bytes(batch, n)) return BAS_ERR_WORKSPACE;
   const int family = flags & 3;
-  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | 0x700 | 0x7000)) != 0) return BAS_ERR_INVALID_ARGUMENT;
+  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_BF16 | 0x700 | 0x7000)) != 0) return BAS_ERR_INVALID_ARGUMENT;
 
   DeviceInfo di;
   int st = device_info(&di);
@@ -177,7 +177,7 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   // Measured on B200, the tcgen05 kernel is the faster one at every batch size (it issues a quarter
   // of the copies per byte), so it is the default; the CUDA-core kernel runs on request.
   const bool small = (family == 1);
-  if (small && batch > 8) return BAS_ERR_UNSUPPORTED;
+  if (small && (batch > 8 || (flags & BAS_GEMM_BF16) != 0)) return BAS_ERR_UNSUPPORTED;   // the CUDA-core kernel is fp16 only
   cudaError_t e = small ? launch_gemv(p, grid_cap, s) : launch_umma(p, grid_cap, s);
   return e == cudaSuccess ? BAS_OK : cuda_fail(e);
 }
@@ -221,6 +221,8 @@ static int select_common(const void* x_dev, int64_t ldx, int batch, int k, int m
   if (batch <= 0 || k < kBlockK || ldx < k || !aligned16(x_dev) || (ldx & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
   const int nb = k / kBlockK;  // trailing K mod 64 channels are never scored (d_eff)
   if (nb > BAS_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
+  const int bf16 = (score_kind & BAS_SCORE_BF16) != 0 ? 1 : 0;
+  score_kind &= ~BAS_SCORE_BF16;
   if (score_kind != BAS_SCORE_NORM && score_kind != BAS_SCORE_ENERGY) return BAS_ERR_INVALID_ARGUMENT;
   if (n_keep < 0 || n_keep > nb) return BAS_ERR_INVALID_ARGUMENT;
   if (ws_dev == nullptr || ws_bytes < bas_select_workspace_bytes(k)) return BAS_ERR_WORKSPACE;
@@ -236,6 +238,7 @@ static int select_common(const void* x_dev, int64_t ldx, int batch, int k, int m
   p.mode = mode;
   p.n_keep = n_keep;
   p.score_kind = score_kind;
+  p.bf16 = bf16;
   p.energy_keep = energy_keep;
   p.ids_out = ids_out_dev;
   p.count_out = count_out_dev;
@@ -259,6 +262,14 @@ int bas_select_budget(const void* x_dev, int64_t ldx, int batch, int k, double e
                       void* ws_dev, size_t ws_bytes, void* stream) {
   return select_common(x_dev, ldx, batch, k, 1, min_keep, BAS_SCORE_ENERGY, energy_keep, ids_out_dev, count_out_dev,
                        bitmap_out_dev, scores_out_dev, ws_dev, ws_bytes, stream);
+}
+
+int bas_select_budget_ex(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
+                         int score_flags, int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
+                         double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream) {
+  if ((score_flags & ~BAS_SCORE_BF16) != 0) return BAS_ERR_INVALID_ARGUMENT;
+  return select_common(x_dev, ldx, batch, k, 1, min_keep, BAS_SCORE_ENERGY | score_flags, energy_keep, ids_out_dev,
+                       count_out_dev, bitmap_out_dev, scores_out_dev, ws_dev, ws_bytes, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -283,6 +284,13 @@ __device__ __forceinline__ int warp_stage_ids(const int32_t* __restrict__ ids, c
                                               int lane) {
   const int none[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   return warp_stage_ids(ids, count_dev, k_host, bitmap, nb, s_ids, status, lane, false, none);
+}
+
+// fp32 -> the output's 16-bit type (round to nearest even), stored through the fp16-typed pointer
+// that stands for either container.
+__device__ __forceinline__ void store_out16(__half* dst, float v, bool bf16) {
+  const unsigned short bits = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+  *reinterpret_cast<unsigned short*>(dst) = bits;
 }
 
 // Zero-fill of Y when the active set is empty (the reference's `out.zero_()`).

@@ -32,6 +32,7 @@ struct GemmParams {
 };
 
 constexpr int kFlagStableIds = 16;   // BAS_GEMM_IDS_STABLE: the id list is not written by the previous kernel
+constexpr int kFlagBf16 = 32;        // BAS_GEMM_BF16: X, W and Y are bfloat16 (same 16-bit containers)
 
 // Launch with the programmatic-serialization attribute, so that this kernel's preamble (and, when
 // the ids are stable, its weight copies) may overlap the tail of the previous kernel in the stream.
@@ -79,6 +80,7 @@ struct SelectParams {
   int mode;           // 0 = top-k, 1 = energy budget
   int n_keep;         // top-k: blocks to keep; budget: min_keep
   int score_kind;     // BAS_SCORE_NORM / BAS_SCORE_ENERGY
+  int bf16;           // x holds bfloat16 instead of fp16
   double energy_keep; // budget mode
   int32_t* ids_out;
   int32_t* count_out;

@@ -91,12 +91,22 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     if (pr < pairs) {
       const int jj = pr / p.batch, b = pr - jj * p.batch;
       const uint4 v = __ldg((const uint4*)(p.x + (size_t)b * p.ldx + (size_t)(j0 + jj) * kBlockK) + sub);
-      const __half2* h = (const __half2*)&v;
+      if (p.bf16) {
+        const unsigned int* wds = (const unsigned int*)&v;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float2 f = __half22float2(h[q]);
-        e += (double)(f.x * f.x);   // a product of two fp16 values is exact in fp32
-        e += (double)(f.y * f.y);
+        for (int q = 0; q < 4; ++q) {   // a bf16 is the upper half of an fp32; squares are taken in fp64 (range)
+          const double lo = (double)__uint_as_float(wds[q] << 16), hi = (double)__uint_as_float(wds[q] & 0xffff0000u);
+          e += lo * lo;
+          e += hi * hi;
+        }
+      } else {
+        const __half2* h = (const __half2*)&v;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = __half22float2(h[q]);
+          e += (double)(f.x * f.x);   // a product of two fp16 values is exact in fp32
+          e += (double)(f.y * f.y);
+        }
       }
     }
     e += __shfl_xor_sync(0xffffffffu, e, 1);
@@ -237,6 +247,8 @@ extern "C" BAS_API int bas_select_topk_noalloc(const void* x_dev, int64_t ldx, i
     return BAS_ERR_INVALID_ARGUMENT;
   const int nb = k / kBlockK;
   if (nb > BAS_NOALLOC_MAX_BLOCKS) return BAS_ERR_TOO_LARGE;   // the fixed scratch holds no more scores
+  const int bf16 = (score_kind & BAS_SCORE_BF16) != 0 ? 1 : 0;
+  score_kind &= ~BAS_SCORE_BF16;
   if (score_kind != BAS_SCORE_NORM && score_kind != BAS_SCORE_ENERGY) return BAS_ERR_INVALID_ARGUMENT;
   if (n_keep < 0 || n_keep > nb) return BAS_ERR_INVALID_ARGUMENT;
 
@@ -263,6 +275,7 @@ extern "C" BAS_API int bas_select_topk_noalloc(const void* x_dev, int64_t ldx, i
   p.mode = 0;
   p.n_keep = n_keep;
   p.score_kind = score_kind;
+  p.bf16 = bf16;
   p.energy_keep = 0.0;
   p.ids_out = ids_out_dev;
   p.count_out = count_out_dev;

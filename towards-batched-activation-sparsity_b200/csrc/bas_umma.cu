@@ -74,7 +74,9 @@ inline size_t umma_fixed_smem(int nb) {
 template <int BPAD>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
     umma_colsplit_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
-  constexpr uint32_t kIdesc = umma_idesc_f16(128, BPAD);
+  const bool bf16 = (p.flags & kFlagBf16) != 0;
+  // operand formats: bits 7-9 (A) and 10-12 (B) of the instruction descriptor, 0 = fp16, 1 = bf16
+  const uint32_t kIdesc = umma_idesc_f16(128, BPAD) | (bf16 ? ((1u << 7) | (1u << 10)) : 0u);
   constexpr int kXTileBytes = BPAD * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sp = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
@@ -362,7 +364,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         // empty active set: the epilogue threads of the whole grid zero Y between them
         const long long total = (long long)p.batch * p.n;
         for (long long e = (long long)blockIdx.x * kEpiThreads + et; e < total; e += (long long)gridDim.x * kEpiThreads)
-          p.y[(e / p.n) * p.ldy + (e % p.n)] = __float2half_rn(0.f);
+          p.y[(e / p.n) * p.ldy + (e % p.n)] = __float2half_rn(0.f);   // +0 in either format
       } else if (ok) {
         for (int sub = 0; sub < n_sub && ok; ++sub) {
           const int wsub = min(TW, width - sub * TW);
@@ -425,7 +427,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
               if (rr < wsub && col < p.n) {
 #pragma unroll
                 for (int b = 0; b < NV; ++b)
-                  if (16 * CH0 + b < p.batch) p.y[(size_t)(16 * CH0 + b) * p.ldy + col] = __float2half_rn(v[b]);
+                  if (16 * CH0 + b < p.batch) store_out16(p.y + (size_t)(16 * CH0 + b) * p.ldy + col, v[b], bf16);
               }
             } else {
               // Cluster mode (one pass per CTA): batch row b is finished by rank b % C.  Push this
@@ -525,10 +527,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 sum.w += t.w;
               }
             const int row0 = 4 * qd * C + rank;
-            p.y[(size_t)row0 * p.ldy + col] = __float2half_rn(sum.x);
-            if (row0 + C < p.batch) p.y[(size_t)(row0 + C) * p.ldy + col] = __float2half_rn(sum.y);
-            if (row0 + 2 * C < p.batch) p.y[(size_t)(row0 + 2 * C) * p.ldy + col] = __float2half_rn(sum.z);
-            if (row0 + 3 * C < p.batch) p.y[(size_t)(row0 + 3 * C) * p.ldy + col] = __float2half_rn(sum.w);
+            store_out16(p.y + (size_t)row0 * p.ldy + col, sum.x, bf16);
+            if (row0 + C < p.batch) store_out16(p.y + (size_t)(row0 + C) * p.ldy + col, sum.y, bf16);
+            if (row0 + 2 * C < p.batch) store_out16(p.y + (size_t)(row0 + 2 * C) * p.ldy + col, sum.z, bf16);
+            if (row0 + 3 * C < p.batch) store_out16(p.y + (size_t)(row0 + 3 * C) * p.ldy + col, sum.w, bf16);
           }
         }
       }
@@ -566,9 +568,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 struct MapKey {
   const void* x;
   long long ldx;
-  int batch, k, bpad;
+  int batch, k, bpad, bf16;
   bool operator==(const MapKey& o) const {
-    return x == o.x && ldx == o.ldx && batch == o.batch && k == o.k && bpad == o.bpad;
+    return x == o.x && ldx == o.ldx && batch == o.batch && k == o.k && bpad == o.bpad && bf16 == o.bf16;
   }
 };
 struct MapKeyHash {
@@ -577,7 +579,7 @@ struct MapKeyHash {
     h = h * 1000003u ^ (size_t)m.ldx;
     h = h * 1000003u ^ (size_t)m.batch;
     h = h * 1000003u ^ (size_t)m.k;
-    return h * 1000003u ^ (size_t)m.bpad;
+    return h * 1000003u ^ (size_t)(m.bpad * 2 + m.bf16);
   }
 };
 
@@ -595,11 +597,12 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   return fn;
 }
 
-// X[batch, K] fp16, row stride ldx: inner dimension K, box {64 channels, bpad rows}, 128-byte swizzle.
+// X[batch, K] fp16 or bf16, row stride ldx: inner dimension K, box {64 channels, bpad rows}, 128-byte swizzle.
 cudaError_t get_x_tensor_map(const GemmParams& p, int bpad, CUtensorMap* out) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  const MapKey key{p.x, p.ldx, p.batch, p.k, bpad};
+  const int bf16 = (p.flags & kFlagBf16) != 0 ? 1 : 0;
+  const MapKey key{p.x, p.ldx, p.batch, p.k, bpad, bf16};
   {
     std::lock_guard<std::mutex> lk(mu);
     auto it = cache.find(key);
@@ -614,7 +617,7 @@ cudaError_t get_x_tensor_map(const GemmParams& p, int bpad, CUtensorMap* out) {
   const cuuint64_t gstride[1] = {(cuuint64_t)p.ldx * 2};
   const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)bpad};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(p.x), gdim, gstride, box, estr,
+  const CUresult r = encode(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(p.x), gdim, gstride, box, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;

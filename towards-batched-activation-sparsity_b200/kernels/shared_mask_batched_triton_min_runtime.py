@@ -6,11 +6,12 @@ end-to-end decode scripts run against it unchanged; the work is done by libbas (
 sm_100a CUDA) instead of Triton kernels.  Differences a caller can observe:
 
 * ``num_split_k`` and the ``tile_*`` arguments are accepted and ignored: the split of the active
-  blocks over the GPU is chosen inside the kernel (a persistent stream-K partition), and the
-  result does not depend on it beyond fp32 rounding.
+  blocks over the GPU is chosen inside the library (column ranges per CTA or per cluster), and
+  the result does not depend on it beyond fp32 rounding.
 * The tensor returned by ``_get_prepacked_weight_block_major`` is an opaque uint8 buffer in
   libbas's tile-major layout, not the reference's ``[K/64, 64, N]`` view.  No caller reads it.
-* float16 only.  There is no CPU path: CPU tensors raise ``ValueError``.
+* float16 or bfloat16 (x, weight and out alike).  There is no CPU path: CPU tensors raise
+  ``ValueError``.
 """
 
 from __future__ import annotations
