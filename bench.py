@@ -219,13 +219,13 @@ def _graph_time_us(torch, stream, build, calls_per_graph: int, reps: int, repeat
     return float(statistics.median(vals))
 
 
-def _layer_stack(torch, dist, dev, world, rank, stream, fuse=False) -> dict:
+def _layer_stack(torch, dist, dev, world, rank, stream, fuse=False, allreduce="nccl") -> dict:
     """The Llama-2-7B decode-step linear stack (32 layers x 7 masked projections, B = 16, sparsity
     0.638), column-/row-parallel over the ranks with an NCCL all-reduce after o and down: one CUDA
     graph per step where NCCL allows capture, timed by CUDA events, max over ranks."""
     from bas import tp
 
-    stack = tp.DecodeLinearStack(32, 16, 0.638, dev, world, rank, fuse_shared_inputs=fuse)
+    stack = tp.DecodeLinearStack(32, 16, 0.638, dev, world, rank, fuse_shared_inputs=fuse, allreduce=allreduce)
     with torch.cuda.stream(stream):
         for _ in range(3):
             stack.step()
@@ -258,6 +258,7 @@ def _layer_stack(torch, dist, dev, world, rank, stream, fuse=False) -> dict:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    stack.close()
     return {"layers": 32, "linears_per_step": len(stack.items), "batch": 16, "sparsity": 0.638,
             "parallelism": f"tp{world}: column-parallel q/k/v/gate/up, row-parallel o/down + all-reduce",
             "ms_per_step": round(ms, 4), "active_weight_gb_per_step": round(stack.active_bytes / 1e9, 3),
@@ -435,8 +436,18 @@ def run_gpu(args) -> None:
         # the same step with q/k/v and gate/up stacked into one masked GEMM each (they share their
         # input and mask in the model; here the q and gate inputs and masks stand for the group)
         stacked = _layer_stack(torch, dist, dev, world, rank, stream, fuse=True)
-        layer_stack["stacked_qkv_gateup"] = {k: stacked[k] for k in
-                                             ("linears_per_step", "ms_per_step", "active_weight_gbs", "launch")}
+        keys = ("linears_per_step", "ms_per_step", "active_weight_gbs", "launch")
+        layer_stack["stacked_qkv_gateup"] = {k: stacked[k] for k in keys}
+        if world > 1:
+            # the same two steps with o/down summed over the ranks inside the contraction kernel
+            # (fp32 partials read from the peers over NVLink) instead of by an NCCL all-reduce
+            for name, fuse in (("in_kernel_sum", False), ("in_kernel_sum_stacked_qkv_gateup", True)):
+                torch.cuda.empty_cache()
+                try:
+                    r = _layer_stack(torch, dist, dev, world, rank, stream, fuse=fuse, allreduce="in_kernel")
+                    layer_stack[name] = {k: r[k] for k in keys}
+                except Exception as exc:
+                    layer_stack[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     except Exception as exc:
         layer_stack = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     torch.cuda.empty_cache()
@@ -509,7 +520,7 @@ def run_gpu(args) -> None:
         }
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
         # profiles/umma_colsplit_down_proj_b64.md (same workload, one launch)
-        roofline["traffic"] = 44_349_696
+        roofline["traffic"] = 44_313_984
         cpu = cpu_baseline() if world == 1 else None
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,

@@ -166,6 +166,40 @@ BAS_API int bas_select_topk_noalloc(const void* x_dev, int64_t ldx, int batch, i
                                     int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
                                     double* scores_out_dev, void* stream);
 
+/* ---- row-parallel contraction with the sum over ranks formed in the kernel -------------------
+ * No counterpart in the reference (it is single-GPU).  For the o / down projections of a
+ * tensor-parallel layer: every rank (one process per GPU of one box) multiplies its K-shard and
+ * the partial outputs are added inside the contraction kernel, through an exchange area that each
+ * rank maps into its peers (CUDA IPC, plain peer loads over NVLink).  CTA c of every rank writes
+ * its fp32 partial to its own area, publishes a call counter, waits (bounded, about a second) for
+ * the peers' counters and adds the partials in rank order: the result is identical on all ranks
+ * and does not depend on timing.  A wait that runs out sets BAS_DEV_WAIT_EXPIRED and leaves Y of
+ * that CTA unwritten.  All ranks must issue the same sequence of bas_gemm_allreduce calls on a
+ * group (same batch and n per call, n at most the group's); calls on one group must not overlap
+ * on a GPU.
+ *
+ *   bas_tp_create   allocates and zeroes this rank's area for outputs of up to max_batch x n
+ *   bas_tp_handle   writes the area's BAS_TP_HANDLE_BYTES-byte inter-process handle
+ *   bas_tp_connect  takes all ranks' handles (world x BAS_TP_HANDLE_BYTES, rank order; the caller
+ *                   gathers them with whatever transport it has) and maps the peers' areas; every
+ *                   rank must have returned from it before the first bas_gemm_allreduce
+ *   bas_gemm_allreduce  bas_gemm_ex with k = this rank's K-shard; y receives the full sum
+ *   bas_tp_disconnect unmaps the peers' areas; bas_tp_destroy does that too and frees this rank's
+ *                   own area, which no peer may still have mapped: disconnect on every rank, meet
+ *                   (a barrier of the caller's), then destroy */
+typedef struct bas_tp bas_tp;
+#define BAS_TP_HANDLE_BYTES 64
+#define BAS_TP_MAX_RANKS 8
+BAS_API int bas_tp_create(bas_tp** out, int rank, int world, int max_batch, int n);
+BAS_API int bas_tp_handle(bas_tp* tp, void* handle_out);
+BAS_API int bas_tp_connect(bas_tp* tp, const void* handles);
+BAS_API int bas_tp_disconnect(bas_tp* tp);
+BAS_API void bas_tp_destroy(bas_tp* tp);
+BAS_API int bas_gemm_allreduce(bas_tp* tp, const void* x_dev, int64_t ldx, const void* packed_dev,
+                               const int32_t* ids_dev, const int32_t* count_dev, int k_host,
+                               const uint8_t* bitmap_dev, int batch, int k, int n, void* y_dev, int64_t ldy,
+                               void* ws_dev, size_t ws_bytes, int flags, void* stream);
+
 /* ---- host-buffer operator -------------------------------------------------------------------
  * The call pattern of _sparse_linear (scripts/bench_roundrobin_e2e_decode.py:179-284) for a caller
  * whose activations live in host memory: a handle owns the packed weight, the device staging

@@ -606,3 +606,36 @@ def test_bf16_selection_is_bit_exact(dev, b, k, kind):
         want = O.energy_budget_ids(scores, 0.8, 2)
         assert int(count_b.item()) == want.size
         assert np.array_equal(ids_b[: want.size].cpu().numpy(), want)
+
+
+# ---------------------------------------------------------------------------------------------
+# row-parallel sum formed inside the kernel: the one-rank case (publish, collect nothing, convert)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("b,k,n,n_keep", [(16, 11008, 4096, 62), (64, 11008, 4096, 83), (2, 4096, 4096, 13),
+                                          (5, 512, 24000, 5), (33, 1088, 4104, 9)])
+def test_in_kernel_sum_with_one_rank_equals_plain_call(dev, b, k, n, n_keep):
+    ops = _ops()
+    nb = (k + 63) // 64
+    x = torch.from_numpy(O.make_activations(b, k, seed=b)).to(dev)
+    w = torch.from_numpy(O.make_weight(n, k, seed=b + 1)).to(dev)
+    packed = ops.pack_weight(w)
+    group = ops.ExchangeGroup(dev, 64, n)
+    try:
+        for rep in range(5):          # call numbers 1..5: both partial buffers, several times
+            ids = torch.from_numpy(O.random_active_blocks(nb, max(1, n_keep - rep), seed=rep)).to(dev)
+            want = torch.empty(b, n, dtype=torch.float16, device=dev)
+            got = torch.full((b, n), float("nan"), dtype=torch.float16, device=dev)
+            ops.gemm(x, packed, want, ids=ids)
+            ops.gemm(x, packed, got, ids=ids, tp=group, ids_stable=bool(rep & 1))
+            torch.cuda.synchronize()
+            assert ops.read_status(dev) == 0
+            assert torch.equal(got, want)
+        # an empty active set known only on the device: this rank's partial is zero
+        got = torch.full((b, n), float("nan"), dtype=torch.float16, device=dev)
+        ops.gemm(x, packed, got, ids=ids, count=torch.zeros(1, dtype=torch.int32, device=dev), k_host=int(ids.numel()),
+                 tp=group)
+        torch.cuda.synchronize()
+        assert ops.read_status(dev) == 0
+        assert float(got.float().abs().max().item()) == 0.0
+    finally:
+        group.close()

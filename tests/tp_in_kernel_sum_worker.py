@@ -1,0 +1,79 @@
+"""One rank of the multi-GPU test of the row-parallel sum formed inside the contraction kernel
+(started by tests/test_tp_gpu.py through torch.distributed.run, one process per GPU).  Not a test
+module itself."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "towards-batched-activation-sparsity_b200"))
+
+from bas import ops, tp          # noqa: E402
+from oracle import bas_oracle as O   # noqa: E402
+
+TOL = 2e-3
+
+
+def main() -> None:
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    group = ops.ExchangeGroup(dev, 64, 4104)
+    failures = []
+    call = 0
+    for b, k, n, n_keep in [(16, 11008, 4096, 62), (64, 11008, 4096, 83), (2, 4096, 4096, 13), (33, 1088, 4104, 9),
+                            (16, 11008, 4096, 3), (16, 11008, 4096, 62)]:
+        nb = (k + 63) // 64
+        x_h = O.make_activations(b, k, seed=100 + call, dist="laplace")
+        w_h = O.make_weight(n, k, seed=200 + call)
+        ids_h = O.random_active_blocks(nb, n_keep, seed=300 + call)
+        b0, b1 = tp.row_shard_blocks(k, world, rank)
+        k0, k1 = b0 * 64, min(b1 * 64, k)
+        x = torch.from_numpy(x_h).to(dev)
+        packed = ops.pack_weight(torch.from_numpy(np.ascontiguousarray(w_h[:, k0:k1])).to(dev))
+        bitmap = torch.from_numpy(O.build_bitmap(ids_h, nb)).to(dev)
+        out = torch.full((b, n), float("nan"), dtype=torch.float16, device=dev)
+        for rep in range(3):
+            out.fill_(float("nan"))
+            ops.gemm(x[:, k0:k1], packed, out, bitmap=bitmap[b0:b1], tp=group, ids_stable=bool(rep & 1))
+            call += 1
+        torch.cuda.synchronize()
+        status = ops.read_status(dev)
+        err = O.max_err_ratio(out.float().cpu().numpy(), O.masked_gemm(x_h, w_h, ids_h))
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        same = all(torch.equal(g, gathered[0]) for g in gathered)
+        if status != 0 or not err <= TOL or not same:
+            failures.append((b, k, n, n_keep, status, err, same))
+    # the layer stack: in-kernel sums against NCCL all-reduces of fp16 partials
+    outs = {}
+    for mode in ("nccl", "in_kernel"):
+        stack = tp.DecodeLinearStack(1, 16, 0.638, dev, world, rank, seed=3, allreduce=mode)
+        stack.step()
+        stack.step()
+        torch.cuda.synchronize()
+        outs[mode] = [o.float().clone() for lin, _, _, o in stack.items if lin.spec.parallel == "row"]
+        if ops.read_status(dev) != 0:
+            failures.append(("stack status", mode))
+        stack.close()
+        del stack
+    for a, c in zip(outs["nccl"], outs["in_kernel"]):
+        d = float((a - c).abs().max() / c.abs().max())
+        if not d <= 4e-3:       # the NCCL path rounds every rank's partial to fp16 first
+            failures.append(("stack", d))
+    group.close()
+    flag = torch.tensor([len(failures)], device=dev)
+    dist.all_reduce(flag)
+    if rank == 0:
+        print("TP_IN_KERNEL_SUM", "OK" if int(flag.item()) == 0 else f"FAILED {failures}", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag.item()) == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -13,6 +13,7 @@ SCORE_ENERGY = 1
 IDS_STABLE = 16          # BAS_GEMM_IDS_STABLE
 GEMM_BF16 = 32           # BAS_GEMM_BF16
 SCORE_BF16 = 256         # BAS_SCORE_BF16
+TP_HANDLE_BYTES = 64     # BAS_TP_HANDLE_BYTES
 
 _PKG = Path(__file__).resolve().parent.parent
 lib_path = _PKG / "libbas.so"
@@ -56,6 +57,12 @@ _SIGNATURES = {
     "bas_select_budget": (_i, [_vp, _i64, _i, _i, C.c_double, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bas_select_budget_ex": (_i, [_vp, _i64, _i, _i, C.c_double, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bas_select_topk_noalloc": (_i, [_vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "bas_tp_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i]),
+    "bas_tp_handle": (_i, [_vp, _vp]),
+    "bas_tp_connect": (_i, [_vp, _vp]),
+    "bas_tp_disconnect": (_i, [_vp]),
+    "bas_tp_destroy": (None, [_vp]),
+    "bas_gemm_allreduce": (_i, [_vp, _vp, _i64, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i64, _vp, _sz, _i, _vp]),
     "bas_linear_create": (_i, [C.POINTER(_vp), _vp, _i, _i, _i]),
     "bas_linear_forward_host": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "bas_linear_forward_host_ids": (_i, [_vp, _vp, _i, _vp, _i, _vp]),

@@ -15,7 +15,8 @@ from typing import Optional
 import torch
 
 from . import abi as _abi
-from .abi import BLOCK_K, GEMM_BF16, IDS_STABLE, MAX_BATCH, SCORE_BF16, SCORE_ENERGY, SCORE_NORM, check, lib
+from .abi import (BLOCK_K, GEMM_BF16, IDS_STABLE, MAX_BATCH, SCORE_BF16, SCORE_ENERGY, SCORE_NORM, TP_HANDLE_BYTES,
+                  check, lib)
 
 _PACKED: dict[tuple, torch.Tensor] = {}
 _PACK_STATS = {"hits": 0, "misses": 0}
@@ -130,7 +131,7 @@ def read_status(device: Optional[torch.device] = None) -> int:
 def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: Optional[torch.Tensor] = None,
          count: Optional[torch.Tensor] = None, k_host: Optional[int] = None,
          bitmap: Optional[torch.Tensor] = None, family: int = 0, ids_stable: bool = False,
-         cluster: int = 0, pairs: int = 0) -> None:
+         cluster: int = 0, pairs: int = 0, tp=None) -> None:
     """out2d[B, N] = x2d[B, K] restricted to the active blocks, times W^T.
 
     ``ids`` int32 device list (``count``: optional int32[1] device-side length, ``k_host`` an upper
@@ -140,6 +141,8 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
     ``cluster``: 0 lets the library choose; 1, 2 or 4 forces the tcgen05 kernel's cluster size.
     ``pairs``: 0 lets the library choose; 2, 3 or 4 forces its number of copy/MMA warp pairs.
     x, out (and the weight that was packed) are all float16 or all bfloat16.
+    ``tp``: an :class:`ExchangeGroup`; x and packed are then this rank's K-shard and out receives
+    the sum over the group's ranks, formed inside the kernel (every rank must make the same call).
     Batches above 64 rows are run in slices of 64."""
     _require_cuda_fp16(x2d, "x")
     _require_cuda_fp16(out2d, "out")
@@ -171,7 +174,8 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
         for b0 in range(0, bt, MAX_BATCH):
             bsz = min(MAX_BATCH, bt - b0)
             xs, ys = x2d[b0:b0 + bsz], out2d[b0:b0 + bsz]
-            check(lib.bas_gemm_ex(
+            fn = lib.bas_gemm_ex if tp is None else (lambda *a: lib.bas_gemm_allreduce(tp.handle, *a))
+            check(fn(
                 xs.data_ptr(), xs.stride(0), packed.data_ptr(),
                 ids.data_ptr() if ids is not None and bitmap is None else None,
                 count.data_ptr() if count is not None else None, int(k_host),
@@ -179,6 +183,64 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
                 bsz, k, n, ys.data_ptr(), ys.stride(0), ws.data_ptr(), ws.numel(),
                 int(family) | (IDS_STABLE if ids_stable else 0) | bf16 | (int(cluster) << 8) | (int(pairs) << 12), stream),
                 "bas_gemm")
+
+
+class ExchangeGroup:
+    """This rank's exchange area for row-parallel contractions summed inside the kernel, connected
+    to the areas of the other ranks of ``group`` (one process per GPU, all on one box).  The handles
+    travel through ``torch.distributed``; construction is collective and ends with a barrier."""
+
+    def __init__(self, device, max_batch: int, n: int, group=None):
+        import ctypes
+
+        import torch.distributed as dist
+
+        self.device = torch.device(device)
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.group = group
+        self.world = dist.get_world_size(group) if multi else 1
+        self.rank = dist.get_rank(group) if multi else 0
+        self.handle = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            check(lib.bas_tp_create(ctypes.byref(self.handle), self.rank, self.world, int(max_batch), int(n)),
+                  "bas_tp_create")
+            mine = (ctypes.c_ubyte * TP_HANDLE_BYTES)()
+            check(lib.bas_tp_handle(self.handle, mine), "bas_tp_handle")
+            if multi:
+                local = torch.tensor(list(mine), dtype=torch.uint8, device=self.device)
+                gathered = [torch.empty_like(local) for _ in range(self.world)]
+                dist.all_gather(gathered, local, group=group)
+                blob = bytes(torch.cat(gathered).cpu().tolist())
+            else:
+                blob = bytes(mine)
+            buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
+            check(lib.bas_tp_connect(self.handle, buf), "bas_tp_connect")
+            if multi:
+                dist.barrier(group=group)      # nobody publishes into an area that is not mapped yet
+
+    def close(self) -> None:
+        """Collective: every rank unmaps its peers, all meet, then each frees its own area."""
+        import torch.distributed as dist
+
+        if not self.handle:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            lib.bas_tp_disconnect(self.handle)
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            lib.bas_tp_destroy(self.handle)
+        self.handle = None
+
+    def __del__(self):
+        # not collective: a group that was never closed is left to process exit when it has peers
+        try:
+            if self.handle and self.world == 1:
+                self.close()
+        except Exception:
+            pass
 
 
 def build_bitmap(ids: torch.Tensor, nb: int, device=None, count: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -99,16 +99,22 @@ class ShardedLinear:
         self.n_local = shard.shape[0]
         self.packed = ops.pack_weight(shard.contiguous()) if self.n_local and self.k_local else None
 
-    def forward(self, x2d, bitmap, out2d, ids_stable: bool = True):
+    def forward(self, x2d, bitmap, out2d, ids_stable: bool = True, exchange=None):
         """x2d is the replicated [B, K] activation, bitmap the replicated uint8[K/64] mask.  Writes
-        this rank's output slice (column-parallel) or partial sum (row-parallel) into out2d."""
+        this rank's output slice (column-parallel) or partial sum (row-parallel) into out2d; with an
+        ``exchange`` group a row-parallel linear writes the sum over all ranks instead (formed inside
+        the contraction kernel), and no collective has to follow."""
         from . import ops
 
         if self.packed is None:
+            if exchange is not None:
+                raise ValueError("a rank without a K-shard cannot take part in the in-kernel sum")
             out2d.zero_()
             return
-        xs = x2d if self.spec.parallel == "column" else x2d[:, self.b0 * BLOCK_K: self.b0 * BLOCK_K + self.k_local]
-        ops.gemm(xs, self.packed, out2d, bitmap=bitmap[self.b0:self.b1], ids_stable=ids_stable)
+        row = self.spec.parallel == "row"
+        xs = x2d[:, self.b0 * BLOCK_K: self.b0 * BLOCK_K + self.k_local] if row else x2d
+        ops.gemm(xs, self.packed, out2d, bitmap=bitmap[self.b0:self.b1], ids_stable=ids_stable,
+                 tp=exchange if row else None)
 
 
 class DecodeLinearStack:
@@ -119,16 +125,23 @@ class DecodeLinearStack:
     linear stack.  Inputs are generated per linear, identically on every rank.
 
     ``fuse_shared_inputs``: q/k/v and gate/up read one activation through one mask (as they do in
-    the model) and run as one masked GEMM each: four launches per layer instead of seven."""
+    the model) and run as one masked GEMM each: four launches per layer instead of seven.
+    ``allreduce``: how the row-parallel partial outputs are summed over the ranks."""
 
     def __init__(self, layers: int, batch: int, sparsity: float, device, world: int = 1, rank: int = 0,
-                 seed: int = 0, group=None, fuse_shared_inputs: bool = False):
+                 seed: int = 0, group=None, fuse_shared_inputs: bool = False, allreduce: str = "nccl"):
         import torch
 
         from . import ops
         from .abi import SCORE_NORM
 
+        if allreduce not in ("nccl", "in_kernel"):
+            raise ValueError("allreduce must be 'nccl' or 'in_kernel'")
         self.world, self.rank, self.group, self.batch = world, rank, group, batch
+        # "in_kernel": o and down add their partial outputs over the ranks inside the contraction
+        # kernel (peer loads over NVLink); "nccl": one all-reduce call after each of them
+        self.exchange = ops.ExchangeGroup(device, batch, max(s.n for s in LLAMA2_7B_LAYER if s.parallel == "row"),
+                                          group) if allreduce == "in_kernel" else None
         self.items = []
         self._shared = {}
         gen = torch.Generator(device=device)
@@ -175,10 +188,16 @@ class DecodeLinearStack:
                 self.active_bytes += n_keep * BLOCK_K * spec.n * 2
         torch.cuda.synchronize(device)
 
+    def close(self) -> None:
+        """Collective when the stack sums inside the kernel: releases the exchange areas."""
+        if self.exchange is not None:
+            self.exchange.close()
+            self.exchange = None
+
     def step(self) -> None:
         import torch.distributed as dist
 
         for lin, x, bitmap, out in self.items:
-            lin.forward(x, bitmap, out)
-            if lin.spec.parallel == "row" and self.world > 1:
+            lin.forward(x, bitmap, out, exchange=self.exchange)
+            if lin.spec.parallel == "row" and self.world > 1 and self.exchange is None:
                 dist.all_reduce(out, group=self.group)

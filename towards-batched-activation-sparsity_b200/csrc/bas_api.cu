@@ -120,9 +120,93 @@ int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream) {
   return e == cudaSuccess ? BAS_OK : cuda_fail(e);
 }
 
-int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
-                const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
-                void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream) {
+// ---------------------------------------------------------------------------------------------
+// exchange areas of a tensor-parallel group (one process per GPU, all on one box)
+// ---------------------------------------------------------------------------------------------
+struct bas_tp {
+  int rank = 0, world = 0, max_batch = 0, n = 0, npad = 0;
+  size_t bytes = 0;
+  unsigned char* area[kTpMaxRanks] = {};   // area[rank] is this rank's own allocation
+  bool opened[kTpMaxRanks] = {};
+};
+
+static size_t tp_area_bytes(int max_batch, int npad) {
+  return (size_t)kTpHeaderBytes + 2 * sizeof(float) * (size_t)max_batch * (size_t)npad;
+}
+
+int bas_tp_create(bas_tp** out, int rank, int world, int max_batch, int n) {
+  if (out == nullptr || world < 1 || world > kTpMaxRanks || rank < 0 || rank >= world || max_batch <= 0 ||
+      max_batch > BAS_MAX_BATCH || n <= 0)
+    return BAS_ERR_INVALID_ARGUMENT;
+  bas_tp* t = new (std::nothrow) bas_tp();
+  if (t == nullptr) return BAS_ERR_CUDA;
+  t->rank = rank;
+  t->world = world;
+  t->max_batch = max_batch;
+  t->n = n;
+  t->npad = padded_cols(n);
+  t->bytes = tp_area_bytes(max_batch, t->npad);
+  void* ptr = nullptr;
+  cudaError_t e = cudaMalloc(&ptr, t->bytes);
+  if (e == cudaSuccess) e = cudaMemset(ptr, 0, t->bytes);   // flags and call counters start at zero
+  if (e != cudaSuccess) {
+    if (ptr != nullptr) cudaFree(ptr);
+    delete t;
+    return cuda_fail(e);
+  }
+  t->area[rank] = (unsigned char*)ptr;
+  *out = t;
+  return BAS_OK;
+}
+
+int bas_tp_handle(bas_tp* t, void* handle_out) {
+  if (t == nullptr || handle_out == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  static_assert(sizeof(cudaIpcMemHandle_t) == BAS_TP_HANDLE_BYTES, "handle size");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, t->area[t->rank]);
+  if (e != cudaSuccess) return cuda_fail(e);
+  std::memcpy(handle_out, &h, sizeof(h));
+  return BAS_OK;
+}
+
+int bas_tp_connect(bas_tp* t, const void* handles) {
+  if (t == nullptr || (t->world > 1 && handles == nullptr)) return BAS_ERR_INVALID_ARGUMENT;
+  for (int q = 0; q < t->world; ++q) {
+    if (q == t->rank || t->opened[q]) continue;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, (const unsigned char*)handles + (size_t)q * BAS_TP_HANDLE_BYTES, sizeof(h));
+    void* ptr = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail(e);
+    t->area[q] = (unsigned char*)ptr;
+    t->opened[q] = true;
+  }
+  return BAS_OK;
+}
+
+int bas_tp_disconnect(bas_tp* t) {
+  if (t == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  cudaError_t first = cudaSuccess;
+  for (int q = 0; q < t->world; ++q)
+    if (t->opened[q]) {
+      cudaError_t e = cudaIpcCloseMemHandle(t->area[q]);
+      if (e != cudaSuccess && first == cudaSuccess) first = e;
+      t->area[q] = nullptr;
+      t->opened[q] = false;
+    }
+  return first == cudaSuccess ? BAS_OK : cuda_fail(first);
+}
+
+void bas_tp_destroy(bas_tp* t) {
+  if (t == nullptr) return;
+  (void)bas_tp_disconnect(t);
+  if (t->area[t->rank] != nullptr) cudaFree(t->area[t->rank]);
+  delete t;
+}
+
+static int gemm_impl(const bas_tp* tp, const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
+                     const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
+                     void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream) {
   if (x_dev == nullptr || packed_dev == nullptr || y_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || k <= 0 || n <= 0 || k_host < 0 || ldx < k || ldy < n) return BAS_ERR_INVALID_ARGUMENT;
   if (batch > BAS_MAX_BATCH) return BAS_ERR_UNSUPPORTED;
@@ -142,7 +226,12 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   if (di.cc_major != 10) return BAS_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
 
-  if (bitmap_dev == nullptr && k_host == 0) {  // empty active set known on the host: Y = 0
+  if (tp != nullptr) {
+    for (int q = 0; q < tp->world; ++q)
+      if (tp->area[q] == nullptr) return BAS_ERR_INVALID_ARGUMENT;   // bas_tp_connect has not run
+    if (batch > tp->max_batch || n > tp->n || family == 1) return BAS_ERR_INVALID_ARGUMENT;
+  }
+  if (tp == nullptr && bitmap_dev == nullptr && k_host == 0) {  // empty active set known on the host: Y = 0
     cudaError_t e = cudaMemset2DAsync(y_dev, (size_t)ldy * 2, 0, (size_t)n * 2, (size_t)batch, s);
     return e == cudaSuccess ? BAS_OK : cuda_fail(e);
   }
@@ -165,6 +254,15 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   p.ldy = (long long)ldy;
   p.flags = flags;
   p.status = (unsigned int*)ws_dev;
+  p.tp = TpExchange{};
+  if (tp != nullptr) {
+    p.tp.world = tp->world;
+    p.tp.rank = tp->rank;
+    p.tp.ldp = tp->npad;
+    p.tp.buf_floats = (long long)tp->max_batch * tp->npad;
+    p.tp.own = tp->area[tp->rank];
+    for (int q = 0; q < tp->world; ++q) p.tp.area[q] = tp->area[q];
+  }
 #ifdef BAS_TRACE
   if (g_trace_dev == nullptr) {
     cudaMalloc(&g_trace_dev, sizeof(long long) * 1024);
@@ -180,6 +278,21 @@ int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const in
   if (small && (batch > 8 || (flags & BAS_GEMM_BF16) != 0)) return BAS_ERR_UNSUPPORTED;   // the CUDA-core kernel is fp16 only
   cudaError_t e = small ? launch_gemv(p, grid_cap, s) : launch_umma(p, grid_cap, s);
   return e == cudaSuccess ? BAS_OK : cuda_fail(e);
+}
+
+int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
+                const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
+                void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream) {
+  return gemm_impl(nullptr, x_dev, ldx, packed_dev, ids_dev, count_dev, k_host, bitmap_dev, batch, k, n, y_dev, ldy,
+                   ws_dev, ws_bytes, flags, stream);
+}
+
+int bas_gemm_allreduce(bas_tp* tp, const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
+                       const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
+                       void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream) {
+  if (tp == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  return gemm_impl(tp, x_dev, ldx, packed_dev, ids_dev, count_dev, k_host, bitmap_dev, batch, k, n, y_dev, ldy, ws_dev,
+                   ws_bytes, flags, stream);
 }
 
 int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev, const int32_t* count_dev,

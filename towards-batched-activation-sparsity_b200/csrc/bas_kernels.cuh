@@ -5,6 +5,24 @@
 
 namespace bas {
 
+// Exchange area of a row-parallel contraction whose sum over the ranks of one box is formed inside
+// the kernel.  Every rank owns one area (device memory mapped into its peers); all areas have the
+// same layout:
+//   [0, 4 * kTpMaxCtas)              flag[c]: number of partials CTA c of this rank has published
+//   [4 * kTpMaxCtas, 8 * kTpMaxCtas) private to the owner: calls CTA c has taken part in
+//   [kTpHeaderBytes, ...)            two partial buffers [rows][ldp] fp32, used alternately
+constexpr int kTpMaxRanks = 8;
+constexpr int kTpMaxCtas = 512;
+constexpr int kTpHeaderBytes = 8 * kTpMaxCtas;
+struct TpExchange {
+  int world;                           // 0: no exchange, the kernel stores Y itself
+  int rank;
+  int ldp;                             // row stride of a partial buffer, in floats
+  long long buf_floats;                // floats per partial buffer
+  unsigned char* own;                  // this rank's area
+  unsigned char* area[kTpMaxRanks];    // every rank's area as mapped here (area[rank] == own)
+};
+
 struct GemmParams {
   const __half* x;          // [batch, K], row stride ldx
   long long ldx;
@@ -21,11 +39,12 @@ struct GemmParams {
   int group;                // blocks per ring slot: one barrier hand-off covers this many chunks
   int wslot;                // bytes reserved per slot for a weight chunk (multiple of 1024)
   int issuers;              // MMA-issuing warps in use (2 or 4), each with its own accumulators
-  int tile_cols;            // output columns one pass of a CTA covers: 128, or 256 (two MMA halves)
+  int tile_cols;            // output columns one pass of a CTA covers (128)
   __half* y;                // [batch, N], row stride ldy
   long long ldy;
   int flags;                // kFlag* bits
   unsigned int* status;     // workspace: status word
+  TpExchange tp;            // row-parallel sum over ranks (world 0 = off)
 #ifdef BAS_TRACE
   long long* trace;         // diagnostic build only: per-role cycle counters of CTA 0
 #endif

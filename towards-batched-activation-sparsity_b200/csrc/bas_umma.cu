@@ -63,6 +63,7 @@ struct UmmaSmemHeader {
   uint32_t tmem_base;
   int k_act;
   int abort_flag;
+  int tp_ready;   // every peer has published its partial of this call
   long long t0;   // diagnostic builds: clock at kernel start
 };
 
@@ -125,6 +126,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     mbar_init(&hdr->acc_empty, kEpiThreads / 32);
     mbar_init(&hdr->ids_ready, 1);
     hdr->abort_flag = 0;
+    hdr->tp_ready = 0;
     hdr->k_act = 0;
     hdr->t0 = BAS_TRACE_CLOCK();
     fence_barrier_init();
@@ -156,6 +158,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   const int n_sub = (width + TW - 1) / TW;
 
   int k_act = 0;
+  // Row-parallel sum over ranks (epilogue threads only): this call's sequence number in the
+  // exchange area and the partial buffer it selects.
+  unsigned int tp_epoch = 0;
+  float* tp_part = nullptr;
   int armed_next = warp, armed_cnt = 0;   // producer warps: next group to arm, groups armed so far
 
   const int P = p.issuers;
@@ -360,7 +366,19 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       constexpr int kChunks = BPAD / 16;
       constexpr int kChunks0 = (kChunks + 1) / 2;   // set 0's chunks; set 1 takes the rest
       if (early_ids) pdl_wait();            // before the first write to Y
-      if (ok && k_act == 0) {
+      if (p.tp.world > 0) {
+        // The counter is private to CTAs of this index; the previous call's CTA wrote it before the
+        // wait above (or warp 0's, which the id barrier orders before this point) returned.
+        tp_epoch = ((const unsigned int*)(p.tp.own + 4 * kTpMaxCtas))[blockIdx.x] + 1u;
+        tp_part = (float*)(p.tp.own + kTpHeaderBytes) + (size_t)(tp_epoch & 1u) * (size_t)p.tp.buf_floats;
+      }
+      if (ok && k_act == 0 && p.tp.world > 0) {
+        // empty active set on this rank: its partial of the elements this CTA owns is zero
+        const int rz = et & 127;
+        for (int c0 = 0; c0 < width; c0 += kTileN)
+          if (c0 + rz < width && n0 + c0 + rz < p.n)
+            for (int row = rank + C * eset; row < p.batch; row += 2 * C) tp_part[(size_t)row * p.tp.ldp + n0 + c0 + rz] = 0.f;
+      } else if (ok && k_act == 0) {
         // empty active set: the epilogue threads of the whole grid zero Y between them
         const long long total = (long long)p.batch * p.n;
         for (long long e = (long long)blockIdx.x * kEpiThreads + et; e < total; e += (long long)gridDim.x * kEpiThreads)
@@ -427,7 +445,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
               if (rr < wsub && col < p.n) {
 #pragma unroll
                 for (int b = 0; b < NV; ++b)
-                  if (16 * CH0 + b < p.batch) store_out16(p.y + (size_t)(16 * CH0 + b) * p.ldy + col, v[b], bf16);
+                  if (16 * CH0 + b < p.batch) {
+                    if (tp_part != nullptr) tp_part[(size_t)(16 * CH0 + b) * p.tp.ldp + col] = v[b];
+                    else store_out16(p.y + (size_t)(16 * CH0 + b) * p.ldy + col, v[b], bf16);
+                  }
               }
             } else {
               // Cluster mode (one pass per CTA): batch row b is finished by rank b % C.  Push this
@@ -527,12 +548,72 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 sum.w += t.w;
               }
             const int row0 = 4 * qd * C + rank;
-            store_out16(p.y + (size_t)row0 * p.ldy + col, sum.x, bf16);
-            if (row0 + C < p.batch) store_out16(p.y + (size_t)(row0 + C) * p.ldy + col, sum.y, bf16);
-            if (row0 + 2 * C < p.batch) store_out16(p.y + (size_t)(row0 + 2 * C) * p.ldy + col, sum.z, bf16);
-            if (row0 + 3 * C < p.batch) store_out16(p.y + (size_t)(row0 + 3 * C) * p.ldy + col, sum.w, bf16);
+            const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (row0 + e * C < p.batch) {
+                if (tp_part != nullptr) tp_part[(size_t)(row0 + e * C) * p.tp.ldp + col] = vals[e];
+                else store_out16(p.y + (size_t)(row0 + e * C) * p.ldy + col, vals[e], bf16);
+              }
           }
         }
+      }
+    }
+  }
+  if (p.tp.world > 0 && warp >= kEpiWarp0) {
+    // ---- sum over the ranks of the box ----
+    // CTA c of every rank has produced the same rows and columns of its rank's partial.  Publish:
+    // all of this CTA's partial stores, then the call number in flag[c] (release, system scope).
+    // Collect: wait (bounded) until every peer's flag[c] has reached the call number, then add the
+    // partials in rank order and store Y.  A peer can be at most one call ahead of this rank, and
+    // it writes the other buffer then.
+    const int et = tid - 32 * kEpiWarp0, eset = et >> 7, rz = et & 127;
+    named_bar_sync(1, kEpiThreads);
+    if (et == 0) {
+      __threadfence_system();
+      st_release_sys_u32((unsigned int*)p.tp.own + blockIdx.x, tp_epoch);
+      ((unsigned int*)(p.tp.own + 4 * kTpMaxCtas))[blockIdx.x] = tp_epoch;
+    }
+    if (warp == kEpiWarp0) {
+      const unsigned int* peer_flag = nullptr;
+#pragma unroll
+      for (int q = 0; q < kTpMaxRanks; ++q)
+        if (q == lane && q < p.tp.world && q != p.tp.rank) peer_flag = (const unsigned int*)p.tp.area[q] + blockIdx.x;
+      bool ready = true;
+      if (peer_flag != nullptr) {
+        const long long t_start = clock64();
+        // signed distance: the counters may wrap
+        while ((int)(ld_acquire_sys_u32(peer_flag) - tp_epoch) < 0) {
+          if (clock64() - t_start > kWaitCycles) {
+            ready = false;
+            break;
+          }
+          __nanosleep(64);
+        }
+      }
+      ready = __all_sync(0xffffffffu, ready);
+      if (lane == 0) {
+        hdr->tp_ready = (ready && hdr->abort_flag == 0) ? 1 : 0;
+        if (!ready) atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
+      }
+    }
+    named_bar_sync(1, kEpiThreads);
+    if (hdr->tp_ready != 0) {
+      const size_t buf_off = (size_t)kTpHeaderBytes / sizeof(float) + (size_t)(tp_epoch & 1u) * (size_t)p.tp.buf_floats;
+      for (int c0 = 0; c0 < width; c0 += kTileN) {
+        const int col = n0 + c0 + rz;
+        if (c0 + rz < width && col < p.n)
+          for (int row = rank + C * eset; row < p.batch; row += 2 * C) {
+            const size_t off = buf_off + (size_t)row * p.tp.ldp + col;
+            float part[kTpMaxRanks];
+#pragma unroll
+            for (int q = 0; q < kTpMaxRanks; ++q)
+              part[q] = (q < p.tp.world) ? ld_relaxed_sys_f32((const float*)p.tp.area[q] + off) : 0.f;
+            float sum = 0.f;
+#pragma unroll
+            for (int q = 0; q < kTpMaxRanks; ++q) sum += part[q];   // rank order
+            store_out16(p.y + (size_t)row * p.ldy + col, sum, bf16);
+          }
       }
     }
   }
@@ -743,6 +824,8 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   p.stages = slots / pairs * pairs;
   p.group = group;
   const size_t smem = fixed + red_bytes + pad + (size_t)p.stages * group * stage_bytes;
+
+  if (p.tp.world > 0 && ranges * cluster > kTpMaxCtas) return cudaErrorInvalidValue;   // one flag per CTA
 
   CUtensorMap xmap;
   cudaError_t e = get_x_tensor_map(p, BPAD, &xmap);
