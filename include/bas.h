@@ -170,10 +170,11 @@ BAS_API int bas_select_topk_noalloc(const void* x_dev, int64_t ldx, int batch, i
  * No counterpart in the reference (it is single-GPU).  For the o / down projections of a
  * tensor-parallel layer: every rank (one process per GPU of one box) multiplies its K-shard and
  * the partial outputs are added inside the contraction kernel, through an exchange area that each
- * rank maps into its peers (CUDA IPC, plain peer loads over NVLink).  CTA c of every rank writes
- * its fp32 partial to its own area, publishes a call counter, waits (bounded, about a second) for
- * the peers' counters and adds the partials in rank order: the result is identical on all ranks
- * and does not depend on timing.  A wait that runs out sets BAS_DEV_WAIT_EXPIRED and leaves Y of
+ * rank maps into its peers (CUDA IPC, plain peer stores over NVLink).  CTA c of every rank sends
+ * its fp32 partial to every rank's area as 64-bit words {value, call number}, polls (bounded, about
+ * a second) its own area until the words of all ranks carry the current call number, and adds them
+ * in rank order: the result is identical on all ranks and does not depend on timing; one NVLink
+ * traversal, no flags or fences.  A wait that runs out sets BAS_DEV_WAIT_EXPIRED and leaves Y of
  * that CTA unwritten.  All ranks must issue the same sequence of bas_gemm_allreduce calls on a
  * group (same batch and n per call, n at most the group's); calls on one group must not overlap
  * on a GPU.

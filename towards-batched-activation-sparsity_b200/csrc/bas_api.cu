@@ -130,8 +130,8 @@ struct bas_tp {
   bool opened[kTpMaxRanks] = {};
 };
 
-static size_t tp_area_bytes(int max_batch, int npad) {
-  return (size_t)kTpHeaderBytes + 2 * sizeof(float) * (size_t)max_batch * (size_t)npad;
+static size_t tp_area_bytes(int world, int max_batch, int npad) {
+  return (size_t)kTpHeaderBytes + 2 * 8 * (size_t)world * (size_t)max_batch * (size_t)npad;
 }
 
 int bas_tp_create(bas_tp** out, int rank, int world, int max_batch, int n) {
@@ -145,10 +145,10 @@ int bas_tp_create(bas_tp** out, int rank, int world, int max_batch, int n) {
   t->max_batch = max_batch;
   t->n = n;
   t->npad = padded_cols(n);
-  t->bytes = tp_area_bytes(max_batch, t->npad);
+  t->bytes = tp_area_bytes(world, max_batch, t->npad);
   void* ptr = nullptr;
   cudaError_t e = cudaMalloc(&ptr, t->bytes);
-  if (e == cudaSuccess) e = cudaMemset(ptr, 0, t->bytes);   // flags and call counters start at zero
+  if (e == cudaSuccess) e = cudaMemset(ptr, 0, t->bytes);   // call counters and the words' call numbers start at zero
   if (e != cudaSuccess) {
     if (ptr != nullptr) cudaFree(ptr);
     delete t;
@@ -259,7 +259,7 @@ static int gemm_impl(const bas_tp* tp, const void* x_dev, int64_t ldx, const voi
     p.tp.world = tp->world;
     p.tp.rank = tp->rank;
     p.tp.ldp = tp->npad;
-    p.tp.buf_floats = (long long)tp->max_batch * tp->npad;
+    p.tp.src_words = (long long)tp->max_batch * tp->npad;
     p.tp.own = tp->area[tp->rank];
     for (int q = 0; q < tp->world; ++q) p.tp.area[q] = tp->area[q];
   }

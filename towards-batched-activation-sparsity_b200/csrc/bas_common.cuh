@@ -286,24 +286,16 @@ __device__ __forceinline__ int warp_stage_ids(const int32_t* __restrict__ ids, c
   return warp_stage_ids(ids, count_dev, k_host, bitmap, nb, s_ids, status, lane, false, none);
 }
 
-// System-scope accesses for data and flags that another GPU of the box reads or writes through a
-// peer mapping (plain per-thread loads and stores over NVLink only).
-__device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// System-scope 64-bit accesses to memory that another GPU of the box reads or writes through a peer
+// mapping (plain per-thread loads and stores over NVLink only).  A 64-bit scalar access is single-copy
+// atomic: a reader sees either the old or the new word, never a mix.
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
-}
-__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
-  float v;
-  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
-// Named barrier among `count` threads of the CTA (count a multiple of 32), id 1..15.
-__device__ __forceinline__ void named_bar_sync(int id, int count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 // fp32 -> the output's 16-bit type (round to nearest even), stored through the fp16-typed pointer

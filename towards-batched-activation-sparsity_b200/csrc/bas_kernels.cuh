@@ -8,19 +8,22 @@ namespace bas {
 // Exchange area of a row-parallel contraction whose sum over the ranks of one box is formed inside
 // the kernel.  Every rank owns one area (device memory mapped into its peers); all areas have the
 // same layout:
-//   [0, 4 * kTpMaxCtas)              flag[c]: number of partials CTA c of this rank has published
-//   [4 * kTpMaxCtas, 8 * kTpMaxCtas) private to the owner: calls CTA c has taken part in
-//   [kTpHeaderBytes, ...)            two partial buffers [rows][ldp] fp32, used alternately
+//   [0, 4 * kTpMaxCtas)      private to the owner: number of exchange calls CTA c has taken part in
+//   [kTpHeaderBytes, ...)    two receive buffers, used alternately; each holds, per source rank, a
+//                            [rows][ldp] array of 8-byte words {fp32 partial, call number}
+// A rank writes its partial straight into every rank's receive buffer (its own included) with single
+// 64-bit stores: a word whose upper half equals the current call number is valid, so no flag, fence
+// or second round trip is needed - the reader polls its own memory.
 constexpr int kTpMaxRanks = 8;
-constexpr int kTpMaxCtas = 512;
-constexpr int kTpHeaderBytes = 8 * kTpMaxCtas;
+constexpr int kTpMaxCtas = 1024;
+constexpr int kTpHeaderBytes = 4 * kTpMaxCtas;
 struct TpExchange {
   int world;                           // 0: no exchange, the kernel stores Y itself
   int rank;
-  int ldp;                             // row stride of a partial buffer, in floats
-  long long buf_floats;                // floats per partial buffer
-  unsigned char* own;                  // this rank's area
-  unsigned char* area[kTpMaxRanks];    // every rank's area as mapped here (area[rank] == own)
+  int ldp;                             // row stride of a receive array, in words
+  long long src_words;                 // words per source rank in one receive buffer (= max rows * ldp)
+  unsigned char* area[kTpMaxRanks];    // every rank's area as mapped here
+  unsigned char* own;                  // == area[rank]
 };
 
 struct GemmParams {

@@ -63,7 +63,6 @@ struct UmmaSmemHeader {
   uint32_t tmem_base;
   int k_act;
   int abort_flag;
-  int tp_ready;   // every peer has published its partial of this call
   long long t0;   // diagnostic builds: clock at kernel start
 };
 
@@ -126,7 +125,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     mbar_init(&hdr->acc_empty, kEpiThreads / 32);
     mbar_init(&hdr->ids_ready, 1);
     hdr->abort_flag = 0;
-    hdr->tp_ready = 0;
     hdr->k_act = 0;
     hdr->t0 = BAS_TRACE_CLOCK();
     fence_barrier_init();
@@ -161,7 +159,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   // Row-parallel sum over ranks (epilogue threads only): this call's sequence number in the
   // exchange area and the partial buffer it selects.
   unsigned int tp_epoch = 0;
-  float* tp_part = nullptr;
+  size_t tp_slot = 0;       // word offset, inside any rank's area, of this rank's array in the current receive buffer
+  // this rank's partial of one output element, sent to every rank of the group (its own included)
+  auto tp_send = [&](int row, int col, float v) {
+    const unsigned long long word = ((unsigned long long)tp_epoch << 32) | (unsigned long long)__float_as_uint(v);
+    const size_t off = tp_slot + (size_t)row * (size_t)p.tp.ldp + (size_t)col;
+#pragma unroll
+    for (int q = 0; q < kTpMaxRanks; ++q)
+      if (q < p.tp.world) st_relaxed_sys_u64((unsigned long long*)p.tp.area[q] + off, word);
+  };
   int armed_next = warp, armed_cnt = 0;   // producer warps: next group to arm, groups armed so far
 
   const int P = p.issuers;
@@ -369,15 +375,17 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       if (p.tp.world > 0) {
         // The counter is private to CTAs of this index; the previous call's CTA wrote it before the
         // wait above (or warp 0's, which the id barrier orders before this point) returned.
-        tp_epoch = ((const unsigned int*)(p.tp.own + 4 * kTpMaxCtas))[blockIdx.x] + 1u;
-        tp_part = (float*)(p.tp.own + kTpHeaderBytes) + (size_t)(tp_epoch & 1u) * (size_t)p.tp.buf_floats;
+        tp_epoch = ((const unsigned int*)p.tp.own)[blockIdx.x] + 1u;
+        tp_slot = (size_t)kTpHeaderBytes / 8 +
+                  ((size_t)(tp_epoch & 1u) * (size_t)p.tp.world + (size_t)p.tp.rank) * (size_t)p.tp.src_words;
       }
+
       if (ok && k_act == 0 && p.tp.world > 0) {
         // empty active set on this rank: its partial of the elements this CTA owns is zero
         const int rz = et & 127;
         for (int c0 = 0; c0 < width; c0 += kTileN)
           if (c0 + rz < width && n0 + c0 + rz < p.n)
-            for (int row = rank + C * eset; row < p.batch; row += 2 * C) tp_part[(size_t)row * p.tp.ldp + n0 + c0 + rz] = 0.f;
+            for (int row = rank + C * eset; row < p.batch; row += 2 * C) tp_send(row, n0 + c0 + rz, 0.f);
       } else if (ok && k_act == 0) {
         // empty active set: the epilogue threads of the whole grid zero Y between them
         const long long total = (long long)p.batch * p.n;
@@ -446,7 +454,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 #pragma unroll
                 for (int b = 0; b < NV; ++b)
                   if (16 * CH0 + b < p.batch) {
-                    if (tp_part != nullptr) tp_part[(size_t)(16 * CH0 + b) * p.tp.ldp + col] = v[b];
+                    if (p.tp.world > 0) tp_send(16 * CH0 + b, col, v[b]);
                     else store_out16(p.y + (size_t)(16 * CH0 + b) * p.ldy + col, v[b], bf16);
                   }
               }
@@ -552,7 +560,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 #pragma unroll
             for (int e = 0; e < 4; ++e)
               if (row0 + e * C < p.batch) {
-                if (tp_part != nullptr) tp_part[(size_t)(row0 + e * C) * p.tp.ldp + col] = vals[e];
+                if (p.tp.world > 0) tp_send(row0 + e * C, col, vals[e]);
                 else store_out16(p.y + (size_t)(row0 + e * C) * p.ldy + col, vals[e], bf16);
               }
           }
@@ -562,60 +570,41 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   }
   if (p.tp.world > 0 && warp >= kEpiWarp0) {
     // ---- sum over the ranks of the box ----
-    // CTA c of every rank has produced the same rows and columns of its rank's partial.  Publish:
-    // all of this CTA's partial stores, then the call number in flag[c] (release, system scope).
-    // Collect: wait (bounded) until every peer's flag[c] has reached the call number, then add the
-    // partials in rank order and store Y.  A peer can be at most one call ahead of this rank, and
-    // it writes the other buffer then.
+    // CTA c of every rank produces the same rows and columns of its rank's partial and has sent them
+    // to all ranks.  Collect: poll (bounded) this rank's own receive buffer until the word of every
+    // source rank carries this call's number, add the partials in rank order and store Y.  A peer
+    // can be at most one call ahead of this rank, and it writes the other buffer then.
     const int et = tid - 32 * kEpiWarp0, eset = et >> 7, rz = et & 127;
-    named_bar_sync(1, kEpiThreads);
-    if (et == 0) {
-      __threadfence_system();
-      st_release_sys_u32((unsigned int*)p.tp.own + blockIdx.x, tp_epoch);
-      ((unsigned int*)(p.tp.own + 4 * kTpMaxCtas))[blockIdx.x] = tp_epoch;
-    }
-    if (warp == kEpiWarp0) {
-      const unsigned int* peer_flag = nullptr;
+    const unsigned long long* recv = (const unsigned long long*)p.tp.own + (size_t)kTpHeaderBytes / 8 +
+                                     (size_t)(tp_epoch & 1u) * (size_t)p.tp.world * (size_t)p.tp.src_words;
+    const long long t_start = clock64();
+    bool good = hdr->abort_flag == 0;
+    for (int c0 = 0; c0 < width && good; c0 += kTileN) {
+      const int col = n0 + c0 + rz;
+      if (c0 + rz < width && col < p.n)
+        for (int row = rank + C * eset; row < p.batch && good; row += 2 * C) {
+          const size_t off = (size_t)row * (size_t)p.tp.ldp + (size_t)col;
+          float sum = 0.f;
 #pragma unroll
-      for (int q = 0; q < kTpMaxRanks; ++q)
-        if (q == lane && q < p.tp.world && q != p.tp.rank) peer_flag = (const unsigned int*)p.tp.area[q] + blockIdx.x;
-      bool ready = true;
-      if (peer_flag != nullptr) {
-        const long long t_start = clock64();
-        // signed distance: the counters may wrap
-        while ((int)(ld_acquire_sys_u32(peer_flag) - tp_epoch) < 0) {
-          if (clock64() - t_start > kWaitCycles) {
-            ready = false;
-            break;
-          }
-          __nanosleep(64);
+          for (int q = 0; q < kTpMaxRanks; ++q)
+            if (q < p.tp.world) {   // rank order
+              unsigned long long word = ld_relaxed_sys_u64(recv + (size_t)q * (size_t)p.tp.src_words + off);
+              while ((unsigned int)(word >> 32) != tp_epoch) {
+                if (clock64() - t_start > kWaitCycles) {
+                  good = false;
+                  break;
+                }
+                __nanosleep(32);
+                word = ld_relaxed_sys_u64(recv + (size_t)q * (size_t)p.tp.src_words + off);
+              }
+              sum += __uint_as_float((unsigned int)word);
+            }
+          if (good) store_out16(p.y + (size_t)row * p.ldy + col, sum, bf16);
         }
-      }
-      ready = __all_sync(0xffffffffu, ready);
-      if (lane == 0) {
-        hdr->tp_ready = (ready && hdr->abort_flag == 0) ? 1 : 0;
-        if (!ready) atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
-      }
     }
-    named_bar_sync(1, kEpiThreads);
-    if (hdr->tp_ready != 0) {
-      const size_t buf_off = (size_t)kTpHeaderBytes / sizeof(float) + (size_t)(tp_epoch & 1u) * (size_t)p.tp.buf_floats;
-      for (int c0 = 0; c0 < width; c0 += kTileN) {
-        const int col = n0 + c0 + rz;
-        if (c0 + rz < width && col < p.n)
-          for (int row = rank + C * eset; row < p.batch; row += 2 * C) {
-            const size_t off = buf_off + (size_t)row * p.tp.ldp + col;
-            float part[kTpMaxRanks];
-#pragma unroll
-            for (int q = 0; q < kTpMaxRanks; ++q)
-              part[q] = (q < p.tp.world) ? ld_relaxed_sys_f32((const float*)p.tp.area[q] + off) : 0.f;
-            float sum = 0.f;
-#pragma unroll
-            for (int q = 0; q < kTpMaxRanks; ++q) sum += part[q];   // rank order
-            store_out16(p.y + (size_t)row * p.ldy + col, sum, bf16);
-          }
-      }
-    }
+    if (!good && hdr->abort_flag == 0) atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
+    // the call counter of this CTA index advances whatever happened, so that the ranks stay in step
+    if (et == 0) ((unsigned int*)p.tp.own)[blockIdx.x] = tp_epoch;
   }
   if (tid == 32 * kEpiWarp0) BAS_TRACE_SET(12, BAS_TRACE_CLOCK() - hdr->t0);    // cluster combine done
   if (hdr->abort_flag != 0 && warp < P && lane == 0) {
