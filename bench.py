@@ -460,18 +460,35 @@ def run_gpu(args) -> None:
         h = ctypes.c_void_p()
         abi.check(abi.lib.bas_linear_create(ctypes.byref(h), w_host.ctypes.data, N_OUT, K_IN, 64), "bas_linear_create")
         handles.append(h)
-    x_host = {bb: O.make_activations(bb, K_IN, seed=1000 + bb, dist="laplace") for bb in BATCHES}
-    y_host = {bb: np.empty((bb, N_OUT), np.float16) for bb in BATCHES}
+    # the step's inputs and results live in page-locked host memory, as a serving host keeps them
+    pinned = {}
+
+    def pinned_array(key, shape, dtype):
+        t = torch.empty(shape, dtype=dtype, pin_memory=True)
+        pinned[key] = t                 # keeps the allocation alive
+        return t.numpy()
+
+    x_host, y_host = {}, {}
+    for bb in BATCHES:
+        x_host[bb] = pinned_array(("x", bb), (bb, K_IN), torch.float16)
+        x_host[bb][...] = O.make_activations(bb, K_IN, seed=1000 + bb, dist="laplace")
+        y_host[bb] = pinned_array(("y", bb), (bb, N_OUT), torch.float16)
     ids_host = {bb: np.full(NB, -1, np.int32) for bb in BATCHES}
     call = {"i": 0}
 
     def e2e_step():
+        # the three calls of a step are independent: submit them on three handles (own streams, so the
+        # copies of one overlap the kernels of another), then collect the three results
+        used = []
         for bb in BATCHES:
             h = handles[call["i"] % E2E_COPIES]
             call["i"] += 1
-            abi.check(abi.lib.bas_linear_forward_host(h, x_host[bb].ctypes.data, bb, N_KEEP[bb], abi.SCORE_NORM,
-                                                      y_host[bb].ctypes.data, ids_host[bb].ctypes.data),
-                      "bas_linear_forward_host")
+            abi.check(abi.lib.bas_linear_submit_host(h, x_host[bb].ctypes.data, bb, N_KEEP[bb], abi.SCORE_NORM,
+                                                     y_host[bb].ctypes.data, ids_host[bb].ctypes.data),
+                      "bas_linear_submit_host")
+            used.append(h)
+        for h in used:
+            abi.check(abi.lib.bas_linear_wait(h), "bas_linear_wait")
 
     for _ in range(5):
         e2e_step()
@@ -506,7 +523,7 @@ def run_gpu(args) -> None:
            "h2d_bytes_per_step": sum(bb * K_IN * 2 for bb in BATCHES),
            "d2h_bytes_per_step": sum(bb * N_OUT * 2 + N_KEEP[bb] * 4 for bb in BATCHES) + 3 * 4,
            "ms_per_step": e2e_dt * 1e3, "steps": e2e_steps,
-           "api": "bas_linear_forward_host: H2D X, device-side top-k selection, GEMM, D2H Y, per call"}
+           "api": "bas_linear_submit_host x3 + bas_linear_wait x3 per step: H2D X from pinned memory, device-side top-k selection, GEMM, D2H Y and ids, per call"}
 
     clocks = sampler.stop()
 

@@ -77,7 +77,8 @@ BAS_API int bas_pack_weight(const void* w_dev, int n, int k, int64_t ldw, void* 
  * The active set is given EITHER as an id list (ids_dev, k_host entries; if count_dev is non-null
  * the kernel reads the number of entries from device memory instead, k_host being an upper bound)
  * OR as a byte map (bitmap_dev[K/64], non-zero = active), the form the bitmap kernels consume
- * (kernels/...min_runtime.py:847).  ids may be unsorted; they must be distinct.  An id outside
+ * (kernels/...min_runtime.py:847); k_host is then only a hint of how many blocks are active
+ * (0 = unknown), used to size the grid.  ids may be unsorted; they must be distinct.  An id outside
  * [0, ceil(K/64)) is skipped and flagged in the device status word.  An empty set writes zeros
  * (kernels/...min_runtime.py:1252-1254).
  *
@@ -86,7 +87,7 @@ BAS_API int bas_pack_weight(const void* w_dev, int n, int k, int64_t ldw, void* 
  *   ws_dev  workspace of at least bas_gemm_workspace_bytes(batch, n) bytes, zero-filled once with
  *           bas_workspace_init().  It holds the device status word; the kernels keep all partial
  *           sums on chip, so calls may share it freely.
- * Batches of 1..8 rows run the CUDA-core split-K kernel, 9..64 rows the tcgen05 kernel. */
+ * Every batch size runs the tcgen05 kernel unless bas_gemm_ex is asked for the CUDA-core one. */
 BAS_API size_t bas_gemm_workspace_bytes(int batch, int n);
 BAS_API int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream);
 BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
@@ -105,7 +106,9 @@ BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, con
  *   BAS_GEMM_BF16  X, the packed weight and Y hold bfloat16 instead of fp16 (the reference's kernels
  *             take either, kernels/...min_runtime.py:21); tcgen05 kernel only.
  *   bits 12-14 copy/MMA warp pairs of the tcgen05 kernel: 0 = chosen by the ring size, else 2, 3
- *             or 4 (a tuning knob; results differ only in fp32 summation order). */
+ *             or 4 (a tuning knob; results differ only in fp32 summation order).
+ *   bits 16-23 upper bound on the CTAs of the tcgen05 kernel: 0 = chosen by the amount of work
+ *             (a tuning knob). */
 #define BAS_GEMM_IDS_STABLE 16
 #define BAS_GEMM_BF16 32
 BAS_API int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
@@ -213,6 +216,15 @@ BAS_API int bas_linear_forward_host(bas_linear* h, const void* x_host, int batch
                             void* y_host, int32_t* ids_host_out);
 BAS_API int bas_linear_forward_host_ids(bas_linear* h, const void* x_host, int batch, const int32_t* ids_host,
                                 int n_ids, void* y_host);
+/* bas_linear_forward_host in two halves: submit enqueues the copies and kernels on the handle's own
+ * stream and returns; wait blocks until they are done and fills y_host / ids_host_out.  One forward
+ * may be in flight per handle; forwards submitted on different handles overlap (copies of one with
+ * kernels of another).  x_host must stay untouched, and y_host / ids_host_out unread, until wait
+ * returns.  Buffers that are page-locked (cudaMallocHost, cudaHostRegister) are copied from and to
+ * directly; others go through the handle's pinned staging buffers. */
+BAS_API int bas_linear_submit_host(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind,
+                                   void* y_host, int32_t* ids_host_out);
+BAS_API int bas_linear_wait(bas_linear* h);
 BAS_API void bas_linear_destroy(bas_linear* h);
 
 #ifdef __cplusplus

@@ -57,7 +57,7 @@ def main() -> None:
         stack.step()
         stack.step()
         torch.cuda.synchronize()
-        outs[mode] = [o.float().clone() for lin, _, _, o in stack.items if lin.spec.parallel == "row"]
+        outs[mode] = [o.float().clone() for lin, _, _, o, _ in stack.items if lin.spec.parallel == "row"]
         if ops.read_status(dev) != 0:
             failures.append(("stack status", mode))
         stack.close()

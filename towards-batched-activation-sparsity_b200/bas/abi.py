@@ -66,6 +66,8 @@ _SIGNATURES = {
     "bas_linear_create": (_i, [C.POINTER(_vp), _vp, _i, _i, _i]),
     "bas_linear_forward_host": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "bas_linear_forward_host_ids": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
+    "bas_linear_submit_host": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
+    "bas_linear_wait": (_i, [_vp]),
     "bas_linear_destroy": (None, [_vp]),
 }
 for _name, (_res, _args) in _SIGNATURES.items():

@@ -131,15 +131,16 @@ def read_status(device: Optional[torch.device] = None) -> int:
 def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: Optional[torch.Tensor] = None,
          count: Optional[torch.Tensor] = None, k_host: Optional[int] = None,
          bitmap: Optional[torch.Tensor] = None, family: int = 0, ids_stable: bool = False,
-         cluster: int = 0, pairs: int = 0, tp=None) -> None:
+         cluster: int = 0, pairs: int = 0, tp=None, max_ctas: int = 0) -> None:
     """out2d[B, N] = x2d[B, K] restricted to the active blocks, times W^T.
 
     ``ids`` int32 device list (``count``: optional int32[1] device-side length, ``k_host`` an upper
-    bound) or ``bitmap`` uint8[K/64].  ``family``: 0 by batch size, 1 CUDA-core, 2 tcgen05.
+    bound) or ``bitmap`` uint8[K/64] (``k_host`` then optionally tells how many blocks to expect).  ``family``: 0 by batch size, 1 CUDA-core, 2 tcgen05.
     ``ids_stable``: promise that ``ids`` is not written by the kernel launched just before this
     call on the stream; the kernel then streams weights while that kernel is still finishing.
     ``cluster``: 0 lets the library choose; 1, 2 or 4 forces the tcgen05 kernel's cluster size.
     ``pairs``: 0 lets the library choose; 2, 3 or 4 forces its number of copy/MMA warp pairs.
+    ``max_ctas``: 0 lets the library choose; else an upper bound (up to 255) on the kernel's CTAs.
     x, out (and the weight that was packed) are all float16 or all bfloat16.
     ``tp``: an :class:`ExchangeGroup`; x and packed are then this rank's K-shard and out receives
     the sum over the group's ranks, formed inside the kernel (every rank must make the same call).
@@ -165,7 +166,7 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
     else:
         if bitmap.dtype != torch.uint8 or not bitmap.is_contiguous():
             raise TypeError("bitmap must be a contiguous uint8 tensor")
-        k_host = 0
+        k_host = int(k_host) if k_host is not None else 0      # with a byte map: a hint, 0 = unknown
     if x2d.data_ptr() % 16 or x2d.stride(0) % 8 or k % 8:
         raise ValueError("x rows must be 16-byte aligned and K a multiple of 8")
     with torch.cuda.device(x2d.device):
@@ -181,7 +182,7 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
                 count.data_ptr() if count is not None else None, int(k_host),
                 bitmap.data_ptr() if bitmap is not None else None,
                 bsz, k, n, ys.data_ptr(), ys.stride(0), ws.data_ptr(), ws.numel(),
-                int(family) | (IDS_STABLE if ids_stable else 0) | bf16 | (int(cluster) << 8) | (int(pairs) << 12), stream),
+                int(family) | (IDS_STABLE if ids_stable else 0) | bf16 | (int(cluster) << 8) | (int(pairs) << 12) | (int(max_ctas) << 16), stream),
                 "bas_gemm")
 
 

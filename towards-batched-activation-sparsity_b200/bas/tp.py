@@ -99,7 +99,7 @@ class ShardedLinear:
         self.n_local = shard.shape[0]
         self.packed = ops.pack_weight(shard.contiguous()) if self.n_local and self.k_local else None
 
-    def forward(self, x2d, bitmap, out2d, ids_stable: bool = True, exchange=None):
+    def forward(self, x2d, bitmap, out2d, ids_stable: bool = True, exchange=None, n_keep: int = 0):
         """x2d is the replicated [B, K] activation, bitmap the replicated uint8[K/64] mask.  Writes
         this rank's output slice (column-parallel) or partial sum (row-parallel) into out2d; with an
         ``exchange`` group a row-parallel linear writes the sum over all ranks instead (formed inside
@@ -113,7 +113,10 @@ class ShardedLinear:
             return
         row = self.spec.parallel == "row"
         xs = x2d[:, self.b0 * BLOCK_K: self.b0 * BLOCK_K + self.k_local] if row else x2d
-        ops.gemm(xs, self.packed, out2d, bitmap=bitmap[self.b0:self.b1], ids_stable=ids_stable,
+        # n_keep: active blocks of the whole mask; a K-shard expects its share of them
+        nb_all = bitmap.numel()
+        hint = max(1, (int(n_keep) * (self.b1 - self.b0) + nb_all - 1) // nb_all) if n_keep else 0
+        ops.gemm(xs, self.packed, out2d, bitmap=bitmap[self.b0:self.b1], k_host=hint, ids_stable=ids_stable,
                  tp=exchange if row else None)
 
 
@@ -184,7 +187,7 @@ class DecodeLinearStack:
                     lin = ShardedLinear(spec, w, world, rank)
                 del w
                 out = torch.zeros(batch, lin.n_local, dtype=torch.float16, device=device)
-                self.items.append((lin, x, bitmap, out))
+                self.items.append((lin, x, bitmap, out, n_keep))
                 self.active_bytes += n_keep * BLOCK_K * spec.n * 2
         torch.cuda.synchronize(device)
 
@@ -197,7 +200,7 @@ class DecodeLinearStack:
     def step(self) -> None:
         import torch.distributed as dist
 
-        for lin, x, bitmap, out in self.items:
-            lin.forward(x, bitmap, out, exchange=self.exchange)
+        for lin, x, bitmap, out, n_keep in self.items:
+            lin.forward(x, bitmap, out, exchange=self.exchange, n_keep=n_keep)
             if lin.spec.parallel == "row" and self.world > 1 and self.exchange is None:
                 dist.all_reduce(out, group=self.group)

@@ -213,12 +213,15 @@ static int gemm_impl(const bas_tp* tp, const void* x_dev, int64_t ldx, const voi
   const int nb = (k + kBlockK - 1) / kBlockK;
   if (nb > BAS_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
   if (bitmap_dev == nullptr && ids_dev == nullptr && k_host > 0) return BAS_ERR_INVALID_ARGUMENT;
-  if (bitmap_dev == nullptr && k_host > nb) return BAS_ERR_INVALID_ARGUMENT;  // ids are distinct
+  if (k_host > nb) {
+    if (bitmap_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;  // ids are distinct
+    k_host = nb;                                                 // with a byte map k_host is only a hint
+  }
   // bulk copies: 16-byte aligned rows whose valid length is a multiple of 16 bytes
   if (!aligned16(x_dev) || !aligned16(packed_dev) || (ldx & 7) != 0 || (k & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
   if (ws_dev == nullptr || ws_bytes < bas_gemm_workspace_bytes(batch, n)) return BAS_ERR_WORKSPACE;
   const int family = flags & 3;
-  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_BF16 | 0x700 | 0x7000)) != 0) return BAS_ERR_INVALID_ARGUMENT;
+  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_BF16 | 0x700 | 0x7000 | 0xff0000)) != 0) return BAS_ERR_INVALID_ARGUMENT;
 
   DeviceInfo di;
   int st = device_info(&di);
@@ -403,6 +406,11 @@ struct bas_linear {
   void* y_pin = nullptr;
   int32_t* ids_pin = nullptr;
   long long ldx = 0;
+  // the forward in flight (bas_linear_submit_host .. bas_linear_wait)
+  bool pending = false, y_direct = false;
+  void* pend_y = nullptr;
+  int32_t* pend_ids = nullptr;
+  int pend_batch = 0, pend_k = 0;
 };
 
 static void linear_free(bas_linear* h) {
@@ -464,15 +472,34 @@ int bas_linear_create(bas_linear** out, const void* w_host, int n, int k, int ma
   return BAS_OK;
 }
 
-static int linear_forward(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind,
-                          const int32_t* ids_host, int n_ids, void* y_host, int32_t* ids_host_out) {
+// Host memory that the CUDA driver knows as page-locked (cudaMallocHost / cudaHostRegister) can be
+// the source or target of an asynchronous copy itself; anything else goes through the handle's own
+// pinned staging buffers.
+static bool is_pinned_host(const void* ptr) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  return attr.type == cudaMemoryTypeHost;
+}
+
+// Enqueue one forward on the handle's stream: X host -> device, selection (or the caller's ids),
+// contraction, Y (and ids, status word) device -> host.  Nothing is waited for.
+static int linear_submit(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind,
+                         const int32_t* ids_host, int n_ids, void* y_host, int32_t* ids_host_out) {
   if (h == nullptr || x_host == nullptr || y_host == nullptr) return BAS_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || batch > h->max_batch) return BAS_ERR_INVALID_ARGUMENT;
+  if (h->pending) return BAS_ERR_INVALID_ARGUMENT;   // one forward in flight per handle
   cudaStream_t s = h->stream;
-  // host -> pinned -> device (rows padded to a multiple of 8 channels; the padding stays zero)
+  // host (-> pinned) -> device (rows padded to a multiple of 8 channels; the padding stays zero)
   const size_t row = (size_t)h->k * 2;
-  std::memcpy(h->x_pin, x_host, row * batch);
-  cudaError_t e = cudaMemcpy2DAsync(h->x_dev, (size_t)h->ldx * 2, h->x_pin, row, row, batch, cudaMemcpyHostToDevice, s);
+  const void* x_src = x_host;
+  if (!is_pinned_host(x_host)) {
+    std::memcpy(h->x_pin, x_host, row * batch);
+    x_src = h->x_pin;
+  }
+  cudaError_t e = cudaMemcpy2DAsync(h->x_dev, (size_t)h->ldx * 2, x_src, row, row, batch, cudaMemcpyHostToDevice, s);
   if (e != cudaSuccess) return cuda_fail(e);
   int st;
   int k_host;
@@ -495,7 +522,8 @@ static int linear_forward(bas_linear* h, const void* x_host, int batch, int n_ke
   st = bas_gemm(h->x_dev, h->ldx, h->packed, h->ids_dev, count_dev, k_host, nullptr, batch, (int)h->ldx, h->n, h->y_dev,
                 h->n, h->gemm_ws, h->gemm_ws_bytes, s);
   if (st != BAS_OK) return st;
-  e = cudaMemcpyAsync(h->y_pin, h->y_dev, (size_t)batch * h->n * 2, cudaMemcpyDeviceToHost, s);
+  h->y_direct = is_pinned_host(y_host);
+  e = cudaMemcpyAsync(h->y_direct ? y_host : h->y_pin, h->y_dev, (size_t)batch * h->n * 2, cudaMemcpyDeviceToHost, s);
   if (e != cudaSuccess) return cuda_fail(e);
   if (ids_host_out != nullptr && k_host > 0) {
     e = cudaMemcpyAsync(h->ids_pin, h->ids_dev, sizeof(int32_t) * k_host, cudaMemcpyDeviceToHost, s);
@@ -504,16 +532,43 @@ static int linear_forward(bas_linear* h, const void* x_host, int batch, int n_ke
   unsigned int* flag_pin = (unsigned int*)(h->ids_pin + h->nb);
   e = cudaMemcpyAsync(flag_pin, h->gemm_ws, sizeof(unsigned int), cudaMemcpyDeviceToHost, s);
   if (e != cudaSuccess) return cuda_fail(e);
-  e = cudaStreamSynchronize(s);
+  h->pending = true;
+  h->pend_y = y_host;
+  h->pend_ids = ids_host_out;
+  h->pend_batch = batch;
+  h->pend_k = k_host;
+  return BAS_OK;
+}
+
+// Wait for the handle's forward in flight and hand its results to the caller's buffers.
+static int linear_wait(bas_linear* h) {
+  if (h == nullptr || !h->pending) return BAS_ERR_INVALID_ARGUMENT;
+  h->pending = false;
+  cudaError_t e = cudaStreamSynchronize(h->stream);
   if (e != cudaSuccess) return cuda_fail(e);
-  std::memcpy(y_host, h->y_pin, (size_t)batch * h->n * 2);
-  if (ids_host_out != nullptr && k_host > 0) std::memcpy(ids_host_out, h->ids_pin, sizeof(int32_t) * k_host);
+  if (!h->y_direct) std::memcpy(h->pend_y, h->y_pin, (size_t)h->pend_batch * h->n * 2);
+  if (h->pend_ids != nullptr && h->pend_k > 0) std::memcpy(h->pend_ids, h->ids_pin, sizeof(int32_t) * h->pend_k);
+  unsigned int* flag_pin = (unsigned int*)(h->ids_pin + h->nb);
   if (*flag_pin != 0) {
-    cudaMemsetAsync(h->gemm_ws, 0, sizeof(unsigned int), s);
+    cudaMemsetAsync(h->gemm_ws, 0, sizeof(unsigned int), h->stream);
     return BAS_ERR_DEVICE_FLAG;
   }
   return BAS_OK;
 }
+
+static int linear_forward(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind,
+                          const int32_t* ids_host, int n_ids, void* y_host, int32_t* ids_host_out) {
+  const int st = linear_submit(h, x_host, batch, n_keep, score_kind, ids_host, n_ids, y_host, ids_host_out);
+  return st != BAS_OK ? st : linear_wait(h);
+}
+
+int bas_linear_submit_host(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind, void* y_host,
+                           int32_t* ids_host_out) {
+  if (h == nullptr || n_keep < 1 || n_keep > h->k / kBlockK) return BAS_ERR_INVALID_ARGUMENT;
+  return linear_submit(h, x_host, batch, n_keep, score_kind, nullptr, -1, y_host, ids_host_out);
+}
+
+int bas_linear_wait(bas_linear* h) { return linear_wait(h); }
 
 int bas_linear_forward_host(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind, void* y_host,
                             int32_t* ids_host_out) {

@@ -8,15 +8,15 @@ namespace bas {
 // Exchange area of a row-parallel contraction whose sum over the ranks of one box is formed inside
 // the kernel.  Every rank owns one area (device memory mapped into its peers); all areas have the
 // same layout:
-//   [0, 4 * kTpMaxCtas)      private to the owner: number of exchange calls CTA c has taken part in
+//   [0, kTpHeaderBytes)      private to the owner: word 0 = exchange calls completed, word 1 = CTAs
+//                            of the current call that have finished
 //   [kTpHeaderBytes, ...)    two receive buffers, used alternately; each holds, per source rank, a
 //                            [rows][ldp] array of 8-byte words {fp32 partial, call number}
 // A rank writes its partial straight into every rank's receive buffer (its own included) with single
 // 64-bit stores: a word whose upper half equals the current call number is valid, so no flag, fence
 // or second round trip is needed - the reader polls its own memory.
 constexpr int kTpMaxRanks = 8;
-constexpr int kTpMaxCtas = 1024;
-constexpr int kTpHeaderBytes = 4 * kTpMaxCtas;
+constexpr int kTpHeaderBytes = 256;
 struct TpExchange {
   int world;                           // 0: no exchange, the kernel stores Y itself
   int rank;

@@ -54,6 +54,16 @@ __device__ __forceinline__ int red_swizzle(int nbi, int r) {
   return nbi == 32 ? (r & 7) : nbi == 16 ? ((r >> 1) & 3) : nbi == 8 ? ((r >> 2) & 1) : 0;
 }
 
+// This rank's partial of one output element, sent to every rank of a tensor-parallel group (its own
+// included) as one 64-bit word {value, call number}.  Kept out of line: the exchange is the rare
+// path and must not bloat the epilogue's unrolled store loops.
+__device__ __noinline__ void tp_send_word(const TpExchange& tp, unsigned int epoch, size_t slot, int row, int col, float v) {
+  const unsigned long long word = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
+  const size_t off = slot + (size_t)row * (size_t)tp.ldp + (size_t)col;
+#pragma unroll 1
+  for (int q = 0; q < tp.world; ++q) st_relaxed_sys_u64((unsigned long long*)tp.area[q] + off, word);
+}
+
 struct UmmaSmemHeader {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
@@ -73,7 +83,7 @@ inline size_t umma_fixed_smem(int nb) {
 
 template <int BPAD>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
-    umma_colsplit_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
+    umma_colsplit_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
   const bool bf16 = (p.flags & kFlagBf16) != 0;
   // operand formats: bits 7-9 (A) and 10-12 (B) of the instruction descriptor, 0 = fp16, 1 = bf16
   const uint32_t kIdesc = umma_idesc_f16(128, BPAD) | (bf16 ? ((1u << 7) | (1u << 10)) : 0u);
@@ -160,14 +170,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   // exchange area and the partial buffer it selects.
   unsigned int tp_epoch = 0;
   size_t tp_slot = 0;       // word offset, inside any rank's area, of this rank's array in the current receive buffer
-  // this rank's partial of one output element, sent to every rank of the group (its own included)
-  auto tp_send = [&](int row, int col, float v) {
-    const unsigned long long word = ((unsigned long long)tp_epoch << 32) | (unsigned long long)__float_as_uint(v);
-    const size_t off = tp_slot + (size_t)row * (size_t)p.tp.ldp + (size_t)col;
-#pragma unroll
-    for (int q = 0; q < kTpMaxRanks; ++q)
-      if (q < p.tp.world) st_relaxed_sys_u64((unsigned long long*)p.tp.area[q] + off, word);
-  };
+  auto tp_send = [&](int row, int col, float v) { tp_send_word(p.tp, tp_epoch, tp_slot, row, col, v); };
   int armed_next = warp, armed_cnt = 0;   // producer warps: next group to arm, groups armed so far
 
   const int P = p.issuers;
@@ -373,9 +376,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       constexpr int kChunks0 = (kChunks + 1) / 2;   // set 0's chunks; set 1 takes the rest
       if (early_ids) pdl_wait();            // before the first write to Y
       if (p.tp.world > 0) {
-        // The counter is private to CTAs of this index; the previous call's CTA wrote it before the
-        // wait above (or warp 0's, which the id barrier orders before this point) returned.
-        tp_epoch = ((const unsigned int*)p.tp.own)[blockIdx.x] + 1u;
+        // The rank's call counter: advanced by the last CTA to finish the previous call, i.e. before
+        // the wait above (or warp 0's, which the id barrier orders before this point) returned.
+        tp_epoch = __ldcg((const unsigned int*)p.tp.own) + 1u;
         tp_slot = (size_t)kTpHeaderBytes / 8 +
                   ((size_t)(tp_epoch & 1u) * (size_t)p.tp.world + (size_t)p.tp.rank) * (size_t)p.tp.src_words;
       }
@@ -451,12 +454,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             if (C == 1) {
               const int col = n0 + sub * TW + rr;
               if (rr < wsub && col < p.n) {
+                if (p.tp.world > 0) {
 #pragma unroll
-                for (int b = 0; b < NV; ++b)
-                  if (16 * CH0 + b < p.batch) {
-                    if (p.tp.world > 0) tp_send(16 * CH0 + b, col, v[b]);
-                    else store_out16(p.y + (size_t)(16 * CH0 + b) * p.ldy + col, v[b], bf16);
-                  }
+                  for (int b = 0; b < NV; ++b)
+                    if (16 * CH0 + b < p.batch) tp_send(16 * CH0 + b, col, v[b]);
+                } else {
+#pragma unroll
+                  for (int b = 0; b < NV; ++b)
+                    if (16 * CH0 + b < p.batch) store_out16(p.y + (size_t)(16 * CH0 + b) * p.ldy + col, v[b], bf16);
+                }
               }
             } else {
               // Cluster mode (one pass per CTA): batch row b is finished by rank b % C.  Push this
@@ -584,27 +590,40 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       if (c0 + rz < width && col < p.n)
         for (int row = rank + C * eset; row < p.batch && good; row += 2 * C) {
           const size_t off = (size_t)row * (size_t)p.tp.ldp + (size_t)col;
+          unsigned long long words[kTpMaxRanks];
+#pragma unroll
+          for (int q = 0; q < kTpMaxRanks; ++q)   // all sources at once: their latencies overlap
+            words[q] = (q < p.tp.world) ? ld_relaxed_sys_u64(recv + (size_t)q * (size_t)p.tp.src_words + off) : 0ull;
           float sum = 0.f;
 #pragma unroll
           for (int q = 0; q < kTpMaxRanks; ++q)
             if (q < p.tp.world) {   // rank order
-              unsigned long long word = ld_relaxed_sys_u64(recv + (size_t)q * (size_t)p.tp.src_words + off);
-              while ((unsigned int)(word >> 32) != tp_epoch) {
+              while ((unsigned int)(words[q] >> 32) != tp_epoch) {
                 if (clock64() - t_start > kWaitCycles) {
                   good = false;
                   break;
                 }
                 __nanosleep(32);
-                word = ld_relaxed_sys_u64(recv + (size_t)q * (size_t)p.tp.src_words + off);
+                words[q] = ld_relaxed_sys_u64(recv + (size_t)q * (size_t)p.tp.src_words + off);
               }
-              sum += __uint_as_float((unsigned int)word);
+              sum += __uint_as_float((unsigned int)words[q]);
             }
           if (good) store_out16(p.y + (size_t)row * p.ldy + col, sum, bf16);
         }
     }
     if (!good && hdr->abort_flag == 0) atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
-    // the call counter of this CTA index advances whatever happened, so that the ranks stay in step
-    if (et == 0) ((unsigned int*)p.tp.own)[blockIdx.x] = tp_epoch;
+    // The rank's call counter advances whatever happened, so that the ranks stay in step: the last CTA
+    // to get here does it (every CTA has read the counter by then; the next call reads it only after
+    // this grid has completed).
+    if (et == 0) {
+      unsigned int* ctr = (unsigned int*)p.tp.own;
+      __threadfence();
+      if (atomicAdd(ctr + 1, 1u) == gridDim.x - 1) {
+        ctr[1] = 0u;
+        ctr[0] = tp_epoch;
+        __threadfence();
+      }
+    }
   }
   if (tid == 32 * kEpiWarp0) BAS_TRACE_SET(12, BAS_TRACE_CLOCK() - hdr->t0);    // cluster combine done
   if (hdr->abort_flag != 0 && warp < P && lane == 0) {
@@ -749,20 +768,36 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   const int units = p.npad / 8;
   const size_t fixed = umma_fixed_smem(p.nb);
 
-  // Work split (measured): a cluster of 4 CTAs per column range of up to 128 columns when the
-  // output is narrow enough for that (up to 4224 columns on a 148-SM part), for batches of up to 32
-  // rows else a cluster of 2, else one CTA per range walking 128-column passes.  A cluster finishes
-  // its range in one pass.  Passes of 256 columns were tried and lost to these at every width.
+  // Work split (measured).  Bringing up a CTA of this kernel costs the launch about 25 ns, one after
+  // the other, and an SM can take in about 100 GB/s: small problems finish sooner on few CTAs, and
+  // only tens of megabytes want every SM.  The grid is sized for about 96 KiB of weights per CTA.
+  // Shape: a cluster of 4 CTAs per column range of up to 128 columns (the cluster splits the active
+  // blocks and finishes its range in one pass) when that does not overshoot the CTA budget by more
+  // than half - always, for batches above 32 rows, whose activation traffic a cluster divides by
+  // four - else a cluster of 2 (batch <= 32), else one CTA per range walking 128-column passes.
   const int forced = (p.flags >> 8) & 7;
-  int cluster = 1, ranges = sm_count < units ? sm_count : units;
+  const int cta_cap = ((p.flags >> 16) & 0xff) != 0 ? ((p.flags >> 16) & 0xff) : sm_count;   // tuning knob
+  // active blocks expected: the list length, or with a byte map the caller's hint (else half of all)
+  const int k_est = p.k_host > 0 ? p.k_host : (p.nb + 1) / 2;
+  const double bytes = (double)k_est * kBlockK * 2.0 * (double)p.n;
+  int budget = (int)(bytes / (96.0 * 1024.0)) + 1;
+  if (budget < 16) budget = 16;
+  if (budget > cta_cap) budget = cta_cap;
+  const int r_min = (units + kTileN / 8 - 1) / (kTileN / 8);   // fewest ranges of at most 128 columns
+  // without a cluster: one pass per CTA where the CTA cap allows it (a second pass re-reads X)
+  int cluster = 1, ranges = budget > r_min ? budget : (r_min < cta_cap ? r_min : cta_cap);
+  if (ranges > units) ranges = units;
   for (int c = 4; c >= 2 && forced != 1; c -= 2) {
     if (forced != 0 && c != forced) continue;
     if (forced == 0 && c == 2 && BPAD > 32) continue;
-    const int resident = max_resident_clusters<BPAD>(c, kSmemBudget, sm_count);
-    const int r = resident < units ? resident : units;
-    if (r < 1) continue;
-    if (((units + r - 1) / r) * 8 > kTileN) continue;   // the widest range must fit one pass
-    if (r * c < (sm_count * 3) / 4) continue;           // too few SMs would be busy
+    int resident = max_resident_clusters<BPAD>(c, kSmemBudget, sm_count);
+    if (resident > cta_cap / c) resident = cta_cap / c;
+    if (resident > units) resident = units;
+    if (r_min > resident) continue;                                   // the widest range must fit one pass
+    if (forced == 0 && BPAD <= 32 && 2 * r_min * c > 3 * budget) continue;   // too many CTAs for the work
+    int r = budget / c;
+    if (r < r_min) r = r_min;
+    if (r > resident) r = resident;
     cluster = c;
     ranges = r;
     break;
@@ -813,8 +848,6 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   p.stages = slots / pairs * pairs;
   p.group = group;
   const size_t smem = fixed + red_bytes + pad + (size_t)p.stages * group * stage_bytes;
-
-  if (p.tp.world > 0 && ranges * cluster > kTpMaxCtas) return cudaErrorInvalidValue;   // one flag per CTA
 
   CUtensorMap xmap;
   cudaError_t e = get_x_tensor_map(p, BPAD, &xmap);
