@@ -81,7 +81,9 @@ inline size_t umma_fixed_smem(int nb) {
   return 1024 /*alignment slack*/ + (sizeof(UmmaSmemHeader) + 127) / 128 * 128 + umma_ids_bytes(nb) + 1024;
 }
 
-template <int BPAD>
+// TP: the row-parallel variant that exchanges partial sums with the other ranks of a box instead of
+// storing Y directly (a template parameter, so that the plain kernel carries none of that code).
+template <int BPAD, bool TP>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
     umma_colsplit_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
   const bool bf16 = (p.flags & kFlagBf16) != 0;
@@ -375,7 +377,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       constexpr int kChunks = BPAD / 16;
       constexpr int kChunks0 = (kChunks + 1) / 2;   // set 0's chunks; set 1 takes the rest
       if (early_ids) pdl_wait();            // before the first write to Y
-      if (p.tp.world > 0) {
+      if (TP) {
         // The rank's call counter: advanced by the last CTA to finish the previous call, i.e. before
         // the wait above (or warp 0's, which the id barrier orders before this point) returned.
         tp_epoch = __ldcg((const unsigned int*)p.tp.own) + 1u;
@@ -383,7 +385,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                   ((size_t)(tp_epoch & 1u) * (size_t)p.tp.world + (size_t)p.tp.rank) * (size_t)p.tp.src_words;
       }
 
-      if (ok && k_act == 0 && p.tp.world > 0) {
+      if (TP && ok && k_act == 0) {
         // empty active set on this rank: its partial of the elements this CTA owns is zero
         const int rz = et & 127;
         for (int c0 = 0; c0 < width; c0 += kTileN)
@@ -454,7 +456,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             if (C == 1) {
               const int col = n0 + sub * TW + rr;
               if (rr < wsub && col < p.n) {
-                if (p.tp.world > 0) {
+                if (TP) {
 #pragma unroll
                   for (int b = 0; b < NV; ++b)
                     if (16 * CH0 + b < p.batch) tp_send(16 * CH0 + b, col, v[b]);
@@ -566,7 +568,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 #pragma unroll
             for (int e = 0; e < 4; ++e)
               if (row0 + e * C < p.batch) {
-                if (p.tp.world > 0) tp_send(row0 + e * C, col, vals[e]);
+                if (TP) tp_send(row0 + e * C, col, vals[e]);
                 else store_out16(p.y + (size_t)(row0 + e * C) * p.ldy + col, vals[e], bf16);
               }
           }
@@ -574,7 +576,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       }
     }
   }
-  if (p.tp.world > 0 && warp >= kEpiWarp0) {
+  if (TP && warp >= kEpiWarp0) {
     // ---- sum over the ranks of the box ----
     // CTA c of every rank produces the same rows and columns of its rank's partial and has sent them
     // to all ranks.  Collect: poll (bounded) this rank's own receive buffer until the word of every
@@ -745,7 +747,7 @@ int max_resident_clusters(int cluster, size_t smem, int sm_count) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, umma_colsplit_kernel<BPAD>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, umma_colsplit_kernel<BPAD, false>, &cfg) != cudaSuccess) {
     (void)cudaGetLastError();
     n = 0;
   }
@@ -761,7 +763,9 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !attr_done[dev]) {
     cudaError_t e =
-        cudaFuncSetAttribute(umma_colsplit_kernel<BPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(umma_colsplit_kernel<BPAD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(umma_colsplit_kernel<BPAD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
@@ -853,7 +857,9 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   cudaError_t e = get_x_tensor_map(p, BPAD, &xmap);
   if (e != cudaSuccess) return e;
   count_launch();
-  return launch_with_pdl(umma_colsplit_kernel<BPAD>, ranges * cluster, kUmmaThreads, smem, cluster, stream, p, xmap);
+  if (p.tp.world > 0)
+    return launch_with_pdl(umma_colsplit_kernel<BPAD, true>, ranges * cluster, kUmmaThreads, smem, cluster, stream, p, xmap);
+  return launch_with_pdl(umma_colsplit_kernel<BPAD, false>, ranges * cluster, kUmmaThreads, smem, cluster, stream, p, xmap);
 }
 
 }  // namespace
