@@ -739,3 +739,34 @@ def test_host_buffer_operator_overlapped_submits(dev, pin):
     finally:
         for h in handles:
             L.lib.bas_linear_destroy(h)
+
+
+def test_sparse_linear_budget_mode_fixed_ids_and_dense_fallback(dev):
+    """The decode operator's other modes: energy budget with the count kept on the device, reuse of
+    a given mask, and the dense path for prefill shapes and density 1."""
+    ops = _ops()
+    b, k, n = 16, 4096, 1024
+    w = O.make_weight(n, k, seed=9)
+    tw = torch.from_numpy(w).to(dev)
+    x = O.make_activations(b, k, seed=21, dist="laplace")
+    tx = torch.from_numpy(x).to(dev)
+    energy = O.block_scores(x, O.SCORE_ENERGY)
+    for keep in (0.5, 0.9, 0.999):
+        ids = O.energy_budget_ids(energy, keep, 2)
+        y = ops.sparse_linear(tx, tw, 0.0, energy_keep=keep, min_keep=2)
+        torch.cuda.synchronize()
+        assert y.shape == (b, n)
+        assert O.max_err_ratio(y.cpu().numpy(), O.masked_gemm(x, w, ids)) <= TOL, keep
+    fixed = O.random_active_blocks(k // 64, 11, seed=4)
+    y = ops.sparse_linear(tx, tw, 0.3, fixed_active_blocks=torch.from_numpy(fixed).to(dev))
+    torch.cuda.synchronize()
+    assert O.max_err_ratio(y.cpu().numpy(), O.masked_gemm(x, w, fixed)) <= TOL
+    dense = (tx.float() @ tw.float().t()).cpu().numpy()
+    y = ops.sparse_linear(tx, tw, 1.0)
+    assert O.max_err_ratio(y.float().cpu().numpy(), dense) <= TOL
+    prefill = torch.from_numpy(O.make_activations(6, k, seed=3)).to(dev).reshape(2, 3, k)      # 3 positions: dense
+    y = ops.sparse_linear(prefill, tw, 0.3)
+    assert y.shape == (2, 3, n)
+    want = (prefill.float() @ tw.float().t()).cpu().numpy()
+    assert O.max_err_ratio(y.float().cpu().numpy(), want) <= TOL
+    assert ops.read_status(dev) == 0

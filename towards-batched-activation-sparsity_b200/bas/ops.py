@@ -318,13 +318,23 @@ def _select(x2d, mode, n_keep, score_kind, energy_keep, ids_out, count_out, bitm
 
 def sparse_linear(x: torch.Tensor, weight: torch.Tensor, density: float, *, score_kind: int = SCORE_NORM,
                   cache_prefix: str = "sparse_linear", out: Optional[torch.Tensor] = None,
-                  fixed_active_blocks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  fixed_active_blocks: Optional[torch.Tensor] = None, energy_keep: Optional[float] = None,
+                  min_keep: int = 1) -> torch.Tensor:
     """The decode-time operator of the reference's ``_sparse_linear``
     (scripts/bench_roundrobin_e2e_decode.py:179-284) as two chained launches: select, then GEMM
-    reading the id list from device memory.  x is [B, K] or [B, 1, K]."""
+    reading the id list (and its length) from device memory.  x is [B, K] or [B, 1, K].
+
+    * More than one position per sequence (prefill) or ``density >= 1`` runs the dense
+      ``F.linear``, as the reference does (:200-201).
+    * ``fixed_active_blocks``: skip the selection and use these ids (mask reuse, :209-210).
+    * ``energy_keep``: keep the shortest descending-energy prefix of blocks that reaches this
+      fraction of the total energy, at least ``min_keep`` blocks - the variable-count mode of
+      scripts/bench_alpaca_energy_budget_e2e.py:49-56, without its host synchronisation: the count
+      stays on the device and the contraction reads it there.
+    """
     x3 = x.reshape(x.shape[0], 1, x.shape[1]) if x.dim() == 2 else x
-    if x3.shape[1] != 1:
-        raise ValueError("decode only: the sequence dimension must be 1")
+    if x3.shape[1] != 1 or (energy_keep is None and fixed_active_blocks is None and float(density) >= 1.0):
+        return torch.nn.functional.linear(x, weight)
     bt, k = x3.shape[0], x3.shape[2]
     n = weight.shape[0]
     x2d = x3.reshape(bt, k)
@@ -332,11 +342,15 @@ def sparse_linear(x: torch.Tensor, weight: torch.Tensor, density: float, *, scor
     if out is None:
         out = torch.empty(bt, 1, n, device=x.device, dtype=x.dtype)
     out2d = out.view(bt, n)
+    nb = k // BLOCK_K
     if fixed_active_blocks is not None:
         ids = fixed_active_blocks.to(device=x.device, dtype=torch.int32).contiguous()
         gemm(x2d, packed, out2d, ids=ids)
+    elif energy_keep is not None:
+        ids, count = select_budget(x2d, float(energy_keep), int(min_keep))
+        gemm(x2d, packed, out2d, ids=ids, count=count, k_host=nb)
     else:
-        n_keep = n_keep_from_density(density, k // BLOCK_K)
+        n_keep = n_keep_from_density(density, nb, min_keep)
         ids, count = select_topk(x2d, n_keep, score_kind)
         gemm(x2d, packed, out2d, ids=ids, count=count, k_host=n_keep)
     return out.reshape(bt, n) if x.dim() == 2 else out

@@ -4,6 +4,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <vector>
 
 #include "bas_kernels.cuh"
 
@@ -411,6 +412,16 @@ struct bas_linear {
   void* pend_y = nullptr;
   int32_t* pend_ids = nullptr;
   int pend_batch = 0, pend_k = 0;
+  // recurring forwards, captured as CUDA graphs
+  struct FwdGraph {
+    int batch, n_keep, score_kind;
+    const void* x_src;
+    void* y_dst;
+    bool want_ids;
+    cudaGraphExec_t exec;
+    bool failed;
+  };
+  std::vector<FwdGraph> graphs;
 };
 
 static void linear_free(bas_linear* h) {
@@ -424,6 +435,8 @@ static void linear_free(bas_linear* h) {
   if (h->x_pin) cudaFreeHost(h->x_pin);
   if (h->y_pin) cudaFreeHost(h->y_pin);
   if (h->ids_pin) cudaFreeHost(h->ids_pin);
+  for (auto& g : h->graphs)
+    if (g.exec != nullptr) cudaGraphExecDestroy(g.exec);
   if (h->stream) cudaStreamDestroy(h->stream);
   delete h;
 }
@@ -484,6 +497,79 @@ static bool is_pinned_host(const void* ptr) {
   return attr.type == cudaMemoryTypeHost;
 }
 
+// The stream work of one forward with device-side selection: X host -> device, selection,
+// contraction, Y, ids and the status word device -> host.  Nothing is waited for.
+static int linear_enqueue_selected(bas_linear* h, const void* x_src, int batch, int n_keep, int score_kind, void* y_dst,
+                                   bool want_ids) {
+  cudaStream_t s = h->stream;
+  const size_t row = (size_t)h->k * 2;
+  cudaError_t e = cudaMemcpy2DAsync(h->x_dev, (size_t)h->ldx * 2, x_src, row, row, batch, cudaMemcpyHostToDevice, s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  int st = bas_select_topk(h->x_dev, h->ldx, batch, h->k, n_keep, score_kind, h->ids_dev, h->ids_dev + h->nb, nullptr,
+                           nullptr, h->sel_ws, h->sel_ws_bytes, s);
+  if (st != BAS_OK) return st;
+  st = bas_gemm(h->x_dev, h->ldx, h->packed, h->ids_dev, h->ids_dev + h->nb, n_keep, nullptr, batch, (int)h->ldx, h->n,
+                h->y_dev, h->n, h->gemm_ws, h->gemm_ws_bytes, s);
+  if (st != BAS_OK) return st;
+  e = cudaMemcpyAsync(y_dst, h->y_dev, (size_t)batch * h->n * 2, cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (want_ids) {
+    e = cudaMemcpyAsync(h->ids_pin, h->ids_dev, sizeof(int32_t) * n_keep, cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  e = cudaMemcpyAsync(h->ids_pin + h->nb, h->gemm_ws, sizeof(unsigned int), cudaMemcpyDeviceToHost, s);
+  return e == cudaSuccess ? BAS_OK : cuda_fail(e);
+}
+
+// A forward that recurs with the same sizes and buffers is replayed as one CUDA graph launch instead
+// of six stream calls (the host-side cost of a call is mostly those).  The first occurrence runs
+// eagerly (it also performs every one-time set-up that must not happen under capture), the second is
+// captured, later ones are replays.  BAS_LINEAR_GRAPHS=0 keeps everything eager.
+static bool linear_graphs_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("BAS_LINEAR_GRAPHS");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+static int linear_run_selected(bas_linear* h, const void* x_src, int batch, int n_keep, int score_kind, void* y_dst,
+                               bool want_ids) {
+  if (!linear_graphs_enabled()) return linear_enqueue_selected(h, x_src, batch, n_keep, score_kind, y_dst, want_ids);
+  bas_linear::FwdGraph* g = nullptr;
+  for (auto& c : h->graphs)
+    if (c.batch == batch && c.n_keep == n_keep && c.score_kind == score_kind && c.x_src == x_src && c.y_dst == y_dst &&
+        c.want_ids == want_ids)
+      g = &c;
+  if (g == nullptr) {
+    if (h->graphs.size() >= 8) {   // forget the oldest
+      if (h->graphs.front().exec != nullptr) cudaGraphExecDestroy(h->graphs.front().exec);
+      h->graphs.erase(h->graphs.begin());
+    }
+    h->graphs.push_back(bas_linear::FwdGraph{batch, n_keep, score_kind, x_src, y_dst, want_ids, nullptr, false});
+    return linear_enqueue_selected(h, x_src, batch, n_keep, score_kind, y_dst, want_ids);
+  }
+  if (g->exec == nullptr && !g->failed) {
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamBeginCapture(h->stream, cudaStreamCaptureModeThreadLocal);
+    if (e == cudaSuccess) {
+      const int st = linear_enqueue_selected(h, x_src, batch, n_keep, score_kind, y_dst, want_ids);
+      e = cudaStreamEndCapture(h->stream, &graph);
+      if (st == BAS_OK && e == cudaSuccess && graph != nullptr) e = cudaGraphInstantiate(&g->exec, graph, 0);
+      else if (e == cudaSuccess) e = cudaErrorUnknown;
+      if (graph != nullptr) cudaGraphDestroy(graph);
+    }
+    if (e != cudaSuccess || g->exec == nullptr) {
+      (void)cudaGetLastError();
+      g->exec = nullptr;
+      g->failed = true;
+    }
+  }
+  if (g->exec == nullptr) return linear_enqueue_selected(h, x_src, batch, n_keep, score_kind, y_dst, want_ids);
+  const cudaError_t e = cudaGraphLaunch(g->exec, h->stream);
+  return e == cudaSuccess ? BAS_OK : cuda_fail(e);
+}
+
 // Enqueue one forward on the handle's stream: X host -> device, selection (or the caller's ids),
 // contraction, Y (and ids, status word) device -> host.  Nothing is waited for.
 static int linear_submit(bas_linear* h, const void* x_host, int batch, int n_keep, int score_kind,
@@ -499,39 +585,32 @@ static int linear_submit(bas_linear* h, const void* x_host, int batch, int n_kee
     std::memcpy(h->x_pin, x_host, row * batch);
     x_src = h->x_pin;
   }
-  cudaError_t e = cudaMemcpy2DAsync(h->x_dev, (size_t)h->ldx * 2, x_src, row, row, batch, cudaMemcpyHostToDevice, s);
-  if (e != cudaSuccess) return cuda_fail(e);
-  int st;
+  h->y_direct = is_pinned_host(y_host);
+  void* y_dst = h->y_direct ? y_host : h->y_pin;
   int k_host;
-  const int32_t* count_dev = nullptr;
   if (ids_host != nullptr || n_ids == 0) {
     if (n_ids < 0 || n_ids > h->nb) return BAS_ERR_INVALID_ARGUMENT;
+    cudaError_t e = cudaMemcpy2DAsync(h->x_dev, (size_t)h->ldx * 2, x_src, row, row, batch, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return cuda_fail(e);
     if (n_ids > 0) {
       std::memcpy(h->ids_pin, ids_host, sizeof(int32_t) * n_ids);
       e = cudaMemcpyAsync(h->ids_dev, h->ids_pin, sizeof(int32_t) * n_ids, cudaMemcpyHostToDevice, s);
       if (e != cudaSuccess) return cuda_fail(e);
     }
     k_host = n_ids;
-  } else {
-    st = bas_select_topk(h->x_dev, h->ldx, batch, h->k, n_keep, score_kind, h->ids_dev, h->ids_dev + h->nb, nullptr,
-                         nullptr, h->sel_ws, h->sel_ws_bytes, s);
+    const int st = bas_gemm(h->x_dev, h->ldx, h->packed, h->ids_dev, nullptr, k_host, nullptr, batch, (int)h->ldx, h->n,
+                            h->y_dev, h->n, h->gemm_ws, h->gemm_ws_bytes, s);
     if (st != BAS_OK) return st;
-    k_host = n_keep;
-    count_dev = h->ids_dev + h->nb;
-  }
-  st = bas_gemm(h->x_dev, h->ldx, h->packed, h->ids_dev, count_dev, k_host, nullptr, batch, (int)h->ldx, h->n, h->y_dev,
-                h->n, h->gemm_ws, h->gemm_ws_bytes, s);
-  if (st != BAS_OK) return st;
-  h->y_direct = is_pinned_host(y_host);
-  e = cudaMemcpyAsync(h->y_direct ? y_host : h->y_pin, h->y_dev, (size_t)batch * h->n * 2, cudaMemcpyDeviceToHost, s);
-  if (e != cudaSuccess) return cuda_fail(e);
-  if (ids_host_out != nullptr && k_host > 0) {
-    e = cudaMemcpyAsync(h->ids_pin, h->ids_dev, sizeof(int32_t) * k_host, cudaMemcpyDeviceToHost, s);
+    e = cudaMemcpyAsync(y_dst, h->y_dev, (size_t)batch * h->n * 2, cudaMemcpyDeviceToHost, s);
     if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaMemcpyAsync(h->ids_pin + h->nb, h->gemm_ws, sizeof(unsigned int), cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return cuda_fail(e);
+    ids_host_out = nullptr;   // the caller's own ids: nothing to hand back
+  } else {
+    k_host = n_keep;
+    const int st = linear_run_selected(h, x_src, batch, n_keep, score_kind, y_dst, ids_host_out != nullptr);
+    if (st != BAS_OK) return st;
   }
-  unsigned int* flag_pin = (unsigned int*)(h->ids_pin + h->nb);
-  e = cudaMemcpyAsync(flag_pin, h->gemm_ws, sizeof(unsigned int), cudaMemcpyDeviceToHost, s);
-  if (e != cudaSuccess) return cuda_fail(e);
   h->pending = true;
   h->pend_y = y_host;
   h->pend_ids = ids_host_out;
