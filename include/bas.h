@@ -150,6 +150,22 @@ BAS_API int bas_select_budget_ex(const void* x_dev, int64_t ldx, int batch, int 
                          int score_flags, int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
                          double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream);
 
+/* ---- selection and contraction in one call -------------------------------------------------
+ * The chain of _sparse_linear (scripts/bench_roundrobin_e2e_decode.py:179-284): select the batch's
+ * blocks, then multiply.  Where the contraction runs in clusters (outputs of up to about 9 000
+ * columns) the selection runs inside the contraction kernel - every cluster scores X for itself, its
+ * CTAs sharing the blocks - so the chain is one launch; elsewhere it is the two launches
+ * bas_select_topk / bas_select_budget_ex + bas_gemm.  Same ids, same sums either way.
+ *   energy_keep < 0   top-k of n_keep blocks by score_kind (| BAS_SCORE_BF16 with BAS_GEMM_BF16)
+ *   energy_keep >= 0  energy budget, at least n_keep blocks
+ *   ids_out_dev [>= K/64], count_out_dev [1]  required; bitmap_out_dev, scores_out_dev optional
+ *   flags: BAS_GEMM_BF16 and the tuning bits of bas_gemm_ex */
+BAS_API int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, int batch, int k, int n, int n_keep,
+                            int score_kind, double energy_keep, void* y_dev, int64_t ldy, int32_t* ids_out_dev,
+                            int32_t* count_out_dev, uint8_t* bitmap_out_dev, double* scores_out_dev,
+                            void* gemm_ws_dev, size_t gemm_ws_bytes, void* select_ws_dev, size_t select_ws_bytes,
+                            int flags, void* stream);
+
 /* ---- selection for callers that must not allocate -------------------------------------------
  * No counterpart in the reference.  Same result as bas_select_topk, but the caller passes no
  * workspace and the library allocates nothing: the kernel's scratch (one fp64 score per block and

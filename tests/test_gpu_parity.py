@@ -770,3 +770,75 @@ def test_sparse_linear_budget_mode_fixed_ids_and_dense_fallback(dev):
     want = (prefill.float() @ tw.float().t()).cpu().numpy()
     assert O.max_err_ratio(y.float().cpu().numpy(), want) <= TOL
     assert ops.read_status(dev) == 0
+
+
+# ---------------------------------------------------------------------------------------------
+# selection inside the contraction kernel
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("b,k,n,kind", [(16, 11008, 4096, 1), (2, 4096, 4096, 0), (64, 11008, 4096, 0), (33, 1088, 1000, 1),
+                                        (16, 4096, 11008, 0), (5, 4160, 512, 1)])
+def test_select_gemm_matches_the_two_launch_chain(dev, b, k, n, kind):
+    """Ids bit-exact against the oracle, sums within tolerance, optional outputs filled - whether the
+    shape runs the selection inside the contraction kernel or falls back to two launches."""
+    ops = _ops()
+    nb = k // 64
+    w = O.make_weight(n, k, seed=b)
+    packed = ops.pack_weight(torch.from_numpy(w).to(dev))
+    for step, density in enumerate((0.36, 0.1, 0.9)):
+        x = O.make_activations(b, k, seed=40 + step + b, dist="laplace")
+        tx = torch.from_numpy(x).to(dev)
+        scores = O.block_scores(x, kind)
+        n_keep = O.n_keep_from_density(density, nb)
+        want_ids = O.topk_ids(scores, n_keep)
+        out = torch.full((b, n), float("nan"), dtype=torch.float16, device=dev)
+        ids_out = torch.full((nb,), -1, dtype=torch.int32, device=dev)
+        count_out = torch.zeros(1, dtype=torch.int32, device=dev)
+        bitmap = torch.full((nb,), 7, dtype=torch.uint8, device=dev)
+        got_scores = torch.zeros(nb, dtype=torch.float64, device=dev)
+        ops.select_gemm(tx, packed, out, n_keep, kind, ids_out=ids_out, count_out=count_out, bitmap_out=bitmap,
+                        scores_out=got_scores)
+        torch.cuda.synchronize()
+        assert ops.read_status(dev) == 0
+        assert int(count_out.item()) == n_keep
+        assert np.array_equal(ids_out[:n_keep].cpu().numpy(), want_ids)
+        assert np.array_equal(bitmap.cpu().numpy(), O.build_bitmap(want_ids, nb))
+        assert np.array_equal(got_scores.cpu().numpy(), scores)
+        assert O.max_err_ratio(out.cpu().numpy(), O.masked_gemm(x, w, want_ids)) <= TOL
+    # energy budget, variable count
+    x = O.make_activations(b, k, seed=99 + b, dist="laplace")
+    energy = O.block_scores(x, O.SCORE_ENERGY)
+    for keep in (0.5, 0.95):
+        want_ids = O.energy_budget_ids(energy, keep, 2)
+        out = torch.full((b, n), float("nan"), dtype=torch.float16, device=dev)
+        ids_out, count_out = ops.select_gemm(torch.from_numpy(x).to(dev), packed, out, 2, O.SCORE_ENERGY, energy_keep=keep)
+        torch.cuda.synchronize()
+        assert int(count_out.item()) == want_ids.size
+        assert np.array_equal(ids_out[: want_ids.size].cpu().numpy(), want_ids)
+        assert O.max_err_ratio(out.cpu().numpy(), O.masked_gemm(x, w, want_ids)) <= TOL
+
+
+def test_select_gemm_ties_and_chained_calls(dev):
+    """Equal scores go to the lower id inside the kernel too; calls in a row hand back their own masks."""
+    ops = _ops()
+    b, k, n = 16, 4096, 2048
+    nb = k // 64
+    w = O.make_weight(n, k, seed=1)
+    packed = ops.pack_weight(torch.from_numpy(w).to(dev))
+    x = np.zeros((b, k), np.float16)
+    x[:, : 64 * 10] = 1.0                     # ten blocks with the same score, the rest zero
+    out = torch.empty(b, n, dtype=torch.float16, device=dev)
+    ids, count = ops.select_gemm(torch.from_numpy(x).to(dev), packed, out, 14, O.SCORE_NORM)
+    torch.cuda.synchronize()
+    assert np.array_equal(ids[:14].cpu().numpy(), np.arange(14, dtype=np.int32))
+    xs = [O.make_activations(b, k, seed=300 + i, dist="laplace") for i in range(6)]
+    txs = [torch.from_numpy(v).to(dev) for v in xs]
+    outs = [torch.empty(b, n, dtype=torch.float16, device=dev) for _ in xs]
+    idbufs = [torch.empty(nb, dtype=torch.int32, device=dev) for _ in xs]
+    cnt = torch.empty(1, dtype=torch.int32, device=dev)
+    for i in range(6):
+        ops.select_gemm(txs[i], packed, outs[i], 23, O.SCORE_ENERGY, ids_out=idbufs[i], count_out=cnt)
+    torch.cuda.synchronize()
+    for i in range(6):
+        want = O.topk_ids(O.block_scores(xs[i], O.SCORE_ENERGY), 23)
+        assert np.array_equal(idbufs[i][:23].cpu().numpy(), want), i
+        assert O.max_err_ratio(outs[i].cpu().numpy(), O.masked_gemm(xs[i], w, want)) <= TOL, i

@@ -316,13 +316,55 @@ def _select(x2d, mode, n_keep, score_kind, energy_keep, ids_out, count_out, bitm
         return ids_out, count_out
 
 
+def select_gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, n_keep: int,
+                score_kind: int = SCORE_NORM, *, energy_keep: Optional[float] = None,
+                ids_out: Optional[torch.Tensor] = None, count_out: Optional[torch.Tensor] = None,
+                bitmap_out: Optional[torch.Tensor] = None, scores_out: Optional[torch.Tensor] = None,
+                cluster: int = 0, max_ctas: int = 0):
+    """Batch-shared mask selection and the masked contraction in one call (one launch where the
+    contraction runs in clusters, else the two-launch chain; same ids and sums).  ``energy_keep``
+    switches from top-k of ``n_keep`` to the energy budget with at least ``n_keep`` blocks.
+    Returns (ids buffer, count int32[1]); the first ``count`` ids are the kept blocks, ascending."""
+    _require_cuda_fp16(x2d, "x")
+    _require_cuda_fp16(out2d, "out")
+    if x2d.dtype != out2d.dtype:
+        raise TypeError("x and out must have the same dtype")
+    if x2d.dim() != 2 or out2d.dim() != 2 or x2d.stride(1) != 1 or out2d.stride(1) != 1:
+        raise ValueError("x and out must be 2-D with unit inner stride")
+    bt, k = x2d.shape
+    n = out2d.shape[1]
+    if bt > MAX_BATCH or out2d.shape[0] != bt:
+        raise ValueError(f"batch must agree and be at most {MAX_BATCH}")
+    nb = k // BLOCK_K
+    if nb < 1:
+        raise ValueError("K must be at least 64")
+    if ids_out is None or count_out is None:
+        ids_buf, cnt_buf = _select_buffers(x2d.device, nb)
+        ids_out = ids_out if ids_out is not None else ids_buf
+        count_out = count_out if count_out is not None else cnt_buf
+    if scores_out is not None and scores_out.dtype != torch.float64:
+        raise TypeError("scores_out must be float64")
+    bf16 = x2d.dtype == torch.bfloat16
+    with torch.cuda.device(x2d.device):
+        gws, sws = gemm_workspace(x2d.device), select_workspace(x2d.device, k)
+        check(lib.bas_select_gemm(
+            x2d.data_ptr(), x2d.stride(0), packed.data_ptr(), bt, k, n, int(n_keep),
+            int(score_kind) | (SCORE_BF16 if bf16 else 0), float(energy_keep) if energy_keep is not None else -1.0,
+            out2d.data_ptr(), out2d.stride(0), ids_out.data_ptr(), count_out.data_ptr(),
+            bitmap_out.data_ptr() if bitmap_out is not None else None,
+            scores_out.data_ptr() if scores_out is not None else None,
+            gws.data_ptr(), gws.numel(), sws.data_ptr(), sws.numel(),
+            (GEMM_BF16 if bf16 else 0) | (int(cluster) << 8) | (int(max_ctas) << 16), _stream_ptr()), "bas_select_gemm")
+    return ids_out, count_out
+
+
 def sparse_linear(x: torch.Tensor, weight: torch.Tensor, density: float, *, score_kind: int = SCORE_NORM,
                   cache_prefix: str = "sparse_linear", out: Optional[torch.Tensor] = None,
                   fixed_active_blocks: Optional[torch.Tensor] = None, energy_keep: Optional[float] = None,
                   min_keep: int = 1) -> torch.Tensor:
     """The decode-time operator of the reference's ``_sparse_linear``
-    (scripts/bench_roundrobin_e2e_decode.py:179-284) as two chained launches: select, then GEMM
-    reading the id list (and its length) from device memory.  x is [B, K] or [B, 1, K].
+    (scripts/bench_roundrobin_e2e_decode.py:179-284) through :func:`select_gemm`: selection and
+    contraction in one launch where the shape allows, else chained, never a host round trip.  x is [B, K] or [B, 1, K].
 
     * More than one position per sequence (prefill) or ``density >= 1`` runs the dense
       ``F.linear``, as the reference does (:200-201).
@@ -346,11 +388,16 @@ def sparse_linear(x: torch.Tensor, weight: torch.Tensor, density: float, *, scor
     if fixed_active_blocks is not None:
         ids = fixed_active_blocks.to(device=x.device, dtype=torch.int32).contiguous()
         gemm(x2d, packed, out2d, ids=ids)
+    elif bt > MAX_BATCH:
+        if energy_keep is not None:
+            ids, count = select_budget(x2d, float(energy_keep), int(min_keep))
+            gemm(x2d, packed, out2d, ids=ids, count=count, k_host=nb)
+        else:
+            n_keep = n_keep_from_density(density, nb, min_keep)
+            ids, count = select_topk(x2d, n_keep, score_kind)
+            gemm(x2d, packed, out2d, ids=ids, count=count, k_host=n_keep)
     elif energy_keep is not None:
-        ids, count = select_budget(x2d, float(energy_keep), int(min_keep))
-        gemm(x2d, packed, out2d, ids=ids, count=count, k_host=nb)
+        select_gemm(x2d, packed, out2d, int(min_keep), SCORE_ENERGY, energy_keep=float(energy_keep))
     else:
-        n_keep = n_keep_from_density(density, nb, min_keep)
-        ids, count = select_topk(x2d, n_keep, score_kind)
-        gemm(x2d, packed, out2d, ids=ids, count=count, k_host=n_keep)
+        select_gemm(x2d, packed, out2d, n_keep_from_density(density, nb, min_keep), score_kind)
     return out.reshape(bt, n) if x.dim() == 2 else out

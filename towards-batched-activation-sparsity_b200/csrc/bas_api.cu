@@ -205,15 +205,18 @@ void bas_tp_destroy(bas_tp* t) {
   delete t;
 }
 
-static int gemm_impl(const bas_tp* tp, const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
-                     const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
-                     void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream) {
+// `sel` (optional): run the mask selection inside the contraction kernel; ids_dev / count_dev /
+// bitmap_dev are then ignored.  Returns BAS_ERR_UNSUPPORTED without launching when the work split of
+// this shape has no cluster to run it in.
+static int gemm_impl(const bas_tp* tp, const FusedSelect* sel, const void* x_dev, int64_t ldx, const void* packed_dev,
+                     const int32_t* ids_dev, const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch,
+                     int k, int n, void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream) {
   if (x_dev == nullptr || packed_dev == nullptr || y_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || k <= 0 || n <= 0 || k_host < 0 || ldx < k || ldy < n) return BAS_ERR_INVALID_ARGUMENT;
   if (batch > BAS_MAX_BATCH) return BAS_ERR_UNSUPPORTED;
   const int nb = (k + kBlockK - 1) / kBlockK;
   if (nb > BAS_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
-  if (bitmap_dev == nullptr && ids_dev == nullptr && k_host > 0) return BAS_ERR_INVALID_ARGUMENT;
+  if (sel == nullptr && bitmap_dev == nullptr && ids_dev == nullptr && k_host > 0) return BAS_ERR_INVALID_ARGUMENT;
   if (k_host > nb) {
     if (bitmap_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;  // ids are distinct
     k_host = nb;                                                 // with a byte map k_host is only a hint
@@ -235,7 +238,7 @@ static int gemm_impl(const bas_tp* tp, const void* x_dev, int64_t ldx, const voi
       if (tp->area[q] == nullptr) return BAS_ERR_INVALID_ARGUMENT;   // bas_tp_connect has not run
     if (batch > tp->max_batch || n > tp->n || family == 1) return BAS_ERR_INVALID_ARGUMENT;
   }
-  if (tp == nullptr && bitmap_dev == nullptr && k_host == 0) {  // empty active set known on the host: Y = 0
+  if (tp == nullptr && sel == nullptr && bitmap_dev == nullptr && k_host == 0) {  // empty active set known on the host: Y = 0
     cudaError_t e = cudaMemset2DAsync(y_dev, (size_t)ldy * 2, 0, (size_t)n * 2, (size_t)batch, s);
     return e == cudaSuccess ? BAS_OK : cuda_fail(e);
   }
@@ -258,6 +261,13 @@ static int gemm_impl(const bas_tp* tp, const void* x_dev, int64_t ldx, const voi
   p.ldy = (long long)ldy;
   p.flags = flags;
   p.status = (unsigned int*)ws_dev;
+  p.sel = FusedSelect{};
+  if (sel != nullptr) {
+    p.sel = *sel;
+    p.ids = nullptr;
+    p.count_dev = nullptr;
+    p.bitmap = nullptr;
+  }
   p.tp = TpExchange{};
   if (tp != nullptr) {
     p.tp.world = tp->world;
@@ -280,23 +290,25 @@ static int gemm_impl(const bas_tp* tp, const void* x_dev, int64_t ldx, const voi
   // of the copies per byte), so it is the default; the CUDA-core kernel runs on request.
   const bool small = (family == 1);
   if (small && (batch > 8 || (flags & BAS_GEMM_BF16) != 0)) return BAS_ERR_UNSUPPORTED;   // the CUDA-core kernel is fp16 only
+  if (small && sel != nullptr) return BAS_ERR_UNSUPPORTED;
   cudaError_t e = small ? launch_gemv(p, grid_cap, s) : launch_umma(p, grid_cap, s);
+  if (e == cudaErrorNotSupported && sel != nullptr) return BAS_ERR_UNSUPPORTED;
   return e == cudaSuccess ? BAS_OK : cuda_fail(e);
 }
 
 int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
                 const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
                 void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream) {
-  return gemm_impl(nullptr, x_dev, ldx, packed_dev, ids_dev, count_dev, k_host, bitmap_dev, batch, k, n, y_dev, ldy,
-                   ws_dev, ws_bytes, flags, stream);
+  return gemm_impl(nullptr, nullptr, x_dev, ldx, packed_dev, ids_dev, count_dev, k_host, bitmap_dev, batch, k, n, y_dev,
+                   ldy, ws_dev, ws_bytes, flags, stream);
 }
 
 int bas_gemm_allreduce(bas_tp* tp, const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
                        const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
                        void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream) {
   if (tp == nullptr) return BAS_ERR_INVALID_ARGUMENT;
-  return gemm_impl(tp, x_dev, ldx, packed_dev, ids_dev, count_dev, k_host, bitmap_dev, batch, k, n, y_dev, ldy, ws_dev,
-                   ws_bytes, flags, stream);
+  return gemm_impl(tp, nullptr, x_dev, ldx, packed_dev, ids_dev, count_dev, k_host, bitmap_dev, batch, k, n, y_dev, ldy,
+                   ws_dev, ws_bytes, flags, stream);
 }
 
 int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev, const int32_t* count_dev,
@@ -387,6 +399,43 @@ int bas_select_budget_ex(const void* x_dev, int64_t ldx, int batch, int k, doubl
   if ((score_flags & ~BAS_SCORE_BF16) != 0) return BAS_ERR_INVALID_ARGUMENT;
   return select_common(x_dev, ldx, batch, k, 1, min_keep, BAS_SCORE_ENERGY | score_flags, energy_keep, ids_out_dev,
                        count_out_dev, bitmap_out_dev, scores_out_dev, ws_dev, ws_bytes, stream);
+}
+
+int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, int batch, int k, int n, int n_keep,
+                    int score_kind, double energy_keep, void* y_dev, int64_t ldy, int32_t* ids_out_dev,
+                    int32_t* count_out_dev, uint8_t* bitmap_out_dev, double* scores_out_dev, void* gemm_ws_dev,
+                    size_t gemm_ws_bytes, void* select_ws_dev, size_t select_ws_bytes, int flags, void* stream) {
+  if (ids_out_dev == nullptr || count_out_dev == nullptr || k < kBlockK) return BAS_ERR_INVALID_ARGUMENT;
+  const int bf16 = (score_kind & BAS_SCORE_BF16) != 0 ? 1 : 0;
+  if (bf16 != ((flags & BAS_GEMM_BF16) != 0 ? 1 : 0)) return BAS_ERR_INVALID_ARGUMENT;   // one dtype for X
+  const int kind = score_kind & ~BAS_SCORE_BF16;
+  const bool budget = energy_keep >= 0.0;
+  const int nb_sel = k / kBlockK;
+  if ((kind != BAS_SCORE_NORM && kind != BAS_SCORE_ENERGY) || n_keep < 0 || n_keep > nb_sel ||
+      (flags & (3 | BAS_GEMM_IDS_STABLE)) != 0)
+    return BAS_ERR_INVALID_ARGUMENT;
+  FusedSelect sel;
+  sel.mode = budget ? 2 : 1;
+  sel.n_keep = n_keep;
+  sel.score_kind = budget ? BAS_SCORE_ENERGY : kind;
+  sel.nb_sel = nb_sel;
+  sel.energy_keep = budget ? energy_keep : 0.0;
+  sel.ids_out = ids_out_dev;
+  sel.count_out = count_out_dev;
+  sel.bitmap_out = bitmap_out_dev;
+  sel.scores_out = scores_out_dev;
+  // grid sizing: the blocks to expect
+  const int k_est = budget ? (nb_sel + 1) / 2 : (n_keep > 0 ? n_keep : 1);
+  int st = gemm_impl(nullptr, &sel, x_dev, ldx, packed_dev, nullptr, nullptr, k_est, nullptr, batch, k, n, y_dev, ldy,
+                     gemm_ws_dev, gemm_ws_bytes, flags, stream);
+  if (st != BAS_ERR_UNSUPPORTED) return st;
+  // no cluster for this shape: the two-launch chain, same results
+  st = select_common(x_dev, ldx, batch, k, budget ? 1 : 0, n_keep, sel.score_kind | (bf16 ? BAS_SCORE_BF16 : 0),
+                     sel.energy_keep, ids_out_dev, count_out_dev, bitmap_out_dev, scores_out_dev, select_ws_dev,
+                     select_ws_bytes, stream);
+  if (st != BAS_OK) return st;
+  return gemm_impl(nullptr, nullptr, x_dev, ldx, packed_dev, ids_out_dev, count_out_dev, budget ? nb_sel : n_keep, nullptr,
+                   batch, k, n, y_dev, ldy, gemm_ws_dev, gemm_ws_bytes, flags, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -204,6 +204,9 @@ __device__ __forceinline__ void dsmem_st_f32(uint32_t addr, float v) {
 __device__ __forceinline__ void dsmem_st_v4_f32(uint32_t addr, float a, float b, float c, float d) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+__device__ __forceinline__ void dsmem_st_f64(uint32_t cluster_addr, double v) {
+  asm volatile("st.shared::cluster.f64 [%0], %1;" ::"r"(cluster_addr), "d"(v) : "memory");
+}
 __device__ __forceinline__ float dsmem_ld_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");

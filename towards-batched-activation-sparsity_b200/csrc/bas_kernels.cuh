@@ -26,6 +26,21 @@ struct TpExchange {
   unsigned char* own;                  // == area[rank]
 };
 
+// Mask selection run inside the contraction kernel (cluster modes only): every cluster scores all
+// blocks of X, its CTAs sharing the blocks and exchanging the scores through shared memory, ranks them
+// and compacts the kept ids straight into the id list the contraction then walks.
+struct FusedSelect {
+  int mode;            // 0 = off (ids / byte map given), 1 = top-k, 2 = energy budget
+  int n_keep;          // top-k: blocks to keep; budget: minimum to keep
+  int score_kind;      // BAS_SCORE_NORM / BAS_SCORE_ENERGY
+  int nb_sel;          // K / 64 rounded down: trailing channels are never scored
+  double energy_keep;  // budget mode
+  int32_t* ids_out;    // optional outputs, written by CTA 0 only
+  int32_t* count_out;
+  uint8_t* bitmap_out;
+  double* scores_out;
+};
+
 struct GemmParams {
   const __half* x;          // [batch, K], row stride ldx
   long long ldx;
@@ -48,6 +63,7 @@ struct GemmParams {
   int flags;                // kFlag* bits
   unsigned int* status;     // workspace: status word
   TpExchange tp;            // row-parallel sum over ranks (world 0 = off)
+  FusedSelect sel;          // mask selection inside the kernel (mode 0 = off)
 #ifdef BAS_TRACE
   long long* trace;         // diagnostic build only: per-role cycle counters of CTA 0
 #endif

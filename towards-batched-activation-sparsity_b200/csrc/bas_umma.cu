@@ -73,6 +73,8 @@ struct UmmaSmemHeader {
   uint32_t tmem_base;
   int k_act;
   int abort_flag;
+  int sel_keep;               // in-kernel selection: blocks kept
+  int sel_warp_cnt[kUmmaThreads / 32];
   long long t0;   // diagnostic builds: clock at kernel start
 };
 
@@ -81,9 +83,147 @@ inline size_t umma_fixed_smem(int nb) {
   return 1024 /*alignment slack*/ + (sizeof(UmmaSmemHeader) + 127) / 128 * 128 + umma_ids_bytes(nb) + 1024;
 }
 
+// Bytes of scratch the in-kernel selection needs in the (not yet used) ring area: scores, ranks and
+// rank order of all blocks, then the per-(block, row) scores of this CTA's share of the blocks.
+inline size_t fused_select_scratch(int nb_sel, int cluster, int batch) {
+  const size_t per_block = sizeof(double) + 2 * sizeof(int);
+  const size_t mine = (size_t)(nb_sel + cluster - 1) / cluster;
+  return ((size_t)nb_sel * per_block + 15) / 16 * 16 + mine * (size_t)batch * sizeof(double);
+}
+
+// The batch-shared mask selection of select_kernel (same arithmetic: fp64 sums of exact squares, rows
+// added in order, ties to the lower id), run by one cluster for itself.  CTA `crank` scores blocks
+// crank, crank + C, ...; the scores go to every CTA of the cluster through distributed shared memory;
+// then every CTA ranks all blocks and compacts the kept ids, ascending, into s_ids.  Returns the
+// number kept.  All threads of the CTA (and all CTAs of the cluster) must call it.
+__device__ __forceinline__ int fused_select(const GemmParams& p, uint8_t* scratch, uint16_t* s_ids, int* s_warp_cnt,
+                                            int* s_keep, int crank, int C, int tid, int nthreads) {
+  const int nb = p.sel.nb_sel, batch = p.batch;
+  const bool bf16 = (p.flags & kFlagBf16) != 0;
+  double* s_score = (double*)scratch;
+  int* s_rank = (int*)(s_score + nb);
+  int* s_order = s_rank + nb;
+  double* s_pair = (double*)(scratch + ((size_t)nb * (sizeof(double) + 2 * sizeof(int)) + 15) / 16 * 16);
+  const int lane = tid & 31, warp = tid >> 5;
+  const int nmine = (nb > crank) ? (nb - crank + C - 1) / C : 0;
+
+  // ---- scores of this CTA's blocks: 8 lanes per (block, row) pair, 16 bytes per lane ----
+  const int sub = tid & 7, grp = tid >> 3;
+  const int pairs = nmine * batch;
+  for (int base = 0; base < pairs; base += nthreads / 8) {
+    const int pr = base + grp;
+    double e = 0.0;
+    if (pr < pairs) {
+      const int jj = pr / batch, b = pr - jj * batch;
+      const uint4 v = __ldg((const uint4*)(p.x + (size_t)b * p.ldx + (size_t)(crank + jj * C) * kBlockK) + sub);
+      if (bf16) {
+        const unsigned int* wds = (const unsigned int*)&v;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const double lo = (double)__uint_as_float(wds[q] << 16), hi = (double)__uint_as_float(wds[q] & 0xffff0000u);
+          e += lo * lo;
+          e += hi * hi;
+        }
+      } else {
+        const __half2* h = (const __half2*)&v;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = __half22float2(h[q]);
+          e += (double)(f.x * f.x);
+          e += (double)(f.y * f.y);
+        }
+      }
+    }
+    e += __shfl_xor_sync(0xffffffffu, e, 1);
+    e += __shfl_xor_sync(0xffffffffu, e, 2);
+    e += __shfl_xor_sync(0xffffffffu, e, 4);
+    if (pr < pairs && sub == 0) s_pair[pr] = (p.sel.score_kind == BAS_SCORE_NORM) ? sqrt(e) : e;
+  }
+  __syncthreads();
+  const uint32_t score_base = smem_u32(s_score);
+  for (int jj = tid; jj < nmine; jj += nthreads) {
+    double sum = 0.0;
+    for (int b = 0; b < batch; ++b) sum += s_pair[jj * batch + b];   // batch rows in order
+    const double score = sum / (double)batch;
+    const int j = crank + jj * C;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (q < C) dsmem_st_f64(dsmem_addr(score_base + (uint32_t)j * 8u, (uint32_t)q), score);
+  }
+  cluster_sync_all();   // every CTA of the cluster now holds every score
+
+  // ---- rank all blocks: four threads per block ----
+  for (int j0 = 0; j0 < nb; j0 += nthreads / 4) {
+    const int j = j0 + (tid >> 2), quad = tid & 3;
+    int rank = 0;
+    if (j < nb) {
+      const double sj = s_score[j];
+      for (int i = quad; i < nb; i += 4) {
+        const double si = s_score[i];
+        rank += (si > sj || (si == sj && i < j)) ? 1 : 0;
+      }
+    }
+    rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+    rank += __shfl_xor_sync(0xffffffffu, rank, 2);
+    if (j < nb && quad == 0) {
+      s_rank[j] = rank;
+      s_order[rank] = j;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int keep = p.sel.n_keep;
+    if (p.sel.mode == 2) {
+      // energy budget: shortest descending prefix whose sum reaches energy_keep of the total
+      double total = 0.0;
+      for (int r = 0; r < nb; ++r) total += s_score[s_order[r]];
+      const double thresh = p.sel.energy_keep * total;
+      double cum = 0.0;
+      int kk = nb;
+      for (int r = 0; r < nb; ++r) {
+        cum += s_score[s_order[r]];
+        if (cum >= thresh) {
+          kk = r + 1;
+          break;
+        }
+      }
+      keep = max(p.sel.n_keep, min(nb, kk));
+    }
+    *s_keep = min(max(keep, 0), nb);
+  }
+  __syncthreads();
+  const int keep = *s_keep;
+  // ---- ascending compaction of the kept ids; CTA 0 also writes the caller's outputs ----
+  const bool writer = blockIdx.x == 0;
+  int running = 0;
+  for (int base = 0; base < nb; base += nthreads) {
+    const int j = base + tid;
+    const bool kept = (j < nb) && (s_rank[j] < keep);
+    if (writer && j < nb) {
+      if (p.sel.bitmap_out != nullptr) p.sel.bitmap_out[j] = kept ? 1 : 0;
+      if (p.sel.scores_out != nullptr) p.sel.scores_out[j] = s_score[j];
+    }
+    const unsigned m = __ballot_sync(0xffffffffu, kept);
+    if (lane == 0) s_warp_cnt[warp] = __popc(m);
+    __syncthreads();
+    int off = running;
+    for (int w = 0; w < warp; ++w) off += s_warp_cnt[w];
+    if (kept) {
+      const int pos = off + __popc(m & ((1u << lane) - 1u));
+      s_ids[pos] = (uint16_t)j;
+      if (writer && p.sel.ids_out != nullptr) p.sel.ids_out[pos] = j;
+    }
+    for (int w = 0; w < nthreads / 32; ++w) running += s_warp_cnt[w];
+    __syncthreads();
+  }
+  if (writer && tid == 0 && p.sel.count_out != nullptr) *p.sel.count_out = keep;
+  return keep;
+}
+
 // TP: the row-parallel variant that exchanges partial sums with the other ranks of a box instead of
 // storing Y directly (a template parameter, so that the plain kernel carries none of that code).
-template <int BPAD, bool TP>
+// SEL: the variant that selects the mask itself (cluster modes, not combined with TP).
+template <int BPAD, bool TP, bool SEL>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
     umma_colsplit_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
   const bool bf16 = (p.flags & kFlagBf16) != 0;
@@ -123,7 +263,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   // The id list may be the previous kernel's output unless the caller declared it stable; X and Y
   // always wait for the previous kernel.  A stable list is requested right away, so that its load
   // latency runs under the set-up below.
-  const bool early_ids = (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
+  const bool early_ids = !SEL && (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
   int first_ids[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (warp == 0 && early_ids)
     warp_load_id_batch(p.ids, p.bitmap, p.bitmap != nullptr ? p.nb : p.k_host, 0, lane, first_ids);
@@ -167,6 +307,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   constexpr int TW = kTileN;                        // columns per pass
   const int n_sub = (width + TW - 1) / TW;
 
+  if (SEL) {
+    // Mask selection by this cluster, for itself.  X (and the caller's id / count / byte-map arrays,
+    // which CTA 0 writes) may still be in use by the kernel before this one: wait first.
+    pdl_wait();
+    const int kept = fused_select(p, s_stage, s_ids, hdr->sel_warp_cnt, &hdr->sel_keep, rank, C, tid, kUmmaThreads);
+    if (tid == 0) hdr->k_act = kept;
+    __syncthreads();
+  }
+
   int k_act = 0;
   // Row-parallel sum over ranks (epilogue threads only): this call's sequence number in the
   // exchange area and the partial buffer it selects.
@@ -179,9 +328,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   if (warp < kProducers) {
     // ------------------------------ id staging (warp 0) + producers ------------------------------
     if (warp == 0) {
-      if (!early_ids) pdl_wait();
-      k_act = warp_stage_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids, p.status, lane,
-                             early_ids, first_ids);
+      if (SEL) {
+        k_act = hdr->k_act;     // the list is already in s_ids
+      } else {
+        if (!early_ids) pdl_wait();
+        k_act = warp_stage_ids(p.ids, p.count_dev, p.k_host, p.bitmap, p.nb, s_ids, p.status, lane, early_ids,
+                               first_ids);
+      }
       if (lane == 0) {
         hdr->k_act = k_act;
         mbar_arrive(&hdr->ids_ready);
@@ -747,7 +900,7 @@ int max_resident_clusters(int cluster, size_t smem, int sm_count) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, umma_colsplit_kernel<BPAD, false>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, umma_colsplit_kernel<BPAD, false, false>, &cfg) != cudaSuccess) {
     (void)cudaGetLastError();
     n = 0;
   }
@@ -762,10 +915,14 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-    cudaError_t e =
-        cudaFuncSetAttribute(umma_colsplit_kernel<BPAD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(umma_colsplit_kernel<BPAD, false, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(umma_colsplit_kernel<BPAD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      e = cudaFuncSetAttribute(umma_colsplit_kernel<BPAD, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               227 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(umma_colsplit_kernel<BPAD, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               227 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
@@ -856,10 +1013,21 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   CUtensorMap xmap;
   cudaError_t e = get_x_tensor_map(p, BPAD, &xmap);
   if (e != cudaSuccess) return e;
+  if (p.sel.mode != 0) {
+    // the in-kernel selection needs a cluster to share the scoring and room for its scratch in the ring
+    if (cluster < 2 || p.tp.world > 0 ||
+        fused_select_scratch(p.sel.nb_sel, cluster, p.batch) > (size_t)p.stages * group * stage_bytes)
+      return cudaErrorNotSupported;
+    count_launch();
+    return launch_with_pdl(umma_colsplit_kernel<BPAD, false, true>, ranges * cluster, kUmmaThreads, smem, cluster, stream,
+                           p, xmap);
+  }
   count_launch();
   if (p.tp.world > 0)
-    return launch_with_pdl(umma_colsplit_kernel<BPAD, true>, ranges * cluster, kUmmaThreads, smem, cluster, stream, p, xmap);
-  return launch_with_pdl(umma_colsplit_kernel<BPAD, false>, ranges * cluster, kUmmaThreads, smem, cluster, stream, p, xmap);
+    return launch_with_pdl(umma_colsplit_kernel<BPAD, true, false>, ranges * cluster, kUmmaThreads, smem, cluster, stream,
+                           p, xmap);
+  return launch_with_pdl(umma_colsplit_kernel<BPAD, false, false>, ranges * cluster, kUmmaThreads, smem, cluster, stream, p,
+                         xmap);
 }
 
 }  // namespace
