@@ -424,10 +424,24 @@ def run_gpu(args) -> None:
             sel, cnt = ops.select_topk(x_steps[s % 11], n_keep4, abi.SCORE_ENERGY)
             ops.gemm(x_steps[s % 11], packed[s], outs[b], ids=sel, count=cnt, k_host=n_keep4)
 
+    def one_launch():
+        for s in range(ROTATE):
+            ops.select_gemm(x_steps[s % 11], packed[s], outs[b], n_keep4, abi.SCORE_ENERGY)
+
     sel_us = _graph_time_us(torch, stream, select_only, ROTATE, reps)
     chain_us = _graph_time_us(torch, stream, chain, ROTATE, reps)
+    fused_us = _graph_time_us(torch, stream, one_launch, ROTATE, reps)
+    # same mask and same sums from the one-launch form as from the oracle's ids (not timed)
+    sel_ids, _ = ops.select_gemm(x_steps[3], packed[0], outs[b], n_keep4, abi.SCORE_ENERGY)
+    torch.cuda.synchronize()
+    want_ids = O.topk_ids(O.block_scores(x_steps[3].cpu().numpy(), abi.SCORE_ENERGY), n_keep4)
+    if not np.array_equal(sel_ids[:n_keep4].cpu().numpy(), want_ids):
+        raise SystemExit("in-kernel selection disagrees with the oracle's ids")
     online = {"batch": b, "keep_blocks": n_keep4, "select_us": round(sel_us, 3), "select_plus_gemm_us": round(chain_us, 3),
-              "score": "energy"}
+              "selection_inside_gemm_us": round(fused_us, 3), "score": "energy",
+              "note": "select_us: selection kernel alone; select_plus_gemm_us: two launches; "
+                      "selection_inside_gemm_us: bas_select_gemm (one call; it selects inside the contraction "
+                      "kernel only where that is the faster form, i.e. batches of a few rows)"}
 
     # ---- the sharded decode-step linear stack (all ranks take part) ----
     try:

@@ -108,7 +108,9 @@ BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, con
  *   bits 12-14 copy/MMA warp pairs of the tcgen05 kernel: 0 = chosen by the ring size, else 2, 3
  *             or 4 (a tuning knob; results differ only in fp32 summation order).
  *   bits 16-23 upper bound on the CTAs of the tcgen05 kernel: 0 = chosen by the amount of work
- *             (a tuning knob). */
+ *             (a tuning knob).
+ *   bit 24    bas_select_gemm only: select inside the contraction kernel whenever the shape has
+ *             clusters, also where the two-launch chain is measured faster (a tuning knob). */
 #define BAS_GEMM_IDS_STABLE 16
 #define BAS_GEMM_BF16 32
 BAS_API int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
@@ -152,10 +154,11 @@ BAS_API int bas_select_budget_ex(const void* x_dev, int64_t ldx, int batch, int 
 
 /* ---- selection and contraction in one call -------------------------------------------------
  * The chain of _sparse_linear (scripts/bench_roundrobin_e2e_decode.py:179-284): select the batch's
- * blocks, then multiply.  Where the contraction runs in clusters (outputs of up to about 9 000
- * columns) the selection runs inside the contraction kernel - every cluster scores X for itself, its
- * CTAs sharing the blocks - so the chain is one launch; elsewhere it is the two launches
- * bas_select_topk / bas_select_budget_ex + bas_gemm.  Same ids, same sums either way.
+ * blocks, then multiply.  Where the contraction runs in clusters and the scoring is small (up to
+ * about 256 (block, row) pairs per CTA: batches of a few rows) the selection runs inside the
+ * contraction kernel - every cluster scores X for itself, its CTAs sharing the blocks - so the chain
+ * is one launch; elsewhere it is the two launches bas_select_topk / bas_select_budget_ex + bas_gemm,
+ * which is the faster form there.  Same ids, same sums either way.
  *   energy_keep < 0   top-k of n_keep blocks by score_kind (| BAS_SCORE_BF16 with BAS_GEMM_BF16)
  *   energy_keep >= 0  energy budget, at least n_keep blocks
  *   ids_out_dev [>= K/64], count_out_dev [1]  required; bitmap_out_dev, scores_out_dev optional

@@ -225,7 +225,7 @@ static int gemm_impl(const bas_tp* tp, const FusedSelect* sel, const void* x_dev
   if (!aligned16(x_dev) || !aligned16(packed_dev) || (ldx & 7) != 0 || (k & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
   if (ws_dev == nullptr || ws_bytes < bas_gemm_workspace_bytes(batch, n)) return BAS_ERR_WORKSPACE;
   const int family = flags & 3;
-  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_BF16 | 0x700 | 0x7000 | 0xff0000)) != 0) return BAS_ERR_INVALID_ARGUMENT;
+  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_BF16 | 0x700 | 0x7000 | 0xff0000 | (1 << 24))) != 0) return BAS_ERR_INVALID_ARGUMENT;
 
   DeviceInfo di;
   int st = device_info(&di);
@@ -554,12 +554,23 @@ static int linear_enqueue_selected(bas_linear* h, const void* x_src, int batch, 
   const size_t row = (size_t)h->k * 2;
   cudaError_t e = cudaMemcpy2DAsync(h->x_dev, (size_t)h->ldx * 2, x_src, row, row, batch, cudaMemcpyHostToDevice, s);
   if (e != cudaSuccess) return cuda_fail(e);
-  int st = bas_select_topk(h->x_dev, h->ldx, batch, h->k, n_keep, score_kind, h->ids_dev, h->ids_dev + h->nb, nullptr,
-                           nullptr, h->sel_ws, h->sel_ws_bytes, s);
-  if (st != BAS_OK) return st;
-  st = bas_gemm(h->x_dev, h->ldx, h->packed, h->ids_dev, h->ids_dev + h->nb, n_keep, nullptr, batch, (int)h->ldx, h->n,
-                h->y_dev, h->n, h->gemm_ws, h->gemm_ws_bytes, s);
-  if (st != BAS_OK) return st;
+  int st;
+  if (h->ldx == h->k) {
+    // selection and contraction: one launch where the shape allows, else two
+    st = bas_select_gemm(h->x_dev, h->ldx, h->packed, batch, h->k, h->n, n_keep, score_kind, -1.0, h->y_dev, h->n,
+                         h->ids_dev, h->ids_dev + h->nb, nullptr, nullptr, h->gemm_ws, h->gemm_ws_bytes, h->sel_ws,
+                         h->sel_ws_bytes, 0, s);
+    if (st != BAS_OK) return st;
+  } else {
+    // K is not a multiple of 8: the selection scores the K real channels, the contraction runs over
+    // the zero-padded rows
+    st = bas_select_topk(h->x_dev, h->ldx, batch, h->k, n_keep, score_kind, h->ids_dev, h->ids_dev + h->nb, nullptr,
+                         nullptr, h->sel_ws, h->sel_ws_bytes, s);
+    if (st != BAS_OK) return st;
+    st = bas_gemm(h->x_dev, h->ldx, h->packed, h->ids_dev, h->ids_dev + h->nb, n_keep, nullptr, batch, (int)h->ldx, h->n,
+                  h->y_dev, h->n, h->gemm_ws, h->gemm_ws_bytes, s);
+    if (st != BAS_OK) return st;
+  }
   e = cudaMemcpyAsync(y_dst, h->y_dev, (size_t)batch * h->n * 2, cudaMemcpyDeviceToHost, s);
   if (e != cudaSuccess) return cuda_fail(e);
   if (want_ids) {

@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(256) build_bitmap_kernel(const int32_t* __rest
 // Restates scripts/bench_roundrobin_e2e_decode.py:90-113 and
 // scripts/bench_alpaca_energy_budget_e2e.py:43-62 in one launch without host synchronisation.
 // ---------------------------------------------------------------------------------------------
-constexpr int kSelThreads = 256;
+constexpr int kSelThreads = 1024;                    // largest block size; the launch picks 256 or 1024
 constexpr int kSelBlocksPerCta = 2;                  // activation blocks scored per CTA
 constexpr int kSelMaxBatch = 1024;
 
@@ -79,13 +79,14 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   pdl_launch_dependents();
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nthreads = (int)blockDim.x;   // 256 for small batches, 1024 for large ones (measured)
   const int j0 = blockIdx.x * kSelBlocksPerCta;
   const int nj = min(kSelBlocksPerCta, p.nb - j0);
 
   // ---- phase 1: 8 lanes per (row, block) pair, 16 bytes per lane ----
   const int sub = tid & 7, grp = tid >> 3;           // 32 groups of 8 lanes
   const int pairs = nj * p.batch;
-  for (int base = 0; base < pairs; base += kSelThreads / 8) {
+  for (int base = 0; base < pairs; base += nthreads / 8) {
     const int pr = base + grp;
     double e = 0.0;
     if (pr < pairs) {
@@ -138,13 +139,15 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   double* s_score = s_dyn;                              // [nb]
   int* s_rank = (int*)(s_dyn + p.nb);                   // [nb]
   int* s_order = s_rank + p.nb;                         // [nb] block id at each rank (budget mode)
-  for (int j = tid; j < p.nb; j += kSelThreads) {
+  for (int j = tid; j < p.nb; j += nthreads) {
     const double s = __ldcg(p.ws_scores + j);
     s_score[j] = s;
     if (p.scores_out != nullptr) p.scores_out[j] = s;
   }
   __syncthreads();
-  for (int j = tid; j < p.nb; j += kSelThreads) {
+  // one thread per block counts the blocks that rank before it (about 30 k comparisons in all: the
+  // instruction issue of one SM bounds this step at roughly 0.8 us whatever the thread count)
+  for (int j = tid; j < p.nb; j += nthreads) {
     const double sj = s_score[j];
     int rank = 0;
     for (int i = 0; i < p.nb; ++i) {
@@ -176,7 +179,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   const int keep = s_keep;
   // ascending compaction of the kept ids
   int running = 0;
-  for (int base = 0; base < p.nb; base += kSelThreads) {
+  for (int base = 0; base < p.nb; base += nthreads) {
     const int j = base + tid;
     const bool kept = (j < p.nb) && (s_rank[j] < keep);
     if (j < p.nb && p.bitmap_out != nullptr) p.bitmap_out[j] = kept ? 1 : 0;
@@ -186,7 +189,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     int off = running;
     for (int w = 0; w < warp; ++w) off += s_warp_cnt[w];
     if (kept) p.ids_out[off + __popc(m & ((1u << lane) - 1u))] = j;
-    for (int w = 0; w < kSelThreads / 32; ++w) running += s_warp_cnt[w];
+    for (int w = 0; w < nthreads / 32; ++w) running += s_warp_cnt[w];
     __syncthreads();
   }
   if (tid == 0) *p.count_out = keep;
@@ -221,7 +224,8 @@ cudaError_t launch_select(const SelectParams& p, int sm_count, cudaStream_t stre
     if (smem > 96 * 1024) return cudaErrorInvalidValue;
   }
   count_launch();
-  return launch_with_pdl(select_kernel, grid, kSelThreads, smem, 1, stream, p);
+  // 1024 threads score 128 (block, row) pairs per round instead of 32: pays from about 32 rows
+  return launch_with_pdl(select_kernel, grid, p.batch >= 32 ? kSelThreads : 256, smem, 1, stream, p);
 }
 
 }  // namespace bas

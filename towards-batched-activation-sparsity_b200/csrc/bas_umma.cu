@@ -97,7 +97,8 @@ inline size_t fused_select_scratch(int nb_sel, int cluster, int batch) {
 // then every CTA ranks all blocks and compacts the kept ids, ascending, into s_ids.  Returns the
 // number kept.  All threads of the CTA (and all CTAs of the cluster) must call it.
 __device__ __forceinline__ int fused_select(const GemmParams& p, uint8_t* scratch, uint16_t* s_ids, int* s_warp_cnt,
-                                            int* s_keep, int crank, int C, int tid, int nthreads) {
+                                            int* s_keep, int crank, int C, int tid, int nthreads,
+                                            [[maybe_unused]] long long t0) {
   const int nb = p.sel.nb_sel, batch = p.batch;
   const bool bf16 = (p.flags & kFlagBf16) != 0;
   double* s_score = (double*)scratch;
@@ -107,17 +108,28 @@ __device__ __forceinline__ int fused_select(const GemmParams& p, uint8_t* scratc
   const int lane = tid & 31, warp = tid >> 5;
   const int nmine = (nb > crank) ? (nb - crank + C - 1) / C : 0;
 
-  // ---- scores of this CTA's blocks: 8 lanes per (block, row) pair, 16 bytes per lane ----
+  // ---- scores of this CTA's blocks: 8 lanes per (block, row) pair, 16 bytes per lane; four pairs
+  // per lane group and round, loaded together so that their latencies overlap ----
   const int sub = tid & 7, grp = tid >> 3;
   const int pairs = nmine * batch;
-  for (int base = 0; base < pairs; base += nthreads / 8) {
-    const int pr = base + grp;
-    double e = 0.0;
-    if (pr < pairs) {
-      const int jj = pr / batch, b = pr - jj * batch;
-      const uint4 v = __ldg((const uint4*)(p.x + (size_t)b * p.ldx + (size_t)(crank + jj * C) * kBlockK) + sub);
+  const int groups = nthreads / 8;
+  for (int base = 0; base < pairs; base += 4 * groups) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int pr = base + u * groups + grp;
+      v[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (pr < pairs) {
+        const int jj = pr / batch, b = pr - jj * batch;
+        v[u] = __ldg((const uint4*)(p.x + (size_t)b * p.ldx + (size_t)(crank + jj * C) * kBlockK) + sub);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int pr = base + u * groups + grp;
+      double e = 0.0;
       if (bf16) {
-        const unsigned int* wds = (const unsigned int*)&v;
+        const unsigned int* wds = (const unsigned int*)&v[u];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const double lo = (double)__uint_as_float(wds[q] << 16), hi = (double)__uint_as_float(wds[q] & 0xffff0000u);
@@ -125,7 +137,7 @@ __device__ __forceinline__ int fused_select(const GemmParams& p, uint8_t* scratc
           e += hi * hi;
         }
       } else {
-        const __half2* h = (const __half2*)&v;
+        const __half2* h = (const __half2*)&v[u];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const float2 f = __half22float2(h[q]);
@@ -133,13 +145,14 @@ __device__ __forceinline__ int fused_select(const GemmParams& p, uint8_t* scratc
           e += (double)(f.y * f.y);
         }
       }
+      e += __shfl_xor_sync(0xffffffffu, e, 1);
+      e += __shfl_xor_sync(0xffffffffu, e, 2);
+      e += __shfl_xor_sync(0xffffffffu, e, 4);
+      if (pr < pairs && sub == 0) s_pair[pr] = (p.sel.score_kind == BAS_SCORE_NORM) ? sqrt(e) : e;
     }
-    e += __shfl_xor_sync(0xffffffffu, e, 1);
-    e += __shfl_xor_sync(0xffffffffu, e, 2);
-    e += __shfl_xor_sync(0xffffffffu, e, 4);
-    if (pr < pairs && sub == 0) s_pair[pr] = (p.sel.score_kind == BAS_SCORE_NORM) ? sqrt(e) : e;
   }
   __syncthreads();
+  if (tid == 0) BAS_TRACE_SET(20, BAS_TRACE_CLOCK() - t0);   // pair scores done
   const uint32_t score_base = smem_u32(s_score);
   for (int jj = tid; jj < nmine; jj += nthreads) {
     double sum = 0.0;
@@ -151,15 +164,19 @@ __device__ __forceinline__ int fused_select(const GemmParams& p, uint8_t* scratc
       if (q < C) dsmem_st_f64(dsmem_addr(score_base + (uint32_t)j * 8u, (uint32_t)q), score);
   }
   cluster_sync_all();   // every CTA of the cluster now holds every score
+  if (tid == 0) BAS_TRACE_SET(21, BAS_TRACE_CLOCK() - t0);   // scores exchanged
 
   // ---- rank all blocks: four threads per block ----
+  // Scores are sums of squares or of norms: never negative, never NaN for finite inputs, so they order
+  // like their bit patterns read as unsigned integers (integer compares are far cheaper than fp64 ones).
+  const unsigned long long* s_bits = (const unsigned long long*)s_score;
   for (int j0 = 0; j0 < nb; j0 += nthreads / 4) {
     const int j = j0 + (tid >> 2), quad = tid & 3;
     int rank = 0;
     if (j < nb) {
-      const double sj = s_score[j];
+      const unsigned long long sj = s_bits[j];
       for (int i = quad; i < nb; i += 4) {
-        const double si = s_score[i];
+        const unsigned long long si = s_bits[i];
         rank += (si > sj || (si == sj && i < j)) ? 1 : 0;
       }
     }
@@ -171,6 +188,7 @@ __device__ __forceinline__ int fused_select(const GemmParams& p, uint8_t* scratc
     }
   }
   __syncthreads();
+  if (tid == 0) BAS_TRACE_SET(22, BAS_TRACE_CLOCK() - t0);   // ranked
   if (tid == 0) {
     int keep = p.sel.n_keep;
     if (p.sel.mode == 2) {
@@ -217,6 +235,7 @@ __device__ __forceinline__ int fused_select(const GemmParams& p, uint8_t* scratc
     __syncthreads();
   }
   if (writer && tid == 0 && p.sel.count_out != nullptr) *p.sel.count_out = keep;
+  if (tid == 0) BAS_TRACE_SET(23, BAS_TRACE_CLOCK() - t0);   // list compacted
   return keep;
 }
 
@@ -311,7 +330,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     // Mask selection by this cluster, for itself.  X (and the caller's id / count / byte-map arrays,
     // which CTA 0 writes) may still be in use by the kernel before this one: wait first.
     pdl_wait();
-    const int kept = fused_select(p, s_stage, s_ids, hdr->sel_warp_cnt, &hdr->sel_keep, rank, C, tid, kUmmaThreads);
+    if (tid == 0) BAS_TRACE_SET(19, BAS_TRACE_CLOCK() - hdr->t0);   // previous kernel done
+    const int kept = fused_select(p, s_stage, s_ids, hdr->sel_warp_cnt, &hdr->sel_keep, rank, C, tid, kUmmaThreads,
+                                  hdr->t0);
     if (tid == 0) hdr->k_act = kept;
     __syncthreads();
   }
@@ -1015,7 +1036,11 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   if (e != cudaSuccess) return e;
   if (p.sel.mode != 0) {
     // the in-kernel selection needs a cluster to share the scoring and room for its scratch in the ring
-    if (cluster < 2 || p.tp.world > 0 ||
+    // ... and pays only while a CTA's share of the scoring is small (every cluster repeats it:
+    // measured against the two-launch chain, up to about 256 (block, row) pairs per CTA)
+    const long long pairs_per_cta = (long long)((p.sel.nb_sel + cluster - 1) / cluster) * p.batch;
+    const bool forced_sel = (p.flags & (1 << 24)) != 0;   // tuning knob: in-kernel selection whatever the size
+    if (cluster < 2 || p.tp.world > 0 || (pairs_per_cta > 256 && !forced_sel) ||
         fused_select_scratch(p.sel.nb_sel, cluster, p.batch) > (size_t)p.stages * group * stage_bytes)
       return cudaErrorNotSupported;
     count_launch();
