@@ -494,7 +494,7 @@ def run_gpu(args) -> None:
         # the three calls of a step are independent: submit them on three handles (own streams, so the
         # copies of one overlap the kernels of another), then collect the three results
         used = []
-        for bb in sorted(BATCHES, reverse=True):      # largest upload first: its kernels run under the others' copies
+        for bb in BATCHES:                            # smallest upload first (measured: 116 vs 127 us per step)
             h = handles[call["i"] % E2E_COPIES]
             call["i"] += 1
             abi.check(abi.lib.bas_linear_submit_host(h, x_host[bb].ctypes.data, bb, N_KEEP[bb], abi.SCORE_NORM,
