@@ -842,3 +842,24 @@ def test_select_gemm_ties_and_chained_calls(dev):
         want = O.topk_ids(O.block_scores(xs[i], O.SCORE_ENERGY), 23)
         assert np.array_equal(idbufs[i][:23].cpu().numpy(), want), i
         assert O.max_err_ratio(outs[i].cpu().numpy(), O.masked_gemm(xs[i], w, want)) <= TOL, i
+
+
+@pytest.mark.parametrize("b,k,n", [(4, 4096, 2048), (16, 11008, 4096)])
+def test_select_gemm_bf16(dev, b, k, n):
+    """bf16 activations through the one-call selection + contraction (in-kernel selection for the
+    small case, the two-launch chain for the large one)."""
+    ops = _ops()
+    nb = k // 64
+    x, w = _bf16_inputs(b, k, n, seed=60 + b, dist="laplace")
+    tx = torch.from_numpy(x).to(dev).to(torch.bfloat16)
+    packed = ops.pack_weight(torch.from_numpy(w).to(dev).to(torch.bfloat16))
+    scores = O.block_scores(x, O.SCORE_ENERGY)
+    n_keep = O.n_keep_from_density(0.36, nb)
+    want = O.topk_ids(scores, n_keep)
+    out = torch.full((b, n), float("nan"), dtype=torch.bfloat16, device=dev)
+    ids, count = ops.select_gemm(tx, packed, out, n_keep, O.SCORE_ENERGY)
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
+    assert int(count.item()) == n_keep
+    assert np.array_equal(ids[:n_keep].cpu().numpy(), want)
+    assert O.max_err_ratio(out.float().cpu().numpy(), O.masked_gemm(x, w, want)) <= TOL_BF16

@@ -447,14 +447,19 @@ struct bas_linear {
   uint8_t* packed = nullptr;
   __half* x_dev = nullptr;
   __half* y_dev = nullptr;
-  int32_t* ids_dev = nullptr;    // [nb] ids followed by [1] count
-  void* gemm_ws = nullptr;
+  // one small device block, mirrored in pinned host memory and fetched with a single copy:
+  // [0, 256) the contraction's workspace (status word first), then [nb] ids and [1] count
+  void* small_dev = nullptr;
+  void* small_pin = nullptr;
+  size_t small_bytes = 0;
+  int32_t* ids_dev = nullptr;    // inside small_dev
+  void* gemm_ws = nullptr;       // inside small_dev
   size_t gemm_ws_bytes = 0;
   void* sel_ws = nullptr;
   size_t sel_ws_bytes = 0;
   void* x_pin = nullptr;         // pinned staging, so that the copies are truly asynchronous
   void* y_pin = nullptr;
-  int32_t* ids_pin = nullptr;
+  int32_t* ids_pin = nullptr;    // inside small_pin
   long long ldx = 0;
   // the forward in flight (bas_linear_submit_host .. bas_linear_wait)
   bool pending = false, y_direct = false;
@@ -478,12 +483,11 @@ static void linear_free(bas_linear* h) {
   if (h->packed) cudaFree(h->packed);
   if (h->x_dev) cudaFree(h->x_dev);
   if (h->y_dev) cudaFree(h->y_dev);
-  if (h->ids_dev) cudaFree(h->ids_dev);
-  if (h->gemm_ws) cudaFree(h->gemm_ws);
+  if (h->small_dev) cudaFree(h->small_dev);
   if (h->sel_ws) cudaFree(h->sel_ws);
   if (h->x_pin) cudaFreeHost(h->x_pin);
   if (h->y_pin) cudaFreeHost(h->y_pin);
-  if (h->ids_pin) cudaFreeHost(h->ids_pin);
+  if (h->small_pin) cudaFreeHost(h->small_pin);
   for (auto& g : h->graphs)
     if (g.exec != nullptr) cudaGraphExecDestroy(g.exec);
   if (h->stream) cudaStreamDestroy(h->stream);
@@ -509,14 +513,17 @@ int bas_linear_create(bas_linear** out, const void* w_host, int n, int k, int ma
   BAS_TRY(cudaMalloc(&h->packed, bas_packed_weight_bytes(n, k)));
   BAS_TRY(cudaMalloc(&h->x_dev, (size_t)max_batch * h->ldx * 2));
   BAS_TRY(cudaMalloc(&h->y_dev, (size_t)max_batch * n * 2));
-  BAS_TRY(cudaMalloc(&h->ids_dev, sizeof(int32_t) * ((size_t)h->nb + 1)));
   h->gemm_ws_bytes = bas_gemm_workspace_bytes(max_batch, n);
+  h->small_bytes = h->gemm_ws_bytes + sizeof(int32_t) * ((size_t)h->nb + 1);
+  BAS_TRY(cudaMalloc(&h->small_dev, h->small_bytes));
+  h->gemm_ws = h->small_dev;
+  h->ids_dev = (int32_t*)((uint8_t*)h->small_dev + h->gemm_ws_bytes);
   h->sel_ws_bytes = bas_select_workspace_bytes(k);
-  BAS_TRY(cudaMalloc(&h->gemm_ws, h->gemm_ws_bytes));
   BAS_TRY(cudaMalloc(&h->sel_ws, h->sel_ws_bytes));
   BAS_TRY(cudaMallocHost(&h->x_pin, (size_t)max_batch * h->ldx * 2));
   BAS_TRY(cudaMallocHost(&h->y_pin, (size_t)max_batch * n * 2));
-  BAS_TRY(cudaMallocHost((void**)&h->ids_pin, sizeof(int32_t) * ((size_t)h->nb + 1)));
+  BAS_TRY(cudaMallocHost(&h->small_pin, h->small_bytes));
+  h->ids_pin = (int32_t*)((uint8_t*)h->small_pin + h->gemm_ws_bytes);
   BAS_TRY(cudaMemsetAsync(h->x_dev, 0, (size_t)max_batch * h->ldx * 2, h->stream));
   BAS_TRY(cudaMemsetAsync(h->gemm_ws, 0, h->gemm_ws_bytes, h->stream));
   BAS_TRY(cudaMemsetAsync(h->sel_ws, 0, h->sel_ws_bytes, h->stream));
@@ -573,11 +580,9 @@ static int linear_enqueue_selected(bas_linear* h, const void* x_src, int batch, 
   }
   e = cudaMemcpyAsync(y_dst, h->y_dev, (size_t)batch * h->n * 2, cudaMemcpyDeviceToHost, s);
   if (e != cudaSuccess) return cuda_fail(e);
-  if (want_ids) {
-    e = cudaMemcpyAsync(h->ids_pin, h->ids_dev, sizeof(int32_t) * n_keep, cudaMemcpyDeviceToHost, s);
-    if (e != cudaSuccess) return cuda_fail(e);
-  }
-  e = cudaMemcpyAsync(h->ids_pin + h->nb, h->gemm_ws, sizeof(unsigned int), cudaMemcpyDeviceToHost, s);
+  // status word, and the ids when the caller wants them: one copy
+  e = cudaMemcpyAsync(h->small_pin, h->small_dev, want_ids ? h->gemm_ws_bytes + sizeof(int32_t) * n_keep : sizeof(unsigned int),
+                      cudaMemcpyDeviceToHost, s);
   return e == cudaSuccess ? BAS_OK : cuda_fail(e);
 }
 
@@ -663,7 +668,7 @@ static int linear_submit(bas_linear* h, const void* x_host, int batch, int n_kee
     if (st != BAS_OK) return st;
     e = cudaMemcpyAsync(y_dst, h->y_dev, (size_t)batch * h->n * 2, cudaMemcpyDeviceToHost, s);
     if (e != cudaSuccess) return cuda_fail(e);
-    e = cudaMemcpyAsync(h->ids_pin + h->nb, h->gemm_ws, sizeof(unsigned int), cudaMemcpyDeviceToHost, s);
+    e = cudaMemcpyAsync(h->small_pin, h->gemm_ws, sizeof(unsigned int), cudaMemcpyDeviceToHost, s);
     if (e != cudaSuccess) return cuda_fail(e);
     ids_host_out = nullptr;   // the caller's own ids: nothing to hand back
   } else {
@@ -687,7 +692,7 @@ static int linear_wait(bas_linear* h) {
   if (e != cudaSuccess) return cuda_fail(e);
   if (!h->y_direct) std::memcpy(h->pend_y, h->y_pin, (size_t)h->pend_batch * h->n * 2);
   if (h->pend_ids != nullptr && h->pend_k > 0) std::memcpy(h->pend_ids, h->ids_pin, sizeof(int32_t) * h->pend_k);
-  unsigned int* flag_pin = (unsigned int*)(h->ids_pin + h->nb);
+  unsigned int* flag_pin = (unsigned int*)h->small_pin;
   if (*flag_pin != 0) {
     cudaMemsetAsync(h->gemm_ws, 0, sizeof(unsigned int), h->stream);
     return BAS_ERR_DEVICE_FLAG;
