@@ -571,7 +571,7 @@ def run_gpu(args) -> None:
         dist.destroy_process_group()
 
 
-def run_profile_case(batch: int) -> None:
+def run_profile_case(batch: int, family: int = 0) -> None:
     """A few eager launches of one batch size on 4 rotating weight copies (360 MB, larger than L2):
     the small case that profiler captures of the contraction kernels are taken on."""
     import torch
@@ -587,9 +587,9 @@ def run_profile_case(batch: int) -> None:
     out = torch.zeros(batch, N_OUT, dtype=torch.float16, device=dev)
     for i in range(8):
         ids, cnt = ops.select_topk(x, nk, abi.SCORE_NORM)
-        ops.gemm(x, packed[i % 4], out, ids=ids)
+        ops.gemm(x, packed[i % 4], out, ids=ids, family=family)
     torch.cuda.synchronize()
-    print(f"profile case B={batch}: 8 select + 8 gemm launches, status {ops.read_status(dev)}")
+    print(f"profile case B={batch} family={family}: 8 select + 8 gemm launches, status {ops.read_status(dev)}")
 
 
 def main() -> None:
@@ -600,6 +600,8 @@ def main() -> None:
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--profile-case", type=int, default=0, metavar="B",
                     help="run only a few eager launches at batch B (for profiler captures) and exit")
+    ap.add_argument("--profile-family", type=int, default=0, choices=[0, 1, 2],
+                    help="kernel family of the profile case: 0 default, 1 CUDA-core kernel (batch <= 8), 2 tcgen05")
     args = ap.parse_args()
     # stdout carries exactly one JSON line: libraries that chat on fd 1 (NCCL prints its version
     # there) are sent to stderr, and the line is written to the saved descriptor at the end.
@@ -608,7 +610,7 @@ def main() -> None:
     _STDOUT_FD = os.dup(1)
     os.dup2(2, 1)
     if args.profile_case:
-        run_profile_case(args.profile_case)
+        run_profile_case(args.profile_case, args.profile_family)
     elif args.impl == "reference":
         run_reference(args)
     else:
