@@ -950,36 +950,40 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   const int units = p.npad / 8;
   const size_t fixed = umma_fixed_smem(p.nb);
 
-  // Work split (measured).  Bringing up a CTA of this kernel costs the launch about 25 ns, one after
-  // the other, and an SM can take in about 100 GB/s: small problems finish sooner on few CTAs, and
-  // only tens of megabytes want every SM.  The grid is sized for about 96 KiB of weights per CTA.
-  // Shape: a cluster of 4 CTAs per column range of up to 128 columns (the cluster splits the active
-  // blocks and finishes its range in one pass) when that does not overshoot the CTA budget by more
-  // than half - always, for batches above 32 rows, whose activation traffic a cluster divides by
-  // four - else a cluster of 2 (batch <= 32), else one CTA per range walking 128-column passes.
+  // Work split (measured over output widths 512..22016, 1.5..65 MB of active weights, batches 2..64).
+  // Two things decide it.  (1) How many CTAs: consecutive calls of a stream overlap - the next call's
+  // CTAs come up on free SMs, stage their ids and stream a ring-full of weights while this call is
+  // still running - but only if this call leaves SMs free; and one SM takes in about 100 GB/s, so
+  // about half the SMs already saturate HBM.  Hence: about 96 KiB of active weights per CTA for
+  // small problems, at most half the SMs up to about 25 MB, all but twenty of them beyond.  (2) The
+  // shape: a cluster of 4 CTAs per column range of up to 128 columns (the cluster splits the active
+  // blocks, quartering the copies and MMAs issued per byte and the activation traffic per SM, and
+  // finishes its range in one pass), else a cluster of 2, else one CTA per range walking 128-column
+  // passes; the first of these whose CTA count stays within 15 % of the target is taken.
   const int forced = (p.flags >> 8) & 7;
   const int cta_cap = ((p.flags >> 16) & 0xff) != 0 ? ((p.flags >> 16) & 0xff) : sm_count;   // tuning knob
   // active blocks expected: the list length, or with a byte map the caller's hint (else half of all)
   const int k_est = p.k_host > 0 ? p.k_host : (p.nb + 1) / 2;
   const double bytes = (double)k_est * kBlockK * 2.0 * (double)p.n;
-  int budget = (int)(bytes / (96.0 * 1024.0)) + 1;
-  if (budget < 16) budget = 16;
-  if (budget > cta_cap) budget = cta_cap;
+  int target = (int)(bytes / (96.0 * 1024.0)) + 1;
+  if (target < 16) target = 16;
+  if (target > sm_count / 2) target = (bytes >= 25.0e6) ? sm_count - 20 : sm_count / 2;
+  if (target > cta_cap) target = cta_cap;
   const int r_min = (units + kTileN / 8 - 1) / (kTileN / 8);   // fewest ranges of at most 128 columns
-  // without a cluster: one pass per CTA where the CTA cap allows it (a second pass re-reads X)
-  int cluster = 1, ranges = budget > r_min ? budget : (r_min < cta_cap ? r_min : cta_cap);
+  // without a cluster: one pass per CTA (a second pass re-reads X) if that takes at most twice the
+  // target number of CTAs
+  int cluster = 1, ranges = (r_min > target && r_min <= 2 * target && r_min <= cta_cap) ? r_min : target;
   if (ranges > units) ranges = units;
   for (int c = 4; c >= 2 && forced != 1; c -= 2) {
     if (forced != 0 && c != forced) continue;
-    if (forced == 0 && c == 2 && BPAD > 32) continue;
     int resident = max_resident_clusters<BPAD>(c, kSmemBudget, sm_count);
     if (resident > cta_cap / c) resident = cta_cap / c;
     if (resident > units) resident = units;
-    if (r_min > resident) continue;                                   // the widest range must fit one pass
-    if (forced == 0 && BPAD <= 32 && 2 * r_min * c > 3 * budget) continue;   // too many CTAs for the work
-    int r = budget / c;
+    if (r_min > resident) continue;                               // the widest range must fit one pass
+    int r = target / c;
     if (r < r_min) r = r_min;
     if (r > resident) r = resident;
+    if (forced == 0 && 20 * r * c > 23 * target) continue;        // too many CTAs for the work
     cluster = c;
     ranges = r;
     break;
