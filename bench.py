@@ -551,7 +551,7 @@ def run_gpu(args) -> None:
         }
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
         # profiles/umma_colsplit_down_proj_b64.md (same workload, one launch)
-        roofline["traffic"] = 44_313_984
+        roofline["traffic"] = 44_325_760
         cpu = cpu_baseline() if world == 1 else None
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
