@@ -764,27 +764,39 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     for (int c0 = 0; c0 < width && good; c0 += kTileN) {
       const int col = n0 + c0 + rz;
       if (c0 + rz < width && col < p.n)
-        for (int row = rank + C * eset; row < p.batch && good; row += 2 * C) {
+        for (int row = rank + C * eset; row < p.batch && good; row += 4 * C) {
+          // two of this thread's rows per round, all their source words requested together: the
+          // round trips to memory overlap instead of adding up
+          const int row2 = row + 2 * C;
+          const bool have2 = row2 < p.batch;
           const size_t off = (size_t)row * (size_t)p.tp.ldp + (size_t)col;
-          unsigned long long words[kTpMaxRanks];
+          const size_t off2 = (size_t)(have2 ? row2 : row) * (size_t)p.tp.ldp + (size_t)col;
+          unsigned long long words[kTpMaxRanks], words2[kTpMaxRanks];
 #pragma unroll
-          for (int q = 0; q < kTpMaxRanks; ++q)   // all sources at once: their latencies overlap
+          for (int q = 0; q < kTpMaxRanks; ++q) {
             words[q] = (q < p.tp.world) ? ld_relaxed_sys_u64(recv + (size_t)q * (size_t)p.tp.src_words + off) : 0ull;
-          float sum = 0.f;
+            words2[q] = (q < p.tp.world) ? ld_relaxed_sys_u64(recv + (size_t)q * (size_t)p.tp.src_words + off2) : 0ull;
+          }
+          float sum = 0.f, sum2 = 0.f;
 #pragma unroll
           for (int q = 0; q < kTpMaxRanks; ++q)
             if (q < p.tp.world) {   // rank order
-              while ((unsigned int)(words[q] >> 32) != tp_epoch) {
+              while ((unsigned int)(words[q] >> 32) != tp_epoch || (unsigned int)(words2[q] >> 32) != tp_epoch) {
                 if (clock64() - t_start > kWaitCycles) {
                   good = false;
                   break;
                 }
                 __nanosleep(32);
                 words[q] = ld_relaxed_sys_u64(recv + (size_t)q * (size_t)p.tp.src_words + off);
+                words2[q] = ld_relaxed_sys_u64(recv + (size_t)q * (size_t)p.tp.src_words + off2);
               }
               sum += __uint_as_float((unsigned int)words[q]);
+              sum2 += __uint_as_float((unsigned int)words2[q]);
             }
-          if (good) store_out16(p.y + (size_t)row * p.ldy + col, sum, bf16);
+          if (good) {
+            store_out16(p.y + (size_t)row * p.ldy + col, sum, bf16);
+            if (have2) store_out16(p.y + (size_t)row2 * p.ldy + col, sum2, bf16);
+          }
         }
     }
     if (!good && hdr->abort_flag == 0) atomicOr(p.status, BAS_DEV_WAIT_EXPIRED);
@@ -968,6 +980,9 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   int target = (int)(bytes / (96.0 * 1024.0)) + 1;
   if (target < 16) target = 16;
   if (target > sm_count / 2) target = (bytes >= 25.0e6) ? sm_count - 20 : sm_count / 2;
+  // a call that also exchanges its result with the other ranks of a box spreads that work (a few
+  // words per thread to send and to wait for) over at least half the SMs
+  if (p.tp.world > 1 && target < sm_count / 2) target = sm_count / 2;
   if (target > cta_cap) target = cta_cap;
   const int r_min = (units + kTileN / 8 - 1) / (kTileN / 8);   // fewest ranges of at most 128 columns
   // without a cluster: one pass per CTA (a second pass re-reads X) if that takes at most twice the
