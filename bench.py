@@ -544,7 +544,7 @@ def run_gpu(args) -> None:
     if rank == 0:
         dom = per_batch["64"]
         roofline = {
-            "bound": "hbm", "kernel": "umma_colsplit_kernel<64> (B=64, 83 of 172 blocks)",
+            "bound": "hbm", "kernel": "umma_colsplit_kernel<64, false, false> (B=64, 83 of 172 blocks)",
             "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
             "algorithmic_bytes_per_launch": N_KEEP[64] * SLAB_BYTES, "traffic": None,
