@@ -21,6 +21,10 @@
 // them and store or, in cluster mode, push them to the owning CTA.  All waits are bounded mbarrier
 // waits; TMEM is released on every path.
 //
+// Two variants are instantiated beside the plain kernel: TP sends the result as fp32 partials to the
+// other ranks of a box and adds theirs (row-parallel linears), SEL selects the batch's mask itself
+// before multiplying (cluster modes, small batches).
+//
 // Replaces the reference's bitmap/index-list tl.dot kernels and their split-K
 // pairs (kernels/shared_mask_batched_triton_min_runtime.py:814-874, 1150-1216, 1956-1988).
 #include "bas_kernels.cuh"
