@@ -50,6 +50,30 @@ def main() -> None:
         same = all(torch.equal(g, gathered[0]) for g in gathered)
         if status != 0 or not err <= TOL or not same:
             failures.append((b, k, n, n_keep, status, err, same))
+    # ranks that split the work differently (another grid size, another cluster shape, an id list of
+    # another length): elements are exchanged by (row, column), so the sums must not care
+    for b, k, n, n_keep in [(16, 11008, 4096, 62), (64, 4096, 4096, 23), (5, 2048, 4104, 9)]:
+        nb = (k + 63) // 64
+        x_h = O.make_activations(b, k, seed=500 + call, dist="laplace")
+        w_h = O.make_weight(n, k, seed=600 + call)
+        ids_h = O.random_active_blocks(nb, n_keep, seed=700 + call)
+        b0, b1 = tp.row_shard_blocks(k, world, rank)
+        k0, k1 = b0 * 64, min(b1 * 64, k)
+        local = ids_h[(ids_h >= b0) & (ids_h < b1)] - b0
+        x = torch.from_numpy(x_h).to(dev)
+        packed = ops.pack_weight(torch.from_numpy(np.ascontiguousarray(w_h[:, k0:k1])).to(dev))
+        out = torch.full((b, n), float("nan"), dtype=torch.float16, device=dev)
+        ops.gemm(x[:, k0:k1], packed, out, ids=torch.from_numpy(np.ascontiguousarray(local, dtype=np.int32)).to(dev),
+                 tp=group, cluster=(1, 2, 4, 0)[rank % 4], max_ctas=(40, 96, 0, 148)[rank % 4])
+        call += 1
+        torch.cuda.synchronize()
+        status = ops.read_status(dev)
+        err = O.max_err_ratio(out.float().cpu().numpy(), O.masked_gemm(x_h, w_h, ids_h))
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        same = all(torch.equal(g, gathered[0]) for g in gathered)
+        if status != 0 or not err <= TOL or not same:
+            failures.append(("mixed grids", b, k, n, n_keep, status, err, same))
     # the layer stack: in-kernel sums against NCCL all-reduces of fp16 partials
     outs = {}
     for mode in ("nccl", "in_kernel"):
