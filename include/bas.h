@@ -101,6 +101,12 @@ BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, con
  *             with this flag it starts streaming weight tiles while the previous kernel is still
  *             draining, and waits for it only before reading X and writing Y.  Without the flag
  *             only the kernel's own preamble overlaps.  Ignored when count_dev is given.
+ *   BAS_GEMM_X_STABLE  (with BAS_GEMM_IDS_STABLE, tcgen05 kernel; ignored otherwise) the caller
+ *             promises the same of x_dev: X was complete before the preceding kernel started
+ *             (a resident input, or the X the preceding call of this library already read, as for
+ *             q/k/v or gate/up of one layer).  Nothing the kernel reads then depends on the kernel
+ *             before it: it streams and multiplies straight through and waits for that kernel only
+ *             before its first store to Y.
  *   bits 8-10 cluster size of the tcgen05 kernel: 0 = chosen by batch size, else 1, 2 or 4 CTAs
  *             share the active blocks of one column range (reduced on chip, in rank order).
  *   BAS_GEMM_BF16  X, the packed weight and Y hold bfloat16 instead of fp16 (the reference's kernels
@@ -113,6 +119,7 @@ BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, con
  *             clusters, also where the two-launch chain is measured faster (a tuning knob). */
 #define BAS_GEMM_IDS_STABLE 16
 #define BAS_GEMM_BF16 32
+#define BAS_GEMM_X_STABLE 64
 BAS_API int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
                 const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
                 void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream);
@@ -147,6 +154,17 @@ BAS_API int bas_select_topk(const void* x_dev, int64_t ldx, int batch, int k, in
 BAS_API int bas_select_budget(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
                       int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
                       double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream);
+/* bas_select_topk with the two optional score modifiers of _select_active_blocks
+ * (scripts/bench_roundrobin_e2e_decode.py:104-112, arguments block_score_scale and block_prior):
+ *   chan_scale_dev  optional fp32 [>= 64 * (K/64)], 16-byte aligned: with it a block's score is
+ *                   mean_b sum_i x[b,i]^2 * chan_scale[i], whatever score_kind says (as in the reference)
+ *   block_mult_dev  optional fp32 [K/64]: factor on the batch-mean score.  The reference's
+ *                   clamp(prior + eps, 1e-6) ** alpha is evaluated by the caller, once per prior.
+ * With both null it is bas_select_topk. */
+BAS_API int bas_select_topk_weighted(const void* x_dev, int64_t ldx, int batch, int k, int n_keep, int score_kind,
+                             const float* chan_scale_dev, const float* block_mult_dev, int32_t* ids_out_dev,
+                             int32_t* count_out_dev, uint8_t* bitmap_out_dev, double* scores_out_dev,
+                             void* ws_dev, size_t ws_bytes, void* stream);
 /* The same with score_flags = 0 or BAS_SCORE_BF16. */
 BAS_API int bas_select_budget_ex(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
                          int score_flags, int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,

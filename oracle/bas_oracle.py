@@ -114,10 +114,65 @@ def topk_ids(scores: np.ndarray, n_keep: int) -> np.ndarray:
     return np.sort(order[: int(n_keep)]).astype(np.int32)
 
 
+def make_channel_scale(k: int, seed: int) -> np.ndarray:
+    """Seeded float32 [k] positive per-channel weights, the stand-in for the squared column norms of
+    a weight that the reference passes as ``block_score_scale``."""
+    rng = np.random.default_rng(seed + 7_000_003)
+    return rng.uniform(0.25, 4.0, size=int(k)).astype(np.float32)
+
+
+def make_block_prior(nb: int, seed: int) -> np.ndarray:
+    """Seeded float32 [nb] in [0, 1): the stand-in for a per-block activation frequency
+    (``block_prior``)."""
+    rng = np.random.default_rng(seed + 9_000_011)
+    return rng.uniform(0.0, 1.0, size=int(nb)).astype(np.float32)
+
+
+def prior_multiplier(prior: np.ndarray, alpha: float = 1.0, eps: float = 0.1) -> np.ndarray:
+    """float32 [nb]: ``clamp(prior + eps, min=1e-6) ** alpha`` evaluated in float32, the factor the
+    reference multiplies the scores by (scripts/bench_roundrobin_e2e_decode.py:109-112)."""
+    p32 = np.asarray(prior, dtype=np.float32) + np.float32(eps)
+    p32 = np.maximum(p32, np.float32(1e-6))
+    return np.power(p32, np.float32(alpha)).astype(np.float32)
+
+
+def weighted_block_scores(x: np.ndarray, chan_scale: np.ndarray | None, block_mult: np.ndarray | None,
+                          kind: int = SCORE_NORM, block_k: int = BLOCK_K) -> np.ndarray:
+    """float64 [nb] scores with the reference's two optional modifiers
+    (scripts/bench_roundrobin_e2e_decode.py:104-112).  With ``chan_scale`` the score is
+    mean_b sum_i x[b,i]^2 * chan_scale[i] whatever ``kind`` says; ``block_mult`` (see
+    prior_multiplier) then multiplies the batch mean."""
+    if chan_scale is None:
+        s = block_scores(x, kind, block_k)
+    else:
+        x2 = np.asarray(x).reshape(-1, x.shape[-1])
+        nb = x2.shape[1] // block_k
+        xb = x2[:, : nb * block_k].astype(np.float64).reshape(x2.shape[0], nb, block_k)
+        sc = np.asarray(chan_scale, dtype=np.float32)[: nb * block_k].astype(np.float64).reshape(nb, block_k)
+        e = np.zeros((x2.shape[0], nb), dtype=np.float64)
+        for i in range(block_k):
+            e += (xb[:, :, i] * xb[:, :, i]) * sc[None, :, i]
+        s = np.zeros(nb, dtype=np.float64)
+        for b in range(x2.shape[0]):
+            s += e[b]
+        s = s / float(x2.shape[0])
+    if block_mult is not None:
+        s = s * np.asarray(block_mult, dtype=np.float32).astype(np.float64)
+    return s
+
+
 def select_active_blocks(x: np.ndarray, density: float, kind: int = SCORE_NORM,
-                         block_k: int = BLOCK_K) -> np.ndarray:
-    """Scores + uniform top-k, the per-step batch-shared mask (``_select_active_blocks``)."""
-    s = block_scores(x, kind, block_k)
+                         block_k: int = BLOCK_K, block_prior: np.ndarray | None = None,
+                         prior_alpha: float = 1.0, prior_eps: float = 0.1,
+                         block_score_scale: np.ndarray | None = None) -> np.ndarray:
+    """Scores + uniform top-k, the per-step batch-shared mask (``_select_active_blocks``,
+    scripts/bench_roundrobin_e2e_decode.py:90-113), with its optional channel weights and block
+    prior.  Like the reference, a prior whose length is not the block count is ignored."""
+    nb = np.asarray(x).shape[-1] // block_k
+    mult = None
+    if block_prior is not None and int(np.asarray(block_prior).size) == nb:
+        mult = prior_multiplier(block_prior, prior_alpha, prior_eps)
+    s = weighted_block_scores(x, block_score_scale, mult, kind, block_k)
     return topk_ids(s, n_keep_from_density(density, s.size))
 
 

@@ -7,7 +7,8 @@ Run where the reference checkout is available (it needs no GPU):
 The inputs are seeded and come from oracle/bas_oracle.py, so only the reference's OUTPUTS
 are stored (ids, bitmaps, small output matrices).  What is recorded, and from where:
 
-* selection_norm    scripts/bench_roundrobin_e2e_decode.py  _select_active_blocks
+* selection_norm    scripts/bench_roundrobin_e2e_decode.py  _select_active_blocks (also with its
+                    block_score_scale and block_prior arguments)
 * selection_energy  scripts/bench_alpaca_energy_budget_e2e.py  _block_energy, _topk_active,
                     _energy_budget_active
 * bitmap            kernels/shared_mask_batched_triton_min_runtime.py  _build_active_k_bitmap
@@ -52,6 +53,8 @@ SELECT_CASES = [
 ] + [(16, 11008, 0.36, "laplace", 100 + s) for s in range(11)]   # per-step online selection
 
 BUDGET_KEEPS = [0.5, 0.9, 0.99]
+N_WEIGHTED = 10                # the first cases are also recorded with channel weights / a block prior
+PRIOR_ALPHA, PRIOR_EPS = 0.5, 0.05
 
 GEMM_CASES = [
     # (batch, K, N, n_keep, dist, seed, split_k)
@@ -108,6 +111,17 @@ def main() -> None:
         for keep in BUDGET_KEEPS:
             ids_b = EB._energy_budget_active(energy, keep).numpy()
             out[f"select{ci}_budget{int(round(keep * 100))}_ids"] = ids_b.astype(np.int32)
+        if ci < N_WEIGHTED:
+            # the optional channel weights and block prior of _select_active_blocks
+            scale = torch.from_numpy(O.make_channel_scale(k, seed))
+            prior = torch.from_numpy(O.make_block_prior(nb, seed))
+            out[f"select{ci}_scale_ids"] = RR._select_active_blocks(
+                x3, density, 64, block_score_scale=scale).numpy().astype(np.int32)
+            out[f"select{ci}_prior_ids"] = RR._select_active_blocks(
+                x3, density, 64, block_prior=prior, prior_alpha=PRIOR_ALPHA, prior_eps=PRIOR_EPS).numpy().astype(np.int32)
+            out[f"select{ci}_scale_prior_ids"] = RR._select_active_blocks(
+                x3, density, 64, block_prior=prior, prior_alpha=1.0, prior_eps=0.1,
+                block_score_scale=scale).numpy().astype(np.int32)
         meta["select"].append(dict(batch=b, k=k, density=density, dist=dist, seed=seed))
 
     # ---- bitmap ----

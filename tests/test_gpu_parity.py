@@ -196,10 +196,12 @@ def test_block_additivity_at_full_size(dev, b):
     assert np.abs(ya + yb - yab).max() <= 2e-3 * scale
 
 
+@pytest.mark.parametrize("x_stable", [False, True])
 @pytest.mark.parametrize("b", [2, 16, 64])
-def test_back_to_back_launches_with_stable_ids(dev, b):
+def test_back_to_back_launches_with_stable_ids(dev, b, x_stable):
     """Chained launches overlap (programmatic dependent launch); with stable ids the next kernel
-    streams weights while the previous one drains.  Every result must still be exact."""
+    streams weights while the previous one drains, with stable X it also multiplies and waits
+    only before it stores.  Every result must still be exact."""
     ops = _ops()
     k, n = 11008, 4096
     w = O.make_weight(n, k, seed=41)
@@ -212,11 +214,40 @@ def test_back_to_back_launches_with_stable_ids(dev, b):
     torch.cuda.synchronize()
     for rep in range(3):
         for i in range(4):
-            ops.gemm(txs[i], packed, outs[i], ids=tids[i], ids_stable=True)
+            ops.gemm(txs[i], packed, outs[i], ids=tids[i], ids_stable=True, x_stable=x_stable)
     torch.cuda.synchronize()
     assert ops.read_status(dev) == 0
     for i in range(4):
         assert O.max_err_ratio(outs[i].cpu().numpy(), O.masked_gemm(xs[i], w, idl[i])) <= TOL
+
+
+def test_stable_x_chain_writing_one_output(dev):
+    """Calls that declare X stable still write Y in stream order: a chain of calls that all store
+    to ONE output buffer (different active sets, different rows of work) leaves the last call's
+    result, and a call whose output is a later call's input is ordered by leaving the flag off."""
+    ops = _ops()
+    b, k, n = 16, 4096, 4096
+    w = O.make_weight(n, k, seed=51)
+    packed = ops.pack_weight(torch.from_numpy(w).to(dev))
+    x = O.make_activations(b, k, seed=52)
+    tx = torch.from_numpy(x).to(dev)
+    idl = [O.random_active_blocks(64, nk, seed=nk) for nk in (60, 5, 33, 12)]
+    tids = [torch.from_numpy(i).to(dev) for i in idl]
+    out = torch.full((b, n), float("nan"), dtype=torch.float16, device=dev)
+    mid = torch.empty((b, n), dtype=torch.float16, device=dev)
+    torch.cuda.synchronize()
+    for i in range(4):
+        ops.gemm(tx, packed, out, ids=tids[i], ids_stable=True, x_stable=True)
+    torch.cuda.synchronize()
+    assert O.max_err_ratio(out.cpu().numpy(), O.masked_gemm(x, w, idl[3])) <= TOL
+    # producer -> consumer: the second call reads what the first stored, so it does not set the flag
+    ops.gemm(tx, packed, mid, ids=tids[0], ids_stable=True, x_stable=True)
+    ops.gemm(mid, packed, out, ids=tids[2], ids_stable=True)
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
+    y1 = mid.cpu().numpy()
+    assert O.max_err_ratio(y1, O.masked_gemm(x, w, idl[0])) <= TOL
+    assert O.max_err_ratio(out.cpu().numpy(), O.masked_gemm(y1, w, idl[2])) <= TOL
 
 
 @pytest.mark.parametrize("b", [2, 16])
@@ -313,6 +344,65 @@ def test_selection_matches_oracle(dev, b, k, kind):
         want = O.topk_ids(O.block_scores(x, kind), n_keep)
         assert cnt == n_keep and np.array_equal(ids, want)
         assert bm.sum() == n_keep
+
+
+def test_weighted_selection_matches_reference_golden(dev, golden):
+    """Channel weights and block prior of _select_active_blocks
+    (scripts/bench_roundrobin_e2e_decode.py:104-112) through bas_select_topk_weighted: ids bit-exact
+    against the vectors recorded from the reference and against the oracle, scores to fp64 rounding."""
+    ops = _ops()
+    data, meta = golden
+    n_cases = 0
+    for ci, c in enumerate(meta["select"]):
+        if f"select{ci}_scale_ids" not in data or c["k"] % 8:
+            continue
+        x = O.make_activations(c["batch"], c["k"], c["seed"], c["dist"])
+        nb = c["k"] // 64
+        n_keep = O.n_keep_from_density(c["density"], nb)
+        scale = O.make_channel_scale(c["k"], c["seed"])
+        prior = O.make_block_prior(nb, c["seed"])
+        tx = torch.from_numpy(x).to(dev)
+        tscale = torch.from_numpy(scale).to(dev)
+        tprior = torch.from_numpy(prior).to(dev)
+        for name, sc, mult, o_mult in (
+                ("scale", tscale, None, None),
+                ("prior", None, ops.prior_multiplier(tprior, 0.5, 0.05), O.prior_multiplier(prior, 0.5, 0.05)),
+                ("scale_prior", tscale, ops.prior_multiplier(tprior), O.prior_multiplier(prior))):
+            got_scores = torch.empty(nb, dtype=torch.float64, device=dev)
+            bm = torch.empty(nb, dtype=torch.uint8, device=dev)
+            ids, cnt = ops.select_topk(tx, n_keep, O.SCORE_NORM, chan_scale=sc, block_mult=mult,
+                                       scores_out=got_scores, bitmap_out=bm)
+            ref = data[f"select{ci}_{name}_ids"]
+            assert int(cnt.item()) == n_keep
+            assert np.array_equal(ids.cpu().numpy(), ref), f"case {ci} {name}"
+            assert np.array_equal(bm.cpu().numpy(), O.build_bitmap(ref, nb))
+            want = O.weighted_block_scores(x, scale if sc is not None else None, o_mult, O.SCORE_NORM)
+            np.testing.assert_allclose(got_scores.cpu().numpy(), want, rtol=1e-13)
+            if mult is not None:   # torch on the device and numpy agree on the float32 factor
+                np.testing.assert_allclose(mult.cpu().numpy(), o_mult, rtol=2e-7)
+        n_cases += 1
+    assert n_cases >= 9
+
+
+def test_weighted_selection_in_sparse_linear(dev):
+    """The decode operator with a block prior and channel weights: same ids as the oracle, output
+    within the contraction tolerance; a prior of the wrong length is ignored like in the reference."""
+    ops = _ops()
+    b, k, n = 16, 4096, 512
+    x = O.make_activations(b, k, 41, "normal")
+    w = O.make_weight(n, k, 42)
+    scale = O.make_channel_scale(k, 43)
+    prior = O.make_block_prior(k // 64, 44)
+    tx, tw = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
+    y = ops.sparse_linear(tx, tw, 0.36, block_mult=ops.prior_multiplier(torch.from_numpy(prior).to(dev)),
+                          block_score_scale=torch.from_numpy(scale).to(dev), cache_prefix="weighted_sel")
+    ids = O.select_active_blocks(x, 0.36, block_prior=prior, block_score_scale=scale)
+    ref = O.masked_gemm(x, w, ids)
+    assert O.max_err_ratio(y.float().cpu().numpy(), ref) <= 2e-3
+    assert not np.array_equal(ids, O.select_active_blocks(x, 0.36))
+    y2 = ops.sparse_linear(tx, tw, 0.36, block_mult=torch.ones(5, device=dev), cache_prefix="weighted_sel")
+    ref2 = O.masked_gemm(x, w, O.select_active_blocks(x, 0.36))
+    assert O.max_err_ratio(y2.float().cpu().numpy(), ref2) <= 2e-3
 
 
 def test_selection_ties_go_to_lower_index(dev):

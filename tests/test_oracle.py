@@ -49,6 +49,33 @@ def test_selection_budget_matches_reference(golden):
             assert np.array_equal(ids, ref), f"case {ci} keep {keep}: {ids.size} vs {ref.size}"
 
 
+def test_weighted_selection_matches_reference(golden):
+    """_select_active_blocks with block_score_scale and / or block_prior
+    (scripts/bench_roundrobin_e2e_decode.py:104-112), recorded from the reference."""
+    data, meta = golden
+    n_cases = 0
+    for ci, c in enumerate(meta["select"]):
+        if f"select{ci}_scale_ids" not in data:
+            continue
+        x = O.make_activations(c["batch"], c["k"], c["seed"], c["dist"])
+        scale = O.make_channel_scale(c["k"], c["seed"])
+        prior = O.make_block_prior(c["k"] // 64, c["seed"])
+        assert np.array_equal(O.select_active_blocks(x, c["density"], block_score_scale=scale),
+                              data[f"select{ci}_scale_ids"]), ci
+        assert np.array_equal(O.select_active_blocks(x, c["density"], block_prior=prior, prior_alpha=0.5,
+                                                     prior_eps=0.05), data[f"select{ci}_prior_ids"]), ci
+        assert np.array_equal(O.select_active_blocks(x, c["density"], block_prior=prior, block_score_scale=scale),
+                              data[f"select{ci}_scale_prior_ids"]), ci
+        n_cases += 1
+    assert n_cases == 10
+
+
+def test_prior_of_wrong_length_is_ignored():
+    x = O.make_activations(4, 640, 3, "normal")
+    assert np.array_equal(O.select_active_blocks(x, 0.5, block_prior=np.ones(7, np.float32)),
+                          O.select_active_blocks(x, 0.5))
+
+
 def test_norm_and_energy_select_different_sets(golden):
     data, _ = golden
     assert not np.array_equal(data["select0_norm_ids"], data["select0_energy_ids"])

@@ -11,6 +11,7 @@ MAX_BATCH = 64
 SCORE_NORM = 0
 SCORE_ENERGY = 1
 IDS_STABLE = 16          # BAS_GEMM_IDS_STABLE
+X_STABLE = 64            # BAS_GEMM_X_STABLE
 GEMM_BF16 = 32           # BAS_GEMM_BF16
 SCORE_BF16 = 256         # BAS_SCORE_BF16
 TP_HANDLE_BYTES = 64     # BAS_TP_HANDLE_BYTES
@@ -54,6 +55,7 @@ _SIGNATURES = {
     "bas_build_bitmap": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "bas_select_workspace_bytes": (_sz, [_i]),
     "bas_select_topk": (_i, [_vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "bas_select_topk_weighted": (_i, [_vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bas_select_budget": (_i, [_vp, _i64, _i, _i, C.c_double, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bas_select_budget_ex": (_i, [_vp, _i64, _i, _i, C.c_double, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bas_select_gemm": (_i, [_vp, _i64, _vp, _i, _i, _i, _i, _i, C.c_double, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _sz,

@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 from . import abi as _abi
-from .abi import (BLOCK_K, GEMM_BF16, IDS_STABLE, MAX_BATCH, SCORE_BF16, SCORE_ENERGY, SCORE_NORM, TP_HANDLE_BYTES,
+from .abi import (BLOCK_K, GEMM_BF16, IDS_STABLE, X_STABLE, MAX_BATCH, SCORE_BF16, SCORE_ENERGY, SCORE_NORM, TP_HANDLE_BYTES,
                   check, lib)
 
 _PACKED: dict[tuple, torch.Tensor] = {}
@@ -131,13 +131,16 @@ def read_status(device: Optional[torch.device] = None) -> int:
 def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: Optional[torch.Tensor] = None,
          count: Optional[torch.Tensor] = None, k_host: Optional[int] = None,
          bitmap: Optional[torch.Tensor] = None, family: int = 0, ids_stable: bool = False,
-         cluster: int = 0, pairs: int = 0, tp=None, max_ctas: int = 0) -> None:
+         x_stable: bool = False, cluster: int = 0, pairs: int = 0, tp=None, max_ctas: int = 0) -> None:
     """out2d[B, N] = x2d[B, K] restricted to the active blocks, times W^T.
 
     ``ids`` int32 device list (``count``: optional int32[1] device-side length, ``k_host`` an upper
     bound) or ``bitmap`` uint8[K/64] (``k_host`` then optionally tells how many blocks to expect).  ``family``: 0 by batch size, 1 CUDA-core, 2 tcgen05.
     ``ids_stable``: promise that ``ids`` is not written by the kernel launched just before this
     call on the stream; the kernel then streams weights while that kernel is still finishing.
+    ``x_stable`` (with ``ids_stable``): the same promise for ``x2d`` - it was complete before the kernel
+    launched just before this call started (a resident input, or the x that call already read); the
+    kernel then waits for its predecessor only before it stores ``out2d``.
     ``cluster``: 0 lets the library choose; 1, 2 or 4 forces the tcgen05 kernel's cluster size.
     ``pairs``: 0 lets the library choose; 2, 3 or 4 forces its number of copy/MMA warp pairs.
     ``max_ctas``: 0 lets the library choose; else an upper bound (up to 255) on the kernel's CTAs.
@@ -182,7 +185,7 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
                 count.data_ptr() if count is not None else None, int(k_host),
                 bitmap.data_ptr() if bitmap is not None else None,
                 bsz, k, n, ys.data_ptr(), ys.stride(0), ws.data_ptr(), ws.numel(),
-                int(family) | (IDS_STABLE if ids_stable else 0) | bf16 | (int(cluster) << 8) | (int(pairs) << 12) | (int(max_ctas) << 16), stream),
+                int(family) | (IDS_STABLE if ids_stable else 0) | (X_STABLE if ids_stable and x_stable else 0) | bf16 | (int(cluster) << 8) | (int(pairs) << 12) | (int(max_ctas) << 16), stream),
                 "bas_gemm")
 
 
@@ -272,10 +275,24 @@ def _select_buffers(device: torch.device, nb: int):
 
 def select_topk(x2d: torch.Tensor, n_keep: int, score_kind: int = SCORE_NORM, *,
                 ids_out: Optional[torch.Tensor] = None, count_out: Optional[torch.Tensor] = None,
-                bitmap_out: Optional[torch.Tensor] = None, scores_out: Optional[torch.Tensor] = None):
+                bitmap_out: Optional[torch.Tensor] = None, scores_out: Optional[torch.Tensor] = None,
+                chan_scale: Optional[torch.Tensor] = None, block_mult: Optional[torch.Tensor] = None):
     """Device-side batch-shared top-k selection.  Returns (ids[:n_keep] int32 ascending, count int32[1]);
-    both stay on the device.  Without explicit outputs, per-stream buffers are reused."""
-    return _select(x2d, 0, int(n_keep), score_kind, 0.0, ids_out, count_out, bitmap_out, scores_out)
+    both stay on the device.  Without explicit outputs, per-stream buffers are reused.
+
+    ``chan_scale`` (float32 [>= 64 * (K // 64)]) and ``block_mult`` (float32 [K // 64]) are the
+    reference's optional score modifiers (scripts/bench_roundrobin_e2e_decode.py:104-112): weighted
+    squares per channel, and a factor per block (see :func:`prior_multiplier`)."""
+    return _select(x2d, 0, int(n_keep), score_kind, 0.0, ids_out, count_out, bitmap_out, scores_out,
+                   chan_scale, block_mult)
+
+
+def prior_multiplier(block_prior: torch.Tensor, prior_alpha: float = 1.0, prior_eps: float = 0.1) -> torch.Tensor:
+    """float32 ``clamp(prior + eps, min=1e-6) ** alpha``, the factor the reference applies to the block
+    scores (scripts/bench_roundrobin_e2e_decode.py:109-112).  A prior is fixed per projection:
+    evaluate this once and pass the result as ``block_mult``."""
+    p = block_prior.to(dtype=torch.float32)
+    return torch.clamp(p + float(prior_eps), min=1e-6).pow(float(prior_alpha)).contiguous()
 
 
 def select_budget(x2d: torch.Tensor, energy_keep: float, min_keep: int = 1, *,
@@ -286,8 +303,19 @@ def select_budget(x2d: torch.Tensor, energy_keep: float, min_keep: int = 1, *,
     return _select(x2d, 1, int(min_keep), SCORE_ENERGY, float(energy_keep), ids_out, count_out, bitmap_out, scores_out)
 
 
-def _select(x2d, mode, n_keep, score_kind, energy_keep, ids_out, count_out, bitmap_out, scores_out):
+def _select(x2d, mode, n_keep, score_kind, energy_keep, ids_out, count_out, bitmap_out, scores_out,
+            chan_scale=None, block_mult=None):
     _require_cuda_fp16(x2d, "x")
+    for name, t, need in (("chan_scale", chan_scale, (x2d.shape[1] // BLOCK_K) * BLOCK_K),
+                          ("block_mult", block_mult, x2d.shape[1] // BLOCK_K)):
+        if t is None:
+            continue
+        if mode != 0:
+            raise ValueError(f"{name} applies to the top-k selection only")
+        if not t.is_cuda or t.device != x2d.device or t.dtype != torch.float32 or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous float32 tensor on x's device")
+        if t.numel() < need:
+            raise ValueError(f"{name} needs at least {need} elements")
     if x2d.dim() != 2 or x2d.stride(1) != 1:
         raise ValueError("x must be 2-D with unit inner stride")
     bt, k = x2d.shape
@@ -307,6 +335,12 @@ def _select(x2d, mode, n_keep, score_kind, energy_keep, ids_out, count_out, bitm
                 scores_out.data_ptr() if scores_out is not None else None,
                 ws.data_ptr(), ws.numel(), _stream_ptr())
         bf16 = SCORE_BF16 if x2d.dtype == torch.bfloat16 else 0
+        if mode == 0 and (chan_scale is not None or block_mult is not None):
+            check(lib.bas_select_topk_weighted(x2d.data_ptr(), x2d.stride(0), bt, k, n_keep, int(score_kind) | bf16,
+                                               chan_scale.data_ptr() if chan_scale is not None else None,
+                                               block_mult.data_ptr() if block_mult is not None else None, *args),
+                  "bas_select_topk_weighted")
+            return ids_out[:n_keep], count_out
         if mode == 0:
             check(lib.bas_select_topk(x2d.data_ptr(), x2d.stride(0), bt, k, n_keep, int(score_kind) | bf16, *args),
                   "bas_select_topk")
@@ -361,7 +395,8 @@ def select_gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, n_
 def sparse_linear(x: torch.Tensor, weight: torch.Tensor, density: float, *, score_kind: int = SCORE_NORM,
                   cache_prefix: str = "sparse_linear", out: Optional[torch.Tensor] = None,
                   fixed_active_blocks: Optional[torch.Tensor] = None, energy_keep: Optional[float] = None,
-                  min_keep: int = 1) -> torch.Tensor:
+                  min_keep: int = 1, block_mult: Optional[torch.Tensor] = None,
+                  block_score_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The decode-time operator of the reference's ``_sparse_linear``
     (scripts/bench_roundrobin_e2e_decode.py:179-284) through :func:`select_gemm`: selection and
     contraction in one launch where the shape allows, else chained, never a host round trip.  x is [B, K] or [B, 1, K].
@@ -373,6 +408,9 @@ def sparse_linear(x: torch.Tensor, weight: torch.Tensor, density: float, *, scor
       fraction of the total energy, at least ``min_keep`` blocks - the variable-count mode of
       scripts/bench_alpaca_energy_budget_e2e.py:49-56, without its host synchronisation: the count
       stays on the device and the contraction reads it there.
+    * ``block_score_scale`` / ``block_mult``: the reference's channel weights and block prior
+      (:104-112; ``block_mult = prior_multiplier(prior, alpha, eps)``, and like the reference a
+      factor whose length is not the block count is ignored); top-k mode only, two launches.
     """
     x3 = x.reshape(x.shape[0], 1, x.shape[1]) if x.dim() == 2 else x
     if x3.shape[1] != 1 or (energy_keep is None and fixed_active_blocks is None and float(density) >= 1.0):
@@ -385,9 +423,16 @@ def sparse_linear(x: torch.Tensor, weight: torch.Tensor, density: float, *, scor
         out = torch.empty(bt, 1, n, device=x.device, dtype=x.dtype)
     out2d = out.view(bt, n)
     nb = k // BLOCK_K
+    if block_mult is not None and block_mult.numel() != nb:
+        block_mult = None
+    weighted = energy_keep is None and (block_mult is not None or block_score_scale is not None)
     if fixed_active_blocks is not None:
         ids = fixed_active_blocks.to(device=x.device, dtype=torch.int32).contiguous()
         gemm(x2d, packed, out2d, ids=ids)
+    elif weighted:
+        n_keep = n_keep_from_density(density, nb, min_keep)
+        ids, count = select_topk(x2d, n_keep, score_kind, chan_scale=block_score_scale, block_mult=block_mult)
+        gemm(x2d, packed, out2d, ids=ids, count=count, k_host=n_keep)
     elif bt > MAX_BATCH:
         if energy_keep is not None:
             ids, count = select_budget(x2d, float(energy_keep), int(min_keep))

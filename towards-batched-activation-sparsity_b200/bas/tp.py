@@ -68,6 +68,7 @@ LLAMA2_7B_LAYER = (
 # Projections that read the same activation through the same mask can run as one masked GEMM over
 # their concatenated output columns (the reference's own CLI assumes this for q/k/v,
 # kernels/shared_mask_batched_triton_min_runtime.py:4645): q+k+v and gate+up.
+SHARES_PREVIOUS_INPUT = ("k_proj", "v_proj", "up_proj")
 FUSED_GROUPS = (("qkv_proj", ("q_proj", "k_proj", "v_proj")), ("gate_up_proj", ("gate_proj", "up_proj")))
 
 
@@ -99,7 +100,8 @@ class ShardedLinear:
         self.n_local = shard.shape[0]
         self.packed = ops.pack_weight(shard.contiguous()) if self.n_local and self.k_local else None
 
-    def forward(self, x2d, bitmap, out2d, ids_stable: bool = True, exchange=None, n_keep: int = 0):
+    def forward(self, x2d, bitmap, out2d, ids_stable: bool = True, exchange=None, n_keep: int = 0,
+                x_stable: bool = False):
         """x2d is the replicated [B, K] activation, bitmap the replicated uint8[K/64] mask.  Writes
         this rank's output slice (column-parallel) or partial sum (row-parallel) into out2d; with an
         ``exchange`` group a row-parallel linear writes the sum over all ranks instead (formed inside
@@ -117,7 +119,7 @@ class ShardedLinear:
         nb_all = bitmap.numel()
         hint = max(1, (int(n_keep) * (self.b1 - self.b0) + nb_all - 1) // nb_all) if n_keep else 0
         ops.gemm(xs, self.packed, out2d, bitmap=bitmap[self.b0:self.b1], k_host=hint, ids_stable=ids_stable,
-                 tp=exchange if row else None)
+                 x_stable=x_stable, tp=exchange if row else None)
 
 
 class DecodeLinearStack:
@@ -201,6 +203,9 @@ class DecodeLinearStack:
         import torch.distributed as dist
 
         for lin, x, bitmap, out, n_keep in self.items:
-            lin.forward(x, bitmap, out, exchange=self.exchange, n_keep=n_keep)
+            # k, v and up read, in the model, the activation the call before them (q, gate) has already
+            # read: only these declare their input stable
+            lin.forward(x, bitmap, out, exchange=self.exchange, n_keep=n_keep,
+                        x_stable=lin.spec.name in SHARES_PREVIOUS_INPUT)
             if lin.spec.parallel == "row" and self.world > 1 and self.exchange is None:
                 dist.all_reduce(out, group=self.group)

@@ -225,7 +225,7 @@ static int gemm_impl(const bas_tp* tp, const FusedSelect* sel, const void* x_dev
   if (!aligned16(x_dev) || !aligned16(packed_dev) || (ldx & 7) != 0 || (k & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
   if (ws_dev == nullptr || ws_bytes < bas_gemm_workspace_bytes(batch, n)) return BAS_ERR_WORKSPACE;
   const int family = flags & 3;
-  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_BF16 | 0x700 | 0x7000 | 0xff0000 | (1 << 24))) != 0) return BAS_ERR_INVALID_ARGUMENT;
+  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_X_STABLE | BAS_GEMM_BF16 | 0x700 | 0x7000 | 0xff0000 | (1 << 24))) != 0) return BAS_ERR_INVALID_ARGUMENT;
 
   DeviceInfo di;
   int st = device_info(&di);
@@ -307,8 +307,9 @@ int bas_gemm_allreduce(bas_tp* tp, const void* x_dev, int64_t ldx, const void* p
                        const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
                        void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream) {
   if (tp == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  // calls that exchange partial sums with other ranks stay one deep: the X-stable promise is not used
   return gemm_impl(tp, nullptr, x_dev, ldx, packed_dev, ids_dev, count_dev, k_host, bitmap_dev, batch, k, n, y_dev, ldy,
-                   ws_dev, ws_bytes, flags, stream);
+                   ws_dev, ws_bytes, flags & ~BAS_GEMM_X_STABLE, stream);
 }
 
 int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev, const int32_t* count_dev,
@@ -345,7 +346,9 @@ size_t bas_select_workspace_bytes(int k) {
 
 static int select_common(const void* x_dev, int64_t ldx, int batch, int k, int mode, int n_keep, int score_kind,
                          double energy_keep, int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
-                         double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream) {
+                         double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream,
+                         const float* chan_scale_dev = nullptr, const float* block_mult_dev = nullptr) {
+  if (chan_scale_dev != nullptr && !aligned16(chan_scale_dev)) return BAS_ERR_INVALID_ARGUMENT;
   if (x_dev == nullptr || ids_out_dev == nullptr || count_out_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || k < kBlockK || ldx < k || !aligned16(x_dev) || (ldx & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
   const int nb = k / kBlockK;  // trailing K mod 64 channels are never scored (d_eff)
@@ -375,6 +378,9 @@ static int select_common(const void* x_dev, int64_t ldx, int batch, int k, int m
   p.scores_out = scores_out_dev;
   p.ws_done = (unsigned int*)ws_dev;
   p.ws_scores = (double*)((uint8_t*)ws_dev + 256);
+  p.chan_scale = chan_scale_dev;
+  p.block_mult = block_mult_dev;
+  if (chan_scale_dev != nullptr) p.score_kind = BAS_SCORE_ENERGY;   // weighted squares, no root (as the reference)
   cudaError_t e = launch_select(p, di.sm_count, (cudaStream_t)stream);
   return e == cudaSuccess ? BAS_OK : cuda_fail(e);
 }
@@ -384,6 +390,14 @@ int bas_select_topk(const void* x_dev, int64_t ldx, int batch, int k, int n_keep
                     size_t ws_bytes, void* stream) {
   return select_common(x_dev, ldx, batch, k, 0, n_keep, score_kind, 0.0, ids_out_dev, count_out_dev, bitmap_out_dev,
                        scores_out_dev, ws_dev, ws_bytes, stream);
+}
+
+int bas_select_topk_weighted(const void* x_dev, int64_t ldx, int batch, int k, int n_keep, int score_kind,
+                             const float* chan_scale_dev, const float* block_mult_dev, int32_t* ids_out_dev,
+                             int32_t* count_out_dev, uint8_t* bitmap_out_dev, double* scores_out_dev, void* ws_dev,
+                             size_t ws_bytes, void* stream) {
+  return select_common(x_dev, ldx, batch, k, 0, n_keep, score_kind, 0.0, ids_out_dev, count_out_dev, bitmap_out_dev,
+                       scores_out_dev, ws_dev, ws_bytes, stream, chan_scale_dev, block_mult_dev);
 }
 
 int bas_select_budget(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
@@ -412,7 +426,7 @@ int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, int 
   const bool budget = energy_keep >= 0.0;
   const int nb_sel = k / kBlockK;
   if ((kind != BAS_SCORE_NORM && kind != BAS_SCORE_ENERGY) || n_keep < 0 || n_keep > nb_sel ||
-      (flags & (3 | BAS_GEMM_IDS_STABLE)) != 0)
+      (flags & (3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_X_STABLE)) != 0)
     return BAS_ERR_INVALID_ARGUMENT;
   FusedSelect sel;
   sel.mode = budget ? 2 : 1;

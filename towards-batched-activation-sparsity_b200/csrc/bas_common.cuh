@@ -97,6 +97,45 @@ __device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_s
                "l"(__cvta_generic_to_global(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+// L2 eviction policies for the copies below.  Weights are read once per call and never again before
+// gigabytes of other weights have passed: marked evict-first they do not push the small, re-read
+// operands (activations, id lists, outputs) out of L2; those are marked evict-last.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ int ld_nc_keep_s32(const int32_t* p, uint64_t policy) {
+  int v;
+  asm volatile("ld.global.nc.L2::cache_hint.s32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(policy));
+  return v;
+}
+__device__ __forceinline__ unsigned int ld_nc_keep_u8(const uint8_t* p, uint64_t policy) {
+  unsigned int v;
+  asm volatile("ld.global.nc.L2::cache_hint.u8 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(policy));
+  return v;
+}
+__device__ __forceinline__ void bulk_copy_g2s_hint(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar,
+                                                   uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(__cvta_generic_to_global(gmem_src)), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], "
+      "[%4], %5;" ::"r"(smem_u32(smem_dst)),
+      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
 // 2-D tiled load through a tensor map; x (innermost coordinate) times the element size must be a
 // multiple of 16 bytes.  Out-of-range elements arrive as zeros and still count towards the bytes.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -224,11 +263,12 @@ __device__ __forceinline__ float dsmem_ld_f32(uint32_t addr) {
 // that their latencies overlap.
 __device__ __forceinline__ void warp_load_id_batch(const int32_t* __restrict__ ids, const uint8_t* __restrict__ bitmap,
                                                    int n_src, int base0, int lane, int (&raw)[8]) {
+  const uint64_t keep = l2_policy_evict_last();   // the list is read by every CTA, and small
 #pragma unroll
   for (int u = 0; u < 8; ++u) {
     const int e = base0 + u * 32 + lane;
     raw[u] = 0;
-    if (e < n_src) raw[u] = (bitmap != nullptr) ? (int)bitmap[e] : __ldg(ids + e);
+    if (e < n_src) raw[u] = (bitmap != nullptr) ? (int)ld_nc_keep_u8(bitmap + e, keep) : ld_nc_keep_s32(ids + e, keep);
   }
 }
 

@@ -70,6 +70,7 @@ struct GemmParams {
 };
 
 constexpr int kFlagStableIds = 16;   // BAS_GEMM_IDS_STABLE: the id list is not written by the previous kernel
+constexpr int kFlagStableX = 64;     // BAS_GEMM_X_STABLE: nor is X (only with kFlagStableIds)
 constexpr int kFlagBf16 = 32;        // BAS_GEMM_BF16: X, W and Y are bfloat16 (same 16-bit containers)
 
 // Launch with the programmatic-serialization attribute, so that this kernel's preamble (and, when
@@ -126,6 +127,8 @@ struct SelectParams {
   double* scores_out;
   double* ws_scores;      // workspace: [nb] fp64 batch-summed scores
   unsigned int* ws_done;  // workspace: CTA arrival counter
+  const float* chan_scale = nullptr;   // optional [64 * nb]: per-channel weight of the squares (16-byte aligned)
+  const float* block_mult = nullptr;   // optional [nb]: factor on the batch-mean score
 };
 cudaError_t launch_select(const SelectParams& p, int sm_count, cudaStream_t stream);
 

@@ -92,7 +92,27 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     if (pr < pairs) {
       const int jj = pr / p.batch, b = pr - jj * p.batch;
       const uint4 v = __ldg((const uint4*)(p.x + (size_t)b * p.ldx + (size_t)(j0 + jj) * kBlockK) + sub);
-      if (p.bf16) {
+      if (p.chan_scale != nullptr) {
+        // weighted squares: sum_i x_i^2 * scale_i (scripts/bench_roundrobin_e2e_decode.py:106-108)
+        const float4* scp = (const float4*)(p.chan_scale + (size_t)(j0 + jj) * kBlockK) + 2 * sub;
+        const float4 s0 = __ldg(scp), s1 = __ldg(scp + 1);
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        const unsigned int* wds = (const unsigned int*)&v;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          double lo, hi;
+          if (p.bf16) {
+            lo = (double)__uint_as_float(wds[q] << 16);
+            hi = (double)__uint_as_float(wds[q] & 0xffff0000u);
+          } else {
+            const float2 f = __half22float2(*(const __half2*)&wds[q]);
+            lo = (double)f.x;
+            hi = (double)f.y;
+          }
+          e += (lo * lo) * (double)sc[2 * q];
+          e += (hi * hi) * (double)sc[2 * q + 1];
+        }
+      } else if (p.bf16) {
         const unsigned int* wds = (const unsigned int*)&v;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {   // a bf16 is the upper half of an fp32; squares are taken in fp64 (range)
@@ -122,7 +142,9 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   if (tid < nj) {
     double s = 0.0;
     for (int b = 0; b < p.batch; ++b) s += s_dyn[tid * p.batch + b];   // batch rows in order
-    p.ws_scores[j0 + tid] = s / (double)p.batch;
+    s = s / (double)p.batch;
+    if (p.block_mult != nullptr) s *= (double)__ldg(p.block_mult + j0 + tid);
+    p.ws_scores[j0 + tid] = s;
     __threadfence();
   }
   __syncthreads();

@@ -287,9 +287,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   // always wait for the previous kernel.  A stable list is requested right away, so that its load
   // latency runs under the set-up below.
   const bool early_ids = !SEL && (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
+  // With X stable as well nothing this kernel reads depends on the kernel before it: copies and MMAs
+  // run straight through, and only the epilogue waits, before the first store to Y.
+  const bool early_x = early_ids && (p.flags & kFlagStableX) != 0;
   int first_ids[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (warp == 0 && early_ids)
     warp_load_id_batch(p.ids, p.bitmap, p.bitmap != nullptr ? p.nb : p.k_host, 0, lane, first_ids);
+#ifdef BAS_EARLY_LD
+  if (early_ids && tid == 0) pdl_launch_dependents();
+#endif
 
   if (tid < S) {
     mbar_init(&hdr->full[tid], 1);
@@ -386,8 +392,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         wbytes = min(TW, width - sub * TW) * kRowBytes;
         return true;
       };
+      // weights stream through L2 once (evict-first); the activations are re-read by every cluster
+      // and by the next call (evict-last)
+      const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
       int g = warp;
-      if (early_ids) {
+      if (early_ids && !early_x) {
         // Stream the first ring-full of weight chunks while the previous kernel is still draining,
         // then wait for it before loading X.
         const int ahead = min(S, NG);
@@ -398,8 +407,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           if (lane == 0) mbar_arrive_expect_tx(&hdr->full[ga], total);
           __syncwarp();
           if (have)
-            bulk_copy_g2s(s_stage + (size_t)ga * stage_bytes + (size_t)lane * tile_bytes,
-                          p.packed + ((size_t)j * p.npad + n0 + sub * TW) * kRowBytes, wbytes, &hdr->full[ga]);
+            bulk_copy_g2s_hint(s_stage + (size_t)ga * stage_bytes + (size_t)lane * tile_bytes,
+                               p.packed + ((size_t)j * p.npad + n0 + sub * TW) * kRowBytes, wbytes, &hdr->full[ga],
+                               pol_w);
           armed_next = ga + P;
           ++armed_cnt;
         }
@@ -407,8 +417,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         for (int ga = warp; ga < ahead; ga += P) {
           int sub = 0, j = 0, wbytes = 0;
           if (lane_tile(ga, sub, j, wbytes))
-            tma_load_2d(s_stage + (size_t)ga * stage_bytes + (size_t)lane * tile_bytes + p.wslot, &xmap, j * kBlockK, 0,
-                        &hdr->full[ga]);
+            tma_load_2d_hint(s_stage + (size_t)ga * stage_bytes + (size_t)lane * tile_bytes + p.wslot, &xmap, j * kBlockK,
+                             0, &hdr->full[ga], pol_x);
         }
         g = armed_next;
       }
@@ -433,8 +443,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         [[maybe_unused]] const long long tr1 = BAS_TRACE_CLOCK();
         if (have) {
           uint8_t* st = s_stage + (size_t)s * stage_bytes + (size_t)lane * tile_bytes;
-          bulk_copy_g2s(st, p.packed + ((size_t)j * p.npad + n0 + sub * TW) * kRowBytes, wbytes, &hdr->full[s]);
-          tma_load_2d(st + p.wslot, &xmap, j * kBlockK, 0, &hdr->full[s]);
+          bulk_copy_g2s_hint(st, p.packed + ((size_t)j * p.npad + n0 + sub * TW) * kRowBytes, wbytes, &hdr->full[s], pol_w);
+          tma_load_2d_hint(st + p.wslot, &xmap, j * kBlockK, 0, &hdr->full[s], pol_x);
         }
         armed_next = g + P;
         ++armed_cnt;
@@ -1006,6 +1016,17 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
     cluster = c;
     ranges = r;
     break;
+  }
+  // A call that declared both its id list and X stable does not depend on the call before it until
+  // it stores: such calls pipeline several deep (each waits, in its epilogue, for its predecessor to
+  // complete, so the stores stay in stream order).  Small grids are then best - one CTA per
+  // 128-column range, no cluster, nothing to combine - because the next calls fill the other SMs
+  // (measured: 32 CTAs per call for 4096 columns, 86 for 11008).
+  const bool pipelined = (p.flags & kFlagStableX) != 0 && (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr &&
+                         p.sel.mode == 0 && p.tp.world == 0;
+  if (pipelined && forced == 0 && ((p.flags >> 16) & 0xff) == 0 && r_min >= 16 && r_min <= sm_count) {
+    cluster = 1;
+    ranges = r_min;
   }
   const int tile_cols = kTileN;
   const int wmax = ((units + ranges - 1) / ranges) * 8;
