@@ -318,7 +318,7 @@ def run_gpu(args) -> None:
         for b in BATCHES:
             c = counter["i"] % ROTATE
             counter["i"] += 1
-            ops.gemm(xs[b], packed[c], outs[b], ids=ids[b], ids_stable=True)
+            ops.gemm(xs[b], packed[c], outs[b], ids=ids[b], ids_stable=True, x_stable=True)
 
     # ---- the K timed steps ----
     GS = 16                                                     # steps per captured graph
@@ -383,19 +383,29 @@ def run_gpu(args) -> None:
     for b in BATCHES:
         def sparse_cold(b=b):
             for c in range(ROTATE):
+                ops.gemm(xs[b], packed[c], outs[b], ids=ids[b], ids_stable=True, x_stable=True)
+
+        def sparse_cold_ids_only(b=b):        # X may be the previous call's output: one call deep
+            for c in range(ROTATE):
                 ops.gemm(xs[b], packed[c], outs[b], ids=ids[b], ids_stable=True)
+
+        def sparse_cold_plain(b=b):           # no promises: what the drop-in wrappers launch
+            for c in range(ROTATE):
+                ops.gemm(xs[b], packed[c], outs[b], ids=ids[b])
 
         def dense_cold(b=b):
             for c in range(ROTATE):
                 torch.mm(xs[b], dense_wt[c], out=dense_outs[b])
 
         def sparse_hot(b=b):
-            ops.gemm(xs[b], packed[0], outs[b], ids=ids[b], ids_stable=True)
+            ops.gemm(xs[b], packed[0], outs[b], ids=ids[b], ids_stable=True, x_stable=True)
 
         def dense_hot(b=b):
             torch.mm(xs[b], dense_wt[0], out=dense_outs[b])
 
         us = _graph_time_us(torch, stream, sparse_cold, ROTATE, reps)
+        us_ids = _graph_time_us(torch, stream, sparse_cold_ids_only, ROTATE, reps)
+        us_plain = _graph_time_us(torch, stream, sparse_cold_plain, ROTATE, reps)
         dus = _graph_time_us(torch, stream, dense_cold, ROTATE, reps)
         hus = _graph_time_us(torch, stream, sparse_hot, 1, 200)
         hdus = _graph_time_us(torch, stream, dense_hot, 1, 200)
@@ -406,6 +416,8 @@ def run_gpu(args) -> None:
             "us": round(us, 3), "dense_cublas_us": round(dus, 3), "speedup_vs_cublas": round(dus / us, 3),
             "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peaks["hbm_gbs"], 4),
             "frac_of_8000": round(gbs / 8000.0, 4),
+            "ids_stable_only_us": round(us_ids, 3), "ids_stable_only_speedup_vs_cublas": round(dus / us_ids, 3),
+            "no_promises_us": round(us_plain, 3), "no_promises_speedup_vs_cublas": round(dus / us_plain, 3),
             "l2_resident_us": round(hus, 3), "l2_resident_dense_us": round(hdus, 3),
             "l2_resident_speedup": round(hdus / hus, 3),
         }
@@ -548,6 +560,8 @@ def run_gpu(args) -> None:
             "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
             "algorithmic_bytes_per_launch": N_KEEP[64] * SLAB_BYTES, "traffic": None,
+            "duration": "timed region / launches: the chain's launches overlap (32 CTAs each, about four calls "
+                        "resident), so this is the period of the chain, not the lifetime of one launch",
         }
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
         # profiles/umma_colsplit_down_proj_b64.md (same workload, one launch)
@@ -558,8 +572,12 @@ def run_gpu(args) -> None:
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD,
-                       "step": "3 masked GEMMs (B=2,16,64), masks fixed ahead of the step (ids declared stable: "
-                               "weight tiles of call i+1 stream while call i drains)",
+                       "step": "3 masked GEMMs (B=2,16,64); activations and masks are resident before the chain of "
+                               "calls starts and declared so (BAS_GEMM_IDS_STABLE | BAS_GEMM_X_STABLE): independent "
+                               "calls of a stream pipeline several deep, each waiting for its predecessor only "
+                               "before it stores.  per_batch also has the same chains with only the masks declared "
+                               "stable (ids_stable_only_*) and with nothing declared, as the drop-in wrappers "
+                               "launch (no_promises_*): one call deep",
                        "l2": f"cold: every call reads one of {ROTATE} rotating weight copies (1.4 GB in rotation)",
                        "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
                        "timing": "CUDA-graph replays of 16 steps, CUDA events on the launch stream, max over ranks"},
@@ -571,9 +589,11 @@ def run_gpu(args) -> None:
         dist.destroy_process_group()
 
 
-def run_profile_case(batch: int, family: int = 0) -> None:
+def run_profile_case(batch: int, family: int = 0, pipelined: bool = False) -> None:
     """A few eager launches of one batch size on 4 rotating weight copies (360 MB, larger than L2):
-    the small case that profiler captures of the contraction kernels are taken on."""
+    the small case that profiler captures of the contraction kernels are taken on.  ``pipelined``:
+    the masks are selected once, ahead, and the calls declare ids and X stable - the grid (one CTA per
+    128-column range) that the benchmark's chains run."""
     import torch
 
     from bas import abi, ops
@@ -585,11 +605,17 @@ def run_profile_case(batch: int, family: int = 0) -> None:
     nk = N_KEEP.get(batch, O.n_keep_from_density(0.36, NB))
     x = torch.from_numpy(O.make_activations(batch, K_IN, seed=1000 + batch, dist="laplace")).to(dev)
     out = torch.zeros(batch, N_OUT, dtype=torch.float16, device=dev)
-    for i in range(8):
-        ids, cnt = ops.select_topk(x, nk, abi.SCORE_NORM)
-        ops.gemm(x, packed[i % 4], out, ids=ids, family=family)
+    if pipelined:
+        ids = ops.select_topk(x, nk, abi.SCORE_NORM)[0].clone()
+        torch.cuda.synchronize()
+        for i in range(8):
+            ops.gemm(x, packed[i % 4], out, ids=ids, family=family, ids_stable=True, x_stable=True)
+    else:
+        for i in range(8):
+            ids, cnt = ops.select_topk(x, nk, abi.SCORE_NORM)
+            ops.gemm(x, packed[i % 4], out, ids=ids, family=family)
     torch.cuda.synchronize()
-    print(f"profile case B={batch} family={family}: 8 select + 8 gemm launches, status {ops.read_status(dev)}")
+    print(f"profile case B={batch} family={family} pipelined={pipelined}: 8 gemm launches, status {ops.read_status(dev)}")
 
 
 def main() -> None:
@@ -602,6 +628,8 @@ def main() -> None:
                     help="run only a few eager launches at batch B (for profiler captures) and exit")
     ap.add_argument("--profile-family", type=int, default=0, choices=[0, 1, 2],
                     help="kernel family of the profile case: 0 default, 1 CUDA-core kernel (batch <= 8), 2 tcgen05")
+    ap.add_argument("--profile-pipelined", action="store_true",
+                    help="profile case: masks fixed ahead, calls declare ids and X stable (the benchmark's chains)")
     args = ap.parse_args()
     # stdout carries exactly one JSON line: libraries that chat on fd 1 (NCCL prints its version
     # there) are sent to stderr, and the line is written to the saved descriptor at the end.
@@ -610,7 +638,7 @@ def main() -> None:
     _STDOUT_FD = os.dup(1)
     os.dup2(2, 1)
     if args.profile_case:
-        run_profile_case(args.profile_case, args.profile_family)
+        run_profile_case(args.profile_case, args.profile_family, args.profile_pipelined)
     elif args.impl == "reference":
         run_reference(args)
     else:

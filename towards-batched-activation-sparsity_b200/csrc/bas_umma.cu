@@ -293,9 +293,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   int first_ids[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (warp == 0 && early_ids)
     warp_load_id_batch(p.ids, p.bitmap, p.bitmap != nullptr ? p.nb : p.k_host, 0, lane, first_ids);
-#ifdef BAS_EARLY_LD
-  if (early_ids && tid == 0) pdl_launch_dependents();
-#endif
 
   if (tid < S) {
     mbar_init(&hdr->full[tid], 1);
