@@ -230,40 +230,56 @@ def _layer_stack(torch, dist, dev, world, rank, stream, fuse=False, allreduce="n
     from bas import tp
 
     stack = tp.DecodeLinearStack(32, 16, 0.638, dev, world, rank, fuse_shared_inputs=fuse, allreduce=allreduce)
-    with torch.cuda.stream(stream):
-        for _ in range(3):
-            stack.step()
-    torch.cuda.synchronize()
-    mode = "cuda graph"
-    try:
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=stream):
-            stack.step()
-        run = g.replay
-    except Exception as exc:      # a collective that refuses capture: time eager launches instead
-        mode = f"eager ({type(exc).__name__})"
-        run = stack.step
-    torch.cuda.synchronize()
-    reps = 10
-    with torch.cuda.stream(stream):
-        run()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-        for _ in range(reps):
+    def timed():
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                stack.step()
+        torch.cuda.synchronize()
+        mode = "cuda graph"
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                stack.step()
+            run = g.replay
+        except Exception as exc:      # a collective that refuses capture: time eager launches instead
+            mode = f"eager ({type(exc).__name__})"
+            run = stack.step
+        torch.cuda.synchronize()
+        reps = 10
+        with torch.cuda.stream(stream):
             run()
-        e1.record(stream)
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / reps
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(reps):
+                run()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, mode
+
+    ms, mode = timed()
+    extra = {}
+    if world == 1 and not fuse:
+        # throughput probe: the same 224 calls with every input declared stable (they are: the stack's
+        # inputs are generated ahead), i.e. no call depends on the one before it
+        stack.independent_calls = True
+        ms_ind, _ = timed()
+        stack.independent_calls = False
+        extra = {"independent_calls": {"ms_per_step": round(ms_ind, 4),
+                                       "active_weight_gbs": round(stack.active_bytes / (ms_ind * 1e-3) / 1e9, 1),
+                                       "note": "every call declares ids and X stable (a probe of the chain's throughput over "
+                                               "the seven shapes); ms_per_step above declares X stable only for k, v and up, "
+                                               "which in the model read what q / gate have already read"}}
     stack.close()
-    return {"layers": 32, "linears_per_step": len(stack.items), "batch": 16, "sparsity": 0.638,
+    return {**extra, "layers": 32, "linears_per_step": len(stack.items), "batch": 16, "sparsity": 0.638,
             "parallelism": f"tp{world}: column-parallel q/k/v/gate/up, row-parallel o/down + all-reduce",
             "ms_per_step": round(ms, 4), "active_weight_gb_per_step": round(stack.active_bytes / 1e9, 3),
             "active_weight_gbs": round(stack.active_bytes / (ms * 1e-3) / 1e9, 1), "launch": mode}

@@ -106,7 +106,10 @@ BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, con
  *             (a resident input, or the X the preceding call of this library already read, as for
  *             q/k/v or gate/up of one layer).  Nothing the kernel reads then depends on the kernel
  *             before it: it streams and multiplies straight through and waits for that kernel only
- *             before its first store to Y.
+ *             before its first store to Y.  Such calls are given a small grid (one CTA per 128 output
+ *             columns) so that several of them are resident at once: meant for chains launched back
+ *             to back (one CUDA graph, or a launch loop that keeps ahead of the GPU); a call that
+ *             runs alone takes about twice as long with the flag as without it.
  *   bits 8-10 cluster size of the tcgen05 kernel: 0 = chosen by batch size, else 1, 2 or 4 CTAs
  *             share the active blocks of one column range (reduced on chip, in rank order).
  *   BAS_GEMM_BF16  X, the packed weight and Y hold bfloat16 instead of fp16 (the reference's kernels

@@ -147,6 +147,10 @@ class DecodeLinearStack:
         # kernel (peer loads over NVLink); "nccl": one all-reduce call after each of them
         self.exchange = ops.ExchangeGroup(device, batch, max(s.n for s in LLAMA2_7B_LAYER if s.parallel == "row"),
                                           group) if allreduce == "in_kernel" else None
+        # True: every call declares its input stable, which the stack's pre-generated inputs literally
+        # are (a throughput probe over the seven shapes; a model's o, down, q and gate depend on the
+        # kernel before them and could not)
+        self.independent_calls = False
         self.items = []
         self._shared = {}
         gen = torch.Generator(device=device)
@@ -206,6 +210,6 @@ class DecodeLinearStack:
             # k, v and up read, in the model, the activation the call before them (q, gate) has already
             # read: only these declare their input stable
             lin.forward(x, bitmap, out, exchange=self.exchange, n_keep=n_keep,
-                        x_stable=lin.spec.name in SHARES_PREVIOUS_INPUT)
+                        x_stable=self.independent_calls or lin.spec.name in SHARES_PREVIOUS_INPUT)
             if lin.spec.parallel == "row" and self.world > 1 and self.exchange is None:
                 dist.all_reduce(out, group=self.group)
