@@ -250,6 +250,41 @@ def test_stable_x_chain_writing_one_output(dev):
     assert O.max_err_ratio(out.cpu().numpy(), O.masked_gemm(y1, w, idl[2])) <= TOL
 
 
+@pytest.mark.parametrize("b,k,n", [(16, 4096, 11008), (2, 4096, 2048), (64, 4096, 1024), (33, 1024, 4096 + 40)])
+def test_stable_x_chain_in_cuda_graph(dev, b, k, n):
+    """A CUDA graph of eight calls that declare ids and X stable (the form the benchmark times), over
+    output widths on both sides of the small-grid rule, replayed twice: every output exact."""
+    ops = _ops()
+    w = O.make_weight(n, k, seed=61)
+    packed = ops.pack_weight(torch.from_numpy(w).to(dev))
+    nb = k // 64
+    xs = [O.make_activations(b, k, seed=700 + i) for i in range(4)]
+    idl = [O.random_active_blocks(nb, max(1, nb // 4 + 3 * i), seed=10 + i) for i in range(4)]
+    txs = [torch.from_numpy(x).to(dev) for x in xs]
+    tids = [torch.from_numpy(i).to(dev) for i in idl]
+    outs = [torch.full((b, n), float("nan"), dtype=torch.float16, device=dev) for _ in range(4)]
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for i in range(4):      # warm-up outside the capture (tensor maps, function attributes)
+            ops.gemm(txs[i], packed, outs[i], ids=tids[i], ids_stable=True, x_stable=True)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        for rep in range(2):
+            for i in range(4):
+                ops.gemm(txs[i], packed, outs[i], ids=tids[i], ids_stable=True, x_stable=True)
+    for o in outs:
+        o.fill_(float("nan"))
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        g.replay()
+        g.replay()
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
+    for i in range(4):
+        assert O.max_err_ratio(outs[i].cpu().numpy(), O.masked_gemm(xs[i], w, idl[i])) <= TOL
+
+
 @pytest.mark.parametrize("b", [2, 16])
 def test_all_ids_bad_writes_zeros(dev, b):
     ops = _ops()
