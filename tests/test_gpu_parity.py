@@ -285,6 +285,52 @@ def test_stable_x_chain_in_cuda_graph(dev, b, k, n):
         assert O.max_err_ratio(outs[i].cpu().numpy(), O.masked_gemm(xs[i], w, idl[i])) <= TOL
 
 
+@pytest.mark.parametrize("form", ["empty", "bitmap", "cluster2", "cluster4", "capped", "bf16", "count"])
+def test_stable_x_variants(dev, form):
+    """Calls that declare X stable on the kernel's other paths: an empty active set (zero fill), a byte
+    map, forced cluster sizes and a capped grid (partials combined through the cluster before the
+    store), bfloat16, and a device-side count (which makes the kernel ignore both promises).  Three
+    calls back to back into one output; the last one's result must be there."""
+    ops = _ops()
+    b, k, n = 16, 4096, 4096
+    nb = k // 64
+    w = O.make_weight(n, k, seed=71)
+    x = O.make_activations(b, k, seed=72)
+    dt = torch.bfloat16 if form == "bf16" else torch.float16
+    if form == "bf16":
+        w, x = O.round_to_bf16(w.astype(np.float32)), O.round_to_bf16(x.astype(np.float32))
+    tw, tx = torch.from_numpy(w).to(dev).to(dt), torch.from_numpy(x).to(dev).to(dt)
+    packed = ops.pack_weight(tw)
+    out = torch.full((b, n), float("nan"), dtype=dt, device=dev)
+    idl = [O.random_active_blocks(nb, nk, seed=nk) for nk in (40, 9, 0 if form == "empty" else 21)]
+    torch.cuda.synchronize()
+    for ids in idl:
+        kw = dict(ids_stable=True, x_stable=True)
+        if form == "bitmap":
+            kw["bitmap"] = torch.from_numpy(O.build_bitmap(ids, nb)).to(dev)
+        else:
+            kw["ids"] = torch.from_numpy(ids).to(dev)
+        if form == "cluster2":
+            kw["cluster"] = 2
+        elif form == "cluster4":
+            kw["cluster"] = 4
+        elif form == "capped":
+            kw["max_ctas"] = 64
+        elif form == "count":
+            kw["count"] = torch.tensor([ids.size], dtype=torch.int32, device=dev)
+            kw["k_host"] = nb
+            kw["ids"] = torch.from_numpy(np.concatenate([ids, np.zeros(nb - ids.size, np.int32)])).to(dev)
+        ops.gemm(tx, packed, out, **kw)
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
+    ref = O.masked_gemm(x, w, idl[-1])
+    got = out.float().cpu().numpy()
+    if form == "empty":
+        assert not got.any()
+    else:
+        assert O.max_err_ratio(got, ref) <= (2.0 ** -7 if form == "bf16" else TOL)
+
+
 @pytest.mark.parametrize("b", [2, 16])
 def test_all_ids_bad_writes_zeros(dev, b):
     ops = _ops()
