@@ -582,6 +582,11 @@ def run_gpu(args) -> None:
             "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
             "algorithmic_bytes_per_launch": N_KEEP[64] * SLAB_BYTES, "traffic": None,
+            "one_call_deep": {"achieved": round(N_KEEP[64] * SLAB_BYTES / (dom["ids_stable_only_us"] * 1e-6) / 1e9, 1),
+                              "frac": round(N_KEEP[64] * SLAB_BYTES / (dom["ids_stable_only_us"] * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
+                              "note": "the same call when X may be the previous kernel's output (launches do not "
+                                      "overlap beyond a ring-full of weights): the 128-CTA cluster grid of "
+                                      "profiles/umma_colsplit_down_proj_b64.md"},
             "duration": "timed region / launches: the chain's launches overlap (32 CTAs each, about four calls "
                         "resident), so this is the period of the chain, not the lifetime of one launch",
         }
