@@ -458,6 +458,18 @@ def run_gpu(args) -> None:
             sel, cnt = ops.select_topk(x_steps[s % 11], n_keep4, abi.SCORE_ENERGY)
             ops.gemm(x_steps[s % 11], packed[s], outs[b], ids=sel, count=cnt, k_host=n_keep4)
 
+    # the same chain with the next step's selection overlapping this step's contraction: the steps
+    # alternate between two id buffers and the selection declares its inputs stable
+    sel_bufs = [(torch.empty(NB, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev))
+                for _ in range(2)]
+
+    def chain_overlapped():
+        for s in range(ROTATE):
+            ids_buf, cnt_buf = sel_bufs[s & 1]
+            sel, cnt = ops.select_topk(x_steps[s % 11], n_keep4, abi.SCORE_ENERGY, ids_out=ids_buf, count_out=cnt_buf,
+                                       inputs_stable=True)
+            ops.gemm(x_steps[s % 11], packed[s], outs[b], ids=sel, count=cnt, k_host=n_keep4)
+
     def one_launch():
         for s in range(ROTATE):
             ops.select_gemm(x_steps[s % 11], packed[s], outs[b], n_keep4, abi.SCORE_ENERGY)
@@ -465,6 +477,7 @@ def run_gpu(args) -> None:
     sel_us = _graph_time_us(torch, stream, select_only, ROTATE, reps)
     chain_us = _graph_time_us(torch, stream, chain, ROTATE, reps)
     fused_us = _graph_time_us(torch, stream, one_launch, ROTATE, reps)
+    overlapped_us = _graph_time_us(torch, stream, chain_overlapped, ROTATE, reps)
     # same mask and same sums from the one-launch form as from the oracle's ids (not timed)
     sel_ids, _ = ops.select_gemm(x_steps[3], packed[0], outs[b], n_keep4, abi.SCORE_ENERGY)
     torch.cuda.synchronize()
@@ -472,10 +485,13 @@ def run_gpu(args) -> None:
     if not np.array_equal(sel_ids[:n_keep4].cpu().numpy(), want_ids):
         raise SystemExit("in-kernel selection disagrees with the oracle's ids")
     online = {"batch": b, "keep_blocks": n_keep4, "select_us": round(sel_us, 3), "select_plus_gemm_us": round(chain_us, 3),
-              "selection_inside_gemm_us": round(fused_us, 3), "score": "energy",
+              "selection_inside_gemm_us": round(fused_us, 3),
+              "select_plus_gemm_overlapped_us": round(overlapped_us, 3), "score": "energy",
               "note": "select_us: selection kernel alone; select_plus_gemm_us: two launches; "
                       "selection_inside_gemm_us: bas_select_gemm (one call; it selects inside the contraction "
-                      "kernel only where that is the faster form, i.e. batches of a few rows)"}
+                      "kernel only where that is the faster form, i.e. batches of a few rows); "
+                      "select_plus_gemm_overlapped_us: the two launches per step, with step i+1's selection "
+                      "(BAS_SCORE_INPUTS_STABLE, alternating id buffers) scoring while step i's contraction runs"}
 
     # ---- the sharded decode-step linear stack (all ranks take part) ----
     try:

@@ -51,7 +51,15 @@ typedef enum bas_status {
 typedef enum bas_score_kind {
   BAS_SCORE_NORM = 0,  /* mean_b ||x_b,block||_2 : scripts/bench_roundrobin_e2e_decode.py:103-105 */
   BAS_SCORE_ENERGY = 1, /* mean_b ||x_b,block||^2 : scripts/bench_alpaca_energy_budget_e2e.py:43-46 */
-  BAS_SCORE_BF16 = 256  /* OR into score_kind: x holds bfloat16 instead of fp16 */
+  BAS_SCORE_BF16 = 256, /* OR into score_kind: x holds bfloat16 instead of fp16 */
+  /* OR into score_kind of bas_select_topk / bas_select_topk_weighted: the caller promises that no
+   * kernel that can still be running when this call starts (the kernel preceding it in the stream,
+   * and earlier ones where that kernel itself was allowed to start early) writes x_dev or touches
+   * this call's outputs or workspace - e.g. the preceding kernel is the contraction of the PREVIOUS
+   * step, launched without promises, reading the other of two alternating id buffers.  The
+   * selection then scores while that kernel is still running and waits for it only before it
+   * writes ids, count and byte map. */
+  BAS_SCORE_INPUTS_STABLE = 512
 } bas_score_kind;
 
 BAS_API const char* bas_status_string(int status);

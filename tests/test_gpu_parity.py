@@ -486,6 +486,39 @@ def test_weighted_selection_in_sparse_linear(dev):
     assert O.max_err_ratio(y2.float().cpu().numpy(), ref2) <= 2e-3
 
 
+@pytest.mark.parametrize("b", [2, 16, 64])
+def test_selection_with_stable_inputs_in_a_chain(dev, b):
+    """Online selection over several steps, the selection of step i+1 declaring its inputs stable so
+    that it scores while the contraction of step i runs (two alternating id buffers): every step's
+    ids are bit-exact and every step's output within tolerance."""
+    ops = _ops()
+    k, n, steps = 11008, 4096, 6
+    nb = k // 64
+    n_keep = O.n_keep_from_density(0.36, nb)
+    w = O.make_weight(n, k, seed=81)
+    packed = ops.pack_weight(torch.from_numpy(w).to(dev))
+    xs = [O.make_activations(b, k, seed=800 + i, dist="laplace") for i in range(steps)]
+    txs = [torch.from_numpy(x).to(dev) for x in xs]
+    bufs = [(torch.full((nb,), -1, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev))
+            for _ in range(2)]
+    outs = [torch.full((b, n), float("nan"), dtype=torch.float16, device=dev) for _ in range(steps)]
+    torch.cuda.synchronize()
+    for i in range(steps):          # nothing but the library's own launches in the stream: they overlap
+        ids_buf, cnt_buf = bufs[i & 1]
+        sel, cnt = ops.select_topk(txs[i], n_keep, O.SCORE_ENERGY, ids_out=ids_buf, count_out=cnt_buf,
+                                   inputs_stable=True)
+        ops.gemm(txs[i], packed, outs[i], ids=sel, count=cnt, k_host=n_keep)
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
+    for i in range(steps):
+        want = O.topk_ids(O.block_scores(xs[i], O.SCORE_ENERGY), n_keep)
+        if i >= steps - 2:          # the two buffers still hold the last two steps' ids
+            assert int(bufs[i & 1][1].item()) == n_keep
+            assert np.array_equal(bufs[i & 1][0][:n_keep].cpu().numpy(), want), f"step {i}"
+        # a step that multiplied through another step's mask would miss the tolerance by far
+        assert O.max_err_ratio(outs[i].cpu().numpy(), O.masked_gemm(xs[i], w, want)) <= TOL, f"step {i}"
+
+
 def test_selection_ties_go_to_lower_index(dev):
     x = np.zeros((4, 640), np.float16)
     x[:, 64:128] = 1.0

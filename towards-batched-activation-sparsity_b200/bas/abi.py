@@ -14,6 +14,7 @@ IDS_STABLE = 16          # BAS_GEMM_IDS_STABLE
 X_STABLE = 64            # BAS_GEMM_X_STABLE
 GEMM_BF16 = 32           # BAS_GEMM_BF16
 SCORE_BF16 = 256         # BAS_SCORE_BF16
+SCORE_INPUTS_STABLE = 512   # BAS_SCORE_INPUTS_STABLE
 TP_HANDLE_BYTES = 64     # BAS_TP_HANDLE_BYTES
 
 _PKG = Path(__file__).resolve().parent.parent

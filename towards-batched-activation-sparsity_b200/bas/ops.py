@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 from . import abi as _abi
-from .abi import (BLOCK_K, GEMM_BF16, IDS_STABLE, X_STABLE, MAX_BATCH, SCORE_BF16, SCORE_ENERGY, SCORE_NORM, TP_HANDLE_BYTES,
+from .abi import (BLOCK_K, GEMM_BF16, IDS_STABLE, X_STABLE, MAX_BATCH, SCORE_BF16, SCORE_INPUTS_STABLE, SCORE_ENERGY, SCORE_NORM, TP_HANDLE_BYTES,
                   check, lib)
 
 _PACKED: dict[tuple, torch.Tensor] = {}
@@ -276,15 +276,20 @@ def _select_buffers(device: torch.device, nb: int):
 def select_topk(x2d: torch.Tensor, n_keep: int, score_kind: int = SCORE_NORM, *,
                 ids_out: Optional[torch.Tensor] = None, count_out: Optional[torch.Tensor] = None,
                 bitmap_out: Optional[torch.Tensor] = None, scores_out: Optional[torch.Tensor] = None,
-                chan_scale: Optional[torch.Tensor] = None, block_mult: Optional[torch.Tensor] = None):
+                chan_scale: Optional[torch.Tensor] = None, block_mult: Optional[torch.Tensor] = None,
+                inputs_stable: bool = False):
     """Device-side batch-shared top-k selection.  Returns (ids[:n_keep] int32 ascending, count int32[1]);
     both stay on the device.  Without explicit outputs, per-stream buffers are reused.
 
     ``chan_scale`` (float32 [>= 64 * (K // 64)]) and ``block_mult`` (float32 [K // 64]) are the
     reference's optional score modifiers (scripts/bench_roundrobin_e2e_decode.py:104-112): weighted
-    squares per channel, and a factor per block (see :func:`prior_multiplier`)."""
-    return _select(x2d, 0, int(n_keep), score_kind, 0.0, ids_out, count_out, bitmap_out, scores_out,
-                   chan_scale, block_mult)
+    squares per channel, and a factor per block (see :func:`prior_multiplier`).
+
+    ``inputs_stable``: promise that no kernel still running when this call starts writes ``x2d`` or
+    touches the outputs (pass explicit ``ids_out`` / ``count_out`` that alternate between steps) or
+    the selection workspace; the scoring then overlaps the kernel launched before this call."""
+    return _select(x2d, 0, int(n_keep), int(score_kind) | (SCORE_INPUTS_STABLE if inputs_stable else 0), 0.0,
+                   ids_out, count_out, bitmap_out, scores_out, chan_scale, block_mult)
 
 
 def prior_multiplier(block_prior: torch.Tensor, prior_alpha: float = 1.0, prior_eps: float = 0.1) -> torch.Tensor:

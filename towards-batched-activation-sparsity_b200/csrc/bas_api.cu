@@ -354,7 +354,8 @@ static int select_common(const void* x_dev, int64_t ldx, int batch, int k, int m
   const int nb = k / kBlockK;  // trailing K mod 64 channels are never scored (d_eff)
   if (nb > BAS_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
   const int bf16 = (score_kind & BAS_SCORE_BF16) != 0 ? 1 : 0;
-  score_kind &= ~BAS_SCORE_BF16;
+  const int inputs_stable = (score_kind & BAS_SCORE_INPUTS_STABLE) != 0 ? 1 : 0;
+  score_kind &= ~(BAS_SCORE_BF16 | BAS_SCORE_INPUTS_STABLE);
   if (score_kind != BAS_SCORE_NORM && score_kind != BAS_SCORE_ENERGY) return BAS_ERR_INVALID_ARGUMENT;
   if (n_keep < 0 || n_keep > nb) return BAS_ERR_INVALID_ARGUMENT;
   if (ws_dev == nullptr || ws_bytes < bas_select_workspace_bytes(k)) return BAS_ERR_WORKSPACE;
@@ -380,6 +381,7 @@ static int select_common(const void* x_dev, int64_t ldx, int batch, int k, int m
   p.ws_scores = (double*)((uint8_t*)ws_dev + 256);
   p.chan_scale = chan_scale_dev;
   p.block_mult = block_mult_dev;
+  p.inputs_stable = inputs_stable;
   if (chan_scale_dev != nullptr) p.score_kind = BAS_SCORE_ENERGY;   // weighted squares, no root (as the reference)
   cudaError_t e = launch_select(p, di.sm_count, (cudaStream_t)stream);
   return e == cudaSuccess ? BAS_OK : cuda_fail(e);

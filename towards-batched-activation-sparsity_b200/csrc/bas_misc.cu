@@ -75,7 +75,10 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   // Launched with programmatic stream serialization: everything this kernel reads (X) or writes
   // (ids, count, byte map, workspace) may still be in use by the kernel before it, so the wait comes
   // first; the kernel after it may be set up meanwhile and waits for this grid's completion itself.
-  pdl_wait();
+  // With BAS_SCORE_INPUTS_STABLE the caller has promised that the preceding kernel neither writes X nor
+  // touches this call's outputs and workspace: the scoring then runs beside that kernel (on SMs it
+  // leaves free), and the wait moves to the end, where it only keeps completions in stream order.
+  if (!p.inputs_stable) pdl_wait();
   pdl_launch_dependents();
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -154,6 +157,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     if (s_last) *p.ws_done = 0u;   // re-arm for the next call
   }
   __syncthreads();
+  if (p.inputs_stable) pdl_wait();   // no CTA leaves, and nothing below is written, before the preceding kernel is done
   if (!s_last) return;
   __threadfence();
 
