@@ -76,8 +76,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   // (ids, count, byte map, workspace) may still be in use by the kernel before it, so the wait comes
   // first; the kernel after it may be set up meanwhile and waits for this grid's completion itself.
   // With BAS_SCORE_INPUTS_STABLE the caller has promised that the preceding kernel neither writes X nor
-  // touches this call's outputs and workspace: the scoring then runs beside that kernel (on SMs it
-  // leaves free), and the wait moves to the end, where it only keeps completions in stream order.
+  // touches this call's outputs and workspace: scoring and ranking then run beside that kernel (on SMs
+  // it leaves free), and the wait moves to just before the outputs are written.
   if (!p.inputs_stable) pdl_wait();
   pdl_launch_dependents();
 
@@ -157,7 +157,6 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     if (s_last) *p.ws_done = 0u;   // re-arm for the next call
   }
   __syncthreads();
-  if (p.inputs_stable) pdl_wait();   // no CTA leaves, and nothing below is written, before the preceding kernel is done
   if (!s_last) return;
   __threadfence();
 
@@ -168,7 +167,6 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   for (int j = tid; j < p.nb; j += nthreads) {
     const double s = __ldcg(p.ws_scores + j);
     s_score[j] = s;
-    if (p.scores_out != nullptr) p.scores_out[j] = s;
   }
   __syncthreads();
   // one thread per block counts the blocks that rank before it (about 30 k comparisons in all: the
@@ -203,11 +201,16 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   }
   __syncthreads();
   const int keep = s_keep;
+  // Stable inputs: everything so far ran beside the preceding kernel and wrote only the workspace and
+  // shared memory.  The caller's outputs are written after that kernel has completed; as this CTA is
+  // part of the grid, the grid also completes after it, which keeps completions in stream order.
+  if (p.inputs_stable) pdl_wait();
   // ascending compaction of the kept ids
   int running = 0;
   for (int base = 0; base < p.nb; base += nthreads) {
     const int j = base + tid;
     const bool kept = (j < p.nb) && (s_rank[j] < keep);
+    if (j < p.nb && p.scores_out != nullptr) p.scores_out[j] = s_score[j];
     if (j < p.nb && p.bitmap_out != nullptr) p.bitmap_out[j] = kept ? 1 : 0;
     const unsigned m = __ballot_sync(0xffffffffu, kept);
     if (lane == 0) s_warp_cnt[warp] = __popc(m);
