@@ -250,10 +250,13 @@ def test_stable_x_chain_writing_one_output(dev):
     assert O.max_err_ratio(out.cpu().numpy(), O.masked_gemm(y1, w, idl[2])) <= TOL
 
 
-@pytest.mark.parametrize("b,k,n", [(16, 4096, 11008), (2, 4096, 2048), (64, 4096, 1024), (33, 1024, 4096 + 40)])
+@pytest.mark.parametrize("b,k,n", [(16, 4096, 11008), (2, 4096, 2048), (64, 4096, 1024), (33, 1024, 4096 + 40),
+                                   (32, 4096, 11008), (8, 2048, 12304), (48, 1024, 11008)])
 def test_stable_x_chain_in_cuda_graph(dev, b, k, n):
     """A CUDA graph of eight calls that declare ids and X stable (the form the benchmark times), over
-    output widths on both sides of the small-grid rule, replayed twice: every output exact."""
+    output widths on both sides of the small-grid rule (wide outputs run two 128-column passes per CTA
+    into separate accumulator columns up to 32 rows, one pass beyond), replayed twice: every output
+    exact."""
     ops = _ops()
     w = O.make_weight(n, k, seed=61)
     packed = ops.pack_weight(torch.from_numpy(w).to(dev))

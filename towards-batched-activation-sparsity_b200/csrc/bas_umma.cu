@@ -484,14 +484,24 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         const int NG = (M + G - 1) / G;
         int cur_sub = 0;       // sub-tile this issuer's accumulator currently holds
         bool fresh = true;     // nothing multiplied into it yet
+        // Passes with accumulator columns of their own (pass s at column offset s * BPAD): nothing is
+        // handed to the epilogue between passes, so a CTA whose epilogue may not store yet (it waits for
+        // the preceding kernel) keeps multiplying; one hand-over at the very end.
+        const bool multi = (p.flags & kFlagMultiAcc) != 0;
+        bool any_mma = false;
         // Finish with sub-tiles [cur_sub, target): tell the epilogue (the commit waits for this
         // issuer's MMAs), then wait until it has drained them before the accumulator is reused.
         auto advance_to = [&](int target) -> bool {
           while (cur_sub < target) {
+            if (multi && cur_sub + 1 < n_sub) {
+              ++cur_sub;
+              fresh = true;
+              continue;
+            }
             if (w == 0) BAS_TRACE_SET(16, BAS_TRACE_CLOCK() - hdr->t0);   // issuer 0: last MMA of the sub-tile issued
-            if (!fresh) umma_commit(&hdr->acc_full);
+            if (multi ? any_mma : !fresh) umma_commit(&hdr->acc_full);
             else mbar_arrive(&hdr->acc_full);
-            if (cur_sub + 1 < n_sub && !mbar_wait(&hdr->acc_empty, cur_sub & 1, abort_flag)) return false;
+            if (!multi && cur_sub + 1 < n_sub && !mbar_wait(&hdr->acc_empty, cur_sub & 1, abort_flag)) return false;
             ++cur_sub;
             fresh = true;
           }
@@ -522,9 +532,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             for (int ks = 0; ks < 4; ++ks) {
               // 16 channels = 32 bytes along K: +2 in the descriptor's 16-byte address units; the
               // first MMA into a fresh accumulator overwrites it instead of adding
-              umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc, (fresh && ks == 0) ? 0u : 1u);
+              umma_f16_ss(d + (multi ? (uint32_t)(cur_sub * BPAD) : 0u), adesc + (uint64_t)(2 * ks),
+                          bdesc + (uint64_t)(2 * ks), kIdesc, (fresh && ks == 0) ? 0u : 1u);
             }
             fresh = false;
+            any_mma = true;
             if (++ii == k_mine) {
               ii = 0;
               ++sub;
@@ -566,6 +578,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       constexpr int kChunks = BPAD / 16;
       constexpr int kChunks0 = (kChunks + 1) / 2;   // set 0's chunks; set 1 takes the rest
       if (early_ids && !late_wait) pdl_wait();   // before the first write to Y (late_wait: at the stores)
+      const bool multi = (p.flags & kFlagMultiAcc) != 0;   // see the issuers: one hand-over for all passes
       if (TP) {
         // The rank's call counter: advanced by the last CTA to finish the previous call, i.e. before
         // the wait above (or warp 0's, which the id barrier orders before this point) returned.
@@ -589,9 +602,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       } else if (ok) {
         for (int sub = 0; sub < n_sub && ok; ++sub) {
           const int wsub = min(TW, width - sub * TW);
-          if (k_mine > 0) {
+          if (k_mine > 0 && (!multi || sub == 0)) {
             // warp-uniform verdict: tcgen05.ld below needs the whole warp
-            if (!__all_sync(0xffffffffu, mbar_wait(&hdr->acc_full, sub & 1, abort_flag))) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&hdr->acc_full, multi ? 0 : (sub & 1), abort_flag))) {
               ok = false;
               break;
             }
@@ -624,7 +637,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 #pragma unroll
                       for (int cc = 0; cc < NCH; ++cc)
                         tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) +
-                                               (uint32_t)((w0 + wi) * 64 + (CH0 + cc) * 16),
+                                               (uint32_t)((w0 + wi) * 64 + (CH0 + cc) * 16 + (multi ? sub * BPAD : 0)),
                                            regs[wi][cc]);
                     }
                   tmem_ld_wait();
@@ -1031,6 +1044,13 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   if (pipelined && forced == 0 && ((p.flags >> 16) & 0xff) == 0 && r_min >= 16 && r_min <= sm_count) {
     cluster = 1;
     ranges = r_min;
+    // Wide outputs (more ranges than half the SMs) at batches of up to 32 rows: two 128-column passes
+    // per CTA, each pass with accumulator columns of its own, so that again several calls fit.
+    if (r_min > sm_count / 2 && 2 * BPAD <= 64) {
+      ranges = (r_min + 1) / 2;
+      if (((units + ranges - 1) / ranges) * 8 <= 2 * kTileN) p.flags |= kFlagMultiAcc;
+      else ranges = r_min;
+    }
   }
   // Measured over the layer stack's shapes: waiting for the predecessor only at the stores pays (4-17 %)
   // when this call leaves at least half the SMs to its successors, and costs 7 % on the 86-CTA grid.
