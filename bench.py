@@ -338,7 +338,7 @@ def run_gpu(args) -> None:
         for b in BATCHES:
             c = counter["i"] % ROTATE
             counter["i"] += 1
-            ops.gemm(xs[b], packed[c], outs[b], ids=ids[b], ids_stable=True, x_stable=True)
+            ops.gemm(xs[b], packed[c], outs[b], ids=ids[b], ids_stable=True, x_stable=True, next_independent=True)
 
     # ---- the K timed steps ----
     GS = 16                                                     # steps per captured graph
@@ -403,7 +403,7 @@ def run_gpu(args) -> None:
     for b in BATCHES:
         def sparse_cold(b=b):
             for c in range(ROTATE):
-                ops.gemm(xs[b], packed[c], outs[b], ids=ids[b], ids_stable=True, x_stable=True)
+                ops.gemm(xs[b], packed[c], outs[b], ids=ids[b], ids_stable=True, x_stable=True, next_independent=True)
 
         def sparse_cold_ids_only(b=b):        # X may be the previous call's output: one call deep
             for c in range(ROTATE):
@@ -616,7 +616,7 @@ def run_gpu(args) -> None:
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD,
                        "step": "3 masked GEMMs (B=2,16,64); activations and masks are resident before the chain of "
-                               "calls starts and declared so (BAS_GEMM_IDS_STABLE | BAS_GEMM_X_STABLE): independent "
+                               "calls starts and declared so (BAS_GEMM_IDS_STABLE | BAS_GEMM_X_STABLE | BAS_GEMM_NEXT_INDEPENDENT): independent "
                                "calls of a stream pipeline several deep, each waiting for its predecessor only "
                                "before it stores.  per_batch also has the same chains with only the masks declared "
                                "stable (ids_stable_only_*) and with nothing declared, as the drop-in wrappers "
@@ -652,7 +652,7 @@ def run_profile_case(batch: int, family: int = 0, pipelined: bool = False) -> No
         ids = ops.select_topk(x, nk, abi.SCORE_NORM)[0].clone()
         torch.cuda.synchronize()
         for i in range(8):
-            ops.gemm(x, packed[i % 4], out, ids=ids, family=family, ids_stable=True, x_stable=True)
+            ops.gemm(x, packed[i % 4], out, ids=ids, family=family, ids_stable=True, x_stable=True, next_independent=True)
     else:
         for i in range(8):
             ids, cnt = ops.select_topk(x, nk, abi.SCORE_NORM)

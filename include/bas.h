@@ -114,10 +114,15 @@ BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, con
  *             (a resident input, or the X the preceding call of this library already read, as for
  *             q/k/v or gate/up of one layer).  Nothing the kernel reads then depends on the kernel
  *             before it: it streams and multiplies straight through and waits for that kernel only
- *             before its first store to Y.  Such calls are given a small grid (one CTA per 128 output
- *             columns) so that several of them are resident at once: meant for chains launched back
- *             to back (one CUDA graph, or a launch loop that keeps ahead of the GPU); a call that
- *             runs alone takes about twice as long with the flag as without it.
+ *             before its first store to Y.
+ *             Such calls are given a small grid (one CTA per 128 output columns) so that several of
+ *             them are resident at once: meant for calls launched back to back (one CUDA graph, or
+ *             a launch loop that keeps ahead of the GPU); a call that runs alone takes about twice
+ *             as long with the flag as without it.
+ *   BAS_GEMM_NEXT_INDEPENDENT  (with the two flags above) a hint, not a promise: the call after
+ *             this one will carry BAS_GEMM_X_STABLE too (a chain of independent calls).  Outputs of
+ *             more than 9 472 columns at batches of up to 32 rows then run two 128-column passes per
+ *             CTA on half as many CTAs, which pays only if the next calls do run beside this one.
  *   bits 8-10 cluster size of the tcgen05 kernel: 0 = chosen by batch size, else 1, 2 or 4 CTAs
  *             share the active blocks of one column range (reduced on chip, in rank order).
  *   BAS_GEMM_BF16  X, the packed weight and Y hold bfloat16 instead of fp16 (the reference's kernels
@@ -131,6 +136,7 @@ BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, con
 #define BAS_GEMM_IDS_STABLE 16
 #define BAS_GEMM_BF16 32
 #define BAS_GEMM_X_STABLE 64
+#define BAS_GEMM_NEXT_INDEPENDENT 128
 BAS_API int bas_gemm_ex(const void* x_dev, int64_t ldx, const void* packed_dev, const int32_t* ids_dev,
                 const int32_t* count_dev, int k_host, const uint8_t* bitmap_dev, int batch, int k, int n,
                 void* y_dev, int64_t ldy, void* ws_dev, size_t ws_bytes, int flags, void* stream);

@@ -214,7 +214,7 @@ def test_back_to_back_launches_with_stable_ids(dev, b, x_stable):
     torch.cuda.synchronize()
     for rep in range(3):
         for i in range(4):
-            ops.gemm(txs[i], packed, outs[i], ids=tids[i], ids_stable=True, x_stable=x_stable)
+            ops.gemm(txs[i], packed, outs[i], ids=tids[i], ids_stable=True, x_stable=x_stable, next_independent=x_stable)
     torch.cuda.synchronize()
     assert ops.read_status(dev) == 0
     for i in range(4):
@@ -237,7 +237,7 @@ def test_stable_x_chain_writing_one_output(dev):
     mid = torch.empty((b, n), dtype=torch.float16, device=dev)
     torch.cuda.synchronize()
     for i in range(4):
-        ops.gemm(tx, packed, out, ids=tids[i], ids_stable=True, x_stable=True)
+        ops.gemm(tx, packed, out, ids=tids[i], ids_stable=True, x_stable=True, next_independent=True)
     torch.cuda.synchronize()
     assert O.max_err_ratio(out.cpu().numpy(), O.masked_gemm(x, w, idl[3])) <= TOL
     # producer -> consumer: the second call reads what the first stored, so it does not set the flag
@@ -269,13 +269,13 @@ def test_stable_x_chain_in_cuda_graph(dev, b, k, n):
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         for i in range(4):      # warm-up outside the capture (tensor maps, function attributes)
-            ops.gemm(txs[i], packed, outs[i], ids=tids[i], ids_stable=True, x_stable=True)
+            ops.gemm(txs[i], packed, outs[i], ids=tids[i], ids_stable=True, x_stable=True, next_independent=True)
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g, stream=stream):
         for rep in range(2):
             for i in range(4):
-                ops.gemm(txs[i], packed, outs[i], ids=tids[i], ids_stable=True, x_stable=True)
+                ops.gemm(txs[i], packed, outs[i], ids=tids[i], ids_stable=True, x_stable=True, next_independent=True)
     for o in outs:
         o.fill_(float("nan"))
     torch.cuda.synchronize()
@@ -308,7 +308,7 @@ def test_stable_x_variants(dev, form):
     idl = [O.random_active_blocks(nb, nk, seed=nk) for nk in (40, 9, 0 if form == "empty" else 21)]
     torch.cuda.synchronize()
     for ids in idl:
-        kw = dict(ids_stable=True, x_stable=True)
+        kw = dict(ids_stable=True, x_stable=True, next_independent=True)
         if form == "bitmap":
             kw["bitmap"] = torch.from_numpy(O.build_bitmap(ids, nb)).to(dev)
         else:

@@ -12,6 +12,7 @@ SCORE_NORM = 0
 SCORE_ENERGY = 1
 IDS_STABLE = 16          # BAS_GEMM_IDS_STABLE
 X_STABLE = 64            # BAS_GEMM_X_STABLE
+NEXT_INDEPENDENT = 128   # BAS_GEMM_NEXT_INDEPENDENT
 GEMM_BF16 = 32           # BAS_GEMM_BF16
 SCORE_BF16 = 256         # BAS_SCORE_BF16
 SCORE_INPUTS_STABLE = 512   # BAS_SCORE_INPUTS_STABLE

@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 from . import abi as _abi
-from .abi import (BLOCK_K, GEMM_BF16, IDS_STABLE, X_STABLE, MAX_BATCH, SCORE_BF16, SCORE_INPUTS_STABLE, SCORE_ENERGY, SCORE_NORM, TP_HANDLE_BYTES,
+from .abi import (BLOCK_K, GEMM_BF16, IDS_STABLE, X_STABLE, NEXT_INDEPENDENT, MAX_BATCH, SCORE_BF16, SCORE_INPUTS_STABLE, SCORE_ENERGY, SCORE_NORM, TP_HANDLE_BYTES,
                   check, lib)
 
 _PACKED: dict[tuple, torch.Tensor] = {}
@@ -131,7 +131,7 @@ def read_status(device: Optional[torch.device] = None) -> int:
 def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: Optional[torch.Tensor] = None,
          count: Optional[torch.Tensor] = None, k_host: Optional[int] = None,
          bitmap: Optional[torch.Tensor] = None, family: int = 0, ids_stable: bool = False,
-         x_stable: bool = False, cluster: int = 0, pairs: int = 0, tp=None, max_ctas: int = 0) -> None:
+         x_stable: bool = False, next_independent: bool = False, cluster: int = 0, pairs: int = 0, tp=None, max_ctas: int = 0) -> None:
     """out2d[B, N] = x2d[B, K] restricted to the active blocks, times W^T.
 
     ``ids`` int32 device list (``count``: optional int32[1] device-side length, ``k_host`` an upper
@@ -141,6 +141,8 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
     ``x_stable`` (with ``ids_stable``): the same promise for ``x2d`` - it was complete before the kernel
     launched just before this call started (a resident input, or the x that call already read); the
     kernel then waits for its predecessor only before it stores ``out2d``.
+    ``next_independent`` (with both promises): a hint that the call after this one will be launched
+    with ``x_stable`` too (a chain of independent calls); wide outputs then take an even smaller grid.
     ``cluster``: 0 lets the library choose; 1, 2 or 4 forces the tcgen05 kernel's cluster size.
     ``pairs``: 0 lets the library choose; 2, 3 or 4 forces its number of copy/MMA warp pairs.
     ``max_ctas``: 0 lets the library choose; else an upper bound (up to 255) on the kernel's CTAs.
@@ -185,7 +187,7 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
                 count.data_ptr() if count is not None else None, int(k_host),
                 bitmap.data_ptr() if bitmap is not None else None,
                 bsz, k, n, ys.data_ptr(), ys.stride(0), ws.data_ptr(), ws.numel(),
-                int(family) | (IDS_STABLE if ids_stable else 0) | (X_STABLE if ids_stable and x_stable else 0) | bf16 | (int(cluster) << 8) | (int(pairs) << 12) | (int(max_ctas) << 16), stream),
+                int(family) | (IDS_STABLE if ids_stable else 0) | (X_STABLE if ids_stable and x_stable else 0) | (NEXT_INDEPENDENT if next_independent else 0) | bf16 | (int(cluster) << 8) | (int(pairs) << 12) | (int(max_ctas) << 16), stream),
                 "bas_gemm")
 
 

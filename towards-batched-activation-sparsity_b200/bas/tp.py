@@ -101,7 +101,7 @@ class ShardedLinear:
         self.packed = ops.pack_weight(shard.contiguous()) if self.n_local and self.k_local else None
 
     def forward(self, x2d, bitmap, out2d, ids_stable: bool = True, exchange=None, n_keep: int = 0,
-                x_stable: bool = False):
+                x_stable: bool = False, next_independent: bool = False):
         """x2d is the replicated [B, K] activation, bitmap the replicated uint8[K/64] mask.  Writes
         this rank's output slice (column-parallel) or partial sum (row-parallel) into out2d; with an
         ``exchange`` group a row-parallel linear writes the sum over all ranks instead (formed inside
@@ -119,7 +119,7 @@ class ShardedLinear:
         nb_all = bitmap.numel()
         hint = max(1, (int(n_keep) * (self.b1 - self.b0) + nb_all - 1) // nb_all) if n_keep else 0
         ops.gemm(xs, self.packed, out2d, bitmap=bitmap[self.b0:self.b1], k_host=hint, ids_stable=ids_stable,
-                 x_stable=x_stable, tp=exchange if row else None)
+                 x_stable=x_stable, next_independent=next_independent, tp=exchange if row else None)
 
 
 class DecodeLinearStack:
@@ -210,6 +210,7 @@ class DecodeLinearStack:
             # k, v and up read, in the model, the activation the call before them (q, gate) has already
             # read: only these declare their input stable
             lin.forward(x, bitmap, out, exchange=self.exchange, n_keep=n_keep,
-                        x_stable=self.independent_calls or lin.spec.name in SHARES_PREVIOUS_INPUT)
+                        x_stable=self.independent_calls or lin.spec.name in SHARES_PREVIOUS_INPUT,
+                        next_independent=self.independent_calls)
             if lin.spec.parallel == "row" and self.world > 1 and self.exchange is None:
                 dist.all_reduce(out, group=self.group)

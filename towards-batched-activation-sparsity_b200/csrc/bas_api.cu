@@ -225,7 +225,7 @@ static int gemm_impl(const bas_tp* tp, const FusedSelect* sel, const void* x_dev
   if (!aligned16(x_dev) || !aligned16(packed_dev) || (ldx & 7) != 0 || (k & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
   if (ws_dev == nullptr || ws_bytes < bas_gemm_workspace_bytes(batch, n)) return BAS_ERR_WORKSPACE;
   const int family = flags & 3;
-  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_X_STABLE | BAS_GEMM_BF16 | 0x700 | 0x7000 | 0xff0000 | (1 << 24))) != 0) return BAS_ERR_INVALID_ARGUMENT;
+  if (flags < 0 || family > 2 || (flags & ~(3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_X_STABLE | BAS_GEMM_NEXT_INDEPENDENT | BAS_GEMM_BF16 | 0x700 | 0x7000 | 0xff0000 | (1 << 24))) != 0) return BAS_ERR_INVALID_ARGUMENT;
 
   DeviceInfo di;
   int st = device_info(&di);
@@ -428,7 +428,7 @@ int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, int 
   const bool budget = energy_keep >= 0.0;
   const int nb_sel = k / kBlockK;
   if ((kind != BAS_SCORE_NORM && kind != BAS_SCORE_ENERGY) || n_keep < 0 || n_keep > nb_sel ||
-      (flags & (3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_X_STABLE)) != 0)
+      (flags & (3 | BAS_GEMM_IDS_STABLE | BAS_GEMM_X_STABLE | BAS_GEMM_NEXT_INDEPENDENT)) != 0)
     return BAS_ERR_INVALID_ARGUMENT;
   FusedSelect sel;
   sel.mode = budget ? 2 : 1;

@@ -73,6 +73,7 @@ constexpr int kFlagStableIds = 16;   // BAS_GEMM_IDS_STABLE: the id list is not 
 constexpr int kFlagStableX = 64;     // BAS_GEMM_X_STABLE: nor is X (only with kFlagStableIds)
 constexpr int kFlagLateWait = 1 << 25;   // set by the launcher (stable X, grid of at most half the SMs): wait for the predecessor only at the stores
 constexpr int kFlagMultiAcc = 1 << 26;   // set by the launcher: every 128-column pass of a CTA has accumulator columns of its own
+constexpr int kFlagNextIndependent = 128;   // BAS_GEMM_NEXT_INDEPENDENT: the next call can run beside this one (grid-size hint)
 constexpr int kFlagBf16 = 32;        // BAS_GEMM_BF16: X, W and Y are bfloat16 (same 16-bit containers)
 
 // Launch with the programmatic-serialization attribute, so that this kernel's preamble (and, when

@@ -1044,9 +1044,12 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
   if (pipelined && forced == 0 && ((p.flags >> 16) & 0xff) == 0 && r_min >= 16 && r_min <= sm_count) {
     cluster = 1;
     ranges = r_min;
-    // Wide outputs (more ranges than half the SMs) at batches of up to 32 rows: two 128-column passes
-    // per CTA, each pass with accumulator columns of its own, so that again several calls fit.
-    if (r_min > sm_count / 2 && 2 * BPAD <= 64) {
+    // Wide outputs (more ranges than half the SMs) at batches of up to 32 rows, where the caller says
+    // that the call after this one is independent too (BAS_GEMM_NEXT_INDEPENDENT: a deep chain): two
+    // 128-column passes per CTA, each pass with accumulator columns of its own, so that again several
+    // calls fit.  Followed by a call that has to wait for it, this grid is the slower one (measured on
+    // the layer stack: up before down).
+    if ((p.flags & kFlagNextIndependent) != 0 && r_min > sm_count / 2 && 2 * BPAD <= 64) {
       ranges = (r_min + 1) / 2;
       if (((units + ranges - 1) / ranges) * 8 <= 2 * kTileN) p.flags |= kFlagMultiAcc;
       else ranges = r_min;
