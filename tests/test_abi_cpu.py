@@ -28,6 +28,27 @@ def test_library_exports_every_declared_symbol():
     assert not missing_in_binding, f"ctypes binding lacks {missing_in_binding}"
 
 
+def test_flag_constants_match_the_header():
+    """The Python binding's flag values are the header's: a drifted constant would silently turn a
+    caller's promise into another flag."""
+    from bas import abi as L
+
+    text = (ROOT / "include" / "bas.h").read_text()
+    defines = {m.group(1): int(m.group(2)) for m in re.finditer(r"#define\s+(BAS_[A-Z_]+)\s+(\d+)\b", text)}
+    enums = {m.group(1): int(m.group(2)) for m in re.finditer(r"\b(BAS_SCORE_[A-Z_0-9]+)\s*=\s*(\d+)", text)}
+    assert defines["BAS_GEMM_IDS_STABLE"] == L.IDS_STABLE
+    assert defines["BAS_GEMM_X_STABLE"] == L.X_STABLE
+    assert defines["BAS_GEMM_NEXT_INDEPENDENT"] == L.NEXT_INDEPENDENT
+    assert defines["BAS_GEMM_BF16"] == L.GEMM_BF16
+    assert enums["BAS_SCORE_NORM"] == L.SCORE_NORM and enums["BAS_SCORE_ENERGY"] == L.SCORE_ENERGY
+    assert enums["BAS_SCORE_BF16"] == L.SCORE_BF16
+    assert enums["BAS_SCORE_INPUTS_STABLE"] == L.SCORE_INPUTS_STABLE
+    # flag bits the library does not know are refused, not ignored
+    dummy = ctypes.c_void_p(4096)
+    st = L.lib.bas_gemm_ex(dummy, 64, dummy, dummy, None, 1, None, 2, 64, 128, dummy, 128, dummy, 1 << 30, 1 << 27, None)
+    assert st == 1
+
+
 def test_host_only_entry_points():
     from bas import abi as L
 
