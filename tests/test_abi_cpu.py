@@ -34,7 +34,7 @@ def test_flag_constants_match_the_header():
     from bas import abi as L
 
     text = (ROOT / "include" / "bas.h").read_text()
-    defines = {m.group(1): int(m.group(2)) for m in re.finditer(r"#define\s+(BAS_[A-Z_]+)\s+(\d+)\b", text)}
+    defines = {m.group(1): int(m.group(2)) for m in re.finditer(r"#define\s+(BAS_[A-Z_0-9]+)\s+(\d+)\b", text)}
     enums = {m.group(1): int(m.group(2)) for m in re.finditer(r"\b(BAS_SCORE_[A-Z_0-9]+)\s*=\s*(\d+)", text)}
     assert defines["BAS_GEMM_IDS_STABLE"] == L.IDS_STABLE
     assert defines["BAS_GEMM_X_STABLE"] == L.X_STABLE
