@@ -114,7 +114,9 @@ BAS_API int bas_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, con
  *             (a resident input, or the X the preceding call of this library already read, as for
  *             q/k/v or gate/up of one layer).  Nothing the kernel reads then depends on the kernel
  *             before it: it streams and multiplies straight through and waits for that kernel only
- *             before its first store to Y.
+ *             before its first store to Y.  A preceding call that carries the flag itself may have
+ *             started before ITS predecessor finished: X must then not be that call's output
+ *             either, and so on back to the last call launched without the flag.
  *             Such calls are given a small grid (one CTA per 128 output columns) so that several of
  *             them are resident at once: meant for calls launched back to back (one CUDA graph, or
  *             a launch loop that keeps ahead of the GPU); a call that runs alone takes about twice
