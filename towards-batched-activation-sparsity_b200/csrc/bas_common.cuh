@@ -97,14 +97,8 @@ __device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_s
                "l"(__cvta_generic_to_global(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
-// L2 eviction policies for the copies below.  Weights are read once per call and never again before
-// gigabytes of other weights have passed: marked evict-first they do not push the small, re-read
-// operands (activations, id lists, outputs) out of L2; those are marked evict-last.
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
+// L2 eviction policy for the small operands that every CTA and the next call re-read (activations,
+// id lists): evict-last, so that the weights streaming past do not push them out of L2.
 __device__ __forceinline__ uint64_t l2_policy_evict_last() {
   uint64_t pol;
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
@@ -119,14 +113,6 @@ __device__ __forceinline__ unsigned int ld_nc_keep_u8(const uint8_t* p, uint64_t
   unsigned int v;
   asm volatile("ld.global.nc.L2::cache_hint.u8 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(policy));
   return v;
-}
-__device__ __forceinline__ void bulk_copy_g2s_hint(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar,
-                                                   uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
-          smem_u32(smem_dst)),
-      "l"(__cvta_generic_to_global(gmem_src)), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
-      : "memory");
 }
 __device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar,
                                                  uint64_t policy) {
