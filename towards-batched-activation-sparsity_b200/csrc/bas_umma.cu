@@ -21,6 +21,11 @@
 // them and store or, in cluster mode, push them to the owning CTA.  All waits are bounded mbarrier
 // waits; TMEM is released on every path.
 //
+// Calls that declared their id list and X stable (nothing they read depends on the kernel before
+// them) run on a small grid - one CTA per 128-column range, wide outputs optionally two passes per CTA
+// with accumulator columns per pass - and wait for their predecessor only before they store, so
+// that several calls of a stream are resident at once.
+//
 // Two variants are instantiated beside the plain kernel: TP sends the result as fp32 partials to the
 // other ranks of a box and adds theirs (row-parallel linears), SEL selects the batch's mask itself
 // before multiplying (cluster modes, small batches).
@@ -283,9 +288,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   }
 #endif
 
-  // The id list may be the previous kernel's output unless the caller declared it stable; X and Y
-  // always wait for the previous kernel.  A stable list is requested right away, so that its load
-  // latency runs under the set-up below.
+  // The id list may be the previous kernel's output unless the caller declared it stable; so may X
+  // unless declared stable too; Y always waits for the previous kernel.  A stable list is requested
+  // right away, so that its load latency runs under the set-up below.
   const bool early_ids = !SEL && (p.flags & kFlagStableIds) != 0 && p.count_dev == nullptr;
   // With X stable as well nothing this kernel reads depends on the kernel before it: copies and MMAs
   // run straight through, and only the epilogue waits, before the first store to Y.
