@@ -70,6 +70,20 @@ def test_weighted_selection_matches_reference(golden):
     assert n_cases == 10
 
 
+def test_prior_multiplier_follows_the_reference_formula():
+    """clamp(prior + eps, min=1e-6) ** alpha in float32
+    (scripts/bench_roundrobin_e2e_decode.py:109-112), against the same expression in torch on CPU."""
+    import torch
+
+    prior = O.make_block_prior(172, 5)
+    prior[:3] = [-1.0, 0.0, -0.05]                    # the clamp's branch
+    for alpha, eps in ((1.0, 0.1), (0.5, 0.05), (2.0, 0.0)):
+        want = torch.clamp(torch.from_numpy(prior) + float(eps), min=1e-6).pow(float(alpha)).numpy()
+        got = O.prior_multiplier(prior, alpha, eps)
+        assert got.dtype == np.float32
+        np.testing.assert_allclose(got, want, rtol=3e-7, atol=0)
+
+
 def test_prior_of_wrong_length_is_ignored():
     x = O.make_activations(4, 640, 3, "normal")
     assert np.array_equal(O.select_active_blocks(x, 0.5, block_prior=np.ones(7, np.float32)),
