@@ -206,6 +206,57 @@ BAS_API int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_d
                             void* gemm_ws_dev, size_t gemm_ws_bytes, void* select_ws_dev, size_t select_ws_bytes,
                             int flags, void* stream);
 
+/* ---- a list of contractions as one launch ---------------------------------------------------
+ * The call pattern of a decode step: the reference patches every nn.Linear of the model and runs
+ * them one after the other, 224 per token for Llama-2-7B (scripts/bench_roundrobin_e2e_decode.py:331-503),
+ * and its benchmark adds the 224 per-projection times up per step
+ * (scripts/bench_perstep_actual_kernel_speedup.py:268-293).  A bas_list holds such a sequence of
+ * bas_gemm calls and runs it as ONE persistent kernel: the CTAs walk the list, the weight tiles of
+ * a call are fetched while the call before it is still being finished (weights never depend on
+ * it), and only a call's activations wait - for the call named in depends_on, on a counter in
+ * device memory.  Same sums as the single calls, same rounding; results do not depend on timing.
+ *
+ *   depends_on  index of an EARLIER call of the list that must be complete before x_dev is read
+ *               (normally the call that writes x_dev), or -1: x_dev is complete before the launch.
+ *               A call may overwrite a buffer that an earlier call reads only if it depends,
+ *               directly or through other calls, on that earlier call.
+ *   id lists, counts and byte maps must be complete before the launch (they may change between
+ *   runs); K / 64 of a call is at most BAS_LIST_MAX_BLOCKS, a list holds at most BAS_LIST_MAX_CALLS.
+ *   flags of bas_list_create: BAS_GEMM_BF16 and the tuning bits 8-10 (cluster size), 12-14 (warp
+ *   pairs) and 16-23 (upper bound on the CTAs) of bas_gemm_ex.
+ *
+ * bas_list_create allocates a few hundred bytes per call of device memory and uploads the
+ * descriptors (synchronous); bas_list_run only launches, so it may be captured in a CUDA graph.
+ * Runs of one list must not overlap on the GPU.  bas_list_read_status is bas_read_device_status for
+ * the list's own status word.  A run that reported BAS_DEV_WAIT_EXPIRED leaves the list's counters
+ * inconsistent: call bas_list_reset (synchronous) before the next run.
+ * bas_list_set_wait changes the bound of the kernel's waits (default about one second) and, for
+ * tests of the expiry path only, names a call whose dependency is never seen complete (-1: none). */
+#define BAS_LIST_MAX_BLOCKS 1024
+#define BAS_LIST_MAX_CALLS 4096
+typedef struct bas_list_call {
+  const void* x_dev;
+  int64_t ldx;
+  const void* packed_dev;
+  const int32_t* ids_dev;
+  const int32_t* count_dev;
+  const uint8_t* bitmap_dev;
+  void* y_dev;
+  int64_t ldy;
+  int32_t k_host, batch, k, n;
+  int32_t depends_on;
+  int32_t reserved;
+} bas_list_call;
+typedef struct bas_list bas_list;
+BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_calls, int flags);
+BAS_API int bas_list_run(bas_list* l, void* stream);
+BAS_API int bas_list_read_status(bas_list* l, unsigned int* flags_out, void* stream);
+BAS_API int bas_list_reset(bas_list* l);
+BAS_API int bas_list_set_wait(bas_list* l, double wait_ms, int never_ready_call);
+/* ctas, cluster size, ring slots and warp pairs of the list's kernel (any pointer may be null). */
+BAS_API int bas_list_info(const bas_list* l, int* ctas, int* cluster, int* slots, int* pairs);
+BAS_API void bas_list_destroy(bas_list* l);
+
 /* ---- selection for callers that must not allocate -------------------------------------------
  * No counterpart in the reference.  Same result as bas_select_topk, but the caller passes no
  * workspace and the library allocates nothing: the kernel's scratch (one fp64 score per block and

@@ -18,6 +18,21 @@ SCORE_BF16 = 256         # BAS_SCORE_BF16
 SCORE_INPUTS_STABLE = 512   # BAS_SCORE_INPUTS_STABLE
 TP_HANDLE_BYTES = 64     # BAS_TP_HANDLE_BYTES
 
+LIST_MAX_BLOCKS = 1024  # BAS_LIST_MAX_BLOCKS
+LIST_MAX_CALLS = 4096   # BAS_LIST_MAX_CALLS
+DEV_BAD_BLOCK_ID = 1     # BAS_DEV_BAD_BLOCK_ID
+DEV_WAIT_EXPIRED = 2     # BAS_DEV_WAIT_EXPIRED
+
+
+class ListCall(C.Structure):
+    """``bas_list_call`` of include/bas.h."""
+
+    _fields_ = [("x_dev", C.c_void_p), ("ldx", C.c_int64), ("packed_dev", C.c_void_p), ("ids_dev", C.c_void_p),
+                ("count_dev", C.c_void_p), ("bitmap_dev", C.c_void_p), ("y_dev", C.c_void_p), ("ldy", C.c_int64),
+                ("k_host", C.c_int32), ("batch", C.c_int32), ("k", C.c_int32), ("n", C.c_int32),
+                ("depends_on", C.c_int32), ("reserved", C.c_int32)]
+
+
 _PKG = Path(__file__).resolve().parent.parent
 lib_path = _PKG / "libbas.so"
 
@@ -69,6 +84,13 @@ _SIGNATURES = {
     "bas_tp_disconnect": (_i, [_vp]),
     "bas_tp_destroy": (None, [_vp]),
     "bas_gemm_allreduce": (_i, [_vp, _vp, _i64, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i64, _vp, _sz, _i, _vp]),
+    "bas_list_create": (_i, [C.POINTER(_vp), _vp, _i, _i]),
+    "bas_list_run": (_i, [_vp, _vp]),
+    "bas_list_read_status": (_i, [_vp, C.POINTER(C.c_uint), _vp]),
+    "bas_list_reset": (_i, [_vp]),
+    "bas_list_set_wait": (_i, [_vp, C.c_double, _i]),
+    "bas_list_info": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
+    "bas_list_destroy": (None, [_vp]),
     "bas_linear_create": (_i, [C.POINTER(_vp), _vp, _i, _i, _i]),
     "bas_linear_forward_host": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "bas_linear_forward_host_ids": (_i, [_vp, _vp, _i, _vp, _i, _vp]),

@@ -191,6 +191,110 @@ def gemm(x2d: torch.Tensor, packed: torch.Tensor, out2d: torch.Tensor, *, ids: O
                 "bas_gemm")
 
 
+class GemmList:
+    """A fixed sequence of :func:`gemm` calls run as ONE persistent kernel (``bas_list_*``): the
+    decode step's chain of linears (the reference runs 224 patched forwards per token,
+    scripts/bench_roundrobin_e2e_decode.py:331-503) without a kernel boundary between them.
+
+    ``calls``: dicts with ``x`` [B, K], ``packed``, ``out`` [B, N], one of ``ids`` / ``bitmap``
+    (``count``, ``k_host`` as for :func:`gemm`) and ``depends_on``: index of the earlier call that
+    must be complete before ``x`` is read (normally the call that writes it), or -1.  Masks must be
+    complete before :meth:`run`; they may change between runs.  All tensors are kept alive by the
+    list.  :meth:`run` launches on the current stream, allocates nothing and can be captured in a
+    CUDA graph; runs of one list must not overlap."""
+
+    def __init__(self, calls, *, cluster: int = 0, pairs: int = 0, max_ctas: int = 0, min_units: int = 0):
+        import ctypes
+
+        calls = list(calls)
+        if not calls:
+            raise ValueError("a list needs at least one call")
+        arr = (_abi.ListCall * len(calls))()
+        self._keep = []
+        dtype = calls[0]["x"].dtype
+        self.device = calls[0]["x"].device
+        for i, c in enumerate(calls):
+            x, out, packed = c["x"], c["out"], c["packed"]
+            _require_cuda_fp16(x, "x")
+            _require_cuda_fp16(out, "out")
+            if x.dtype != dtype or out.dtype != dtype:
+                raise TypeError("all x and out of a list must have one dtype")
+            if x.dim() != 2 or out.dim() != 2 or x.stride(1) != 1 or out.stride(1) != 1 or x.shape[0] != out.shape[0]:
+                raise ValueError("x and out must be 2-D with unit inner stride and the same batch")
+            if x.shape[0] > MAX_BATCH:
+                raise ValueError(f"a call of a list takes at most {MAX_BATCH} rows")
+            ids, bitmap, count = c.get("ids"), c.get("bitmap"), c.get("count")
+            k_host = c.get("k_host")
+            if bitmap is None:
+                if ids is None:
+                    raise ValueError("either ids or bitmap is required")
+                if ids.dtype != torch.int32 or not ids.is_contiguous():
+                    raise TypeError("ids must be a contiguous int32 tensor")
+                k_host = int(ids.numel()) if k_host is None else int(k_host)
+            else:
+                if bitmap.dtype != torch.uint8 or not bitmap.is_contiguous():
+                    raise TypeError("bitmap must be a contiguous uint8 tensor")
+                k_host = int(k_host) if k_host is not None else 0
+            a = arr[i]
+            a.x_dev, a.ldx, a.packed_dev = x.data_ptr(), x.stride(0), packed.data_ptr()
+            a.ids_dev = ids.data_ptr() if ids is not None and bitmap is None and ids.numel() else None
+            a.count_dev = count.data_ptr() if count is not None else None
+            a.bitmap_dev = bitmap.data_ptr() if bitmap is not None else None
+            a.y_dev, a.ldy = out.data_ptr(), out.stride(0)
+            a.k_host, a.batch, a.k, a.n = k_host, x.shape[0], x.shape[1], out.shape[1]
+            a.depends_on = int(c.get("depends_on", -1))
+            self._keep.append((x, out, packed, ids, bitmap, count))
+        self.n_calls = len(calls)
+        self.handle = ctypes.c_void_p()
+        flags = (GEMM_BF16 if dtype == torch.bfloat16 else 0) | (int(cluster) << 8) | (int(pairs) << 12) | (int(max_ctas) << 16) | (int(min_units) << 24)
+        with torch.cuda.device(self.device):
+            check(lib.bas_list_create(ctypes.byref(self.handle), arr, len(calls), flags), "bas_list_create")
+
+    def run(self) -> None:
+        with torch.cuda.device(self.device):
+            check(lib.bas_list_run(self.handle, _stream_ptr()), "bas_list_run")
+
+    def read_status(self) -> int:
+        """Synchronously read and clear the list's device status word."""
+        import ctypes
+
+        flags = ctypes.c_uint(0)
+        with torch.cuda.device(self.device):
+            check(lib.bas_list_read_status(self.handle, ctypes.byref(flags), _stream_ptr()), "bas_list_read_status")
+        return int(flags.value)
+
+    def reset(self) -> None:
+        """After a run that reported an expired wait: synchronise and zero the completion counters."""
+        with torch.cuda.device(self.device):
+            check(lib.bas_list_reset(self.handle), "bas_list_reset")
+
+    def set_wait(self, wait_ms: float, never_ready_call: int = -1) -> None:
+        """Bound of the kernel's waits; ``never_ready_call`` (tests of the expiry path) names a call
+        whose dependency is never seen complete."""
+        check(lib.bas_list_set_wait(self.handle, float(wait_ms), int(never_ready_call)), "bas_list_set_wait")
+
+    def info(self) -> dict:
+        import ctypes
+
+        v = [ctypes.c_int(0) for _ in range(4)]
+        check(lib.bas_list_info(self.handle, *[ctypes.byref(t) for t in v]), "bas_list_info")
+        return dict(zip(("ctas", "cluster", "slots", "pairs"), (int(t.value) for t in v)))
+
+    def close(self) -> None:
+        if self.handle:
+            with torch.cuda.device(self.device):
+                torch.cuda.synchronize()
+                lib.bas_list_destroy(self.handle)
+            self.handle = None
+            self._keep = []
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class ExchangeGroup:
     """This rank's exchange area for row-parallel contractions summed inside the kernel, connected
     to the areas of the other ranks of ``group`` (one process per GPU, all on one box).  The handles

@@ -203,6 +203,32 @@ class DecodeLinearStack:
             self.exchange.close()
             self.exchange = None
 
+    # what each projection's input is the output of, in the model (attention itself is not part of
+    # the stack: o reads what follows v)
+    MODEL_DEPENDENCY = {"q_proj": "down_proj", "k_proj": "down_proj", "v_proj": "down_proj", "qkv_proj": "down_proj",
+                        "o_proj": ("v_proj", "qkv_proj"), "gate_proj": "o_proj", "up_proj": "o_proj",
+                        "gate_up_proj": "o_proj", "down_proj": ("up_proj", "gate_up_proj")}
+
+    def make_list(self, dependencies: bool = True, **tuning):
+        """The whole step as one persistent launch (``ops.GemmList``): single GPU only.  With
+        ``dependencies`` every call waits for the call whose output its input is in the model; without,
+        no call waits for any other (a probe of the kernel's streaming rate)."""
+        from . import ops
+
+        if self.world != 1:
+            raise ValueError("the one-launch step needs the sums over ranks inside it: single GPU only")
+        last = {}
+        calls = []
+        for lin, x, bitmap, out, n_keep in self.items:
+            dep = -1
+            if dependencies:
+                want = self.MODEL_DEPENDENCY[lin.spec.name]
+                for name in (want if isinstance(want, tuple) else (want,)):
+                    dep = max(dep, last.get(name, -1))
+            last[lin.spec.name] = len(calls)
+            calls.append({"x": x, "packed": lin.packed, "out": out, "bitmap": bitmap, "k_host": n_keep, "depends_on": dep})
+        return ops.GemmList(calls, **tuning)
+
     def step(self) -> None:
         import torch.distributed as dist
 

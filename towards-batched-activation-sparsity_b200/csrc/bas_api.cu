@@ -27,12 +27,14 @@ bool pdl_enabled() {
   return on;
 }
 
-namespace {
-
-int cuda_fail(cudaError_t e) {
+int record_cuda_error(cudaError_t e) {
   g_last_cuda_error = (int)e;
   return BAS_ERR_CUDA;
 }
+
+namespace {
+
+int cuda_fail(cudaError_t e) { return record_cuda_error(e); }
 
 struct DeviceInfo {
   int sm_count = 0;

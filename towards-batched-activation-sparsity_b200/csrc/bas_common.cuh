@@ -87,6 +87,65 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
+// The same with the bound given by the caller (kernels whose wait limit is a launch parameter).
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long limit) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag != 0 || clock64() - t0 > limit) return false;
+  }
+  return true;
+}
+// Wait on a barrier of this CTA on which threads of OTHER CTAs of the cluster arrive (release at
+// cluster scope): the acquire makes what they wrote into this CTA's shared memory visible.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster_for(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                      long long limit) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if (*abort_flag != 0 || clock64() - t0 > limit) return false;
+  }
+  return true;
+}
+// Arrive on a barrier that lives in the shared memory of a CTA of this cluster (address from
+// dsmem_addr); releases, at cluster scope, what this thread wrote (and observed) before.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+// Orders this thread's generic-proxy accesses (plain loads and stores, also those it has observed
+// through an acquire) against its asynchronous-proxy accesses (bulk / tensor copies), all state spaces.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Completion counters in global memory that CTAs of one grid hand work over through.
+__device__ __forceinline__ unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add_u32(unsigned int* p, unsigned int v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Shared-memory word one warp publishes to the other warps of its CTA.
+__device__ __forceinline__ void st_release_cta_shared_u32(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_cta_shared_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+
 // ---------------------------------------------------------------------------------------------
 // bulk asynchronous copies (TMA unit), completion counted in bytes on an mbarrier
 // ---------------------------------------------------------------------------------------------
@@ -264,7 +323,8 @@ __device__ __forceinline__ void warp_load_id_batch(const int32_t* __restrict__ i
 __device__ __forceinline__ int warp_stage_ids(const int32_t* __restrict__ ids, const int32_t* __restrict__ count_dev,
                                               int k_host, const uint8_t* __restrict__ bitmap, int nb,
                                               uint16_t* __restrict__ s_ids, unsigned int* __restrict__ status,
-                                              int lane, bool have_first, const int (&first)[8]) {
+                                              int lane, bool have_first, const int (&first)[8],
+                                              bool report_bad = (blockIdx.x == 0)) {
   int n_src = nb;
   if (bitmap == nullptr) {
     n_src = k_host;
@@ -302,7 +362,7 @@ __device__ __forceinline__ int warp_stage_ids(const int32_t* __restrict__ ids, c
     }
   }
   bad = __any_sync(0xffffffffu, bad);
-  if (bad && lane == 0 && blockIdx.x == 0) atomicOr(status, BAS_DEV_BAD_BLOCK_ID);
+  if (bad && lane == 0 && report_bad) atomicOr(status, BAS_DEV_BAD_BLOCK_ID);
   __syncwarp();
   return off;
 }

@@ -137,5 +137,9 @@ struct SelectParams {
 cudaError_t launch_select(const SelectParams& p, int sm_count, cudaStream_t stream);
 
 void count_launch(int n = 1);
+// Remembers a failed CUDA call for bas_last_cuda_error() on this thread; returns BAS_ERR_CUDA.
+int record_cuda_error(cudaError_t e);
+// cuTensorMapEncodeTiled of the loaded driver as an untyped pointer (null if unavailable).
+void* tensor_map_encoder();
 
 }  // namespace bas

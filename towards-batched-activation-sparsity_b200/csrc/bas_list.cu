@@ -1,0 +1,961 @@
+// A whole list of masked contractions as ONE persistent launch (bas_list_*).
+//
+// A decode step is a chain of small linears (224 for Llama-2-7B; the reference patches every one of
+// them, scripts/bench_roundrobin_e2e_decode.py:331-503, and its benchmark sums them per step,
+// scripts/bench_perstep_actual_kernel_speedup.py:268-293).  Launched one by one, each pays set-up,
+// first-byte latency, accumulator read-out and the hand-over to the next kernel, during which its SMs
+// do not stream.  Here the CTAs stay resident and walk the list:
+//
+//   * the ring of weight tiles runs across call boundaries: a call's weights never depend on the
+//     call before it, so they are fetched while that call is still being finished;
+//   * only a call's activation tiles wait - on a completion counter in global memory that the
+//     CTAs finishing the call it depends on add to (release) and the reader polls (acquire, bounded);
+//   * accumulators are double-buffered in tensor memory, so the MMAs of the next unit run while
+//     the previous one is read out, combined across the cluster and stored.
+//
+// Work split: a cluster of C CTAs owns, for every call, one contiguous range of output columns
+// (narrow outputs use fewer clusters, rotating, so that consecutive small calls land on different
+// SMs); the range is walked in column tiles of at most 128; the cluster's CTAs deal the call's active
+// blocks out round-robin and add their fp32 partials through distributed shared memory in rank
+// order (mbarriers in the owner's shared memory, no cluster-wide barrier inside the loop).
+//
+// Roles per CTA: warps 0..3 issue copies (each compacts the call's id list for itself; warp 0 also
+// publishes the call's tile counts to the other roles), warps 4..7 issue MMAs (one thread each, own
+// accumulators), warps 8..15 read out, combine, store and signal completion.  Every wait is bounded
+// by a launch parameter and reports through the status word.
+#include "bas_kernels.cuh"
+
+#include <cudaTypedefs.h>
+
+#include <cstddef>
+#include <cstring>
+#include <new>
+#include <type_traits>
+#include <vector>
+
+namespace bas {
+
+namespace {
+
+constexpr int kLProducers = 4;
+constexpr int kLIssuers = 4;
+constexpr int kLEpiWarp0 = kLProducers + kLIssuers;
+constexpr int kLEpiThreads = 256;
+constexpr int kLThreads = 32 * kLEpiWarp0 + kLEpiThreads;
+constexpr int kLMmaSpanBytes = 128 * kRowBytes;
+
+// Device-side description of one call, written once by bas_list_create.
+struct alignas(128) ListCallDev {
+  CUtensorMap xmap;            // X[batch, K]: box {64 channels, BPAD rows}, 128-byte swizzle
+  const uint8_t* packed;
+  const int32_t* ids;
+  const int32_t* count_dev;
+  const uint8_t* bitmap;
+  __half* y;
+  long long ldy;
+  int k_host, batch, n, nb;
+  int units;                   // padded output columns / 8
+  int ranges;                  // clusters that take part in this call
+  int range_off;               // the first of them (the others follow, modulo the cluster count)
+  int dep;                     // call whose completion X waits for, or -1
+  unsigned int dep_contrib;    // CTAs that report the completion of call `dep`
+  int pad[5];
+};
+static_assert(sizeof(ListCallDev) == 256, "call descriptor layout");
+
+struct ListHeaderDev {
+  unsigned int epoch;      // completed runs of the list: counters below are never reset, targets grow
+  unsigned int arrived;    // CTAs of the current run that have finished
+  unsigned int status;     // BAS_DEV_* bits
+  unsigned int pad;
+};
+
+struct ListParams {
+  const ListCallDev* calls;
+  int n_calls;
+  ListHeaderDev* hdr;
+  unsigned int* done;        // [n_calls] completion counters
+  int cluster;               // CTAs per cluster (1, 2, 4)
+  int n_clusters;
+  int stages;                // ring slots, a multiple of `pairs`
+  int pairs;                 // copy/MMA warp pairs in use
+  int wslot;                 // bytes reserved per slot for a weight tile (multiple of 1024)
+  int nb_max;                // largest K / 64 of the list
+  int bf16;
+  int stall_call;            // tests of the expiry path: this call's dependency is never seen complete (-1: off)
+  long long wait_cycles;     // bound of every wait
+};
+
+struct ListSmemHeader {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint64_t red_full[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  unsigned int calls_staged;   // records [0, calls_staged) are valid
+  unsigned int epi_arrived;    // epilogue warps that have finished their part of a call (8 per call)
+};
+
+// Per-call record published by copy warp 0: bit 31 = this CTA takes part, bits 16..23 = column
+// tiles of its range, bits 0..15 = active blocks of this CTA.
+__device__ __forceinline__ unsigned int make_record(bool part, int n_sub, int k_mine) {
+  return (part ? 0x80000000u : 0u) | ((unsigned int)n_sub << 16) | (unsigned int)k_mine;
+}
+
+// This cluster's share of a call.
+struct Share {
+  bool part;
+  int n0, width, n_sub, tw;   // first column, columns, column tiles, columns per tile (multiple of 8)
+};
+__device__ __forceinline__ Share call_share(int units, int ranges, int range_off, int cid, int n_clusters) {
+  Share s;
+  int range = cid - range_off;
+  if (range < 0) range += n_clusters;
+  s.part = range < ranges;
+  s.n0 = s.width = s.n_sub = 0;
+  s.tw = 8;
+  if (s.part) {
+    s.n0 = col_begin(range, units, ranges);
+    s.width = col_begin(range + 1, units, ranges) - s.n0;
+    s.n_sub = (s.width + kTileN - 1) / kTileN;
+    if (s.n_sub > 0) s.tw = ((s.width + s.n_sub - 1) / s.n_sub + 7) & ~7;
+  }
+  return s;
+}
+
+// Read-only load of a pointer-valued field of a call descriptor.
+template <typename T>
+__device__ __forceinline__ T* ldg_ptr(T* const* field) {
+  return (T*)(uintptr_t)__ldg((const unsigned long long*)field);
+}
+
+// The fields of a call descriptor that the copy warps need, fetched as four 16-byte loads that stay
+// where they are written (volatile), so that a call's descriptor can be requested two calls ahead
+// and its id list one call ahead: at a call boundary everything is already in registers.
+struct CallRegs {
+  uint4 a, b, c, d;   // {packed, ids}, {count_dev, bitmap}, {k_host, batch, n, nb}, {units, ranges, range_off, dep}
+};
+__device__ __forceinline__ uint4 ld_nc_v4(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+  return v;
+}
+__device__ __forceinline__ CallRegs load_call_regs(const ListCallDev* cd) {
+  const uint8_t* base = (const uint8_t*)cd;
+  CallRegs r;
+  r.a = ld_nc_v4(base + offsetof(ListCallDev, packed));
+  r.b = ld_nc_v4(base + offsetof(ListCallDev, count_dev));
+  r.c = ld_nc_v4(base + offsetof(ListCallDev, k_host));
+  r.d = ld_nc_v4(base + offsetof(ListCallDev, units));
+  return r;
+}
+__device__ __forceinline__ const void* regs_ptr(unsigned int lo, unsigned int hi) {
+  return (const void*)(uintptr_t)(((unsigned long long)hi << 32) | (unsigned long long)lo);
+}
+
+__device__ __forceinline__ int red_swizzle_l(int nbi, int r) {
+  return nbi == 32 ? (r & 7) : nbi == 16 ? ((r >> 1) & 3) : nbi == 8 ? ((r >> 2) & 1) : 0;
+}
+
+template <int BPAD>
+__global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_constant__ ListParams p) {
+  constexpr int kXTileBytes = BPAD * 128;
+  constexpr int kAccCols = 2 * kLIssuers * BPAD;                      // two buffers of one accumulator per issuer
+  constexpr int kTmemCols = kAccCols <= 128 ? 128 : kAccCols <= 256 ? 256 : 512;
+  const uint32_t kIdesc = umma_idesc_f16(128, BPAD) | (p.bf16 ? ((1u << 7) | (1u << 10)) : 0u);
+  const bool bf16 = p.bf16 != 0;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sp = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  ListSmemHeader* hdr = (ListSmemHeader*)sp;
+  sp += (sizeof(ListSmemHeader) + 127) / 128 * 128;
+  unsigned int* s_rec = (unsigned int*)sp;                 // [n_calls]
+  sp += ((size_t)p.n_calls * 4 + 127) / 128 * 128;
+  uint16_t* s_ids_all = (uint16_t*)sp;                     // [kLProducers][nb_max]
+  const size_t ids_stride = ((size_t)p.nb_max * 2 + 127) / 128 * 128;
+  sp += ids_stride * kLProducers;
+  uint32_t* s_def_all = (uint32_t*)sp;                     // [kLProducers][kMaxStages] deferred activation copies
+  sp += sizeof(uint32_t) * kMaxStages * kLProducers;
+  float* s_red = (float*)sp;                               // [2][source rank][128][row slots]
+  const int C = p.cluster;
+  if (C > 1) sp += 2 * (size_t)BPAD * kTileN * sizeof(float);
+  uint8_t* s_stage = (uint8_t*)(((uintptr_t)sp + 1023) & ~(uintptr_t)1023);
+  const int S = p.stages, P = p.pairs;
+  const int tile_bytes = p.wslot + kXTileBytes;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile int* abort_flag = &hdr->abort_flag;
+  const long long limit = p.wait_cycles;
+
+  if (tid < S) {
+    mbar_init(&hdr->full[tid], 1);
+    mbar_init(&hdr->empty[tid], 1);
+    fence_barrier_init();
+  } else if (tid == 64) {
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&hdr->acc_full[b], P);
+      mbar_init(&hdr->acc_empty[b], kLEpiThreads / 32);
+      mbar_init(&hdr->red_full[b], C * (kLEpiThreads / 32));
+    }
+    hdr->abort_flag = 0;
+    hdr->calls_staged = 0u;
+    hdr->epi_arrived = 0u;
+    fence_barrier_init();
+  }
+  if (warp == kLEpiWarp0) {
+    tmem_alloc(&hdr->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  // peers arrive on this CTA's barriers: they must be initialised in every CTA before anyone starts
+  if (C > 1) cluster_sync_all();
+  const uint32_t tmem_base = hdr->tmem_base;
+
+  // Everything read below (descriptors are fixed, but X, the id lists, the counters and the epoch)
+  // may be written by the kernel before this one in the stream.
+  pdl_wait();
+  const unsigned int epoch = __ldcg(&p.hdr->epoch);
+
+  const int rank = (C > 1) ? (int)cluster_ctarank() : 0;
+  const int cid = blockIdx.x / C;
+  int armed_cnt = 0;       // copy warps: tiles armed so far (lane 0)
+
+  if (warp < kLProducers) {
+    // ================================ copy warps ================================
+    if (warp < P) {
+      uint16_t* s_ids = (uint16_t*)((uint8_t*)s_ids_all + ids_stride * warp);
+      uint32_t* s_def = s_def_all + kMaxStages * warp;   // entries {slot << 24 | call << 12 | block}: at most S / P
+      const int per_lap = S / P;
+      const uint64_t pol_x = l2_policy_evict_last();
+      int slot = warp, lap = 0;        // next slot of this pair and how often it has been used
+      int t0mod = 0;                   // tiles of all earlier units, modulo P
+      int def_head = 0, ndef = 0;      // deferred activation copies: oldest entry (ring index into s_def) and how many
+      int dep_ok = -1;                 // the dependency last seen complete
+      bool ok = true;
+
+      // Issue the activation copy of the oldest deferred tile; `block`: wait for its call's dependency.
+      // `force`: issue it whatever the dependency says (giving up: nobody consumes the tile, but its barrier
+      // must complete before the CTA may leave).
+      auto flush_one = [&](bool block, bool force) -> bool {   // lane 0 only; false = not ready (or gave up: ok cleared)
+        const uint32_t e = s_def[def_head % kMaxStages];
+        const int dslot = (int)(e >> 24), dcall = (int)((e >> 12) & 0xfffu), dj = (int)(e & 0xfffu);
+        const ListCallDev* cd = p.calls + dcall;
+        const int dep = __ldg(&cd->dep);
+        if (!force && dep >= 0 && dep != dep_ok) {
+          const unsigned int target = (epoch + 1u) * __ldg(&cd->dep_contrib);
+          const bool stalled = dcall == p.stall_call;
+          bool ready = !stalled && (int)(ld_acquire_gpu_u32(p.done + dep) - target) >= 0;
+          if (!ready && block) {
+            const long long t_start = clock64();
+            while (true) {
+              ready = !stalled && (int)(ld_acquire_gpu_u32(p.done + dep) - target) >= 0;
+              if (ready) break;
+              if (*abort_flag != 0 || clock64() - t_start > limit) {
+                ok = false;
+                return false;
+              }
+              __nanosleep(40);
+            }
+          }
+          if (!ready) return false;
+          fence_proxy_async_all();   // the tensor copy below reads what other CTAs stored with plain stores
+          dep_ok = dep;
+        }
+        tma_load_2d_hint(s_stage + (size_t)dslot * tile_bytes + p.wslot, &cd->xmap, dj * kBlockK, 0, &hdr->full[dslot], pol_x);
+        ++def_head;
+        --ndef;
+        return true;
+      };
+
+      CallRegs cur = load_call_regs(p.calls);
+      CallRegs nxt = load_call_regs(p.calls + (p.n_calls > 1 ? 1 : 0));
+      int raw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      bool have_raw = false;
+      // id batch of a call whose descriptor is in registers (lists with a device-side count are read at the boundary)
+      auto prefetch_ids = [&](const CallRegs& r, int (&dst)[8]) -> bool {
+        if (regs_ptr(r.b.x, r.b.y) != nullptr) return false;
+        const uint8_t* bm = (const uint8_t*)regs_ptr(r.b.z, r.b.w);
+        warp_load_id_batch((const int32_t*)regs_ptr(r.a.z, r.a.w), bm, bm != nullptr ? (int)r.c.w : (int)r.c.x, 0, lane, dst);
+        return true;
+      };
+      have_raw = prefetch_ids(cur, raw);
+
+      for (int c = 0; c < p.n_calls && ok; ++c) {
+        const ListCallDev* cd = p.calls + c;
+        const CallRegs nn = load_call_regs(p.calls + (c + 2 < p.n_calls ? c + 2 : c));   // in flight during this call
+        const int units = (int)cur.d.x, ranges = (int)cur.d.y, range_off = (int)cur.d.z, dep = (int)cur.d.w;
+        const Share sh = call_share(units, ranges, range_off, cid, p.n_clusters);
+        int k_mine = 0;
+        if (sh.part) {
+          const int k_act = warp_stage_ids((const int32_t*)regs_ptr(cur.a.z, cur.a.w), (const int32_t*)regs_ptr(cur.b.x, cur.b.y),
+                                           (int)cur.c.x, (const uint8_t*)regs_ptr(cur.b.z, cur.b.w), (int)cur.c.w, s_ids,
+                                           &p.hdr->status, lane, have_raw, raw, warp == 0 && rank == 0 && sh.n0 == 0);
+          k_mine = (k_act > rank) ? (k_act - rank + C - 1) / C : 0;
+        }
+        if (warp == 0 && lane == 0) {
+          s_rec[c] = make_record(sh.part, sh.n_sub, k_mine);
+          st_release_cta_shared_u32(&hdr->calls_staged, (unsigned int)(c + 1));
+        }
+        // the next call's id list: requested now, used at the next boundary
+        int raw_n[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const bool have_n = (c + 1 < p.n_calls) ? prefetch_ids(nxt, raw_n) : false;
+        if (lane == 0 && sh.part && k_mine > 0) {
+          const uint8_t* packed = (const uint8_t*)regs_ptr(cur.a.x, cur.a.y);
+          const int npad = units * 8;
+          for (int sub = 0; sub < sh.n_sub && ok; ++sub) {
+            const int c0 = sh.n0 + sub * sh.tw;
+            const int wbytes = min(sh.tw, sh.width - sub * sh.tw) * kRowBytes;
+            int i = warp - t0mod;
+            if (i < 0) i += P;
+            for (; i < k_mine; i += P) {
+              // the slot about to be reused may still hold a tile whose activations were never
+              // requested: that one has to go out first, whatever it waits for
+              while (ndef >= per_lap && ok) (void)flush_one(true, false);
+              if (!ok) break;
+              if (lap > 0 && !mbar_wait_for(&hdr->empty[slot], (lap - 1) & 1, abort_flag, limit)) {
+                ok = false;
+                break;
+              }
+              const int j = s_ids[rank + i * C];
+              mbar_arrive_expect_tx(&hdr->full[slot], wbytes + kXTileBytes);
+              uint8_t* st = s_stage + (size_t)slot * tile_bytes;
+              bulk_copy_g2s(st, packed + ((size_t)j * npad + c0) * kRowBytes, wbytes, &hdr->full[slot]);
+              ++armed_cnt;
+              if (ndef == 0 && (dep < 0 || dep == dep_ok)) {
+                tma_load_2d_hint(st + p.wslot, &cd->xmap, j * kBlockK, 0, &hdr->full[slot], pol_x);
+              } else {
+                s_def[(def_head + ndef) % kMaxStages] = ((uint32_t)slot << 24) | ((uint32_t)c << 12) | (uint32_t)j;
+                ++ndef;
+                while (ndef > 0 && flush_one(false, false)) {
+                }
+              }
+              slot += P;
+              if (slot >= S) {
+                slot -= S;
+                ++lap;
+              }
+            }
+            t0mod += k_mine % P;
+            if (t0mod >= P) t0mod -= P;
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        cur = nxt;
+        nxt = nn;
+        have_raw = have_n;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) raw[e] = raw_n[e];
+      }
+      if (lane == 0) {
+        while (ndef > 0 && ok) (void)flush_one(true, false);
+        if (!ok) {
+          atomicOr(&p.hdr->status, BAS_DEV_WAIT_EXPIRED);
+          hdr->abort_flag = 1;
+          while (ndef > 0) (void)flush_one(false, true);
+        }
+      }
+      __syncwarp();
+    }
+    if (warp == 0) pdl_launch_dependents();
+  } else if (warp < kLEpiWarp0) {
+    // ================================ MMA issuers ================================
+    const int w = warp - kLProducers;
+    if (lane == 0 && w < P) {
+      bool ok = true;
+      int slot = w, fph = 0, t0mod = 0, u = 0;
+      for (int c = 0; c < p.n_calls && ok; ++c) {
+        // the call's record: published by copy warp 0 before it issues the call's first tile
+        if (ld_acquire_cta_shared_u32(&hdr->calls_staged) <= (unsigned int)c) {
+          const long long t_start = clock64();
+          while (ld_acquire_cta_shared_u32(&hdr->calls_staged) <= (unsigned int)c) {
+            if (*abort_flag != 0 || clock64() - t_start > limit) {
+              ok = false;
+              break;
+            }
+          }
+          if (!ok) break;
+        }
+        const unsigned int rec = s_rec[c];
+        if ((rec & 0x80000000u) == 0u) continue;
+        const int n_sub = (int)((rec >> 16) & 0xffu), k_mine = (int)(rec & 0xffffu);
+        for (int sub = 0; sub < n_sub && ok; ++sub, ++u) {
+          const int b = u & 1;
+          // the accumulator buffer is free once the epilogue has read out unit u - 2; passing this
+          // wait also means that every issuer has signed off that unit
+          if (u >= 2 && !mbar_wait_for(&hdr->acc_empty[b], ((u >> 1) - 1) & 1, abort_flag, limit)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t d = tmem_base + (uint32_t)((b * kLIssuers + w) * BPAD);
+          bool fresh = true;
+          int i = w - t0mod;
+          if (i < 0) i += P;
+          for (; i < k_mine; i += P) {
+            if (!mbar_wait_for(&hdr->full[slot], fph, abort_flag, limit)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t st = smem_u32(s_stage + (size_t)slot * tile_bytes);
+            const uint64_t adesc = umma_desc_kmajor_sw128(st);
+            const uint64_t bdesc = umma_desc_kmajor_sw128(st + p.wslot);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc, (fresh && ks == 0) ? 0u : 1u);
+            fresh = false;
+            umma_commit(&hdr->empty[slot]);   // the slot is free once these MMAs have read it
+            slot += P;
+            if (slot >= S) {
+              slot -= S;
+              fph ^= 1;
+            }
+          }
+          if (!ok) break;
+          if (!fresh) umma_commit(&hdr->acc_full[b]);
+          else mbar_arrive(&hdr->acc_full[b]);
+          t0mod += k_mine % P;
+          if (t0mod >= P) t0mod -= P;
+        }
+      }
+      if (!ok) {
+        atomicOr(&p.hdr->status, BAS_DEV_WAIT_EXPIRED);
+        hdr->abort_flag = 1;
+      }
+    }
+  } else {
+    // ================================ epilogue ================================
+    const int q = warp & 3;
+    const int r = q * 32 + lane;             // row of the accumulator = column within the tile
+    const int et = tid - 32 * kLEpiWarp0;
+    const int eset = et >> 7;
+    constexpr int kChunks = BPAD / 16;
+    constexpr int kChunks0 = (kChunks + 1) / 2;
+    bool ok = true;
+    int t0mod = 0, u = 0;
+    for (int c = 0; c < p.n_calls && ok; ++c) {
+      {
+        bool ready = ld_acquire_cta_shared_u32(&hdr->calls_staged) > (unsigned int)c;
+        if (!__all_sync(0xffffffffu, ready)) {
+          const long long t_start = clock64();
+          while (true) {
+            ready = ld_acquire_cta_shared_u32(&hdr->calls_staged) > (unsigned int)c;
+            const bool give_up = *abort_flag != 0 || clock64() - t_start > limit;
+            if (__all_sync(0xffffffffu, ready)) break;
+            if (__any_sync(0xffffffffu, give_up)) {
+              ok = false;
+              break;
+            }
+          }
+          if (!ok) break;
+        }
+      }
+      const unsigned int rec = s_rec[c];
+      if ((rec & 0x80000000u) == 0u) continue;
+      const int k_mine = (int)(rec & 0xffffu);
+      const ListCallDev* cd = p.calls + c;
+      const Share sh = call_share(__ldg(&cd->units), __ldg(&cd->ranges), __ldg(&cd->range_off), cid, p.n_clusters);
+      __half* y = ldg_ptr(&cd->y);
+      const long long ldy = __ldg(&cd->ldy);
+      const int batch = __ldg(&cd->batch), n = __ldg(&cd->n);
+
+      for (int sub = 0; sub < sh.n_sub && ok; ++sub, ++u) {
+        const int b = u & 1;
+        const int c0 = sh.n0 + sub * sh.tw;
+        const int wsub = min(sh.tw, sh.width - sub * sh.tw);
+        if (!__all_sync(0xffffffffu, mbar_wait_for(&hdr->acc_full[b], (u >> 1) & 1, abort_flag, limit))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        float* red_buf = s_red + (size_t)b * BPAD * kTileN;
+
+        auto emit = [&](auto ch0_c, auto nch_c) {
+          constexpr int CH0 = decltype(ch0_c)::value, NCH = decltype(nch_c)::value;
+          constexpr int NV = NCH * 16;
+          constexpr int IB = (BPAD == 16) ? 4 : (NCH == 1) ? 2 : 1;
+          float v[NV];
+#pragma unroll
+          for (int e = 0; e < NV; ++e) v[e] = 0.f;
+          if (k_mine > 0) {
+#pragma unroll
+            for (int w0 = 0; w0 < kLIssuers; w0 += IB) {
+              if (w0 < P) {
+                uint32_t regs[IB][NCH][16];
+#pragma unroll
+                for (int wi = 0; wi < IB; ++wi)
+                  if (w0 + wi < P) {
+#pragma unroll
+                    for (int cc = 0; cc < NCH; ++cc)
+                      tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) +
+                                             (uint32_t)((b * kLIssuers + w0 + wi) * BPAD + (CH0 + cc) * 16),
+                                         regs[wi][cc]);
+                  }
+                tmem_ld_wait();
+#pragma unroll
+                for (int wi = 0; wi < IB; ++wi) {
+                  const int w = w0 + wi;
+                  int first = w - t0mod;      // this issuer's first tile of the unit
+                  if (first < 0) first += P;
+                  if (w < P && first < k_mine) {   // issuer order: the sum never depends on timing
+#pragma unroll
+                    for (int cc = 0; cc < NCH; ++cc)
+#pragma unroll
+                      for (int e = 0; e < 16; ++e) v[cc * 16 + e] += __uint_as_float(regs[wi][cc][e]);
+                  }
+                }
+              }
+            }
+          }
+          if (C == 1) {
+            const int col = c0 + r;
+            if (r < wsub && col < n) {
+#pragma unroll
+              for (int e = 0; e < NV; ++e)
+                if (16 * CH0 + e < batch) store_out16(y + (size_t)(16 * CH0 + e) * ldy + col, v[e], bf16);
+            }
+          } else {
+            // batch row b is finished by rank b % C: push this CTA's partial of each row into the
+            // owner's receive buffer [source rank][column][row slot], four row slots per 16-byte store
+            const int nbi = BPAD / C;
+            const int sw = red_swizzle_l(nbi, r);
+            float* mine_l = red_buf + (rank * kTileN + r) * nbi;
+            const uint32_t mine = smem_u32(mine_l);
+            uint32_t owner[4];
+#pragma unroll
+            for (int o = 0; o < 4; ++o) owner[o] = dsmem_addr(mine, (uint32_t)(o & (C - 1)));
+            if (C == 4) {
+#pragma unroll
+              for (int o = 0; o < 4; ++o)
+#pragma unroll
+                for (int c4 = 0; c4 < NCH; ++c4) {   // slots 4*b4 .. 4*b4+3 <-> rows 16*b4 + o + {0,4,8,12}
+                  const int b4 = CH0 + c4;
+                  if (16 * b4 + o < batch) {
+                    const float4 val = make_float4(v[16 * c4 + o], v[16 * c4 + o + 4], v[16 * c4 + o + 8], v[16 * c4 + o + 12]);
+                    if (o == rank) *(float4*)(mine_l + 4 * (b4 ^ sw)) = val;
+                    else dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * (b4 ^ sw)), val.x, val.y, val.z, val.w);
+                  }
+                }
+            } else {
+#pragma unroll
+              for (int o = 0; o < 2; ++o)
+#pragma unroll
+                for (int c8 = 0; c8 < 2 * NCH; ++c8) {   // slots 4*b8 .. 4*b8+3 <-> rows 8*b8 + o + {0,2,4,6}
+                  const int b8 = 2 * CH0 + c8;
+                  if (8 * b8 + o < batch) {
+                    const float4 val = make_float4(v[8 * c8 + o], v[8 * c8 + o + 2], v[8 * c8 + o + 4], v[8 * c8 + o + 6]);
+                    if (o == rank) *(float4*)(mine_l + 4 * (b8 ^ sw)) = val;
+                    else dsmem_st_v4_f32(owner[o] + (uint32_t)(16 * (b8 ^ sw)), val.x, val.y, val.z, val.w);
+                  }
+                }
+            }
+          }
+        };
+        using std::integral_constant;
+        if constexpr (kChunks == 1) {
+          if (eset == 0) emit(integral_constant<int, 0>{}, integral_constant<int, 1>{});
+        } else {
+          if (eset == 0) emit(integral_constant<int, 0>{}, integral_constant<int, kChunks0>{});
+          else emit(integral_constant<int, kChunks0>{}, integral_constant<int, kChunks - kChunks0>{});
+        }
+        // the accumulators have been read: the issuers may overwrite this buffer (unit u + 2)
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&hdr->acc_empty[b]);
+
+        if (C > 1) {
+          // tell every owner that this warp's pushes are on their way (release at cluster scope, after
+          // the warp's stores), then wait until all warps of all CTAs of the cluster have told this one
+          if (lane == 0) {
+            fence_acq_rel_cluster();
+            const uint32_t bar = smem_u32(&hdr->red_full[b]);
+            for (int o = 0; o < C; ++o) mbar_arrive_remote(dsmem_addr(bar, (uint32_t)o));
+          }
+          if (!__all_sync(0xffffffffu, mbar_wait_cluster_for(&hdr->red_full[b], (u >> 1) & 1, abort_flag, limit))) {
+            ok = false;
+            break;
+          }
+          const int rr = et & 127;
+          const int nbi = BPAD / C;
+          const int sw = red_swizzle_l(nbi, rr);
+          const int col = c0 + rr;
+          if (rr < wsub && col < n) {
+            for (int qd = eset; 4 * qd * C + rank < batch; qd += 2) {
+              float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int s = 0; s < 4; ++s)
+                if (s < C) {   // rank order
+                  const float4 t = *(const float4*)(red_buf + (s * kTileN + rr) * nbi + 4 * (qd ^ sw));
+                  sum.x += t.x;
+                  sum.y += t.y;
+                  sum.z += t.z;
+                  sum.w += t.w;
+                }
+              const int row0 = 4 * qd * C + rank;
+              const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (row0 + e * C < batch) store_out16(y + (size_t)(row0 + e * C) * ldy + col, vals[e], bf16);
+            }
+          }
+        }
+        t0mod += k_mine % P;
+        if (t0mod >= P) t0mod -= P;
+      }
+      if (!ok) break;
+      // This CTA's part of call c is in global memory: report it.  Readers fetch it with tensor copies.
+      // (The last of the eight warps to get here does it; nothing blocks, so a warp that gave up
+      // cannot strand the others.)
+      // One fence per warp: it orders the stores of the warp's other lanes too (they precede it
+      // through the warp barrier).
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence();
+        if ((atomicAdd(&hdr->epi_arrived, 1u) & 7u) == 7u) {
+          __threadfence();
+          fence_proxy_async_all();
+          red_release_gpu_add_u32(p.done + c, 1u);
+        }
+      }
+    }
+    if (!ok) {
+      atomicOr(&p.hdr->status, BAS_DEV_WAIT_EXPIRED);
+      hdr->abort_flag = 1;
+    }
+  }
+
+  // ---- common tail ----
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (hdr->abort_flag != 0 && warp < P && lane == 0) {
+    // Gave up somewhere: do not leave while copies may still be landing in this CTA's memory (every
+    // armed tile has had both its copies issued by now): wait, bounded, for this warp's last lap of slots.
+    int zero = 0;
+    const int per_lap = S / P;
+    int k = armed_cnt - 1;
+    for (int i = 0; i < per_lap && k >= 0; ++i, --k) {
+      const int g = warp + k * P;
+      (void)mbar_wait_for(&hdr->full[g % S], (g / S) & 1, &zero, 2000000);
+    }
+  }
+  __syncthreads();
+  if (C > 1) cluster_sync_all();   // no CTA leaves while a peer may still push into it or arrive on its barriers
+  if (warp == kLEpiWarp0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (tid == 0) {
+    // the last CTA of the run advances the epoch: the counters keep growing, the targets with them
+    __threadfence();
+    if (atomicAdd(&p.hdr->arrived, 1u) == gridDim.x - 1) {
+      p.hdr->arrived = 0u;
+      p.hdr->epoch = epoch + 1u;
+      __threadfence();
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kLSmemBudget = 224 * 1024;
+
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Shared memory in front of the ring, as the kernel carves it up.
+size_t list_fixed_smem(int n_calls, int nb_max, int cluster, int bpad) {
+  return 128 + round_up(sizeof(ListSmemHeader), 128) + round_up((size_t)n_calls * 4, 128) +
+         round_up((size_t)nb_max * 2, 128) * kLProducers + sizeof(uint32_t) * kMaxStages * kLProducers +
+         (cluster > 1 ? 2 * (size_t)bpad * kTileN * sizeof(float) : 0) + 1024;
+}
+
+template <int BPAD>
+cudaError_t list_prepare_kernel() {
+  static bool done[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(umma_list_kernel<BPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64) done[dev] = true;
+  return cudaSuccess;
+}
+
+template <int BPAD>
+int list_resident_clusters(int cluster, size_t smem, int sm_count) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(sm_count / cluster * cluster));
+  cfg.blockDim = dim3(kLThreads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cluster > 1 ? 1 : 0;
+  int n = 0;
+  if (cluster == 1) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, umma_list_kernel<BPAD>, kLThreads, smem) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return 0;
+    }
+    return per_sm > 0 ? sm_count : 0;
+  }
+  if (cudaOccupancyMaxActiveClusters(&n, umma_list_kernel<BPAD>, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    n = 0;
+  }
+  return n;
+}
+
+template <int BPAD>
+cudaError_t list_launch(const ListParams& p, size_t smem, cudaStream_t stream) {
+  return launch_with_pdl(umma_list_kernel<BPAD>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p);
+}
+
+}  // namespace
+}  // namespace bas
+
+using namespace bas;
+
+struct bas_list {
+  int n_calls = 0, bpad = 0, sm_count = 0;
+  size_t smem = 0;
+  void* dev_block = nullptr;   // header, counters, descriptors
+  size_t dev_bytes = 0;
+  ListParams params = {};
+};
+
+namespace {
+
+template <typename F>
+auto by_bpad(int bpad, F&& f) {
+  switch (bpad) {
+    case 16: return f(std::integral_constant<int, 16>{});
+    case 32: return f(std::integral_constant<int, 32>{});
+    case 48: return f(std::integral_constant<int, 48>{});
+    default: return f(std::integral_constant<int, 64>{});
+  }
+}
+
+inline bool list_aligned16(const void* ptr) { return (((uintptr_t)ptr) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_calls, int flags) {
+  if (out == nullptr || calls == nullptr || n_calls <= 0) return BAS_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  if (n_calls > BAS_LIST_MAX_CALLS) return BAS_ERR_UNSUPPORTED;
+  if (flags < 0 || (flags & ~(BAS_GEMM_BF16 | 0x700 | 0x7000 | 0xff0000 | 0x3f000000)) != 0) return BAS_ERR_INVALID_ARGUMENT;
+  int dev = 0, sm_count = 0, cc_major = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  if (cc_major != 10) return BAS_ERR_UNSUPPORTED;
+
+  // ---- argument checks (those of bas_gemm, per call) and the list-wide sizes ----
+  int max_batch = 0, nb_max = 1;
+  for (int c = 0; c < n_calls; ++c) {
+    const bas_list_call& a = calls[c];
+    if (a.x_dev == nullptr || a.packed_dev == nullptr || a.y_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+    if (a.batch <= 0 || a.k <= 0 || a.n <= 0 || a.k_host < 0 || a.ldx < a.k || a.ldy < a.n) return BAS_ERR_INVALID_ARGUMENT;
+    if (a.batch > BAS_MAX_BATCH) return BAS_ERR_UNSUPPORTED;
+    const int nb = (a.k + kBlockK - 1) / kBlockK;
+    if (nb > BAS_LIST_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
+    if (a.bitmap_dev == nullptr && a.ids_dev == nullptr && a.k_host > 0) return BAS_ERR_INVALID_ARGUMENT;
+    if (a.bitmap_dev == nullptr && a.k_host > nb) return BAS_ERR_INVALID_ARGUMENT;
+    if (!list_aligned16(a.x_dev) || !list_aligned16(a.packed_dev) || (a.ldx & 7) != 0 || (a.k & 7) != 0)
+      return BAS_ERR_INVALID_ARGUMENT;
+    if (a.depends_on < -1 || a.depends_on >= c) return BAS_ERR_INVALID_ARGUMENT;
+    if (a.batch > max_batch) max_batch = a.batch;
+    if (nb > nb_max) nb_max = nb;
+  }
+  const int bpad = (max_batch + 15) / 16 * 16;
+  e = by_bpad(bpad, [](auto b) { return list_prepare_kernel<decltype(b)::value>(); });
+  if (e != cudaSuccess) return record_cuda_error(e);
+
+  // ---- cluster size and grid: the largest cluster whose resident count covers at least half the SMs ----
+  const int forced = (flags >> 8) & 7;
+  const int cta_cap = ((flags >> 16) & 0xff) != 0 ? ((flags >> 16) & 0xff) : sm_count;
+  int cluster = 1, n_clusters = 0;
+  for (int cl = 4; cl >= 1; cl >>= 1) {
+    if (forced != 0 && cl != forced) continue;
+    int r = by_bpad(bpad, [&](auto b) { return list_resident_clusters<decltype(b)::value>(cl, kLSmemBudget, sm_count); });
+    if (r > cta_cap / cl) r = cta_cap / cl;
+    if (r <= 0) continue;
+    if (forced == 0 && cl > 1 && r * cl * 2 < sm_count) continue;
+    cluster = cl;
+    n_clusters = r;
+    break;
+  }
+  if (n_clusters <= 0) return BAS_ERR_UNSUPPORTED;
+
+  // ---- per call: the clusters that take part, and the widest column tile of the list ----
+  const int min_units = ((flags >> 24) & 0x3f) != 0 ? ((flags >> 24) & 0x3f) : 8;   // tuning knob
+  std::vector<ListCallDev> host((size_t)n_calls);
+  int off = 0, tw_max = 8;
+  for (int c = 0; c < n_calls; ++c) {
+    const bas_list_call& a = calls[c];
+    ListCallDev& d = host[(size_t)c];
+    std::memset(&d, 0, sizeof(d));
+    const int npad = padded_cols(a.n), units = npad / 8;
+    int ranges = units / min_units;      // no range narrower than min_units * 8 columns where the output allows
+    if (ranges < 1) ranges = 1;
+    if (ranges > n_clusters) ranges = n_clusters;
+    // widest range of this call, its column tiles
+    const int wmax = ((units + ranges - 1) / ranges) * 8;
+    const int n_sub = (wmax + kTileN - 1) / kTileN;
+    if (n_sub > 16) return BAS_ERR_UNSUPPORTED;
+    const int tw = ((wmax + n_sub - 1) / n_sub + 7) & ~7;
+    if (tw > tw_max) tw_max = tw;
+    d.packed = (const uint8_t*)a.packed_dev;
+    d.ids = a.bitmap_dev != nullptr ? nullptr : a.ids_dev;
+    d.count_dev = a.bitmap_dev != nullptr ? nullptr : a.count_dev;
+    d.bitmap = a.bitmap_dev;
+    d.y = (__half*)a.y_dev;
+    d.ldy = (long long)a.ldy;
+    d.nb = (a.k + kBlockK - 1) / kBlockK;
+    d.k_host = a.k_host > d.nb ? d.nb : a.k_host;
+    d.batch = a.batch;
+    d.n = a.n;
+    d.units = units;
+    d.ranges = ranges;
+    d.range_off = (ranges < n_clusters) ? off : 0;
+    if (ranges < n_clusters) off = (off + ranges) % n_clusters;
+    d.dep = a.depends_on;
+    d.dep_contrib = a.depends_on >= 0 ? (unsigned int)(host[(size_t)a.depends_on].ranges * cluster) : 0u;
+    // X[batch, K]: inner dimension K, box {64 channels, bpad rows}, 128-byte swizzle, zeros out of range
+    auto encode = (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder();
+    if (encode == nullptr) return record_cuda_error(cudaErrorNotSupported);
+    const cuuint64_t gdim[2] = {(cuuint64_t)a.k, (cuuint64_t)a.batch};
+    const cuuint64_t gstride[1] = {(cuuint64_t)a.ldx * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)bpad};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(&d.xmap, (flags & BAS_GEMM_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                              2, const_cast<void*>(a.x_dev), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue);
+  }
+
+  // ---- ring: slots of one weight tile + one activation tile ----
+  const int wslot = (int)round_up((size_t)tw_max * kRowBytes, 1024);
+  const size_t tile_bytes = (size_t)wslot + (size_t)bpad * 128;
+  const size_t fixed = list_fixed_smem(n_calls, nb_max, cluster, bpad);
+  const size_t pad = (size_t)kLMmaSpanBytes > (size_t)wslot ? (size_t)kLMmaSpanBytes - (size_t)wslot : 0;
+  if (fixed + pad + 2 * tile_bytes > kLSmemBudget) return BAS_ERR_UNSUPPORTED;
+  int slots = (int)((kLSmemBudget - fixed - pad) / tile_bytes);
+  if (slots > kMaxStages) slots = kMaxStages;
+  int pairs = (flags >> 12) & 7;
+  if (pairs < 2 || pairs > kLIssuers || slots / pairs == 0) {
+    pairs = 0;
+    int best = 2;
+    for (int cnd = kLIssuers; cnd >= 2; --cnd) {
+      const int kept = slots / cnd * cnd;
+      if (kept * 4 >= slots * 3) {
+        pairs = cnd;
+        break;
+      }
+      if (kept > slots / best * best) best = cnd;
+    }
+    if (pairs == 0) pairs = best;
+  }
+  slots = slots / pairs * pairs;
+  if (slots < 2) return BAS_ERR_UNSUPPORTED;
+
+  bas_list* l = new (std::nothrow) bas_list();
+  if (l == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  l->n_calls = n_calls;
+  l->bpad = bpad;
+  l->sm_count = sm_count;
+  l->smem = fixed + pad + (size_t)slots * tile_bytes;
+  const size_t counters_off = 256;
+  const size_t desc_off = counters_off + round_up((size_t)n_calls * 4, 256);
+  l->dev_bytes = desc_off + sizeof(ListCallDev) * (size_t)n_calls;
+  e = cudaMalloc(&l->dev_block, l->dev_bytes);
+  if (e == cudaSuccess) e = cudaMemset(l->dev_block, 0, desc_off);
+  if (e == cudaSuccess)
+    e = cudaMemcpy((uint8_t*)l->dev_block + desc_off, host.data(), sizeof(ListCallDev) * (size_t)n_calls, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    if (l->dev_block != nullptr) cudaFree(l->dev_block);
+    delete l;
+    return record_cuda_error(e);
+  }
+  ListParams& p = l->params;
+  p.calls = (const ListCallDev*)((uint8_t*)l->dev_block + desc_off);
+  p.n_calls = n_calls;
+  p.hdr = (ListHeaderDev*)l->dev_block;
+  p.done = (unsigned int*)((uint8_t*)l->dev_block + counters_off);
+  p.cluster = cluster;
+  p.n_clusters = n_clusters;
+  p.stages = slots;
+  p.pairs = pairs;
+  p.wslot = wslot;
+  p.nb_max = nb_max;
+  p.bf16 = (flags & BAS_GEMM_BF16) != 0 ? 1 : 0;
+  p.stall_call = -1;
+  p.wait_cycles = kWaitCycles;
+  *out = l;
+  return BAS_OK;
+}
+
+BAS_API int bas_list_run(bas_list* l, void* stream) {
+  if (l == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  count_launch();
+  const cudaError_t e = by_bpad(l->bpad, [&](auto b) {
+    return list_launch<decltype(b)::value>(l->params, l->smem, (cudaStream_t)stream);
+  });
+  return e == cudaSuccess ? BAS_OK : record_cuda_error(e);
+}
+
+BAS_API int bas_list_read_status(bas_list* l, unsigned int* flags_out, void* stream) {
+  if (l == nullptr || flags_out == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e = cudaMemcpyAsync(flags_out, &l->params.hdr->status, sizeof(unsigned int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(&l->params.hdr->status, 0, sizeof(unsigned int), s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  return e == cudaSuccess ? BAS_OK : record_cuda_error(e);
+}
+
+BAS_API int bas_list_reset(bas_list* l) {
+  if (l == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemset(l->dev_block, 0, (size_t)((const uint8_t*)l->params.calls - (const uint8_t*)l->dev_block));
+  return e == cudaSuccess ? BAS_OK : record_cuda_error(e);
+}
+
+BAS_API int bas_list_set_wait(bas_list* l, double wait_ms, int never_ready_call) {
+  if (l == nullptr || !(wait_ms > 0.0) || wait_ms > 10000.0 || never_ready_call < -1 || never_ready_call >= l->n_calls)
+    return BAS_ERR_INVALID_ARGUMENT;
+  l->params.wait_cycles = (long long)(wait_ms * 2.0e6);   // clock64 ticks at about 2 GHz
+  l->params.stall_call = never_ready_call;
+  return BAS_OK;
+}
+
+BAS_API int bas_list_info(const bas_list* l, int* ctas, int* cluster, int* slots, int* pairs) {
+  if (l == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  if (ctas != nullptr) *ctas = l->params.n_clusters * l->params.cluster;
+  if (cluster != nullptr) *cluster = l->params.cluster;
+  if (slots != nullptr) *slots = l->params.stages;
+  if (pairs != nullptr) *pairs = l->params.pairs;
+  return BAS_OK;
+}
+
+BAS_API void bas_list_destroy(bas_list* l) {
+  if (l == nullptr) return;
+  if (l->dev_block != nullptr) cudaFree(l->dev_block);
+  delete l;
+}
+
+}  // extern "C"

@@ -1136,6 +1136,9 @@ cudaError_t launch_umma_b(GemmParams p, int sm_count, cudaStream_t stream) {
 
 }  // namespace
 
+// cuTensorMapEncodeTiled of the loaded driver (null if it has none); shared with the list kernel's host side.
+void* tensor_map_encoder() { return (void*)get_encode_fn(); }
+
 cudaError_t launch_umma(const GemmParams& p, int sm_count, cudaStream_t stream) {
   const int bpad = (p.batch + 15) / 16 * 16;
   switch (bpad) {
