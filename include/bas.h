@@ -189,6 +189,15 @@ BAS_API int bas_select_budget_ex(const void* x_dev, int64_t ldx, int batch, int 
                          int score_flags, int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
                          double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream);
 
+/* bas_select_budget_ex with the dense fallback of _patch_adaptive
+ * (scripts/bench_alpaca_energy_budget_e2e.py:104-109) taken on the device: when the budget keeps more
+ * than full_above blocks, every block is kept (count = K/64), so that the contraction that follows
+ * computes the dense product without the host having to read the count. */
+BAS_API int bas_select_budget_capped(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
+                             int full_above, int score_flags, int32_t* ids_out_dev, int32_t* count_out_dev,
+                             uint8_t* bitmap_out_dev, double* scores_out_dev, void* ws_dev, size_t ws_bytes,
+                             void* stream);
+
 /* ---- selection and contraction in one call -------------------------------------------------
  * The chain of _sparse_linear (scripts/bench_roundrobin_e2e_decode.py:179-284): select the batch's
  * blocks, then multiply.  Where the contraction runs in clusters and the scoring is small (up to

@@ -106,12 +106,20 @@ def block_scores(x: np.ndarray, kind: int = SCORE_NORM, block_k: int = BLOCK_K) 
     return s / float(x2.shape[0])
 
 
+def descending_order(scores: np.ndarray) -> np.ndarray:
+    """Block ids from the largest score to the smallest; equal scores go to the lower id and a NaN
+    ranks above everything, +inf included (the order of ``torch.topk`` and of a descending
+    ``torch.sort``), all NaNs alike.  A total order whatever the scores hold."""
+    s = np.asarray(scores, dtype=np.float64)
+    nan = np.isnan(s)
+    clean = np.where(nan, np.inf, s)
+    return np.lexsort((np.arange(s.size), -clean, ~nan))   # NaNs first, then by -score, then by index
+
+
 def topk_ids(scores: np.ndarray, n_keep: int) -> np.ndarray:
     """Ascending int32 ids of the ``n_keep`` largest scores; equal scores go to the lower id
     (``torch.topk(score, k).indices.sort()`` at bench_roundrobin_e2e_decode.py:113)."""
-    s = np.asarray(scores, dtype=np.float64)
-    order = np.lexsort((np.arange(s.size), -s))  # by -score, then by index
-    return np.sort(order[: int(n_keep)]).astype(np.int32)
+    return np.sort(descending_order(scores)[: int(n_keep)]).astype(np.int32)
 
 
 def make_channel_scale(k: int, seed: int) -> np.ndarray:
@@ -180,10 +188,14 @@ def energy_budget_ids(energy: np.ndarray, energy_keep: float, min_keep: int = 1)
     """Smallest prefix of the descending energies whose sum reaches ``energy_keep`` of the
     total (``_energy_budget_active``, bench_alpaca_energy_budget_e2e.py:49-56): ascending ids."""
     e = np.asarray(energy, dtype=np.float64)
-    order = np.lexsort((np.arange(e.size), -e))
-    cum = np.cumsum(e[order])
-    thresh = float(energy_keep) * float(cum[-1])
-    k = int(np.searchsorted(cum, thresh, side="left")) + 1
+    order = descending_order(e)
+    with np.errstate(invalid="ignore"):
+        cum = np.cumsum(e[order])
+        thresh = float(energy_keep) * float(cum[-1])
+    if np.isnan(thresh):                       # not a number in the energies: every block is kept
+        k = int(e.size)
+    else:
+        k = int(np.searchsorted(cum, thresh, side="left")) + 1
     k = max(int(min_keep), min(int(e.size), k))
     return np.sort(order[:k]).astype(np.int32)
 

@@ -1070,3 +1070,57 @@ def test_select_gemm_bf16(dev, b, k, n):
     assert int(count.item()) == n_keep
     assert np.array_equal(ids[:n_keep].cpu().numpy(), want)
     assert O.max_err_ratio(out.float().cpu().numpy(), O.masked_gemm(x, w, want)) <= TOL_BF16
+
+
+@pytest.mark.parametrize("b,k", [(2, 1024), (16, 4096), (64, 11008)])
+def test_selection_with_non_finite_activations(dev, b, k):
+    """NaN and infinities in X (and an infinity times a zero channel weight) take the defined path:
+    NaN ranks above +inf, equal scores to the lower id, exactly n_keep ids, nothing out of bounds -
+    top-k, weighted, budget and the one-call selection + contraction alike."""
+    ops = _ops()
+    nb = k // 64
+    x = O.make_activations(b, k, seed=b + k, dist="laplace")
+    x[0, 64 * 3 + 5] = np.nan
+    x[b - 1, 64 * 7] = np.inf
+    x[b // 2, 64 * 9 + 1] = -np.inf
+    x[0, 64 * 11] = np.inf
+    x[0, 64 * 11 + 1] = np.nan
+    tx = torch.from_numpy(x).to(dev)
+    guard = 7
+    for kind in (O.SCORE_NORM, O.SCORE_ENERGY):
+        for n_keep in (1, 3, nb // 3, nb):
+            ids_buf = torch.full((nb + guard,), -7, dtype=torch.int32, device=dev)
+            cnt = torch.zeros(1, dtype=torch.int32, device=dev)
+            ops.select_topk(tx, n_keep, kind, ids_out=ids_buf, count_out=cnt)
+            torch.cuda.synchronize()
+            got = ids_buf.cpu().numpy()
+            with np.errstate(invalid="ignore", over="ignore"):
+                want = O.topk_ids(O.block_scores(x, kind), n_keep)
+            assert int(cnt.item()) == n_keep
+            assert np.array_equal(got[:n_keep], want), (kind, n_keep)
+            assert (got[n_keep:] == -7).all(), "wrote past n_keep ids"
+    # an infinite activation under a zero channel weight is not a number: weighted mode
+    scale = O.make_channel_scale(k, seed=1)
+    scale[64 * 7] = 0.0
+    ids_buf = torch.full((nb + guard,), -7, dtype=torch.int32, device=dev)
+    cnt = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.select_topk(tx, 5, O.SCORE_NORM, ids_out=ids_buf, count_out=cnt, chan_scale=torch.from_numpy(scale).to(dev))
+    torch.cuda.synchronize()
+    with np.errstate(invalid="ignore", over="ignore"):
+        want = O.topk_ids(O.weighted_block_scores(x, scale, None), 5)
+    assert np.array_equal(ids_buf[:5].cpu().numpy(), want) and (ids_buf[5:].cpu().numpy() == -7).all()
+    # budget: the total is not a number, so every block is kept
+    ids_buf = torch.full((nb + guard,), -7, dtype=torch.int32, device=dev)
+    ops.select_budget(tx, 0.5, 1, ids_out=ids_buf, count_out=cnt)
+    torch.cuda.synchronize()
+    assert int(cnt.item()) == nb and np.array_equal(ids_buf[:nb].cpu().numpy(), np.arange(nb, dtype=np.int32))
+    # selection + contraction in one call: same ids on both of its paths; the kernel must not fault
+    w = O.make_weight(256, k, seed=2)
+    out = torch.empty(b, 256, dtype=torch.float16, device=dev)
+    ids_buf = torch.full((nb + guard,), -7, dtype=torch.int32, device=dev)
+    ops.select_gemm(tx, ops.pack_weight(torch.from_numpy(w).to(dev)), out, 6, O.SCORE_ENERGY, ids_out=ids_buf, count_out=cnt)
+    torch.cuda.synchronize()
+    with np.errstate(invalid="ignore", over="ignore"):
+        want = O.topk_ids(O.block_scores(x, O.SCORE_ENERGY), 6)
+    assert int(cnt.item()) == 6 and np.array_equal(ids_buf[:6].cpu().numpy(), want)
+    assert ops.read_status(dev) == 0

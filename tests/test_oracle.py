@@ -185,3 +185,25 @@ def test_bf16_rounding_matches_torch():
                         np.array([0.0, -0.0, 1.0, 1.00390625, 1.005859375, 3.0e38, 1e-40], np.float32)])
     want = torch.from_numpy(a).to(torch.bfloat16).to(torch.float32).numpy()
     assert np.array_equal(O.round_to_bf16(a), want)
+
+
+def test_nan_and_inf_scores_rank_like_torch_topk():
+    """Not-a-number ranks above +inf (torch.topk, torch.sort descending), equal scores to the lower id:
+    the order is total, so exactly n_keep ids come back whatever the activations hold."""
+    torch = pytest.importorskip("torch")
+    s = np.array([1.0, np.nan, np.inf, 0.5, np.nan, -np.inf, 2.0, np.inf], np.float64)
+    order = O.descending_order(s)
+    assert order.tolist() == [1, 4, 2, 7, 6, 0, 3, 5]
+    for n_keep in range(1, 9):
+        ids = O.topk_ids(s, n_keep)
+        assert ids.size == n_keep and np.array_equal(ids, np.sort(order[:n_keep]))
+        # torch agrees on WHICH scores are kept (its order among equal scores is unspecified)
+        tk = torch.topk(torch.from_numpy(s), n_keep).values.numpy()
+        np.testing.assert_array_equal(np.sort(np.nan_to_num(tk, nan=1e300)), np.sort(np.nan_to_num(s[ids], nan=1e300)))
+    x = O.make_activations(4, 512, seed=3)
+    x[1, 70] = np.nan
+    x[2, 200] = np.inf
+    assert O.select_active_blocks(x, 0.25, O.SCORE_NORM).tolist() == [1, 3]
+    # a total that is not a number keeps every block; an infinite one keeps the infinite block
+    assert O.energy_budget_ids(np.array([1.0, np.nan, 3.0]), 0.5).tolist() == [0, 1, 2]
+    assert O.energy_budget_ids(np.array([1.0, np.inf, 3.0]), 0.5).tolist() == [1]

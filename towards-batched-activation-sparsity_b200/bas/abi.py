@@ -75,6 +75,7 @@ _SIGNATURES = {
     "bas_select_topk_weighted": (_i, [_vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bas_select_budget": (_i, [_vp, _i64, _i, _i, C.c_double, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bas_select_budget_ex": (_i, [_vp, _i64, _i, _i, C.c_double, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "bas_select_budget_capped": (_i, [_vp, _i64, _i, _i, C.c_double, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bas_select_gemm": (_i, [_vp, _i64, _vp, _i, _i, _i, _i, _i, C.c_double, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _sz,
                              _vp, _sz, _i, _vp]),
     "bas_select_topk_noalloc": (_i, [_vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),

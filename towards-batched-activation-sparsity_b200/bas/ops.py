@@ -408,14 +408,18 @@ def prior_multiplier(block_prior: torch.Tensor, prior_alpha: float = 1.0, prior_
 
 def select_budget(x2d: torch.Tensor, energy_keep: float, min_keep: int = 1, *,
                   ids_out: Optional[torch.Tensor] = None, count_out: Optional[torch.Tensor] = None,
-                  bitmap_out: Optional[torch.Tensor] = None, scores_out: Optional[torch.Tensor] = None):
+                  bitmap_out: Optional[torch.Tensor] = None, scores_out: Optional[torch.Tensor] = None,
+                  full_above: Optional[int] = None):
     """Device-side energy-budget selection (variable count).  Returns (ids buffer [nb], count int32[1]);
-    only the first ``count`` ids are meaningful, and reading ``count`` on the host synchronises."""
-    return _select(x2d, 1, int(min_keep), SCORE_ENERGY, float(energy_keep), ids_out, count_out, bitmap_out, scores_out)
+    only the first ``count`` ids are meaningful, and reading ``count`` on the host synchronises.
+    ``full_above``: a budget that keeps more blocks than this keeps them all (the reference's dense
+    fallback, scripts/bench_alpaca_energy_budget_e2e.py:104-109, decided on the device)."""
+    return _select(x2d, 1, int(min_keep), SCORE_ENERGY, float(energy_keep), ids_out, count_out, bitmap_out, scores_out,
+                   full_above=full_above)
 
 
 def _select(x2d, mode, n_keep, score_kind, energy_keep, ids_out, count_out, bitmap_out, scores_out,
-            chan_scale=None, block_mult=None):
+            chan_scale=None, block_mult=None, full_above=None):
     _require_cuda_fp16(x2d, "x")
     for name, t, need in (("chan_scale", chan_scale, (x2d.shape[1] // BLOCK_K) * BLOCK_K),
                           ("block_mult", block_mult, x2d.shape[1] // BLOCK_K)):
@@ -456,6 +460,10 @@ def _select(x2d, mode, n_keep, score_kind, energy_keep, ids_out, count_out, bitm
             check(lib.bas_select_topk(x2d.data_ptr(), x2d.stride(0), bt, k, n_keep, int(score_kind) | bf16, *args),
                   "bas_select_topk")
             return ids_out[:n_keep], count_out
+        if full_above is not None:
+            check(lib.bas_select_budget_capped(x2d.data_ptr(), x2d.stride(0), bt, k, energy_keep, n_keep, int(full_above),
+                                               bf16, *args), "bas_select_budget_capped")
+            return ids_out, count_out
         check(lib.bas_select_budget_ex(x2d.data_ptr(), x2d.stride(0), bt, k, energy_keep, n_keep, bf16, *args),
               "bas_select_budget_ex")
         return ids_out, count_out

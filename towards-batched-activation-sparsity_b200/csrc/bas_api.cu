@@ -349,7 +349,8 @@ size_t bas_select_workspace_bytes(int k) {
 static int select_common(const void* x_dev, int64_t ldx, int batch, int k, int mode, int n_keep, int score_kind,
                          double energy_keep, int32_t* ids_out_dev, int32_t* count_out_dev, uint8_t* bitmap_out_dev,
                          double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream,
-                         const float* chan_scale_dev = nullptr, const float* block_mult_dev = nullptr) {
+                         const float* chan_scale_dev = nullptr, const float* block_mult_dev = nullptr,
+                         int full_above = 0x7fffffff) {
   if (chan_scale_dev != nullptr && !aligned16(chan_scale_dev)) return BAS_ERR_INVALID_ARGUMENT;
   if (x_dev == nullptr || ids_out_dev == nullptr || count_out_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || k < kBlockK || ldx < k || !aligned16(x_dev) || (ldx & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
@@ -384,6 +385,7 @@ static int select_common(const void* x_dev, int64_t ldx, int batch, int k, int m
   p.chan_scale = chan_scale_dev;
   p.block_mult = block_mult_dev;
   p.inputs_stable = inputs_stable;
+  p.full_above = full_above;
   if (chan_scale_dev != nullptr) p.score_kind = BAS_SCORE_ENERGY;   // weighted squares, no root (as the reference)
   cudaError_t e = launch_select(p, di.sm_count, (cudaStream_t)stream);
   return e == cudaSuccess ? BAS_OK : cuda_fail(e);
@@ -417,6 +419,14 @@ int bas_select_budget_ex(const void* x_dev, int64_t ldx, int batch, int k, doubl
   if ((score_flags & ~BAS_SCORE_BF16) != 0) return BAS_ERR_INVALID_ARGUMENT;
   return select_common(x_dev, ldx, batch, k, 1, min_keep, BAS_SCORE_ENERGY | score_flags, energy_keep, ids_out_dev,
                        count_out_dev, bitmap_out_dev, scores_out_dev, ws_dev, ws_bytes, stream);
+}
+
+int bas_select_budget_capped(const void* x_dev, int64_t ldx, int batch, int k, double energy_keep, int min_keep,
+                             int full_above, int score_flags, int32_t* ids_out_dev, int32_t* count_out_dev,
+                             uint8_t* bitmap_out_dev, double* scores_out_dev, void* ws_dev, size_t ws_bytes, void* stream) {
+  if ((score_flags & ~BAS_SCORE_BF16) != 0 || full_above < 0) return BAS_ERR_INVALID_ARGUMENT;
+  return select_common(x_dev, ldx, batch, k, 1, min_keep, BAS_SCORE_ENERGY | score_flags, energy_keep, ids_out_dev,
+                       count_out_dev, bitmap_out_dev, scores_out_dev, ws_dev, ws_bytes, stream, nullptr, nullptr, full_above);
 }
 
 int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_dev, int batch, int k, int n, int n_keep,

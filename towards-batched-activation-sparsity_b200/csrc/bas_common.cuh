@@ -387,6 +387,15 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned 
   return v;
 }
 
+// Ranking key of a block score: unsigned keys order like the scores, with every NaN alike and
+// above +infinity (torch.topk and a descending sort put NaN first), so that ranking by
+// (key descending, id ascending) is a total order whatever the inputs hold.
+__device__ __forceinline__ unsigned long long score_key(double s) {
+  unsigned long long u = (unsigned long long)__double_as_longlong(s);
+  if (s != s) u = 0x7ff8000000000000ull;
+  return (u >> 63) != 0ull ? ~u : (u | 0x8000000000000000ull);
+}
+
 // fp32 -> the output's 16-bit type (round to nearest even), stored through the fp16-typed pointer
 // that stands for either container.
 __device__ __forceinline__ void store_out16(__half* dst, float v, bool bf16) {

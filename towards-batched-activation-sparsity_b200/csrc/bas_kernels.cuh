@@ -132,6 +132,7 @@ struct SelectParams {
   unsigned int* ws_done;  // workspace: CTA arrival counter
   const float* chan_scale = nullptr;   // optional [64 * nb]: per-channel weight of the squares (16-byte aligned)
   const float* block_mult = nullptr;   // optional [nb]: factor on the batch-mean score
+  int full_above = 0x7fffffff;   // budget mode: a kept count above this keeps every block (the dense fallback)
   int inputs_stable = 0;   // BAS_SCORE_INPUTS_STABLE: score at once, wait for the preceding kernel only before leaving
 };
 cudaError_t launch_select(const SelectParams& p, int sm_count, cudaStream_t stream);

@@ -28,6 +28,7 @@
 #include <cudaTypedefs.h>
 
 #include <cstddef>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <type_traits>
@@ -36,6 +37,22 @@
 namespace bas {
 
 namespace {
+
+// Diagnostic build (-DBAS_TRACE): CTA 0 stamps the global timer at a few events of each of the first
+// calls into a device array that bas_list_debug_trace() copies out.  Compiled out of the product.
+#ifdef BAS_TRACE
+constexpr int kLTraceCalls = 256, kLTraceEvents = 8;
+#define BAS_LTRACE(call, ev)                                                                      \
+  do {                                                                                            \
+    if (p.trace != nullptr && blockIdx.x == p.trace_cta && (call) < kLTraceCalls) {               \
+      unsigned long long gt_;                                                                     \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                                     \
+      p.trace[(call) * kLTraceEvents + (ev)] = (long long)gt_;                                    \
+    }                                                                                             \
+  } while (0)
+#else
+#define BAS_LTRACE(call, ev) do { } while (0)
+#endif
 
 constexpr int kLProducers = 4;
 constexpr int kLIssuers = 4;
@@ -58,7 +75,7 @@ struct alignas(128) ListCallDev {
   int ranges;                  // clusters that take part in this call
   int range_off;               // the first of them (the others follow, modulo the cluster count)
   int dep;                     // call whose completion X waits for, or -1
-  unsigned int dep_contrib;    // CTAs that report the completion of call `dep`
+  unsigned int dep_contrib;    // warps that report the completion of call `dep` (eight per CTA taking part)
   int pad[5];
 };
 static_assert(sizeof(ListCallDev) == 256, "call descriptor layout");
@@ -84,6 +101,10 @@ struct ListParams {
   int bf16;
   int stall_call;            // tests of the expiry path: this call's dependency is never seen complete (-1: off)
   long long wait_cycles;     // bound of every wait
+#ifdef BAS_TRACE
+  long long* trace;          // diagnostic build only
+  int trace_cta;
+#endif
 };
 
 struct ListSmemHeader {
@@ -95,13 +116,14 @@ struct ListSmemHeader {
   uint32_t tmem_base;
   int abort_flag;
   unsigned int calls_staged;   // records [0, calls_staged) are valid
-  unsigned int epi_arrived;    // epilogue warps that have finished their part of a call (8 per call)
+  unsigned int pad;
 };
 
-// Per-call record published by copy warp 0: bit 31 = this CTA takes part, bits 16..23 = column
-// tiles of its range, bits 0..15 = active blocks of this CTA.
-__device__ __forceinline__ unsigned int make_record(bool part, int n_sub, int k_mine) {
-  return (part ? 0x80000000u : 0u) | ((unsigned int)n_sub << 16) | (unsigned int)k_mine;
+// Per-call record published by copy warp 0: bit 31 = this CTA takes part, bit 30 = its column tiles
+// are at most 64 wide and multiplied with M = 64 instructions, bits 16..23 = column tiles of its
+// range, bits 0..15 = active blocks of this CTA.
+__device__ __forceinline__ unsigned int make_record(bool part, bool m64, int n_sub, int k_mine) {
+  return (part ? 0x80000000u : 0u) | (m64 ? 0x40000000u : 0u) | ((unsigned int)n_sub << 16) | (unsigned int)k_mine;
 }
 
 // This cluster's share of a call.
@@ -164,7 +186,8 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
   constexpr int kXTileBytes = BPAD * 128;
   constexpr int kAccCols = 2 * kLIssuers * BPAD;                      // two buffers of one accumulator per issuer
   constexpr int kTmemCols = kAccCols <= 128 ? 128 : kAccCols <= 256 ? 256 : 512;
-  const uint32_t kIdesc = umma_idesc_f16(128, BPAD) | (p.bf16 ? ((1u << 7) | (1u << 10)) : 0u);
+  const uint32_t kFmt = p.bf16 ? ((1u << 7) | (1u << 10)) : 0u;
+  const uint32_t kIdesc = umma_idesc_f16(128, BPAD) | kFmt, kIdesc64 = umma_idesc_f16(64, BPAD) | kFmt;
   const bool bf16 = p.bf16 != 0;
 
   extern __shared__ uint8_t smem_raw[];
@@ -201,7 +224,6 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     }
     hdr->abort_flag = 0;
     hdr->calls_staged = 0u;
-    hdr->epi_arrived = 0u;
     fence_barrier_init();
   }
   if (warp == kLEpiWarp0) {
@@ -265,6 +287,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
           if (!ready) return false;
           fence_proxy_async_all();   // the tensor copy below reads what other CTAs stored with plain stores
           dep_ok = dep;
+          if (warp == 0) BAS_LTRACE(dcall, 1);
         }
         tma_load_2d_hint(s_stage + (size_t)dslot * tile_bytes + p.wslot, &cd->xmap, dj * kBlockK, 0, &hdr->full[dslot], pol_x);
         ++def_head;
@@ -298,12 +321,15 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
           k_mine = (k_act > rank) ? (k_act - rank + C - 1) / C : 0;
         }
         if (warp == 0 && lane == 0) {
-          s_rec[c] = make_record(sh.part, sh.n_sub, k_mine);
+          // An MMA costs the tensor core by the rows of the weight operand it reads (measured: 39
+          // cycles per M = 128 instruction, 23 per M = 64): tiles of up to 64 columns use the short form.
+          s_rec[c] = make_record(sh.part, C == 1 && sh.tw <= 64, sh.n_sub, k_mine);
           st_release_cta_shared_u32(&hdr->calls_staged, (unsigned int)(c + 1));
         }
         // the next call's id list: requested now, used at the next boundary
         int raw_n[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         const bool have_n = (c + 1 < p.n_calls) ? prefetch_ids(nxt, raw_n) : false;
+        if (warp == 0 && lane == 0) BAS_LTRACE(c, 0);
         if (lane == 0 && sh.part && k_mine > 0) {
           const uint8_t* packed = (const uint8_t*)regs_ptr(cur.a.x, cur.a.y);
           const int npad = units * 8;
@@ -344,6 +370,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
             if (t0mod >= P) t0mod -= P;
           }
         }
+        if (warp == 0 && lane == 0) BAS_LTRACE(c, 2);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         cur = nxt;
         nxt = nn;
@@ -383,6 +410,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         const unsigned int rec = s_rec[c];
         if ((rec & 0x80000000u) == 0u) continue;
         const int n_sub = (int)((rec >> 16) & 0xffu), k_mine = (int)(rec & 0xffffu);
+        const uint32_t idesc = (rec & 0x40000000u) != 0u ? kIdesc64 : kIdesc;
         for (int sub = 0; sub < n_sub && ok; ++sub, ++u) {
           const int b = u & 1;
           // the accumulator buffer is free once the epilogue has read out unit u - 2; passing this
@@ -402,12 +430,13 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               break;
             }
             tc_fence_after_sync();
+            if (w == 0 && fresh && sub == 0) BAS_LTRACE(c, 3);
             const uint32_t st = smem_u32(s_stage + (size_t)slot * tile_bytes);
             const uint64_t adesc = umma_desc_kmajor_sw128(st);
             const uint64_t bdesc = umma_desc_kmajor_sw128(st + p.wslot);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
-              umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), kIdesc, (fresh && ks == 0) ? 0u : 1u);
+              umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), idesc, (fresh && ks == 0) ? 0u : 1u);
             fresh = false;
             umma_commit(&hdr->empty[slot]);   // the slot is free once these MMAs have read it
             slot += P;
@@ -419,6 +448,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
           if (!ok) break;
           if (!fresh) umma_commit(&hdr->acc_full[b]);
           else mbar_arrive(&hdr->acc_full[b]);
+          if (w == 0 && sub == n_sub - 1) BAS_LTRACE(c, 4);
           t0mod += k_mine % P;
           if (t0mod >= P) t0mod -= P;
         }
@@ -431,7 +461,6 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
   } else {
     // ================================ epilogue ================================
     const int q = warp & 3;
-    const int r = q * 32 + lane;             // row of the accumulator = column within the tile
     const int et = tid - 32 * kLEpiWarp0;
     const int eset = et >> 7;
     constexpr int kChunks = BPAD / 16;
@@ -458,6 +487,9 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
       const unsigned int rec = s_rec[c];
       if ((rec & 0x80000000u) == 0u) continue;
       const int k_mine = (int)(rec & 0xffffu);
+      // Row of the accumulator (= column within the tile) that this thread reads: M = 128 fills all
+      // 128 lanes of tensor memory; M = 64 puts rows 16q .. 16q+15 on the first 16 lanes of quarter q.
+      const int r = (rec & 0x40000000u) != 0u ? (lane < 16 ? 16 * q + lane : kTileN) : q * 32 + lane;
       const ListCallDev* cd = p.calls + c;
       const Share sh = call_share(__ldg(&cd->units), __ldg(&cd->ranges), __ldg(&cd->range_off), cid, p.n_clusters);
       __half* y = ldg_ptr(&cd->y);
@@ -473,6 +505,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
           break;
         }
         tc_fence_after_sync();
+        if (et == 0 && sub == sh.n_sub - 1) BAS_LTRACE(c, 5);
         float* red_buf = s_red + (size_t)b * BPAD * kTileN;
 
         auto emit = [&](auto ch0_c, auto nch_c) {
@@ -608,19 +641,15 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         if (t0mod >= P) t0mod -= P;
       }
       if (!ok) break;
-      // This CTA's part of call c is in global memory: report it.  Readers fetch it with tensor copies.
-      // (The last of the eight warps to get here does it; nothing blocks, so a warp that gave up
-      // cannot strand the others.)
-      // One fence per warp: it orders the stores of the warp's other lanes too (they precede it
-      // through the warp barrier).
+      // This CTA's part of call c is in global memory: report it.  Every warp adds one to the call's
+      // counter with release semantics at GPU scope; that orders the stores of the warp's other lanes
+      // too (they precede it through the warp barrier).  Nothing blocks, so a warp that gave up cannot
+      // strand the others, and no heavier fence is needed: the readers acquire the counter.
       __syncwarp();
+      if (et == 0) BAS_LTRACE(c, 6);
       if (lane == 0) {
-        __threadfence();
-        if ((atomicAdd(&hdr->epi_arrived, 1u) & 7u) == 7u) {
-          __threadfence();
-          fence_proxy_async_all();
-          red_release_gpu_add_u32(p.done + c, 1u);
-        }
+        red_release_gpu_add_u32(p.done + c, 1u);
+        if (et == 0) BAS_LTRACE(c, 7);
       }
     }
     if (!ok) {
@@ -786,20 +815,16 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
   e = by_bpad(bpad, [](auto b) { return list_prepare_kernel<decltype(b)::value>(); });
   if (e != cudaSuccess) return record_cuda_error(e);
 
-  // ---- cluster size and grid: the largest cluster whose resident count covers at least half the SMs ----
+  // ---- cluster size and grid ----
+  // One CTA per column range unless the caller asks for clusters: measured on the Llama-2-7B stack
+  // (batch 16) the cluster modes, whose CTAs meet once per column tile to add their partials, run at a
+  // third of the rate of independent CTAs, with or without dependencies between the calls.
   const int forced = (flags >> 8) & 7;
   const int cta_cap = ((flags >> 16) & 0xff) != 0 ? ((flags >> 16) & 0xff) : sm_count;
-  int cluster = 1, n_clusters = 0;
-  for (int cl = 4; cl >= 1; cl >>= 1) {
-    if (forced != 0 && cl != forced) continue;
-    int r = by_bpad(bpad, [&](auto b) { return list_resident_clusters<decltype(b)::value>(cl, kLSmemBudget, sm_count); });
-    if (r > cta_cap / cl) r = cta_cap / cl;
-    if (r <= 0) continue;
-    if (forced == 0 && cl > 1 && r * cl * 2 < sm_count) continue;
-    cluster = cl;
-    n_clusters = r;
-    break;
-  }
+  if (forced != 0 && forced != 1 && forced != 2 && forced != 4) return BAS_ERR_INVALID_ARGUMENT;
+  const int cluster = forced != 0 ? forced : 1;
+  int n_clusters = by_bpad(bpad, [&](auto b) { return list_resident_clusters<decltype(b)::value>(cluster, kLSmemBudget, sm_count); });
+  if (n_clusters > cta_cap / cluster) n_clusters = cta_cap / cluster;
   if (n_clusters <= 0) return BAS_ERR_UNSUPPORTED;
 
   // ---- per call: the clusters that take part, and the widest column tile of the list ----
@@ -835,7 +860,7 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
     d.range_off = (ranges < n_clusters) ? off : 0;
     if (ranges < n_clusters) off = (off + ranges) % n_clusters;
     d.dep = a.depends_on;
-    d.dep_contrib = a.depends_on >= 0 ? (unsigned int)(host[(size_t)a.depends_on].ranges * cluster) : 0u;
+    d.dep_contrib = a.depends_on >= 0 ? (unsigned int)(host[(size_t)a.depends_on].ranges * cluster * (kLEpiThreads / 32)) : 0u;
     // X[batch, K]: inner dimension K, box {64 channels, bpad rows}, 128-byte swizzle, zeros out of range
     auto encode = (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder();
     if (encode == nullptr) return record_cuda_error(cudaErrorNotSupported);
@@ -857,6 +882,10 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
   if (fixed + pad + 2 * tile_bytes > kLSmemBudget) return BAS_ERR_UNSUPPORTED;
   int slots = (int)((kLSmemBudget - fixed - pad) / tile_bytes);
   if (slots > kMaxStages) slots = kMaxStages;
+  if (const char* cap = std::getenv("BAS_LIST_MAX_SLOTS")) {   // tuning knob
+    const int v = std::atoi(cap);
+    if (v >= 2 && v < slots) slots = v;
+  }
   int pairs = (flags >> 12) & 7;
   if (pairs < 2 || pairs > kLIssuers || slots / pairs == 0) {
     pairs = 0;
@@ -906,6 +935,12 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
   p.bf16 = (flags & BAS_GEMM_BF16) != 0 ? 1 : 0;
   p.stall_call = -1;
   p.wait_cycles = kWaitCycles;
+#ifdef BAS_TRACE
+  p.trace = nullptr;
+  p.trace_cta = 0;
+  if (cudaMalloc(&p.trace, sizeof(long long) * kLTraceCalls * kLTraceEvents) == cudaSuccess)
+    cudaMemset(p.trace, 0, sizeof(long long) * kLTraceCalls * kLTraceEvents);
+#endif
   *out = l;
   return BAS_OK;
 }
@@ -951,6 +986,20 @@ BAS_API int bas_list_info(const bas_list* l, int* ctas, int* cluster, int* slots
   if (pairs != nullptr) *pairs = l->params.pairs;
   return BAS_OK;
 }
+
+#ifdef BAS_TRACE
+// Diagnostic build: copies the event stamps ([call][event], nanoseconds of the global timer) to the host,
+// clears them and chooses the CTA that stamps the next runs.
+BAS_API int bas_list_debug_trace(bas_list* l, long long* out, int n, int next_cta) {
+  if (l == nullptr || l->params.trace == nullptr) return 1;
+  const size_t total = (size_t)kLTraceCalls * kLTraceEvents;
+  const size_t cnt = (size_t)n < total ? (size_t)n : total;
+  cudaError_t e = cudaMemcpy(out, l->params.trace, sizeof(long long) * cnt, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) e = cudaMemset(l->params.trace, 0, sizeof(long long) * total);
+  l->params.trace_cta = next_cta;
+  return e == cudaSuccess ? 0 : 4;
+}
+#endif
 
 BAS_API void bas_list_destroy(bas_list* l) {
   if (l == nullptr) return;

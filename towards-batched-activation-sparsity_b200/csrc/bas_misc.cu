@@ -162,20 +162,23 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
 
   // ---- phase 2: one CTA ranks all blocks ----
   double* s_score = s_dyn;                              // [nb]
-  int* s_rank = (int*)(s_dyn + p.nb);                   // [nb]
+  unsigned long long* s_key = (unsigned long long*)(s_dyn + p.nb);   // [nb] ranking keys (score_key)
+  int* s_rank = (int*)(s_key + p.nb);                   // [nb]
   int* s_order = s_rank + p.nb;                         // [nb] block id at each rank (budget mode)
   for (int j = tid; j < p.nb; j += nthreads) {
     const double s = __ldcg(p.ws_scores + j);
     s_score[j] = s;
+    s_key[j] = score_key(s);
   }
   __syncthreads();
   // one thread per block counts the blocks that rank before it (about 30 k comparisons in all: the
-  // instruction issue of one SM bounds this step at roughly 0.8 us whatever the thread count)
+  // instruction issue of one SM bounds this step at roughly 0.8 us whatever the thread count).
+  // Keys are totally ordered (NaN ranks first, like torch.topk), so the ranks are a permutation.
   for (int j = tid; j < p.nb; j += nthreads) {
-    const double sj = s_score[j];
+    const unsigned long long sj = s_key[j];
     int rank = 0;
     for (int i = 0; i < p.nb; ++i) {
-      const double si = s_score[i];
+      const unsigned long long si = s_key[i];
       rank += (si > sj || (si == sj && i < j)) ? 1 : 0;
     }
     s_rank[j] = rank;
@@ -185,7 +188,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   if (tid == 0) {
     int keep = p.n_keep;
     if (p.mode == 1) {
-      // energy budget: shortest descending prefix whose sum reaches energy_keep of the total
+      // energy budget: shortest descending prefix whose sum reaches energy_keep of the total (a total
+      // that is not a number keeps every block)
       double total = 0.0;
       for (int r = 0; r < p.nb; ++r) total += s_score[s_order[r]];
       const double thresh = p.energy_keep * total;
@@ -196,6 +200,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         if (cum >= thresh) { kk = r + 1; break; }
       }
       keep = max(p.n_keep, min(p.nb, kk));
+      if (keep > p.full_above) keep = p.nb;   // too little would be skipped: run every block
     }
     s_keep = min(max(keep, 0), p.nb);
   }
@@ -217,7 +222,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     __syncthreads();
     int off = running;
     for (int w = 0; w < warp; ++w) off += s_warp_cnt[w];
-    if (kept) p.ids_out[off + __popc(m & ((1u << lane) - 1u))] = j;
+    const int pos = off + __popc(m & ((1u << lane) - 1u));
+    if (kept && pos < keep) p.ids_out[pos] = j;
     for (int w = 0; w < nthreads / 32; ++w) running += s_warp_cnt[w];
     __syncthreads();
   }
@@ -245,7 +251,7 @@ cudaError_t launch_select(const SelectParams& p, int sm_count, cudaStream_t stre
   if (p.batch > kSelMaxBatch) return cudaErrorInvalidValue;
   const int grid = (p.nb + kSelBlocksPerCta - 1) / kSelBlocksPerCta;
   const size_t phase1 = sizeof(double) * kSelBlocksPerCta * (size_t)p.batch;
-  const size_t phase2 = (sizeof(double) + 2 * sizeof(int)) * (size_t)p.nb;
+  const size_t phase2 = (2 * sizeof(double) + 2 * sizeof(int)) * (size_t)p.nb;
   const size_t smem = phase1 > phase2 ? phase1 : phase2;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);

@@ -95,7 +95,7 @@ inline size_t umma_fixed_smem(int nb) {
 // Bytes of scratch the in-kernel selection needs in the (not yet used) ring area: scores, ranks and
 // rank order of all blocks, then the per-(block, row) scores of this CTA's share of the blocks.
 inline size_t fused_select_scratch(int nb_sel, int cluster, int batch) {
-  const size_t per_block = sizeof(double) + 2 * sizeof(int);
+  const size_t per_block = 2 * sizeof(double) + 2 * sizeof(int);
   const size_t mine = (size_t)(nb_sel + cluster - 1) / cluster;
   return ((size_t)nb_sel * per_block + 15) / 16 * 16 + mine * (size_t)batch * sizeof(double);
 }
@@ -111,9 +111,10 @@ __device__ __forceinline__ int fused_select(const GemmParams& p, uint8_t* scratc
   const int nb = p.sel.nb_sel, batch = p.batch;
   const bool bf16 = (p.flags & kFlagBf16) != 0;
   double* s_score = (double*)scratch;
-  int* s_rank = (int*)(s_score + nb);
+  unsigned long long* s_key = (unsigned long long*)(s_score + nb);   // ranking keys (score_key)
+  int* s_rank = (int*)(s_key + nb);
   int* s_order = s_rank + nb;
-  double* s_pair = (double*)(scratch + ((size_t)nb * (sizeof(double) + 2 * sizeof(int)) + 15) / 16 * 16);
+  double* s_pair = (double*)(scratch + ((size_t)nb * (2 * sizeof(double) + 2 * sizeof(int)) + 15) / 16 * 16);
   const int lane = tid & 31, warp = tid >> 5;
   const int nmine = (nb > crank) ? (nb - crank + C - 1) / C : 0;
 
@@ -175,10 +176,11 @@ __device__ __forceinline__ int fused_select(const GemmParams& p, uint8_t* scratc
   cluster_sync_all();   // every CTA of the cluster now holds every score
   if (tid == 0) BAS_TRACE_SET(21, BAS_TRACE_CLOCK() - t0);   // scores exchanged
 
-  // ---- rank all blocks: four threads per block ----
-  // Scores are sums of squares or of norms: never negative, never NaN for finite inputs, so they order
-  // like their bit patterns read as unsigned integers (integer compares are far cheaper than fp64 ones).
-  const unsigned long long* s_bits = (const unsigned long long*)s_score;
+  // ---- rank all blocks: four threads per block, on the same totally ordered keys as select_kernel
+  // (integer compares are also far cheaper than fp64 ones) ----
+  for (int j = tid; j < nb; j += nthreads) s_key[j] = score_key(s_score[j]);
+  __syncthreads();
+  const unsigned long long* s_bits = s_key;
   for (int j0 = 0; j0 < nb; j0 += nthreads / 4) {
     const int j = j0 + (tid >> 2), quad = tid & 3;
     int rank = 0;
@@ -235,8 +237,8 @@ __device__ __forceinline__ int fused_select(const GemmParams& p, uint8_t* scratc
     __syncthreads();
     int off = running;
     for (int w = 0; w < warp; ++w) off += s_warp_cnt[w];
-    if (kept) {
-      const int pos = off + __popc(m & ((1u << lane) - 1u));
+    const int pos = off + __popc(m & ((1u << lane) - 1u));
+    if (kept && pos < keep) {
       s_ids[pos] = (uint16_t)j;
       if (writer && p.sel.ids_out != nullptr) p.sel.ids_out[pos] = j;
     }

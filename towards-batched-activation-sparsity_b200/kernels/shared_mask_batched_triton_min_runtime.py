@@ -108,7 +108,8 @@ def _prepacked_block_sparse_gemm_from_active_blocks_bitmap_preload(
             raise ValueError(f"total_k_blocks={total_k_blocks} does not match K={x.shape[-1]}")
         if int(prebuilt_bitmap.numel()) != nb:
             raise ValueError(f"bitmap has {prebuilt_bitmap.numel()} entries, expected {nb}")
-        _ops.gemm(x2d, packed, y2d, bitmap=prebuilt_bitmap)
+        # the id list and the byte map agree in every caller: its length sizes the launch
+        _ops.gemm(x2d, packed, y2d, bitmap=prebuilt_bitmap, k_host=min(int(active_blocks.numel()), nb))
     else:
         _ops.gemm(x2d, packed, y2d, ids=_ids32(active_blocks))
 
