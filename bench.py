@@ -10,15 +10,16 @@ W fp16 [4096, 11008] ~ N(0, 0.02^2), 172 blocks of 64 channels, batch-shared top
 three masked GEMMs B = 2, 16, 64.  The metric is the active-weight HBM bandwidth of a step:
 (34 + 62 + 83) * 64 * 4096 * 2 bytes divided by the step time.
 
-Timing: the K timed steps are CUDA-graph replays (16 steps per graph, each call on one of 16
-rotating weight copies so that a weight tile is never found in L2), bracketed by CUDA events on the
-launching stream.  Activations and masks are resident before a chain of calls starts and the calls
-say so (ids and X declared stable), so consecutive, independent calls overlap on the GPU several
-deep; each still stores its result only after the call before it has completed.  The same chains
-with fewer promises (one call deep, as the drop-in wrappers launch) are reported in per_batch beside
-the headline.  Per-batch microseconds, the dense cuBLAS baseline and the roofline figure come
-from per-batch graphs timed the same way inside this program.  With --gpus N every rank runs the
-same workload on its own GPU (independent decode replicas, no collective on the data path).
+Timing: the K timed steps run as list launches (bas_list_*: 16 steps = 48 independent calls per
+persistent launch, each call on one of 16 rotating weight copies so that a weight tile is never
+found in L2), bracketed by CUDA events on the launching stream; the region is timed five times and
+the median reported.  Activations and masks are resident before a launch.  The same calls as
+single launches - pipelined several deep (ids and X declared stable), one call deep, and with no
+promises, as the drop-in wrappers launch - are reported in per_batch beside the headline, with
+dense cuBLAS timed the same way; `speedup_vs_cublas` is the like-for-like ratio (one call at a
+time, cold L2, no promises).  With --gpus N every rank runs the same workload on its own GPU
+(independent decode replicas, no collective on the data path); the sharded layer stack, which does
+use collectives, is reported in `layer_stack` with a parity check against the unsharded product.
 """
 
 from __future__ import annotations
@@ -48,6 +49,10 @@ SPARSITY = {2: 0.803, 16: 0.638, 64: 0.520}
 SLAB_BYTES = 64 * N_OUT * 2                          # one active 64-row weight slab
 STEP_BYTES = sum(N_KEEP.values()) * SLAB_BYTES       # algorithmic bytes of one step
 ROTATE = 16                                          # weight copies cycled through (cold L2)
+# dram__bytes_read.sum + dram__bytes_write.sum of one list launch of 16 steps (ncu; the command is in the
+# summary under profiles/ named for the list kernel and this workload)
+LIST_TRAFFIC_16_STEPS = None
+TRAFFIC_NOTE = "not captured yet"
 METRIC = "block-sparse GEMM active-weight HBM bandwidth, down_proj, batch 2/16/64 (us & speedup vs cuBLAS in per_batch)"
 WORKLOAD = ("llama2-7b down_proj X[B,11008] Laplace x W[4096,11008] N(0,0.02), B in {2,16,64}, "
             "batch-shared top-k block masks 34/62/83 of 172")
@@ -94,6 +99,29 @@ def _cpu_step(w, xs) -> None:
         O.masked_linear_torch_cpu(xs[b], w, ids.numpy())
 
 
+def _cpu_config1() -> dict:
+    """The specification's CPU-runnable case: X [16, 4096] N(0,1), W [4096, 4096] N(0, 0.02), seed 0, the
+    32 of 64 blocks with the largest batch-summed L2 norm; selection + masked linear on the host cores."""
+    import torch
+    from oracle import bas_oracle as O
+
+    x = torch.from_numpy(O.make_activations(16, 4096, seed=0))
+    w = torch.from_numpy(O.make_weight(4096, 4096, seed=0))
+    def once():
+        ids = O.select_active_blocks_torch_cpu(x.reshape(16, 1, 4096), 0.5, O.SCORE_NORM)
+        return O.masked_linear_torch_cpu(x, w, ids.numpy())
+    for _ in range(3):
+        once()
+    times = []
+    for _ in range(20):
+        t0 = time.perf_counter()
+        once()
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return {"ms": round(med * 1e3, 4), "active_weight_gbs": round(32 * 64 * 4096 * 2 / med / 1e9, 2),
+            "what": "X[16,4096] x W[4096,4096], 32 of 64 blocks kept by batch-summed block L2 norm, fp16 torch CPU"}
+
+
 def cpu_baseline(max_seconds: float = 12.0, max_steps: int = 30) -> dict:
     """Time the reference's CPU path (selection + F.linear(x * blockmask, W), fp16) on all host cores."""
     import torch
@@ -112,7 +140,7 @@ def cpu_baseline(max_seconds: float = 12.0, max_steps: int = 30) -> dict:
     return {"value": STEP_BYTES / med / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
             "sample": f"{len(times)} steps of the same workload (selection + fp16 F.linear on the masked input, "
                       f"torch CPU), median {med * 1e3:.2f} ms per step",
-            "ms_per_step": med * 1e3}
+            "ms_per_step": med * 1e3, "single_masked_linear": _cpu_config1()}
 
 
 def run_reference(args) -> None:
@@ -225,25 +253,32 @@ def _graph_time_us(torch, stream, build, calls_per_graph: int, reps: int, repeat
 
 def _layer_stack(torch, dist, dev, world, rank, stream, fuse=False, allreduce="nccl") -> dict:
     """The Llama-2-7B decode-step linear stack (32 layers x 7 masked projections, B = 16, sparsity
-    0.638), column-/row-parallel over the ranks with an NCCL all-reduce after o and down: one CUDA
-    graph per step where NCCL allows capture, timed by CUDA events, max over ranks."""
+    0.638), column-/row-parallel over the ranks with the row-parallel sums by NCCL all-reduce or inside
+    the contraction kernel: one CUDA graph per step where NCCL allows capture, timed by CUDA events,
+    max over ranks.  Before timing, one step is checked against the unsharded product (fp32, first
+    layer) and the masks are compared across the ranks.  On one GPU the step is also timed as ONE
+    persistent launch over the list of its calls, with the model's dependencies and without."""
     from bas import tp
 
     stack = tp.DecodeLinearStack(32, 16, 0.638, dev, world, rank, fuse_shared_inputs=fuse, allreduce=allreduce)
-    def timed():
+    parity = stack.parity_check(layers=1)
+    if not (parity["ids_equal"] and parity["max_err"] <= 2e-3):
+        raise SystemExit(f"sharded stack disagrees with the unsharded product: {parity}")
+
+    def timed(step):
         with torch.cuda.stream(stream):
             for _ in range(3):
-                stack.step()
+                step()
         torch.cuda.synchronize()
         mode = "cuda graph"
         try:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
-                stack.step()
+                step()
             run = g.replay
         except Exception as exc:      # a collective that refuses capture: time eager launches instead
             mode = f"eager ({type(exc).__name__})"
-            run = stack.step
+            run = step
         torch.cuda.synchronize()
         reps = 10
         with torch.cuda.stream(stream):
@@ -265,24 +300,186 @@ def _layer_stack(torch, dist, dev, world, rank, stream, fuse=False, allreduce="n
             ms = float(t.item())
         return ms, mode
 
-    ms, mode = timed()
+    def gbs(ms):
+        return round(stack.active_bytes / (ms * 1e-3) / 1e9, 1)
+
+    ms, mode = timed(stack.step)
     extra = {}
-    if world == 1 and not fuse:
-        # throughput probe: the same 224 calls with every input declared stable (they are: the stack's
-        # inputs are generated ahead), i.e. no call depends on the one before it
-        stack.independent_calls = True
-        ms_ind, _ = timed()
-        stack.independent_calls = False
-        extra = {"independent_calls": {"ms_per_step": round(ms_ind, 4),
-                                       "active_weight_gbs": round(stack.active_bytes / (ms_ind * 1e-3) / 1e9, 1),
-                                       "note": "every call declares ids and X stable (a probe of the chain's throughput over "
-                                               "the seven shapes); ms_per_step above declares X stable only for k, v and up, "
-                                               "which in the model read what q / gate have already read"}}
+    if world == 1:
+        # the whole step as one persistent launch: the calls wait for one another as in the model ...
+        lst = stack.make_list(dependencies=True)
+        ms_dep, _ = timed(lst.run)
+        status = lst.read_status()
+        # ... and checked like the per-call step (the list wrote the same output buffers)
+        par_l = stack.parity_check_outputs(layers=1)
+        lst.close()
+        lst = stack.make_list(dependencies=False)
+        ms_free, _ = timed(lst.run)
+        status |= lst.read_status()
+        info = lst.info()
+        lst.close()
+        if status != 0 or not par_l["max_err"] <= 2e-3:
+            raise SystemExit(f"one-launch stack: device status {status}, parity {par_l}")
+        extra["one_launch"] = {
+            "ms_per_step": round(ms_dep, 4), "active_weight_gbs": gbs(ms_dep), "launches_per_step": 1,
+            "max_err_vs_unsharded_fp32": round(par_l["max_err"], 6), "ctas": info["ctas"],
+            "no_dependencies": {"ms_per_step": round(ms_free, 4), "active_weight_gbs": gbs(ms_free)},
+            "note": "bas_list_run: one persistent kernel walks the step's calls; every call waits for the call whose "
+                    "output its input is in the model (q/k/v <- down of the layer before, o <- v, gate/up <- o, down <- up); "
+                    "no_dependencies: the same list with no call waiting for another"}
+        if not fuse:
+            # throughput probe: the same 224 single launches with every input declared stable
+            stack.independent_calls = True
+            ms_ind, _ = timed(stack.step)
+            stack.independent_calls = False
+            extra["independent_calls"] = {"ms_per_step": round(ms_ind, 4), "active_weight_gbs": gbs(ms_ind),
+                                          "note": "single launches, every call declares ids and X stable; ms_per_step above "
+                                                  "declares X stable only for k, v and up, which read what q / gate have read"}
     stack.close()
     return {**extra, "layers": 32, "linears_per_step": len(stack.items), "batch": 16, "sparsity": 0.638,
-            "parallelism": f"tp{world}: column-parallel q/k/v/gate/up, row-parallel o/down + all-reduce",
+            "parallelism": f"tp{world}: column-parallel q/k/v/gate/up, row-parallel o/down + "
+                           + ("all-reduce" if allreduce == "nccl" else "sum inside the contraction kernel"),
             "ms_per_step": round(ms, 4), "active_weight_gb_per_step": round(stack.active_bytes / 1e9, 3),
-            "active_weight_gbs": round(stack.active_bytes / (ms * 1e-3) / 1e9, 1), "launch": mode}
+            "active_weight_gbs": gbs(ms), "launch": mode,
+            "tp_parity": {"checked": parity["checked"], "max_err": round(parity["max_err"], 6), "ids_equal": parity["ids_equal"]}}
+
+
+def _sweep_gate_up(torch, ops, abi, O, dev, stream, peaks) -> dict:
+    """The sparsity sweep of the specification on the gate/up shape: X [B, 4096] N(0,1), W [11008, 4096],
+    B in {1..64}, block sparsity 0 .. 0.95 in steps of 0.05, top-k masks by block L2 norm; per point the
+    masked GEMM as the drop-in wrappers launch it (single launches, no promises) against dense cuBLAS,
+    both on 8 rotating weight copies (cold L2).  The reference's tuner walks the same grid
+    (scripts/profile_kernel_configs.py:86-216).  Every point is also appended to
+    gpurun_out/sweep_gate_up.jsonl as it is measured."""
+    k, n, nb, rot = 4096, 11008, 64, 8
+    w = torch.from_numpy(O.make_weight(n, k, seed=3)).to(dev)
+    packed = [ops.pack_weight(w) for _ in range(rot)]
+    dense_wt = [w.t().contiguous() for _ in range(rot)]
+    log = None
+    try:
+        (ROOT / "gpurun_out").mkdir(exist_ok=True)
+        log = open(ROOT / "gpurun_out" / "sweep_gate_up.jsonl", "w")
+    except OSError:
+        log = None
+    sparsities = [round(0.05 * i, 2) for i in range(20)]
+    out = {"shape": "X[B,4096] x W[11008,4096], 64 blocks", "sparsity": sparsities, "per_batch": {},
+           "protocol": "single launches with no promises vs torch.mm, 8 rotating weight copies (cold L2), CUDA-graph replays"}
+    for b in (1, 2, 4, 8, 16, 32, 64):
+        x = torch.from_numpy(O.make_activations(b, k, seed=300 + b)).to(dev)
+        y = torch.zeros(b, n, dtype=torch.float16, device=dev)
+        yd = torch.zeros(b, n, dtype=torch.float16, device=dev)
+
+        def dense():
+            for c in range(rot):
+                torch.mm(x, dense_wt[c], out=yd)
+
+        dense_us = _graph_time_us(torch, stream, dense, rot, 8, repeats=2)
+        us_row, sp_row = [], []
+        for sp in sparsities:
+            n_keep = O.n_keep_from_density(1.0 - sp, nb)
+            ids = ops.select_topk(x, n_keep, abi.SCORE_NORM)[0].clone()
+
+            def sparse():
+                for c in range(rot):
+                    ops.gemm(x, packed[c], y, ids=ids)
+
+            us = _graph_time_us(torch, stream, sparse, rot, 8, repeats=2)
+            us_row.append(round(us, 2))
+            sp_row.append(round(dense_us / us, 3))
+            if log is not None:
+                log.write(json.dumps({"batch": b, "sparsity": sp, "active_blocks": n_keep, "us": us, "dense_cublas_us": dense_us,
+                                      "speedup": dense_us / us, "gbs": n_keep * 64 * n * 2 / us / 1e3}) + "\n")
+                log.flush()
+        first_win = next((sparsities[i] for i, v in enumerate(sp_row) if v >= 1.0), None)
+        out["per_batch"][str(b)] = {"dense_cublas_us": round(dense_us, 2), "us": us_row, "speedup_vs_cublas": sp_row,
+                                    "lowest_sparsity_faster_than_dense": first_win}
+    if log is not None:
+        log.close()
+    del packed, dense_wt
+    torch.cuda.empty_cache()
+    return out
+
+
+def _reference_triton(torch, O, dev, stream, xs, ids_by_batch) -> dict:
+    """The reference's own Triton kernels (kernels/shared_mask_batched_triton_min_runtime.py:684-733,
+    814-874, 1150-1216, 1898-1988, through its wrappers :1064-1454), JIT-compiled for this GPU from the
+    copy under baseline/_ref and timed with the protocol of per_batch.no_promises_us: the best of the
+    index-list and bitmap families with split-K 1, 2, 4, 8 per batch size."""
+    import importlib.util
+
+    path = ROOT / "baseline" / "_ref" / "kernels" / "shared_mask_batched_triton_min_runtime.py"
+    if not path.exists():
+        return {"unavailable": "baseline/_ref/kernels is not filled (python baseline/fill_ref.py)"}
+    for key, val in (("TEAL_EXP_ENABLE_SPLIT_K_1D", "0"), ("TEAL_EXP_USE_RUN_COMPRESSED_METADATA", "0"),
+                     ("TEAL_EXP_SORT_ACTIVE_BLOCKS", "0")):      # as the reference's scripts set them before importing
+        os.environ.setdefault(key, val)
+    try:
+        spec = importlib.util.spec_from_file_location("reference_triton_kernels", path)
+        ref = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref)
+    except Exception as exc:
+        return {"unavailable": f"import failed: {type(exc).__name__}: {exc}"[:200]}
+    rot = 8
+    ws = [torch.from_numpy(O.make_weight(N_OUT, K_IN, seed=0)).to(dev) for _ in range(rot)]
+    out = {}
+    for b in BATCHES:
+        x3 = xs[b].reshape(b, 1, K_IN)
+        y3 = torch.zeros(b, 1, N_OUT, dtype=torch.float16, device=dev)
+        ids = ids_by_batch[b]
+        bitmap = ref._build_active_k_bitmap(ids, NB, dev)
+        tile = dict(tile_b=16 if b <= 16 else 32, tile_n=64, tile_warps=4, tile_stages=3)
+        best, errors = None, []
+        for kind, sk in [("bitmap", 1), ("naive", 1)] + [(f, kk) for kk in (2, 4, 8) for f in ("naive", "bitmap")]:
+            def call(c, kind=kind, sk=sk):
+                if kind == "naive":
+                    ref._prepacked_block_sparse_gemm_from_active_blocks_splitk(
+                        x3, ws[c], ids, y3, cache_prefix=f"bench{c}", num_split_k=sk, **tile)
+                elif sk == 1:
+                    ref._prepacked_block_sparse_gemm_from_active_blocks_bitmap_preload(
+                        x3, ws[c], ids, y3, cache_prefix=f"bench{c}", total_k_blocks=NB, prebuilt_bitmap=bitmap)
+                else:
+                    ref._prepacked_block_sparse_gemm_from_active_blocks_bitmap_preload_splitk(
+                        x3, ws[c], ids, y3, cache_prefix=f"bench{c}", total_k_blocks=NB, prebuilt_bitmap=bitmap,
+                        num_split_k=sk, **tile)
+
+            def chain():
+                for c in range(rot):
+                    call(c)
+
+            try:
+                us = _graph_time_us(torch, stream, chain, rot, 20, repeats=2)
+            except Exception as exc:
+                errors.append(f"{kind}/K{sk}: {type(exc).__name__}"[:60])
+                torch.cuda.synchronize()
+                continue
+            if best is None or us < best[0]:
+                best = (us, kind, sk)
+        if best is None:
+            out[str(b)] = {"unavailable": "; ".join(errors)[:200]}
+        else:
+            out[str(b)] = {"us": round(best[0], 2), "family": best[1], "split_k": best[2]}
+    del ws
+    torch.cuda.empty_cache()
+    return out
+
+
+def _thesis_protocol() -> dict:
+    """The reference's own two-step kernel benchmark, both scripts unmodified against the drop-in
+    module (bas/refscripts.py): mean kernel speed-up over dense per batch size over the thesis's 55
+    per-step oracle schedules x 224 projections (one call replayed on one weight, as the thesis timed it)."""
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "scripts" / "bench_perstep_actual_kernel_speedup.py").exists():
+        return {"unavailable": "baseline/_ref/scripts is not filled (python baseline/fill_ref.py)"}
+    from bas import refscripts
+
+    try:
+        with tempfile.TemporaryDirectory() as tmp:
+            res = refscripts.run_thesis_protocol(ref_root, Path(tmp), batch_sizes=(2, 4, 8, 16, 32, 64), quiet=True)
+    except Exception as exc:
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    return {"kernel_speedup_vs_dense": {str(r["batch_size"]): round(float(r["kernel_speedup"]), 3) for r in res["rows"]},
+            "thesis_a100x": {"2": 1.948, "4": 1.945, "8": 1.761, "16": 1.602, "32": 1.405, "64": 1.203},
+            "how": "scripts/profile_kernel_configs.py then scripts/bench_perstep_actual_kernel_speedup.py, unmodified"}
 
 
 def run_gpu(args) -> None:
@@ -332,75 +529,92 @@ def run_gpu(args) -> None:
     if ops.read_status(dev) != 0:
         raise SystemExit("device status word is not clean")
 
-    counter = {"i": 0}
+    # ---- the K timed steps: list launches of up to 16 steps (48 independent calls) each ----
+    GS = 16
 
-    def one_step():
-        for b in BATCHES:
-            c = counter["i"] % ROTATE
-            counter["i"] += 1
-            ops.gemm(xs[b], packed[c], outs[b], ids=ids[b], ids_stable=True, x_stable=True, next_independent=True)
+    def step_list(n_steps):
+        calls = []
+        for i in range(n_steps):
+            for j, b in enumerate(BATCHES):
+                calls.append({"x": xs[b], "packed": packed[(i * len(BATCHES) + j) % ROTATE], "out": outs[b], "ids": ids[b]})
+        return ops.GemmList(calls, min_units=16)
 
-    # ---- the K timed steps ----
-    GS = 16                                                     # steps per captured graph
-    def build_steps(n):
-        def f():
-            for _ in range(n):
-                one_step()
-        return f
-
+    # up to 48 steps are one launch; longer runs are launches of 16 steps, the last one taking the remainder too
+    if args.steps <= 3 * GS:
+        n_full, rem = 0, args.steps
+    else:
+        n_full, rem = divmod(args.steps, GS)
+        if rem:
+            n_full, rem = n_full - 1, rem + GS
+    lists = {n: step_list(n) for n in {GS if n_full else 0, rem} - {0}}
     with torch.cuda.stream(stream):
         for _ in range(max(args.warmup, 3)):
-            one_step()
+            for l in lists.values():
+                l.run()
     torch.cuda.synchronize()
-    n_full, rem = divmod(args.steps, GS)
-    graphs = {}
-    for n in {GS if n_full else 0, rem} - {0}:
-        counter["i"] = 0
-        before = launch_count()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=stream):
-            build_steps(n)()
-        graphs[n] = (g, launch_count() - before)
-    torch.cuda.synchronize()
-    with torch.cuda.stream(stream):                              # warm the graphs themselves
-        for n, (g, _) in graphs.items():
-            g.replay()
-    torch.cuda.synchronize()
+    for l in lists.values():
+        if l.read_status() != 0:
+            raise SystemExit("list launch reported a device flag")
+    for b in BATCHES:       # the list wrote the same outputs as the guarded single calls
+        mask = torch.zeros(NB, device=dev)
+        mask[ids[b].long()] = 1
+        ref = (xs[b].float() * mask.repeat_interleave(64)) @ w.float().t()
+        err = ((outs[b].float() - ref).abs().max() / ref.abs().max()).item()
+        if not err <= 2e-3:
+            raise SystemExit(f"list launch: parity check failed at B={b}: max err ratio {err:.3e}")
 
     try:
         gpu_id = "GPU-" + str(torch.cuda.get_device_properties(dev).uuid).replace("GPU-", "")
     except AttributeError:
         gpu_id = str(local)
     sampler = ClockSampler(gpu_id)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches = 0
-    with torch.cuda.stream(stream):
-        e0.record(stream)
+
+    def region():
+        n = 0
         for _ in range(n_full):
-            graphs[GS][0].replay()
-            launches += graphs[GS][1]
+            lists[GS].run()
+            n += 1
         if rem:
-            graphs[rem][0].replay()
-            launches += graphs[rem][1]
-        e1.record(stream)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    ms_total = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+            lists[rem].run()
+            n += 1
+        return n
+
+    region_ms = []
+    launches = 0
+    for _ in range(5):                                           # median of five timed regions of K steps
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = launch_count()
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            region()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        launches = launch_count() - before
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            dist.barrier()
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        region_ms.append(ms)
+    ms_total = statistics.median(region_ms)
     ms_per_step = ms_total / args.steps
     value = world * STEP_BYTES / (ms_per_step * 1e-3) / 1e9
+    # the dominant kernel: one list launch of GS steps (or of all K when K < 16), timed alone
+    dom_steps = GS if n_full else rem
+    dom_us = _graph_time_us(torch, stream, lists[dom_steps].run, 1, 20) if rank == 0 else 0.0
+    list_info = lists[dom_steps].info()
 
     # ---- per-batch kernel time, dense cuBLAS, selection, fused chain (rank 0's GPU) ----
     per_batch = {}
     reps = 60
     for b in BATCHES:
+        lb = ops.GemmList([{"x": xs[b], "packed": packed[c], "out": outs[b], "ids": ids[b]} for c in range(ROTATE)],
+                          min_units=16)
+
         def sparse_cold(b=b):
             for c in range(ROTATE):
                 ops.gemm(xs[b], packed[c], outs[b], ids=ids[b], ids_stable=True, x_stable=True, next_independent=True)
@@ -425,6 +639,8 @@ def run_gpu(args) -> None:
         def dense_hot(b=b):
             torch.mm(xs[b], dense_wt[0], out=dense_outs[b])
 
+        us_list = _graph_time_us(torch, stream, lb.run, ROTATE, reps)
+        lb.close()
         us = _graph_time_us(torch, stream, sparse_cold, ROTATE, reps)
         us_ids = _graph_time_us(torch, stream, sparse_cold_ids_only, ROTATE, reps)
         us_plain = _graph_time_us(torch, stream, sparse_cold_plain, ROTATE, reps)
@@ -432,17 +648,22 @@ def run_gpu(args) -> None:
         hus = _graph_time_us(torch, stream, sparse_hot, 1, 200)
         hdus = _graph_time_us(torch, stream, dense_hot, 1, 200)
         bytes_b = N_KEEP[b] * SLAB_BYTES
-        gbs = bytes_b / (us * 1e-6) / 1e9
+        gbs = bytes_b / (us_list * 1e-6) / 1e9
         per_batch[str(b)] = {
             "sparsity": SPARSITY[b], "active_blocks": N_KEEP[b], "active_weight_mb": round(bytes_b / 1e6, 2),
-            "us": round(us, 3), "dense_cublas_us": round(dus, 3), "speedup_vs_cublas": round(dus / us, 3),
-            "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peaks["hbm_gbs"], 4),
+            "us": round(us_list, 3), "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peaks["hbm_gbs"], 4),
             "frac_of_8000": round(gbs / 8000.0, 4),
+            "dense_cublas_us": round(dus, 3),
+            "speedup_vs_cublas": round(dus / us_plain, 3),
+            "no_promises_us": round(us_plain, 3), "no_promises_gbs": round(bytes_b / (us_plain * 1e-6) / 1e9, 1),
             "ids_stable_only_us": round(us_ids, 3), "ids_stable_only_speedup_vs_cublas": round(dus / us_ids, 3),
-            "no_promises_us": round(us_plain, 3), "no_promises_speedup_vs_cublas": round(dus / us_plain, 3),
+            "pipelined_single_launches_us": round(us, 3),
+            "chain_throughput_vs_serial_cublas": round(dus / us_list, 3),
             "l2_resident_us": round(hus, 3), "l2_resident_dense_us": round(hdus, 3),
             "l2_resident_speedup": round(hdus / hus, 3),
-        }
+            "note": "us: per call inside one list launch of 16 independent calls (cold L2); speedup_vs_cublas: "
+                    "like for like, single launches with no promises against cuBLAS, both cold and one at a time; "
+                    "chain_throughput_vs_serial_cublas: the list's period against serialised cuBLAS calls"}
 
     # per-step online selection fused ahead of the GEMM (B = 16, energy score, keep 36 %)
     b = 16
@@ -493,6 +714,21 @@ def run_gpu(args) -> None:
                       "select_plus_gemm_overlapped_us: the two launches per step, with step i+1's selection "
                       "(BAS_SCORE_INPUTS_STABLE, alternating id buffers) scoring while step i's contraction runs"}
 
+    # ---- rank 0 at N = 1: sparsity sweep on the gate/up shape, the reference's Triton kernels on this GPU,
+    # and the reference's own two benchmark scripts against the drop-in ----
+    sweep = ref_triton = thesis = None
+    if world == 1 and not args.quick:
+        sweep = _sweep_gate_up(torch, ops, abi, O, dev, stream, peaks)
+        ref_triton = _reference_triton(torch, O, dev, stream, xs, ids)
+        for bb in BATCHES:
+            r = ref_triton.get(str(bb)) if isinstance(ref_triton, dict) else None
+            if isinstance(r, dict) and "us" in r:
+                per_batch[str(bb)]["reference_triton_us"] = r["us"]
+                per_batch[str(bb)]["reference_triton_variant"] = f"{r['family']}, split-K {r['split_k']}"
+                per_batch[str(bb)]["speedup_vs_reference_triton"] = round(r["us"] / per_batch[str(bb)]["no_promises_us"], 3)
+        thesis = _thesis_protocol()
+        torch.cuda.empty_cache()
+
     # ---- the sharded decode-step linear stack (all ranks take part) ----
     try:
         layer_stack = _layer_stack(torch, dist, dev, world, rank, stream)
@@ -500,8 +736,8 @@ def run_gpu(args) -> None:
         # the same step with q/k/v and gate/up stacked into one masked GEMM each (they share their
         # input and mask in the model; here the q and gate inputs and masks stand for the group)
         stacked = _layer_stack(torch, dist, dev, world, rank, stream, fuse=True)
-        keys = ("linears_per_step", "ms_per_step", "active_weight_gbs", "launch")
-        layer_stack["stacked_qkv_gateup"] = {k: stacked[k] for k in keys}
+        keys = ("linears_per_step", "ms_per_step", "active_weight_gbs", "launch", "tp_parity", "one_launch")
+        layer_stack["stacked_qkv_gateup"] = {k: stacked[k] for k in keys if k in stacked}
         if world > 1:
             # the same two steps with o/down summed over the ranks inside the contraction kernel
             # (fp32 partials read from the peers over NVLink) instead of by an NCCL all-reduce
@@ -509,7 +745,7 @@ def run_gpu(args) -> None:
                 torch.cuda.empty_cache()
                 try:
                     r = _layer_stack(torch, dist, dev, world, rank, stream, fuse=fuse, allreduce="in_kernel")
-                    layer_stack[name] = {k: r[k] for k in keys}
+                    layer_stack[name] = {k: r[k] for k in keys if k in r}
                 except Exception as exc:
                     layer_stack[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     except Exception as exc:
@@ -592,39 +828,38 @@ def run_gpu(args) -> None:
     clocks = sampler.stop()
 
     if rank == 0:
-        dom = per_batch["64"]
+        list_bytes = dom_steps * STEP_BYTES
+        achieved = list_bytes / (dom_us * 1e-6) / 1e9
+        one_deep = {str(bb): {"us": per_batch[str(bb)]["no_promises_us"], "achieved": per_batch[str(bb)]["no_promises_gbs"],
+                              "frac": round(per_batch[str(bb)]["no_promises_gbs"] / peaks["hbm_gbs"], 4)} for bb in BATCHES}
         roofline = {
-            "bound": "hbm", "kernel": "umma_colsplit_kernel<64, false, false> (B=64, 83 of 172 blocks)",
-            "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
-            "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
-            "algorithmic_bytes_per_launch": N_KEEP[64] * SLAB_BYTES, "traffic": None,
-            "one_call_deep": {"achieved": round(N_KEEP[64] * SLAB_BYTES / (dom["ids_stable_only_us"] * 1e-6) / 1e9, 1),
-                              "frac": round(N_KEEP[64] * SLAB_BYTES / (dom["ids_stable_only_us"] * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
-                              "note": "the same call when X may be the previous kernel's output (launches do not "
-                                      "overlap beyond a ring-full of weights): the 128-CTA cluster grid of "
-                                      "profiles/umma_colsplit_down_proj_b64.md"},
-            "duration": "timed region / launches: the chain's launches overlap (32 CTAs each, about four calls "
-                        "resident), so this is the period of the chain, not the lifetime of one launch",
+            "bound": "hbm", "kernel": f"umma_list_kernel<64> over {dom_steps} steps = {dom_steps * len(BATCHES)} calls "
+                                      f"(B = 2/16/64, 34/62/83 of 172 blocks), {list_info['ctas']} CTAs",
+            "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peaks["source"] + " (stream copy, burst)",
+            "algorithmic_bytes_per_launch": list_bytes, "launch_us": round(dom_us, 2),
+            "duration": "CUDA events around replays of the one launch, on the launching stream",
+            # dram__bytes_read.sum + dram__bytes_write.sum of one such launch (ncu, 16 steps), see TRAFFIC_NOTE
+            "traffic": LIST_TRAFFIC_16_STEPS * dom_steps // 16 if LIST_TRAFFIC_16_STEPS else None,
+            "traffic_note": TRAFFIC_NOTE,
+            "one_call_deep_all": one_deep,
+            "one_call_deep_note": "single launches with no promises (what the drop-in wrappers run), cold L2",
         }
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
-        # profiles/umma_colsplit_pipelined_down_proj_b64.md (same workload and grid, one launch)
-        roofline["traffic"] = 44_305_920
         cpu = cpu_baseline() if world == 1 else None
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD,
-                       "step": "3 masked GEMMs (B=2,16,64); activations and masks are resident before the chain of "
-                               "calls starts and declared so (BAS_GEMM_IDS_STABLE | BAS_GEMM_X_STABLE | BAS_GEMM_NEXT_INDEPENDENT): independent "
-                               "calls of a stream pipeline several deep, each waiting for its predecessor only "
-                               "before it stores.  per_batch also has the same chains with only the masks declared "
-                               "stable (ids_stable_only_*) and with nothing declared, as the drop-in wrappers "
-                               "launch (no_promises_*): one call deep",
+                       "step": "3 masked GEMMs (B=2,16,64); activations and masks are resident before the launch; the K steps "
+                               "run as list launches of up to 16 steps (bas_list_run: one persistent kernel per launch walks "
+                               "48 independent calls).  per_batch has the same calls as single launches with fewer promises",
                        "l2": f"cold: every call reads one of {ROTATE} rotating weight copies (1.4 GB in rotation)",
                        "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
-                       "timing": "CUDA-graph replays of 16 steps, CUDA events on the launch stream, max over ranks"},
-            "per_batch": per_batch, "online_selection": online, "layer_stack": layer_stack, "roofline": roofline, "cpu_baseline": cpu,
+                       "timing": "CUDA events on the launch stream around the K steps, median of 5 regions, max over ranks",
+                       "region_ms": [round(v, 4) for v in region_ms]},
+            "per_batch": per_batch, "online_selection": online, "layer_stack": layer_stack, "sweep_gate_up": sweep,
+            "reference_triton": ref_triton, "thesis_protocol": thesis, "roofline": roofline, "cpu_baseline": cpu,
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
         _emit(line)
@@ -661,16 +896,47 @@ def run_profile_case(batch: int, family: int = 0, pipelined: bool = False) -> No
     print(f"profile case B={batch} family={family} pipelined={pipelined}: 8 gemm launches, status {ops.read_status(dev)}")
 
 
+def run_profile_list(steps: int) -> None:
+    """Three eager list launches of `steps` benchmark steps each (16 rotating weight copies, 1.4 GB):
+    the case that profiler captures of the list kernel are taken on."""
+    import torch
+
+    from bas import abi, ops
+    from oracle import bas_oracle as O
+
+    dev = torch.device("cuda", 0)
+    w = torch.from_numpy(O.make_weight(N_OUT, K_IN, seed=0)).to(dev)
+    packed = [ops.pack_weight(w) for _ in range(ROTATE)]
+    xs = {b: torch.from_numpy(O.make_activations(b, K_IN, seed=1000 + b, dist="laplace")).to(dev) for b in BATCHES}
+    ids = {b: ops.select_topk(xs[b], N_KEEP[b], abi.SCORE_NORM)[0].clone() for b in BATCHES}
+    outs = {b: torch.zeros(b, N_OUT, dtype=torch.float16, device=dev) for b in BATCHES}
+    calls = []
+    for i in range(steps):
+        for j, b in enumerate(BATCHES):
+            calls.append({"x": xs[b], "packed": packed[(i * len(BATCHES) + j) % ROTATE], "out": outs[b], "ids": ids[b]})
+    lst = ops.GemmList(calls, min_units=16)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        lst.run()
+    torch.cuda.synchronize()
+    print(f"profile list: 3 launches of {steps} steps ({len(calls)} calls, {steps * STEP_BYTES} algorithmic bytes each), "
+          f"{lst.info()}, status {lst.read_status()}")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--quick", action="store_true",
+                    help="skip the sparsity sweep, the reference's Triton kernels and the reference's scripts")
     ap.add_argument("--profile-case", type=int, default=0, metavar="B",
                     help="run only a few eager launches at batch B (for profiler captures) and exit")
     ap.add_argument("--profile-family", type=int, default=0, choices=[0, 1, 2],
                     help="kernel family of the profile case: 0 default, 1 CUDA-core kernel (batch <= 8), 2 tcgen05")
+    ap.add_argument("--profile-list", type=int, default=0, metavar="STEPS",
+                    help="run only three eager list launches of STEPS benchmark steps (for profiler captures) and exit")
     ap.add_argument("--profile-pipelined", action="store_true",
                     help="profile case: masks fixed ahead, calls declare ids and X stable (the benchmark's chains)")
     args = ap.parse_args()
@@ -680,7 +946,9 @@ def main() -> None:
     sys.stdout.flush()
     _STDOUT_FD = os.dup(1)
     os.dup2(2, 1)
-    if args.profile_case:
+    if args.profile_list:
+        run_profile_list(args.profile_list)
+    elif args.profile_case:
         run_profile_case(args.profile_case, args.profile_family, args.profile_pipelined)
     elif args.impl == "reference":
         run_reference(args)

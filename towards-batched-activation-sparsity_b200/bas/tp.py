@@ -152,6 +152,8 @@ class DecodeLinearStack:
         # kernel before them and could not)
         self.independent_calls = False
         self.items = []
+        self.item_meta = []      # per item: (layer, [index of each stacked projection in LLAMA2_7B_LAYER])
+        self.seed = seed
         self._shared = {}
         gen = torch.Generator(device=device)
         self.active_bytes = 0
@@ -173,6 +175,7 @@ class DecodeLinearStack:
 
         for li in range(layers):
             pending = {}     # fused group name -> [spec, weights]
+            pending_si = {}
             for si, spec in enumerate(LLAMA2_7B_LAYER):
                 gen.manual_seed(seed * 1_000_003 + li * 16 + si)
                 w = (torch.randn(spec.n, spec.k, generator=gen, device=device, dtype=torch.float32) * 0.02).half()
@@ -181,16 +184,19 @@ class DecodeLinearStack:
                     members = dict(FUSED_GROUPS)[group_name]
                     entry = pending.setdefault(group_name, [spec, []])
                     entry[1].append(w)
+                    pending_si.setdefault(group_name, []).append(si)
                     if len(entry[1]) < len(members):
                         continue
                     first, ws = entry
                     spec = LinearSpec(group_name, sum(t.shape[0] for t in ws), first.k, "column", first.dist)
                     x, bitmap, n_keep = shared_input(first)
                     lin = ShardedLinear(spec, ws, world, rank)
+                    self.item_meta.append((li, list(pending_si[group_name])))
                     del ws, entry[1][:]
                 else:
                     x, bitmap, n_keep = shared_input(spec)
                     lin = ShardedLinear(spec, w, world, rank)
+                    self.item_meta.append((li, [si]))
                 del w
                 out = torch.zeros(batch, lin.n_local, dtype=torch.float16, device=device)
                 self.items.append((lin, x, bitmap, out, n_keep))
@@ -202,6 +208,57 @@ class DecodeLinearStack:
         if self.exchange is not None:
             self.exchange.close()
             self.exchange = None
+
+    def parity_check(self, layers: int = 1) -> dict:
+        """Run one step and compare this rank's outputs of the first ``layers`` layers with the
+        unsharded product, computed here in fp32 from the regenerated full weights (the single-GPU
+        result is the oracle of the sharded one): a column-parallel output against its column range, a
+        row-parallel output - after the sum over ranks - against the whole product.  Also checks that
+        every rank holds the same masks (a hash of every byte map, gathered over the group).
+        Returns ``{"checked", "max_err", "ids_equal"}`` with the maximum taken over the ranks; collective."""
+        self.step()
+        return self.parity_check_outputs(layers)
+
+    def parity_check_outputs(self, layers: int = 1) -> dict:
+        """The comparison of :meth:`parity_check` on whatever the output buffers hold now."""
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.synchronize()
+        dev = self.items[0][1].device
+        gen = torch.Generator(device=dev)
+        max_err, checked = 0.0, 0
+        for (lin, x, bitmap, out, _), (li, sis) in zip(self.items, self.item_meta):
+            if li >= layers:
+                continue
+            mask = bitmap.to(torch.float32).repeat_interleave(BLOCK_K)[: x.shape[1]]
+            xm = x.float() * mask
+            parts = []
+            for si, (a, b) in zip(sis, lin.part_bounds if lin.spec.parallel == "column" else [(0, lin.spec.n)]):
+                spec = LLAMA2_7B_LAYER[si]
+                gen.manual_seed(self.seed * 1_000_003 + li * 16 + si)
+                w = (torch.randn(spec.n, spec.k, generator=gen, device=dev, dtype=torch.float32) * 0.02).half()
+                parts.append((xm @ w.float().t())[:, a:b])
+                del w
+            ref = torch.cat(parts, dim=1)
+            err = float((out.float() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+            max_err = max(max_err, err)
+            checked += 1
+        # same masks everywhere: position-weighted sum and population of every byte map
+        sig = []
+        for name in sorted(self._shared):
+            bm = self._shared[name][1].to(torch.int64)
+            sig += [int((bm * torch.arange(1, bm.numel() + 1, device=bm.device)).sum()), int(bm.sum())]
+        ids_equal = True
+        if self.world > 1:
+            mine = torch.tensor(sig, dtype=torch.int64, device=dev)
+            gathered = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(gathered, mine, group=self.group)
+            ids_equal = all(bool(torch.equal(g, gathered[0])) for g in gathered)
+            t = torch.tensor([max_err], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            max_err = float(t.item())
+        return {"checked": checked, "max_err": max_err, "ids_equal": bool(ids_equal)}
 
     # what each projection's input is the output of, in the model (attention itself is not part of
     # the stack: o reads what follows v)

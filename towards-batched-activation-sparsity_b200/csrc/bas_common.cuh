@@ -136,6 +136,13 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu_u32(const unsigned int* p
 __device__ __forceinline__ void red_release_gpu_add_u32(unsigned int* p, unsigned int v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Arrival counter in shared memory: orders, at CTA scope, what the arriving thread wrote (and
+// observed) before against what the thread that reads the count does afterwards.
+__device__ __forceinline__ unsigned int atom_add_acq_rel_cta_shared_u32(unsigned int* p, unsigned int v) {
+  unsigned int old;
+  asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(p)), "r"(v) : "memory");
+  return old;
+}
 // Shared-memory word one warp publishes to the other warps of its CTA.
 __device__ __forceinline__ void st_release_cta_shared_u32(unsigned int* p, unsigned int v) {
   asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");

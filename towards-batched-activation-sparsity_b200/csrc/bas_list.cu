@@ -75,7 +75,7 @@ struct alignas(128) ListCallDev {
   int ranges;                  // clusters that take part in this call
   int range_off;               // the first of them (the others follow, modulo the cluster count)
   int dep;                     // call whose completion X waits for, or -1
-  unsigned int dep_contrib;    // warps that report the completion of call `dep` (eight per CTA taking part)
+  unsigned int dep_contrib;    // CTAs that report the completion of call `dep`
   int pad[5];
 };
 static_assert(sizeof(ListCallDev) == 256, "call descriptor layout");
@@ -116,6 +116,8 @@ struct ListSmemHeader {
   uint32_t tmem_base;
   int abort_flag;
   unsigned int calls_staged;   // records [0, calls_staged) are valid
+  unsigned int epi_arrived;    // epilogue warps that have finished their part of a call (eight per call)
+  unsigned int dep_seen;       // 1 + the call whose completion copy warp 0 has seen last (0: none yet)
   unsigned int pad;
 };
 
@@ -224,6 +226,8 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     }
     hdr->abort_flag = 0;
     hdr->calls_staged = 0u;
+    hdr->epi_arrived = 0u;
+    hdr->dep_seen = 0u;
     fence_barrier_init();
   }
   if (warp == kLEpiWarp0) {
@@ -269,13 +273,26 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         const ListCallDev* cd = p.calls + dcall;
         const int dep = __ldg(&cd->dep);
         if (!force && dep >= 0 && dep != dep_ok) {
+          // Copy warp 0 polls the counter in global memory and tells the other copy warps through a
+          // word in shared memory (one reader per CTA on the counter's cache line, not four).
           const unsigned int target = (epoch + 1u) * __ldg(&cd->dep_contrib);
           const bool stalled = dcall == p.stall_call;
-          bool ready = !stalled && (int)(ld_acquire_gpu_u32(p.done + dep) - target) >= 0;
+          unsigned int polls = 0u;
+          auto is_ready = [&]() -> bool {
+            if (stalled) return false;
+            if (warp != 0) {
+              if (ld_acquire_cta_shared_u32(&hdr->dep_seen) == (unsigned int)dep + 1u) return true;
+              if ((++polls & 7u) != 1u) return false;   // warp 0 may be waiting for another call: look for oneself now and then
+            }
+            if ((int)(ld_acquire_gpu_u32(p.done + dep) - target) < 0) return false;
+            if (warp == 0) st_release_cta_shared_u32(&hdr->dep_seen, (unsigned int)dep + 1u);
+            return true;
+          };
+          bool ready = is_ready();
           if (!ready && block) {
             const long long t_start = clock64();
             while (true) {
-              ready = !stalled && (int)(ld_acquire_gpu_u32(p.done + dep) - target) >= 0;
+              ready = is_ready();
               if (ready) break;
               if (*abort_flag != 0 || clock64() - t_start > limit) {
                 ok = false;
@@ -641,15 +658,17 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         if (t0mod >= P) t0mod -= P;
       }
       if (!ok) break;
-      // This CTA's part of call c is in global memory: report it.  Every warp adds one to the call's
-      // counter with release semantics at GPU scope; that orders the stores of the warp's other lanes
-      // too (they precede it through the warp barrier).  Nothing blocks, so a warp that gave up cannot
-      // strand the others, and no heavier fence is needed: the readers acquire the counter.
+      // This CTA's part of call c is in global memory: report it, once per CTA.  Every warp arrives on a
+      // counter in shared memory (release at CTA scope, after its lanes' stores, which precede the
+      // arrival through the warp barrier); the last of the eight adds one to the call's counter in
+      // global memory with release semantics at GPU scope, which covers the other warps' stores as well
+      // (they happen before it).  Nothing blocks, so a warp that gave up cannot strand the others, and
+      // no separate fence is needed: the readers acquire the counter.
       __syncwarp();
       if (et == 0) BAS_LTRACE(c, 6);
-      if (lane == 0) {
+      if (lane == 0 && (atom_add_acq_rel_cta_shared_u32(&hdr->epi_arrived, 1u) & 7u) == 7u) {
         red_release_gpu_add_u32(p.done + c, 1u);
-        if (et == 0) BAS_LTRACE(c, 7);
+        BAS_LTRACE(c, 7);
       }
     }
     if (!ok) {
@@ -860,7 +879,7 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
     d.range_off = (ranges < n_clusters) ? off : 0;
     if (ranges < n_clusters) off = (off + ranges) % n_clusters;
     d.dep = a.depends_on;
-    d.dep_contrib = a.depends_on >= 0 ? (unsigned int)(host[(size_t)a.depends_on].ranges * cluster * (kLEpiThreads / 32)) : 0u;
+    d.dep_contrib = a.depends_on >= 0 ? (unsigned int)(host[(size_t)a.depends_on].ranges * cluster) : 0u;
     // X[batch, K]: inner dimension K, box {64 channels, bpad rows}, 128-byte swizzle, zeros out of range
     auto encode = (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder();
     if (encode == nullptr) return record_cuda_error(cudaErrorNotSupported);
