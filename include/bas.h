@@ -65,6 +65,11 @@ typedef enum bas_score_kind {
 BAS_API const char* bas_status_string(int status);
 /* cudaError_t of the last failing CUDA call made by this library on the calling thread. */
 BAS_API int bas_last_cuda_error(void);
+/* Bound of the kernels' waits (barriers inside a CTA, counters between CTAs, words from other ranks)
+ * for launches made from now on, process-wide: default about one second, accepted up to 10 s.  A
+ * wait that runs out sets BAS_DEV_WAIT_EXPIRED and the kernel returns.  Tests shorten it to see that
+ * path; a serving host may want it below its own watchdog. */
+BAS_API int bas_set_wait_ms(double wait_ms);
 /* Number of kernels this library has launched from this process (all threads). */
 BAS_API unsigned long long bas_launch_count(void);
 

@@ -91,6 +91,38 @@ def main() -> None:
         if not d <= 4e-3:       # the NCCL path rounds every rank's partial to fp16 first
             failures.append(("stack", d))
     group.close()
+    # A rank that stays away: every rank but rank 0 leaves out one call (between steps, nothing of its
+    # own in flight).  Rank 0's kernel sends its words, polls for the others' with a bound of a few
+    # milliseconds, gives up, reports BAS_DEV_WAIT_EXPIRED through the status word and returns: an error
+    # code, not a hang.  The group's call counters are out of step afterwards, so it is destroyed.
+    from bas import abi
+    late = ops.ExchangeGroup(dev, 16, 4096)
+    x_h, w_h = O.make_activations(16, 1024, seed=900), O.make_weight(4096, 1024, seed=901)
+    b0, b1 = tp.row_shard_blocks(1024, world, rank)
+    x = torch.from_numpy(x_h).to(dev)[:, b0 * 64:b1 * 64]
+    packed = ops.pack_weight(torch.from_numpy(np.ascontiguousarray(w_h[:, b0 * 64:b1 * 64])).to(dev))
+    ids = torch.arange(b1 - b0, dtype=torch.int32, device=dev)
+    out = torch.full((16, 4096), float("nan"), dtype=torch.float16, device=dev)
+    ops.gemm(x, packed, out, ids=ids, tp=late)                    # everybody: a complete call
+    torch.cuda.synchronize()
+    err = O.max_err_ratio(out.float().cpu().numpy(), O.masked_gemm(x_h, w_h, np.arange(16, dtype=np.int32)))
+    if ops.read_status(dev) != 0 or not err <= TOL:
+        failures.append(("late group, first call", err))
+    dist.barrier()
+    if rank == 0:
+        abi.check(abi.lib.bas_set_wait_ms(5.0), "bas_set_wait_ms")
+        out.fill_(float("nan"))
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        ops.gemm(x, packed, out, ids=ids, tp=late)                # the others never make this call
+        t1.record()
+        torch.cuda.synchronize()
+        status = ops.read_status(dev)
+        abi.check(abi.lib.bas_set_wait_ms(1000.0), "bas_set_wait_ms")
+        if not (status & abi.DEV_WAIT_EXPIRED) or t0.elapsed_time(t1) > 2000.0 or not bool(torch.isnan(out).all()):
+            failures.append(("expiry", status, t0.elapsed_time(t1), int(torch.isnan(out).sum())))
+    dist.barrier()
+    late.close()
     flag = torch.tensor([len(failures)], device=dev)
     dist.all_reduce(flag)
     if rank == 0:

@@ -62,6 +62,7 @@ _SIGNATURES = {
     "bas_status_string": (C.c_char_p, [_i]),
     "bas_last_cuda_error": (_i, []),
     "bas_launch_count": (C.c_ulonglong, []),
+    "bas_set_wait_ms": (_i, [C.c_double]),
     "bas_packed_weight_bytes": (_sz, [_i, _i]),
     "bas_pack_weight": (_i, [_vp, _i, _i, _i64, _vp, _vp]),
     "bas_gemm_workspace_bytes": (_sz, [_i, _i]),

@@ -17,6 +17,9 @@ static long long* g_trace_dev = nullptr;   // diagnostic build only
 static std::atomic<unsigned long long> g_launches{0};
 static thread_local int g_last_cuda_error = 0;
 
+static std::atomic<long long> g_wait_cycles{kWaitCycles};
+long long wait_cycles_now() { return g_wait_cycles.load(std::memory_order_relaxed); }
+
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 bool pdl_enabled() {
@@ -94,6 +97,12 @@ const char* bas_status_string(int status) {
 }
 
 int bas_last_cuda_error(void) { return g_last_cuda_error; }
+
+int bas_set_wait_ms(double wait_ms) {
+  if (!(wait_ms > 0.0) || wait_ms > 10000.0) return BAS_ERR_INVALID_ARGUMENT;
+  g_wait_cycles.store((long long)(wait_ms * 2.0e6), std::memory_order_relaxed);   // clock64 ticks at about 2 GHz
+  return BAS_OK;
+}
 
 unsigned long long bas_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -263,6 +272,7 @@ static int gemm_impl(const bas_tp* tp, const FusedSelect* sel, const void* x_dev
   p.ldy = (long long)ldy;
   p.flags = flags;
   p.status = (unsigned int*)ws_dev;
+  p.wait_cycles = wait_cycles_now();
   p.sel = FusedSelect{};
   if (sel != nullptr) {
     p.sel = *sel;

@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
         const int total = __reduce_add_sync(0xffffffffu, have ? wbytes + B * xbytes : 0);
         bool ok = true;
         if (lane == 0) {
-          if (g >= S) ok = mbar_wait(&hdr->empty[s], ph, abort_flag);
+          if (g >= S) ok = mbar_wait_for(&hdr->empty[s], ph, abort_flag, p.wait_cycles);
           if (ok) mbar_arrive_expect_tx(&hdr->full[s], total);
         }
         if (!__shfl_sync(0xffffffffu, ok, 0)) {
@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
       }
     }
   } else {
-    bool ok = __all_sync(0xffffffffu, mbar_wait(&hdr->ids_ready, 0, abort_flag));
+    bool ok = __all_sync(0xffffffffu, mbar_wait_for(&hdr->ids_ready, 0, abort_flag, p.wait_cycles));
     const int k_act = ok ? hdr->k_act : 0;
     const int M = n_sub * k_act;
     const int NG = (M + G - 1) / G;
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
       int s = 0, fph = 0;
       for (int g = 0; g < NG && ok; ++g) {
         // the verdict is made warp-uniform so that the warp-level primitives below stay converged
-        if (!__all_sync(0xffffffffu, mbar_wait(&hdr->full[s], fph, abort_flag))) {
+        if (!__all_sync(0xffffffffu, mbar_wait_for(&hdr->full[s], fph, abort_flag, p.wait_cycles))) {
           ok = false;
           break;
         }
@@ -229,8 +229,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
           if (pos == 0 || i == 0) {
             // xready is arrived by the converter after it has seen the slot's copies land; a slot that
             // straddles two sub-tiles is waited for again, which returns at once.
-            if (!__all_sync(0xffffffffu, mbar_wait(&hdr->xready[s], fph, abort_flag) &&
-                                             mbar_wait(&hdr->full[s], fph, abort_flag))) {
+            if (!__all_sync(0xffffffffu, mbar_wait_for(&hdr->xready[s], fph, abort_flag, p.wait_cycles) &&
+                                             mbar_wait_for(&hdr->full[s], fph, abort_flag, p.wait_cycles))) {
               ok = false;
               break;
             }
@@ -305,7 +305,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colsplit_kernel(const Ge
   if (hdr->abort_flag != 0 && tid == 0) {
     // Gave up somewhere: do not leave while bulk copies may still be landing in this CTA's memory.
     int zero = 0;
-    for (int g = max(0, armed - S); g < armed; ++g) (void)mbar_wait(&hdr->full[g % S], (g / S) & 1, &zero);
+    for (int g = max(0, armed - S); g < armed; ++g) (void)mbar_wait_for(&hdr->full[g % S], (g / S) & 1, &zero, p.wait_cycles);
   }
 }
 

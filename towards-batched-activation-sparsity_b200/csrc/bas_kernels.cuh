@@ -62,6 +62,7 @@ struct GemmParams {
   long long ldy;
   int flags;                // kFlag* bits
   unsigned int* status;     // workspace: status word
+  long long wait_cycles;    // bound of every wait of the kernel (bas_set_wait_ms)
   TpExchange tp;            // row-parallel sum over ranks (world 0 = off)
   FusedSelect sel;          // mask selection inside the kernel (mode 0 = off)
 #ifdef BAS_TRACE
@@ -138,6 +139,8 @@ struct SelectParams {
 cudaError_t launch_select(const SelectParams& p, int sm_count, cudaStream_t stream);
 
 void count_launch(int n = 1);
+// Bound, in clock64 ticks, that launches take for their waits (about one second unless bas_set_wait_ms changed it).
+long long wait_cycles_now();
 // Remembers a failed CUDA call for bas_last_cuda_error() on this thread; returns BAS_ERR_CUDA.
 int record_cuda_error(cudaError_t e);
 // cuTensorMapEncodeTiled of the loaded driver as an untyped pointer (null if unavailable).

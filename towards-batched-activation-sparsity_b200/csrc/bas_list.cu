@@ -953,7 +953,7 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
   p.nb_max = nb_max;
   p.bf16 = (flags & BAS_GEMM_BF16) != 0 ? 1 : 0;
   p.stall_call = -1;
-  p.wait_cycles = kWaitCycles;
+  p.wait_cycles = wait_cycles_now();
 #ifdef BAS_TRACE
   p.trace = nullptr;
   p.trace_cta = 0;

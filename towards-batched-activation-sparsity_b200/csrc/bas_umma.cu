@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       pdl_launch_dependents();
     } else {
       // ordered after warp 0's wait for the previous kernel by the barrier
-      if (__all_sync(0xffffffffu, mbar_wait(&hdr->ids_ready, 0, abort_flag))) k_act = hdr->k_act;
+      if (__all_sync(0xffffffffu, mbar_wait_for(&hdr->ids_ready, 0, abort_flag, p.wait_cycles))) k_act = hdr->k_act;
     }
     const int k_mine = (k_act > rank) ? (k_act - rank + C - 1) / C : 0;
     const int M = n_sub * k_mine;                // tiles of this CTA: sub-tile major, active block minor
@@ -438,7 +438,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         const int total = __reduce_add_sync(0xffffffffu, have ? wbytes + kXTileBytes : 0);
         bool ok = true;
         if (lane == 0) {
-          if (lap > 0) ok = mbar_wait(&hdr->empty[s], (lap - 1) & 1, abort_flag);
+          if (lap > 0) ok = mbar_wait_for(&hdr->empty[s], (lap - 1) & 1, abort_flag, p.wait_cycles);
           if (ok) mbar_arrive_expect_tx(&hdr->full[s], total);
         }
         if (!__shfl_sync(0xffffffffu, ok, 0)) {
@@ -471,7 +471,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       }
     }
   } else {
-    bool ok = __all_sync(0xffffffffu, mbar_wait(&hdr->ids_ready, 0, abort_flag));
+    bool ok = __all_sync(0xffffffffu, mbar_wait_for(&hdr->ids_ready, 0, abort_flag, p.wait_cycles));
     k_act = hdr->k_act;
     const int k_mine = (ok && k_act > rank) ? (k_act - rank + C - 1) / C : 0;
     const int M = n_sub * k_mine;
@@ -508,7 +508,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             if (w == 0) BAS_TRACE_SET(16, BAS_TRACE_CLOCK() - hdr->t0);   // issuer 0: last MMA of the sub-tile issued
             if (multi ? any_mma : !fresh) umma_commit(&hdr->acc_full);
             else mbar_arrive(&hdr->acc_full);
-            if (!multi && cur_sub + 1 < n_sub && !mbar_wait(&hdr->acc_empty, cur_sub & 1, abort_flag)) return false;
+            if (!multi && cur_sub + 1 < n_sub && !mbar_wait_for(&hdr->acc_empty, cur_sub & 1, abort_flag, p.wait_cycles)) return false;
             ++cur_sub;
             fresh = true;
           }
@@ -517,7 +517,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         int s = w % S, fph = (w / S) & 1;
         for (int g = w; g < NG && ok; g += NI) {
           [[maybe_unused]] const long long tr0 = BAS_TRACE_CLOCK();
-          if (!mbar_wait(&hdr->full[s], fph, abort_flag)) {
+          if (!mbar_wait_for(&hdr->full[s], fph, abort_flag, p.wait_cycles)) {
             ok = false;
             break;
           }
@@ -611,7 +611,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           const int wsub = min(TW, width - sub * TW);
           if (k_mine > 0 && (!multi || sub == 0)) {
             // warp-uniform verdict: tcgen05.ld below needs the whole warp
-            if (!__all_sync(0xffffffffu, mbar_wait(&hdr->acc_full, multi ? 0 : (sub & 1), abort_flag))) {
+            if (!__all_sync(0xffffffffu, mbar_wait_for(&hdr->acc_full, multi ? 0 : (sub & 1), abort_flag, p.wait_cycles))) {
               ok = false;
               break;
             }
@@ -820,7 +820,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           for (int q = 0; q < kTpMaxRanks; ++q)
             if (q < p.tp.world) {   // rank order
               while ((unsigned int)(words[q] >> 32) != tp_epoch || (unsigned int)(words2[q] >> 32) != tp_epoch) {
-                if (clock64() - t_start > kWaitCycles) {
+                if (clock64() - t_start > p.wait_cycles) {
                   good = false;
                   break;
                 }
@@ -857,7 +857,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     int zero = 0;
     const int per_lap = S / P;   // this warp's groups in one trip round the ring
     for (int i = 0, g = armed_next - P; i < min(armed_cnt, per_lap) && g >= 0; ++i, g -= P)
-      (void)mbar_wait(&hdr->full[g % S], (g / S) & 1, &zero);
+      (void)mbar_wait_for(&hdr->full[g % S], (g / S) & 1, &zero, p.wait_cycles);
   }
   if (warp == kEpiWarp0) {
     tc_fence_after_sync();
