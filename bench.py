@@ -51,8 +51,9 @@ STEP_BYTES = sum(N_KEEP.values()) * SLAB_BYTES       # algorithmic bytes of one 
 ROTATE = 16                                          # weight copies cycled through (cold L2)
 # dram__bytes_read.sum + dram__bytes_write.sum of one list launch of 16 steps (ncu; the command is in the
 # summary under profiles/ named for the list kernel and this workload)
-LIST_TRAFFIC_16_STEPS = None
-TRAFFIC_NOTE = "not captured yet"
+LIST_TRAFFIC_16_STEPS = 1_511_690_000
+TRAFFIC_NOTE = ("ncu capture of one 16-step launch (python bench.py --profile-list 16), scaled by the steps of the timed launch: "
+                "traffic grows in proportion to the calls walked")
 METRIC = "block-sparse GEMM active-weight HBM bandwidth, down_proj, batch 2/16/64 (us & speedup vs cuBLAS in per_batch)"
 WORKLOAD = ("llama2-7b down_proj X[B,11008] Laplace x W[4096,11008] N(0,0.02), B in {2,16,64}, "
             "batch-shared top-k block masks 34/62/83 of 172")
@@ -608,6 +609,19 @@ def run_gpu(args) -> None:
     dom_us = _graph_time_us(torch, stream, lists[dom_steps].run, 1, 20) if rank == 0 else 0.0
     list_info = lists[dom_steps].info()
 
+    if args.headline_only:
+        clocks = sampler.stop()
+        if rank == 0:
+            _emit({"metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+                   "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                   "dtype": "f16", "data": "synthetic", "config": {"workload": WORKLOAD, "headline_only": True},
+                   "roofline": {"bound": "hbm", "achieved": round(dom_steps * STEP_BYTES / (dom_us * 1e-6) / 1e9, 1),
+                                "peak": peaks["hbm_gbs"], "unit": "GB/s", "launch_us": round(dom_us, 2)},
+                   "gpu_launches": launches, "clocks": clocks})
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     # ---- per-batch kernel time, dense cuBLAS, selection, fused chain (rank 0's GPU) ----
     per_batch = {}
     reps = 60
@@ -929,6 +943,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=4000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--headline-only", action="store_true",
+                    help="time the K steps only and print a short line (the case the profiler's launch list is taken on)")
     ap.add_argument("--quick", action="store_true",
                     help="skip the sparsity sweep, the reference's Triton kernels and the reference's scripts")
     ap.add_argument("--profile-case", type=int, default=0, metavar="B",
