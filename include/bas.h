@@ -160,7 +160,10 @@ BAS_API int bas_build_bitmap(const int32_t* ids_dev, const int32_t* count_dev, i
  * Replaces _select_active_blocks (scripts/bench_roundrobin_e2e_decode.py:90-113) and
  * _block_energy + _topk_active / _energy_budget_active
  * (scripts/bench_alpaca_energy_budget_e2e.py:43-62): one launch, no host synchronisation.
- * Scores are accumulated in fp64 from the exact fp16 (or, with BAS_SCORE_BF16, bfloat16) inputs; equal scores go to the lower id.
+ * Scores are accumulated in fp64 from the exact fp16 (or, with BAS_SCORE_BF16, bfloat16) inputs; equal scores go to
+ * the lower id, and a score that is not a number ranks above +infinity (the order of torch.topk and of a
+ * descending torch.sort), so the ranking is a total order whatever X holds: exactly n_keep ids are written.
+ * A budget whose total is not a number keeps every block.
  *
  *   ids_out_dev     int32 [>= n_keep] (top-k) or [>= K/64] (budget): ascending active ids
  *   count_out_dev   int32 [1]: number of ids written
@@ -299,7 +302,8 @@ BAS_API int bas_select_topk_noalloc(const void* x_dev, int64_t ldx, int batch, i
  * a second) its own area until the words of all ranks carry the current call number, and adds them
  * in rank order: the result is identical on all ranks and does not depend on timing; one NVLink
  * traversal, no flags or fences.  A wait that runs out sets BAS_DEV_WAIT_EXPIRED and leaves Y of
- * that CTA unwritten.  All ranks must issue the same sequence of bas_gemm_allreduce calls on a
+ * that CTA unwritten; the ranks' call numbers are out of step from then on, so the group is dead:
+ * disconnect and destroy it on every rank and create a new one.  All ranks must issue the same sequence of bas_gemm_allreduce calls on a
  * group (same batch and n per call, n at most the group's); calls on one group must not overlap
  * on a GPU.
  *

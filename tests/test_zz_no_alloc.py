@@ -52,3 +52,40 @@ def test_noalloc_selection_matches_regular_entry_point_twice():
     st = abi.lib.bas_select_topk_noalloc(big.data_ptr(), big.stride(0), 1, 64 * 1025, 1, 0, ids.data_ptr(),
                                          cnt.data_ptr(), None, None, stream)
     assert st == 6                                                     # BAS_ERR_TOO_LARGE
+
+
+def test_noalloc_calls_back_to_back_on_one_stream_and_bfloat16():
+    """Two calls enqueued on one stream with no synchronisation between them (different K, so the
+    second finds the first's scores in the shared scratch), then a bfloat16 call: each against the
+    regular entry point.  Calls of one stream are ordered, so they may share the array."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bas import abi, ops
+
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.current_stream().cuda_stream
+    cases = [(16, 11008, 62, O.SCORE_ENERGY, torch.float16), (64, 2048, 7, O.SCORE_NORM, torch.float16),
+             (8, 4096, 23, O.SCORE_ENERGY, torch.bfloat16)]
+    xs, got = [], []
+    for call, (b, k, n_keep, kind, dt) in enumerate(cases):
+        x = torch.from_numpy(O.make_activations(b, k, seed=950 + call, dist="laplace")).to(dev).to(dt)
+        ids = torch.full((k // 64,), -1, dtype=torch.int32, device=dev)
+        cnt = torch.full((1,), -1, dtype=torch.int32, device=dev)
+        xs.append(x)
+        got.append((ids, cnt))
+    torch.cuda.synchronize()
+    for (b, k, n_keep, kind, dt), x, (ids, cnt) in zip(cases, xs, got):      # enqueued back to back
+        flags = kind | (256 if dt == torch.bfloat16 else 0)                   # BAS_SCORE_BF16
+        abi.check(abi.lib.bas_select_topk_noalloc(x.data_ptr(), x.stride(0), b, k, n_keep, flags, ids.data_ptr(),
+                                                  cnt.data_ptr(), None, None, stream), "bas_select_topk_noalloc")
+    torch.cuda.synchronize()
+    for (b, k, n_keep, kind, dt), x, (ids, cnt) in zip(cases, xs, got):
+        want_ids, want_cnt = ops.select_topk(x, n_keep, kind)
+        torch.cuda.synchronize()
+        assert int(cnt.item()) == n_keep == int(want_cnt.item())
+        assert torch.equal(ids[:n_keep], want_ids[:n_keep])
+    # more rows than the selection kernel takes: refused before anything is enqueued
+    tall = torch.zeros(1025, 64, dtype=torch.float16, device=dev)
+    st = abi.lib.bas_select_topk_noalloc(tall.data_ptr(), tall.stride(0), 1025, 64, 1, 0, got[0][0].data_ptr(),
+                                         got[0][1].data_ptr(), None, None, stream)
+    assert st == 2                                                     # BAS_ERR_UNSUPPORTED

@@ -144,7 +144,7 @@ class DecodeLinearStack:
             raise ValueError("allreduce must be 'nccl' or 'in_kernel'")
         self.world, self.rank, self.group, self.batch = world, rank, group, batch
         # "in_kernel": o and down add their partial outputs over the ranks inside the contraction
-        # kernel (peer loads over NVLink); "nccl": one all-reduce call after each of them
+        # kernel (peer stores over NVLink, each rank polls its own area); "nccl": one all-reduce call after each of them
         self.exchange = ops.ExchangeGroup(device, batch, max(s.n for s in LLAMA2_7B_LAYER if s.parallel == "row"),
                                           group) if allreduce == "in_kernel" else None
         # True: every call declares its input stable, which the stack's pre-generated inputs literally

@@ -18,7 +18,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libbas.so"
 SOURCES = ["bas_api.cu", "bas_gemv.cu", "bas_umma.cu", "bas_misc.cu", "bas_list.cu"]
-HEADERS = [CSRC / "bas_common.cuh", CSRC / "bas_kernels.cuh", HERE.parent / "include" / "bas.h"]
+HEADERS = [CSRC / "bas_common.cuh", CSRC / "bas_kernels.cuh", CSRC / "bas_trace.cuh", HERE.parent / "include" / "bas.h"]
 
 
 def _nvcc() -> str:

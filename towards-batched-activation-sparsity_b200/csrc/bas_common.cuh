@@ -9,20 +9,9 @@
 #include <stdint.h>
 
 #include "../../include/bas.h"
+#include "bas_trace.cuh"
 
 namespace bas {
-
-// Diagnostic build (-DBAS_TRACE): CTA 0 adds the cycles its roles spend waiting and working to a
-// small device array that bas_debug_trace() copies out.  Compiled out of the product.
-#ifdef BAS_TRACE
-#define BAS_TRACE_ADD(slot, cycles) do { if (blockIdx.x == 0 && p.trace != nullptr) atomicAdd((unsigned long long*)&p.trace[slot], (unsigned long long)(cycles)); } while (0)
-#define BAS_TRACE_CLOCK() clock64()
-#define BAS_TRACE_SET(slot, v) do { if (blockIdx.x == 0 && p.trace != nullptr && (slot) < 512) p.trace[slot] = (long long)(v); } while (0)
-#else
-#define BAS_TRACE_SET(slot, v) do { } while (0)
-#define BAS_TRACE_ADD(slot, cycles) do { } while (0)
-#define BAS_TRACE_CLOCK() 0LL
-#endif
 
 constexpr int kBlockK = BAS_BLOCK_K;                 // channels per activation block
 constexpr int kTileN = BAS_TILE_N;                   // widest column sub-tile one pass handles

@@ -38,22 +38,6 @@ namespace bas {
 
 namespace {
 
-// Diagnostic build (-DBAS_TRACE): CTA 0 stamps the global timer at a few events of each of the first
-// calls into a device array that bas_list_debug_trace() copies out.  Compiled out of the product.
-#ifdef BAS_TRACE
-constexpr int kLTraceCalls = 256, kLTraceEvents = 8;
-#define BAS_LTRACE(call, ev)                                                                      \
-  do {                                                                                            \
-    if (p.trace != nullptr && blockIdx.x == p.trace_cta && (call) < kLTraceCalls) {               \
-      unsigned long long gt_;                                                                     \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                                     \
-      p.trace[(call) * kLTraceEvents + (ev)] = (long long)gt_;                                    \
-    }                                                                                             \
-  } while (0)
-#else
-#define BAS_LTRACE(call, ev) do { } while (0)
-#endif
-
 constexpr int kLProducers = 4;
 constexpr int kLIssuers = 4;
 constexpr int kLEpiWarp0 = kLProducers + kLIssuers;
@@ -957,8 +941,8 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
 #ifdef BAS_TRACE
   p.trace = nullptr;
   p.trace_cta = 0;
-  if (cudaMalloc(&p.trace, sizeof(long long) * kLTraceCalls * kLTraceEvents) == cudaSuccess)
-    cudaMemset(p.trace, 0, sizeof(long long) * kLTraceCalls * kLTraceEvents);
+  if (cudaMalloc(&p.trace, sizeof(long long) * BAS_LTRACE_CALLS * BAS_LTRACE_EVENTS) == cudaSuccess)
+    cudaMemset(p.trace, 0, sizeof(long long) * BAS_LTRACE_CALLS * BAS_LTRACE_EVENTS);
 #endif
   *out = l;
   return BAS_OK;
@@ -1011,7 +995,7 @@ BAS_API int bas_list_info(const bas_list* l, int* ctas, int* cluster, int* slots
 // clears them and chooses the CTA that stamps the next runs.
 BAS_API int bas_list_debug_trace(bas_list* l, long long* out, int n, int next_cta) {
   if (l == nullptr || l->params.trace == nullptr) return 1;
-  const size_t total = (size_t)kLTraceCalls * kLTraceEvents;
+  const size_t total = (size_t)BAS_LTRACE_CALLS * BAS_LTRACE_EVENTS;
   const size_t cnt = (size_t)n < total ? (size_t)n : total;
   cudaError_t e = cudaMemcpy(out, l->params.trace, sizeof(long long) * cnt, cudaMemcpyDeviceToHost);
   if (e == cudaSuccess) e = cudaMemset(l->params.trace, 0, sizeof(long long) * total);

@@ -1,6 +1,8 @@
 // Weight prepack, bitmap build and the per-step batch-shared mask selection.
 #include "bas_kernels.cuh"
 
+#include <atomic>
+
 namespace bas {
 
 namespace {
@@ -290,20 +292,26 @@ extern "C" BAS_API int bas_select_topk_noalloc(const void* x_dev, int64_t ldx, i
   score_kind &= ~BAS_SCORE_BF16;
   if (score_kind != BAS_SCORE_NORM && score_kind != BAS_SCORE_ENERGY) return BAS_ERR_INVALID_ARGUMENT;
   if (n_keep < 0 || n_keep > nb) return BAS_ERR_INVALID_ARGUMENT;
+  if (batch > kSelMaxBatch) return BAS_ERR_UNSUPPORTED;   // before anything is enqueued
 
   // In host code the array's name is only a handle; the device address has to be asked for, once per
-  // device, with that device current.  The first call on a device does this.
-  static void* scratch_addr[64] = {};
+  // device, with that device current.  The first call on a device does this (any thread may be first:
+  // the cache entries are atomic, and every thread that looks the address up gets the same answer).
+  static std::atomic<void*> scratch_addr[64];
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BAS_ERR_CUDA;
-  void* scratch = scratch_addr[dev];
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  if (dev < 0 || dev >= 64) return BAS_ERR_UNSUPPORTED;
+  void* scratch = scratch_addr[dev].load(std::memory_order_acquire);
   if (scratch == nullptr) {
-    if (cudaGetSymbolAddress(&scratch, g_select_scratch) != cudaSuccess || scratch == nullptr) return BAS_ERR_CUDA;
-    scratch_addr[dev] = scratch;
+    e = cudaGetSymbolAddress(&scratch, g_select_scratch);
+    if (e != cudaSuccess || scratch == nullptr) return record_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
+    scratch_addr[dev].store(scratch, std::memory_order_release);
   }
   cudaStream_t s = (cudaStream_t)stream;
   // The array keeps whatever the previous call left: the arrival counter must start at zero.
-  if (cudaMemsetAsync(scratch, 0, 256, s) != cudaSuccess) return BAS_ERR_CUDA;
+  e = cudaMemsetAsync(scratch, 0, 256, s);
+  if (e != cudaSuccess) return record_cuda_error(e);
 
   SelectParams p;
   p.x = (const __half*)x_dev;
@@ -322,5 +330,6 @@ extern "C" BAS_API int bas_select_topk_noalloc(const void* x_dev, int64_t ldx, i
   p.scores_out = scores_out_dev;
   p.ws_done = (unsigned int*)scratch;
   p.ws_scores = (double*)((unsigned char*)scratch + 256);
-  return launch_select(p, 0, s) == cudaSuccess ? BAS_OK : BAS_ERR_CUDA;
+  e = launch_select(p, 0, s);
+  return e == cudaSuccess ? BAS_OK : record_cuda_error(e);
 }

@@ -275,20 +275,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &hdr->abort_flag;
-#ifdef BAS_TRACE
-  int trace_launch = -1;   // diagnostic builds: wall-clock start and end of CTA 0 of every launch
-  if (blockIdx.x == 0 && tid == 0 && p.trace != nullptr) {
-    trace_launch = (int)atomicAdd((unsigned long long*)&p.trace[30], 1ull);
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-    if (trace_launch < 100) p.trace[300 + 2 * trace_launch] = (long long)gt;
-  }
-  if (tid == 0 && p.trace != nullptr && blockIdx.x < 200) {   // every CTA of the latest launch
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-    p.trace[600 + 2 * blockIdx.x] = (long long)gt;
-  }
-#endif
+  BAS_TRACE_LAUNCH_BEGIN();
 
   // The id list may be the previous kernel's output unless the caller declared it stable; so may X
   // unless declared stable too; Y always waits for the previous kernel.  A stable list is requested
@@ -863,18 +850,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
-#ifdef BAS_TRACE
-  if (trace_launch >= 0 && trace_launch < 100) {
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-    p.trace[301 + 2 * trace_launch] = (long long)gt;
-  }
-  if (tid == 0 && p.trace != nullptr && blockIdx.x < 200) {
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-    p.trace[601 + 2 * blockIdx.x] = (long long)gt;
-  }
-#endif
+  BAS_TRACE_LAUNCH_END();
 }
 
 // ---------------------------------------------------------------------------------------------
