@@ -766,78 +766,77 @@ def run_gpu(args) -> None:
         layer_stack = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     torch.cuda.empty_cache()
 
-    # ---- end to end through the host-buffer operator (pinned staging inside the library) ----
+    # ---- end to end through the host-buffer operator: a step is one submission ----
     import ctypes
-    handles = []
-    E2E_COPIES = 4
-    for _ in range(E2E_COPIES):
-        h = ctypes.c_void_p()
-        abi.check(abi.lib.bas_linear_create(ctypes.byref(h), w_host.ctypes.data, N_OUT, K_IN, 64), "bas_linear_create")
-        handles.append(h)
-    # the step's inputs and results live in page-locked host memory, as a serving host keeps them
-    pinned = {}
+    calls = (abi.StepCall * len(BATCHES))()
+    for c, bb in zip(calls, BATCHES):
+        c.w_host, c.n, c.k, c.batch, c.n_keep, c.score_kind = w_host.ctypes.data, N_OUT, K_IN, bb, N_KEEP[bb], abi.SCORE_NORM
+    E2E_DEPTH = 3
+    hstep = ctypes.c_void_p()
+    abi.check(abi.lib.bas_step_create(ctypes.byref(hstep), calls, len(BATCHES), E2E_DEPTH), "bas_step_create")
+    # the step's inputs and results live in page-locked host memory, as a serving host keeps them; one
+    # set of buffers per step in flight
+    pinned = []
 
-    def pinned_array(key, shape, dtype):
+    def pinned_array(shape, dtype):
         t = torch.empty(shape, dtype=dtype, pin_memory=True)
-        pinned[key] = t                 # keeps the allocation alive
+        pinned.append(t)                # keeps the allocation alive
         return t.numpy()
 
-    x_host, y_host = {}, {}
-    for bb in BATCHES:
-        x_host[bb] = pinned_array(("x", bb), (bb, K_IN), torch.float16)
-        x_host[bb][...] = O.make_activations(bb, K_IN, seed=1000 + bb, dist="laplace")
-        y_host[bb] = pinned_array(("y", bb), (bb, N_OUT), torch.float16)
-    ids_host = {bb: np.full(NB, -1, np.int32) for bb in BATCHES}
-    call = {"i": 0}
+    sets = []
+    for _ in range(E2E_DEPTH):
+        xh = [pinned_array((bb, K_IN), torch.float16) for bb in BATCHES]
+        yh = [pinned_array((bb, N_OUT), torch.float16) for bb in BATCHES]
+        ih = [np.full(NB, -1, np.int32) for bb in BATCHES]
+        for arr, bb in zip(xh, BATCHES):
+            arr[...] = O.make_activations(bb, K_IN, seed=1000 + bb, dist="laplace")
+        ptrs = tuple((ctypes.c_void_p * len(BATCHES))(*[a.ctypes.data for a in group]) for group in (xh, yh, ih))
+        sets.append((xh, yh, ih, ptrs))
 
-    def e2e_step():
-        # the three calls of a step are independent: submit them on three handles (own streams, so the
-        # copies of one overlap the kernels of another), then collect the three results
-        used = []
-        for bb in BATCHES:                            # smallest upload first (measured: 116 vs 127 us per step)
-            h = handles[call["i"] % E2E_COPIES]
-            call["i"] += 1
-            abi.check(abi.lib.bas_linear_submit_host(h, x_host[bb].ctypes.data, bb, N_KEEP[bb], abi.SCORE_NORM,
-                                                     y_host[bb].ctypes.data, ids_host[bb].ctypes.data),
-                      "bas_linear_submit_host")
-            used.append(h)
-        for h in used:
-            abi.check(abi.lib.bas_linear_wait(h), "bas_linear_wait")
+    def e2e_run(n_steps):
+        # keep E2E_DEPTH steps in flight: every step's uploads, kernels and downloads are inside the region
+        for i in range(n_steps):
+            if i >= E2E_DEPTH:
+                abi.check(abi.lib.bas_step_wait(hstep), "bas_step_wait")
+            px, py, pi = sets[i % E2E_DEPTH][3]
+            abi.check(abi.lib.bas_step_submit(hstep, px, py, pi), "bas_step_submit")
+        for _ in range(min(n_steps, E2E_DEPTH)):
+            abi.check(abi.lib.bas_step_wait(hstep), "bas_step_wait")
 
-    for _ in range(5):
-        e2e_step()
-    e2e_steps = max(20, min(args.steps, 500))
+    e2e_run(9)
+    e2e_steps = max(60, min(args.steps, 600))
     if world > 1:
         dist.barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_run(e2e_steps)
     e2e_dt = (time.perf_counter() - t0) / e2e_steps
+    # one step alone, nothing else in flight: the latency of a step
+    lat = []
+    for _ in range(20):
+        t1 = time.perf_counter()
+        e2e_run(1)
+        lat.append(time.perf_counter() - t1)
     if world > 1:
         t = torch.tensor([e2e_dt], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_dt = float(t.item())
-    for h in handles:
-        abi.lib.bas_linear_destroy(h)
-    for bb in BATCHES:      # the e2e outputs are real results: same masks, same sums as the resident path
-        ops.gemm(xs[bb], packed[0], outs[bb], ids=ids[bb])
-        torch.cuda.synchronize()
-        d = np.abs(y_host[bb].astype(np.float32) - outs[bb].float().cpu().numpy()).max()
-        same_ids = np.array_equal(ids_host[bb][:N_KEEP[bb]], ids[bb].cpu().numpy())
-        if os.environ.get("BAS_BENCH_DEBUG"):
-            mask = torch.zeros(NB, device=dev); mask[ids[bb].long()] = 1
-            ref = ((xs[bb].float() * mask.repeat_interleave(64)) @ w.float().t()).cpu().numpy()
-            print("debug B", bb, "e2e vs ref", np.abs(y_host[bb].astype(np.float32) - ref).max(),
-                  "resident vs ref", np.abs(outs[bb].float().cpu().numpy() - ref).max(),
-                  "x_host==xs", np.array_equal(x_host[bb], xs[bb].cpu().numpy()), file=sys.stderr)
-        if not same_ids or not d <= 2e-3 * float(outs[bb].float().abs().max().item()):
-            raise SystemExit(f"end-to-end result differs from the resident-input path at B={bb}: "
-                             f"ids equal {same_ids}, max |dy| {d:.3e}")
+    abi.lib.bas_step_destroy(hstep)
+    for xh, yh, ih, _ in sets:      # the e2e outputs are real results: same masks, same sums as the resident path
+        for j, bb in enumerate(BATCHES):
+            ops.gemm(xs[bb], packed[0], outs[bb], ids=ids[bb])
+            torch.cuda.synchronize()
+            d = np.abs(yh[j].astype(np.float32) - outs[bb].float().cpu().numpy()).max()
+            same_ids = np.array_equal(ih[j][:N_KEEP[bb]], ids[bb].cpu().numpy())
+            if not same_ids or not d <= 2e-3 * float(outs[bb].float().abs().max().item()):
+                raise SystemExit(f"end-to-end result differs from the resident-input path at B={bb}: "
+                                 f"ids equal {same_ids}, max |dy| {d:.3e}")
     e2e = {"value": world * STEP_BYTES / e2e_dt / 1e9, "unit": "GB/s",
            "h2d_bytes_per_step": sum(bb * K_IN * 2 for bb in BATCHES),
-           "d2h_bytes_per_step": sum(bb * N_OUT * 2 + N_KEEP[bb] * 4 for bb in BATCHES) + 3 * 4,
-           "ms_per_step": e2e_dt * 1e3, "steps": e2e_steps,
-           "api": "bas_linear_submit_host x3 + bas_linear_wait x3 per step: H2D X from pinned memory, device-side top-k selection, GEMM, D2H Y and ids, per call"}
+           "d2h_bytes_per_step": sum(bb * N_OUT * 2 + (NB + 1) * 4 for bb in BATCHES) + 16,
+           "ms_per_step": e2e_dt * 1e3, "steps": e2e_steps, "steps_in_flight": E2E_DEPTH,
+           "one_step_alone_ms": round(statistics.median(lat) * 1e3, 4),
+           "api": "bas_step_submit / bas_step_wait: per step H2D of the three X from page-locked memory, three device-side "
+                  "top-k selections, one list launch for the three GEMMs, D2H of the three Y, the ids and the status word"}
 
     clocks = sampler.stop()
 

@@ -352,6 +352,27 @@ BAS_API int bas_linear_submit_host(bas_linear* h, const void* x_host, int batch,
 BAS_API int bas_linear_wait(bas_linear* h);
 BAS_API void bas_linear_destroy(bas_linear* h);
 
+/* ---- host-buffer operator for a whole step -------------------------------------------------
+ * The call pattern of the patched model's token loop (scripts/bench_roundrobin_e2e_decode.py:515-548:
+ * every linear of a step runs _sparse_linear, :179-284) for a caller whose activations live in host
+ * memory, taken a STEP at a time: bas_step_submit enqueues, on a stream of the step's slot, the
+ * upload of every call's X, the device-side top-k selections, ONE list launch for all contractions
+ * and the download of every Y and id list, and returns; bas_step_wait blocks until the oldest
+ * submitted step is done.  Up to `depth` steps are in flight, so the copies of one step run beside
+ * the kernels of another; a step that recurs with the same page-locked buffers is replayed as one
+ * CUDA-graph launch.  Calls that name the same w_host (fp16 [n, k] row-major) share one packed copy.
+ * x_host[c] is fp16 [batch_c, k_c], y_host[c] fp16 [batch_c, n_c], ids_host_out (optional, entries may
+ * be null) receives n_keep_c ascending ids per call; all must stay valid until the step's wait returns. */
+typedef struct bas_step_call {
+  const void* w_host;
+  int32_t n, k, batch, n_keep, score_kind, reserved;
+} bas_step_call;
+typedef struct bas_step bas_step;
+BAS_API int bas_step_create(bas_step** out, const bas_step_call* calls, int n_calls, int depth);
+BAS_API int bas_step_submit(bas_step* s, const void* const* x_host, void* const* y_host, int32_t* const* ids_host_out);
+BAS_API int bas_step_wait(bas_step* s);
+BAS_API void bas_step_destroy(bas_step* s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -33,6 +33,13 @@ class ListCall(C.Structure):
                 ("depends_on", C.c_int32), ("reserved", C.c_int32)]
 
 
+class StepCall(C.Structure):
+    """``bas_step_call`` of include/bas.h."""
+
+    _fields_ = [("w_host", C.c_void_p), ("n", C.c_int32), ("k", C.c_int32), ("batch", C.c_int32), ("n_keep", C.c_int32),
+                ("score_kind", C.c_int32), ("reserved", C.c_int32)]
+
+
 _PKG = Path(__file__).resolve().parent.parent
 lib_path = _PKG / "libbas.so"
 
@@ -93,6 +100,10 @@ _SIGNATURES = {
     "bas_list_set_wait": (_i, [_vp, C.c_double, _i]),
     "bas_list_info": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     "bas_list_destroy": (None, [_vp]),
+    "bas_step_create": (_i, [C.POINTER(_vp), _vp, _i, _i]),
+    "bas_step_submit": (_i, [_vp, _vp, _vp, _vp]),
+    "bas_step_wait": (_i, [_vp]),
+    "bas_step_destroy": (None, [_vp]),
     "bas_linear_create": (_i, [C.POINTER(_vp), _vp, _i, _i, _i]),
     "bas_linear_forward_host": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "bas_linear_forward_host_ids": (_i, [_vp, _vp, _i, _vp, _i, _vp]),

@@ -29,6 +29,7 @@
 
 #include <cstddef>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <new>
 #include <type_traits>
@@ -1009,5 +1010,295 @@ BAS_API void bas_list_destroy(bas_list* l) {
   if (l->dev_block != nullptr) cudaFree(l->dev_block);
   delete l;
 }
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// host-buffer operator for a whole step (bas_step_*): the calls of one decode step whose activations
+// live in host memory, as ONE unit of submission - all uploads, the mask selections, one list
+// launch for all contractions, all downloads - with several steps in flight on streams of their own.
+// ---------------------------------------------------------------------------------------------
+struct bas_step {
+  struct Call {
+    int n, k, nb, batch, n_keep, score_kind;
+    long long ldx;
+    uint8_t* packed;         // owned by the step unless shared with an earlier call of the same weight
+    size_t x_off, y_off;     // element offsets into a slot's device X / Y blocks
+    size_t ids_off;          // int32 offset into a slot's id block
+  };
+  struct Slot {
+    cudaStream_t stream = nullptr;
+    __half* x_dev = nullptr;
+    __half* y_dev = nullptr;
+    uint8_t* small_dev = nullptr;     // [ids of all calls][pad] ; the list's status word is copied beside it
+    uint8_t* small_pin = nullptr;
+    uint8_t* sel_ws = nullptr;        // one selection workspace per call (the calls' selections run side by side)
+    cudaStream_t aux[3] = {nullptr, nullptr, nullptr};   // branches beside `stream` for uploads + selections
+    cudaEvent_t fork = nullptr, join[3] = {nullptr, nullptr, nullptr};
+    bas_list* list = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    std::vector<const void*> key;     // host pointers the graph was captured with
+    std::vector<int32_t*> ids_out;
+    bool pending = false, graph_failed = false;
+  };
+  std::vector<Call> calls;
+  std::vector<uint8_t*> owned_packed;
+  std::vector<Slot> slots;
+  size_t x_elems = 0, y_elems = 0, ids_count = 0, small_bytes = 0, sel_ws_bytes = 0;
+  unsigned long long submitted = 0, waited = 0;
+};
+
+namespace {
+
+bool step_is_pinned(const void* ptr) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  return attr.type == cudaMemoryTypeHost;
+}
+
+// The stream work of one step: uploads, selections, the list launch, downloads.  Nothing is waited for.
+int step_enqueue(bas_step* st, bas_step::Slot& sl, const void* const* x_host, void* const* y_host) {
+  cudaStream_t s = sl.stream;
+  // Upload and selection of call c run on branch c % branches: a call's selection starts as soon as its
+  // own X has arrived, and the calls' selections (a few microseconds of latency each) overlap.
+  const int branches = (int)std::min<size_t>(st->calls.size(), 4);
+  cudaError_t e = cudaEventRecord(sl.fork, s);
+  for (int i = 1; i < branches && e == cudaSuccess; ++i) e = cudaStreamWaitEvent(sl.aux[i - 1], sl.fork, 0);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  int32_t* ids_base = (int32_t*)sl.small_dev;
+  for (size_t c = 0; c < st->calls.size(); ++c) {
+    const bas_step::Call& a = st->calls[c];
+    cudaStream_t bs = (c % branches == 0) ? s : sl.aux[c % branches - 1];
+    const size_t row = (size_t)a.k * 2;
+    e = cudaMemcpy2DAsync(sl.x_dev + a.x_off, (size_t)a.ldx * 2, x_host[c], row, row, (size_t)a.batch, cudaMemcpyHostToDevice, bs);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    // count goes to the last word of the call's id block (nb + 1 words per call)
+    const int rc = bas_select_topk(sl.x_dev + a.x_off, a.ldx, a.batch, a.k, a.n_keep, a.score_kind, ids_base + a.ids_off,
+                                   ids_base + a.ids_off + a.nb, nullptr, nullptr, sl.sel_ws + c * st->sel_ws_bytes,
+                                   st->sel_ws_bytes, bs);
+    if (rc != BAS_OK) return rc;
+  }
+  for (int i = 1; i < branches; ++i) {
+    e = cudaEventRecord(sl.join[i - 1], sl.aux[i - 1]);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, sl.join[i - 1], 0);
+    if (e != cudaSuccess) return record_cuda_error(e);
+  }
+  int rc = bas_list_run(sl.list, s);
+  if (rc != BAS_OK) return rc;
+  for (size_t c = 0; c < st->calls.size(); ++c) {
+    const bas_step::Call& a = st->calls[c];
+    cudaError_t e = cudaMemcpyAsync(y_host[c], sl.y_dev + a.y_off, (size_t)a.batch * a.n * 2, cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return record_cuda_error(e);
+  }
+  // the ids of every call and, behind them, the list's status word: one block, one copy
+  e = cudaMemcpyAsync(sl.small_dev + st->ids_count * 4, &sl.list->params.hdr->status, sizeof(unsigned int),
+                                  cudaMemcpyDeviceToDevice, s);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(sl.small_pin, sl.small_dev, st->small_bytes, cudaMemcpyDeviceToHost, s);
+  return e == cudaSuccess ? BAS_OK : record_cuda_error(e);
+}
+
+void step_free(bas_step* st) {
+  if (st == nullptr) return;
+  for (auto& sl : st->slots) {
+    if (sl.stream != nullptr) cudaStreamSynchronize(sl.stream);
+    if (sl.exec != nullptr) cudaGraphExecDestroy(sl.exec);
+    if (sl.list != nullptr) bas_list_destroy(sl.list);
+    if (sl.x_dev != nullptr) cudaFree(sl.x_dev);
+    if (sl.y_dev != nullptr) cudaFree(sl.y_dev);
+    if (sl.small_dev != nullptr) cudaFree(sl.small_dev);
+    if (sl.sel_ws != nullptr) cudaFree(sl.sel_ws);
+    if (sl.small_pin != nullptr) cudaFreeHost(sl.small_pin);
+    for (int i = 0; i < 3; ++i) {
+      if (sl.aux[i] != nullptr) cudaStreamDestroy(sl.aux[i]);
+      if (sl.join[i] != nullptr) cudaEventDestroy(sl.join[i]);
+    }
+    if (sl.fork != nullptr) cudaEventDestroy(sl.fork);
+    if (sl.stream != nullptr) cudaStreamDestroy(sl.stream);
+  }
+  for (uint8_t* ptr : st->owned_packed) cudaFree(ptr);
+  delete st;
+}
+
+}  // namespace
+
+extern "C" {
+
+BAS_API int bas_step_create(bas_step** out, const bas_step_call* calls, int n_calls, int depth) {
+  if (out == nullptr || calls == nullptr || n_calls <= 0 || n_calls > 1024 || depth < 1 || depth > 8) return BAS_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  bas_step* st = new (std::nothrow) bas_step();
+  if (st == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  cudaError_t e = cudaSuccess;
+  int rc = BAS_OK;
+  int k_max = 0;
+  // ---- weights: packed once; calls that name the same host weight share the pack ----
+  for (int c = 0; c < n_calls && rc == BAS_OK && e == cudaSuccess; ++c) {
+    const bas_step_call& in = calls[c];
+    if (in.w_host == nullptr || in.n <= 0 || in.k < kBlockK || in.batch <= 0 || in.batch > BAS_MAX_BATCH || in.n_keep < 1 ||
+        in.n_keep > in.k / kBlockK || (in.score_kind != BAS_SCORE_NORM && in.score_kind != BAS_SCORE_ENERGY)) {
+      rc = BAS_ERR_INVALID_ARGUMENT;
+      break;
+    }
+    bas_step::Call a;
+    a.n = in.n;
+    a.k = in.k;
+    a.nb = (in.k + kBlockK - 1) / kBlockK;
+    a.batch = in.batch;
+    a.n_keep = in.n_keep;
+    a.score_kind = in.score_kind;
+    a.ldx = ((long long)in.k + 7) / 8 * 8;
+    a.packed = nullptr;
+    for (int p = 0; p < c; ++p)
+      if (calls[p].w_host == in.w_host && calls[p].n == in.n && calls[p].k == in.k) a.packed = st->calls[(size_t)p].packed;
+    if (a.packed == nullptr) {
+      __half* w_dev = nullptr;
+      e = cudaMalloc(&w_dev, (size_t)in.n * in.k * 2);
+      if (e == cudaSuccess) e = cudaMalloc(&a.packed, bas_packed_weight_bytes(in.n, in.k));
+      if (e == cudaSuccess) st->owned_packed.push_back(a.packed);
+      if (e == cudaSuccess) e = cudaMemcpy(w_dev, in.w_host, (size_t)in.n * in.k * 2, cudaMemcpyHostToDevice);
+      if (e == cudaSuccess) rc = bas_pack_weight(w_dev, in.n, in.k, in.k, a.packed, nullptr);
+      if (e == cudaSuccess) e = cudaDeviceSynchronize();
+      if (w_dev != nullptr) cudaFree(w_dev);
+    }
+    a.x_off = st->x_elems;
+    a.y_off = st->y_elems;
+    a.ids_off = st->ids_count;
+    st->x_elems += (size_t)a.batch * (size_t)a.ldx;
+    st->y_elems += (size_t)a.batch * (size_t)a.n;
+    st->ids_count += (size_t)a.nb + 1;
+    if (in.k > k_max) k_max = in.k;
+    st->calls.push_back(a);
+  }
+  st->small_bytes = st->ids_count * 4 + 16;
+  st->sel_ws_bytes = (bas_select_workspace_bytes(k_max) + 255) / 256 * 256;
+  // ---- slots: device blocks, a stream and a list of the step's contractions each ----
+  st->slots.resize((size_t)depth);
+  for (auto& sl : st->slots) {
+    if (rc != BAS_OK || e != cudaSuccess) break;
+    e = cudaStreamCreateWithFlags(&sl.stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaMalloc(&sl.x_dev, st->x_elems * 2);
+    if (e == cudaSuccess) e = cudaMemset(sl.x_dev, 0, st->x_elems * 2);          // row padding stays zero
+    if (e == cudaSuccess) e = cudaMalloc(&sl.y_dev, st->y_elems * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&sl.small_dev, st->small_bytes);
+    if (e == cudaSuccess) e = cudaMemset(sl.small_dev, 0, st->small_bytes);
+    if (e == cudaSuccess) e = cudaMallocHost(&sl.small_pin, st->small_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&sl.sel_ws, st->sel_ws_bytes * (size_t)n_calls);
+    if (e == cudaSuccess) e = cudaMemset(sl.sel_ws, 0, st->sel_ws_bytes * (size_t)n_calls);
+    for (int i = 0; i < 3 && e == cudaSuccess; ++i) {
+      e = cudaStreamCreateWithFlags(&sl.aux[i], cudaStreamNonBlocking);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&sl.join[i], cudaEventDisableTiming);
+    }
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&sl.fork, cudaEventDisableTiming);
+    if (e != cudaSuccess) break;
+    std::vector<bas_list_call> lc((size_t)n_calls);
+    for (int c = 0; c < n_calls; ++c) {
+      const bas_step::Call& a = st->calls[(size_t)c];
+      bas_list_call& d = lc[(size_t)c];
+      std::memset(&d, 0, sizeof(d));
+      d.x_dev = sl.x_dev + a.x_off;
+      d.ldx = a.ldx;
+      d.packed_dev = a.packed;
+      d.ids_dev = (const int32_t*)sl.small_dev + a.ids_off;
+      d.k_host = a.n_keep;
+      d.batch = a.batch;
+      d.k = (int)a.ldx;
+      d.n = a.n;
+      d.y_dev = sl.y_dev + a.y_off;
+      d.ldy = a.n;
+      d.depends_on = -1;
+    }
+    rc = bas_list_create(&sl.list, lc.data(), n_calls, 16 << 24);   // 128-column ranges: mixed batch sizes up to 64
+  }
+  if (rc == BAS_OK && e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (rc != BAS_OK || e != cudaSuccess) {
+    step_free(st);
+    return rc != BAS_OK ? rc : record_cuda_error(e);
+  }
+  *out = st;
+  return BAS_OK;
+}
+
+BAS_API int bas_step_submit(bas_step* st, const void* const* x_host, void* const* y_host, int32_t* const* ids_host_out) {
+  if (st == nullptr || x_host == nullptr || y_host == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  bas_step::Slot& sl = st->slots[(size_t)(st->submitted % st->slots.size())];
+  if (sl.pending) return BAS_ERR_INVALID_ARGUMENT;   // every slot is in flight: wait first
+  const size_t n = st->calls.size();
+  std::vector<const void*> key;
+  key.reserve(2 * n);
+  bool pinned = true;
+  for (size_t c = 0; c < n; ++c) {
+    if (x_host[c] == nullptr || y_host[c] == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+    key.push_back(x_host[c]);
+    key.push_back(y_host[c]);
+  }
+  int rc;
+  if (sl.exec != nullptr && sl.key == key) {
+    const cudaError_t e = cudaGraphLaunch(sl.exec, sl.stream);
+    rc = e == cudaSuccess ? BAS_OK : record_cuda_error(e);
+  } else {
+    // A step that recurs with the same page-locked buffers is captured on its second occurrence and
+    // replayed from then on (one graph launch instead of a dozen stream calls).
+    for (size_t c = 0; c < 2 * n && pinned; ++c) pinned = step_is_pinned(key[c]);
+    const bool capture = pinned && !sl.graph_failed && sl.key == key && sl.exec == nullptr;
+    if (sl.key != key && sl.exec != nullptr) {
+      cudaGraphExecDestroy(sl.exec);
+      sl.exec = nullptr;
+    }
+    sl.key = key;
+    if (capture) {
+      cudaGraph_t graph = nullptr;
+      cudaError_t e = cudaStreamBeginCapture(sl.stream, cudaStreamCaptureModeThreadLocal);
+      if (e == cudaSuccess) {
+        rc = step_enqueue(st, sl, x_host, y_host);
+        e = cudaStreamEndCapture(sl.stream, &graph);
+        if (rc == BAS_OK && e == cudaSuccess && graph != nullptr) e = cudaGraphInstantiate(&sl.exec, graph, 0);
+        else if (e == cudaSuccess) e = cudaErrorUnknown;
+        if (graph != nullptr) cudaGraphDestroy(graph);
+      }
+      if (e != cudaSuccess || sl.exec == nullptr) {
+        (void)cudaGetLastError();
+        sl.exec = nullptr;
+        sl.graph_failed = true;
+        rc = step_enqueue(st, sl, x_host, y_host);
+      } else {
+        e = cudaGraphLaunch(sl.exec, sl.stream);
+        rc = e == cudaSuccess ? BAS_OK : record_cuda_error(e);
+      }
+    } else {
+      rc = step_enqueue(st, sl, x_host, y_host);
+    }
+  }
+  if (rc != BAS_OK) return rc;
+  sl.ids_out.assign(n, nullptr);
+  if (ids_host_out != nullptr)
+    for (size_t c = 0; c < n; ++c) sl.ids_out[c] = ids_host_out[c];
+  sl.pending = true;
+  ++st->submitted;
+  return BAS_OK;
+}
+
+BAS_API int bas_step_wait(bas_step* st) {
+  if (st == nullptr || st->waited >= st->submitted) return BAS_ERR_INVALID_ARGUMENT;
+  bas_step::Slot& sl = st->slots[(size_t)(st->waited % st->slots.size())];
+  ++st->waited;
+  sl.pending = false;
+  const cudaError_t e = cudaStreamSynchronize(sl.stream);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  const int32_t* ids = (const int32_t*)sl.small_pin;
+  for (size_t c = 0; c < st->calls.size(); ++c)
+    if (sl.ids_out[c] != nullptr) std::memcpy(sl.ids_out[c], ids + st->calls[c].ids_off, sizeof(int32_t) * (size_t)st->calls[c].n_keep);
+  unsigned int flags = 0;
+  std::memcpy(&flags, sl.small_pin + st->ids_count * 4, sizeof(flags));
+  if (flags != 0) {
+    cudaMemsetAsync(&sl.list->params.hdr->status, 0, sizeof(unsigned int), sl.stream);
+    return BAS_ERR_DEVICE_FLAG;
+  }
+  return BAS_OK;
+}
+
+BAS_API void bas_step_destroy(bas_step* st) { step_free(st); }
 
 }  // extern "C"
