@@ -186,8 +186,8 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
   uint16_t* s_ids_all = (uint16_t*)sp;                     // [kLProducers][nb_max]
   const size_t ids_stride = ((size_t)p.nb_max * 2 + 127) / 128 * 128;
   sp += ids_stride * kLProducers;
-  uint32_t* s_def_all = (uint32_t*)sp;                     // [kLProducers][kMaxStages] deferred activation copies
-  sp += sizeof(uint32_t) * kMaxStages * kLProducers;
+  uint2* s_def_all = (uint2*)sp;                           // [kLProducers][kMaxStages] deferred activation copies
+  sp += sizeof(uint2) * kMaxStages * kLProducers;
   float* s_red = (float*)sp;                               // [2][source rank][128][row slots]
   const int C = p.cluster;
   if (C > 1) sp += 2 * (size_t)BPAD * kTileN * sizeof(float);
@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     // ================================ copy warps ================================
     if (warp < P) {
       uint16_t* s_ids = (uint16_t*)((uint8_t*)s_ids_all + ids_stride * warp);
-      uint32_t* s_def = s_def_all + kMaxStages * warp;   // entries {slot << 24 | call << 12 | block}: at most S / P
+      uint2* s_def = s_def_all + kMaxStages * warp;   // entries {slot << 24 | call << 12 | block, dependency + 1}: at most S / P
       const int per_lap = S / P;
       const uint64_t pol_x = l2_policy_evict_last();
       int slot = warp, lap = 0;        // next slot of this pair and how often it has been used
@@ -248,15 +248,19 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
       int def_head = 0, ndef = 0;      // deferred activation copies: oldest entry (ring index into s_def) and how many
       int dep_ok = -1;                 // the dependency last seen complete
       bool ok = true;
+#ifdef BAS_TRACE_PRODUCER
+      int trace_flushes = 0, trace_last_call = -1;
+#endif
 
       // Issue the activation copy of the oldest deferred tile; `block`: wait for its call's dependency.
       // `force`: issue it whatever the dependency says (giving up: nobody consumes the tile, but its barrier
       // must complete before the CTA may leave).
       auto flush_one = [&](bool block, bool force) -> bool {   // lane 0 only; false = not ready (or gave up: ok cleared)
-        const uint32_t e = s_def[def_head % kMaxStages];
+        const uint2 e2 = s_def[def_head % kMaxStages];
+        const uint32_t e = e2.x;
         const int dslot = (int)(e >> 24), dcall = (int)((e >> 12) & 0xfffu), dj = (int)(e & 0xfffu);
         const ListCallDev* cd = p.calls + dcall;
-        const int dep = __ldg(&cd->dep);
+        const int dep = (int)e2.y - 1;
         if (!force && dep >= 0 && dep != dep_ok) {
           // Copy warp 0 polls the counter in global memory and tells the other copy warps through a
           // word in shared memory (one reader per CTA on the counter's cache line, not four).
@@ -291,7 +295,15 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
           dep_ok = dep;
           if (warp == 0) BAS_LTRACE(dcall, 1);
         }
+#ifdef BAS_TRACE_PRODUCER
+        if (warp == 0) BAS_LTRACE_TILE(dcall, trace_flushes, 0);
+#endif
         tma_load_2d_hint(s_stage + (size_t)dslot * tile_bytes + p.wslot, &cd->xmap, dj * kBlockK, 0, &hdr->full[dslot], pol_x);
+#ifdef BAS_TRACE_PRODUCER
+        if (warp == 0) BAS_LTRACE_TILE(dcall, trace_flushes, 1);
+        trace_flushes = (dcall == trace_last_call) ? trace_flushes + 1 : 1;
+        trace_last_call = dcall;
+#endif
         ++def_head;
         --ndef;
         return true;
@@ -343,7 +355,11 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
             for (; i < k_mine; i += P) {
               // the slot about to be reused may still hold a tile whose activations were never
               // requested: that one has to go out first, whatever it waits for
-              while (ndef >= per_lap && ok) (void)flush_one(true, false);
+              if (ndef >= per_lap) {
+                while (ndef >= per_lap && ok) (void)flush_one(true, false);
+                while (ndef > 0 && ok && flush_one(false, false)) {   // and with it everything else that has become ready
+                }
+              }
               if (!ok) break;
               if (lap > 0 && !mbar_wait_for(&hdr->empty[slot], (lap - 1) & 1, abort_flag, limit)) {
                 ok = false;
@@ -357,7 +373,8 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               if (ndef == 0 && (dep < 0 || dep == dep_ok)) {
                 tma_load_2d_hint(st + p.wslot, &cd->xmap, j * kBlockK, 0, &hdr->full[slot], pol_x);
               } else {
-                s_def[(def_head + ndef) % kMaxStages] = ((uint32_t)slot << 24) | ((uint32_t)c << 12) | (uint32_t)j;
+                s_def[(def_head + ndef) % kMaxStages] =
+                    make_uint2(((uint32_t)slot << 24) | ((uint32_t)c << 12) | (uint32_t)j, (uint32_t)(dep + 1));
                 ++ndef;
                 while (ndef > 0 && flush_one(false, false)) {
                 }
@@ -433,6 +450,9 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
             }
             tc_fence_after_sync();
             if (w == 0 && fresh && sub == 0) BAS_LTRACE(c, 3);
+#ifndef BAS_TRACE_PRODUCER
+            if (w == 0) BAS_LTRACE_TILE(c, (i - (i % P)) / P, 0);
+#endif
             const uint32_t st = smem_u32(s_stage + (size_t)slot * tile_bytes);
             const uint64_t adesc = umma_desc_kmajor_sw128(st);
             const uint64_t bdesc = umma_desc_kmajor_sw128(st + p.wslot);
@@ -441,6 +461,9 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               umma_f16_ss(d, adesc + (uint64_t)(2 * ks), bdesc + (uint64_t)(2 * ks), idesc, (fresh && ks == 0) ? 0u : 1u);
             fresh = false;
             umma_commit(&hdr->empty[slot]);   // the slot is free once these MMAs have read it
+#ifndef BAS_TRACE_PRODUCER
+            if (w == 0) BAS_LTRACE_TILE(c, (i - (i % P)) / P, 1);
+#endif
             slot += P;
             if (slot >= S) {
               slot -= S;
@@ -704,7 +727,7 @@ inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // Shared memory in front of the ring, as the kernel carves it up.
 size_t list_fixed_smem(int n_calls, int nb_max, int cluster, int bpad) {
   return 128 + round_up(sizeof(ListSmemHeader), 128) + round_up((size_t)n_calls * 4, 128) +
-         round_up((size_t)nb_max * 2, 128) * kLProducers + sizeof(uint32_t) * kMaxStages * kLProducers +
+         round_up((size_t)nb_max * 2, 128) * kLProducers + sizeof(uint2) * kMaxStages * kLProducers +
          (cluster > 1 ? 2 * (size_t)bpad * kTileN * sizeof(float) : 0) + 1024;
 }
 
@@ -942,8 +965,9 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
 #ifdef BAS_TRACE
   p.trace = nullptr;
   p.trace_cta = 0;
-  if (cudaMalloc(&p.trace, sizeof(long long) * BAS_LTRACE_CALLS * BAS_LTRACE_EVENTS) == cudaSuccess)
-    cudaMemset(p.trace, 0, sizeof(long long) * BAS_LTRACE_CALLS * BAS_LTRACE_EVENTS);
+  // [0, CALLS): the last stamp of each event over the CTAs; [CALLS, 2 CALLS): the first (kept by atomicMin, so it starts at all ones)
+  if (cudaMalloc(&p.trace, sizeof(long long) * 2 * BAS_LTRACE_CALLS * BAS_LTRACE_EVENTS) == cudaSuccess)
+    cudaMemset(p.trace, 0, sizeof(long long) * 2 * BAS_LTRACE_CALLS * BAS_LTRACE_EVENTS);
 #endif
   *out = l;
   return BAS_OK;
@@ -996,7 +1020,7 @@ BAS_API int bas_list_info(const bas_list* l, int* ctas, int* cluster, int* slots
 // clears them and chooses the CTA that stamps the next runs.
 BAS_API int bas_list_debug_trace(bas_list* l, long long* out, int n, int next_cta) {
   if (l == nullptr || l->params.trace == nullptr) return 1;
-  const size_t total = (size_t)BAS_LTRACE_CALLS * BAS_LTRACE_EVENTS;
+  const size_t half = (size_t)BAS_LTRACE_CALLS * BAS_LTRACE_EVENTS, total = 2 * half;
   const size_t cnt = (size_t)n < total ? (size_t)n : total;
   cudaError_t e = cudaMemcpy(out, l->params.trace, sizeof(long long) * cnt, cudaMemcpyDeviceToHost);
   if (e == cudaSuccess) e = cudaMemset(l->params.trace, 0, sizeof(long long) * total);

@@ -49,6 +49,16 @@
       p.trace[(call) * BAS_LTRACE_EVENTS + (ev)] = (long long)gt_;                                \
     }                                                                                             \
   } while (0)
+// second half of the array: issuer 0's tiles of a call, stamped when their data is seen (even slots) and
+// when their MMAs have been issued (odd slots), the first four tiles of the call
+#define BAS_LTRACE_TILE(call, k, phase)                                                           \
+  do {                                                                                            \
+    if (p.trace != nullptr && blockIdx.x == p.trace_cta && (call) < BAS_LTRACE_CALLS && (k) < 4) { \
+      unsigned long long gt_;                                                                     \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                                     \
+      p.trace[(BAS_LTRACE_CALLS + (call)) * BAS_LTRACE_EVENTS + 2 * (k) + (phase)] = (long long)gt_; \
+    }                                                                                             \
+  } while (0)
 #else
 #define BAS_TRACE_SET(slot, v) do { } while (0)
 #define BAS_TRACE_ADD(slot, cycles) do { } while (0)
@@ -56,4 +66,5 @@
 #define BAS_TRACE_LAUNCH_BEGIN() do { } while (0)
 #define BAS_TRACE_LAUNCH_END() do { } while (0)
 #define BAS_LTRACE(call, ev) do { } while (0)
+#define BAS_LTRACE_TILE(call, k, phase) do { } while (0)
 #endif
