@@ -39,10 +39,11 @@ namespace bas {
 
 namespace {
 
-constexpr int kLProducers = 4;
-constexpr int kLIssuers = 4;
-constexpr int kLEpiWarp0 = kLProducers + kLIssuers;
-constexpr int kLEpiThreads = 256;
+constexpr int kLProducers = 4;          // copy-issuing warps
+constexpr int kLIssuers = 8;            // MMA-issuing warps available: issuing the four MMAs of a tile costs one thread
+                                        // about 560 cycles (measured), the tensor core 92 to 156; eight threads keep it fed
+constexpr int kLEpiWarp0 = kLProducers + kLIssuers;   // a multiple of 4: an epilogue warp reads the TMEM lane quarter warp % 4
+constexpr int kLEpiThreads = 128;       // one epilogue warp per quarter
 constexpr int kLThreads = 32 * kLEpiWarp0 + kLEpiThreads;
 constexpr int kLMmaSpanBytes = 128 * kRowBytes;
 
@@ -80,7 +81,8 @@ struct ListParams {
   int cluster;               // CTAs per cluster (1, 2, 4)
   int n_clusters;
   int stages;                // ring slots, a multiple of `pairs`
-  int pairs;                 // copy/MMA warp pairs in use
+  int pairs;                 // copy warps in use (copy warp q issues the tiles t with t % pairs == q)
+  int issuers;               // MMA-issuing warps in use, a multiple of `pairs` (issuer w multiplies the tiles t % issuers == w)
   int wslot;                 // bytes reserved per slot for a weight tile (multiple of 1024)
   int nb_max;                // largest K / 64 of the list
   int bf16;
@@ -171,7 +173,8 @@ __device__ __forceinline__ int red_swizzle_l(int nbi, int r) {
 template <int BPAD>
 __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_constant__ ListParams p) {
   constexpr int kXTileBytes = BPAD * 128;
-  constexpr int kAccCols = 2 * kLIssuers * BPAD;                      // two buffers of one accumulator per issuer
+  constexpr int kAccIssuers = (2 * kLIssuers * BPAD <= 512) ? kLIssuers : 4;   // tensor memory has 512 columns
+  constexpr int kAccCols = 2 * kAccIssuers * BPAD;                    // two buffers of one accumulator per issuer
   constexpr int kTmemCols = kAccCols <= 128 ? 128 : kAccCols <= 256 ? 256 : 512;
   const uint32_t kFmt = p.bf16 ? ((1u << 7) | (1u << 10)) : 0u;
   const uint32_t kIdesc = umma_idesc_f16(128, BPAD) | kFmt, kIdesc64 = umma_idesc_f16(64, BPAD) | kFmt;
@@ -192,7 +195,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
   const int C = p.cluster;
   if (C > 1) sp += 2 * (size_t)BPAD * kTileN * sizeof(float);
   uint8_t* s_stage = (uint8_t*)(((uintptr_t)sp + 1023) & ~(uintptr_t)1023);
-  const int S = p.stages, P = p.pairs;
+  const int S = p.stages, P = p.pairs, PI = p.issuers;
   const int tile_bytes = p.wslot + kXTileBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -205,7 +208,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     fence_barrier_init();
   } else if (tid == 64) {
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&hdr->acc_full[b], P);
+      mbar_init(&hdr->acc_full[b], PI);
       mbar_init(&hdr->acc_empty[b], kLEpiThreads / 32);
       mbar_init(&hdr->red_full[b], C * (kLEpiThreads / 32));
     }
@@ -411,9 +414,9 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
   } else if (warp < kLEpiWarp0) {
     // ================================ MMA issuers ================================
     const int w = warp - kLProducers;
-    if (lane == 0 && w < P) {
+    if (lane == 0 && w < PI) {
       bool ok = true;
-      int slot = w, fph = 0, t0mod = 0, u = 0;
+      int slot = w % S, fph = (w / S) & 1, t0mod = 0, u = 0;
       for (int c = 0; c < p.n_calls && ok; ++c) {
         // the call's record: published by copy warp 0 before it issues the call's first tile
         if (ld_acquire_cta_shared_u32(&hdr->calls_staged) <= (unsigned int)c) {
@@ -439,19 +442,33 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
             break;
           }
           tc_fence_after_sync();
-          const uint32_t d = tmem_base + (uint32_t)((b * kLIssuers + w) * BPAD);
+          const uint32_t d = tmem_base + (uint32_t)((b * kAccIssuers + w) * BPAD);
           bool fresh = true;
           int i = w - t0mod;
-          if (i < 0) i += P;
-          for (; i < k_mine; i += P) {
+          if (i < 0) i += PI;
+          for (; i < k_mine; i += PI) {
             if (!mbar_wait_for(&hdr->full[slot], fph, abort_flag, limit)) {
               ok = false;
               break;
             }
-            tc_fence_after_sync();
+            // (no tcgen05 fence here: the tile was written by bulk copies and observed through the barrier; the
+            // fence after the accumulator hand-over above is the only ordering against other threads' tcgen05
+            // operations that the MMAs need, and one fence per tile cost the issuer about 0.3 us each)
             if (w == 0 && fresh && sub == 0) BAS_LTRACE(c, 3);
-#ifndef BAS_TRACE_PRODUCER
-            if (w == 0) BAS_LTRACE_TILE(c, (i - (i % P)) / P, 0);
+#ifdef BAS_TRACE
+            if (w == 0 && p.trace != nullptr && blockIdx.x == p.trace_cta && c < BAS_LTRACE_CALLS && i / PI < 4) {
+              // low bits of the stamp: which of this issuer's next three slots already hold their tile
+              unsigned long long gt_;
+              asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));
+              unsigned long long mask = 0;
+              int s2 = slot, ph2 = fph;
+              for (int q = 0; q < 3; ++q) {
+                s2 += PI;
+                if (s2 >= S) { s2 -= S; ph2 ^= 1; }
+                if (mbar_test_wait(&hdr->full[s2], ph2)) mask |= 1ull << q;
+              }
+              p.trace[(BAS_LTRACE_CALLS + c) * BAS_LTRACE_EVENTS + 2 * (i / PI)] = (long long)((gt_ & ~7ull) | mask);
+            }
 #endif
             const uint32_t st = smem_u32(s_stage + (size_t)slot * tile_bytes);
             const uint64_t adesc = umma_desc_kmajor_sw128(st);
@@ -462,9 +479,9 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
             fresh = false;
             umma_commit(&hdr->empty[slot]);   // the slot is free once these MMAs have read it
 #ifndef BAS_TRACE_PRODUCER
-            if (w == 0) BAS_LTRACE_TILE(c, (i - (i % P)) / P, 1);
+            if (w == 0) BAS_LTRACE_TILE(c, i / PI, 1);
 #endif
-            slot += P;
+            slot += PI;
             if (slot >= S) {
               slot -= S;
               fph ^= 1;
@@ -474,8 +491,8 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
           if (!fresh) umma_commit(&hdr->acc_full[b]);
           else mbar_arrive(&hdr->acc_full[b]);
           if (w == 0 && sub == n_sub - 1) BAS_LTRACE(c, 4);
-          t0mod += k_mine % P;
-          if (t0mod >= P) t0mod -= P;
+          t0mod += k_mine % PI;
+          if (t0mod >= PI) t0mod -= PI;
         }
       }
       if (!ok) {
@@ -487,7 +504,6 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     // ================================ epilogue ================================
     const int q = warp & 3;
     const int et = tid - 32 * kLEpiWarp0;
-    const int eset = et >> 7;
     constexpr int kChunks = BPAD / 16;
     constexpr int kChunks0 = (kChunks + 1) / 2;
     bool ok = true;
@@ -542,16 +558,16 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
           for (int e = 0; e < NV; ++e) v[e] = 0.f;
           if (k_mine > 0) {
 #pragma unroll
-            for (int w0 = 0; w0 < kLIssuers; w0 += IB) {
-              if (w0 < P) {
+            for (int w0 = 0; w0 < kAccIssuers; w0 += IB) {
+              if (w0 < PI) {
                 uint32_t regs[IB][NCH][16];
 #pragma unroll
                 for (int wi = 0; wi < IB; ++wi)
-                  if (w0 + wi < P) {
+                  if (w0 + wi < PI) {
 #pragma unroll
                     for (int cc = 0; cc < NCH; ++cc)
                       tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) +
-                                             (uint32_t)((b * kLIssuers + w0 + wi) * BPAD + (CH0 + cc) * 16),
+                                             (uint32_t)((b * kAccIssuers + w0 + wi) * BPAD + (CH0 + cc) * 16),
                                          regs[wi][cc]);
                   }
                 tmem_ld_wait();
@@ -559,8 +575,8 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
                 for (int wi = 0; wi < IB; ++wi) {
                   const int w = w0 + wi;
                   int first = w - t0mod;      // this issuer's first tile of the unit
-                  if (first < 0) first += P;
-                  if (w < P && first < k_mine) {   // issuer order: the sum never depends on timing
+                  if (first < 0) first += PI;
+                  if (w < PI && first < k_mine) {   // issuer order: the sum never depends on timing
 #pragma unroll
                     for (int cc = 0; cc < NCH; ++cc)
 #pragma unroll
@@ -615,11 +631,12 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
           }
         };
         using std::integral_constant;
+        // the batch rows in two rounds of at most 32 (the registers of one round hold 16 values per row chunk)
         if constexpr (kChunks == 1) {
-          if (eset == 0) emit(integral_constant<int, 0>{}, integral_constant<int, 1>{});
+          emit(integral_constant<int, 0>{}, integral_constant<int, 1>{});
         } else {
-          if (eset == 0) emit(integral_constant<int, 0>{}, integral_constant<int, kChunks0>{});
-          else emit(integral_constant<int, kChunks0>{}, integral_constant<int, kChunks - kChunks0>{});
+          emit(integral_constant<int, 0>{}, integral_constant<int, kChunks0>{});
+          emit(integral_constant<int, kChunks0>{}, integral_constant<int, kChunks - kChunks0>{});
         }
         // the accumulators have been read: the issuers may overwrite this buffer (unit u + 2)
         tc_fence_before_sync();
@@ -643,7 +660,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
           const int sw = red_swizzle_l(nbi, rr);
           const int col = c0 + rr;
           if (rr < wsub && col < n) {
-            for (int qd = eset; 4 * qd * C + rank < batch; qd += 2) {
+            for (int qd = 0; 4 * qd * C + rank < batch; ++qd) {
               float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
               for (int s = 0; s < 4; ++s)
@@ -662,19 +679,19 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
             }
           }
         }
-        t0mod += k_mine % P;
-        if (t0mod >= P) t0mod -= P;
+        t0mod += k_mine % PI;
+        if (t0mod >= PI) t0mod -= PI;
       }
       if (!ok) break;
       // This CTA's part of call c is in global memory: report it, once per CTA.  Every warp arrives on a
       // counter in shared memory (release at CTA scope, after its lanes' stores, which precede the
-      // arrival through the warp barrier); the last of the eight adds one to the call's counter in
+      // arrival through the warp barrier); the last of them adds one to the call's counter in
       // global memory with release semantics at GPU scope, which covers the other warps' stores as well
       // (they happen before it).  Nothing blocks, so a warp that gave up cannot strand the others, and
       // no separate fence is needed: the readers acquire the counter.
       __syncwarp();
       if (et == 0) BAS_LTRACE(c, 6);
-      if (lane == 0 && (atom_add_acq_rel_cta_shared_u32(&hdr->epi_arrived, 1u) & 7u) == 7u) {
+      if (lane == 0 && (atom_add_acq_rel_cta_shared_u32(&hdr->epi_arrived, 1u) % (kLEpiThreads / 32)) == kLEpiThreads / 32 - 1) {
         red_release_gpu_add_u32(p.done + c, 1u);
         BAS_LTRACE(c, 7);
       }
@@ -914,10 +931,10 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
     if (v >= 2 && v < slots) slots = v;
   }
   int pairs = (flags >> 12) & 7;
-  if (pairs < 2 || pairs > kLIssuers || slots / pairs == 0) {
+  if (pairs < 2 || pairs > kLProducers || slots / pairs == 0) {
     pairs = 0;
     int best = 2;
-    for (int cnd = kLIssuers; cnd >= 2; --cnd) {
+    for (int cnd = kLProducers; cnd >= 2; --cnd) {
       const int kept = slots / cnd * cnd;
       if (kept * 4 >= slots * 3) {
         pairs = cnd;
@@ -927,7 +944,12 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
     }
     if (pairs == 0) pairs = best;
   }
-  slots = slots / pairs * pairs;
+  // MMA-issuing warps: as many as tensor memory has accumulators for, a multiple of the copy warps;
+  // the ring is a multiple of both, so that every warp always meets the same slots
+  int issuers = (2 * kLIssuers * bpad <= 512) ? kLIssuers : 4;
+  while (issuers > pairs && (issuers % pairs != 0 || slots / issuers == 0)) issuers -= 1;
+  if (issuers < pairs || issuers % pairs != 0) issuers = pairs;
+  slots = slots / issuers * issuers;
   if (slots < 2) return BAS_ERR_UNSUPPORTED;
 
   bas_list* l = new (std::nothrow) bas_list();
@@ -957,6 +979,7 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
   p.n_clusters = n_clusters;
   p.stages = slots;
   p.pairs = pairs;
+  p.issuers = issuers;
   p.wslot = wslot;
   p.nb_max = nb_max;
   p.bf16 = (flags & BAS_GEMM_BF16) != 0 ? 1 : 0;
