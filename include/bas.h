@@ -262,10 +262,19 @@ typedef struct bas_list_call {
   int64_t ldy;
   int32_t k_host, batch, k, n;
   int32_t depends_on;
-  int32_t reserved;
+  int32_t row_parallel;   /* bas_list_create_tp only: 1 = x / packed are this rank's K-shard, y receives the sum over the ranks */
 } bas_list_call;
 typedef struct bas_list bas_list;
 BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_calls, int flags);
+/* A list for one rank of a tensor-parallel group (bas_tp_*, connected): calls marked row_parallel add
+ * their outputs over the ranks inside the kernel - every rank sends a column tile's fp32 partials to the
+ * one rank that owns the tile, which adds them in rank order, rounds once and sends the 16-bit results to
+ * the others; identical bits on all ranks - so a sharded decode step is one launch per rank.  Every rank
+ * must create the same list (same shapes and order; its own shards) and run it equally often; a
+ * row-parallel call must depend, directly or through other calls, on the row-parallel call before it;
+ * one CTA per column range only.  A wait that runs out: as for bas_gemm_allreduce, the group is dead. */
+typedef struct bas_tp bas_tp;
+BAS_API int bas_list_create_tp(bas_list** out, const bas_list_call* calls, int n_calls, int flags, bas_tp* tp);
 BAS_API int bas_list_run(bas_list* l, void* stream);
 BAS_API int bas_list_read_status(bas_list* l, unsigned int* flags_out, void* stream);
 BAS_API int bas_list_reset(bas_list* l);
@@ -316,7 +325,6 @@ BAS_API int bas_select_topk_noalloc(const void* x_dev, int64_t ldx, int batch, i
  *   bas_tp_disconnect unmaps the peers' areas; bas_tp_destroy does that too and frees this rank's
  *                   own area, which no peer may still have mapped: disconnect on every rank, meet
  *                   (a barrier of the caller's), then destroy */
-typedef struct bas_tp bas_tp;
 #define BAS_TP_HANDLE_BYTES 64
 #define BAS_TP_MAX_RANKS 8
 BAS_API int bas_tp_create(bas_tp** out, int rank, int world, int max_batch, int n);

@@ -91,6 +91,72 @@ def main() -> None:
         if not d <= 4e-3:       # the NCCL path rounds every rank's partial to fp16 first
             failures.append(("stack", d))
     group.close()
+    # The same sums inside a list launch: column-parallel -> row-parallel -> column-parallel -> row-parallel,
+    # every call reading the output of the call before it; the row-parallel outputs (summed over the ranks
+    # inside the kernel: partials to the tile's owner, results back) against the oracle and across ranks.
+    lgroup = ops.ExchangeGroup(dev, 64, 4096)
+    for b, kk, cluster_ok in [(16, 2048, True), (64, 4096, True), (5, 1024, True)]:
+        nmid = 4096
+        x_h = O.make_activations(b, kk, seed=800 + b)
+        wa_h, wb_h = O.make_weight(nmid, kk, seed=801 + b, std=0.03), O.make_weight(4096, nmid, seed=802 + b, std=0.03)
+        wc_h, wd_h = O.make_weight(nmid, 4096, seed=803 + b, std=0.03), O.make_weight(1000, nmid, seed=804 + b, std=0.03)
+        ia, ib = O.random_active_blocks(kk // 64, max(1, kk // 128), seed=805), O.random_active_blocks(nmid // 64, 23, seed=806)
+        ic, idd = O.random_active_blocks(64, 30, seed=807), O.random_active_blocks(nmid // 64, 40, seed=808)
+        n0, n1 = tp.column_shard(nmid, world, rank)                   # this rank's columns of the column-parallel calls
+        b0, b1 = n0 // 64, n1 // 64                                   # = its input blocks of the row-parallel calls
+        def pk(w):
+            return ops.pack_weight(torch.from_numpy(np.ascontiguousarray(w)).to(dev))
+        def local_ids(ids):
+            return torch.from_numpy(np.ascontiguousarray(ids[(ids >= b0) & (ids < b1)] - b0, dtype=np.int32)).to(dev)
+        x = torch.from_numpy(x_h).to(dev)
+        ya = torch.full((b, n1 - n0), float("nan"), dtype=torch.float16, device=dev)
+        yb = torch.full((b, 4096), float("nan"), dtype=torch.float16, device=dev)
+        yc = torch.full((b, n1 - n0), float("nan"), dtype=torch.float16, device=dev)
+        yd = torch.full((b, 1000), float("nan"), dtype=torch.float16, device=dev)
+        lst = ops.GemmList([
+            {"x": x, "packed": pk(wa_h[n0:n1]), "out": ya, "ids": torch.from_numpy(ia).to(dev)},
+            {"x": ya, "packed": pk(wb_h[:, n0:n1]), "out": yb, "ids": local_ids(ib), "depends_on": 0, "row_parallel": True},
+            {"x": yb, "packed": pk(wc_h[n0:n1]), "out": yc, "ids": torch.from_numpy(ic).to(dev), "depends_on": 1},
+            {"x": yc, "packed": pk(wd_h[:, n0:n1]), "out": yd, "ids": local_ids(idd), "depends_on": 2, "row_parallel": True},
+        ], tp=lgroup)
+        for rep in range(3):
+            lst.run()
+        torch.cuda.synchronize()
+        status = lst.read_status()
+        # the oracle, stage by stage on the device's own (gathered) inputs
+        def gathered_cols(t):
+            parts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(parts, t.contiguous())
+            return torch.cat(parts, dim=1).float().cpu().numpy()
+        ya_full = gathered_cols(ya)
+        yc_full = gathered_cols(yc)
+        errs = [O.max_err_ratio(ya_full, O.masked_gemm(x_h, wa_h, ia)),
+                O.max_err_ratio(yb.float().cpu().numpy(), O.masked_gemm(ya_full.astype(np.float16), wb_h, ib)),
+                O.max_err_ratio(yc_full, O.masked_gemm(yb.cpu().numpy(), wc_h, ic)),
+                O.max_err_ratio(yd.float().cpu().numpy(), O.masked_gemm(yc_full.astype(np.float16), wd_h, idd))]
+        same = True
+        for t in (yb, yd):
+            parts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(parts, t)
+            same = same and all(torch.equal(g, parts[0]) for g in parts)
+        if status != 0 or not all(e <= TOL for e in errs) or not same:
+            failures.append(("list exchange", b, kk, status, errs, same))
+        lst.close()
+    # the layer stack as one launch per rank against the per-call in-kernel sums
+    stack = tp.DecodeLinearStack(2, 16, 0.638, dev, world, rank, seed=5, allreduce="in_kernel")
+    par = stack.parity_check(layers=2)
+    lst = stack.make_list()
+    for o in [it[3] for it in stack.items]:
+        o.fill_(float("nan"))
+    lst.run()
+    lst.run()
+    torch.cuda.synchronize()
+    par_list = stack.parity_check_outputs(layers=2)
+    if lst.read_status() != 0 or not par["max_err"] <= TOL or not par_list["max_err"] <= TOL or not par_list["ids_equal"]:
+        failures.append(("stack as a list", par, par_list))
+    lst.close()
+    stack.close()
+    lgroup.close()
     # A rank that stays away: every rank but rank 0 leaves out one call (between steps, nothing of its
     # own in flight).  Rank 0's kernel sends its words, polls for the others' with a bound of a few
     # milliseconds, gives up, reports BAS_DEV_WAIT_EXPIRED through the status word and returns: an error

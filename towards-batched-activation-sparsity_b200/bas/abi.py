@@ -30,7 +30,7 @@ class ListCall(C.Structure):
     _fields_ = [("x_dev", C.c_void_p), ("ldx", C.c_int64), ("packed_dev", C.c_void_p), ("ids_dev", C.c_void_p),
                 ("count_dev", C.c_void_p), ("bitmap_dev", C.c_void_p), ("y_dev", C.c_void_p), ("ldy", C.c_int64),
                 ("k_host", C.c_int32), ("batch", C.c_int32), ("k", C.c_int32), ("n", C.c_int32),
-                ("depends_on", C.c_int32), ("reserved", C.c_int32)]
+                ("depends_on", C.c_int32), ("row_parallel", C.c_int32)]
 
 
 class StepCall(C.Structure):
@@ -94,6 +94,7 @@ _SIGNATURES = {
     "bas_tp_destroy": (None, [_vp]),
     "bas_gemm_allreduce": (_i, [_vp, _vp, _i64, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i64, _vp, _sz, _i, _vp]),
     "bas_list_create": (_i, [C.POINTER(_vp), _vp, _i, _i]),
+    "bas_list_create_tp": (_i, [C.POINTER(_vp), _vp, _i, _i, _vp]),
     "bas_list_run": (_i, [_vp, _vp]),
     "bas_list_read_status": (_i, [_vp, C.POINTER(C.c_uint), _vp]),
     "bas_list_reset": (_i, [_vp]),

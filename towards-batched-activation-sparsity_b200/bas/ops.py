@@ -203,7 +203,10 @@ class GemmList:
     list.  :meth:`run` launches on the current stream, allocates nothing and can be captured in a
     CUDA graph; runs of one list must not overlap."""
 
-    def __init__(self, calls, *, cluster: int = 0, pairs: int = 0, max_ctas: int = 0, min_units: int = 0):
+    def __init__(self, calls, *, cluster: int = 0, pairs: int = 0, max_ctas: int = 0, min_units: int = 0, tp=None):
+        """``tp``: an :class:`ExchangeGroup`; calls with ``row_parallel=True`` then hold this rank's K-shard
+        and their outputs are summed over the group's ranks inside the kernel (every rank builds and runs
+        the same list; such a call must depend on the row-parallel call before it)."""
         import ctypes
 
         calls = list(calls)
@@ -243,12 +246,17 @@ class GemmList:
             a.y_dev, a.ldy = out.data_ptr(), out.stride(0)
             a.k_host, a.batch, a.k, a.n = k_host, x.shape[0], x.shape[1], out.shape[1]
             a.depends_on = int(c.get("depends_on", -1))
+            a.row_parallel = 1 if c.get("row_parallel") else 0
             self._keep.append((x, out, packed, ids, bitmap, count))
         self.n_calls = len(calls)
         self.handle = ctypes.c_void_p()
         flags = (GEMM_BF16 if dtype == torch.bfloat16 else 0) | (int(cluster) << 8) | (int(pairs) << 12) | (int(max_ctas) << 16) | (int(min_units) << 24)
+        self.tp = tp
         with torch.cuda.device(self.device):
-            check(lib.bas_list_create(ctypes.byref(self.handle), arr, len(calls), flags), "bas_list_create")
+            if tp is not None:
+                check(lib.bas_list_create_tp(ctypes.byref(self.handle), arr, len(calls), flags, tp.handle), "bas_list_create_tp")
+            else:
+                check(lib.bas_list_create(ctypes.byref(self.handle), arr, len(calls), flags), "bas_list_create")
 
     def run(self) -> None:
         with torch.cuda.device(self.device):

@@ -267,13 +267,15 @@ class DecodeLinearStack:
                         "gate_up_proj": "o_proj", "down_proj": ("up_proj", "gate_up_proj")}
 
     def make_list(self, dependencies: bool = True, **tuning):
-        """The whole step as one persistent launch (``ops.GemmList``): single GPU only.  With
-        ``dependencies`` every call waits for the call whose output its input is in the model; without,
-        no call waits for any other (a probe of the kernel's streaming rate)."""
+        """The whole step as one persistent launch per rank (``ops.GemmList``).  With ``dependencies``
+        every call waits for the call whose output its input is in the model; without, no call waits
+        for any other (a probe of the kernel's streaming rate; single GPU only).  On several ranks the
+        stack must have been built with ``allreduce="in_kernel"``: the row-parallel calls then add their
+        outputs over the ranks inside the list kernel, through the stack's exchange group."""
         from . import ops
 
-        if self.world != 1:
-            raise ValueError("the one-launch step needs the sums over ranks inside it: single GPU only")
+        if self.world != 1 and (self.exchange is None or not dependencies):
+            raise ValueError("on several ranks the one-launch step needs allreduce='in_kernel' and the dependencies")
         last = {}
         calls = []
         for lin, x, bitmap, out, n_keep in self.items:
@@ -283,8 +285,13 @@ class DecodeLinearStack:
                 for name in (want if isinstance(want, tuple) else (want,)):
                     dep = max(dep, last.get(name, -1))
             last[lin.spec.name] = len(calls)
-            calls.append({"x": x, "packed": lin.packed, "out": out, "bitmap": bitmap, "k_host": n_keep, "depends_on": dep})
-        return ops.GemmList(calls, **tuning)
+            row = lin.spec.parallel == "row"
+            xs = x[:, lin.b0 * BLOCK_K: lin.b0 * BLOCK_K + lin.k_local] if row else x
+            nb_all = bitmap.numel()
+            hint = max(1, (int(n_keep) * (lin.b1 - lin.b0) + nb_all - 1) // nb_all)
+            calls.append({"x": xs, "packed": lin.packed, "out": out, "bitmap": bitmap[lin.b0:lin.b1], "k_host": hint,
+                          "depends_on": dep, "row_parallel": row and self.world > 1})
+        return ops.GemmList(calls, tp=self.exchange if self.world > 1 else None, **tuning)
 
     def step(self) -> None:
         import torch.distributed as dist

@@ -135,13 +135,7 @@ int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream) {
 // ---------------------------------------------------------------------------------------------
 // exchange areas of a tensor-parallel group (one process per GPU, all on one box)
 // ---------------------------------------------------------------------------------------------
-struct bas_tp {
-  int rank = 0, world = 0, max_batch = 0, n = 0, npad = 0;
-  size_t bytes = 0;
-  unsigned char* area[kTpMaxRanks] = {};   // area[rank] is this rank's own allocation
-  bool opened[kTpMaxRanks] = {};
-};
-
+// (struct bas_tp: bas_kernels.cuh)
 static size_t tp_area_bytes(int world, int max_batch, int npad) {
   return (size_t)kTpHeaderBytes + 2 * 8 * (size_t)world * (size_t)max_batch * (size_t)npad;
 }

@@ -147,3 +147,12 @@ int record_cuda_error(cudaError_t e);
 void* tensor_map_encoder();
 
 }  // namespace bas
+
+// One rank's view of a tensor-parallel group's exchange areas (bas_tp_* in bas_api.cu; the list kernel's
+// host side reads it too).
+struct bas_tp {
+  int rank = 0, world = 0, max_batch = 0, n = 0, npad = 0;
+  size_t bytes = 0;
+  unsigned char* area[bas::kTpMaxRanks] = {};   // area[rank] is this rank's own allocation
+  bool opened[bas::kTpMaxRanks] = {};
+};

@@ -62,7 +62,8 @@ struct alignas(128) ListCallDev {
   int range_off;               // the first of them (the others follow, modulo the cluster count)
   int dep;                     // call whose completion X waits for, or -1
   unsigned int dep_contrib;    // CTAs that report the completion of call `dep`
-  int pad[5];
+  int tp_index;                // row-parallel calls: position among the list's exchanges (0, 1, ...); else -1
+  int pad[4];
 };
 static_assert(sizeof(ListCallDev) == 256, "call descriptor layout");
 
@@ -88,6 +89,8 @@ struct ListParams {
   int bf16;
   int stall_call;            // tests of the expiry path: this call's dependency is never seen complete (-1: off)
   long long wait_cycles;     // bound of every wait
+  TpExchange tp;             // lists with row-parallel calls: the group's exchange areas (world 0 = none)
+  int n_tp_calls;            // exchanges per run
 #ifdef BAS_TRACE
   long long* trace;          // diagnostic build only
   int trace_cta;
@@ -170,7 +173,9 @@ __device__ __forceinline__ int red_swizzle_l(int nbi, int r) {
   return nbi == 32 ? (r & 7) : nbi == 16 ? ((r >> 1) & 3) : nbi == 8 ? ((r >> 2) & 1) : 0;
 }
 
-template <int BPAD>
+// TP: the variant for lists with row-parallel calls, whose epilogue exchanges partial sums with the other
+// ranks of a box (a template parameter, so that the plain kernel carries none of that code).
+template <int BPAD, bool TP>
 __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_constant__ ListParams p) {
   constexpr int kXTileBytes = BPAD * 128;
   constexpr int kAccIssuers = (2 * kLIssuers * BPAD <= 512) ? kLIssuers : 4;   // tensor memory has 512 columns
@@ -234,6 +239,9 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
   // may be written by the kernel before this one in the stream.
   pdl_wait();
   const unsigned int epoch = __ldcg(&p.hdr->epoch);
+  // exchanges the group has completed before this run: exchange k of the list carries number tp_base + k + 1
+  unsigned int tp_base = 0u;
+  if constexpr (TP) tp_base = __ldcg((const unsigned int*)p.tp.own);
 
   const int rank = (C > 1) ? (int)cluster_ctarank() : 0;
   const int cid = blockIdx.x / C;
@@ -536,6 +544,24 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
       __half* y = ldg_ptr(&cd->y);
       const long long ldy = __ldg(&cd->ldy);
       const int batch = __ldg(&cd->batch), n = __ldg(&cd->n);
+      // Row-parallel call: the tile's fp32 partials of every rank go to ONE rank (the tile's owner, by
+      // tile index), which adds them in rank order, rounds once and sends the 16-bit results to the
+      // others (reduce-scatter, then gather): two NVLink traversals, 1 / world of the bytes of sending
+      // every partial to every rank.  All words are 64-bit {payload, exchange number}: a reader polls
+      // its own memory until the number is the current one; no flags, no fences.
+      int tp_k = -1, tp_owner = 0;
+      unsigned int tp_epoch = 0u;
+      size_t tp_buf = 0;          // word offset of the current receive buffer inside any rank's area
+      if constexpr (TP) {
+        tp_k = __ldg(&cd->tp_index);
+        if (tp_k >= 0) {
+          tp_epoch = tp_base + (unsigned int)tp_k + 1u;
+          tp_buf = (size_t)kTpHeaderBytes / 8 + (size_t)(tp_epoch & 1u) * (size_t)p.tp.world * (size_t)p.tp.src_words;
+          int range = cid - __ldg(&cd->range_off);
+          if (range < 0) range += p.n_clusters;
+          tp_owner = range % p.tp.world;
+        }
+      }
 
       for (int sub = 0; sub < sh.n_sub && ok; ++sub, ++u) {
         const int b = u & 1;
@@ -586,7 +612,18 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               }
             }
           }
-          if (C == 1) {
+          if (TP && tp_k >= 0) {
+            // this rank's partial of column c0 + r, to the tile's owner (padded columns too: they are zero)
+            if (r < wsub) {
+              unsigned long long* dst = (unsigned long long*)p.tp.area[tp_owner] + tp_buf +
+                                        (size_t)p.tp.rank * (size_t)p.tp.src_words + (size_t)(c0 + r);
+#pragma unroll
+              for (int e = 0; e < NV; ++e)
+                if (16 * CH0 + e < batch)
+                  st_relaxed_sys_u64(dst + (size_t)(16 * CH0 + e) * (size_t)p.tp.ldp,
+                                     ((unsigned long long)tp_epoch << 32) | (unsigned long long)__float_as_uint(v[e]));
+            }
+          } else if (C == 1) {
             const int col = c0 + r;
             if (r < wsub && col < n) {
 #pragma unroll
@@ -643,6 +680,75 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         __syncwarp();
         if (lane == 0) mbar_arrive(&hdr->acc_empty[b]);
 
+        if (TP && tp_k >= 0) {
+          // ---- the exchange: (row, column pair) elements of the tile dealt out over the 128 threads ----
+          const int ppr = wsub >> 1, total = batch * ppr;
+          const int world = p.tp.world, me = p.tp.rank;
+          const unsigned long long* own = (const unsigned long long*)p.tp.own + tp_buf;
+          const long long t_start = clock64();
+          bool good = true;
+          for (int e0 = et; e0 < total && good; e0 += kLEpiThreads) {
+            const int row = e0 / ppr, pc = e0 - row * ppr;
+            const int col = c0 + 2 * pc;
+            unsigned short h0, h1;
+            if (tp_owner == me) {
+              // owner: wait for every rank's two partials, add them in rank order, round, keep, send on
+              const size_t off = (size_t)row * (size_t)p.tp.ldp + (size_t)col;
+              unsigned long long wa[kTpMaxRanks], wb[kTpMaxRanks];
+#pragma unroll
+              for (int q = 0; q < kTpMaxRanks; ++q) {
+                wa[q] = (q < world) ? ld_relaxed_sys_u64(own + (size_t)q * (size_t)p.tp.src_words + off) : 0ull;
+                wb[q] = (q < world) ? ld_relaxed_sys_u64(own + (size_t)q * (size_t)p.tp.src_words + off + 1) : 0ull;
+              }
+              float sa = 0.f, sb = 0.f;
+#pragma unroll
+              for (int q = 0; q < kTpMaxRanks; ++q)
+                if (q < world) {
+                  while ((unsigned int)(wa[q] >> 32) != tp_epoch || (unsigned int)(wb[q] >> 32) != tp_epoch) {
+                    if (*abort_flag != 0 || clock64() - t_start > limit) {
+                      good = false;
+                      break;
+                    }
+                    __nanosleep(32);
+                    wa[q] = ld_relaxed_sys_u64(own + (size_t)q * (size_t)p.tp.src_words + off);
+                    wb[q] = ld_relaxed_sys_u64(own + (size_t)q * (size_t)p.tp.src_words + off + 1);
+                  }
+                  sa += __uint_as_float((unsigned int)wa[q]);
+                  sb += __uint_as_float((unsigned int)wb[q]);
+                }
+              if (!good) break;
+              h0 = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sa)) : __half_as_ushort(__float2half_rn(sa));
+              h1 = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sb)) : __half_as_ushort(__float2half_rn(sb));
+              const unsigned long long word = ((unsigned long long)tp_epoch << 32) | ((unsigned long long)h1 << 16) | (unsigned long long)h0;
+              // results travel in the words [row][c0 + pair] of the slot "source = owner" of every other rank
+              const size_t roff = (size_t)me * (size_t)p.tp.src_words + (size_t)row * (size_t)p.tp.ldp + (size_t)(c0 + pc);
+#pragma unroll 1
+              for (int q = 0; q < world; ++q)
+                if (q != me) st_relaxed_sys_u64((unsigned long long*)p.tp.area[q] + tp_buf + roff, word);
+            } else {
+              const unsigned long long* src = own + (size_t)tp_owner * (size_t)p.tp.src_words + (size_t)row * (size_t)p.tp.ldp + (size_t)(c0 + pc);
+              unsigned long long word = ld_relaxed_sys_u64(src);
+              while ((unsigned int)(word >> 32) != tp_epoch) {
+                if (*abort_flag != 0 || clock64() - t_start > limit) {
+                  good = false;
+                  break;
+                }
+                __nanosleep(32);
+                word = ld_relaxed_sys_u64(src);
+              }
+              if (!good) break;
+              h0 = (unsigned short)(word & 0xffffull);
+              h1 = (unsigned short)((word >> 16) & 0xffffull);
+            }
+            unsigned short* yrow = reinterpret_cast<unsigned short*>(y) + (size_t)row * (size_t)ldy;
+            if (col < n) yrow[col] = h0;
+            if (col + 1 < n) yrow[col + 1] = h1;
+          }
+          if (!__all_sync(0xffffffffu, good)) {
+            ok = false;
+            break;
+          }
+        }
         if (C > 1) {
           // tell every owner that this warp's pushes are on their way (release at cluster scope, after
           // the warp's stores), then wait until all warps of all CTAs of the cluster have told this one
@@ -729,6 +835,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     if (atomicAdd(&p.hdr->arrived, 1u) == gridDim.x - 1) {
       p.hdr->arrived = 0u;
       p.hdr->epoch = epoch + 1u;
+      if constexpr (TP) ((unsigned int*)p.tp.own)[0] = tp_base + (unsigned int)p.n_tp_calls;
       __threadfence();
     }
   }
@@ -755,7 +862,8 @@ cudaError_t list_prepare_kernel() {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
-  e = cudaFuncSetAttribute(umma_list_kernel<BPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  e = cudaFuncSetAttribute(umma_list_kernel<BPAD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_list_kernel<BPAD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64) done[dev] = true;
   return cudaSuccess;
@@ -777,13 +885,13 @@ int list_resident_clusters(int cluster, size_t smem, int sm_count) {
   int n = 0;
   if (cluster == 1) {
     int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, umma_list_kernel<BPAD>, kLThreads, smem) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, umma_list_kernel<BPAD, false>, kLThreads, smem) != cudaSuccess) {
       (void)cudaGetLastError();
       return 0;
     }
     return per_sm > 0 ? sm_count : 0;
   }
-  if (cudaOccupancyMaxActiveClusters(&n, umma_list_kernel<BPAD>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, umma_list_kernel<BPAD, false>, &cfg) != cudaSuccess) {
     (void)cudaGetLastError();
     n = 0;
   }
@@ -792,7 +900,9 @@ int list_resident_clusters(int cluster, size_t smem, int sm_count) {
 
 template <int BPAD>
 cudaError_t list_launch(const ListParams& p, size_t smem, cudaStream_t stream) {
-  return launch_with_pdl(umma_list_kernel<BPAD>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p);
+  if (p.tp.world > 0)
+    return launch_with_pdl(umma_list_kernel<BPAD, true>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p);
+  return launch_with_pdl(umma_list_kernel<BPAD, false>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p);
 }
 
 }  // namespace
@@ -826,7 +936,18 @@ inline bool list_aligned16(const void* ptr) { return (((uintptr_t)ptr) & 15u) ==
 
 extern "C" {
 
+static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_calls, int flags, const bas_tp* tp);
+
 BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_calls, int flags) {
+  return list_create_impl(out, calls, n_calls, flags, nullptr);
+}
+
+BAS_API int bas_list_create_tp(bas_list** out, const bas_list_call* calls, int n_calls, int flags, bas_tp* tp) {
+  if (tp == nullptr) return BAS_ERR_INVALID_ARGUMENT;
+  return list_create_impl(out, calls, n_calls, flags, tp);
+}
+
+static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_calls, int flags, const bas_tp* tp) {
   if (out == nullptr || calls == nullptr || n_calls <= 0) return BAS_ERR_INVALID_ARGUMENT;
   *out = nullptr;
   if (n_calls > BAS_LIST_MAX_CALLS) return BAS_ERR_UNSUPPORTED;
@@ -852,6 +973,19 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
     if (!list_aligned16(a.x_dev) || !list_aligned16(a.packed_dev) || (a.ldx & 7) != 0 || (a.k & 7) != 0)
       return BAS_ERR_INVALID_ARGUMENT;
     if (a.depends_on < -1 || a.depends_on >= c) return BAS_ERR_INVALID_ARGUMENT;
+    if (a.row_parallel != 0) {
+      // an exchange needs a connected group that holds this output, and - the two receive buffers alternate - the
+      // exchange before it must be complete on every rank before this one starts: it has to depend on it
+      if (tp == nullptr || a.row_parallel != 1 || a.batch > tp->max_batch || a.n > tp->n) return BAS_ERR_INVALID_ARGUMENT;
+      int prev = -1;
+      for (int q = c - 1; q >= 0 && prev < 0; --q)
+        if (calls[q].row_parallel != 0) prev = q;
+      if (prev >= 0) {
+        int d = a.depends_on;
+        while (d > prev) d = calls[d].depends_on;
+        if (d != prev) return BAS_ERR_INVALID_ARGUMENT;
+      }
+    }
     if (a.batch > max_batch) max_batch = a.batch;
     if (nb > nb_max) nb_max = nb;
   }
@@ -866,6 +1000,11 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
   const int forced = (flags >> 8) & 7;
   const int cta_cap = ((flags >> 16) & 0xff) != 0 ? ((flags >> 16) & 0xff) : sm_count;
   if (forced != 0 && forced != 1 && forced != 2 && forced != 4) return BAS_ERR_INVALID_ARGUMENT;
+  if (tp != nullptr) {
+    if (forced > 1) return BAS_ERR_INVALID_ARGUMENT;           // the exchange is built for one CTA per range
+    for (int q = 0; q < tp->world; ++q)
+      if (tp->area[q] == nullptr) return BAS_ERR_INVALID_ARGUMENT;   // bas_tp_connect has not run
+  }
   const int cluster = forced != 0 ? forced : 1;
   int n_clusters = by_bpad(bpad, [&](auto b) { return list_resident_clusters<decltype(b)::value>(cluster, kLSmemBudget, sm_count); });
   if (n_clusters > cta_cap / cluster) n_clusters = cta_cap / cluster;
@@ -874,7 +1013,7 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
   // ---- per call: the clusters that take part, and the widest column tile of the list ----
   const int min_units = ((flags >> 24) & 0x3f) != 0 ? ((flags >> 24) & 0x3f) : 8;   // tuning knob
   std::vector<ListCallDev> host((size_t)n_calls);
-  int off = 0, tw_max = 8;
+  int off = 0, tw_max = 8, n_tp = 0;
   for (int c = 0; c < n_calls; ++c) {
     const bas_list_call& a = calls[c];
     ListCallDev& d = host[(size_t)c];
@@ -903,6 +1042,7 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
     d.ranges = ranges;
     d.range_off = (ranges < n_clusters) ? off : 0;
     if (ranges < n_clusters) off = (off + ranges) % n_clusters;
+    d.tp_index = a.row_parallel != 0 ? n_tp++ : -1;
     d.dep = a.depends_on;
     d.dep_contrib = a.depends_on >= 0 ? (unsigned int)(host[(size_t)a.depends_on].ranges * cluster) : 0u;
     // X[batch, K]: inner dimension K, box {64 channels, bpad rows}, 128-byte swizzle, zeros out of range
@@ -985,6 +1125,16 @@ BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_ca
   p.bf16 = (flags & BAS_GEMM_BF16) != 0 ? 1 : 0;
   p.stall_call = -1;
   p.wait_cycles = wait_cycles_now();
+  p.tp = TpExchange{};
+  p.n_tp_calls = n_tp;
+  if (tp != nullptr && n_tp > 0) {
+    p.tp.world = tp->world;
+    p.tp.rank = tp->rank;
+    p.tp.ldp = tp->npad;
+    p.tp.src_words = (long long)tp->max_batch * tp->npad;
+    p.tp.own = tp->area[tp->rank];
+    for (int q = 0; q < tp->world; ++q) p.tp.area[q] = tp->area[q];
+  }
 #ifdef BAS_TRACE
   p.trace = nullptr;
   p.trace_cta = 0;
