@@ -47,6 +47,10 @@ typedef enum bas_status {
 /* Bits of the device status word (first 4 bytes of every GEMM workspace). */
 #define BAS_DEV_BAD_BLOCK_ID 1u  /* an id outside [0, K/64) was skipped */
 #define BAS_DEV_WAIT_EXPIRED 2u  /* a bounded barrier wait ran out; the output is not valid */
+/* With it the list kernel leaves a detail in the upper bits, for diagnosis (test for BAS_DEV_WAIT_EXPIRED itself):
+ * bits 16-27 the index of the earliest call in which a wait ran out, bits 8-12 which wait of that call:
+ * 0x100 a copy warp (a dependency or a ring slot), 0x200 an MMA-issuing warp, 0x400 an epilogue warp,
+ * 0x800 / 0x1000 the exchange between ranks, on the rank that adds a tile / on a rank that receives it. */
 
 typedef enum bas_score_kind {
   BAS_SCORE_NORM = 0,  /* mean_b ||x_b,block||_2 : scripts/bench_roundrobin_e2e_decode.py:103-105 */

@@ -156,6 +156,30 @@ def main() -> None:
         failures.append(("stack as a list", par, par_list))
     lst.close()
     stack.close()
+    # Shards of unequal size, as eight ranks get them from the 7B shapes (43 column groups and 43 blocks
+    # over two ranks: 21 / 22), and a rank whose K-shard of o_proj holds no active block at all: it
+    # still has to send its zeros for every tile.
+    small = tuple(tp.LinearSpec(s.name, {4096: 1024, 11008: 2752}[s.n], {4096: 1024, 11008: 2752}[s.k], s.parallel, s.dist)
+                  for s in tp.LLAMA2_7B_LAYER)
+    stack = tp.DecodeLinearStack(2, 16, 0.638, dev, world, rank, seed=7, allreduce="in_kernel", specs=small)
+    bm_o = stack._shared["o_proj"][1]
+    keep = int(bm_o.sum())
+    bm_o.zero_()
+    bm_o[:keep] = 1                       # all active blocks in the first ranks' shards
+    par = stack.parity_check(layers=2)
+    lst = stack.make_list()
+    for o in [it[3] for it in stack.items]:
+        o.fill_(float("nan"))
+    for _ in range(3):
+        lst.run()
+    torch.cuda.synchronize()
+    par_list = stack.parity_check_outputs(layers=2)
+    status = lst.read_status()            # reading clears it
+    if status != 0 or not par["max_err"] <= TOL or not par_list["max_err"] <= TOL or not par_list["ids_equal"]:
+        failures.append(("uneven shards as a list", hex(status), par, par_list))
+        print(f"rank {rank}: uneven shards as a list: status {status:#x}", flush=True)
+    lst.close()
+    stack.close()
     lgroup.close()
     # A rank that stays away: every rank but rank 0 leaves out one call (between steps, nothing of its
     # own in flight).  Rank 0's kernel sends its words, polls for the others' with a bound of a few

@@ -134,7 +134,8 @@ class DecodeLinearStack:
     ``allreduce``: how the row-parallel partial outputs are summed over the ranks."""
 
     def __init__(self, layers: int, batch: int, sparsity: float, device, world: int = 1, rank: int = 0,
-                 seed: int = 0, group=None, fuse_shared_inputs: bool = False, allreduce: str = "nccl"):
+                 seed: int = 0, group=None, fuse_shared_inputs: bool = False, allreduce: str = "nccl",
+                 specs=LLAMA2_7B_LAYER):
         import torch
 
         from . import ops
@@ -145,7 +146,8 @@ class DecodeLinearStack:
         self.world, self.rank, self.group, self.batch = world, rank, group, batch
         # "in_kernel": o and down add their partial outputs over the ranks inside the contraction
         # kernel (peer stores over NVLink, each rank polls its own area); "nccl": one all-reduce call after each of them
-        self.exchange = ops.ExchangeGroup(device, batch, max(s.n for s in LLAMA2_7B_LAYER if s.parallel == "row"),
+        self.specs = tuple(specs)    # the projections of one layer, by the seven names of LLAMA2_7B_LAYER
+        self.exchange = ops.ExchangeGroup(device, batch, max(s.n for s in self.specs if s.parallel == "row"),
                                           group) if allreduce == "in_kernel" else None
         # True: every call declares its input stable, which the stack's pre-generated inputs literally
         # are (a throughput probe over the seven shapes; a model's o, down, q and gate depend on the
@@ -176,7 +178,7 @@ class DecodeLinearStack:
         for li in range(layers):
             pending = {}     # fused group name -> [spec, weights]
             pending_si = {}
-            for si, spec in enumerate(LLAMA2_7B_LAYER):
+            for si, spec in enumerate(self.specs):
                 gen.manual_seed(seed * 1_000_003 + li * 16 + si)
                 w = (torch.randn(spec.n, spec.k, generator=gen, device=device, dtype=torch.float32) * 0.02).half()
                 group_name = fused_of.get(spec.name)
@@ -202,6 +204,11 @@ class DecodeLinearStack:
                 self.items.append((lin, x, bitmap, out, n_keep))
                 self.active_bytes += n_keep * BLOCK_K * spec.n * 2
         torch.cuda.synchronize(device)
+        if world > 1:
+            # the ranks have generated and packed their weights at their own pace: meet before the first
+            # step, whose exchange kernels wait (bounded) for one another inside the kernel
+            import torch.distributed as dist
+            dist.barrier(group=group)
 
     def close(self) -> None:
         """Collective when the stack sums inside the kernel: releases the exchange areas."""
@@ -235,7 +242,7 @@ class DecodeLinearStack:
             xm = x.float() * mask
             parts = []
             for si, (a, b) in zip(sis, lin.part_bounds if lin.spec.parallel == "column" else [(0, lin.spec.n)]):
-                spec = LLAMA2_7B_LAYER[si]
+                spec = self.specs[si]
                 gen.manual_seed(self.seed * 1_000_003 + li * 16 + si)
                 w = (torch.randn(spec.n, spec.k, generator=gen, device=dev, dtype=torch.float32) * 0.02).half()
                 parts.append((xm @ w.float().t())[:, a:b])

@@ -46,6 +46,27 @@ constexpr int kLEpiWarp0 = kLProducers + kLIssuers;   // a multiple of 4: an epi
 constexpr int kLEpiThreads = 128;       // one epilogue warp per quarter
 constexpr int kLThreads = 32 * kLEpiWarp0 + kLEpiThreads;
 constexpr int kLMmaSpanBytes = 128 * kRowBytes;
+// Upper bits of the status word: the role of the first wait of a CTA that ran out (diagnosis only).
+constexpr unsigned int kWhereCopyWarp = 0x100u, kWhereIssuer = 0x200u, kWhereEpilogue = 0x400u,
+                       kWhereExchangeOwner = 0x800u, kWhereExchangeReader = 0x1000u;
+// A wait that runs out leaves its role and its call index (bits 16-27) in the status word.  Of several, the one
+// in the earliest call stays: later calls only wait for what that one did not deliver, but their waits may
+// have started, and so run out, before it.  Roles of the same call are added together.
+__device__ __forceinline__ void record_expiry(unsigned int* status, unsigned int where, int call) {
+  const unsigned int c = (unsigned int)min(call, 4095);
+  unsigned int old = *(volatile unsigned int*)status;
+  for (;;) {
+    const unsigned int old_call = (old >> 16) & 0xfffu;
+    unsigned int want;
+    if ((old & BAS_DEV_WAIT_EXPIRED) == 0u || c < old_call) want = (old & 0xffu) | BAS_DEV_WAIT_EXPIRED | where | (c << 16);
+    else if (c == old_call) want = old | where;
+    else return;
+    if (want == old) return;
+    const unsigned int seen = atomicCAS(status, old, want);
+    if (seen == old) return;
+    old = seen;
+  }
+}
 
 // Device-side description of one call, written once by bas_list_create.
 struct alignas(128) ListCallDev {
@@ -333,7 +354,9 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
       };
       have_raw = prefetch_ids(cur, raw);
 
+      int c_at = 0;   // the call this role is in (for the status detail of a wait that runs out)
       for (int c = 0; c < p.n_calls && ok; ++c) {
+        c_at = c;
         const ListCallDev* cd = p.calls + c;
         const CallRegs nn = load_call_regs(p.calls + (c + 2 < p.n_calls ? c + 2 : c));   // in flight during this call
         const int units = (int)cur.d.x, ranges = (int)cur.d.y, range_off = (int)cur.d.z, dep = (int)cur.d.w;
@@ -411,8 +434,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
       if (lane == 0) {
         while (ndef > 0 && ok) (void)flush_one(true, false);
         if (!ok) {
-          atomicOr(&p.hdr->status, BAS_DEV_WAIT_EXPIRED);
-          hdr->abort_flag = 1;
+          if (atomicExch(&hdr->abort_flag, 1) == 0) record_expiry(&p.hdr->status, kWhereCopyWarp, c_at);   // the first of this CTA: the others only follow it
           while (ndef > 0) (void)flush_one(false, true);
         }
       }
@@ -425,7 +447,9 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     if (lane == 0 && w < PI) {
       bool ok = true;
       int slot = w % S, fph = (w / S) & 1, t0mod = 0, u = 0;
+      int c_at = 0;   // the call this role is in (for the status detail of a wait that runs out)
       for (int c = 0; c < p.n_calls && ok; ++c) {
+        c_at = c;
         // the call's record: published by copy warp 0 before it issues the call's first tile
         if (ld_acquire_cta_shared_u32(&hdr->calls_staged) <= (unsigned int)c) {
           const long long t_start = clock64();
@@ -504,8 +528,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         }
       }
       if (!ok) {
-        atomicOr(&p.hdr->status, BAS_DEV_WAIT_EXPIRED);
-        hdr->abort_flag = 1;
+        if (atomicExch(&hdr->abort_flag, 1) == 0) record_expiry(&p.hdr->status, kWhereIssuer, c_at);   // the first of this CTA: the others only follow it
       }
     }
   } else {
@@ -515,8 +538,11 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     constexpr int kChunks = BPAD / 16;
     constexpr int kChunks0 = (kChunks + 1) / 2;
     bool ok = true;
+    unsigned int where = kWhereEpilogue;     // which of the epilogue's waits ran out first (status bits 8..)
     int t0mod = 0, u = 0;
+    int c_at = 0;   // the call this role is in (for the status detail of a wait that runs out)
     for (int c = 0; c < p.n_calls && ok; ++c) {
+      c_at = c;
       {
         bool ready = ld_acquire_cta_shared_u32(&hdr->calls_staged) > (unsigned int)c;
         if (!__all_sync(0xffffffffu, ready)) {
@@ -560,6 +586,28 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
           int range = cid - __ldg(&cd->range_off);
           if (range < 0) range += p.n_clusters;
           tp_owner = range % p.tp.world;
+          // No active block on this rank: no activation copy made this CTA wait for the call's dependency, yet
+          // its zeros must not leave before it.  The exchange before last used the same words, and only the
+          // chain of dependencies from one row-parallel call to the next says that every rank has read them.
+          const int dep = __ldg(&cd->dep);
+          if (k_mine == 0 && dep >= 0) {
+            const unsigned int target = (epoch + 1u) * __ldg(&cd->dep_contrib);
+            bool ready = true;
+            if (lane == 0) {
+              const long long t_start = clock64();
+              while (c == p.stall_call || (int)(ld_acquire_gpu_u32(p.done + dep) - target) < 0) {
+                if (*abort_flag != 0 || clock64() - t_start > limit) {
+                  ready = false;
+                  break;
+                }
+                __nanosleep(100);
+              }
+            }
+            if (!__all_sync(0xffffffffu, ready)) {
+              ok = false;
+              break;
+            }
+          }
         }
       }
 
@@ -745,6 +793,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
             if (col + 1 < n) yrow[col + 1] = h1;
           }
           if (!__all_sync(0xffffffffu, good)) {
+            where = (tp_owner == p.tp.rank) ? kWhereExchangeOwner : kWhereExchangeReader;
             ok = false;
             break;
           }
@@ -803,8 +852,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
       }
     }
     if (!ok) {
-      atomicOr(&p.hdr->status, BAS_DEV_WAIT_EXPIRED);
-      hdr->abort_flag = 1;
+      if (atomicExch(&hdr->abort_flag, 1) == 0) record_expiry(&p.hdr->status, where, c_at);   // the first of this CTA: the others only follow it
     }
   }
 
