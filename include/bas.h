@@ -246,6 +246,17 @@ BAS_API int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_d
  *   flags of bas_list_create: BAS_GEMM_BF16 and the tuning bits 8-10 (cluster size), 12-14 (warp
  *   pairs) and 16-23 (upper bound on the CTAs) of bas_gemm_ex.
  *
+ * Selection inside the list (a decode step computes every mask from the activation it is about to
+ * multiply: scripts/bench_roundrobin_e2e_decode.py:90-113, 331-360).  An entry with op = BAS_LIST_SELECT is
+ * bas_select_topk as part of the launch: x_dev / ldx / batch / k (a multiple of 64) describe X, k_host is the
+ * number of blocks to keep, score_kind the score, depends_on the call that writes X; every other field is
+ * zero.  Its CTAs score the blocks with the arithmetic of bas_select_topk (same bits) as soon as X is
+ * complete.  A contraction whose mask_entry names that entry (same X: same batch, same depends_on) ranks the
+ * scores at its call boundary - (score descending, id ascending), NaN first - and runs with the kept blocks in
+ * ascending order, exactly as if bas_select_topk's list had been passed; its weights cannot be fetched before
+ * the mask exists, so such a call costs one more hop than a call whose mask was known before the launch.
+ * Several calls may use one entry (q, k and v; gate and up).  Top-k only; one CTA per column range only.
+ *
  * bas_list_create allocates a few hundred bytes per call of device memory and uploads the
  * descriptors (synchronous); bas_list_run only launches, so it may be captured in a CUDA graph.
  * Runs of one list must not overlap on the GPU.  bas_list_read_status is bas_read_device_status for
@@ -255,6 +266,8 @@ BAS_API int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_d
  * tests of the expiry path only, names a call whose dependency is never seen complete (-1: none). */
 #define BAS_LIST_MAX_BLOCKS 1024
 #define BAS_LIST_MAX_CALLS 4096
+#define BAS_LIST_GEMM 0
+#define BAS_LIST_SELECT 1
 typedef struct bas_list_call {
   const void* x_dev;
   int64_t ldx;
@@ -267,6 +280,11 @@ typedef struct bas_list_call {
   int32_t k_host, batch, k, n;
   int32_t depends_on;
   int32_t row_parallel;   /* bas_list_create_tp only: 1 = x / packed are this rank's K-shard, y receives the sum over the ranks */
+  int32_t op;             /* BAS_LIST_GEMM (0) or BAS_LIST_SELECT */
+  int32_t mask_entry;     /* GEMM: 1 + index of the earlier BAS_LIST_SELECT entry whose mask it runs with; 0: ids / count / byte map above */
+  int32_t mask_block0;    /* GEMM with mask_entry: the block of that mask which is block 0 of this call (a K-shard); else 0 */
+  int32_t score_kind;     /* SELECT: BAS_SCORE_NORM or BAS_SCORE_ENERGY */
+  int32_t* ids_out_dev;   /* GEMM with mask_entry, optional: receives the kept ids of the whole mask, ascending (k_host of the entry) */
 } bas_list_call;
 typedef struct bas_list bas_list;
 BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_calls, int flags);

@@ -30,7 +30,11 @@ class ListCall(C.Structure):
     _fields_ = [("x_dev", C.c_void_p), ("ldx", C.c_int64), ("packed_dev", C.c_void_p), ("ids_dev", C.c_void_p),
                 ("count_dev", C.c_void_p), ("bitmap_dev", C.c_void_p), ("y_dev", C.c_void_p), ("ldy", C.c_int64),
                 ("k_host", C.c_int32), ("batch", C.c_int32), ("k", C.c_int32), ("n", C.c_int32),
-                ("depends_on", C.c_int32), ("row_parallel", C.c_int32)]
+                ("depends_on", C.c_int32), ("row_parallel", C.c_int32), ("op", C.c_int32), ("mask_entry", C.c_int32),
+                ("mask_block0", C.c_int32), ("score_kind", C.c_int32), ("ids_out_dev", C.c_void_p)]
+
+
+LIST_GEMM, LIST_SELECT = 0, 1
 
 
 class StepCall(C.Structure):

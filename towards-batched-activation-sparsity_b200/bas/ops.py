@@ -199,7 +199,14 @@ class GemmList:
     ``calls``: dicts with ``x`` [B, K], ``packed``, ``out`` [B, N], one of ``ids`` / ``bitmap``
     (``count``, ``k_host`` as for :func:`gemm`) and ``depends_on``: index of the earlier call that
     must be complete before ``x`` is read (normally the call that writes it), or -1.  Masks must be
-    complete before :meth:`run`; they may change between runs.  All tensors are kept alive by the
+    complete before :meth:`run`; they may change between runs.
+
+    Selection inside the launch: an entry ``{"select": x, "n_keep": n, "score_kind": SCORE_NORM,
+    "depends_on": d}`` scores the blocks of ``x`` as :func:`select_topk` does (same bits) once call ``d``
+    is complete; a call with ``"mask_from": index_of_that_entry`` instead of ``ids`` / ``bitmap`` then runs
+    with the top-``n`` blocks (``"mask_block0"``: the block of the mask that is its block 0, for a K-shard;
+    ``"ids_out"``: an int32 tensor that receives the kept ids of the whole mask, ascending).  Indices in
+    ``depends_on`` / ``mask_from`` count entries of both kinds.  All tensors are kept alive by the
     list.  :meth:`run` launches on the current stream, allocates nothing and can be captured in a
     CUDA graph; runs of one list must not overlap."""
 
@@ -214,9 +221,22 @@ class GemmList:
             raise ValueError("a list needs at least one call")
         arr = (_abi.ListCall * len(calls))()
         self._keep = []
-        dtype = calls[0]["x"].dtype
-        self.device = calls[0]["x"].device
+        first = calls[0]["select"] if "select" in calls[0] else calls[0]["x"]
+        dtype = first.dtype
+        self.device = first.device
         for i, c in enumerate(calls):
+            a = arr[i]
+            if "select" in c:
+                x = c["select"]
+                _require_cuda_fp16(x, "select")
+                if x.dtype != dtype or x.dim() != 2 or x.stride(1) != 1:
+                    raise ValueError("a selection entry's x must be 2-D with unit inner stride and the list's dtype")
+                a.op, a.x_dev, a.ldx = _abi.LIST_SELECT, x.data_ptr(), x.stride(0)
+                a.batch, a.k, a.k_host = x.shape[0], x.shape[1], int(c["n_keep"])
+                a.score_kind = int(c.get("score_kind", _abi.SCORE_NORM))
+                a.depends_on = int(c.get("depends_on", -1))
+                self._keep.append((x,))
+                continue
             x, out, packed = c["x"], c["out"], c["packed"]
             _require_cuda_fp16(x, "x")
             _require_cuda_fp16(out, "out")
@@ -228,7 +248,14 @@ class GemmList:
                 raise ValueError(f"a call of a list takes at most {MAX_BATCH} rows")
             ids, bitmap, count = c.get("ids"), c.get("bitmap"), c.get("count")
             k_host = c.get("k_host")
-            if bitmap is None:
+            mask_from, ids_out = c.get("mask_from"), c.get("ids_out")
+            if mask_from is not None:
+                if ids is not None or bitmap is not None or count is not None:
+                    raise ValueError("a call with mask_from takes no ids, bitmap or count")
+                if ids_out is not None and (ids_out.dtype != torch.int32 or not ids_out.is_contiguous()):
+                    raise TypeError("ids_out must be a contiguous int32 tensor")
+                k_host = 0
+            elif bitmap is None:
                 if ids is None:
                     raise ValueError("either ids or bitmap is required")
                 if ids.dtype != torch.int32 or not ids.is_contiguous():
@@ -238,7 +265,6 @@ class GemmList:
                 if bitmap.dtype != torch.uint8 or not bitmap.is_contiguous():
                     raise TypeError("bitmap must be a contiguous uint8 tensor")
                 k_host = int(k_host) if k_host is not None else 0
-            a = arr[i]
             a.x_dev, a.ldx, a.packed_dev = x.data_ptr(), x.stride(0), packed.data_ptr()
             a.ids_dev = ids.data_ptr() if ids is not None and bitmap is None and ids.numel() else None
             a.count_dev = count.data_ptr() if count is not None else None
@@ -247,7 +273,10 @@ class GemmList:
             a.k_host, a.batch, a.k, a.n = k_host, x.shape[0], x.shape[1], out.shape[1]
             a.depends_on = int(c.get("depends_on", -1))
             a.row_parallel = 1 if c.get("row_parallel") else 0
-            self._keep.append((x, out, packed, ids, bitmap, count))
+            if mask_from is not None:
+                a.mask_entry, a.mask_block0 = int(mask_from) + 1, int(c.get("mask_block0", 0))
+                a.ids_out_dev = ids_out.data_ptr() if ids_out is not None else None
+            self._keep.append((x, out, packed, ids, bitmap, count, ids_out))
         self.n_calls = len(calls)
         self.handle = ctypes.c_void_p()
         flags = (GEMM_BF16 if dtype == torch.bfloat16 else 0) | (int(cluster) << 8) | (int(pairs) << 12) | (int(max_ctas) << 16) | (int(min_units) << 24)

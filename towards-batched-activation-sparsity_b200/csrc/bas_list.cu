@@ -84,7 +84,18 @@ struct alignas(128) ListCallDev {
   int dep;                     // call whose completion X waits for, or -1
   unsigned int dep_contrib;    // CTAs that report the completion of call `dep`
   int tp_index;                // row-parallel calls: position among the list's exchanges (0, 1, ...); else -1
-  int pad[4];
+  // Selection inside the list.  A selection entry (n == 0) has no weights and no output: `packed` holds its X,
+  // `ldy` the row stride of X in elements, `k_host` the number of blocks to keep, `batch` / `nb` as usual; its
+  // CTAs score the blocks and publish the scores.  A contraction that takes its mask from such an entry has
+  // k_host = -(entry + 1) and ranks the entry's scores at its call boundary.
+  int score_kind;              // selection entry: BAS_SCORE_NORM / BAS_SCORE_ENERGY
+  unsigned int mask_contrib;   // consumer: CTAs that report the entry's completion
+  int mask_block0;             // consumer: block of the entry's mask that is this call's block 0 (K-shards)
+  int mask_nb;                 // consumer: blocks of the entry
+  int mask_keep;               // consumer: blocks the entry keeps
+  int pad0;
+  double* scores;              // entry: its per-block scores [nb]; consumer: the entry's
+  int32_t* ids_out;            // consumer: where the kept ids of the whole mask go (ascending), or null
 };
 static_assert(sizeof(ListCallDev) == 256, "call descriptor layout");
 
@@ -107,6 +118,7 @@ struct ListParams {
   int issuers;               // MMA-issuing warps in use, a multiple of `pairs` (issuer w multiplies the tiles t % issuers == w)
   int wslot;                 // bytes reserved per slot for a weight tile (multiple of 1024)
   int nb_max;                // largest K / 64 of the list
+  int sel_nb_max;            // largest K / 64 of its selection entries (0: the list has none)
   int bf16;
   int stall_call;            // tests of the expiry path: this call's dependency is never seen complete (-1: off)
   long long wait_cycles;     // bound of every wait
@@ -129,7 +141,7 @@ struct ListSmemHeader {
   unsigned int calls_staged;   // records [0, calls_staged) are valid
   unsigned int epi_arrived;    // epilogue warps that have finished their part of a call (eight per call)
   unsigned int dep_seen;       // 1 + the call whose completion copy warp 0 has seen last (0: none yet)
-  unsigned int pad;
+  unsigned int sel_arrived;    // copy warps that have published their scores of a selection entry
 };
 
 // Per-call record published by copy warp 0: bit 31 = this CTA takes part, bit 30 = its column tiles
@@ -194,6 +206,112 @@ __device__ __forceinline__ int red_swizzle_l(int nbi, int r) {
   return nbi == 32 ? (r & 7) : nbi == 16 ? ((r >> 1) & 3) : nbi == 8 ? ((r >> 2) & 1) : 0;
 }
 
+// ---- selection inside the list ---------------------------------------------------------------
+// Score of activation block j, by one warp: exactly the arithmetic of the selection kernel (bas_misc.cu), so
+// that both give the same bits.  Eight lanes per (row, block) pair, 16 bytes per lane: exact squares summed in
+// fp64 in element order, then over the eight lanes by a butterfly; optional square root; the rows added in
+// row order; divided by the batch.  Rows go four at a time, sixteen in flight.  X may have been written by
+// this launch: loads bypass the non-coherent path.  The result is the same in every lane.
+__device__ __forceinline__ double warp_block_score(const __half* x, long long ldx, int batch, int j, bool bf16,
+                                                   bool norm, int lane) {
+  const int sub = lane & 7, grp = lane >> 3;
+  double s = 0.0;
+  for (int b0 = 0; b0 < batch; b0 += 16) {
+    uint4 v[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int b = b0 + 4 * r + grp;
+      v[r] = make_uint4(0u, 0u, 0u, 0u);
+      if (b < batch) v[r] = __ldcg((const uint4*)(x + (size_t)b * (size_t)ldx + (size_t)j * kBlockK) + sub);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const unsigned int* wds = (const unsigned int*)&v[r];
+      double e = 0.0;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (bf16) {   // a bf16 is the upper half of an fp32; its square is taken in fp64 (range)
+          const double lo = (double)__uint_as_float(wds[q] << 16), hi = (double)__uint_as_float(wds[q] & 0xffff0000u);
+          e += lo * lo;
+          e += hi * hi;
+        } else {
+          const float2 f = __half22float2(*(const __half2*)&wds[q]);
+          e += (double)(f.x * f.x);   // a product of two fp16 values is exact in fp32
+          e += (double)(f.y * f.y);
+        }
+      }
+      e += __shfl_xor_sync(0xffffffffu, e, 1);
+      e += __shfl_xor_sync(0xffffffffu, e, 2);
+      e += __shfl_xor_sync(0xffffffffu, e, 4);
+      if (norm) e = sqrt(e);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const double eg = __shfl_sync(0xffffffffu, e, 8 * g);
+        if (b0 + 4 * r + g < batch) s += eg;
+      }
+    }
+  }
+  return s / (double)batch;
+}
+
+// Top-`keep` of `nb` blocks by (key descending, id ascending), by one warp from keys in its own shared memory.
+// Of the kept blocks those in [block0, block0 + nb_local) are written to ids (local numbers, ascending); all of
+// them to ids_out when that is given.  Returns how many landed in ids.  A block's rank is the number of keys
+// above it plus the equal keys before it; the second term is only evaluated when the first alone keeps more
+// than `keep` blocks (some keys at the boundary are equal), which the count of the first pass tells.
+__device__ __forceinline__ int warp_rank_select(const unsigned long long* keys, int nb, int keep, int block0, int nb_local,
+                                                uint16_t* ids, int32_t* ids_out, int lane) {
+  constexpr int KPL = 4;   // keys per lane and pass
+  int kept_local = 0;
+  for (int exact = 0; exact < 2; ++exact) {
+    int total = 0;
+    kept_local = 0;
+    for (int base = 0; base < nb; base += 32 * KPL) {
+      unsigned long long mine[KPL];
+      int cnt[KPL];
+#pragma unroll
+      for (int t = 0; t < KPL; ++t) {
+        const int j = base + 32 * t + lane;
+        mine[t] = j < nb ? keys[j] : 0ull;
+        cnt[t] = 0;
+      }
+      const int nt = min(KPL, (nb - base + 31) / 32);   // chunks of this pass that hold blocks at all
+      if (exact == 0) {
+        for (int i = 0; i < nb; ++i) {
+          const unsigned long long si = keys[i];
+#pragma unroll
+          for (int t = 0; t < KPL; ++t)
+            if (t < nt) cnt[t] += (si > mine[t]) ? 1 : 0;
+        }
+      } else {
+        for (int i = 0; i < nb; ++i) {
+          const unsigned long long si = keys[i];
+#pragma unroll
+          for (int t = 0; t < KPL; ++t)
+            if (t < nt) cnt[t] += (si > mine[t] || (si == mine[t] && i < base + 32 * t + lane)) ? 1 : 0;
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < KPL; ++t) {
+        if (t < nt) {
+          const int j = base + 32 * t + lane;
+          const bool sel = j < nb && cnt[t] < keep;
+          const bool loc = sel && j >= block0 && j < block0 + nb_local;
+          const unsigned int ms = __ballot_sync(0xffffffffu, sel), ml = __ballot_sync(0xffffffffu, loc);
+          const unsigned int below = (1u << lane) - 1u;
+          if (loc) ids[kept_local + __popc(ml & below)] = (uint16_t)(j - block0);
+          if (sel && ids_out != nullptr && total + __popc(ms & below) < keep) ids_out[total + __popc(ms & below)] = j;
+          total += __popc(ms);
+          kept_local += __popc(ml);
+        }
+      }
+    }
+    if (total <= keep) break;   // no tie across the boundary: the first pass was exact
+  }
+  __syncwarp();
+  return kept_local;
+}
+
 // TP: the variant for lists with row-parallel calls, whose epilogue exchanges partial sums with the other
 // ranks of a box (a template parameter, so that the plain kernel carries none of that code).
 template <int BPAD, bool TP>
@@ -217,6 +335,9 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
   sp += ids_stride * kLProducers;
   uint2* s_def_all = (uint2*)sp;                           // [kLProducers][kMaxStages] deferred activation copies
   sp += sizeof(uint2) * kMaxStages * kLProducers;
+  unsigned long long* s_keys_all = (unsigned long long*)sp;   // [kLProducers][sel_nb_max] ranking keys (lists with selection entries)
+  const size_t keys_stride = ((size_t)p.sel_nb_max * 8 + 127) / 128 * 128;
+  sp += keys_stride * kLProducers;
   float* s_red = (float*)sp;                               // [2][source rank][128][row slots]
   const int C = p.cluster;
   if (C > 1) sp += 2 * (size_t)BPAD * kTileN * sizeof(float);
@@ -242,6 +363,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     hdr->calls_staged = 0u;
     hdr->epi_arrived = 0u;
     hdr->dep_seen = 0u;
+    hdr->sel_arrived = 0u;
     fence_barrier_init();
   }
   if (warp == kLEpiWarp0) {
@@ -272,6 +394,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     // ================================ copy warps ================================
     if (warp < P) {
       uint16_t* s_ids = (uint16_t*)((uint8_t*)s_ids_all + ids_stride * warp);
+      unsigned long long* s_keys = (unsigned long long*)((uint8_t*)s_keys_all + keys_stride * warp);
       uint2* s_def = s_def_all + kMaxStages * warp;   // entries {slot << 24 | call << 12 | block, dependency + 1}: at most S / P
       const int per_lap = S / P;
       const uint64_t pol_x = l2_policy_evict_last();
@@ -341,13 +464,50 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         return true;
       };
 
+      // Wait (bounded) until call d has been reported complete by `contrib` CTAs; the whole warp calls this.
+      // Activation copies of earlier calls keep going out meanwhile: call d may be waiting for them.
+      auto wait_call = [&](int d, unsigned int contrib) -> bool {
+        bool ready = true;
+        if (lane == 0 && d != dep_ok) {
+          const unsigned int target = (epoch + 1u) * contrib;
+          const long long t_start = clock64();
+          unsigned int polls = 0u;
+          for (;;) {
+            bool seen = false;
+            if (warp != 0 && ld_acquire_cta_shared_u32(&hdr->dep_seen) == (unsigned int)d + 1u) {
+              seen = true;
+            } else if (warp == 0 || (++polls & 7u) == 1u) {
+              if ((int)(ld_acquire_gpu_u32(p.done + d) - target) >= 0) {
+                seen = true;
+                if (warp == 0) st_release_cta_shared_u32(&hdr->dep_seen, (unsigned int)d + 1u);
+              }
+            }
+            if (seen) break;
+            while (ndef > 0 && ok && flush_one(false, false)) {
+            }
+            if (!ok || *abort_flag != 0 || clock64() - t_start > limit) {
+              ready = false;
+              break;
+            }
+            __nanosleep(40);
+          }
+          if (ready) {
+            fence_proxy_async_all();
+            dep_ok = d;
+          }
+        }
+        ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
+        __syncwarp();
+        return ready;
+      };
+
       CallRegs cur = load_call_regs(p.calls);
       CallRegs nxt = load_call_regs(p.calls + (p.n_calls > 1 ? 1 : 0));
       int raw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       bool have_raw = false;
       // id batch of a call whose descriptor is in registers (lists with a device-side count are read at the boundary)
       auto prefetch_ids = [&](const CallRegs& r, int (&dst)[8]) -> bool {
-        if (regs_ptr(r.b.x, r.b.y) != nullptr) return false;
+        if (regs_ptr(r.b.x, r.b.y) != nullptr || (int)r.c.x < 0 || (int)r.c.z == 0) return false;   // (or no list at all)
         const uint8_t* bm = (const uint8_t*)regs_ptr(r.b.z, r.b.w);
         warp_load_id_batch((const int32_t*)regs_ptr(r.a.z, r.a.w), bm, bm != nullptr ? (int)r.c.w : (int)r.c.x, 0, lane, dst);
         return true;
@@ -362,23 +522,62 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         const int units = (int)cur.d.x, ranges = (int)cur.d.y, range_off = (int)cur.d.z, dep = (int)cur.d.w;
         const Share sh = call_share(units, ranges, range_off, cid, p.n_clusters);
         int k_mine = 0;
-        if (sh.part) {
-          const int k_act = warp_stage_ids((const int32_t*)regs_ptr(cur.a.z, cur.a.w), (const int32_t*)regs_ptr(cur.b.x, cur.b.y),
-                                           (int)cur.c.x, (const uint8_t*)regs_ptr(cur.b.z, cur.b.w), (int)cur.c.w, s_ids,
-                                           &p.hdr->status, lane, have_raw, raw, warp == 0 && rank == 0 && sh.n0 == 0);
+        const bool is_sel = (int)cur.c.z == 0;                                   // a selection entry: no output columns
+        const int mask_call = (int)cur.c.x < 0 ? -(int)cur.c.x - 1 : -1;         // the entry this call's mask comes from
+        if (is_sel) {
+          if (sh.part) {
+            // This CTA's blocks of the entry (range, range + ranges, ...), dealt out over its copy warps: wait for
+            // X, score, publish; the CTA reports once all its copy warps have.
+            if (dep >= 0 && !wait_call(dep, __ldg(&cd->dep_contrib))) ok = false;
+            if (ok) {
+              int range = cid - range_off;
+              if (range < 0) range += p.n_clusters;
+              const __half* xs = (const __half*)regs_ptr(cur.a.x, cur.a.y);
+              const long long ldx = __ldg(&cd->ldy);
+              double* scores = ldg_ptr(&cd->scores);
+              const bool norm = __ldg(&cd->score_kind) == BAS_SCORE_NORM;
+              for (int j = range + ranges * warp; j < (int)cur.c.w; j += ranges * P) {
+                const double sc = warp_block_score(xs, ldx, (int)cur.c.y, j, bf16, norm, lane);
+                if (lane == 0) scores[j] = sc;
+              }
+              __syncwarp();
+              if (lane == 0 && (atom_add_acq_rel_cta_shared_u32(&hdr->sel_arrived, 1u) % (unsigned int)P) == (unsigned int)P - 1u)
+                red_release_gpu_add_u32(p.done + c, 1u);
+            }
+          }
+        } else if (sh.part) {
+          int k_act = 0;
+          if (mask_call >= 0) {
+            // the mask is ranked here, by every copy warp for itself, from the scores the entry's CTAs published
+            if (!wait_call(mask_call, __ldg(&cd->mask_contrib))) ok = false;
+            if (ok) {
+              if (lane == 0) dep_ok = dep;     // the entry waited for the same call as this one: X is complete too
+              const double* scores = ldg_ptr(&cd->scores);
+              const int mnb = __ldg(&cd->mask_nb);
+              for (int j = lane; j < mnb; j += 32) s_keys[j] = score_key(__ldcg(scores + j));
+              __syncwarp();
+              k_act = warp_rank_select(s_keys, mnb, __ldg(&cd->mask_keep), __ldg(&cd->mask_block0), (int)cur.c.w, s_ids,
+                                       (warp == 0 && rank == 0 && sh.n0 == 0) ? ldg_ptr(&cd->ids_out) : nullptr, lane);
+            }
+          } else {
+            k_act = warp_stage_ids((const int32_t*)regs_ptr(cur.a.z, cur.a.w), (const int32_t*)regs_ptr(cur.b.x, cur.b.y),
+                                   (int)cur.c.x, (const uint8_t*)regs_ptr(cur.b.z, cur.b.w), (int)cur.c.w, s_ids,
+                                   &p.hdr->status, lane, have_raw, raw, warp == 0 && rank == 0 && sh.n0 == 0);
+          }
           k_mine = (k_act > rank) ? (k_act - rank + C - 1) / C : 0;
         }
         if (warp == 0 && lane == 0) {
           // An MMA costs the tensor core by the rows of the weight operand it reads (measured: 39
           // cycles per M = 128 instruction, 23 per M = 64): tiles of up to 64 columns use the short form.
-          s_rec[c] = make_record(sh.part, C == 1 && sh.tw <= 64, sh.n_sub, k_mine);
+          // (A selection entry is the copy warps' business alone: the other warps skip it.)
+          s_rec[c] = make_record(sh.part && !is_sel, C == 1 && sh.tw <= 64, sh.n_sub, k_mine);
           st_release_cta_shared_u32(&hdr->calls_staged, (unsigned int)(c + 1));
         }
         // the next call's id list: requested now, used at the next boundary
         int raw_n[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         const bool have_n = (c + 1 < p.n_calls) ? prefetch_ids(nxt, raw_n) : false;
         if (warp == 0 && lane == 0) BAS_LTRACE(c, 0);
-        if (lane == 0 && sh.part && k_mine > 0) {
+        if (lane == 0 && sh.part && !is_sel && k_mine > 0) {
           const uint8_t* packed = (const uint8_t*)regs_ptr(cur.a.x, cur.a.y);
           const int npad = units * 8;
           for (int sub = 0; sub < sh.n_sub && ok; ++sub) {
@@ -897,9 +1096,10 @@ constexpr size_t kLSmemBudget = 224 * 1024;
 inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Shared memory in front of the ring, as the kernel carves it up.
-size_t list_fixed_smem(int n_calls, int nb_max, int cluster, int bpad) {
+size_t list_fixed_smem(int n_calls, int nb_max, int sel_nb_max, int cluster, int bpad) {
   return 128 + round_up(sizeof(ListSmemHeader), 128) + round_up((size_t)n_calls * 4, 128) +
          round_up((size_t)nb_max * 2, 128) * kLProducers + sizeof(uint2) * kMaxStages * kLProducers +
+         round_up((size_t)sel_nb_max * 8, 128) * kLProducers +
          (cluster > 1 ? 2 * (size_t)bpad * kTileN * sizeof(float) : 0) + 1024;
 }
 
@@ -1008,16 +1208,45 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   if (cc_major != 10) return BAS_ERR_UNSUPPORTED;
 
   // ---- argument checks (those of bas_gemm, per call) and the list-wide sizes ----
-  int max_batch = 0, nb_max = 1;
+  int max_batch = 0, nb_max = 1, sel_nb_max = 0, n_sel = 0, n_gemm = 0;
   for (int c = 0; c < n_calls; ++c) {
     const bas_list_call& a = calls[c];
+    if (a.op == BAS_LIST_SELECT) {
+      // a selection entry: X, its shape, how many blocks to keep, what it waits for - and nothing else
+      if (a.x_dev == nullptr || a.batch <= 0 || a.k < kBlockK || (a.k % kBlockK) != 0 || a.ldx < a.k) return BAS_ERR_INVALID_ARGUMENT;
+      if (a.batch > BAS_MAX_BATCH || a.k / kBlockK > BAS_LIST_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
+      if (a.k_host < 0 || a.k_host > a.k / kBlockK) return BAS_ERR_INVALID_ARGUMENT;
+      if (a.score_kind != BAS_SCORE_NORM && a.score_kind != BAS_SCORE_ENERGY) return BAS_ERR_INVALID_ARGUMENT;
+      if (!list_aligned16(a.x_dev) || (a.ldx & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
+      if (a.depends_on < -1 || a.depends_on >= c || a.row_parallel != 0 || a.mask_entry != 0) return BAS_ERR_INVALID_ARGUMENT;
+      if (a.packed_dev != nullptr || a.y_dev != nullptr || a.ids_dev != nullptr || a.count_dev != nullptr ||
+          a.bitmap_dev != nullptr || a.ids_out_dev != nullptr || a.n != 0)
+        return BAS_ERR_INVALID_ARGUMENT;
+      if (a.batch > max_batch) max_batch = a.batch;
+      if (a.k / kBlockK > sel_nb_max) sel_nb_max = a.k / kBlockK;
+      ++n_sel;
+      continue;
+    }
+    if (a.op != BAS_LIST_GEMM) return BAS_ERR_INVALID_ARGUMENT;
+    ++n_gemm;
     if (a.x_dev == nullptr || a.packed_dev == nullptr || a.y_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
     if (a.batch <= 0 || a.k <= 0 || a.n <= 0 || a.k_host < 0 || a.ldx < a.k || a.ldy < a.n) return BAS_ERR_INVALID_ARGUMENT;
     if (a.batch > BAS_MAX_BATCH) return BAS_ERR_UNSUPPORTED;
     const int nb = (a.k + kBlockK - 1) / kBlockK;
     if (nb > BAS_LIST_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
-    if (a.bitmap_dev == nullptr && a.ids_dev == nullptr && a.k_host > 0) return BAS_ERR_INVALID_ARGUMENT;
-    if (a.bitmap_dev == nullptr && a.k_host > nb) return BAS_ERR_INVALID_ARGUMENT;
+    if (a.mask_entry != 0) {
+      // the mask comes from an earlier selection entry of the same X (same shape of the batch, same call waited
+      // for), of which this call may cover a range of blocks
+      const int en = a.mask_entry - 1;
+      if (en < 0 || en >= c || calls[en].op != BAS_LIST_SELECT) return BAS_ERR_INVALID_ARGUMENT;
+      if (a.ids_dev != nullptr || a.count_dev != nullptr || a.bitmap_dev != nullptr) return BAS_ERR_INVALID_ARGUMENT;
+      if (calls[en].depends_on != a.depends_on || calls[en].batch != a.batch || (a.k % kBlockK) != 0) return BAS_ERR_INVALID_ARGUMENT;
+      if (a.mask_block0 < 0 || a.mask_block0 + nb > calls[en].k / kBlockK) return BAS_ERR_INVALID_ARGUMENT;
+    } else {
+      if (a.mask_block0 != 0 || a.ids_out_dev != nullptr) return BAS_ERR_INVALID_ARGUMENT;
+      if (a.bitmap_dev == nullptr && a.ids_dev == nullptr && a.k_host > 0) return BAS_ERR_INVALID_ARGUMENT;
+      if (a.bitmap_dev == nullptr && a.k_host > nb) return BAS_ERR_INVALID_ARGUMENT;
+    }
     if (!list_aligned16(a.x_dev) || !list_aligned16(a.packed_dev) || (a.ldx & 7) != 0 || (a.k & 7) != 0)
       return BAS_ERR_INVALID_ARGUMENT;
     if (a.depends_on < -1 || a.depends_on >= c) return BAS_ERR_INVALID_ARGUMENT;
@@ -1037,6 +1266,7 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
     if (a.batch > max_batch) max_batch = a.batch;
     if (nb > nb_max) nb_max = nb;
   }
+  if (n_gemm == 0) return BAS_ERR_INVALID_ARGUMENT;
   const int bpad = (max_batch + 15) / 16 * 16;
   e = by_bpad(bpad, [](auto b) { return list_prepare_kernel<decltype(b)::value>(); });
   if (e != cudaSuccess) return record_cuda_error(e);
@@ -1053,6 +1283,7 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
     for (int q = 0; q < tp->world; ++q)
       if (tp->area[q] == nullptr) return BAS_ERR_INVALID_ARGUMENT;   // bas_tp_connect has not run
   }
+  if (n_sel > 0 && forced > 1) return BAS_ERR_UNSUPPORTED;         // selection entries: one CTA per range only
   const int cluster = forced != 0 ? forced : 1;
   int n_clusters = by_bpad(bpad, [&](auto b) { return list_resident_clusters<decltype(b)::value>(cluster, kLSmemBudget, sm_count); });
   if (n_clusters > cta_cap / cluster) n_clusters = cta_cap / cluster;
@@ -1061,11 +1292,31 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   // ---- per call: the clusters that take part, and the widest column tile of the list ----
   const int min_units = ((flags >> 24) & 0x3f) != 0 ? ((flags >> 24) & 0x3f) : 8;   // tuning knob
   std::vector<ListCallDev> host((size_t)n_calls);
-  int off = 0, tw_max = 8, n_tp = 0;
+  int off = 0, tw_max = 8, n_tp = 0, sel_seen = 0;
   for (int c = 0; c < n_calls; ++c) {
     const bas_list_call& a = calls[c];
     ListCallDev& d = host[(size_t)c];
     std::memset(&d, 0, sizeof(d));
+    if (a.op == BAS_LIST_SELECT) {
+      // one block per CTA and round where there are enough CTAs; `scores` holds the entry's number until the
+      // device block exists
+      d.nb = a.k / kBlockK;
+      d.ranges = d.nb < n_clusters ? d.nb : n_clusters;
+      d.units = d.ranges;
+      d.range_off = (d.ranges < n_clusters) ? off : 0;
+      if (d.ranges < n_clusters) off = (off + d.ranges) % n_clusters;
+      d.packed = (const uint8_t*)a.x_dev;
+      d.ldy = (long long)a.ldx;
+      d.k_host = a.k_host;
+      d.batch = a.batch;
+      d.n = 0;
+      d.score_kind = a.score_kind;
+      d.tp_index = -1;
+      d.dep = a.depends_on;
+      d.dep_contrib = a.depends_on >= 0 ? (unsigned int)(host[(size_t)a.depends_on].ranges * cluster) : 0u;
+      d.scores = (double*)(uintptr_t)sel_seen++;
+      continue;
+    }
     const int npad = padded_cols(a.n), units = npad / 8;
     int ranges = units / min_units;      // no range narrower than min_units * 8 columns where the output allows
     if (ranges < 1) ranges = 1;
@@ -1084,6 +1335,16 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
     d.ldy = (long long)a.ldy;
     d.nb = (a.k + kBlockK - 1) / kBlockK;
     d.k_host = a.k_host > d.nb ? d.nb : a.k_host;
+    if (a.mask_entry != 0) {
+      const ListCallDev& en = host[(size_t)(a.mask_entry - 1)];
+      d.k_host = -a.mask_entry;                // = -(entry + 1)
+      d.mask_contrib = (unsigned int)(en.ranges * cluster);
+      d.mask_block0 = a.mask_block0;
+      d.mask_nb = en.nb;
+      d.mask_keep = en.k_host;
+      d.scores = en.scores;                    // still the entry's number
+      d.ids_out = a.ids_out_dev;
+    }
     d.batch = a.batch;
     d.n = a.n;
     d.units = units;
@@ -1109,7 +1370,7 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   // ---- ring: slots of one weight tile + one activation tile ----
   const int wslot = (int)round_up((size_t)tw_max * kRowBytes, 1024);
   const size_t tile_bytes = (size_t)wslot + (size_t)bpad * 128;
-  const size_t fixed = list_fixed_smem(n_calls, nb_max, cluster, bpad);
+  const size_t fixed = list_fixed_smem(n_calls, nb_max, sel_nb_max, cluster, bpad);
   const size_t pad = (size_t)kLMmaSpanBytes > (size_t)wslot ? (size_t)kLMmaSpanBytes - (size_t)wslot : 0;
   if (fixed + pad + 2 * tile_bytes > kLSmemBudget) return BAS_ERR_UNSUPPORTED;
   int slots = (int)((kLSmemBudget - fixed - pad) / tile_bytes);
@@ -1148,9 +1409,14 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   l->smem = fixed + pad + (size_t)slots * tile_bytes;
   const size_t counters_off = 256;
   const size_t desc_off = counters_off + round_up((size_t)n_calls * 4, 256);
-  l->dev_bytes = desc_off + sizeof(ListCallDev) * (size_t)n_calls;
+  const size_t scores_off = round_up(desc_off + sizeof(ListCallDev) * (size_t)n_calls, 256);
+  const size_t scores_stride = round_up((size_t)sel_nb_max * sizeof(double), 256);
+  l->dev_bytes = scores_off + scores_stride * (size_t)n_sel;
   e = cudaMalloc(&l->dev_block, l->dev_bytes);
   if (e == cudaSuccess) e = cudaMemset(l->dev_block, 0, desc_off);
+  for (int c = 0; c < n_calls && e == cudaSuccess; ++c)     // the entries' score arrays, now that they have an address
+    if (calls[c].op == BAS_LIST_SELECT || calls[c].mask_entry != 0)
+      host[(size_t)c].scores = (double*)((uint8_t*)l->dev_block + scores_off + scores_stride * (size_t)(uintptr_t)host[(size_t)c].scores);
   if (e == cudaSuccess)
     e = cudaMemcpy((uint8_t*)l->dev_block + desc_off, host.data(), sizeof(ListCallDev) * (size_t)n_calls, cudaMemcpyHostToDevice);
   if (e != cudaSuccess) {
@@ -1170,6 +1436,7 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   p.issuers = issuers;
   p.wslot = wslot;
   p.nb_max = nb_max;
+  p.sel_nb_max = sel_nb_max;
   p.bf16 = (flags & BAS_GEMM_BF16) != 0 ? 1 : 0;
   p.stall_call = -1;
   p.wait_cycles = wait_cycles_now();
