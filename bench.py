@@ -344,6 +344,28 @@ def _layer_stack(torch, dist, dev, world, rank, stream, fuse=False, allreduce="n
                 "note": "bas_list_run: one persistent kernel per rank walks the step's calls; every call waits for the call "
                         "whose output its input is in the model (q/k/v <- down of the layer before, o <- v, gate/up <- o, "
                         "down <- up); on several ranks o and down add their outputs over the ranks inside the kernel"}
+    if "one_launch" in extra and "error" not in extra["one_launch"]:
+        # the same launch with every mask computed inside it from the activation it belongs to (what a decode step
+        # has to do): a selection entry per distinct input, ranked by the calls that use it
+        for o in [it[3] for it in stack.items]:
+            o.zero_()
+        lst = stack.make_list(dependencies=True, select=True)
+        ms_sel, _ = timed(lst.run)
+        status = lst.read_status()
+        par_s = stack.parity_check_outputs(layers=1)
+        lst.close()
+        bad = int(status != 0 or not par_s["max_err"] <= 2e-3)
+        if world > 1:
+            t = torch.tensor([bad], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            bad = int(t.item())
+        if bad and world == 1:
+            raise SystemExit(f"one-launch stack with selection: device status {status:#x}, parity {par_s}")
+        extra["one_launch"]["with_selection"] = (
+            {"error": f"device status {status:#x} on rank {rank}", "parity": par_s} if bad else
+            {"ms_per_step": round(ms_sel, 4), "max_err_vs_unsharded_fp32": round(par_s["max_err"], 6),
+             "note": "masks computed inside the launch: per layer four selection entries (q/k/v, o, gate/up, down), "
+                     "each scored when its input is complete; the outputs equal those of the precomputed masks"})
     if world == 1:
         lst = stack.make_list(dependencies=False)
         ms_free, _ = timed(lst.run)
@@ -734,6 +756,29 @@ def run_gpu(args) -> None:
         for s in range(ROTATE):
             ops.select_gemm(x_steps[s % 11], packed[s], outs[b], n_keep4, abi.SCORE_ENERGY)
 
+    # selection as an entry of the list launch: [score x, contraction that ranks the scores and runs with the kept
+    # blocks] as ONE launch, against the same contraction alone in a launch of its own with the ids given
+    fixed_ids = [ops.select_topk(x_steps[s % 11], n_keep4, abi.SCORE_ENERGY)[0][:n_keep4].clone() for s in range(ROTATE)]
+    sel_lists = [ops.GemmList([{"select": x_steps[s % 11], "n_keep": n_keep4, "score_kind": abi.SCORE_ENERGY},
+                               {"x": x_steps[s % 11], "packed": packed[s], "out": outs[b], "mask_from": 0}])
+                 for s in range(ROTATE)]
+    plain_lists = [ops.GemmList([{"x": x_steps[s % 11], "packed": packed[s], "out": outs[b], "ids": fixed_ids[s]}])
+                   for s in range(ROTATE)]
+
+    def list_select_gemm():
+        for l in sel_lists:
+            l.run()
+
+    def list_gemm():
+        for l in plain_lists:
+            l.run()
+
+    list_sel_us = _graph_time_us(torch, stream, list_select_gemm, ROTATE, reps)
+    list_plain_us = _graph_time_us(torch, stream, list_gemm, ROTATE, reps)
+    for l in sel_lists + plain_lists:
+        if l.read_status() != 0:
+            raise SystemExit("list launch with a selection entry: device status")
+        l.close()
     sel_us = _graph_time_us(torch, stream, select_only, ROTATE, reps)
     chain_us = _graph_time_us(torch, stream, chain, ROTATE, reps)
     fused_us = _graph_time_us(torch, stream, one_launch, ROTATE, reps)
@@ -747,9 +792,13 @@ def run_gpu(args) -> None:
     online = {"batch": b, "keep_blocks": n_keep4, "select_us": round(sel_us, 3), "select_plus_gemm_us": round(chain_us, 3),
               "selection_inside_gemm_us": round(fused_us, 3),
               "select_plus_gemm_overlapped_us": round(overlapped_us, 3), "score": "energy",
+              "list_select_plus_gemm_us": round(list_sel_us, 3), "list_gemm_alone_us": round(list_plain_us, 3),
               "note": "select_us: selection kernel alone; select_plus_gemm_us: two launches; "
                       "selection_inside_gemm_us: bas_select_gemm (one call; it selects inside the contraction "
                       "kernel only where that is the faster form, i.e. batches of a few rows); "
+                      "list_select_plus_gemm_us: one list launch of a selection entry and the contraction that uses "
+                      "its mask (fresh X, no promise), list_gemm_alone_us: the same contraction as a list launch of "
+                      "its own with the ids given; "
                       "select_plus_gemm_overlapped_us: the two launches per step, with step i+1's selection "
                       "(BAS_SCORE_INPUTS_STABLE, alternating id buffers) scoring while step i's contraction runs"}
 

@@ -155,6 +155,19 @@ def main() -> None:
     if lst.read_status() != 0 or not par["max_err"] <= TOL or not par_list["max_err"] <= TOL or not par_list["ids_equal"]:
         failures.append(("stack as a list", par, par_list))
     lst.close()
+    # ... and with the masks computed inside the launch (a row-parallel call keeps its K-shard's part of the mask
+    # that every rank ranks from the same scores)
+    lst = stack.make_list(select=True)
+    for o in [it[3] for it in stack.items]:
+        o.fill_(float("nan"))
+    lst.run()
+    lst.run()
+    torch.cuda.synchronize()
+    par_sel = stack.parity_check_outputs(layers=2)
+    status = lst.read_status()
+    if status != 0 or not par_sel["max_err"] <= TOL:
+        failures.append(("stack as a list with selection", hex(status), par_sel))
+    lst.close()
     stack.close()
     # Shards of unequal size, as eight ranks get them from the 7B shapes (43 column groups and 43 blocks
     # over two ranks: 21 / 22), and a rank whose K-shard of o_proj holds no active block at all: it

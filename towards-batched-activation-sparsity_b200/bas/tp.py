@@ -273,31 +273,49 @@ class DecodeLinearStack:
                         "o_proj": ("v_proj", "qkv_proj"), "gate_proj": "o_proj", "up_proj": "o_proj",
                         "gate_up_proj": "o_proj", "down_proj": ("up_proj", "gate_up_proj")}
 
-    def make_list(self, dependencies: bool = True, **tuning):
+    def make_list(self, dependencies: bool = True, select: bool = False, **tuning):
         """The whole step as one persistent launch per rank (``ops.GemmList``).  With ``dependencies``
         every call waits for the call whose output its input is in the model; without, no call waits
         for any other (a probe of the kernel's streaming rate; single GPU only).  On several ranks the
         stack must have been built with ``allreduce="in_kernel"``: the row-parallel calls then add their
-        outputs over the ranks inside the list kernel, through the stack's exchange group."""
+        outputs over the ranks inside the list kernel, through the stack's exchange group.
+
+        ``select``: the masks are not taken from the stack's byte maps but computed inside the launch, as a
+        decode step has to: one selection entry per distinct input, scored once that input is complete, ranked
+        by the calls that use it.  A row-parallel call ranks
+        the whole (replicated) input's scores and keeps the blocks of its own K-shard."""
         from . import ops
+        from .abi import SCORE_NORM
 
         if self.world != 1 and (self.exchange is None or not dependencies):
             raise ValueError("on several ranks the one-launch step needs allreduce='in_kernel' and the dependencies")
         last = {}
         calls = []
-        for lin, x, bitmap, out, n_keep in self.items:
+        entry_of = {}     # (layer, input name) -> index of its selection entry
+        for (lin, x, bitmap, out, n_keep), (li, _) in zip(self.items, self.item_meta):
             dep = -1
             if dependencies:
                 want = self.MODEL_DEPENDENCY[lin.spec.name]
                 for name in (want if isinstance(want, tuple) else (want,)):
                     dep = max(dep, last.get(name, -1))
-            last[lin.spec.name] = len(calls)
             row = lin.spec.parallel == "row"
             xs = x[:, lin.b0 * BLOCK_K: lin.b0 * BLOCK_K + lin.k_local] if row else x
-            nb_all = bitmap.numel()
-            hint = max(1, (int(n_keep) * (lin.b1 - lin.b0) + nb_all - 1) // nb_all)
-            calls.append({"x": xs, "packed": lin.packed, "out": out, "bitmap": bitmap[lin.b0:lin.b1], "k_host": hint,
-                          "depends_on": dep, "row_parallel": row and self.world > 1})
+            call = {"x": xs, "packed": lin.packed, "out": out, "depends_on": dep, "row_parallel": row and self.world > 1}
+            if select:
+                # one entry per distinct input of a layer (this stack generates an input per projection type, so
+                # only the stacked q+k+v and gate+up share one: four entries per layer then, as in the model)
+                key = (li, x.data_ptr(), dep)
+                if key not in entry_of:
+                    entry_of[key] = len(calls)
+                    calls.append({"select": x, "n_keep": int(n_keep), "score_kind": SCORE_NORM, "depends_on": dep})
+                call["mask_from"] = entry_of[key]
+                call["mask_block0"] = lin.b0 if row else 0
+            else:
+                nb_all = bitmap.numel()
+                call["bitmap"] = bitmap[lin.b0:lin.b1]
+                call["k_host"] = max(1, (int(n_keep) * (lin.b1 - lin.b0) + nb_all - 1) // nb_all)
+            last[lin.spec.name] = len(calls)
+            calls.append(call)
         return ops.GemmList(calls, tp=self.exchange if self.world > 1 else None, **tuning)
 
     def step(self) -> None:

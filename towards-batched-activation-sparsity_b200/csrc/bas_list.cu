@@ -46,6 +46,10 @@ constexpr int kLEpiWarp0 = kLProducers + kLIssuers;   // a multiple of 4: an epi
 constexpr int kLEpiThreads = 128;       // one epilogue warp per quarter
 constexpr int kLThreads = 32 * kLEpiWarp0 + kLEpiThreads;
 constexpr int kLMmaSpanBytes = 128 * kRowBytes;
+// Every CTA reads every score of a selection entry at about the same time: one array would be one hot spot in the
+// L2 (some six hundred warps on the same few lines).  The scoring warp writes each score to this many copies,
+// in different lines, and a reading warp takes the copy that goes with its number.
+constexpr int kSelReplicas = 16;
 // Upper bits of the status word: the role of the first wait of a CTA that ran out (diagnosis only).
 constexpr unsigned int kWhereCopyWarp = 0x100u, kWhereIssuer = 0x200u, kWhereEpilogue = 0x400u,
                        kWhereExchangeOwner = 0x800u, kWhereExchangeReader = 0x1000u;
@@ -84,18 +88,17 @@ struct alignas(128) ListCallDev {
   int dep;                     // call whose completion X waits for, or -1
   unsigned int dep_contrib;    // CTAs that report the completion of call `dep`
   int tp_index;                // row-parallel calls: position among the list's exchanges (0, 1, ...); else -1
-  // Selection inside the list.  A selection entry (n == 0) has no weights and no output: `packed` holds its X,
-  // `ldy` the row stride of X in elements, `k_host` the number of blocks to keep, `batch` / `nb` as usual; its
-  // CTAs score the blocks and publish the scores.  A contraction that takes its mask from such an entry has
-  // k_host = -(entry + 1) and ranks the entry's scores at its call boundary.
-  int score_kind;              // selection entry: BAS_SCORE_NORM / BAS_SCORE_ENERGY
-  unsigned int mask_contrib;   // consumer: CTAs that report the entry's completion
-  int mask_block0;             // consumer: block of the entry's mask that is this call's block 0 (K-shards)
-  int mask_nb;                 // consumer: blocks of the entry
-  int mask_keep;               // consumer: blocks the entry keeps
-  int pad0;
-  double* scores;              // entry: its per-block scores [nb]; consumer: the entry's
-  int32_t* ids_out;            // consumer: where the kept ids of the whole mask go (ascending), or null
+  // Selection inside the list.  A selection entry (n == 0) has no weights and no output; the copy warps of its
+  // CTAs score the blocks of X, publish the scores, wait until all are there, and say for each of their blocks
+  // whether it is among the kept ones.  It keeps, in the fields the copy warps hold in registers:
+  //   packed = X, ids = its score array (see bas_list_create for the layout behind it), count_dev = {row stride
+  //   of X in elements, reports the entry gets}, bitmap = {score kind, reports of the call it waits for};
+  //   k_host = blocks to keep.
+  // A contraction that takes its mask from entry e polls the entry's verdicts at its call boundary; it keeps:
+  //   k_host = -(e + 1), ids = the entry's score array, count_dev = {the entry's blocks, unused},
+  //   bitmap = {first block of the mask that is this call's block 0, unused}.
+  int32_t* ids_out;            // such a contraction: where the kept ids of the whole mask go (ascending), or null
+  int pad[8];
 };
 static_assert(sizeof(ListCallDev) == 256, "call descriptor layout");
 
@@ -119,6 +122,7 @@ struct ListParams {
   int wslot;                 // bytes reserved per slot for a weight tile (multiple of 1024)
   int nb_max;                // largest K / 64 of the list
   int sel_nb_max;            // largest K / 64 of its selection entries (0: the list has none)
+  int sel_rep_stride;        // elements between the copies of an entry's score array (and of its verdict words)
   int bf16;
   int stall_call;            // tests of the expiry path: this call's dependency is never seen complete (-1: off)
   long long wait_cycles;     // bound of every wait
@@ -139,9 +143,11 @@ struct ListSmemHeader {
   uint32_t tmem_base;
   int abort_flag;
   unsigned int calls_staged;   // records [0, calls_staged) are valid
-  unsigned int epi_arrived;    // epilogue warps that have finished their part of a call (eight per call)
+  // Epilogue warps that have finished their part of a call.  One counter per call this CTA takes part in, four
+  // in rotation: a warp can be two column tiles, so at most two such calls, ahead of the slowest one (the
+  // accumulator buffers alternate), and its arrival for the later call must not be counted for the earlier.
+  unsigned int epi_arrived[4];
   unsigned int dep_seen;       // 1 + the call whose completion copy warp 0 has seen last (0: none yet)
-  unsigned int sel_arrived;    // copy warps that have published their scores of a selection entry
 };
 
 // Per-call record published by copy warp 0: bit 31 = this CTA takes part, bit 30 = its column tiles
@@ -254,64 +260,6 @@ __device__ __forceinline__ double warp_block_score(const __half* x, long long ld
   return s / (double)batch;
 }
 
-// Top-`keep` of `nb` blocks by (key descending, id ascending), by one warp from keys in its own shared memory.
-// Of the kept blocks those in [block0, block0 + nb_local) are written to ids (local numbers, ascending); all of
-// them to ids_out when that is given.  Returns how many landed in ids.  A block's rank is the number of keys
-// above it plus the equal keys before it; the second term is only evaluated when the first alone keeps more
-// than `keep` blocks (some keys at the boundary are equal), which the count of the first pass tells.
-__device__ __forceinline__ int warp_rank_select(const unsigned long long* keys, int nb, int keep, int block0, int nb_local,
-                                                uint16_t* ids, int32_t* ids_out, int lane) {
-  constexpr int KPL = 4;   // keys per lane and pass
-  int kept_local = 0;
-  for (int exact = 0; exact < 2; ++exact) {
-    int total = 0;
-    kept_local = 0;
-    for (int base = 0; base < nb; base += 32 * KPL) {
-      unsigned long long mine[KPL];
-      int cnt[KPL];
-#pragma unroll
-      for (int t = 0; t < KPL; ++t) {
-        const int j = base + 32 * t + lane;
-        mine[t] = j < nb ? keys[j] : 0ull;
-        cnt[t] = 0;
-      }
-      const int nt = min(KPL, (nb - base + 31) / 32);   // chunks of this pass that hold blocks at all
-      if (exact == 0) {
-        for (int i = 0; i < nb; ++i) {
-          const unsigned long long si = keys[i];
-#pragma unroll
-          for (int t = 0; t < KPL; ++t)
-            if (t < nt) cnt[t] += (si > mine[t]) ? 1 : 0;
-        }
-      } else {
-        for (int i = 0; i < nb; ++i) {
-          const unsigned long long si = keys[i];
-#pragma unroll
-          for (int t = 0; t < KPL; ++t)
-            if (t < nt) cnt[t] += (si > mine[t] || (si == mine[t] && i < base + 32 * t + lane)) ? 1 : 0;
-        }
-      }
-#pragma unroll
-      for (int t = 0; t < KPL; ++t) {
-        if (t < nt) {
-          const int j = base + 32 * t + lane;
-          const bool sel = j < nb && cnt[t] < keep;
-          const bool loc = sel && j >= block0 && j < block0 + nb_local;
-          const unsigned int ms = __ballot_sync(0xffffffffu, sel), ml = __ballot_sync(0xffffffffu, loc);
-          const unsigned int below = (1u << lane) - 1u;
-          if (loc) ids[kept_local + __popc(ml & below)] = (uint16_t)(j - block0);
-          if (sel && ids_out != nullptr && total + __popc(ms & below) < keep) ids_out[total + __popc(ms & below)] = j;
-          total += __popc(ms);
-          kept_local += __popc(ml);
-        }
-      }
-    }
-    if (total <= keep) break;   // no tie across the boundary: the first pass was exact
-  }
-  __syncwarp();
-  return kept_local;
-}
-
 // TP: the variant for lists with row-parallel calls, whose epilogue exchanges partial sums with the other
 // ranks of a box (a template parameter, so that the plain kernel carries none of that code).
 template <int BPAD, bool TP>
@@ -335,9 +283,6 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
   sp += ids_stride * kLProducers;
   uint2* s_def_all = (uint2*)sp;                           // [kLProducers][kMaxStages] deferred activation copies
   sp += sizeof(uint2) * kMaxStages * kLProducers;
-  unsigned long long* s_keys_all = (unsigned long long*)sp;   // [kLProducers][sel_nb_max] ranking keys (lists with selection entries)
-  const size_t keys_stride = ((size_t)p.sel_nb_max * 8 + 127) / 128 * 128;
-  sp += keys_stride * kLProducers;
   float* s_red = (float*)sp;                               // [2][source rank][128][row slots]
   const int C = p.cluster;
   if (C > 1) sp += 2 * (size_t)BPAD * kTileN * sizeof(float);
@@ -361,9 +306,8 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     }
     hdr->abort_flag = 0;
     hdr->calls_staged = 0u;
-    hdr->epi_arrived = 0u;
+    for (int q = 0; q < 4; ++q) hdr->epi_arrived[q] = 0u;
     hdr->dep_seen = 0u;
-    hdr->sel_arrived = 0u;
     fence_barrier_init();
   }
   if (warp == kLEpiWarp0) {
@@ -394,7 +338,6 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     // ================================ copy warps ================================
     if (warp < P) {
       uint16_t* s_ids = (uint16_t*)((uint8_t*)s_ids_all + ids_stride * warp);
-      unsigned long long* s_keys = (unsigned long long*)((uint8_t*)s_keys_all + keys_stride * warp);
       uint2* s_def = s_def_all + kMaxStages * warp;   // entries {slot << 24 | call << 12 | block, dependency + 1}: at most S / P
       const int per_lap = S / P;
       const uint64_t pol_x = l2_policy_evict_last();
@@ -528,36 +471,118 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
           if (sh.part) {
             // This CTA's blocks of the entry (range, range + ranges, ...), dealt out over its copy warps: wait for
             // X, score, publish; the CTA reports once all its copy warps have.
-            if (dep >= 0 && !wait_call(dep, __ldg(&cd->dep_contrib))) ok = false;
+            if (dep >= 0 && !wait_call(dep, cur.b.w)) ok = false;
+            if (warp == 0 && lane == 0) BAS_LTRACE(c, 3);
             if (ok) {
               int range = cid - range_off;
               if (range < 0) range += p.n_clusters;
+              // (an entry keeps X, its row stride, the score array and the score kind where a contraction keeps its
+              // weights, id list, count and byte map: in the registers fetched two calls ahead)
               const __half* xs = (const __half*)regs_ptr(cur.a.x, cur.a.y);
-              const long long ldx = __ldg(&cd->ldy);
-              double* scores = ldg_ptr(&cd->scores);
-              const bool norm = __ldg(&cd->score_kind) == BAS_SCORE_NORM;
-              for (int j = range + ranges * warp; j < (int)cur.c.w; j += ranges * P) {
+              double* scores = (double*)regs_ptr(cur.a.z, cur.a.w);
+              const long long ldx = (long long)cur.b.x;
+              const bool norm = (int)cur.b.z == BAS_SCORE_NORM;
+              const int nb_e = (int)cur.c.w, keep_e = (int)cur.c.x;
+              const unsigned int own_reports = cur.b.y;
+              bool scored = false;
+              for (int j = range + ranges * warp; j < nb_e; j += ranges * P) {
                 const double sc = warp_block_score(xs, ldx, (int)cur.c.y, j, bf16, norm, lane);
-                if (lane == 0) scores[j] = sc;
+                if (lane < kSelReplicas) scores[(size_t)lane * (size_t)p.sel_rep_stride + j] = sc;
+                scored = true;
               }
-              __syncwarp();
-              if (lane == 0 && (atom_add_acq_rel_cta_shared_u32(&hdr->sel_arrived, 1u) % (unsigned int)P) == (unsigned int)P - 1u)
-                red_release_gpu_add_u32(p.done + c, 1u);
+              // every copy warp that had a block reports for itself (the copy warps of a CTA do not move in step,
+              // so there is no "last of the CTA"); the host knows how many such warps an entry has
+              if (warp == 0 && lane == 0) BAS_LTRACE(c, 4);
+              if (lane == 0 && scored) red_release_gpu_add_u32(p.done + c, 1u);
+              if (warp == 0 && lane == 0) BAS_LTRACE(c, 5);
+              // ... and, once every score is there, says for each of its blocks whether it is kept: its rank among
+              // all blocks is a handful of comparisons per lane.  The answer goes out as a word that validates
+              // itself (the run's number beside the verdict), which the calls that use the mask poll for.
+              if (scored) {
+                if (!wait_call(c, own_reports)) ok = false;
+                if (ok) {
+                  const double* sc_rep = scores + (size_t)((blockIdx.x * kLProducers + warp) % kSelReplicas) * (size_t)p.sel_rep_stride;
+                  unsigned int* flags = (unsigned int*)(scores + (size_t)kSelReplicas * (size_t)p.sel_rep_stride);
+                  for (int j = range + ranges * warp; j < nb_e; j += ranges * P) {
+                    const unsigned long long kj = score_key(__ldcg(sc_rep + j));
+                    int above = 0;
+                    for (int i0 = 0; i0 < nb_e; i0 += 256) {     // 256 scores in flight together
+                      double v8[8];
+#pragma unroll
+                      for (int t = 0; t < 8; ++t) v8[t] = (i0 + lane + 32 * t < nb_e) ? __ldcg(sc_rep + i0 + lane + 32 * t) : 0.0;
+#pragma unroll
+                      for (int t = 0; t < 8; ++t) {
+                        const int i = i0 + lane + 32 * t;
+                        const unsigned long long ki = score_key(v8[t]);
+                        above += (i < nb_e && (ki > kj || (ki == kj && i < j))) ? 1 : 0;
+                      }
+                    }
+                    above = __reduce_add_sync(0xffffffffu, above);
+                    const unsigned int word = ((epoch + 1u) << 1) | (above < keep_e ? 1u : 0u);
+                    if (lane < kSelReplicas) st_release_gpu_u32(flags + (size_t)lane * (size_t)p.sel_rep_stride + j, word);
+                  }
+                }
+              }
             }
           }
         } else if (sh.part) {
           int k_act = 0;
           if (mask_call >= 0) {
-            // the mask is ranked here, by every copy warp for itself, from the scores the entry's CTAs published
-            if (!wait_call(mask_call, __ldg(&cd->mask_contrib))) ok = false;
-            if (ok) {
-              if (lane == 0) dep_ok = dep;     // the entry waited for the same call as this one: X is complete too
-              const double* scores = ldg_ptr(&cd->scores);
-              const int mnb = __ldg(&cd->mask_nb);
-              for (int j = lane; j < mnb; j += 32) s_keys[j] = score_key(__ldcg(scores + j));
-              __syncwarp();
-              k_act = warp_rank_select(s_keys, mnb, __ldg(&cd->mask_keep), __ldg(&cd->mask_block0), (int)cur.c.w, s_ids,
-                                       (warp == 0 && rank == 0 && sh.n0 == 0) ? ldg_ptr(&cd->ids_out) : nullptr, lane);
+            // (such a call keeps the entry's score array, from which the verdicts follow, {blocks of the entry},
+            // and its first block of the mask where the others keep id list, count and byte map)
+            // One word per block of the entry, written by whoever scored the block: valid once it carries this
+            // run's number.  Poll (bounded) until all are; earlier calls' activation copies keep going out meanwhile.
+            const int mnb = (int)(cur.b.x & 0xffffu), mblock0 = (int)cur.b.z;
+            const unsigned int* flags = (const unsigned int*)((const double*)regs_ptr(cur.a.z, cur.a.w) + (size_t)kSelReplicas * (size_t)p.sel_rep_stride) +
+                                        (size_t)((blockIdx.x * kLProducers + warp) % kSelReplicas) * (size_t)p.sel_rep_stride;
+            const unsigned int want = epoch + 1u;
+            int32_t* ids_out = (warp == 0 && rank == 0 && sh.n0 == 0) ? ldg_ptr(&cd->ids_out) : nullptr;
+            const long long t_start = clock64();
+            int total = 0;
+            for (int i0 = 0; i0 < mnb && ok; i0 += 256) {
+              unsigned int w8[8];
+              for (;;) {
+                bool valid = true;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                  const int i = i0 + lane + 32 * t;
+                  w8[t] = (i < mnb) ? ld_acquire_gpu_u32(flags + i) : (want << 1);
+                  valid = valid && (w8[t] >> 1) == want;
+                }
+                if (__all_sync(0xffffffffu, valid)) break;
+                bool give_up = false;
+                if (lane == 0) {
+                  while (ndef > 0 && ok && flush_one(false, false)) {
+                  }
+                  give_up = !ok || *abort_flag != 0 || clock64() - t_start > limit;
+                }
+                if (__shfl_sync(0xffffffffu, give_up ? 1 : 0, 0) != 0) {
+                  ok = false;
+                  break;
+                }
+                __nanosleep(40);
+              }
+              if (!ok) break;
+#pragma unroll
+              for (int t = 0; t < 8; ++t) {
+                const int i = i0 + lane + 32 * t;
+                if (i0 + 32 * t < mnb) {      // (uniform)
+                  const bool sel = i < mnb && (w8[t] & 1u) != 0u;
+                  const bool loc = sel && i >= mblock0 && i < mblock0 + (int)cur.c.w;
+                  const unsigned int ms = __ballot_sync(0xffffffffu, sel), ml = __ballot_sync(0xffffffffu, loc);
+                  const unsigned int below = (1u << lane) - 1u;
+                  if (loc) s_ids[k_act + __popc(ml & below)] = (uint16_t)(i - mblock0);
+                  if (sel && ids_out != nullptr) ids_out[total + __popc(ms & below)] = i;
+                  total += __popc(ms);
+                  k_act += __popc(ml);
+                }
+              }
+            }
+            __syncwarp();
+            if (warp == 0 && lane == 0) BAS_LTRACE(mask_call, 7);
+            if (ok && lane == 0) {
+              fence_proxy_async_all();
+              dep_ok = dep;     // whoever wrote the verdicts had seen X complete: so has this warp now
             }
           } else {
             k_act = warp_stage_ids((const int32_t*)regs_ptr(cur.a.z, cur.a.w), (const int32_t*)regs_ptr(cur.b.x, cur.b.y),
@@ -657,6 +682,9 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               ok = false;
               break;
             }
+            // off the issue slots meanwhile: the copy warp of this quarter of the SM may be scoring or ranking
+            // (a selection) and twelve warps spinning here took three quarters of its instruction slots
+            __nanosleep(64);
           }
           if (!ok) break;
         }
@@ -739,6 +767,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     bool ok = true;
     unsigned int where = kWhereEpilogue;     // which of the epilogue's waits ran out first (status bits 8..)
     int t0mod = 0, u = 0;
+    int n_part = 0;                          // calls this CTA has taken part in so far
     int c_at = 0;   // the call this role is in (for the status detail of a wait that runs out)
     for (int c = 0; c < p.n_calls && ok; ++c) {
       c_at = c;
@@ -754,6 +783,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               ok = false;
               break;
             }
+            __nanosleep(64);   // as in the issuers' wait
           }
           if (!ok) break;
         }
@@ -1045,10 +1075,11 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
       // no separate fence is needed: the readers acquire the counter.
       __syncwarp();
       if (et == 0) BAS_LTRACE(c, 6);
-      if (lane == 0 && (atom_add_acq_rel_cta_shared_u32(&hdr->epi_arrived, 1u) % (kLEpiThreads / 32)) == kLEpiThreads / 32 - 1) {
+      if (lane == 0 && (atom_add_acq_rel_cta_shared_u32(&hdr->epi_arrived[n_part & 3], 1u) % (kLEpiThreads / 32)) == kLEpiThreads / 32 - 1) {
         red_release_gpu_add_u32(p.done + c, 1u);
         BAS_LTRACE(c, 7);
       }
+      ++n_part;
     }
     if (!ok) {
       if (atomicExch(&hdr->abort_flag, 1) == 0) record_expiry(&p.hdr->status, where, c_at);   // the first of this CTA: the others only follow it
@@ -1096,10 +1127,10 @@ constexpr size_t kLSmemBudget = 224 * 1024;
 inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Shared memory in front of the ring, as the kernel carves it up.
-size_t list_fixed_smem(int n_calls, int nb_max, int sel_nb_max, int cluster, int bpad) {
+size_t list_fixed_smem(int n_calls, int nb_max, int cluster, int bpad) {
   return 128 + round_up(sizeof(ListSmemHeader), 128) + round_up((size_t)n_calls * 4, 128) +
          round_up((size_t)nb_max * 2, 128) * kLProducers + sizeof(uint2) * kMaxStages * kLProducers +
-         round_up((size_t)sel_nb_max * 8, 128) * kLProducers +
+
          (cluster > 1 ? 2 * (size_t)bpad * kTileN * sizeof(float) : 0) + 1024;
 }
 
@@ -1161,8 +1192,9 @@ using namespace bas;
 struct bas_list {
   int n_calls = 0, bpad = 0, sm_count = 0;
   size_t smem = 0;
-  void* dev_block = nullptr;   // header, counters, descriptors
+  void* dev_block = nullptr;   // header, counters, descriptors, the selection entries' scores and verdicts
   size_t dev_bytes = 0;
+  size_t sel_off = 0;          // where the last of these start
   ListParams params = {};
 };
 
@@ -1306,15 +1338,14 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
       d.range_off = (d.ranges < n_clusters) ? off : 0;
       if (d.ranges < n_clusters) off = (off + d.ranges) % n_clusters;
       d.packed = (const uint8_t*)a.x_dev;
-      d.ldy = (long long)a.ldx;
+      d.ids = (const int32_t*)(uintptr_t)sel_seen++;                                   // score array: its number for now
+      d.count_dev = (const int32_t*)(uintptr_t)(unsigned long long)a.ldx;              // row stride of X
+      d.bitmap = (const uint8_t*)(uintptr_t)(unsigned long long)(unsigned int)a.score_kind;   // high half: see below
       d.k_host = a.k_host;
       d.batch = a.batch;
       d.n = 0;
-      d.score_kind = a.score_kind;
       d.tp_index = -1;
       d.dep = a.depends_on;
-      d.dep_contrib = a.depends_on >= 0 ? (unsigned int)(host[(size_t)a.depends_on].ranges * cluster) : 0u;
-      d.scores = (double*)(uintptr_t)sel_seen++;
       continue;
     }
     const int npad = padded_cols(a.n), units = npad / 8;
@@ -1338,11 +1369,9 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
     if (a.mask_entry != 0) {
       const ListCallDev& en = host[(size_t)(a.mask_entry - 1)];
       d.k_host = -a.mask_entry;                // = -(entry + 1)
-      d.mask_contrib = (unsigned int)(en.ranges * cluster);
-      d.mask_block0 = a.mask_block0;
-      d.mask_nb = en.nb;
-      d.mask_keep = en.k_host;
-      d.scores = en.scores;                    // still the entry's number
+      d.ids = en.ids;                          // the entry's score array (still its number)
+      d.count_dev = (const int32_t*)(uintptr_t)(unsigned long long)(unsigned int)en.nb;
+      d.bitmap = (const uint8_t*)(uintptr_t)(unsigned long long)(unsigned int)a.mask_block0;
       d.ids_out = a.ids_out_dev;
     }
     d.batch = a.batch;
@@ -1370,7 +1399,7 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   // ---- ring: slots of one weight tile + one activation tile ----
   const int wslot = (int)round_up((size_t)tw_max * kRowBytes, 1024);
   const size_t tile_bytes = (size_t)wslot + (size_t)bpad * 128;
-  const size_t fixed = list_fixed_smem(n_calls, nb_max, sel_nb_max, cluster, bpad);
+  const size_t fixed = list_fixed_smem(n_calls, nb_max, cluster, bpad);
   const size_t pad = (size_t)kLMmaSpanBytes > (size_t)wslot ? (size_t)kLMmaSpanBytes - (size_t)wslot : 0;
   if (fixed + pad + 2 * tile_bytes > kLSmemBudget) return BAS_ERR_UNSUPPORTED;
   int slots = (int)((kLSmemBudget - fixed - pad) / tile_bytes);
@@ -1401,6 +1430,22 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   slots = slots / issuers * issuers;
   if (slots < 2) return BAS_ERR_UNSUPPORTED;
 
+  // A selection entry is reported by every copy warp that scored a block of it (block j: range j % ranges,
+  // warp (j / ranges) % pairs): min(blocks, ranges * pairs) reports.  Whoever waits for an entry expects that many.
+  for (int c = 0; c < n_calls; ++c) {
+    ListCallDev& d = host[(size_t)c];
+    auto reports = [&](int q) -> unsigned int {
+      const ListCallDev& t = host[(size_t)q];
+      if (calls[q].op != BAS_LIST_SELECT) return (unsigned int)(t.ranges * cluster);
+      return (unsigned int)(t.nb < t.ranges * pairs ? t.nb : t.ranges * pairs);
+    };
+    if (d.dep >= 0) d.dep_contrib = reports(d.dep);
+    if (calls[c].op == BAS_LIST_SELECT && d.dep >= 0)       // high half of the `bitmap` slot
+      d.bitmap = (const uint8_t*)((uintptr_t)d.bitmap | ((uintptr_t)d.dep_contrib << 32));
+    if (calls[c].op == BAS_LIST_SELECT)                     // high half of the `count_dev` slot: its own reports
+      d.count_dev = (const int32_t*)((uintptr_t)d.count_dev | ((uintptr_t)reports(c) << 32));
+  }
+
   bas_list* l = new (std::nothrow) bas_list();
   if (l == nullptr) return BAS_ERR_INVALID_ARGUMENT;
   l->n_calls = n_calls;
@@ -1410,13 +1455,18 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   const size_t counters_off = 256;
   const size_t desc_off = counters_off + round_up((size_t)n_calls * 4, 256);
   const size_t scores_off = round_up(desc_off + sizeof(ListCallDev) * (size_t)n_calls, 256);
-  const size_t scores_stride = round_up((size_t)sel_nb_max * sizeof(double), 256);
+  // per entry: kSelReplicas copies of its scores (double[rep_words]) and then as many copies of its verdict
+  // words (unsigned[rep_words]: run number << 1 | kept), which start as zero - the number of no run
+  const size_t rep_words = round_up((size_t)sel_nb_max * sizeof(double), 256) / sizeof(double);
+  const size_t scores_stride = rep_words * kSelReplicas * (sizeof(double) + sizeof(unsigned int));
   l->dev_bytes = scores_off + scores_stride * (size_t)n_sel;
   e = cudaMalloc(&l->dev_block, l->dev_bytes);
   if (e == cudaSuccess) e = cudaMemset(l->dev_block, 0, desc_off);
+  if (e == cudaSuccess && n_sel > 0) e = cudaMemset((uint8_t*)l->dev_block + scores_off, 0, scores_stride * (size_t)n_sel);
+  l->sel_off = scores_off;
   for (int c = 0; c < n_calls && e == cudaSuccess; ++c)     // the entries' score arrays, now that they have an address
     if (calls[c].op == BAS_LIST_SELECT || calls[c].mask_entry != 0)
-      host[(size_t)c].scores = (double*)((uint8_t*)l->dev_block + scores_off + scores_stride * (size_t)(uintptr_t)host[(size_t)c].scores);
+      host[(size_t)c].ids = (const int32_t*)((uint8_t*)l->dev_block + scores_off + scores_stride * (size_t)(uintptr_t)host[(size_t)c].ids);
   if (e == cudaSuccess)
     e = cudaMemcpy((uint8_t*)l->dev_block + desc_off, host.data(), sizeof(ListCallDev) * (size_t)n_calls, cudaMemcpyHostToDevice);
   if (e != cudaSuccess) {
@@ -1437,6 +1487,7 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   p.wslot = wslot;
   p.nb_max = nb_max;
   p.sel_nb_max = sel_nb_max;
+  p.sel_rep_stride = (int)rep_words;
   p.bf16 = (flags & BAS_GEMM_BF16) != 0 ? 1 : 0;
   p.stall_call = -1;
   p.wait_cycles = wait_cycles_now();
@@ -1483,6 +1534,8 @@ BAS_API int bas_list_reset(bas_list* l) {
   if (l == nullptr) return BAS_ERR_INVALID_ARGUMENT;
   cudaError_t e = cudaDeviceSynchronize();
   if (e == cudaSuccess) e = cudaMemset(l->dev_block, 0, (size_t)((const uint8_t*)l->params.calls - (const uint8_t*)l->dev_block));
+  // the run number starts again: verdicts of earlier runs must not pass for those of the runs to come
+  if (e == cudaSuccess && l->dev_bytes > l->sel_off) e = cudaMemset((uint8_t*)l->dev_block + l->sel_off, 0, l->dev_bytes - l->sel_off);
   return e == cudaSuccess ? BAS_OK : record_cuda_error(e);
 }
 
