@@ -364,8 +364,9 @@ def _layer_stack(torch, dist, dev, world, rank, stream, fuse=False, allreduce="n
         extra["one_launch"]["with_selection"] = (
             {"error": f"device status {status:#x} on rank {rank}", "parity": par_s} if bad else
             {"ms_per_step": round(ms_sel, 4), "max_err_vs_unsharded_fp32": round(par_s["max_err"], 6),
-             "note": "masks computed inside the launch: per layer four selection entries (q/k/v, o, gate/up, down), "
-                     "each scored when its input is complete; the outputs equal those of the precomputed masks"})
+             "note": "masks computed inside the launch: one selection entry per distinct input (four per layer when q+k+v "
+                     "and gate+up are stacked, seven otherwise: this stack generates an input per projection), each scored "
+                     "when its input is complete; the outputs equal those of the precomputed masks"})
     if world == 1:
         lst = stack.make_list(dependencies=False)
         ms_free, _ = timed(lst.run)

@@ -682,9 +682,6 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               ok = false;
               break;
             }
-            // off the issue slots meanwhile: the copy warp of this quarter of the SM may be scoring or ranking
-            // (a selection) and twelve warps spinning here took three quarters of its instruction slots
-            __nanosleep(64);
           }
           if (!ok) break;
         }
@@ -783,7 +780,6 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               ok = false;
               break;
             }
-            __nanosleep(64);   // as in the issuers' wait
           }
           if (!ok) break;
         }
