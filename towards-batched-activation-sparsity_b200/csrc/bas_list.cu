@@ -261,8 +261,9 @@ __device__ __forceinline__ double warp_block_score(const __half* x, long long ld
 }
 
 // TP: the variant for lists with row-parallel calls, whose epilogue exchanges partial sums with the other
-// ranks of a box (a template parameter, so that the plain kernel carries none of that code).
-template <int BPAD, bool TP>
+// ranks of a box (a template parameter, so that the plain kernel carries none of that code).  SEL: the variant
+// for lists with selection entries, likewise.
+template <int BPAD, bool TP, bool SEL>
 __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_constant__ ListParams p) {
   constexpr int kXTileBytes = BPAD * 128;
   constexpr int kAccIssuers = (2 * kLIssuers * BPAD <= 512) ? kLIssuers : 4;   // tensor memory has 512 columns
@@ -450,7 +451,8 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
       bool have_raw = false;
       // id batch of a call whose descriptor is in registers (lists with a device-side count are read at the boundary)
       auto prefetch_ids = [&](const CallRegs& r, int (&dst)[8]) -> bool {
-        if (regs_ptr(r.b.x, r.b.y) != nullptr || (int)r.c.x < 0 || (int)r.c.z == 0) return false;   // (or no list at all)
+        if (regs_ptr(r.b.x, r.b.y) != nullptr) return false;
+        if (SEL && ((int)r.c.x < 0 || (int)r.c.z == 0)) return false;   // a mask from an entry, or an entry: no list at all
         const uint8_t* bm = (const uint8_t*)regs_ptr(r.b.z, r.b.w);
         warp_load_id_batch((const int32_t*)regs_ptr(r.a.z, r.a.w), bm, bm != nullptr ? (int)r.c.w : (int)r.c.x, 0, lane, dst);
         return true;
@@ -465,8 +467,8 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         const int units = (int)cur.d.x, ranges = (int)cur.d.y, range_off = (int)cur.d.z, dep = (int)cur.d.w;
         const Share sh = call_share(units, ranges, range_off, cid, p.n_clusters);
         int k_mine = 0;
-        const bool is_sel = (int)cur.c.z == 0;                                   // a selection entry: no output columns
-        const int mask_call = (int)cur.c.x < 0 ? -(int)cur.c.x - 1 : -1;         // the entry this call's mask comes from
+        const bool is_sel = SEL && (int)cur.c.z == 0;                            // a selection entry: no output columns
+        const int mask_call = (SEL && (int)cur.c.x < 0) ? -(int)cur.c.x - 1 : -1;   // the entry this call's mask comes from
         if (is_sel) {
           if (sh.part) {
             // This CTA's blocks of the entry (range, range + ranges, ...), dealt out over its copy warps: wait for
@@ -1137,8 +1139,10 @@ cudaError_t list_prepare_kernel() {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
-  e = cudaFuncSetAttribute(umma_list_kernel<BPAD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_list_kernel<BPAD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  e = cudaFuncSetAttribute(umma_list_kernel<BPAD, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_list_kernel<BPAD, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_list_kernel<BPAD, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_list_kernel<BPAD, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64) done[dev] = true;
   return cudaSuccess;
@@ -1160,13 +1164,13 @@ int list_resident_clusters(int cluster, size_t smem, int sm_count) {
   int n = 0;
   if (cluster == 1) {
     int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, umma_list_kernel<BPAD, false>, kLThreads, smem) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, umma_list_kernel<BPAD, false, false>, kLThreads, smem) != cudaSuccess) {
       (void)cudaGetLastError();
       return 0;
     }
     return per_sm > 0 ? sm_count : 0;
   }
-  if (cudaOccupancyMaxActiveClusters(&n, umma_list_kernel<BPAD, false>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, umma_list_kernel<BPAD, false, false>, &cfg) != cudaSuccess) {
     (void)cudaGetLastError();
     n = 0;
   }
@@ -1176,8 +1180,12 @@ int list_resident_clusters(int cluster, size_t smem, int sm_count) {
 template <int BPAD>
 cudaError_t list_launch(const ListParams& p, size_t smem, cudaStream_t stream) {
   if (p.tp.world > 0)
-    return launch_with_pdl(umma_list_kernel<BPAD, true>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p);
-  return launch_with_pdl(umma_list_kernel<BPAD, false>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p);
+    return p.sel_nb_max > 0
+               ? launch_with_pdl(umma_list_kernel<BPAD, true, true>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p)
+               : launch_with_pdl(umma_list_kernel<BPAD, true, false>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p);
+  return p.sel_nb_max > 0
+             ? launch_with_pdl(umma_list_kernel<BPAD, false, true>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p)
+             : launch_with_pdl(umma_list_kernel<BPAD, false, false>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p);
 }
 
 }  // namespace
