@@ -51,7 +51,7 @@ STEP_BYTES = sum(N_KEEP.values()) * SLAB_BYTES       # algorithmic bytes of one 
 ROTATE = 16                                          # weight copies cycled through (cold L2)
 # dram__bytes_read.sum + dram__bytes_write.sum of one list launch of 16 steps (ncu; the command is in the
 # summary under profiles/ named for the list kernel and this workload)
-LIST_TRAFFIC_16_STEPS = 1_511_690_000
+LIST_TRAFFIC_16_STEPS = 1_511_300_000
 TRAFFIC_NOTE = ("ncu capture of one 16-step launch (python bench.py --profile-list 16), scaled by the steps of the timed launch: "
                 "traffic grows in proportion to the calls walked")
 METRIC = "block-sparse GEMM active-weight HBM bandwidth, down_proj, batch 2/16/64 (us & speedup vs cuBLAS in per_batch)"
