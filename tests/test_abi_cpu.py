@@ -128,3 +128,36 @@ def test_column_split_matches_kernel_rules():
         assert edges[0] == 0 and edges[-1] == units * 8
         widths = np.diff(edges)
         assert (widths > 0).all() and widths.max() - widths.min() <= 8 and (widths % 8 == 0).all()
+
+
+def test_struct_layouts_match_the_header(tmp_path):
+    """The ctypes structures of the binding against what a C compiler makes of include/bas.h: sizes and the
+    offset of every field (a list of calls is passed as an array of these)."""
+    import shutil
+    import subprocess
+
+    from bas import abi as L
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    structs = {"bas_list_call": L.ListCall, "bas_step_call": L.StepCall}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "bas.h"', "int main(void) {"]
+    for cname, st in structs.items():
+        lines.append(f'  printf("{cname} size %zu\\n", sizeof({cname}));')
+        for field, _ in st._fields_:
+            lines.append(f'  printf("{cname} {field} %zu\\n", offsetof({cname}, {field}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.check_call([gcc, "-std=c11", "-I", str(ROOT / "include"), str(src), "-o", str(exe)])
+    out = subprocess.check_output([str(exe)], text=True)
+    seen = 0
+    for row in out.splitlines():
+        cname, field, value = row.split()
+        st = structs[cname]
+        want = ctypes.sizeof(st) if field == "size" else getattr(st, field).offset
+        assert int(value) == want, row
+        seen += 1
+    assert seen == sum(len(st._fields_) + 1 for st in structs.values())
