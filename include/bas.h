@@ -257,6 +257,15 @@ BAS_API int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_d
  * the mask exists, so such a call costs one more hop than a call whose mask was known before the launch.
  * Several calls may use one entry (q, k and v; gate and up).  Top-k only; one CTA per column range only.
  *
+ * Output-block sparsity and compact operands (the reference's 2-D kernels and their compact chaining of
+ * gate/up into down, kernels/shared_mask_batched_triton_min_runtime.py:2289-2386, 2473-2558, 3411-3467,
+ * 3498-3850).  With n_ids_dev a call computes only the output blocks named there (64 columns each, n_host ids in
+ * [0, ceil(n / 64)), complete before the launch, any order): Y[:, 64 o .. 64 o + 63] for every listed o, the other
+ * columns of y are not touched - or, with BAS_LIST_OUT_COMPACT, block q of the list goes to columns 64 q .. of a
+ * y that is n_host * 64 wide.  BAS_LIST_X_COMPACT: x_dev holds only the active input blocks, in the order of the
+ * id list (block i of X belongs to ids_dev[i]; k stays the K of the weight), which is what a compact output of
+ * the call before is.  Not with row_parallel, not with clusters.  An id out of range sets BAS_DEV_BAD_BLOCK_ID.
+ *
  * bas_list_create allocates a few hundred bytes per call of device memory and uploads the
  * descriptors (synchronous); bas_list_run only launches, so it may be captured in a CUDA graph.
  * Runs of one list must not overlap on the GPU.  bas_list_read_status is bas_read_device_status for
@@ -268,6 +277,8 @@ BAS_API int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_d
 #define BAS_LIST_MAX_CALLS 4096
 #define BAS_LIST_GEMM 0
 #define BAS_LIST_SELECT 1
+#define BAS_LIST_OUT_COMPACT 1
+#define BAS_LIST_X_COMPACT 2
 typedef struct bas_list_call {
   const void* x_dev;
   int64_t ldx;
@@ -285,6 +296,9 @@ typedef struct bas_list_call {
   int32_t mask_block0;    /* GEMM with mask_entry: the block of that mask which is block 0 of this call (a K-shard); else 0 */
   int32_t score_kind;     /* SELECT: BAS_SCORE_NORM or BAS_SCORE_ENERGY */
   int32_t* ids_out_dev;   /* GEMM with mask_entry, optional: receives the kept ids of the whole mask, ascending (k_host of the entry) */
+  const int32_t* n_ids_dev; /* GEMM, optional: only these 64-column output blocks are computed (see below); n_host of them */
+  int32_t n_host;
+  int32_t shape_flags;    /* BAS_LIST_OUT_COMPACT | BAS_LIST_X_COMPACT */
 } bas_list_call;
 typedef struct bas_list bas_list;
 BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_calls, int flags);

@@ -31,10 +31,12 @@ class ListCall(C.Structure):
                 ("count_dev", C.c_void_p), ("bitmap_dev", C.c_void_p), ("y_dev", C.c_void_p), ("ldy", C.c_int64),
                 ("k_host", C.c_int32), ("batch", C.c_int32), ("k", C.c_int32), ("n", C.c_int32),
                 ("depends_on", C.c_int32), ("row_parallel", C.c_int32), ("op", C.c_int32), ("mask_entry", C.c_int32),
-                ("mask_block0", C.c_int32), ("score_kind", C.c_int32), ("ids_out_dev", C.c_void_p)]
+                ("mask_block0", C.c_int32), ("score_kind", C.c_int32), ("ids_out_dev", C.c_void_p),
+                ("n_ids_dev", C.c_void_p), ("n_host", C.c_int32), ("shape_flags", C.c_int32)]
 
 
 LIST_GEMM, LIST_SELECT = 0, 1
+LIST_OUT_COMPACT, LIST_X_COMPACT = 1, 2
 
 
 class StepCall(C.Structure):

@@ -206,8 +206,14 @@ class GemmList:
     is complete; a call with ``"mask_from": index_of_that_entry`` instead of ``ids`` / ``bitmap`` then runs
     with the top-``n`` blocks (``"mask_block0"``: the block of the mask that is its block 0, for a K-shard;
     ``"ids_out"``: an int32 tensor that receives the kept ids of the whole mask, ascending).  Indices in
-    ``depends_on`` / ``mask_from`` count entries of both kinds.  All tensors are kept alive by the
-    list.  :meth:`run` launches on the current stream, allocates nothing and can be captured in a
+    ``depends_on`` / ``mask_from`` count entries of both kinds.
+
+    Output-block sparsity and compact operands (the reference's 2-D kernels): ``"n_ids"``, an int32 tensor of
+    64-column output blocks, makes a call compute only those blocks - into their own columns of ``out``
+    (the others are left alone) or, with ``"out_compact": True``, side by side into an ``out`` that is
+    ``len(n_ids) * 64`` wide (``"n"``: the real output width, needed then).  ``"x_compact": True``: ``x`` holds
+    only the active input blocks, in the order of ``ids`` (``"k"``: the weight's K, needed then).  All tensors
+    are kept alive by the list.  :meth:`run` launches on the current stream, allocates nothing and can be captured in a
     CUDA graph; runs of one list must not overlap."""
 
     def __init__(self, calls, *, cluster: int = 0, pairs: int = 0, max_ctas: int = 0, min_units: int = 0, tp=None):
@@ -242,6 +248,9 @@ class GemmList:
             _require_cuda_fp16(out, "out")
             if x.dtype != dtype or out.dtype != dtype:
                 raise TypeError("all x and out of a list must have one dtype")
+            n_ids = c.get("n_ids")
+            if n_ids is not None and (n_ids.dtype != torch.int32 or not n_ids.is_contiguous() or n_ids.numel() == 0):
+                raise TypeError("n_ids must be a contiguous, non-empty int32 tensor")
             if x.dim() != 2 or out.dim() != 2 or x.stride(1) != 1 or out.stride(1) != 1 or x.shape[0] != out.shape[0]:
                 raise ValueError("x and out must be 2-D with unit inner stride and the same batch")
             if x.shape[0] > MAX_BATCH:
@@ -270,13 +279,20 @@ class GemmList:
             a.count_dev = count.data_ptr() if count is not None else None
             a.bitmap_dev = bitmap.data_ptr() if bitmap is not None else None
             a.y_dev, a.ldy = out.data_ptr(), out.stride(0)
-            a.k_host, a.batch, a.k, a.n = k_host, x.shape[0], x.shape[1], out.shape[1]
+            a.k_host, a.batch, a.k, a.n = k_host, x.shape[0], int(c.get("k", x.shape[1])), int(c.get("n", out.shape[1]))
+            if n_ids is not None:
+                a.n_ids_dev, a.n_host = n_ids.data_ptr(), int(n_ids.numel())
+            a.shape_flags = (_abi.LIST_OUT_COMPACT if c.get("out_compact") else 0) | (_abi.LIST_X_COMPACT if c.get("x_compact") else 0)
+            if c.get("x_compact") and x.shape[1] < k_host * BLOCK_K:
+                raise ValueError("a compact x holds one 64-channel block per id")
+            if c.get("out_compact") and n_ids is not None and out.shape[1] < n_ids.numel() * 64:
+                raise ValueError("a compact out holds one 64-column block per entry of n_ids")
             a.depends_on = int(c.get("depends_on", -1))
             a.row_parallel = 1 if c.get("row_parallel") else 0
             if mask_from is not None:
                 a.mask_entry, a.mask_block0 = int(mask_from) + 1, int(c.get("mask_block0", 0))
                 a.ids_out_dev = ids_out.data_ptr() if ids_out is not None else None
-            self._keep.append((x, out, packed, ids, bitmap, count, ids_out))
+            self._keep.append((x, out, packed, ids, bitmap, count, ids_out, n_ids))
         self.n_calls = len(calls)
         self.handle = ctypes.c_void_p()
         flags = (GEMM_BF16 if dtype == torch.bfloat16 else 0) | (int(cluster) << 8) | (int(pairs) << 12) | (int(max_ctas) << 16) | (int(min_units) << 24)

@@ -98,8 +98,17 @@ struct alignas(128) ListCallDev {
   //   k_host = -(e + 1), ids = the entry's score array, count_dev = {the entry's blocks, unused},
   //   bitmap = {first block of the mask that is this call's block 0, unused}.
   int32_t* ids_out;            // such a contraction: where the kept ids of the whole mask go (ascending), or null
-  int pad[8];
+  // Output-block sparsity (bit 30 of range_off): the call computes only the 64-column blocks named in n_ids.  Its
+  // column space is virtual - position q of the list is columns 64 q .. 64 q + 63, `units` counts those - and a
+  // column tile is one block: the weights come from block n_ids[q] of the packed rows (w_rows per K block), the
+  // results go to that block's columns of y or, `out_compact`, to the virtual ones.  Bit 29 of range_off: X holds
+  // the active input blocks only, in list order (tile i reads columns 64 i .. 64 i + 63).
+  const int32_t* n_ids;
+  int w_rows;                  // padded output columns of the packed weight
+  int out_compact;
+  int pad[4];
 };
+constexpr int kRangeOffMask = 0xffff, kCall2d = 1 << 30, kCallXCompact = 1 << 29;
 static_assert(sizeof(ListCallDev) == 256, "call descriptor layout");
 
 struct ListHeaderDev {
@@ -122,6 +131,7 @@ struct ListParams {
   int wslot;                 // bytes reserved per slot for a weight tile (multiple of 1024)
   int nb_max;                // largest K / 64 of the list
   int sel_nb_max;            // largest K / 64 of its selection entries (0: the list has none)
+  int extended;              // the list has selection entries, output-block calls or compact X: the SEL variant runs it
   int sel_rep_stride;        // elements between the copies of an entry's score array (and of its verdict words)
   int bf16;
   int stall_call;            // tests of the expiry path: this call's dependency is never seen complete (-1: off)
@@ -164,12 +174,20 @@ struct Share {
 };
 __device__ __forceinline__ Share call_share(int units, int ranges, int range_off, int cid, int n_clusters) {
   Share s;
-  int range = cid - range_off;
+  int range = cid - (range_off & kRangeOffMask);
   if (range < 0) range += n_clusters;
   s.part = range < ranges;
   s.n0 = s.width = s.n_sub = 0;
   s.tw = 8;
-  if (s.part) {
+  if (s.part && (range_off & kCall2d) != 0) {
+    // output blocks: whole 64-column blocks per range, one block per column tile
+    const int blocks = units >> 3;
+    const int q0 = (int)((long long)range * blocks / ranges), q1 = (int)((long long)(range + 1) * blocks / ranges);
+    s.n0 = q0 * 64;
+    s.width = (q1 - q0) * 64;
+    s.n_sub = q1 - q0;
+    s.tw = 64;
+  } else if (s.part) {
     s.n0 = col_begin(range, units, ranges);
     s.width = col_begin(range + 1, units, ranges) - s.n0;
     s.n_sub = (s.width + kTileN - 1) / kTileN;
@@ -262,7 +280,7 @@ __device__ __forceinline__ double warp_block_score(const __half* x, long long ld
 
 // TP: the variant for lists with row-parallel calls, whose epilogue exchanges partial sums with the other
 // ranks of a box (a template parameter, so that the plain kernel carries none of that code).  SEL: the variant
-// for lists with selection entries, likewise.
+// for lists with selection entries, output-block calls or compact activations, likewise.
 template <int BPAD, bool TP, bool SEL>
 __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_constant__ ListParams p) {
   constexpr int kXTileBytes = BPAD * 128;
@@ -606,10 +624,24 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         if (warp == 0 && lane == 0) BAS_LTRACE(c, 0);
         if (lane == 0 && sh.part && !is_sel && k_mine > 0) {
           const uint8_t* packed = (const uint8_t*)regs_ptr(cur.a.x, cur.a.y);
-          const int npad = units * 8;
+          int npad = units * 8;
+          const bool by_block = SEL && (range_off & kCall2d) != 0;          // output-block sparsity
+          const bool x_compact = SEL && (range_off & kCallXCompact) != 0;   // X holds the active blocks only
+          const int32_t* n_ids = nullptr;
+          if (by_block) {
+            npad = __ldg(&cd->w_rows);
+            n_ids = ldg_ptr(&cd->n_ids);
+          }
           for (int sub = 0; sub < sh.n_sub && ok; ++sub) {
-            const int c0 = sh.n0 + sub * sh.tw;
-            const int wbytes = min(sh.tw, sh.width - sub * sh.tw) * kRowBytes;
+            int c0 = sh.n0 + sub * sh.tw;
+            int wbytes = min(sh.tw, sh.width - sub * sh.tw) * kRowBytes;
+            if (by_block) {
+              // this tile's weights are the rows of output block n_ids[q] (a bad id is reported by the epilogue
+              // and read as the nearest valid block: nothing outside the weight is touched)
+              const int o = min(max(__ldg(n_ids + (c0 >> 6)), 0), (npad - 1) >> 6);
+              c0 = o * 64;
+              wbytes = min(64, npad - c0) * kRowBytes;
+            }
             int i = warp - t0mod;
             if (i < 0) i += P;
             for (; i < k_mine; i += P) {
@@ -630,11 +662,12 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               uint8_t* st = s_stage + (size_t)slot * tile_bytes;
               bulk_copy_g2s(st, packed + ((size_t)j * npad + c0) * kRowBytes, wbytes, &hdr->full[slot]);
               ++armed_cnt;
+              const int xb = x_compact ? rank + i * C : j;     // the block of X that goes with this tile
               if (ndef == 0 && (dep < 0 || dep == dep_ok)) {
-                tma_load_2d_hint(st + p.wslot, &cd->xmap, j * kBlockK, 0, &hdr->full[slot], pol_x);
+                tma_load_2d_hint(st + p.wslot, &cd->xmap, xb * kBlockK, 0, &hdr->full[slot], pol_x);
               } else {
                 s_def[(def_head + ndef) % kMaxStages] =
-                    make_uint2(((uint32_t)slot << 24) | ((uint32_t)c << 12) | (uint32_t)j, (uint32_t)(dep + 1));
+                    make_uint2(((uint32_t)slot << 24) | ((uint32_t)c << 12) | (uint32_t)xb, (uint32_t)(dep + 1));
                 ++ndef;
                 while (ndef > 0 && flush_one(false, false)) {
                 }
@@ -810,7 +843,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         if (tp_k >= 0) {
           tp_epoch = tp_base + (unsigned int)tp_k + 1u;
           tp_buf = (size_t)kTpHeaderBytes / 8 + (size_t)(tp_epoch & 1u) * (size_t)p.tp.world * (size_t)p.tp.src_words;
-          int range = cid - __ldg(&cd->range_off);
+          int range = cid - (__ldg(&cd->range_off) & kRangeOffMask);
           if (range < 0) range += p.n_clusters;
           tp_owner = range % p.tp.world;
           // No active block on this rank: no activation copy made this CTA wait for the call's dependency, yet
@@ -838,10 +871,21 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
         }
       }
 
+      const bool by_block = SEL && (__ldg(&cd->range_off) & kCall2d) != 0;    // output-block sparsity
+      const int32_t* n_ids = by_block ? ldg_ptr(&cd->n_ids) : nullptr;
+      const bool out_compact = by_block && __ldg(&cd->out_compact) != 0;
       for (int sub = 0; sub < sh.n_sub && ok; ++sub, ++u) {
         const int b = u & 1;
         const int c0 = sh.n0 + sub * sh.tw;
         const int wsub = min(sh.tw, sh.width - sub * sh.tw);
+        // where the tile's columns are in the weight (for the bound against n) and where they go in y
+        int wcol0 = c0, ycol0 = c0;
+        if (by_block) {
+          const int o_raw = __ldg(n_ids + (c0 >> 6)), o_max = (n - 1) >> 6;
+          if ((o_raw < 0 || o_raw > o_max) && et == 0) atomicOr(&p.hdr->status, BAS_DEV_BAD_BLOCK_ID);
+          wcol0 = min(max(o_raw, 0), o_max) * 64;
+          if (!out_compact) ycol0 = wcol0;
+        }
         if (!__all_sync(0xffffffffu, mbar_wait_for(&hdr->acc_full[b], (u >> 1) & 1, abort_flag, limit))) {
           ok = false;
           break;
@@ -899,8 +943,8 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
                                      ((unsigned long long)tp_epoch << 32) | (unsigned long long)__float_as_uint(v[e]));
             }
           } else if (C == 1) {
-            const int col = c0 + r;
-            if (r < wsub && col < n) {
+            const int col = ycol0 + r;
+            if (r < wsub && wcol0 + r < n) {
 #pragma unroll
               for (int e = 0; e < NV; ++e)
                 if (16 * CH0 + e < batch) store_out16(y + (size_t)(16 * CH0 + e) * ldy + col, v[e], bf16);
@@ -1180,10 +1224,10 @@ int list_resident_clusters(int cluster, size_t smem, int sm_count) {
 template <int BPAD>
 cudaError_t list_launch(const ListParams& p, size_t smem, cudaStream_t stream) {
   if (p.tp.world > 0)
-    return p.sel_nb_max > 0
+    return p.extended != 0
                ? launch_with_pdl(umma_list_kernel<BPAD, true, true>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p)
                : launch_with_pdl(umma_list_kernel<BPAD, true, false>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p);
-  return p.sel_nb_max > 0
+  return p.extended != 0
              ? launch_with_pdl(umma_list_kernel<BPAD, false, true>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p)
              : launch_with_pdl(umma_list_kernel<BPAD, false, false>, p.n_clusters * p.cluster, kLThreads, smem, p.cluster, stream, p);
 }
@@ -1244,7 +1288,7 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   if (cc_major != 10) return BAS_ERR_UNSUPPORTED;
 
   // ---- argument checks (those of bas_gemm, per call) and the list-wide sizes ----
-  int max_batch = 0, nb_max = 1, sel_nb_max = 0, n_sel = 0, n_gemm = 0;
+  int max_batch = 0, nb_max = 1, sel_nb_max = 0, n_sel = 0, n_gemm = 0, n_shaped = 0;
   for (int c = 0; c < n_calls; ++c) {
     const bas_list_call& a = calls[c];
     if (a.op == BAS_LIST_SELECT) {
@@ -1266,7 +1310,20 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
     if (a.op != BAS_LIST_GEMM) return BAS_ERR_INVALID_ARGUMENT;
     ++n_gemm;
     if (a.x_dev == nullptr || a.packed_dev == nullptr || a.y_dev == nullptr) return BAS_ERR_INVALID_ARGUMENT;
-    if (a.batch <= 0 || a.k <= 0 || a.n <= 0 || a.k_host < 0 || a.ldx < a.k || a.ldy < a.n) return BAS_ERR_INVALID_ARGUMENT;
+    if ((a.shape_flags & ~(BAS_LIST_OUT_COMPACT | BAS_LIST_X_COMPACT)) != 0) return BAS_ERR_INVALID_ARGUMENT;
+    const bool by_block = a.n_ids_dev != nullptr, x_compact = (a.shape_flags & BAS_LIST_X_COMPACT) != 0;
+    if (by_block || x_compact) ++n_shaped;
+    if (by_block) {
+      if (a.n_host <= 0 || a.n_host > (a.n + 63) / 64 || a.row_parallel != 0) return BAS_ERR_INVALID_ARGUMENT;
+    } else if (a.n_host != 0 || (a.shape_flags & BAS_LIST_OUT_COMPACT) != 0) {
+      return BAS_ERR_INVALID_ARGUMENT;
+    }
+    if (x_compact && (a.row_parallel != 0 || a.mask_entry != 0 || a.bitmap_dev != nullptr || a.ids_dev == nullptr))
+      return BAS_ERR_INVALID_ARGUMENT;          // compact X goes with an id list: its order is X's
+    // the widths the caller's buffers must have: compact X holds k_host blocks, a compact Y n_host blocks
+    const long long x_cols = x_compact ? (long long)a.k_host * kBlockK : (long long)a.k;
+    const long long y_cols = (by_block && (a.shape_flags & BAS_LIST_OUT_COMPACT) != 0) ? (long long)a.n_host * 64 : (long long)a.n;
+    if (a.batch <= 0 || a.k <= 0 || a.n <= 0 || a.k_host < 0 || a.ldx < x_cols || a.ldy < y_cols) return BAS_ERR_INVALID_ARGUMENT;
     if (a.batch > BAS_MAX_BATCH) return BAS_ERR_UNSUPPORTED;
     const int nb = (a.k + kBlockK - 1) / kBlockK;
     if (nb > BAS_LIST_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
@@ -1319,7 +1376,7 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
     for (int q = 0; q < tp->world; ++q)
       if (tp->area[q] == nullptr) return BAS_ERR_INVALID_ARGUMENT;   // bas_tp_connect has not run
   }
-  if (n_sel > 0 && forced > 1) return BAS_ERR_UNSUPPORTED;         // selection entries: one CTA per range only
+  if ((n_sel > 0 || n_shaped > 0) && forced > 1) return BAS_ERR_UNSUPPORTED;   // selection entries, output blocks, compact X: one CTA per range only
   const int cluster = forced != 0 ? forced : 1;
   int n_clusters = by_bpad(bpad, [&](auto b) { return list_resident_clusters<decltype(b)::value>(cluster, kLSmemBudget, sm_count); });
   if (n_clusters > cta_cap / cluster) n_clusters = cta_cap / cluster;
@@ -1352,15 +1409,17 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
       d.dep = a.depends_on;
       continue;
     }
-    const int npad = padded_cols(a.n), units = npad / 8;
-    int ranges = units / min_units;      // no range narrower than min_units * 8 columns where the output allows
+    const bool by_block = a.n_ids_dev != nullptr, x_compact = (a.shape_flags & BAS_LIST_X_COMPACT) != 0;
+    // (output blocks: the column space is the list of blocks, 64 columns each, and no range holds part of a block)
+    const int npad = by_block ? a.n_host * 64 : padded_cols(a.n), units = npad / 8;
+    int ranges = by_block ? a.n_host : units / min_units;      // no range narrower than min_units * 8 columns where the output allows
     if (ranges < 1) ranges = 1;
     if (ranges > n_clusters) ranges = n_clusters;
     // widest range of this call, its column tiles
-    const int wmax = ((units + ranges - 1) / ranges) * 8;
-    const int n_sub = (wmax + kTileN - 1) / kTileN;
+    const int wmax = by_block ? ((a.n_host + ranges - 1) / ranges) * 64 : ((units + ranges - 1) / ranges) * 8;
+    const int n_sub = by_block ? wmax / 64 : (wmax + kTileN - 1) / kTileN;
     if (n_sub > 16) return BAS_ERR_UNSUPPORTED;
-    const int tw = ((wmax + n_sub - 1) / n_sub + 7) & ~7;
+    const int tw = by_block ? 64 : ((wmax + n_sub - 1) / n_sub + 7) & ~7;
     if (tw > tw_max) tw_max = tw;
     d.packed = (const uint8_t*)a.packed_dev;
     d.ids = a.bitmap_dev != nullptr ? nullptr : a.ids_dev;
@@ -1382,15 +1441,18 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
     d.n = a.n;
     d.units = units;
     d.ranges = ranges;
-    d.range_off = (ranges < n_clusters) ? off : 0;
+    d.range_off = ((ranges < n_clusters) ? off : 0) | (by_block ? kCall2d : 0) | (x_compact ? kCallXCompact : 0);
     if (ranges < n_clusters) off = (off + ranges) % n_clusters;
+    d.n_ids = a.n_ids_dev;
+    d.w_rows = padded_cols(a.n);
+    d.out_compact = (by_block && (a.shape_flags & BAS_LIST_OUT_COMPACT) != 0) ? 1 : 0;
     d.tp_index = a.row_parallel != 0 ? n_tp++ : -1;
     d.dep = a.depends_on;
     d.dep_contrib = a.depends_on >= 0 ? (unsigned int)(host[(size_t)a.depends_on].ranges * cluster) : 0u;
     // X[batch, K]: inner dimension K, box {64 channels, bpad rows}, 128-byte swizzle, zeros out of range
     auto encode = (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder();
     if (encode == nullptr) return record_cuda_error(cudaErrorNotSupported);
-    const cuuint64_t gdim[2] = {(cuuint64_t)a.k, (cuuint64_t)a.batch};
+    const cuuint64_t gdim[2] = {(cuuint64_t)(x_compact ? (long long)a.k_host * kBlockK : (long long)a.k), (cuuint64_t)a.batch};
     const cuuint64_t gstride[1] = {(cuuint64_t)a.ldx * 2};
     const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)bpad};
     const cuuint32_t estr[2] = {1, 1};
@@ -1491,6 +1553,7 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   p.wslot = wslot;
   p.nb_max = nb_max;
   p.sel_nb_max = sel_nb_max;
+  p.extended = (n_sel > 0 || n_shaped > 0) ? 1 : 0;
   p.sel_rep_stride = (int)rep_words;
   p.bf16 = (flags & BAS_GEMM_BF16) != 0 ? 1 : 0;
   p.stall_call = -1;
