@@ -393,6 +393,56 @@ def _layer_stack(torch, dist, dev, world, rank, stream, fuse=False, allreduce="n
             "tp_parity": {"checked": parity["checked"], "max_err": round(parity["max_err"], 6), "ids_equal": parity["ids_equal"]}}
 
 
+def _two_d_chain(torch, ops, O, dev, stream) -> dict:
+    """up -> down of one Llama-2-7B layer (B = 16) with output-block sparsity: up computes only the 62 of 172
+    intermediate blocks that down's mask keeps and writes them side by side, down reads that compact
+    activation (the reference's 2-D kernels and compact chaining, kernels/...:2289-2894, 3411-3467), against the
+    same pair with up computing all its columns.  One list launch per pair, eight rotating weight pairs (cold L2)."""
+    batch, hidden, inter, rot = 16, 4096, 11008, 8
+    k_up, k_down = 23, 62
+    x = torch.from_numpy(O.make_activations(batch, hidden, seed=500)).to(dev)
+    k_ids = torch.from_numpy(O.random_active_blocks(hidden // 64, k_up, seed=501)).to(dev)
+    mid_ids = torch.from_numpy(O.random_active_blocks(inter // 64, k_down, seed=502)).to(dev)
+    wu = ops.pack_weight(torch.from_numpy(O.make_weight(inter, hidden, seed=503)).to(dev))
+    wd = ops.pack_weight(torch.from_numpy(O.make_weight(hidden, inter, seed=504)).to(dev))
+    wus, wds = [wu.clone() for _ in range(rot)], [wd.clone() for _ in range(rot)]
+    mid_full = torch.zeros(batch, inter, dtype=torch.float16, device=dev)
+    mid_comp = torch.zeros(batch, k_down * 64, dtype=torch.float16, device=dev)
+    y = torch.zeros(batch, hidden, dtype=torch.float16, device=dev)
+    plain = [ops.GemmList([{"x": x, "packed": wus[i], "out": mid_full, "ids": k_ids},
+                           {"x": mid_full, "packed": wds[i], "out": y, "ids": mid_ids, "depends_on": 0}]) for i in range(rot)]
+    two_d = [ops.GemmList([{"x": x, "packed": wus[i], "out": mid_comp, "ids": k_ids, "n_ids": mid_ids, "out_compact": True, "n": inter},
+                           {"x": mid_comp, "packed": wds[i], "out": y, "ids": mid_ids, "x_compact": True, "k": inter, "depends_on": 0}])
+             for i in range(rot)]
+
+    def run(lists):
+        def go():
+            for l in lists:
+                l.run()
+        return go
+
+    us_plain = _graph_time_us(torch, stream, run(plain), rot, 20)
+    y_plain = y.clone()
+    us_2d = _graph_time_us(torch, stream, run(two_d), rot, 20)
+    torch.cuda.synchronize()
+    # the same blocks in the same order; the column tiles differ (64 wide against the even split), and with them
+    # which of a CTA's accumulators a block's partial sum lands in: equal to fp32 rounding
+    diff = float((y.float() - y_plain.float()).abs().max() / y_plain.float().abs().max().clamp_min(1e-30))
+    if not diff <= 2e-3:
+        raise SystemExit(f"2-D chain: differs from the plain pair by {diff}")
+    for l in plain + two_d:
+        if l.read_status() != 0:
+            raise SystemExit("2-D chain: device status")
+        l.close()
+    bytes_plain = (k_up * inter + k_down * hidden) * 64 * 2
+    bytes_2d = (k_up * k_down * 64 + k_down * hidden) * 64 * 2
+    return {"batch": batch, "up_active_blocks": k_up, "down_active_blocks": k_down,
+            "pair_us": round(us_plain, 3), "pair_2d_us": round(us_2d, 3), "speedup": round(us_plain / us_2d, 3),
+            "weight_mb": round(bytes_plain / 1e6, 2), "weight_mb_2d": round(bytes_2d / 1e6, 2), "max_diff_vs_plain": round(diff, 6),
+            "note": "one list launch of [up, down]; 2-D: up computes only the intermediate blocks that down keeps, "
+                    "compact, and down reads the compact activation"}
+
+
 def _sweep_gate_up(torch, ops, abi, O, dev, stream, peaks) -> dict:
     """The sparsity sweep of the specification on the gate/up shape: X [B, 4096] N(0,1), W [11008, 4096],
     B in {1..64}, block sparsity 0 .. 0.95 in steps of 0.05, top-k masks by block L2 norm; per point the
@@ -806,6 +856,7 @@ def run_gpu(args) -> None:
     # ---- rank 0 at N = 1: sparsity sweep on the gate/up shape, the reference's Triton kernels on this GPU,
     # and the reference's own two benchmark scripts against the drop-in ----
     sweep = ref_triton = thesis = None
+    two_d = _two_d_chain(torch, ops, O, dev, stream) if world == 1 else None
     if world == 1 and not args.quick:
         sweep = _sweep_gate_up(torch, ops, abi, O, dev, stream, peaks)
         ref_triton = _reference_triton(torch, O, dev, stream, xs, ids)
@@ -946,7 +997,7 @@ def run_gpu(args) -> None:
                        "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
                        "timing": "CUDA events on the launch stream around the K steps, median of 5 regions, max over ranks",
                        "region_ms": [round(v, 4) for v in region_ms]},
-            "per_batch": per_batch, "online_selection": online, "layer_stack": layer_stack, "sweep_gate_up": sweep,
+            "per_batch": per_batch, "online_selection": online, "layer_stack": layer_stack, "two_d_chain": two_d, "sweep_gate_up": sweep,
             "reference_triton": ref_triton, "thesis_protocol": thesis, "roofline": roofline, "cpu_baseline": cpu,
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
