@@ -12,6 +12,9 @@ sm_100a CUDA) instead of Triton kernels.  Differences a caller can observe:
   libbas's tile-major layout, not the reference's ``[K/64, 64, N]`` view.  No caller reads it.
 * float16 or bfloat16 (x, weight and out alike).  There is no CPU path: CPU tensors raise
   ``ValueError``.
+* The 2-D wrappers (output blocks, compact output, compact input) take the output width from the
+  weight.  The reference's compact wrapper lets its kernel take it from the compact tensor, which masks
+  the output blocks that lie past that width (zeros); here they hold the products.
 """
 
 from __future__ import annotations
