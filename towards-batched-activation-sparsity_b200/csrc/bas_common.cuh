@@ -129,6 +129,11 @@ __device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.ac
 // through an acquire) against its asynchronous-proxy accesses (bulk / tensor copies), all state spaces.
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 // Completion counters in global memory that CTAs of one grid hand work over through.
+__device__ __forceinline__ unsigned int ld_relaxed_gpu_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_release_gpu_u32(unsigned int* p, unsigned int v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

@@ -538,7 +538,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
                       }
                     }
                     above = __reduce_add_sync(0xffffffffu, above);
-                    const unsigned int word = ((epoch + 1u) << 1) | (above < keep_e ? 1u : 0u);
+                    const unsigned int word = (((epoch + 1u) & 0x7fffffffu) << 1) | (above < keep_e ? 1u : 0u);
                     if (lane < kSelReplicas) st_release_gpu_u32(flags + (size_t)lane * (size_t)p.sel_rep_stride + j, word);
                   }
                 }
@@ -555,7 +555,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
             const int mnb = (int)(cur.b.x & 0xffffu), mblock0 = (int)cur.b.z;
             const unsigned int* flags = (const unsigned int*)((const double*)regs_ptr(cur.a.z, cur.a.w) + (size_t)kSelReplicas * (size_t)p.sel_rep_stride) +
                                         (size_t)((blockIdx.x * kLProducers + warp) % kSelReplicas) * (size_t)p.sel_rep_stride;
-            const unsigned int want = epoch + 1u;
+            const unsigned int want = (epoch + 1u) & 0x7fffffffu;
             int32_t* ids_out = (warp == 0 && rank == 0 && sh.n0 == 0) ? ldg_ptr(&cd->ids_out) : nullptr;
             const long long t_start = clock64();
             int total = 0;
@@ -564,12 +564,17 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               for (;;) {
                 bool valid = true;
 #pragma unroll
-                for (int t = 0; t < 8; ++t) {
+                for (int t = 0; t < 8; ++t) {      // relaxed loads: all of a lane's words are in flight together
                   const int i = i0 + lane + 32 * t;
-                  w8[t] = (i < mnb) ? ld_acquire_gpu_u32(flags + i) : (want << 1);
+                  w8[t] = (i < mnb) ? ld_relaxed_gpu_u32(flags + i) : (want << 1);
                   valid = valid && (w8[t] >> 1) == want;
                 }
-                if (__all_sync(0xffffffffu, valid)) break;
+                if (__all_sync(0xffffffffu, valid)) {
+                  // One acquire, of any valid word: its writer had seen X complete (it acquired the counter of the
+                  // call that writes X before it scored), which is all this call needs beyond the words themselves.
+                  if (i0 == 0) (void)ld_acquire_gpu_u32(flags + lane % mnb);
+                  break;
+                }
                 bool give_up = false;
                 if (lane == 0) {
                   while (ndef > 0 && ok && flush_one(false, false)) {
