@@ -897,7 +897,7 @@ def run_gpu(args) -> None:
     calls = (abi.StepCall * len(BATCHES))()
     for c, bb in zip(calls, BATCHES):
         c.w_host, c.n, c.k, c.batch, c.n_keep, c.score_kind = w_host.ctypes.data, N_OUT, K_IN, bb, N_KEEP[bb], abi.SCORE_NORM
-    E2E_DEPTH = 3
+    E2E_DEPTH = 6
     hstep = ctypes.c_void_p()
     abi.check(abi.lib.bas_step_create(ctypes.byref(hstep), calls, len(BATCHES), E2E_DEPTH), "bas_step_create")
     # the step's inputs and results live in page-locked host memory, as a serving host keeps them; one
@@ -938,15 +938,40 @@ def run_gpu(args) -> None:
     e2e_dt = (time.perf_counter() - t0) / e2e_steps
     # one step alone, nothing else in flight: the latency of a step
     lat = []
-    for _ in range(20):
+    for _ in range(2 * E2E_DEPTH + 20):      # (a slot replays its captured step from its third use on)
         t1 = time.perf_counter()
         e2e_run(1)
         lat.append(time.perf_counter() - t1)
+    lat = lat[-20:]
     if world > 1:
         t = torch.tensor([e2e_dt], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_dt = float(t.item())
     abi.lib.bas_step_destroy(hstep)
+    # the bare transfers of a step - the three X up, the three Y down, both directions at once on two streams,
+    # nothing else: what the host link allows for these sizes
+    cs_up, cs_down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    xh_t = [torch.from_numpy(a) for a in sets[0][0]]
+    yh_t = [torch.empty((bb, N_OUT), dtype=torch.float16, pin_memory=True) for bb in BATCHES]
+    xd_t = [torch.empty(bb, K_IN, dtype=torch.float16, device=dev) for bb in BATCHES]
+    yd_t = [torch.zeros(bb, N_OUT, dtype=torch.float16, device=dev) for bb in BATCHES]
+
+    def copies(n):
+        with torch.cuda.stream(cs_up):
+            for _ in range(n):
+                for d_, h_ in zip(xd_t, xh_t):
+                    d_.copy_(h_, non_blocking=True)
+        with torch.cuda.stream(cs_down):
+            for _ in range(n):
+                for h_, d_ in zip(yh_t, yd_t):
+                    h_.copy_(d_, non_blocking=True)
+
+    copies(20)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    copies(300)
+    torch.cuda.synchronize()
+    copies_ms = (time.perf_counter() - t1) / 300 * 1e3
     for xh, yh, ih, _ in sets:      # the e2e outputs are real results: same masks, same sums as the resident path
         for j, bb in enumerate(BATCHES):
             ops.gemm(xs[bb], packed[0], outs[bb], ids=ids[bb])
@@ -961,6 +986,7 @@ def run_gpu(args) -> None:
            "d2h_bytes_per_step": sum(bb * N_OUT * 2 + (NB + 1) * 4 for bb in BATCHES) + 16,
            "ms_per_step": e2e_dt * 1e3, "steps": e2e_steps, "steps_in_flight": E2E_DEPTH,
            "one_step_alone_ms": round(statistics.median(lat) * 1e3, 4),
+           "transfers_alone_ms_per_step": round(copies_ms, 4),
            "api": "bas_step_submit / bas_step_wait: per step H2D of the three X from page-locked memory, three device-side "
                   "top-k selections, one list launch for the three GEMMs, D2H of the three Y, the ids and the status word"}
 

@@ -1710,7 +1710,10 @@ int step_enqueue(bas_step* st, bas_step::Slot& sl, const void* const* x_host, vo
     const bas_step::Call& a = st->calls[c];
     cudaStream_t bs = (c % branches == 0) ? s : sl.aux[c % branches - 1];
     const size_t row = (size_t)a.k * 2;
-    e = cudaMemcpy2DAsync(sl.x_dev + a.x_off, (size_t)a.ldx * 2, x_host[c], row, row, (size_t)a.batch, cudaMemcpyHostToDevice, bs);
+    if ((size_t)a.ldx * 2 == row)      // rows are contiguous on both sides: one plain copy
+      e = cudaMemcpyAsync(sl.x_dev + a.x_off, x_host[c], row * (size_t)a.batch, cudaMemcpyHostToDevice, bs);
+    else
+      e = cudaMemcpy2DAsync(sl.x_dev + a.x_off, (size_t)a.ldx * 2, x_host[c], row, row, (size_t)a.batch, cudaMemcpyHostToDevice, bs);
     if (e != cudaSuccess) return record_cuda_error(e);
     // count goes to the last word of the call's id block (nb + 1 words per call)
     const int rc = bas_select_topk(sl.x_dev + a.x_off, a.ldx, a.batch, a.k, a.n_keep, a.score_kind, ids_base + a.ids_off,
