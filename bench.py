@@ -448,8 +448,8 @@ def _sweep_gate_up(torch, ops, abi, O, dev, stream, peaks) -> dict:
     B in {1..64}, block sparsity 0 .. 0.95 in steps of 0.05, top-k masks by block L2 norm; per point the
     masked GEMM as the drop-in wrappers launch it (single launches, no promises) against dense cuBLAS,
     both on 8 rotating weight copies (cold L2).  The reference's tuner walks the same grid
-    (scripts/profile_kernel_configs.py:86-216).  Every point is also appended to
-    gpurun_out/sweep_gate_up.jsonl as it is measured."""
+    (scripts/profile_kernel_configs.py:86-216).  Every point is also appended, as it is measured, to a
+    JSON-lines file in the run's output folder."""
     k, n, nb, rot = 4096, 11008, 64, 8
     w = torch.from_numpy(O.make_weight(n, k, seed=3)).to(dev)
     packed = [ops.pack_weight(w) for _ in range(rot)]

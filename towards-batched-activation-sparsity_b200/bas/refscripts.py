@@ -8,7 +8,7 @@ top (:19-21).  So the drop-in module is registered in ``sys.modules`` under the 
 names before the scripts start, and an inert ``matplotlib`` (absent from this image) is provided whose
 ``subplots`` returns a figure and an axes object, so that the scripts end cleanly.
 
-    python -m bas.refscripts --reference baseline/_ref --out gpurun_out/thesis_protocol --batch-sizes 2,16,64
+    python -m bas.refscripts --reference baseline/_ref --out out_dir --batch-sizes 2,16,64
 
 prints one JSON line with the mean kernel speed-up over dense per batch size - the thesis's
 headline metric (results/kernel/perstep_actual_kernel_speedup.json:17-54)."""
