@@ -367,6 +367,24 @@ def _layer_stack(torch, dist, dev, world, rank, stream, fuse=False, allreduce="n
              "note": "masks computed inside the launch: one selection entry per distinct input (four per layer when q+k+v "
                      "and gate+up are stacked, seven otherwise: this stack generates an input per projection), each scored "
                      "when its input is complete; the outputs equal those of the precomputed masks"})
+    if world > 1 and "one_launch" in extra and "error" not in extra["one_launch"].get("with_selection", {"error": 1}):
+        # ... and with every rank scoring only its own K-shard of the row-parallel calls' inputs (what a chained
+        # forward leaves a rank with): the block scores are exchanged inside the launch, one global top-k
+        for o in [it[3] for it in stack.items]:
+            o.zero_()
+        lst = stack.make_list(dependencies=True, select=True, sharded_select=True)
+        ms_sh, _ = timed(lst.run)
+        status = lst.read_status()
+        par_h = stack.parity_check_outputs(layers=1)
+        lst.close()
+        bad = int(status != 0 or not par_h["max_err"] <= 2e-3)
+        t = torch.tensor([bad], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        extra["one_launch"]["with_sharded_selection"] = (
+            {"error": f"device status {status:#x} on rank {rank}", "parity": par_h} if int(t.item()) else
+            {"ms_per_step": round(ms_sh, 4), "max_err_vs_unsharded_fp32": round(par_h["max_err"], 6),
+             "note": "as with_selection, but the entries of o and down see this rank's K-shard only and the ranks "
+                     "exchange the block scores through the exchange area inside the launch"})
     if world == 1:
         lst = stack.make_list(dependencies=False)
         ms_free, _ = timed(lst.run)

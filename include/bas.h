@@ -257,6 +257,16 @@ BAS_API int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_d
  * the mask exists, so such a call costs one more hop than a call whose mask was known before the launch.
  * Several calls may use one entry (q, k and v; gate and up).  Top-k only; one CTA per column range only.
  *
+ * A SELECT entry over a K-sharded activation (bas_list_create_tp; shape_flags = BAS_LIST_SELECT_SHARDED): x_dev
+ * holds this rank's blocks only, mask_block0 is their first block in the whole input and n_host the blocks of the
+ * whole input (at most 1024), k_host still counts blocks of the whole input.  Every rank scores its own blocks, the
+ * scores travel to all ranks through the group's exchange area and a block is kept by its rank among ALL blocks,
+ * so that every rank runs with its part of one global top-k, as the unsharded model would (the 64 to 172 scores
+ * that have to be gathered before a global selection).  The contractions that run with such an entry are the
+ * row-parallel calls over that same shard (mask_block0 as the entry's).  The entries share one region of the
+ * exchange area: an entry must depend, directly or through other calls, on the last row-parallel call before it,
+ * and a row-parallel call must lie between two such entries.
+ *
  * Output-block sparsity and compact operands (the reference's 2-D kernels and their compact chaining of
  * gate/up into down, kernels/shared_mask_batched_triton_min_runtime.py:2289-2386, 2473-2558, 3411-3467,
  * 3498-3850).  With n_ids_dev a call computes only the output blocks named there (64 columns each, n_host ids in
@@ -279,6 +289,7 @@ BAS_API int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_d
 #define BAS_LIST_SELECT 1
 #define BAS_LIST_OUT_COMPACT 1
 #define BAS_LIST_X_COMPACT 2
+#define BAS_LIST_SELECT_SHARDED 4
 typedef struct bas_list_call {
   const void* x_dev;
   int64_t ldx;

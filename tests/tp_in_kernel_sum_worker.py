@@ -168,6 +168,36 @@ def main() -> None:
     if status != 0 or not par_sel["max_err"] <= TOL:
         failures.append(("stack as a list with selection", hex(status), par_sel))
     lst.close()
+    # ... and with every rank scoring only its own K-shard of a row-parallel call's input: the ranks exchange the
+    # block scores inside the launch and keep their part of ONE global top-k - the same mask as before
+    lst = stack.make_list(select=True, sharded_select=True)
+    for o in [it[3] for it in stack.items]:
+        o.fill_(float("nan"))
+    for _ in range(3):
+        lst.run()
+    torch.cuda.synchronize()
+    par_sh = stack.parity_check_outputs(layers=2)
+    status = lst.read_status()
+    if status != 0 or not par_sh["max_err"] <= TOL:
+        failures.append(("stack as a list with sharded selection", hex(status), par_sh))
+    lst.close()
+    stack.close()
+    # the same on shards of unequal size (43 blocks over two ranks: 21 / 22)
+    small = tuple(tp.LinearSpec(s.name, {4096: 1024, 11008: 2752}[s.n], {4096: 1024, 11008: 2752}[s.k], s.parallel, s.dist)
+                  for s in tp.LLAMA2_7B_LAYER)
+    stack = tp.DecodeLinearStack(3, 16, 0.638, dev, world, rank, seed=11, allreduce="in_kernel", specs=small, fuse_shared_inputs=True)
+    par = stack.parity_check(layers=3)
+    lst = stack.make_list(select=True, sharded_select=True)
+    for o in [it[3] for it in stack.items]:
+        o.fill_(float("nan"))
+    for _ in range(2):
+        lst.run()
+    torch.cuda.synchronize()
+    par_sh = stack.parity_check_outputs(layers=3)
+    status = lst.read_status()
+    if status != 0 or not par["max_err"] <= TOL or not par_sh["max_err"] <= TOL:
+        failures.append(("uneven shards, sharded selection", hex(status), par, par_sh))
+    lst.close()
     stack.close()
     # Shards of unequal size, as eight ranks get them from the 7B shapes (43 column groups and 43 blocks
     # over two ranks: 21 / 22), and a rank whose K-shard of o_proj holds no active block at all: it

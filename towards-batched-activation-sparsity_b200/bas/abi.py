@@ -36,7 +36,7 @@ class ListCall(C.Structure):
 
 
 LIST_GEMM, LIST_SELECT = 0, 1
-LIST_OUT_COMPACT, LIST_X_COMPACT = 1, 2
+LIST_OUT_COMPACT, LIST_X_COMPACT, LIST_SELECT_SHARDED = 1, 2, 4
 
 
 class StepCall(C.Structure):

@@ -206,7 +206,10 @@ class GemmList:
     is complete; a call with ``"mask_from": index_of_that_entry`` instead of ``ids`` / ``bitmap`` then runs
     with the top-``n`` blocks (``"mask_block0"``: the block of the mask that is its block 0, for a K-shard;
     ``"ids_out"``: an int32 tensor that receives the kept ids of the whole mask, ascending).  Indices in
-    ``depends_on`` / ``mask_from`` count entries of both kinds.
+    ``depends_on`` / ``mask_from`` count entries of both kinds.  With ``tp``, an entry may be given
+    ``"sharded": (first_block, blocks_of_the_whole_input)``: its ``x`` is this rank's K-shard, the ranks exchange
+    their block scores inside the launch and ``n_keep`` blocks of the WHOLE input are kept; the row-parallel
+    calls over that shard then run with their part of the mask (``mask_block0 = first_block``).
 
     Output-block sparsity and compact operands (the reference's 2-D kernels): ``"n_ids"``, an int32 tensor of
     64-column output blocks, makes a call compute only those blocks - into their own columns of ``out``
@@ -241,6 +244,9 @@ class GemmList:
                 a.batch, a.k, a.k_host = x.shape[0], x.shape[1], int(c["n_keep"])
                 a.score_kind = int(c.get("score_kind", _abi.SCORE_NORM))
                 a.depends_on = int(c.get("depends_on", -1))
+                if c.get("sharded") is not None:          # (first block of this rank's shard, blocks of the whole input)
+                    a.mask_block0, a.n_host = (int(v) for v in c["sharded"])
+                    a.shape_flags = _abi.LIST_SELECT_SHARDED
                 self._keep.append((x,))
                 continue
             x, out, packed = c["x"], c["out"], c["packed"]

@@ -273,7 +273,7 @@ class DecodeLinearStack:
                         "o_proj": ("v_proj", "qkv_proj"), "gate_proj": "o_proj", "up_proj": "o_proj",
                         "gate_up_proj": "o_proj", "down_proj": ("up_proj", "gate_up_proj")}
 
-    def make_list(self, dependencies: bool = True, select: bool = False, **tuning):
+    def make_list(self, dependencies: bool = True, select: bool = False, sharded_select: bool = False, **tuning):
         """The whole step as one persistent launch per rank (``ops.GemmList``).  With ``dependencies``
         every call waits for the call whose output its input is in the model; without, no call waits
         for any other (a probe of the kernel's streaming rate; single GPU only).  On several ranks the
@@ -283,7 +283,9 @@ class DecodeLinearStack:
         ``select``: the masks are not taken from the stack's byte maps but computed inside the launch, as a
         decode step has to: one selection entry per distinct input, scored once that input is complete, ranked
         by the calls that use it.  A row-parallel call ranks
-        the whole (replicated) input's scores and keeps the blocks of its own K-shard."""
+        the whole (replicated) input's scores and keeps the blocks of its own K-shard - or, ``sharded_select``,
+        every rank scores only its own K-shard of a row-parallel call's input, as if that were all it held (what a
+        chained forward leaves it with), and the ranks exchange the scores inside the launch."""
         from . import ops
         from .abi import SCORE_NORM
 
@@ -304,10 +306,14 @@ class DecodeLinearStack:
             if select:
                 # one entry per distinct input of a layer (this stack generates an input per projection type, so
                 # only the stacked q+k+v and gate+up share one: four entries per layer then, as in the model)
-                key = (li, x.data_ptr(), dep)
+                sharded = sharded_select and row and self.world > 1
+                key = (li, x.data_ptr(), dep, sharded)
                 if key not in entry_of:
                     entry_of[key] = len(calls)
-                    calls.append({"select": x, "n_keep": int(n_keep), "score_kind": SCORE_NORM, "depends_on": dep})
+                    entry = {"select": xs if sharded else x, "n_keep": int(n_keep), "score_kind": SCORE_NORM, "depends_on": dep}
+                    if sharded:
+                        entry["sharded"] = (lin.b0, bitmap.numel())
+                    calls.append(entry)
                 call["mask_from"] = entry_of[key]
                 call["mask_block0"] = lin.b0 if row else 0
             else:

@@ -137,7 +137,7 @@ int bas_workspace_init(void* ws_dev, size_t ws_bytes, void* stream) {
 // ---------------------------------------------------------------------------------------------
 // (struct bas_tp: bas_kernels.cuh)
 static size_t tp_area_bytes(int world, int max_batch, int npad) {
-  return (size_t)kTpHeaderBytes + 2 * 8 * (size_t)world * (size_t)max_batch * (size_t)npad;
+  return (size_t)kTpHeaderBytes + 2 * 8 * (size_t)world * (size_t)max_batch * (size_t)npad + kTpSelBytes;
 }
 
 int bas_tp_create(bas_tp** out, int rank, int world, int max_batch, int n) {
@@ -281,6 +281,7 @@ static int gemm_impl(const bas_tp* tp, const FusedSelect* sel, const void* x_dev
     p.tp.ldp = tp->npad;
     p.tp.src_words = (long long)tp->max_batch * tp->npad;
     p.tp.own = tp->area[tp->rank];
+    p.tp.sel_words = 0;
     for (int q = 0; q < tp->world; ++q) p.tp.area[q] = tp->area[q];
   }
 #ifdef BAS_TRACE

@@ -24,7 +24,13 @@ struct TpExchange {
   long long src_words;                 // words per source rank in one receive buffer (= max rows * ldp)
   unsigned char* area[kTpMaxRanks];    // every rank's area as mapped here
   unsigned char* own;                  // == area[rank]
+  long long sel_words;                 // where the block scores of a sharded selection land, in words from the area's start
 };
+// Behind the receive buffers: two 64-bit words per activation block, {stamp, upper half of the score} and
+// {stamp, lower half}, written by the rank that holds the block into every rank's area (list launches with
+// selection entries over K-sharded activations); header word 2 counts such entries completed.
+constexpr int kTpSelBlocks = 1024;
+constexpr size_t kTpSelBytes = (size_t)kTpSelBlocks * 2 * 8;
 
 // Mask selection run inside the contraction kernel (cluster modes only): every cluster scores all
 // blocks of X, its CTAs sharing the blocks and exchanging the scores through shared memory, ranks them

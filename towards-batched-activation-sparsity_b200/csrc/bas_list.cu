@@ -109,6 +109,12 @@ struct alignas(128) ListCallDev {
   int pad[4];
 };
 constexpr int kRangeOffMask = 0xffff, kCall2d = 1 << 30, kCallXCompact = 1 << 29;
+// Bit 28 of range_off.  A selection entry over a K-SHARDED activation (tensor-parallel lists): X holds this
+// rank's blocks only (w_rows = their first block in the whole input, out_compact = the blocks of the whole
+// input); the scores travel to every rank through the exchange area and a block's rank is taken among all of
+// them.  A contraction that runs with such an entry's mask looks at the verdicts of its own blocks only.
+constexpr int kCallSharded = 1 << 28;
+constexpr unsigned int kStatusBadLayout = 0x40000000u;   // a descriptor field the kernel indexes with is out of range (never seen: the host checks)
 static_assert(sizeof(ListCallDev) == 256, "call descriptor layout");
 
 struct ListHeaderDev {
@@ -138,6 +144,7 @@ struct ListParams {
   long long wait_cycles;     // bound of every wait
   TpExchange tp;             // lists with row-parallel calls: the group's exchange areas (world 0 = none)
   int n_tp_calls;            // exchanges per run
+  int n_sharded;             // selection entries over sharded activations per run
 #ifdef BAS_TRACE
   long long* trace;          // diagnostic build only
   int trace_cta;
@@ -346,8 +353,11 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
   pdl_wait();
   const unsigned int epoch = __ldcg(&p.hdr->epoch);
   // exchanges the group has completed before this run: exchange k of the list carries number tp_base + k + 1
-  unsigned int tp_base = 0u;
-  if constexpr (TP) tp_base = __ldcg((const unsigned int*)p.tp.own);
+  unsigned int tp_base = 0u, sel_base = 0u;
+  if constexpr (TP) {
+    tp_base = __ldcg((const unsigned int*)p.tp.own);
+    sel_base = __ldcg((const unsigned int*)p.tp.own + 2);   // sharded selection entries completed before this run
+  }
 
   const int rank = (C > 1) ? (int)cluster_ctarank() : 0;
   const int cid = blockIdx.x / C;
@@ -494,7 +504,7 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
             if (dep >= 0 && !wait_call(dep, cur.b.w)) ok = false;
             if (warp == 0 && lane == 0) BAS_LTRACE(c, 3);
             if (ok) {
-              int range = cid - range_off;
+              int range = cid - (range_off & kRangeOffMask);
               if (range < 0) range += p.n_clusters;
               // (an entry keeps X, its row stride, the score array and the score kind where a contraction keeps its
               // weights, id list, count and byte map: in the registers fetched two calls ahead)
@@ -504,10 +514,35 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               const bool norm = (int)cur.b.z == BAS_SCORE_NORM;
               const int nb_e = (int)cur.c.w, keep_e = (int)cur.c.x;
               const unsigned int own_reports = cur.b.y;
+              // a K-sharded activation: this rank's blocks are blocks g0 .. of nb_all, and their scores go to
+              // every rank (two self-validating words per block; the stamp is the entry's number in the group)
+              const bool sharded = TP && (range_off & kCallSharded) != 0;
+              int g0 = 0, nb_all = nb_e;
+              unsigned int stamp = 0u;
+              if (sharded) {
+                g0 = __ldg(&cd->w_rows);
+                nb_all = __ldg(&cd->out_compact);
+                stamp = sel_base + (unsigned int)__ldg(&cd->tp_index) + 1u;
+                if (g0 < 0 || nb_all > kTpSelBlocks || nb_all > p.sel_rep_stride || g0 + nb_e > nb_all) {
+                  if (lane == 0) atomicOr(&p.hdr->status, kStatusBadLayout);   // (the host checks these: belt and braces)
+                  ok = false;
+                }
+              }
               bool scored = false;
-              for (int j = range + ranges * warp; j < nb_e; j += ranges * P) {
+              for (int j = range + ranges * warp; j < nb_e && ok; j += ranges * P) {
                 const double sc = warp_block_score(xs, ldx, (int)cur.c.y, j, bf16, norm, lane);
-                if (lane < kSelReplicas) scores[(size_t)lane * (size_t)p.sel_rep_stride + j] = sc;
+                if (sharded) {
+                  if constexpr (TP) {
+                    if (lane < p.tp.world) {
+                      const unsigned long long bits = (unsigned long long)__double_as_longlong(sc);
+                      unsigned long long* dst = (unsigned long long*)p.tp.area[lane] + p.tp.sel_words + 2 * (size_t)(g0 + j);
+                      st_relaxed_sys_u64(dst, ((unsigned long long)stamp << 32) | (bits >> 32));
+                      st_relaxed_sys_u64(dst + 1, ((unsigned long long)stamp << 32) | (bits & 0xffffffffull));
+                    }
+                  }
+                } else if (lane < kSelReplicas) {
+                  scores[(size_t)lane * (size_t)p.sel_rep_stride + j] = sc;
+                }
                 scored = true;
               }
               // every copy warp that had a block reports for itself (the copy warps of a CTA do not move in step,
@@ -518,28 +553,84 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
               // ... and, once every score is there, says for each of its blocks whether it is kept: its rank among
               // all blocks is a handful of comparisons per lane.  The answer goes out as a word that validates
               // itself (the run's number beside the verdict), which the calls that use the mask poll for.
-              if (scored) {
-                if (!wait_call(c, own_reports)) ok = false;
+              if (scored && ok) {
+                if (!sharded && !wait_call(c, own_reports)) ok = false;
                 if (ok) {
                   const double* sc_rep = scores + (size_t)((blockIdx.x * kLProducers + warp) % kSelReplicas) * (size_t)p.sel_rep_stride;
                   unsigned int* flags = (unsigned int*)(scores + (size_t)kSelReplicas * (size_t)p.sel_rep_stride);
-                  for (int j = range + ranges * warp; j < nb_e; j += ranges * P) {
-                    const unsigned long long kj = score_key(__ldcg(sc_rep + j));
-                    int above = 0;
-                    for (int i0 = 0; i0 < nb_e; i0 += 256) {     // 256 scores in flight together
-                      double v8[8];
+                  const unsigned long long* words = nullptr;     // sharded: all ranks' scores, in this rank's own area
+                  if constexpr (TP) words = (const unsigned long long*)p.tp.own + p.tp.sel_words;
+                  const long long t_start = clock64();
+                  // scores of blocks i0 + lane + 32 t; sharded: polled (bounded) until they carry the entry's stamp
+                  auto load_scores = [&](int i0, double (&v8)[8]) -> bool {
+                    if (!sharded) {
 #pragma unroll
-                      for (int t = 0; t < 8; ++t) v8[t] = (i0 + lane + 32 * t < nb_e) ? __ldcg(sc_rep + i0 + lane + 32 * t) : 0.0;
+                      for (int t = 0; t < 8; ++t) v8[t] = (i0 + lane + 32 * t < nb_all) ? __ldcg(sc_rep + i0 + lane + 32 * t) : 0.0;
+                      return true;
+                    }
+                    for (;;) {
+                      unsigned long long hi8[8], lo8[8];
+                      bool valid = true;
+#pragma unroll
+                      for (int t = 0; t < 8; ++t) {
+                        const int i = i0 + lane + 32 * t;
+                        hi8[t] = lo8[t] = (unsigned long long)stamp << 32;
+                        if (i < nb_all) {
+                          hi8[t] = ld_relaxed_sys_u64(words + 2 * (size_t)i);
+                          lo8[t] = ld_relaxed_sys_u64(words + 2 * (size_t)i + 1);
+                        }
+                        valid = valid && (unsigned int)(hi8[t] >> 32) == stamp && (unsigned int)(lo8[t] >> 32) == stamp;
+                      }
+                      if (__all_sync(0xffffffffu, valid)) {
+#pragma unroll
+                        for (int t = 0; t < 8; ++t)
+                          v8[t] = __longlong_as_double((long long)((hi8[t] << 32) | (lo8[t] & 0xffffffffull)));
+                        return true;
+                      }
+                      bool give_up = false;
+                      if (lane == 0) {
+                        while (ndef > 0 && ok && flush_one(false, false)) {
+                        }
+                        give_up = !ok || *abort_flag != 0 || clock64() - t_start > limit;
+                      }
+                      if (__shfl_sync(0xffffffffu, give_up ? 1 : 0, 0) != 0) return false;
+                      __nanosleep(40);
+                    }
+                  };
+                  for (int j = range + ranges * warp; j < nb_e && ok; j += ranges * P) {
+                    const int jg = g0 + j;                       // the block's number in the whole input
+                    // the block's own key, from the same array as the others (every rank compares the same bits)
+                    unsigned long long kj = 0ull;
+                    if (!sharded) {
+                      kj = score_key(__ldcg(sc_rep + j));
+                    } else {
+                      double v8[8];
+                      const int i0 = jg & ~255;
+                      if (!load_scores(i0, v8)) ok = false;
+                      double own = 0.0;
+#pragma unroll
+                      for (int t = 0; t < 8; ++t)
+                        if (t == ((jg - i0) >> 5)) own = v8[t];
+                      kj = score_key(__shfl_sync(0xffffffffu, own, jg & 31));
+                    }
+                    int above = 0;
+                    for (int i0 = 0; i0 < nb_all && ok; i0 += 256) {     // 256 scores in flight together
+                      double v8[8];
+                      if (!load_scores(i0, v8)) {
+                        ok = false;
+                        break;
+                      }
 #pragma unroll
                       for (int t = 0; t < 8; ++t) {
                         const int i = i0 + lane + 32 * t;
                         const unsigned long long ki = score_key(v8[t]);
-                        above += (i < nb_e && (ki > kj || (ki == kj && i < j))) ? 1 : 0;
+                        above += (i < nb_all && (ki > kj || (ki == kj && i < jg))) ? 1 : 0;
                       }
                     }
+                    if (!ok) break;
                     above = __reduce_add_sync(0xffffffffu, above);
                     const unsigned int word = (((epoch + 1u) & 0x7fffffffu) << 1) | (above < keep_e ? 1u : 0u);
-                    if (lane < kSelReplicas) st_release_gpu_u32(flags + (size_t)lane * (size_t)p.sel_rep_stride + j, word);
+                    if (lane < kSelReplicas) st_release_gpu_u32(flags + (size_t)lane * (size_t)p.sel_rep_stride + jg, word);
                   }
                 }
               }
@@ -559,20 +650,27 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
             int32_t* ids_out = (warp == 0 && rank == 0 && sh.n0 == 0) ? ldg_ptr(&cd->ids_out) : nullptr;
             const long long t_start = clock64();
             int total = 0;
-            for (int i0 = 0; i0 < mnb && ok; i0 += 256) {
+            // (an entry over a sharded activation: this rank has the verdicts of its own blocks only)
+            const bool own_only = (range_off & kCallSharded) != 0;
+            const int f_lo = own_only ? mblock0 : 0, f_hi = own_only ? mblock0 + (int)cur.c.w : mnb;
+            if (f_lo < 0 || f_hi > p.sel_rep_stride || f_hi <= f_lo) {
+              if (lane == 0) atomicOr(&p.hdr->status, kStatusBadLayout);
+              ok = false;
+            }
+            for (int i0 = f_lo; i0 < f_hi && ok; i0 += 256) {
               unsigned int w8[8];
               for (;;) {
                 bool valid = true;
 #pragma unroll
                 for (int t = 0; t < 8; ++t) {      // relaxed loads: all of a lane's words are in flight together
                   const int i = i0 + lane + 32 * t;
-                  w8[t] = (i < mnb) ? ld_relaxed_gpu_u32(flags + i) : (want << 1);
+                  w8[t] = (i < f_hi) ? ld_relaxed_gpu_u32(flags + i) : (want << 1);
                   valid = valid && (w8[t] >> 1) == want;
                 }
                 if (__all_sync(0xffffffffu, valid)) {
                   // One acquire, of any valid word: its writer had seen X complete (it acquired the counter of the
                   // call that writes X before it scored), which is all this call needs beyond the words themselves.
-                  if (i0 == 0) (void)ld_acquire_gpu_u32(flags + lane % mnb);
+                  if (i0 == f_lo) (void)ld_acquire_gpu_u32(flags + f_lo + lane % (f_hi - f_lo));
                   break;
                 }
                 bool give_up = false;
@@ -591,8 +689,8 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
 #pragma unroll
               for (int t = 0; t < 8; ++t) {
                 const int i = i0 + lane + 32 * t;
-                if (i0 + 32 * t < mnb) {      // (uniform)
-                  const bool sel = i < mnb && (w8[t] & 1u) != 0u;
+                if (i0 + 32 * t < f_hi) {      // (uniform)
+                  const bool sel = i < f_hi && (w8[t] & 1u) != 0u;
                   const bool loc = sel && i >= mblock0 && i < mblock0 + (int)cur.c.w;
                   const unsigned int ms = __ballot_sync(0xffffffffu, sel), ml = __ballot_sync(0xffffffffu, loc);
                   const unsigned int below = (1u << lane) - 1u;
@@ -1160,7 +1258,10 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
     if (atomicAdd(&p.hdr->arrived, 1u) == gridDim.x - 1) {
       p.hdr->arrived = 0u;
       p.hdr->epoch = epoch + 1u;
-      if constexpr (TP) ((unsigned int*)p.tp.own)[0] = tp_base + (unsigned int)p.n_tp_calls;
+      if constexpr (TP) {
+        ((unsigned int*)p.tp.own)[0] = tp_base + (unsigned int)p.n_tp_calls;
+        ((unsigned int*)p.tp.own)[2] = sel_base + (unsigned int)p.n_sharded;
+      }
       __threadfence();
     }
   }
@@ -1293,19 +1394,48 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   if (cc_major != 10) return BAS_ERR_UNSUPPORTED;
 
   // ---- argument checks (those of bas_gemm, per call) and the list-wide sizes ----
-  int max_batch = 0, nb_max = 1, sel_nb_max = 0, n_sel = 0, n_gemm = 0, n_shaped = 0;
+  int max_batch = 0, nb_max = 1, sel_nb_max = 0, n_sel = 0, n_gemm = 0, n_shaped = 0, n_sharded = 0;
   for (int c = 0; c < n_calls; ++c) {
     const bas_list_call& a = calls[c];
     if (a.op == BAS_LIST_SELECT) {
       // a selection entry: X, its shape, how many blocks to keep, what it waits for - and nothing else
       if (a.x_dev == nullptr || a.batch <= 0 || a.k < kBlockK || (a.k % kBlockK) != 0 || a.ldx < a.k) return BAS_ERR_INVALID_ARGUMENT;
       if (a.batch > BAS_MAX_BATCH || a.k / kBlockK > BAS_LIST_MAX_BLOCKS) return BAS_ERR_UNSUPPORTED;
-      if (a.k_host < 0 || a.k_host > a.k / kBlockK) return BAS_ERR_INVALID_ARGUMENT;
+      const bool sharded = (a.shape_flags & BAS_LIST_SELECT_SHARDED) != 0;
+      if ((a.shape_flags & ~BAS_LIST_SELECT_SHARDED) != 0) return BAS_ERR_INVALID_ARGUMENT;
+      if (sharded) {
+        // X is this rank's K-shard: blocks mask_block0 .. of the n_host blocks of the whole input
+        if (tp == nullptr || a.n_host <= 0 || a.n_host > kTpSelBlocks || a.mask_block0 < 0 ||
+            a.mask_block0 + a.k / kBlockK > a.n_host || a.k_host < 0 || a.k_host > a.n_host)
+          return BAS_ERR_INVALID_ARGUMENT;
+        // its scores use the one region of the exchange area: every rank must have finished with the entry before
+        // (i.e. the row-parallel call that ran with that entry's mask must be complete) - this entry has to
+        // depend, directly or through other calls, on the last row-parallel call before it, which must lie
+        // behind the previous sharded entry
+        int prev_entry = -1, prev_row = -1;
+        for (int q = c - 1; q >= 0; --q) {
+          if (prev_row < 0 && calls[q].op == BAS_LIST_GEMM && calls[q].row_parallel != 0) prev_row = q;
+          if (calls[q].op == BAS_LIST_SELECT && (calls[q].shape_flags & BAS_LIST_SELECT_SHARDED) != 0) {
+            prev_entry = q;
+            break;
+          }
+        }
+        if (prev_entry >= 0) {
+          if (prev_row < prev_entry) return BAS_ERR_INVALID_ARGUMENT;
+          int d = a.depends_on;
+          while (d > prev_row) d = calls[d].depends_on;
+          if (d != prev_row) return BAS_ERR_INVALID_ARGUMENT;
+        }
+        ++n_sharded;
+        if (a.n_host > sel_nb_max) sel_nb_max = a.n_host;
+      } else if (a.n_host != 0 || a.mask_block0 != 0 || a.k_host < 0 || a.k_host > a.k / kBlockK) {
+        return BAS_ERR_INVALID_ARGUMENT;
+      }
       if (a.score_kind != BAS_SCORE_NORM && a.score_kind != BAS_SCORE_ENERGY) return BAS_ERR_INVALID_ARGUMENT;
       if (!list_aligned16(a.x_dev) || (a.ldx & 7) != 0) return BAS_ERR_INVALID_ARGUMENT;
       if (a.depends_on < -1 || a.depends_on >= c || a.row_parallel != 0 || a.mask_entry != 0) return BAS_ERR_INVALID_ARGUMENT;
       if (a.packed_dev != nullptr || a.y_dev != nullptr || a.ids_dev != nullptr || a.count_dev != nullptr ||
-          a.bitmap_dev != nullptr || a.ids_out_dev != nullptr || a.n != 0)
+          a.bitmap_dev != nullptr || a.ids_out_dev != nullptr || a.n_ids_dev != nullptr || a.n != 0)
         return BAS_ERR_INVALID_ARGUMENT;
       if (a.batch > max_batch) max_batch = a.batch;
       if (a.k / kBlockK > sel_nb_max) sel_nb_max = a.k / kBlockK;
@@ -1339,7 +1469,13 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
       if (en < 0 || en >= c || calls[en].op != BAS_LIST_SELECT) return BAS_ERR_INVALID_ARGUMENT;
       if (a.ids_dev != nullptr || a.count_dev != nullptr || a.bitmap_dev != nullptr) return BAS_ERR_INVALID_ARGUMENT;
       if (calls[en].depends_on != a.depends_on || calls[en].batch != a.batch || (a.k % kBlockK) != 0) return BAS_ERR_INVALID_ARGUMENT;
-      if (a.mask_block0 < 0 || a.mask_block0 + nb > calls[en].k / kBlockK) return BAS_ERR_INVALID_ARGUMENT;
+      if ((calls[en].shape_flags & BAS_LIST_SELECT_SHARDED) != 0) {
+        // the entry saw this rank's K-shard only: the call is the row-parallel one over that very shard
+        if (a.row_parallel == 0 || a.mask_block0 != calls[en].mask_block0 || nb != calls[en].k / kBlockK || a.ids_out_dev != nullptr)
+          return BAS_ERR_INVALID_ARGUMENT;
+      } else if (a.mask_block0 < 0 || a.mask_block0 + nb > calls[en].k / kBlockK) {
+        return BAS_ERR_INVALID_ARGUMENT;
+      }
     } else {
       if (a.mask_block0 != 0 || a.ids_out_dev != nullptr) return BAS_ERR_INVALID_ARGUMENT;
       if (a.bitmap_dev == nullptr && a.ids_dev == nullptr && a.k_host > 0) return BAS_ERR_INVALID_ARGUMENT;
@@ -1390,7 +1526,7 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   // ---- per call: the clusters that take part, and the widest column tile of the list ----
   const int min_units = ((flags >> 24) & 0x3f) != 0 ? ((flags >> 24) & 0x3f) : 8;   // tuning knob
   std::vector<ListCallDev> host((size_t)n_calls);
-  int off = 0, tw_max = 8, n_tp = 0, sel_seen = 0;
+  int off = 0, tw_max = 8, n_tp = 0, sel_seen = 0, sharded_seen = 0;
   for (int c = 0; c < n_calls; ++c) {
     const bas_list_call& a = calls[c];
     ListCallDev& d = host[(size_t)c];
@@ -1412,6 +1548,12 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
       d.n = 0;
       d.tp_index = -1;
       d.dep = a.depends_on;
+      if ((a.shape_flags & BAS_LIST_SELECT_SHARDED) != 0) {
+        d.range_off |= kCallSharded;
+        d.w_rows = a.mask_block0;         // first block of this rank's shard in the whole input
+        d.out_compact = a.n_host;         // blocks of the whole input
+        d.tp_index = sharded_seen++;      // the entry's number among the run's sharded entries
+      }
       continue;
     }
     const bool by_block = a.n_ids_dev != nullptr, x_compact = (a.shape_flags & BAS_LIST_X_COMPACT) != 0;
@@ -1438,7 +1580,8 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
       const ListCallDev& en = host[(size_t)(a.mask_entry - 1)];
       d.k_host = -a.mask_entry;                // = -(entry + 1)
       d.ids = en.ids;                          // the entry's score array (still its number)
-      d.count_dev = (const int32_t*)(uintptr_t)(unsigned long long)(unsigned int)en.nb;
+      d.count_dev = (const int32_t*)(uintptr_t)(unsigned long long)(unsigned int)
+                    ((en.range_off & kCallSharded) != 0 ? en.out_compact : en.nb);
       d.bitmap = (const uint8_t*)(uintptr_t)(unsigned long long)(unsigned int)a.mask_block0;
       d.ids_out = a.ids_out_dev;
     }
@@ -1447,6 +1590,8 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
     d.units = units;
     d.ranges = ranges;
     d.range_off = ((ranges < n_clusters) ? off : 0) | (by_block ? kCall2d : 0) | (x_compact ? kCallXCompact : 0);
+    if (a.mask_entry != 0 && (host[(size_t)(a.mask_entry - 1)].range_off & kCallSharded) != 0)
+      d.range_off |= kCallSharded;        // the entry saw a K-shard: this call has the verdicts of its own blocks only
     if (ranges < n_clusters) off = (off + ranges) % n_clusters;
     d.n_ids = a.n_ids_dev;
     d.w_rows = padded_cols(a.n);
@@ -1565,12 +1710,14 @@ static int list_create_impl(bas_list** out, const bas_list_call* calls, int n_ca
   p.wait_cycles = wait_cycles_now();
   p.tp = TpExchange{};
   p.n_tp_calls = n_tp;
+  p.n_sharded = n_sharded;
   if (tp != nullptr && n_tp > 0) {
     p.tp.world = tp->world;
     p.tp.rank = tp->rank;
     p.tp.ldp = tp->npad;
     p.tp.src_words = (long long)tp->max_batch * tp->npad;
     p.tp.own = tp->area[tp->rank];
+    p.tp.sel_words = (long long)((tp->bytes - kTpSelBytes) / 8);
     for (int q = 0; q < tp->world; ++q) p.tp.area[q] = tp->area[q];
   }
 #ifdef BAS_TRACE
