@@ -251,10 +251,10 @@ BAS_API int bas_select_gemm(const void* x_dev, int64_t ldx, const void* packed_d
  * bas_select_topk as part of the launch: x_dev / ldx / batch / k (a multiple of 64) describe X, k_host is the
  * number of blocks to keep, score_kind the score, depends_on the call that writes X; every other field is
  * zero.  Its CTAs score the blocks with the arithmetic of bas_select_topk (same bits) as soon as X is
- * complete.  A contraction whose mask_entry names that entry (same X: same batch, same depends_on) ranks the
- * scores at its call boundary - (score descending, id ascending), NaN first - and runs with the kept blocks in
- * ascending order, exactly as if bas_select_topk's list had been passed; its weights cannot be fetched before
- * the mask exists, so such a call costs one more hop than a call whose mask was known before the launch.
+ * complete and rank them - (score descending, id ascending), NaN first.  A contraction whose mask_entry names
+ * that entry (same X: same batch, same depends_on) picks the verdicts up at its call boundary and runs with the
+ * kept blocks in ascending order, exactly as if bas_select_topk's list had been passed; its weights cannot be
+ * fetched before the mask exists, so such a call costs more than a call whose mask was known before the launch.
  * Several calls may use one entry (q, k and v; gate and up).  Top-k only; one CTA per column range only.
  *
  * A SELECT entry over a K-sharded activation (bas_list_create_tp; shape_flags = BAS_LIST_SELECT_SHARDED): x_dev
@@ -304,12 +304,13 @@ typedef struct bas_list_call {
   int32_t row_parallel;   /* bas_list_create_tp only: 1 = x / packed are this rank's K-shard, y receives the sum over the ranks */
   int32_t op;             /* BAS_LIST_GEMM (0) or BAS_LIST_SELECT */
   int32_t mask_entry;     /* GEMM: 1 + index of the earlier BAS_LIST_SELECT entry whose mask it runs with; 0: ids / count / byte map above */
-  int32_t mask_block0;    /* GEMM with mask_entry: the block of that mask which is block 0 of this call (a K-shard); else 0 */
+  int32_t mask_block0;    /* GEMM with mask_entry: the block of that mask which is block 0 of this call (a K-shard); else 0.
+                             SELECT with BAS_LIST_SELECT_SHARDED: the first block of this rank's shard in the whole input */
   int32_t score_kind;     /* SELECT: BAS_SCORE_NORM or BAS_SCORE_ENERGY */
   int32_t* ids_out_dev;   /* GEMM with mask_entry, optional: receives the kept ids of the whole mask, ascending (k_host of the entry) */
   const int32_t* n_ids_dev; /* GEMM, optional: only these 64-column output blocks are computed (see below); n_host of them */
-  int32_t n_host;
-  int32_t shape_flags;    /* BAS_LIST_OUT_COMPACT | BAS_LIST_X_COMPACT */
+  int32_t n_host;         /* (SELECT with BAS_LIST_SELECT_SHARDED: the blocks of the whole input) */
+  int32_t shape_flags;    /* GEMM: BAS_LIST_OUT_COMPACT | BAS_LIST_X_COMPACT; SELECT: BAS_LIST_SELECT_SHARDED */
 } bas_list_call;
 typedef struct bas_list bas_list;
 BAS_API int bas_list_create(bas_list** out, const bas_list_call* calls, int n_calls, int flags);
