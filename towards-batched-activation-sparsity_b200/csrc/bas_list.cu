@@ -563,39 +563,39 @@ __global__ void __launch_bounds__(kLThreads, 1) umma_list_kernel(const __grid_co
                   const long long t_start = clock64();
                   // scores of blocks i0 + lane + 32 t; sharded: polled (bounded) until they carry the entry's stamp
                   auto load_scores = [&](int i0, double (&v8)[8]) -> bool {
-                    if (!sharded) {
+                    if constexpr (TP) {
+                      while (sharded) {      // leaves by a return
+                        unsigned long long hi8[8], lo8[8];
+                        bool valid = true;
 #pragma unroll
-                      for (int t = 0; t < 8; ++t) v8[t] = (i0 + lane + 32 * t < nb_all) ? __ldcg(sc_rep + i0 + lane + 32 * t) : 0.0;
-                      return true;
-                    }
-                    for (;;) {
-                      unsigned long long hi8[8], lo8[8];
-                      bool valid = true;
-#pragma unroll
-                      for (int t = 0; t < 8; ++t) {
-                        const int i = i0 + lane + 32 * t;
-                        hi8[t] = lo8[t] = (unsigned long long)stamp << 32;
-                        if (i < nb_all) {
-                          hi8[t] = ld_relaxed_sys_u64(words + 2 * (size_t)i);
-                          lo8[t] = ld_relaxed_sys_u64(words + 2 * (size_t)i + 1);
+                        for (int t = 0; t < 8; ++t) {
+                          const int i = i0 + lane + 32 * t;
+                          hi8[t] = lo8[t] = (unsigned long long)stamp << 32;
+                          if (i < nb_all) {
+                            hi8[t] = ld_relaxed_sys_u64(words + 2 * (size_t)i);
+                            lo8[t] = ld_relaxed_sys_u64(words + 2 * (size_t)i + 1);
+                          }
+                          valid = valid && (unsigned int)(hi8[t] >> 32) == stamp && (unsigned int)(lo8[t] >> 32) == stamp;
                         }
-                        valid = valid && (unsigned int)(hi8[t] >> 32) == stamp && (unsigned int)(lo8[t] >> 32) == stamp;
-                      }
-                      if (__all_sync(0xffffffffu, valid)) {
+                        if (__all_sync(0xffffffffu, valid)) {
 #pragma unroll
-                        for (int t = 0; t < 8; ++t)
-                          v8[t] = __longlong_as_double((long long)((hi8[t] << 32) | (lo8[t] & 0xffffffffull)));
-                        return true;
-                      }
-                      bool give_up = false;
-                      if (lane == 0) {
-                        while (ndef > 0 && ok && flush_one(false, false)) {
+                          for (int t = 0; t < 8; ++t)
+                            v8[t] = __longlong_as_double((long long)((hi8[t] << 32) | (lo8[t] & 0xffffffffull)));
+                          return true;
                         }
-                        give_up = !ok || *abort_flag != 0 || clock64() - t_start > limit;
+                        bool give_up = false;
+                        if (lane == 0) {
+                          while (ndef > 0 && ok && flush_one(false, false)) {
+                          }
+                          give_up = !ok || *abort_flag != 0 || clock64() - t_start > limit;
+                        }
+                        if (__shfl_sync(0xffffffffu, give_up ? 1 : 0, 0) != 0) return false;
+                        __nanosleep(40);
                       }
-                      if (__shfl_sync(0xffffffffu, give_up ? 1 : 0, 0) != 0) return false;
-                      __nanosleep(40);
                     }
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) v8[t] = (i0 + lane + 32 * t < nb_all) ? __ldcg(sc_rep + i0 + lane + 32 * t) : 0.0;
+                    return true;
                   };
                   for (int j = range + ranges * warp; j < nb_e && ok; j += ranges * P) {
                     const int jg = g0 + j;                       // the block's number in the whole input
