@@ -150,9 +150,11 @@ def test_golden_selections_of_the_reference(dev, golden):
     assert checked >= 22
 
 
-def test_chain_with_fresh_masks(dev):
+@pytest.mark.parametrize("max_ctas,pairs", [(0, 0), (3, 0), (8, 2), (50, 3)])
+def test_chain_with_fresh_masks(dev, max_ctas, pairs):
     """x0 -> [select, W0] -> x1 -> [select, W1] -> x2 -> [select, W2]: every mask is computed inside the launch
-    from an activation that the launch itself produced."""
+    from an activation that the launch itself produced.  Also on grids far smaller than the GPU (every CTA then
+    scores many blocks and walks many column ranges) and with fewer copy warps."""
     ops = _ops()
     from bas import abi
     batch, dims, keeps = 16, [4096, 2752, 1024, 4096], [23, 16, 6]
@@ -168,7 +170,7 @@ def test_chain_with_fresh_masks(dev):
         calls.append({"select": bufs[i], "n_keep": keeps[i], "score_kind": abi.SCORE_NORM, "depends_on": dep})
         calls.append({"x": bufs[i], "packed": ops.pack_weight(w), "out": bufs[i + 1], "mask_from": 2 * i,
                       "ids_out": idbufs[i], "depends_on": dep})
-    lst = ops.GemmList(calls)
+    lst = ops.GemmList(calls, max_ctas=max_ctas, pairs=pairs)
     g = None
     for run in range(4):
         for b in bufs[1:]:
