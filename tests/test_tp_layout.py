@@ -66,6 +66,21 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str) -> None:
     t = torch.from_numpy(y_row.astype(np.float64))
     dist.all_reduce(t)
     np.testing.assert_allclose(t.numpy(), full.astype(np.float64), rtol=1e-6, atol=1e-6)
+    # selection from a K-SHARDED input (what the list kernel's sharded entries do over the exchange area): every
+    # rank scores the blocks it holds, the scores are gathered, every rank ranks ALL of them and keeps its own
+    # part - together the ranks hold exactly the unsharded top-k, and the row-parallel sum is the unsharded product
+    mine = O.block_scores(x[:, 64 * b0:64 * b1], O.SCORE_NORM)
+    assert np.array_equal(mine, O.block_scores(x, O.SCORE_NORM)[b0:b1])        # a block's score needs its own channels only
+    shards = [None] * world
+    dist.all_gather_object(shards, mine.tolist())
+    everyone = np.concatenate([np.asarray(sc, dtype=np.float64) for sc in shards])
+    global_ids = O.topk_ids(everyone, len(ids))
+    assert np.array_equal(global_ids, ids)
+    local2 = global_ids[(global_ids >= b0) & (global_ids < b1)] - b0
+    assert np.array_equal(local2, local)
+    kept = [None] * world
+    dist.all_gather_object(kept, (local2 + b0).tolist())
+    assert sorted(j for part in kept for j in part) == ids.tolist()
     Path(out_dir, f"ok{rank}").write_text("ok")
     dist.destroy_process_group()
 
