@@ -1106,6 +1106,26 @@ def run_profile_list(steps: int) -> None:
           f"{lst.info()}, status {lst.read_status()}")
 
 
+def run_profile_stack(layers: int) -> None:
+    """Three eager launches of `layers` layers of the decode stack (B = 16, q+k+v and gate+up stacked) as ONE list
+    with the model's dependencies and every mask computed inside the launch (selection entries): the case that
+    profiler captures of the extended list kernel are taken on.  Four layers hold 0.8 GB of weights."""
+    import torch
+
+    from bas import tp
+
+    dev = torch.device("cuda", 0)
+    stack = tp.DecodeLinearStack(layers, 16, 0.638, dev, 1, 0, seed=5, fuse_shared_inputs=True)
+    lst = stack.make_list(dependencies=True, select=True)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        lst.run()
+    torch.cuda.synchronize()
+    par = stack.parity_check_outputs(layers=1)
+    print(f"profile stack: 3 launches of {layers} layers ({lst.n_calls} entries, {stack.active_bytes} active weight bytes each), "
+          f"{lst.info()}, status {lst.read_status()}, parity {par}")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1122,6 +1142,9 @@ def main() -> None:
                     help="kernel family of the profile case: 0 default, 1 CUDA-core kernel (batch <= 8), 2 tcgen05")
     ap.add_argument("--profile-list", type=int, default=0, metavar="STEPS",
                     help="run only three eager list launches of STEPS benchmark steps (for profiler captures) and exit")
+    ap.add_argument("--profile-stack", type=int, default=0, metavar="LAYERS",
+                    help="run only three eager launches of LAYERS layers of the decode stack as one list with selection "
+                         "entries (for profiler captures) and exit")
     ap.add_argument("--profile-pipelined", action="store_true",
                     help="profile case: masks fixed ahead, calls declare ids and X stable (the benchmark's chains)")
     args = ap.parse_args()
@@ -1133,6 +1156,8 @@ def main() -> None:
     os.dup2(2, 1)
     if args.profile_list:
         run_profile_list(args.profile_list)
+    elif args.profile_stack:
+        run_profile_stack(args.profile_stack)
     elif args.profile_case:
         run_profile_case(args.profile_case, args.profile_family, args.profile_pipelined)
     elif args.impl == "reference":
